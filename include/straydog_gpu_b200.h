@@ -1,0 +1,124 @@
+/* C ABI of the B200 (sm_100a) attention library: libstraydog_gpu_b200.so.
+ *
+ * The sd_* entries keep the names, argument meaning and error behaviour of the reference's
+ * gpu/straydog_gpu.h for the attention path, so that the engine's existing FFI binds them
+ * unchanged; each declaration cites the reference declaration it replaces. The sdx_* entries are
+ * additions the reference has no counterpart for (several sequences in one call, plans that keep
+ * the host work out of the step); they collide with nothing in the reference.
+ *
+ * Conventions (gpu/straydog_gpu.h:1-5): an int result < 0 or a null pointer is a failure which
+ * sd_error() then describes for the calling thread; other int results are 0 or a query's answer.
+ * Handles are opaque. Nothing throws across this boundary. Every device pointer passed to an op
+ * must lie inside an allocation this library made for the same handle (sd_allocate, sd_upload,
+ * sd_buffer): every op checks. Work is queued on the handle's stream; reads synchronise.
+ * No entry falls back to the CPU: without a B200-class GPU sd_create fails.
+ */
+#ifndef STRAYDOG_GPU_B200_H
+#define STRAYDOG_GPU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- errors, devices, memory ---- */
+/* gpu/straydog_gpu.h:17 */
+const char* sd_error(void);
+/* gpu/straydog_gpu.h:18 */
+int sd_device_count(void);
+/* gpu/straydog_gpu.h:33-34. budget: bytes this handle may allocate, at most the free memory. */
+void* sd_create(int ordinal, uint64_t budget);
+void sd_destroy(void* handle);
+/* gpu/straydog_gpu.h:35 */
+int sd_memory(void* handle, uint64_t* used, uint64_t* budget);
+/* gpu/straydog_gpu.h:42,47,57,63,65-67 */
+void* sd_upload(void* handle, const void* data, uint64_t bytes);
+void* sd_allocate(void* handle, uint64_t bytes);
+int sd_write(void* handle, void* pointer, const void* data, uint64_t bytes);
+int sd_release(void* handle, void* pointer);
+int sd_allocation_bytes(void* handle, const void* pointer, uint64_t* bytes);
+int sd_zero(void* handle, void* pointer);
+int sd_download(void* handle, void* pointer, void* output, uint64_t bytes);
+/* gpu/straydog_gpu.h:157-159: a zeroed buffer; byte-range writes and reads. */
+void* sd_buffer(void* handle, uint64_t bytes);
+int sd_buffer_write(void* handle, void* buffer, uint64_t offset, const void* data, uint64_t bytes);
+int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* output, uint64_t bytes);
+
+/* ---- K/V format and staging ---- */
+/* gpu/straydog_gpu.h:113. row: 272 (Q8_0) or 512 (FP16). The attention kernels of this build read Q8_0 rows. */
+int sd_kv_format(void* handle, uint32_t row);
+/* gpu/straydog_gpu.h:114. The VRAM stage of host-resident K/V. With K/V resident in HBM the stage is
+   registered and validated but never needed. */
+int sd_kv_stage(void* handle, void* pointer, uint64_t rows);
+
+/* ---- Qwen3.8-style grouped-query attention over Q8_0 K/V ---- */
+/* gpu/straydog_gpu.h:528. Host pointers. The reference's own shapes: 24 query / 2 K/V heads of 256,
+   scale 1/16, `selected` <= 2052 key positions per step given as floats, then one count per step.
+   input: [steps][24][256] q | [steps][2][256] k | [steps][2][256] v | [steps][selected] | [steps], all F32.
+   Writes rows base..base+steps-1 of `state` (quantised to Q8_0), then attends. output [steps][24][256]. */
+int sd_attention_sequence(void* handle, void* state, uint64_t context, uint64_t base, uint64_t steps, uint64_t selected,
+                          const float* input, uint64_t input_count, float* output, uint64_t output_count);
+/* gpu/straydog_gpu.h:453. Generic dense causal GQA over F32 keys/values [context][kv_heads][dim];
+   device pointers. scratch >= rows * heads * 64 * (dim + 2) * 4 bytes always suffices. */
+int sd_op_attention(void* handle, const float* q, const float* keys, const float* values, uint64_t context,
+                    const int32_t* positions, uint64_t rows, uint64_t heads, uint64_t kv_heads, uint64_t dim, float scale,
+                    const float* gate, float* scratch, uint64_t scratch_bytes, float* out);
+
+/* ---- DeepSeek-V4.1-style latent sparse attention ---- */
+/* gpu/straydog_gpu.h:385-389 */
+int sd_attention_turns_reserve(void* handle, uint64_t rows, uint64_t rope_dims);
+int sd_attention_turns_arm(void* handle, uint64_t rows);
+/* gpu/straydog_gpu.h:398. `compressed` may carry the BF16 tag in bit 0 of the pointer. */
+int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                           uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                           uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
+                           uint64_t rope_dims, const float* frequencies, float* scratch, uint64_t scratch_bytes, float* out);
+/* gpu/straydog_gpu.h:409 */
+int sd_op_top_k(void* handle, const float* scores, uint64_t rows, uint64_t groups, uint64_t k, int32_t* out);
+/* gpu/straydog_gpu.h:459 */
+int sd_op_to_bf16(void* handle, const float* x, uint64_t count, void* out);
+
+/* ---- additions (no counterpart in the reference) ---- */
+/* Waits for everything queued on the handle's stream. */
+int sdx_synchronize(void* handle);
+/* The handle's CUDA stream (a cudaStream_t), for timing with events on the launching stream. */
+void* sdx_stream(void* handle);
+/* Kernels launched through the handle so far. */
+uint64_t sdx_launch_count(void* handle);
+
+/* Appends `steps` tokens' keys and values ([steps][kv_heads][256] F32, device) to a Q8_0 state at rows
+   base..: the reference's write_attention_kv (gpu/kernels.cpp:79-98) for any number of K/V heads. */
+int sdx_kv_write(void* handle, void* state, uint64_t context, uint64_t kv_heads, uint64_t base, uint64_t steps,
+                 const float* keys, const float* values);
+/* `count` Q8_0 rows (272 bytes each, device) as F32 [count][256]: float(int8) * float(block scale). */
+int sdx_kv_decode_rows(void* handle, const void* rows, uint64_t count, float* out);
+
+/* Ragged batch of one-token decodes: sequence s attends rows 0..lengths[s]-1 of states[s] (a Q8_0
+   state of contexts[s] positions, 2 * kv_heads planes). states/contexts/lengths are HOST arrays;
+   q ([sequences][heads][256] FP16) and out ([sequences][heads][256] F32) are device pointers.
+   heads / kv_heads <= 8. */
+int sdx_qsa_decode(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
+                   uint64_t sequences, uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out);
+/* The same in two steps: the plan holds the batch's work list on the device, so that a run is
+   kernel launches only (no host work, no allocation: safe inside a captured graph). */
+void* sdx_qsa_plan(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
+                   uint64_t sequences, uint64_t heads, uint64_t kv_heads);
+int sdx_qsa_plan_run(void* handle, void* plan, float scale, const void* q, float* out);
+int sdx_qsa_plan_info(void* plan, uint64_t* kv_bytes, uint64_t* pieces, uint64_t* ctas, uint64_t* virtual_warps);
+int sdx_qsa_plan_release(void* handle, void* plan);
+/* 1 when a bounded wait inside a decode kernel gave up since the last call (cleared by the call), 0 if none. */
+int sdx_decode_status(void* handle);
+
+/* One decode step of a batch from HOST buffers (the batched twin of sd_attention_sequence): for
+   sequence s the new token's keys/values (k, v: [sequences][kv_heads][256] F32, host) are written
+   to row bases[s] of states[s], then its query (q: [sequences][heads][256] FP16, host) attends rows
+   0..bases[s]; out [sequences][heads][256] F32, host. Copies both ways are inside the call. */
+int sdx_attention_batch(void* handle, void* const* states, const uint64_t* contexts, const uint64_t* bases, uint64_t sequences,
+                        uint64_t heads, uint64_t kv_heads, float scale, const void* q, const float* k, const float* v, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,158 @@
+"""ctypes binding of the CPU oracle (oracle.cpp). TEST INFRASTRUCTURE ONLY.
+
+Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / reference legs import this
+package; the product (straydog_b200) never does.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import build as _build
+
+_lib = C.CDLL(_build.build())
+
+_u64, _f32, _i32 = C.c_uint64, C.c_float, C.c_int
+_p = C.c_void_p
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(_p)
+
+
+def _sig(name, args, res=None):
+    f = getattr(_lib, name)
+    f.argtypes, f.restype = args, res
+    return f
+
+
+_sig("orc_f32_to_f16", [_f32], C.c_uint16)
+_sig("orc_f16_to_f32", [C.c_uint16], _f32)
+_sig("orc_q8_encode_rows", [_p, _u64, _p])
+_sig("orc_q8_decode_rows", [_p, _u64, _p])
+_sig("orc_kv_write", [_p, _u64, _u64, _u64, _u64, _p, _p])
+_sig("orc_attention_sequence", [_p, _u64, _u64, _u64, _u64, _u64, _u64, _p, _f32, _p])
+_sig("orc_gqa_decode_q8", [_p, _u64, _u64, _u64, _u64, _p, _f32, _i32, _p])
+_sig("orc_gqa_prompt_q8", [_p, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _p, _f32, _i32, _p])
+_sig("orc_op_attention", [_p, _p, _p, _u64, _p, _u64, _u64, _u64, _u64, _f32, _p, _p, _p, _p])
+_sig("orc_sparse_attention", [_p, _p, _u64, _p, _u64, _p, _i32, _p, _u64, _p, _u64, _u64, _u64, _f32, _u64, _p, _i32, _p])
+_sig("orc_top_k", [_p, _u64, _u64, _u64, _p])
+_sig("orc_to_bf16", [_p, _u64, _p])
+_sig("orc_threads", [], _i32)
+
+ROW_Q8 = 272
+DIM = 256
+
+
+def threads() -> int:
+    return int(_lib.orc_threads())
+
+
+def f32_to_f16(x: float) -> int:
+    return int(_lib.orc_f32_to_f16(x))
+
+
+def f16_to_f32(h: int) -> float:
+    return float(_lib.orc_f16_to_f32(h))
+
+
+def q8_encode_rows(values: np.ndarray) -> np.ndarray:
+    """[rows, 256] F32 -> [rows, 272] uint8 (Q8_0 rows)."""
+    values = np.ascontiguousarray(values, np.float32).reshape(-1, DIM)
+    out = np.empty((values.shape[0], ROW_Q8), np.uint8)
+    _lib.orc_q8_encode_rows(_ptr(values), values.shape[0], _ptr(out))
+    return out
+
+
+def q8_decode_rows(packed: np.ndarray) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, np.uint8).reshape(-1, ROW_Q8)
+    out = np.empty((packed.shape[0], DIM), np.float32)
+    _lib.orc_q8_decode_rows(_ptr(packed), packed.shape[0], _ptr(out))
+    return out
+
+
+def kv_write(state: np.ndarray, context: int, kv_heads: int, base: int, keys: np.ndarray, values: np.ndarray) -> None:
+    """state: uint8 [2*kv_heads, context, 272], written in place. keys/values [steps, kv_heads, 256]."""
+    keys = np.ascontiguousarray(keys, np.float32)
+    values = np.ascontiguousarray(values, np.float32)
+    assert state.dtype == np.uint8 and state.flags.c_contiguous and state.size == 2 * kv_heads * context * ROW_Q8
+    _lib.orc_kv_write(_ptr(state), context, kv_heads, base, keys.shape[0], _ptr(keys), _ptr(values))
+
+
+def attention_sequence(state, context, heads, kv_heads, base, steps, selected, packed_input, scale=0.0625):
+    packed_input = np.ascontiguousarray(packed_input, np.float32)
+    assert packed_input.size == steps * (heads * DIM + 2 * kv_heads * DIM + selected + 1)
+    out = np.empty((steps, heads, DIM), np.float32)
+    _lib.orc_attention_sequence(_ptr(state), context, heads, kv_heads, base, steps, selected, _ptr(packed_input), scale, _ptr(out))
+    return out
+
+
+def gqa_decode_q8(state, context, length, heads, kv_heads, q_f16, scale, f64=False):
+    """q_f16: [heads, 256] float16."""
+    q = np.ascontiguousarray(q_f16, np.float16)
+    out = np.empty((heads, DIM), np.float32)
+    _lib.orc_gqa_decode_q8(_ptr(state), context, length, heads, kv_heads, _ptr(q), scale, int(f64), _ptr(out))
+    return out
+
+
+def gqa_prompt_q8(state, context, first, heads, kv_heads, q_f16, scale, rows=None, f64=False):
+    """q_f16: [rows, heads, 256] float16; rows: iterable of row numbers to compute (default all). Others stay NaN."""
+    q = np.ascontiguousarray(q_f16, np.float16)
+    n = q.shape[0]
+    out = np.full((n, heads, DIM), np.nan, np.float32)
+    if rows is None:
+        _lib.orc_gqa_prompt_q8(_ptr(state), context, first, n, 0, n, 1, heads, kv_heads, _ptr(q), scale, int(f64), _ptr(out))
+    else:
+        for r in rows:
+            _lib.orc_gqa_prompt_q8(_ptr(state), context, first, n, r, r + 1, 1, heads, kv_heads, _ptr(q), scale, int(f64), _ptr(out))
+    return out
+
+
+def op_attention(q, keys, values, context, positions, rows, heads, kv_heads, dim, scale, gate=None, want64=False):
+    q = np.ascontiguousarray(q, np.float32)
+    keys = np.ascontiguousarray(keys, np.float32)
+    values = np.ascontiguousarray(values, np.float32)
+    positions = np.ascontiguousarray(positions, np.int32)
+    gate = None if gate is None else np.ascontiguousarray(gate, np.float32)
+    out = np.empty((rows, heads, dim), np.float32)
+    out64 = np.empty((rows, heads, dim), np.float64) if want64 else None
+    bound = np.empty((rows, heads, dim), np.float64) if want64 else None
+    _lib.orc_op_attention(_ptr(q), _ptr(keys), _ptr(values), context, _ptr(positions), rows, heads, kv_heads, dim, scale,
+                          _ptr(gate), _ptr(out), _ptr(out64), _ptr(bound))
+    return (out, out64, bound) if want64 else out
+
+
+def sparse_attention(q, raw, raw_rows, positions, window, compressed, selected, selections, sinks, rows, heads, dim, scale,
+                     rope_dims=0, frequencies=None, f64=False):
+    """compressed: float32 [n, dim] or uint16 (BF16 bits) [n, dim]."""
+    q = np.ascontiguousarray(q, np.float32)
+    raw = np.ascontiguousarray(raw, np.float32)
+    positions = np.ascontiguousarray(positions, np.int32)
+    sinks = np.ascontiguousarray(sinks, np.float32)
+    bf16 = compressed is not None and compressed.dtype == np.uint16
+    if compressed is not None:
+        compressed = np.ascontiguousarray(compressed)
+    selected = None if selected is None else np.ascontiguousarray(selected, np.int32)
+    frequencies = None if frequencies is None else np.ascontiguousarray(frequencies, np.float32)
+    out = np.empty((rows, heads, dim), np.float32)
+    _lib.orc_sparse_attention(_ptr(q), _ptr(raw), raw_rows, _ptr(positions), window, _ptr(compressed), int(bf16), _ptr(selected),
+                              selections, _ptr(sinks), rows, heads, dim, scale, rope_dims, _ptr(frequencies), int(f64), _ptr(out))
+    return out
+
+
+def top_k(scores, k):
+    scores = np.ascontiguousarray(scores, np.float32)
+    rows, groups = scores.shape
+    out = np.empty((rows, k), np.int32)
+    _lib.orc_top_k(_ptr(scores), rows, groups, k, _ptr(out))
+    return out
+
+
+def to_bf16(x):
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    _lib.orc_to_bf16(_ptr(x), x.size, _ptr(out))
+    return out
+
+
+def bf16_to_f32(h):
+    return (np.ascontiguousarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)

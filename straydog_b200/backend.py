@@ -1,0 +1,236 @@
+"""Host-side mirror of the reference engine's GPU wrapper for the attention path.
+
+The reference's Rust `Backend` (crates/straydog-engine/src/gpu.rs) and `Ops` (src/ops.rs:878-886,
+1158-1171, 1241-1244) wrap the sd_* C ABI; this module wraps the same entry points of
+libstraydog_gpu_b200.so with the same method names and argument meaning, so that parity tests read
+like the reference's own (tests/attention_gpu.rs, ds_state_bf16_gpu.rs, fused_gpu.rs). A failed call
+raises StraydogError carrying sd_error()'s text, as the Rust wrappers return Err(last_error()).
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+
+_L = None
+
+
+def lib():
+    global _L
+    if _L is None:
+        _L = _lib.load()
+    return _L
+
+
+class StraydogError(RuntimeError):
+    pass
+
+
+def _fail():
+    raise StraydogError(lib().sd_error().decode("utf-8", "replace"))
+
+
+def _check(result):
+    if result is None or (isinstance(result, int) and result < 0):
+        _fail()
+    return result
+
+
+def _host(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+class Buffer:
+    """A device allocation of the backend (zeroed at creation). base() is its device address."""
+
+    def __init__(self, backend, pointer, size):
+        self.backend, self.pointer, self.size = backend, pointer, size
+
+    def base(self):
+        return self.pointer
+
+    def at(self, byte_offset):
+        return self.pointer + byte_offset
+
+    def tagged_bf16(self):
+        """The pointer with the reference's BF16 tag in bit 0 (gpu/ops.hpp:1208-1210)."""
+        return self.pointer | 1
+
+
+class Backend:
+    def __init__(self, ordinal=0, budget=1 << 30):
+        self.handle = lib().sd_create(ordinal, budget)
+        if not self.handle:
+            _fail()
+        self.ordinal = ordinal
+
+    def close(self):
+        if self.handle:
+            lib().sd_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- memory ----
+    def buffer(self, size):
+        pointer = lib().sd_buffer(self.handle, size)
+        if not pointer:
+            _fail()
+        return Buffer(self, pointer, size)
+
+    def upload(self, array):
+        array = np.ascontiguousarray(array)
+        buffer = self.buffer(max(array.nbytes, 4))
+        self.write_buffer(buffer, 0, array)
+        return buffer
+
+    def allocate(self, size):
+        pointer = lib().sd_allocate(self.handle, size)
+        if not pointer:
+            _fail()
+        return Buffer(self, pointer, size)
+
+    def write_buffer(self, buffer, offset, array):
+        array = np.ascontiguousarray(array)
+        _check(lib().sd_buffer_write(self.handle, buffer.pointer, offset, _host(array), array.nbytes))
+
+    def read_buffer(self, buffer, offset, out):
+        assert out.flags.c_contiguous
+        _check(lib().sd_buffer_read(self.handle, buffer.pointer, offset, _host(out), out.nbytes))
+        return out
+
+    def read(self, buffer, dtype, shape, offset=0):
+        return self.read_buffer(buffer, offset, np.empty(shape, dtype))
+
+    def write(self, buffer, array):
+        array = np.ascontiguousarray(array)
+        _check(lib().sd_write(self.handle, buffer.pointer, _host(array), array.nbytes))
+
+    def download(self, buffer, out):
+        _check(lib().sd_download(self.handle, buffer.pointer, _host(out), out.nbytes))
+        return out
+
+    def zero(self, buffer):
+        _check(lib().sd_zero(self.handle, buffer.pointer))
+
+    def release(self, buffer):
+        _check(lib().sd_release(self.handle, buffer.pointer))
+        buffer.pointer = None
+
+    def memory(self):
+        used, budget = C.c_uint64(), C.c_uint64()
+        _check(lib().sd_memory(self.handle, C.byref(used), C.byref(budget)))
+        return used.value, budget.value
+
+    def synchronize(self):
+        _check(lib().sdx_synchronize(self.handle))
+
+    def stream(self):
+        return lib().sdx_stream(self.handle)
+
+    def launch_count(self):
+        return int(lib().sdx_launch_count(self.handle))
+
+    # ---- K/V ----
+    def kv_format(self, row):
+        _check(lib().sd_kv_format(self.handle, row))
+
+    def kv_stage(self, buffer, rows):
+        _check(lib().sd_kv_stage(self.handle, buffer.pointer, rows))
+
+    def kv_write(self, state, context, kv_heads, base, steps, keys, values):
+        _check(lib().sdx_kv_write(self.handle, state.pointer, context, kv_heads, base, steps, keys.pointer, values.pointer))
+
+    def kv_decode_rows(self, rows_pointer, count, out):
+        _check(lib().sdx_kv_decode_rows(self.handle, rows_pointer, count, out.pointer))
+
+    # ---- Qwen-style attention ----
+    def attention_sequence(self, state, context, base, steps, selected, packed_input):
+        """sd_attention_sequence: host floats in, host floats out ([steps, 24, 256])."""
+        packed_input = np.ascontiguousarray(packed_input, np.float32)
+        out = np.empty(steps * 24 * 256, np.float32)
+        _check(lib().sd_attention_sequence(self.handle, state.pointer, context, base, steps, selected, _host(packed_input),
+                                           packed_input.size, _host(out), out.size))
+        return out.reshape(steps, 24, 256)
+
+    def attention(self, q, keys, values, context, positions, rows, heads, kv_heads, dim, scale, gate, scratch, out):
+        """sd_op_attention over device pointers (ints); gate and scratch may be None."""
+        _check(lib().sd_op_attention(self.handle, q, keys, values, context, positions, rows, heads, kv_heads, dim, scale, gate,
+                                     scratch.pointer if scratch else None, scratch.size if scratch else 0, out))
+
+    def qsa_decode(self, states, contexts, lengths, heads, kv_heads, scale, q, out):
+        n = len(states)
+        ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])
+        ctx = (C.c_uint64 * n)(*contexts)
+        lens = (C.c_uint64 * n)(*lengths)
+        _check(lib().sdx_qsa_decode(self.handle, ptrs, ctx, lens, n, heads, kv_heads, scale, q, out))
+
+    def qsa_plan(self, states, contexts, lengths, heads, kv_heads):
+        n = len(states)
+        ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])
+        ctx = (C.c_uint64 * n)(*contexts)
+        lens = (C.c_uint64 * n)(*lengths)
+        plan = lib().sdx_qsa_plan(self.handle, ptrs, ctx, lens, n, heads, kv_heads)
+        if not plan:
+            _fail()
+        return plan
+
+    def qsa_plan_run(self, plan, scale, q, out):
+        _check(lib().sdx_qsa_plan_run(self.handle, plan, scale, q, out))
+
+    def qsa_plan_info(self, plan):
+        vals = [C.c_uint64() for _ in range(4)]
+        _check(lib().sdx_qsa_plan_info(plan, *[C.byref(v) for v in vals]))
+        return dict(zip(("kv_bytes", "pieces", "ctas", "virtual_warps"), [v.value for v in vals]))
+
+    def qsa_plan_release(self, plan):
+        _check(lib().sdx_qsa_plan_release(self.handle, plan))
+
+    def decode_status(self):
+        return _check(lib().sdx_decode_status(self.handle))
+
+    def attention_batch(self, states, contexts, bases, heads, kv_heads, scale, q_host, k_host, v_host, out_host):
+        n = len(states)
+        ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])
+        ctx = (C.c_uint64 * n)(*contexts)
+        bs = (C.c_uint64 * n)(*bases)
+        _check(lib().sdx_attention_batch(self.handle, ptrs, ctx, bs, n, heads, kv_heads, scale, _host(q_host), _host(k_host),
+                                         _host(v_host), _host(out_host)))
+        return out_host
+
+    # ---- DeepSeek-style latent attention ----
+    def attention_turns_reserve(self, rows, rope_dims):
+        _check(lib().sd_attention_turns_reserve(self.handle, rows, rope_dims))
+
+    def attention_turns_arm(self, rows):
+        _check(lib().sd_attention_turns_arm(self.handle, rows))
+
+    def sparse_attention(self, q, raw, raw_rows, positions, window, compressed, selected, sinks, rows, heads, dim, scale, rope,
+                         scratch, out):
+        """compressed: (pointer, rows) or None; selected: (pointer, selections) or None; rope: (rope_dims, frequencies pointer) or None."""
+        c_ptr, c_rows = compressed if compressed else (None, 0)
+        s_ptr, selections = selected if selected else (None, 0)
+        rope_dims, freq = rope if rope else (0, None)
+        _check(lib().sd_op_sparse_attention(self.handle, q, raw, raw_rows, positions, window, c_ptr, c_rows, s_ptr, selections, sinks,
+                                            rows, heads, dim, scale, rope_dims, freq, scratch.pointer if scratch else None,
+                                            scratch.size if scratch else 0, out))
+
+    def top_k(self, scores, rows, groups, k, out):
+        _check(lib().sd_op_top_k(self.handle, scores, rows, groups, k, out))
+
+    def to_bf16(self, x, count, out):
+        _check(lib().sd_op_to_bf16(self.handle, x, count, out))
+
+
+def device_count():
+    return _check(lib().sd_device_count())

@@ -1,0 +1,172 @@
+// Shared host-side state and device-side primitives of the B200 attention library.
+// One Device per sd_create handle: its stream, its allocation map (every op range-checks its
+// pointers against it, as the reference's op_span does: gpu/ops.hpp:8-26) and lazily made scratch.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <initializer_list>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace sdb {
+
+constexpr unsigned kv_row_f16 = 512, kv_row_q8 = 272;   // gpu/core.hpp:403
+constexpr size_t max_batch = 256;                        // gpu/core.hpp:178
+constexpr size_t allocation_tail = 64;                   // gpu/core.hpp:211
+
+extern thread_local std::string last_error;
+
+inline void check_at(cudaError_t error, const char* file, int line) {
+    if (error == cudaSuccess) return;
+    const std::string path(file);
+    const char* text = cudaGetErrorString(error);
+    throw std::runtime_error(std::string(text ? text : "GPU error") + " (" + path.substr(path.find_last_of("/\\") + 1) + ":" +
+                             std::to_string(line) + ", code " + std::to_string(int(error)) + ")");
+}
+#define SDB_CHECK(error) ::sdb::check_at((error), __FILE__, __LINE__)
+
+struct DecodePlan;
+
+struct Device {
+    int ordinal = 0;
+    int sms = 0;
+    cudaStream_t stream = nullptr;
+    uint64_t budget = 0, used = 0;
+    unsigned kv_row = kv_row_q8;
+    std::mutex mutex;
+    std::map<const uint8_t*, size_t> allocations;   // base -> requested bytes
+    // staging for host-pointer entries (page-locked) and device-side workspaces, grown on demand
+    void* pinned = nullptr; size_t pinned_bytes = 0;
+    void* work = nullptr; size_t work_bytes = 0;        // packed inputs / outputs of host-pointer entries
+    void* partial = nullptr; size_t partial_bytes = 0;  // split partials of the decode kernels
+    void* tables = nullptr; size_t tables_bytes = 0;    // work lists of the decode kernels
+    void* append = nullptr; size_t append_bytes = 0;    // plane table of a batched K/V append
+    void* append_pinned = nullptr; size_t append_pinned_bytes = 0;
+    double* turns = nullptr; size_t turns_rows = 0, turns_pairs = 0;   // rope sincos table (forward, inverse)
+    bool turns_ready = false; size_t turns_ready_rows = 0, turns_ready_pairs = 0;
+    void* kv_stage = nullptr; uint64_t kv_stage_rows = 0;
+    uint64_t launches = 0;   // kernels launched through this handle (the benchmark's gpu_launches)
+    explicit Device(int o) : ordinal(o) {}
+};
+
+Device& device(void* handle);   // sets the CUDA device; throws on a null handle
+void* raw_allocate(Device& d, size_t bytes, bool zero);
+void raw_release(Device& d, void* pointer);
+void span(Device& d, const void* pointer, size_t bytes, const char* what);
+void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_host = false);
+
+// a * b * c ... with overflow refusal (gpu/core.hpp:1413 region: an op_span check never passes on a wrapped size)
+inline size_t checked_product(std::initializer_list<uint64_t> factors) {
+    unsigned __int128 total = 1;
+    for (uint64_t f : factors) {
+        total *= f;
+        if (total > (unsigned __int128)(SIZE_MAX / 8)) throw std::runtime_error("Straydog op: a shape overflows the address space");
+    }
+    return size_t(total);
+}
+
+#define SDB_OP_BEGIN try { auto& value = ::sdb::device(handle); (void)value;
+#define SDB_OP_END SDB_CHECK(cudaGetLastError()); return 0; } catch (const std::exception& e) { ::sdb::last_error = e.what(); return -1; }
+
+#if defined(__CUDACC__)
+// ---- device primitives (sm_100a) ----
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// A bounded wait: gives up two seconds after the first failed poll and reports failure, so that a
+// copy that never lands ends the kernel with a status the host reads instead of hanging it.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = global_timer_ns();
+    for (;;) {
+        #pragma unroll 1
+        for (int spin = 0; spin < 64; ++spin)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - start > 2000000000ull) return false;
+    }
+}
+// After a wait gave up: let copies still in flight into this CTA's shared memory land (or not) for a
+// bounded millisecond before the CTA exits.
+__device__ __forceinline__ void drain_delay() {
+    const uint64_t start = global_timer_ns();
+    while (global_timer_ns() - start < 1000000ull) __nanosleep(1000);
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Untiled bulk copy global -> shared (TMA engine), completion on an mbarrier. Both addresses
+// 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// D(16x8, f32) += A(16x16, row) * B(16x8, col); f16 or bf16 operands.
+__device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+    uint32_t out;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(a), "r"(b), "r"(selector));
+    return out;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    uint32_t out;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(hi), "f"(lo));
+    return out;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t out;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(out) : "f"(hi), "f"(lo));
+    return out;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+#endif
+
+}  // namespace sdb

@@ -1,0 +1,279 @@
+// Handles, allocations and transfers of the C ABI: the subset of the reference's memory entries the
+// attention path's callers use (gpu/straydog_gpu.h:17,33-34,42-67,113-114,157-159;
+// gpu/kernels.cpp:3511-3611, 3646-3712, 3771, 4364-4386, 4555-4593). Same conventions: a negative
+// result or a null pointer is a failure that sd_error() describes for the calling thread; the
+// library owns every allocation and each op checks that its pointers lie inside one of them.
+#include "common.cuh"
+#include "../../include/straydog_gpu_b200.h"
+
+namespace sdb {
+
+thread_local std::string last_error;
+
+Device& device(void* handle) {
+    if (!handle) throw std::runtime_error("null Straydog device handle");
+    auto& value = *static_cast<Device*>(handle);
+    SDB_CHECK(cudaSetDevice(value.ordinal));
+    return value;
+}
+
+static std::string budget_exceeded(const Device& d, uint64_t bytes) {
+    return "Straydog VRAM budget exceeded: " + std::to_string(bytes) + " bytes requested, " + std::to_string(d.used) + " of " +
+           std::to_string(d.budget) + " in use";
+}
+
+void* raw_allocate(Device& d, size_t bytes, bool zero) {
+    std::lock_guard<std::mutex> lock(d.mutex);
+    const uint64_t available = d.budget > d.used ? d.budget - d.used : 0;
+    if (!bytes || bytes > available || allocation_tail > available - bytes) throw std::runtime_error(budget_exceeded(d, bytes));
+    void* pointer = nullptr;
+    SDB_CHECK(cudaMalloc(&pointer, bytes + allocation_tail));
+    d.allocations.emplace(static_cast<const uint8_t*>(pointer), bytes);
+    d.used += bytes + allocation_tail;
+    if (zero) {
+        SDB_CHECK(cudaMemsetAsync(pointer, 0, bytes + allocation_tail, d.stream));
+        SDB_CHECK(cudaStreamSynchronize(d.stream));
+    }
+    return pointer;
+}
+
+void raw_release(Device& d, void* pointer) {
+    std::lock_guard<std::mutex> lock(d.mutex);
+    auto found = d.allocations.find(static_cast<const uint8_t*>(pointer));
+    if (found == d.allocations.end()) throw std::runtime_error("unknown Straydog allocation");
+    SDB_CHECK(cudaStreamSynchronize(d.stream));
+    SDB_CHECK(cudaFree(pointer));
+    d.used -= found->second + allocation_tail;
+    d.allocations.erase(found);
+}
+
+// The range [pointer, pointer + bytes) lies inside one allocation of this device (gpu/ops.hpp:8-26).
+void span(Device& d, const void* pointer, size_t bytes, const char* what) {
+    const auto* at = static_cast<const uint8_t*>(pointer);
+    std::lock_guard<std::mutex> lock(d.mutex);
+    auto next = d.allocations.upper_bound(at);
+    if (next != d.allocations.begin()) {
+        --next;
+        if (bytes <= next->second && size_t(at - next->first) <= next->second - bytes) return;
+    }
+    throw std::runtime_error(std::string("Straydog op: ") + what + " is outside this device's allocations");
+}
+
+// Library-owned workspaces (not in the allocation map: callers never see them), grown on demand.
+void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_host) {
+    if (have >= bytes && slot) return slot;
+    SDB_CHECK(cudaStreamSynchronize(d.stream));
+    if (slot) { if (pinned_host) SDB_CHECK(cudaFreeHost(slot)); else SDB_CHECK(cudaFree(slot)); slot = nullptr; have = 0; }
+    const size_t grown = bytes + bytes / 4 + 4096;
+    if (pinned_host) SDB_CHECK(cudaMallocHost(&slot, grown)); else SDB_CHECK(cudaMalloc(&slot, grown));
+    have = grown;
+    return slot;
+}
+
+static void copy_in(Device& d, void* target, const void* data, size_t bytes) {
+    SDB_CHECK(cudaMemcpyAsync(target, data, bytes, cudaMemcpyHostToDevice, d.stream));
+}
+
+}  // namespace sdb
+
+using namespace sdb;
+
+extern "C" {
+
+const char* sd_error(void) { return last_error.c_str(); }
+
+int sd_device_count(void) {
+    int count = 0;
+    const cudaError_t error = cudaGetDeviceCount(&count);
+    if (error != cudaSuccess) { last_error = cudaGetErrorString(error); cudaGetLastError(); return -1; }
+    return count;
+}
+
+void* sd_create(int ordinal, uint64_t budget) {
+    try {
+        int count = 0;
+        SDB_CHECK(cudaGetDeviceCount(&count));
+        if (ordinal < 0 || ordinal >= count) throw std::runtime_error("unknown Straydog device ordinal");
+        auto value = std::make_unique<Device>(ordinal);
+        SDB_CHECK(cudaSetDevice(ordinal));
+        cudaDeviceProp prop{};
+        SDB_CHECK(cudaGetDeviceProperties(&prop, ordinal));
+        // This library holds sm_100a code only: refuse any other device instead of failing at the first launch.
+        if (prop.major != 10)
+            throw std::runtime_error(std::string("this Straydog build holds code for B200-class GPUs (sm_100a) only, not for ") + prop.name);
+        value->sms = prop.multiProcessorCount;
+        size_t available = 0, total = 0;
+        SDB_CHECK(cudaMemGetInfo(&available, &total));
+        if (budget < (1u << 20) || budget > available) throw std::runtime_error("Straydog VRAM budget is unavailable");
+        value->budget = budget;
+        SDB_CHECK(cudaStreamCreateWithFlags(&value->stream, cudaStreamNonBlocking));
+        return value.release();
+    } catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+void sd_destroy(void* handle) {
+    if (!handle) return;
+    auto* value = static_cast<Device*>(handle);
+    if (cudaSetDevice(value->ordinal) == cudaSuccess) {
+        cudaStreamSynchronize(value->stream);
+        for (auto& entry : value->allocations) cudaFree(const_cast<uint8_t*>(entry.first));
+        if (value->pinned) cudaFreeHost(value->pinned);
+        if (value->append_pinned) cudaFreeHost(value->append_pinned);
+        for (void* p : {value->work, value->partial, value->tables, value->append, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
+        cudaStreamDestroy(value->stream);
+        cudaGetLastError();
+    }
+    delete value;
+}
+
+int sd_memory(void* handle, uint64_t* used, uint64_t* budget) {
+    try {
+        auto& value = device(handle);
+        if (used) *used = value.used;
+        if (budget) *budget = value.budget;
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+void* sd_allocate(void* handle, uint64_t bytes) {
+    try { return raw_allocate(device(handle), bytes, false); }
+    catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+void* sd_upload(void* handle, const void* data, uint64_t bytes) {
+    try {
+        auto& value = device(handle);
+        if (!data) throw std::runtime_error("invalid Straydog upload");
+        void* pointer = raw_allocate(value, bytes, false);
+        copy_in(value, pointer, data, bytes);
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return pointer;
+    } catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+int sd_write(void* handle, void* pointer, const void* data, uint64_t bytes) {
+    try {
+        auto& value = device(handle);
+        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
+        if (!data || found == value.allocations.end() || found->second != bytes) throw std::runtime_error("invalid Straydog write");
+        copy_in(value, pointer, data, bytes);
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sd_release(void* handle, void* pointer) {
+    try {
+        auto& value = device(handle);
+        if (pointer == value.kv_stage) { value.kv_stage = nullptr; value.kv_stage_rows = 0; }
+        raw_release(value, pointer);
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sd_allocation_bytes(void* handle, const void* pointer, uint64_t* bytes) {
+    try {
+        auto& value = device(handle);
+        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
+        if (!bytes || found == value.allocations.end()) throw std::runtime_error("unknown Straydog allocation");
+        *bytes = found->second + allocation_tail;
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sd_zero(void* handle, void* pointer) {
+    try {
+        auto& value = device(handle);
+        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
+        if (found == value.allocations.end()) throw std::runtime_error("unknown Straydog state allocation");
+        SDB_CHECK(cudaMemsetAsync(pointer, 0, found->second, value.stream));
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sd_download(void* handle, void* pointer, void* output, uint64_t bytes) {
+    try {
+        auto& value = device(handle);
+        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
+        if (!output || found == value.allocations.end() || found->second != bytes)
+            throw std::runtime_error("Straydog state readback size mismatch");
+        SDB_CHECK(cudaMemcpyAsync(output, pointer, bytes, cudaMemcpyDeviceToHost, value.stream));
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+void* sd_buffer(void* handle, uint64_t bytes) {
+    try { return raw_allocate(device(handle), bytes, true); }
+    catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+int sd_buffer_write(void* handle, void* buffer, uint64_t offset, const void* data, uint64_t bytes) {
+    try {
+        auto& value = device(handle);
+        if (!data || offset > UINT64_MAX - bytes) throw std::runtime_error("invalid Straydog buffer write");
+        span(value, static_cast<uint8_t*>(buffer) + offset, bytes, "a written buffer");
+        copy_in(value, static_cast<uint8_t*>(buffer) + offset, data, bytes);
+        // (the caller's memory may be pageable and reused at once: the copy is finished before returning)
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* output, uint64_t bytes) {
+    try {
+        auto& value = device(handle);
+        if (!output || offset > UINT64_MAX - bytes) throw std::runtime_error("invalid Straydog buffer read");
+        span(value, static_cast<const uint8_t*>(buffer) + offset, bytes, "a read buffer");
+        SDB_CHECK(cudaMemcpyAsync(output, static_cast<const uint8_t*>(buffer) + offset, bytes, cudaMemcpyDeviceToHost, value.stream));
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+// gpu/kernels.cpp:4266-4275: 512 (FP16 rows) or 272 (Q8_0 rows). This library's attention kernels
+// read Q8_0 rows only; FP16 rows are accepted as a format and refused by the kernels that cannot read them.
+int sd_kv_format(void* handle, uint32_t row) {
+    try {
+        auto& value = device(handle);
+        if (row != kv_row_f16 && row != kv_row_q8) throw std::runtime_error("invalid Straydog K/V format");
+        value.kv_row = row;
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+// gpu/kernels.cpp:4277-4290: registers the VRAM stage of host-resident K/V. With every K/V plane in
+// HBM (180 GB) there is nothing to stage: the registration is validated and kept, and the decode
+// view stays {state, context} (gpu/kv_stage.hpp:105-109, mirror = none).
+int sd_kv_stage(void* handle, void* pointer, uint64_t rows) {
+    try {
+        auto& value = device(handle);
+        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
+        if (!rows || rows > (uint64_t(1) << 22) || found == value.allocations.end() || found->second != size_t(rows) * 1024 * 4)
+            throw std::runtime_error("invalid Straydog K/V stage");
+        value.kv_stage = pointer;
+        value.kv_stage_rows = rows;
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sdx_synchronize(void* handle) {
+    try {
+        auto& value = device(handle);
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+void* sdx_stream(void* handle) {
+    try { return device(handle).stream; }
+    catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+uint64_t sdx_launch_count(void* handle) {
+    try { return device(handle).launches; }
+    catch (const std::exception& e) { last_error = e.what(); return 0; }
+}
+
+}  // extern "C"

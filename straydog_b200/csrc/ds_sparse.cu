@@ -1,0 +1,316 @@
+// sd_op_sparse_attention: DeepSeek-V4.1-style latent attention. Each query row attends the window
+// rows of an F32 ring ending at its position and the compressed rows its selection lists (-1: none),
+// keys being also the values, with a per-head sink in the softmax max and denominator; the last
+// rope_dims columns of q are rotated by position * frequency (in double) and the output's rotated back.
+// Reference: gpu/kernels.cpp:5311-5476 (entry, validation), gpu/ops.hpp:1203-1235 (BF16-tagged rows),
+// :1240-1297 (definition), :1309-1327 (key order, rope table), :1528-1538 (inverse rope), :1561-1583 (sink).
+//
+// This file holds the entry, the rope table, the query preparation and the FP32 CUDA-core kernel
+// (exact FP32 products for any operand values); ds_sparse_mma.cu holds the tensor-core kernel the
+// entry prefers when the shape allows it.
+#include "common.cuh"
+#include "ds_sparse.cuh"
+#include "../../include/straydog_gpu_b200.h"
+
+#include <algorithm>
+#include <cstdlib>
+
+namespace sdb {
+
+// One row's rope, once: forward (cos, sin) of p * f, then of that angle times -1.0 by its own sincos
+// (gpu/ops.hpp:1318-1327: "not a negated sine").
+__global__ void sparse_turns_kernel(const int32_t* __restrict__ positions, const float* __restrict__ frequencies, size_t pairs,
+                                    double2* __restrict__ forward, double2* __restrict__ inverse) {
+    const int64_t p = positions[blockIdx.x];
+    for (size_t pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+        double s, c;
+        sincos(double(p) * double(frequencies[pair]), &s, &c);
+        forward[size_t(blockIdx.x) * pairs + pair] = make_double2(c, s);
+        sincos(double(p) * double(frequencies[pair]) * -1.0, &s, &c);
+        inverse[size_t(blockIdx.x) * pairs + pair] = make_double2(c, s);
+    }
+}
+
+// q with its last 2 * pairs columns rotated in adjacent pairs (double arithmetic, rounded to F32:
+// gpu/ops.hpp:1366-1377), as F32 and, for the tensor-core kernel, split into BF16 high and low parts
+// (q = hi + lo up to 2^-17 relative). exact_flag is cleared when any low part is non-zero outside the
+// rotated columns.
+__global__ void __launch_bounds__(256) sparse_prepare_q_kernel(const float* __restrict__ q, size_t heads, size_t dim, size_t pairs,
+                                                               const double2* __restrict__ forward, float* __restrict__ rotated_q,
+                                                               __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                                               int* __restrict__ inexact) {
+    const size_t row = blockIdx.x, plain = dim - 2 * pairs;
+    bool any = false;
+    for (size_t i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+        const size_t head = i / dim, col = i % dim;
+        const float* source = q + (row * heads + head) * dim;
+        float v = source[col];
+        if (col >= plain) {
+            const size_t pair = (col - plain) / 2;
+            const double2 g = forward[row * pairs + pair];
+            const double a = source[plain + 2 * pair], b = source[plain + 2 * pair + 1];
+            v = (col - plain) % 2 == 0 ? float(a * g.x - b * g.y) : float(a * g.y + b * g.x);
+        }
+        const size_t at = (row * heads + head) * dim + col;
+        if (rotated_q) rotated_q[at] = v;
+        if (hi) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            const float rest = v - __bfloat162float(h);
+            hi[at] = h;
+            lo[at] = __float2bfloat16_rn(rest);
+            if (rest != 0.0f && col < plain) any = true;
+        }
+    }
+    if (inexact && any) atomicExch(inexact, 1);
+}
+
+// ---- FP32 kernel: block = (row, group of 4 heads, split); a warp per key ----
+constexpr int kSimtHeads = 4, kSimtWarps = 8;
+
+template<int PER_LANE>
+__global__ void __launch_bounds__(kSimtWarps * 32) sparse_simt_kernel(const SparseArgs a, const float* __restrict__ q, float* __restrict__ partial) {
+    const size_t row = blockIdx.x, head0 = size_t(blockIdx.y) * kSimtHeads, split = blockIdx.z, splits = gridDim.z;
+    const unsigned lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+    const KeyList list = key_list(a, row);
+    const size_t share = (list.total + splits - 1) / splits, begin = min(list.total, split * share), end = min(list.total, begin + share);
+    extern __shared__ float shared[];
+    float* qs = shared;                                  // [kSimtHeads][dim]
+    float* merged = shared + kSimtHeads * a.dim;         // [kSimtHeads][dim]
+    __shared__ float tops[kSimtWarps][kSimtHeads], sums[kSimtWarps][kSimtHeads];
+    for (size_t i = threadIdx.x; i < kSimtHeads * a.dim; i += blockDim.x) {
+        const size_t head = head0 + i / a.dim;
+        qs[i] = head < a.heads ? q[(row * a.heads + head) * a.dim + i % a.dim] : 0.0f;
+        merged[i] = 0.0f;
+    }
+    __syncthreads();
+    float m[kSimtHeads], l[kSimtHeads], acc[kSimtHeads][PER_LANE];
+    #pragma unroll
+    for (int h = 0; h < kSimtHeads; ++h) {
+        m[h] = -INFINITY; l[h] = 0.0f;
+        #pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) acc[h][j] = 0.0f;
+    }
+    for (size_t index = begin + warp; index < end; index += kSimtWarps) {
+        const float* key = key_pointer(a, list, row, index);
+        if (!key) continue;
+        float k[PER_LANE];
+        if (state_is_bf16(key)) {
+            const uint16_t* halves = state_halves(key);
+            #pragma unroll
+            for (int j = 0; j < PER_LANE; ++j) { const size_t d = lane + 32 * j; k[j] = d < a.dim ? __uint_as_float(uint32_t(halves[d]) << 16) : 0.0f; }
+        } else {
+            #pragma unroll
+            for (int j = 0; j < PER_LANE; ++j) { const size_t d = lane + 32 * j; k[j] = d < a.dim ? key[d] : 0.0f; }
+        }
+        #pragma unroll
+        for (int h = 0; h < kSimtHeads; ++h) {
+            float dot = 0.0f;
+            #pragma unroll
+            for (int j = 0; j < PER_LANE; ++j) { const size_t d = lane + 32 * j; dot = fmaf(d < a.dim ? qs[h * a.dim + d] : 0.0f, k[j], dot); }
+            #pragma unroll
+            for (unsigned offset = 16; offset; offset /= 2) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+            const float score = dot * a.scale, next = fmaxf(m[h], score);
+            const float correction = expf(m[h] - next), p = expf(score - next);
+            l[h] = fmaf(l[h], correction, p);
+            #pragma unroll
+            for (int j = 0; j < PER_LANE; ++j) acc[h][j] = fmaf(acc[h][j], correction, p * k[j]);
+            m[h] = next;
+        }
+    }
+    if (lane == 0)
+        #pragma unroll
+        for (int h = 0; h < kSimtHeads; ++h) { tops[warp][h] = m[h]; sums[warp][h] = l[h]; }
+    __syncthreads();
+    float top[kSimtHeads], total[kSimtHeads];
+    #pragma unroll
+    for (int h = 0; h < kSimtHeads; ++h) {
+        top[h] = tops[0][h];
+        for (int w = 1; w < kSimtWarps; ++w) top[h] = fmaxf(top[h], tops[w][h]);
+        total[h] = 0.0f;
+        for (int w = 0; w < kSimtWarps; ++w) total[h] += tops[w][h] == -INFINITY ? 0.0f : sums[w][h] * expf(tops[w][h] - top[h]);
+    }
+    for (int w = 0; w < kSimtWarps; ++w) {   // warps add in turn: a fixed order
+        if (int(warp) == w) {
+            #pragma unroll
+            for (int h = 0; h < kSimtHeads; ++h) {
+                if (m[h] == -INFINITY) continue;
+                const float factor = expf(m[h] - top[h]);
+                #pragma unroll
+                for (int j = 0; j < PER_LANE; ++j) { const size_t d = lane + 32 * j; if (d < a.dim) merged[h * a.dim + d] += factor * acc[h][j]; }
+            }
+        }
+        __syncthreads();
+    }
+    // the split's partial: [dim sums | max | denominator] per (row, head, split)
+    for (size_t i = threadIdx.x; i < kSimtHeads * a.dim; i += blockDim.x) {
+        const size_t h = i / a.dim, head = head0 + h;
+        if (head < a.heads) partial[((row * a.heads + head) * splits + split) * (a.dim + 2) + i % a.dim] = merged[i];
+    }
+    if (threadIdx.x < kSimtHeads && head0 + threadIdx.x < a.heads) {
+        float* at = partial + ((row * a.heads + head0 + threadIdx.x) * splits + split) * (a.dim + 2) + a.dim;
+        at[0] = top[threadIdx.x]; at[1] = total[threadIdx.x];
+    }
+}
+
+// The splits of a (row, head) combined with the head's sink (in the max and the denominator,
+// gpu/ops.hpp:1561-1583), divided, and the rotated columns turned back (gpu/ops.hpp:1528-1538).
+// `log2_domain`: the partial maxima are in the exp2 domain (the tensor-core kernel's), the sink then scaled to it.
+__global__ void __launch_bounds__(128) sparse_combine_kernel(const float* __restrict__ partial, size_t splits, size_t heads, size_t dim,
+                                                             const float* __restrict__ sinks, size_t pairs, const double2* __restrict__ inverse,
+                                                             int log2_domain, float* __restrict__ out) {
+    const size_t item = blockIdx.x, row = item / heads, head = item % heads, plain = dim - 2 * pairs;
+    const float* first = partial + item * splits * (dim + 2);
+    const float unit = log2_domain ? 1.4426950408889634f : 1.0f;
+    const float sink = sinks[head] * unit;
+    float top = sink;
+    for (size_t s = 0; s < splits; ++s) top = fmaxf(top, first[s * (dim + 2) + dim]);
+    const auto weight = [&](float x) { return log2_domain ? exp2f(x) : expf(x); };
+    float denominator = weight(sink - top);   // (a sink of -inf adds 0)
+    for (size_t s = 0; s < splits; ++s) {
+        const float own = first[s * (dim + 2) + dim];
+        if (own != -INFINITY) denominator += first[s * (dim + 2) + dim + 1] * weight(own - top);
+    }
+    for (size_t pair = threadIdx.x; pair < dim / 2 + dim % 2; pair += blockDim.x) {
+        float o[2];
+        #pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const size_t d = 2 * pair + i;
+            float sum = 0.0f;
+            if (d < dim)
+                for (size_t s = 0; s < splits; ++s) {
+                    const float own = first[s * (dim + 2) + dim];
+                    if (own != -INFINITY) sum = fmaf(first[s * (dim + 2) + d], weight(own - top), sum);
+                }
+            o[i] = sum / denominator;
+        }
+        const size_t d = 2 * pair;
+        if (d >= plain && d + 1 < dim) {   // (plain is even whenever dim and rope_dims are: pairs never straddle it)
+            const double2 g = inverse[row * pairs + (d - plain) / 2];
+            const double x = o[0], y = o[1];
+            o[0] = float(x * g.x - y * g.y);
+            o[1] = float(x * g.y + y * g.x);
+        }
+        out[item * dim + d] = o[0];
+        if (d + 1 < dim) out[item * dim + d + 1] = o[1];
+    }
+}
+
+static void turns_reserve(Device& d, size_t rows, size_t pairs) {
+    if (!pairs || !rows) return;
+    if (d.turns && d.turns_rows >= rows && d.turns_pairs == pairs) return;
+    SDB_CHECK(cudaStreamSynchronize(d.stream));
+    if (d.turns) SDB_CHECK(cudaFree(d.turns));
+    d.turns = nullptr;
+    SDB_CHECK(cudaMalloc(reinterpret_cast<void**>(&d.turns), rows * pairs * 2 * sizeof(double2)));
+    d.turns_rows = rows; d.turns_pairs = pairs;
+}
+
+static bool env_flag(const char* name) {
+    const char* v = std::getenv(name);
+    return v && v[0] == '1' && !v[1];
+}
+
+}  // namespace sdb
+
+using namespace sdb;
+
+extern "C" {
+
+int sd_attention_turns_reserve(void* handle, uint64_t rows, uint64_t rope_dims) {
+    try {
+        if (rope_dims > 128 || rope_dims % 2) throw std::runtime_error("invalid Straydog attention rope");
+        turns_reserve(device(handle), size_t(rows), size_t(rope_dims / 2));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+// In the reference the next norm+rope op of exactly `rows` rows then fills the table so that the
+// attention skips its own rope launch (gpu/straydog_gpu.h:386-389). Those ops are outside this
+// library, so nothing ever fills it early: arming is accepted and the attention fills the table itself.
+int sd_attention_turns_arm(void* handle, uint64_t rows) {
+    try {
+        auto& value = device(handle);
+        (void)rows;
+        value.turns_ready = false;
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                           uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                           uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
+                           uint64_t rope_dims, const float* frequencies, float* scratch, uint64_t scratch_bytes, float* out) {
+    SDB_OP_BEGIN
+    if (!rows || rows > 65535 || !heads || !dim || !window || rope_dims % 2 || rope_dims > dim || rope_dims > 128)
+        throw std::runtime_error("invalid Straydog attention shape");
+    if (dim > 1024 || heads > 65535 * kSimtHeads || !raw_rows) throw std::runtime_error("invalid Straydog attention shape");
+    if (rope_dims) span(value, frequencies, size_t(rope_dims / 2) * 4, "rope frequencies");
+    span(value, q, checked_product({rows, heads, dim, 4}), "attention queries");
+    span(value, raw, checked_product({raw_rows, dim, 4}), "window rows");
+    span(value, positions, checked_product({rows, 4}), "query positions");
+    if (selections) {
+        if (state_is_bf16(compressed)) span(value, state_halves(compressed), checked_product({compressed_rows, dim, 2}), "compressed rows");
+        else span(value, compressed, checked_product({compressed_rows, dim, 4}), "compressed rows");
+        span(value, selected, checked_product({rows, selections, 4}), "selected rows");
+    }
+    span(value, sinks, checked_product({heads, 4}), "attention sinks");
+    span(value, out, checked_product({rows, heads, dim, 4}), "an attention output");
+    if (scratch && scratch_bytes) span(value, scratch, size_t(scratch_bytes), "attention scratch");
+
+    const size_t pairs = size_t(rope_dims / 2);
+    double2* forward = nullptr;
+    double2* inverse = nullptr;
+    if (pairs) {
+        turns_reserve(value, size_t(rows), pairs);
+        forward = reinterpret_cast<double2*>(value.turns);
+        inverse = forward + value.turns_rows * pairs;
+        sparse_turns_kernel<<<unsigned(rows), 64, 0, value.stream>>>(positions, frequencies, pairs, forward, inverse);
+        ++value.launches;
+    }
+    value.turns_ready = false;
+
+    SparseArgs args{};
+    args.raw = raw; args.raw_rows = raw_rows; args.positions = positions; args.window = window; args.compressed = compressed;
+    args.compressed_rows = compressed_rows; args.selected = selected; args.selections = selections; args.heads = heads; args.dim = dim;
+    args.scale = scale;
+
+    const bool force_simt = env_flag("SDX_SPARSE_SIMT");
+    if (!force_simt && sparse_mma_supported(args)) {
+        sparse_mma_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        SDB_CHECK(cudaGetLastError());
+        return 0;
+    }
+
+    // FP32 path. Workspace (library-owned, grown on the first call of a size): rotated q, then the splits' partials.
+    const size_t stride = size_t(window + selections);
+    const size_t groups = (heads + kSimtHeads - 1) / kSimtHeads;
+    size_t splits = std::max<size_t>(1, std::min<size_t>({size_t(32), (stride + 63) / 64, size_t(value.sms) * 4 / std::max<size_t>(1, rows * groups)}));
+    splits = std::max<size_t>(splits, 1);
+    const size_t q_bytes = pairs ? (checked_product({rows, heads, dim, 4}) + 255) / 256 * 256 : 0;
+    const size_t partial_bytes = checked_product({rows, heads, splits, dim + 2, 4});
+    auto* work = static_cast<uint8_t*>(ensure(value, value.partial, value.partial_bytes, q_bytes + partial_bytes));
+    const float* q_used = q;
+    if (pairs) {
+        auto* rotated = reinterpret_cast<float*>(work);
+        sparse_prepare_q_kernel<<<unsigned(rows), 256, 0, value.stream>>>(q, heads, dim, pairs, forward, rotated, nullptr, nullptr, nullptr);
+        ++value.launches;
+        q_used = rotated;
+    }
+    auto* partial = reinterpret_cast<float*>(work + q_bytes);
+    const dim3 grid{unsigned(rows), unsigned(groups), unsigned(splits)};
+    const size_t shared = 2 * kSimtHeads * size_t(dim) * 4;
+    const int per_lane = int((dim + 31) / 32);
+    #define SDB_SIMT(N) do { \
+        SDB_CHECK(cudaFuncSetAttribute(sparse_simt_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared))); \
+        sparse_simt_kernel<N><<<grid, kSimtWarps * 32, shared, value.stream>>>(args, q_used, partial); } while (0)
+    if (per_lane <= 4) SDB_SIMT(4); else if (per_lane <= 8) SDB_SIMT(8); else if (per_lane <= 16) SDB_SIMT(16);
+    else if (per_lane <= 18) SDB_SIMT(18); else SDB_SIMT(32);
+    #undef SDB_SIMT
+    ++value.launches;
+    SDB_CHECK(cudaGetLastError());
+    sparse_combine_kernel<<<unsigned(rows * heads), 128, 0, value.stream>>>(partial, splits, heads, dim, sinks, pairs, inverse, 0, out);
+    ++value.launches;
+    SDB_OP_END
+}
+
+}  // extern "C"

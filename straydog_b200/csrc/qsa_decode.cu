@@ -1,0 +1,527 @@
+// Grouped-query decode attention over Q8_0 K/V rows, split-K flash decoding for sm_100a.
+//
+// What it replaces in the reference: qsa_decode_parts + qsa_decode_merge
+// (gpu/sparse_attention_compute.hpp:41-170) behind qsa_attention / qsa_attention_rows (:609-647),
+// generalised from "24 query / 2 KV heads, <= 2052 selected keys of one sequence" to any group of
+// <= 8 query heads per KV head, dense causal key ranges and many sequences in one launch.
+//
+// Design (one persistent CTA per SM, 8 independent warps):
+//   * The batch's (sequence, KV head) segments are laid end to end as a sequence of 16-key tiles and
+//     cut into equal contiguous runs, one per warp (stream-K): every warp streams the same number of
+//     bytes whatever the sequences' lengths. A run crosses segment borders as separate "pieces".
+//   * Each warp owns a ring of STAGES tiles in shared memory. A tile is 16 consecutive K rows and the
+//     same 16 V rows (2 x 4352 contiguous bytes), fetched by two bulk copies (TMA engine) that complete
+//     on the tile's mbarrier; the warp refills a slot as soon as it has consumed it, so STAGES-1 tiles
+//     per warp are always in flight.
+//   * Arithmetic: int8 -> FP16 is exact, so Q.K^T runs on mma.sync.m16n8k16 with the 16 keys as M,
+//     the 8 query heads of the group as N and one 32-column Q8_0 block per two MMAs; the block's FP32
+//     sum is multiplied by the key's FP16 block scale in FP32 (the reference multiplies each value by
+//     the scale before its FMA: the same number up to one rounding). P.V runs as V^T (16 columns x 16
+//     keys, raw int8 as FP16) times P' (keys x heads), where P' = p * (value block scale) rounded to
+//     FP16 once; accumulation is FP32 throughout. Online softmax per warp in the exp2 domain.
+//   * Every piece leaves (unnormalised sum[8][256], max, denominator) in a partial slot; a merge
+//     kernel combines a segment's pieces exactly as qsa_decode_merge does (:139-170).
+#include "common.cuh"
+#include "../../include/straydog_gpu_b200.h"
+
+#include <algorithm>
+
+namespace sdb {
+
+constexpr int kWarps = 8, kTileKeys = 16, kStages = 3;
+constexpr int kTileBytes = 2 * kTileKeys * int(kv_row_q8);   // K rows then V rows: 8704
+constexpr int kPartialFloats = 8 * 258;                      // per piece: 8 heads x (256 sums, max, denominator)
+constexpr size_t kDecodeSmem = size_t(kWarps) * kStages * kTileBytes + size_t(kWarps) * kStages * 8 + 16;
+
+struct Segment {            // one (sequence, KV head)
+    const uint8_t* keys;    // plane base
+    const uint8_t* values;
+    uint32_t q_offset;      // (sequence * heads + kv_head * group) * 256, in query elements
+    uint32_t first_piece, pieces, length;
+};
+struct Piece { uint32_t segment, begin, end, pad; };
+
+struct DecodeArgs {
+    const Segment* segments;
+    const Piece* pieces;
+    const uint32_t* warp_piece;   // [virtual warps + 1]
+    const __half* q;
+    float* partial;
+    uint32_t virtual_warps, ctas;
+    uint32_t group;               // query heads per KV head (<= 8)
+    float scale_log2;             // softmax scale * log2(e)
+    int* status;                  // set to 1 when a bounded wait gave up
+};
+
+// Row of the tile held by the MMA fragment row `g` (0..7); rows g + 8 follow the same map + 8.
+// Even rows go to lanes 0..15 and odd rows to lanes 16..31, which keeps the 8-byte key loads of a
+// half warp on 32 distinct banks with 272-byte rows.
+__device__ __forceinline__ int tile_row(int g) { return 2 * (g & 3) + (g >> 2); }
+
+// Four int8 (a 32-bit word, already xor 0x80808080) -> two FP16 pairs, exactly: 0x64xx is 1024 + xx.
+__device__ __forceinline__ uint32_t bytes01_to_half2(uint32_t x) {
+    const uint32_t h = prmt(x, 0x64646464u, 0x4140u);
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bytes23_to_half2(uint32_t x) {
+    const uint32_t h = prmt(x, 0x64646464u, 0x4342u);
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ float half_at(const uint4& v, int i) {
+    const uint32_t w = i < 2 ? v.x : i < 4 ? v.y : i < 6 ? v.z : v.w;
+    return __half2float(__ushort_as_half(uint16_t(i & 1 ? w >> 16 : w & 0xffffu)));
+}
+
+// The walk of one warp over its pieces' tiles, used twice: by the cursor that issues copies and by
+// the one that consumes them.
+struct Cursor {
+    uint32_t piece, piece_end, key, key_end;
+    const uint8_t* keys;
+    const uint8_t* values;
+    __device__ __forceinline__ void load(const DecodeArgs& a) {
+        if (piece >= piece_end) return;
+        const Piece p = a.pieces[piece];
+        const Segment s = a.segments[p.segment];
+        key = p.begin; key_end = p.end; keys = s.keys; values = s.values;
+    }
+    __device__ __forceinline__ bool done() const { return piece >= piece_end; }
+};
+
+__global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const DecodeArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
+    uint8_t* ring = smem + size_t(warp) * kStages * kTileBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kWarps) * kStages * kTileBytes) + warp * kStages;
+    if (lane == 0)
+        for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+    fence_barrier_init();
+    __syncthreads();
+    // virtual warp v runs on CTA v % ctas: few warps spread over many SMs rather than filling one
+    const uint32_t vwarp = uint32_t(warp) * a.ctas + blockIdx.x;
+    if (vwarp >= a.virtual_warps) return;
+
+    Cursor issue{a.warp_piece[vwarp], a.warp_piece[vwarp + 1], 0, 0, nullptr, nullptr};
+    Cursor use = issue;
+    if (issue.done()) return;
+    issue.load(a);
+    use.load(a);
+
+    // lane 0 issues the tile at the issue cursor into `slot`
+    auto fetch = [&](int slot) {
+        if (issue.done()) return;
+        const uint32_t rows = min(uint32_t(kTileKeys), issue.key_end - issue.key), bytes = rows * kv_row_q8;
+        if (lane == 0) {
+            uint8_t* dst = ring + slot * kTileBytes;
+            mbar_expect_tx(&bars[slot], 2 * bytes);
+            bulk_g2s(dst, issue.keys + size_t(issue.key) * kv_row_q8, bytes, &bars[slot]);
+            bulk_g2s(dst + kTileKeys * kv_row_q8, issue.values + size_t(issue.key) * kv_row_q8, bytes, &bars[slot]);
+        }
+        issue.key += rows;
+        if (issue.key >= issue.key_end) { ++issue.piece; issue.load(a); }
+    };
+    #pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) fetch(s);
+
+    const int r0 = tile_row(g), r1 = r0 + 8;
+    const int ka = tile_row(2 * t), kb = tile_row(2 * t + 1);   // the keys whose P this lane holds after the transpose
+    uint32_t slot = 0, phase = 0, fill = kStages - 1;
+
+    while (!use.done()) {
+        // ---- per piece: this segment's queries as B fragments, fresh softmax state ----
+        const Piece piece = a.pieces[use.piece];
+        const Segment segment = a.segments[piece.segment];
+        uint32_t qf[8][4];
+        {
+            const __half* q = a.q + segment.q_offset + size_t(g) * 256 + 8 * t;
+            #pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (uint32_t(g) < a.group) v = *reinterpret_cast<const uint4*>(q + 32 * b);
+                qf[b][0] = v.x; qf[b][1] = v.y; qf[b][2] = v.z; qf[b][3] = v.w;
+            }
+        }
+        float o[8][2][4];
+        #pragma unroll
+        for (int b = 0; b < 8; ++b)
+            #pragma unroll
+            for (int i = 0; i < 2; ++i)
+                #pragma unroll
+                for (int c = 0; c < 4; ++c) o[b][i][c] = 0.0f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // heads 2t and 2t+1
+
+        while (use.key < use.key_end) {
+            const uint32_t rows = min(uint32_t(kTileKeys), use.key_end - use.key);
+            // refill the slot consumed last iteration (all lanes are past their reads of it)
+            __syncwarp();
+            fetch(int(fill));
+            fill = fill + 1 == kStages ? 0 : fill + 1;
+            if (!mbar_wait(&bars[slot], phase)) { if (lane == 0) atomicExch(a.status, 1); drain_delay(); return; }
+            const uint8_t* kt = ring + slot * kTileBytes;
+            const uint8_t* vt = kt + kTileKeys * kv_row_q8;
+
+            // ---- S = K Q^T: per 32-column block two MMAs into a fresh accumulator, then the block's scale ----
+            const uint4 ks0 = *reinterpret_cast<const uint4*>(kt + r0 * kv_row_q8 + 256);
+            const uint4 ks1 = *reinterpret_cast<const uint4*>(kt + r1 * kv_row_q8 + 256);
+            float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            #pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                uint2 w0 = *reinterpret_cast<const uint2*>(kt + r0 * kv_row_q8 + 32 * b + 8 * t);
+                uint2 w1 = *reinterpret_cast<const uint2*>(kt + r1 * kv_row_q8 + 32 * b + 8 * t);
+                w0.x ^= 0x80808080u; w0.y ^= 0x80808080u; w1.x ^= 0x80808080u; w1.y ^= 0x80808080u;
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                uint32_t af[4] = {bytes01_to_half2(w0.x), bytes01_to_half2(w1.x), bytes23_to_half2(w0.x), bytes23_to_half2(w1.x)};
+                mma_f16(acc, af, qf[b][0], qf[b][1]);
+                uint32_t ag[4] = {bytes01_to_half2(w0.y), bytes01_to_half2(w1.y), bytes23_to_half2(w0.y), bytes23_to_half2(w1.y)};
+                mma_f16(acc, ag, qf[b][2], qf[b][3]);
+                const float c0 = half_at(ks0, b), c1 = half_at(ks1, b);
+                s[0] = fmaf(acc[0], c0, s[0]); s[1] = fmaf(acc[1], c0, s[1]);
+                s[2] = fmaf(acc[2], c1, s[2]); s[3] = fmaf(acc[3], c1, s[3]);
+            }
+            // ---- online softmax (exp2 domain); s[0], s[1]: key r0, heads 2t, 2t+1; s[2], s[3]: key r1 ----
+            const bool live0 = uint32_t(r0) < rows, live1 = uint32_t(r1) < rows;
+            float x[4] = {live0 ? s[0] * a.scale_log2 : -INFINITY, live0 ? s[1] * a.scale_log2 : -INFINITY,
+                          live1 ? s[2] * a.scale_log2 : -INFINITY, live1 ? s[3] * a.scale_log2 : -INFINITY};
+            float top0 = fmaxf(x[0], x[2]), top1 = fmaxf(x[1], x[3]);
+            #pragma unroll
+            for (int offset = 4; offset < 32; offset *= 2) {
+                top0 = fmaxf(top0, __shfl_xor_sync(0xffffffffu, top0, offset));
+                top1 = fmaxf(top1, __shfl_xor_sync(0xffffffffu, top1, offset));
+            }
+            const float n0 = fmaxf(m0, top0), n1 = fmaxf(m1, top1);   // finite: every tile has a live key (row 0)
+            if (__any_sync(0xffffffffu, n0 > m0 || n1 > m1)) {
+                const float f0 = fast_exp2(m0 - n0), f1 = fast_exp2(m1 - n1);   // exp2(-inf) = 0 at the first tile
+                l0 *= f0; l1 *= f1;
+                #pragma unroll
+                for (int b = 0; b < 8; ++b)
+                    #pragma unroll
+                    for (int i = 0; i < 2; ++i) { o[b][i][0] *= f0; o[b][i][1] *= f1; o[b][i][2] *= f0; o[b][i][3] *= f1; }
+                m0 = n0; m1 = n1;
+            }
+            float p[4] = {fast_exp2(x[0] - m0), fast_exp2(x[1] - m1), fast_exp2(x[2] - m0), fast_exp2(x[3] - m1)};
+            l0 += p[0] + p[2]; l1 += p[1] + p[3];
+            // ---- transpose P (keys x heads, FP32) into B-fragment order: lane (g, t) gets head g, keys ka, kb, ka+8, kb+8 ----
+            float pa, pb, pc, pd;
+            {
+                const uint32_t u0 = __float_as_uint(p[0]), u1 = __float_as_uint(p[1]), u2 = __float_as_uint(p[2]), u3 = __float_as_uint(p[3]);
+                const uint32_t lo = movmatrix_trans(prmt(u0, u1, 0x5410u)), hi = movmatrix_trans(prmt(u0, u1, 0x7632u));
+                pa = __uint_as_float(prmt(lo, hi, 0x5410u)); pb = __uint_as_float(prmt(lo, hi, 0x7632u));
+                const uint32_t lo2 = movmatrix_trans(prmt(u2, u3, 0x5410u)), hi2 = movmatrix_trans(prmt(u2, u3, 0x7632u));
+                pc = __uint_as_float(prmt(lo2, hi2, 0x5410u)); pd = __uint_as_float(prmt(lo2, hi2, 0x7632u));
+            }
+            // ---- O^T += V^T P': the value block's scale folded into P (FP32 product, one rounding to FP16) ----
+            uint4 va = *reinterpret_cast<const uint4*>(vt + ka * kv_row_q8 + 256);
+            uint4 vb = *reinterpret_cast<const uint4*>(vt + kb * kv_row_q8 + 256);
+            uint4 vc = *reinterpret_cast<const uint4*>(vt + (ka + 8) * kv_row_q8 + 256);
+            uint4 vd = *reinterpret_cast<const uint4*>(vt + (kb + 8) * kv_row_q8 + 256);
+            if (rows < uint32_t(kTileKeys)) {   // rows past the piece hold stale bytes: their weights are 0, their scales must be too
+                if (uint32_t(ka) >= rows) va = make_uint4(0, 0, 0, 0);
+                if (uint32_t(kb) >= rows) vb = make_uint4(0, 0, 0, 0);
+                if (uint32_t(ka + 8) >= rows) vc = make_uint4(0, 0, 0, 0);
+                if (uint32_t(kb + 8) >= rows) vd = make_uint4(0, 0, 0, 0);
+            }
+            #pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                const uint32_t pb0 = pack_half2(pa * half_at(va, b), pb * half_at(vb, b));
+                const uint32_t pb1 = pack_half2(pc * half_at(vc, b), pd * half_at(vd, b));
+                uint32_t wa = *reinterpret_cast<const uint32_t*>(vt + ka * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
+                uint32_t wb = *reinterpret_cast<const uint32_t*>(vt + kb * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
+                uint32_t wc = *reinterpret_cast<const uint32_t*>(vt + (ka + 8) * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
+                uint32_t wd = *reinterpret_cast<const uint32_t*>(vt + (kb + 8) * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
+                // interleave the two keys' bytes: (a.b0, b.b0, a.b1, b.b1) and (a.b2, b.b2, a.b3, b.b3)
+                const uint32_t u = prmt(wa, wb, 0x5140u), v = prmt(wa, wb, 0x7362u);
+                const uint32_t u2 = prmt(wc, wd, 0x5140u), v2 = prmt(wc, wd, 0x7362u);
+                uint32_t af[4] = {bytes01_to_half2(u), bytes23_to_half2(u), bytes01_to_half2(u2), bytes23_to_half2(u2)};
+                mma_f16(o[b][0], af, pb0, pb1);
+                uint32_t ag[4] = {bytes01_to_half2(v), bytes23_to_half2(v), bytes01_to_half2(v2), bytes23_to_half2(v2)};
+                mma_f16(o[b][1], ag, pb0, pb1);
+            }
+            use.key += rows;
+            if (++slot == kStages) { slot = 0; phase ^= 1; }
+        }
+        // ---- the piece's partial: o[b][i][c] is head 2t + (c & 1), column 32b + 4g + 2i + (c >> 1) ----
+        #pragma unroll
+        for (int offset = 4; offset < 32; offset *= 2) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, offset);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, offset);
+        }
+        float* mine = a.partial + size_t(use.piece) * kPartialFloats;
+        #pragma unroll
+        for (int b = 0; b < 8; ++b)
+            #pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int column = 32 * b + 4 * g + 2 * i;
+                *reinterpret_cast<float2*>(mine + (2 * t) * 258 + column) = make_float2(o[b][i][0], o[b][i][2]);
+                *reinterpret_cast<float2*>(mine + (2 * t + 1) * 258 + column) = make_float2(o[b][i][1], o[b][i][3]);
+            }
+        if (g == 0) {
+            mine[(2 * t) * 258 + 256] = m0; mine[(2 * t) * 258 + 257] = l0;
+            mine[(2 * t + 1) * 258 + 256] = m1; mine[(2 * t + 1) * 258 + 257] = l1;
+        }
+        ++use.piece;
+        use.load(a);
+    }
+}
+
+// Block = (segment, head of the group); thread = output column. The pieces' partials combined as
+// gpu/sparse_attention_compute.hpp:139-170 does: M = max of maxima, factor = exp(max - M) (here
+// exp2: the maxima are kept in the exp2 domain), out = sum factor * acc / sum factor * denominator.
+__global__ void __launch_bounds__(256) qsa_decode_merge_kernel(const Segment* __restrict__ segments, const float* __restrict__ partial,
+                                                               uint32_t group, float* __restrict__ out) {
+    const Segment segment = segments[blockIdx.x];
+    const uint32_t head = blockIdx.y, column = threadIdx.x;
+    const float* first = partial + size_t(segment.first_piece) * kPartialFloats + head * 258;
+    float top = -INFINITY;
+    for (uint32_t piece = 0; piece < segment.pieces; ++piece) top = fmaxf(top, first[size_t(piece) * kPartialFloats + 256]);
+    float numerator = 0.0f, denominator = 0.0f;
+    for (uint32_t piece = 0; piece < segment.pieces; ++piece) {
+        const float* at = first + size_t(piece) * kPartialFloats;
+        const float factor = fast_exp2(at[256] - top);
+        denominator = fmaf(factor, at[257], denominator);
+        numerator = fmaf(factor, at[column], numerator);
+    }
+    out[size_t(segment.q_offset) + size_t(head) * 256 + column] = numerator / denominator;
+    (void)group;
+}
+
+// ---- host: the work list ----
+struct DecodePlan {
+    uint32_t segments = 0, pieces = 0, virtual_warps = 0, ctas = 0, group = 0;
+    uint64_t sequences = 0, heads = 0, kv_heads = 0;
+    uint64_t kv_bytes = 0;
+    // device tables, one allocation: segments | pieces | warp_piece
+    void* tables = nullptr;
+    size_t segment_offset = 0, piece_offset = 0, warp_offset = 0, table_bytes = 0;
+    float* partial = nullptr;
+    int* status = nullptr;
+    bool owns = false;
+};
+
+struct HostTables {
+    std::vector<Segment> segments;
+    std::vector<Piece> pieces;
+    std::vector<uint32_t> warp_piece;
+};
+
+// Cuts the segments' tiles into equal runs, one per virtual warp (at least `min_tiles` each).
+static void build_tables(const std::vector<const uint8_t*>& states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
+                         uint64_t heads, uint64_t kv_heads, uint32_t warps_available, HostTables& out) {
+    const uint64_t group = heads / kv_heads;
+    uint64_t total_tiles = 0;
+    for (uint64_t s = 0; s < sequences; ++s) total_tiles += (lengths[s] + kTileKeys - 1) / kTileKeys * kv_heads;
+    constexpr uint64_t min_tiles = 8;
+    const uint64_t per_warp = std::max<uint64_t>(min_tiles, (total_tiles + warps_available - 1) / warps_available);
+    out.segments.clear(); out.pieces.clear(); out.warp_piece.clear();
+    out.warp_piece.push_back(0);
+    uint64_t room = per_warp;   // tiles the current warp may still take
+    for (uint64_t s = 0; s < sequences; ++s)
+        for (uint64_t kv = 0; kv < kv_heads; ++kv) {
+            Segment segment{};
+            segment.keys = states[s] + kv * contexts[s] * kv_row_q8;
+            segment.values = states[s] + (kv_heads + kv) * contexts[s] * kv_row_q8;
+            segment.q_offset = uint32_t((s * heads + kv * group) * 256);
+            segment.first_piece = uint32_t(out.pieces.size());
+            segment.length = uint32_t(lengths[s]);
+            uint64_t key = 0;
+            while (key < lengths[s]) {
+                if (!room) { out.warp_piece.push_back(uint32_t(out.pieces.size())); room = per_warp; }
+                const uint64_t tiles_left = (lengths[s] - key + kTileKeys - 1) / kTileKeys, take = std::min(room, tiles_left);
+                const uint64_t end = std::min<uint64_t>(lengths[s], key + take * kTileKeys);
+                out.pieces.push_back(Piece{uint32_t(out.segments.size()), uint32_t(key), uint32_t(end), 0});
+                room -= take;
+                key = end;
+            }
+            segment.pieces = uint32_t(out.pieces.size()) - segment.first_piece;
+            out.segments.push_back(segment);
+        }
+    out.warp_piece.push_back(uint32_t(out.pieces.size()));
+}
+
+static void validate_batch(Device& d, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
+                           uint64_t heads, uint64_t kv_heads, std::vector<const uint8_t*>& checked, uint64_t& kv_bytes) {
+    if (d.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's decode attention reads Q8_0 K/V rows only");
+    if (!states || !contexts || !lengths || !sequences || sequences > 65535 || !heads || !kv_heads || heads % kv_heads ||
+        heads / kv_heads > 8 || heads > 1024)
+        throw std::runtime_error("invalid Straydog attention dimensions");
+    checked.resize(sequences);
+    kv_bytes = 0;
+    for (uint64_t s = 0; s < sequences; ++s) {
+        if (!contexts[s] || contexts[s] > (uint64_t(1) << 24) || !lengths[s] || lengths[s] > contexts[s])
+            throw std::runtime_error("invalid Straydog attention dimensions");
+        span(d, states[s], checked_product({contexts[s], 2 * kv_heads, kv_row_q8}), "a K/V state");
+        if (reinterpret_cast<uintptr_t>(states[s]) % 16) throw std::runtime_error("a Straydog K/V state must be 16-byte aligned");
+        checked[s] = static_cast<const uint8_t*>(states[s]);
+        kv_bytes += lengths[s] * 2 * kv_heads * kv_row_q8;
+    }
+}
+
+static void upload_tables(Device& d, const HostTables& host, DecodePlan& plan, void* tables, void* staging) {
+    plan.segment_offset = 0;
+    plan.piece_offset = (host.segments.size() * sizeof(Segment) + 255) / 256 * 256;
+    plan.warp_offset = plan.piece_offset + (host.pieces.size() * sizeof(Piece) + 255) / 256 * 256;
+    auto* stage = static_cast<uint8_t*>(staging);
+    std::memcpy(stage + plan.segment_offset, host.segments.data(), host.segments.size() * sizeof(Segment));
+    std::memcpy(stage + plan.piece_offset, host.pieces.data(), host.pieces.size() * sizeof(Piece));
+    std::memcpy(stage + plan.warp_offset, host.warp_piece.data(), host.warp_piece.size() * 4);
+    SDB_CHECK(cudaMemcpyAsync(tables, stage, plan.table_bytes, cudaMemcpyHostToDevice, d.stream));
+    plan.tables = tables;
+}
+
+static size_t table_bytes_of(const HostTables& host) {
+    return (host.segments.size() * sizeof(Segment) + 255) / 256 * 256 + (host.pieces.size() * sizeof(Piece) + 255) / 256 * 256 +
+           host.warp_piece.size() * 4 + 256;
+}
+
+static void fill_plan(Device& d, const HostTables& host, DecodePlan& plan, uint64_t sequences, uint64_t heads, uint64_t kv_heads) {
+    plan.segments = uint32_t(host.segments.size());
+    plan.pieces = uint32_t(host.pieces.size());
+    plan.virtual_warps = uint32_t(host.warp_piece.size() - 1);
+    plan.ctas = std::min<uint32_t>(uint32_t(d.sms), plan.virtual_warps);
+    plan.group = uint32_t(heads / kv_heads);
+    plan.sequences = sequences; plan.heads = heads; plan.kv_heads = kv_heads;
+    plan.table_bytes = table_bytes_of(host);
+}
+
+static void run_plan(Device& d, const DecodePlan& plan, float scale, const void* q, float* out) {
+    static bool configured[64] = {};
+    if (!configured[d.ordinal & 63]) {
+        SDB_CHECK(cudaFuncSetAttribute(qsa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSmem)));
+        configured[d.ordinal & 63] = true;
+    }
+    DecodeArgs args{};
+    auto* base = static_cast<uint8_t*>(plan.tables);
+    args.segments = reinterpret_cast<const Segment*>(base + plan.segment_offset);
+    args.pieces = reinterpret_cast<const Piece*>(base + plan.piece_offset);
+    args.warp_piece = reinterpret_cast<const uint32_t*>(base + plan.warp_offset);
+    args.q = static_cast<const __half*>(q);
+    args.partial = plan.partial;
+    args.virtual_warps = plan.virtual_warps;
+    args.ctas = plan.ctas;
+    args.group = plan.group;
+    args.scale_log2 = scale * 1.4426950408889634f;
+    args.status = plan.status;
+    qsa_decode_kernel<<<plan.ctas, kWarps * 32, kDecodeSmem, d.stream>>>(args);
+    qsa_decode_merge_kernel<<<dim3(plan.segments, plan.group), 256, 0, d.stream>>>(args.segments, plan.partial, plan.group, out);
+    d.launches += 2;
+}
+
+// The status word of the device's decode kernels (a wait that gave up sets it), read after a synchronising call.
+static int* status_word(Device& d) {
+    static std::map<int, int*> words;
+    static std::mutex mutex;
+    std::lock_guard<std::mutex> lock(mutex);
+    auto found = words.find(d.ordinal);
+    if (found != words.end()) return found->second;
+    int* word = nullptr;
+    SDB_CHECK(cudaMalloc(&word, 256));
+    SDB_CHECK(cudaMemset(word, 0, 256));
+    words[d.ordinal] = word;
+    return word;
+}
+
+void qsa_decode_dense(Device& d, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
+                      uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out) {
+    std::vector<const uint8_t*> checked;
+    uint64_t kv_bytes = 0;
+    validate_batch(d, states, contexts, lengths, sequences, heads, kv_heads, checked, kv_bytes);
+    HostTables host;
+    build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(d.sms) * kWarps, host);
+    DecodePlan plan;
+    fill_plan(d, host, plan, sequences, heads, kv_heads);
+    ensure(d, d.pinned, d.pinned_bytes, plan.table_bytes, true);
+    ensure(d, d.tables, d.tables_bytes, plan.table_bytes);
+    ensure(d, d.partial, d.partial_bytes, size_t(plan.pieces) * kPartialFloats * 4);
+    plan.partial = static_cast<float*>(d.partial);
+    plan.status = status_word(d);
+    // (the staging buffer is reused by the next call: wait for the previous upload to have left it)
+    SDB_CHECK(cudaStreamSynchronize(d.stream));
+    upload_tables(d, host, plan, d.tables, d.pinned);
+    run_plan(d, plan, scale, q, out);
+}
+
+}  // namespace sdb
+
+using namespace sdb;
+
+extern "C" {
+
+int sdx_qsa_decode(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
+                   uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out) {
+    SDB_OP_BEGIN
+    span(value, q, checked_product({sequences, heads, 256, 2}), "attention queries");
+    span(value, out, checked_product({sequences, heads, 256, 4}), "an attention output");
+    qsa_decode_dense(value, states, contexts, lengths, sequences, heads, kv_heads, scale, q, out);
+    SDB_OP_END
+}
+
+void* sdx_qsa_plan(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
+                   uint64_t heads, uint64_t kv_heads) {
+    try {
+        auto& value = device(handle);
+        std::vector<const uint8_t*> checked;
+        uint64_t kv_bytes = 0;
+        validate_batch(value, states, contexts, lengths, sequences, heads, kv_heads, checked, kv_bytes);
+        HostTables host;
+        build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(value.sms) * kWarps, host);
+        auto plan = std::make_unique<DecodePlan>();
+        fill_plan(value, host, *plan, sequences, heads, kv_heads);
+        plan->kv_bytes = kv_bytes;
+        plan->owns = true;
+        void* tables = nullptr;
+        SDB_CHECK(cudaMalloc(&tables, plan->table_bytes));
+        void* partial = nullptr;
+        if (cudaMalloc(&partial, size_t(plan->pieces) * kPartialFloats * 4) != cudaSuccess) { cudaFree(tables); SDB_CHECK(cudaGetLastError()); }
+        plan->partial = static_cast<float*>(partial);
+        plan->status = status_word(value);
+        std::vector<uint8_t> staging(plan->table_bytes);
+        upload_tables(value, host, *plan, tables, staging.data());
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        return plan.release();
+    } catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+int sdx_qsa_plan_run(void* handle, void* plan, float scale, const void* q, float* out) {
+    SDB_OP_BEGIN
+    if (!plan) throw std::runtime_error("null Straydog decode plan");
+    const auto& p = *static_cast<const DecodePlan*>(plan);
+    span(value, q, checked_product({p.sequences, p.heads, 256, 2}), "attention queries");
+    span(value, out, checked_product({p.sequences, p.heads, 256, 4}), "an attention output");
+    run_plan(value, p, scale, q, out);
+    SDB_OP_END
+}
+
+int sdx_qsa_plan_info(void* plan, uint64_t* kv_bytes, uint64_t* pieces, uint64_t* ctas, uint64_t* virtual_warps) {
+    if (!plan) { last_error = "null Straydog decode plan"; return -1; }
+    const auto& p = *static_cast<const DecodePlan*>(plan);
+    if (kv_bytes) *kv_bytes = p.kv_bytes;
+    if (pieces) *pieces = p.pieces;
+    if (ctas) *ctas = p.ctas;
+    if (virtual_warps) *virtual_warps = p.virtual_warps;
+    return 0;
+}
+
+int sdx_qsa_plan_release(void* handle, void* plan) {
+    SDB_OP_BEGIN
+    if (!plan) throw std::runtime_error("null Straydog decode plan");
+    auto* p = static_cast<DecodePlan*>(plan);
+    SDB_CHECK(cudaStreamSynchronize(value.stream));
+    if (p->owns) { cudaFree(p->tables); cudaFree(p->partial); }
+    delete p;
+    SDB_OP_END
+}
+
+// 1 when a bounded wait inside a decode kernel gave up since the last call (the word is cleared), else 0.
+int sdx_decode_status(void* handle) {
+    try {
+        auto& value = device(handle);
+        int* word = status_word(value);
+        int host = 0;
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        SDB_CHECK(cudaMemcpy(&host, word, 4, cudaMemcpyDeviceToHost));
+        if (host) SDB_CHECK(cudaMemset(word, 0, 4));
+        return host;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+}  // extern "C"
