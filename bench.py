@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the Q8_0 GQA decode attention path (the ragged 64-sequence batch).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--scaling weak|strong]
+
+One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE for N > 1). A step is one pass of the
+decode attention over one batch: 64 sequences with context lengths uniform in [1024, 32768], 16 query
+/ 2 K/V heads of 256, Q8_0 K/V rows, FP16 queries, FP32 output. Sequences are independent, so ranks
+share no data: with --scaling weak (default) every rank decodes its own seeded 64-sequence batch; with
+--scaling strong the one 64-sequence batch is dealt over the ranks longest first.
+
+Prints ONE JSON line (rank 0). `value` is K/V gigabytes streamed per second by the whole job with
+everything resident in HBM; `e2e` is the same metric through sdx_attention_batch with host buffers
+(queries, new K/V rows and outputs copied inside the timed call). `roofline` times the streaming
+kernel alone with CUDA events on its own stream. `cpu_baseline` times the CPU oracle on a bounded
+sample. `--impl reference` times the reference's scalar host path (the CPU oracle port) instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HEADS, KV_HEADS, DIM, ROW = 16, 2, 256, 272
+SCALE = 1.0 / 16.0
+SEED = 20261125
+METRIC, UNIT = "decode_attn_kv_gbps", "GB/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.process = None
+        try:
+            self.process = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                             "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def count(self):
+        try:
+            with open(self.file.name) as f:
+                return sum(1 for _ in f)
+        except OSError:
+            return 0
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.process is None:
+            return out
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        self.file.flush()
+        self.file.seek(0)
+        clocks, reasons, power = [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                out["sm_max_mhz"] = float(parts[1])
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, state in zip(names, parts[4:8]):
+                if state.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if clocks:
+            out["sm_mhz"] = statistics.median(clocks)
+            out["samples"] = len(clocks)
+            out["power_w_max"] = max(power)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def batch_for(rank, world, scaling):
+    """(lengths of this rank's sequences, their seeds)."""
+    from straydog_b200.synthetic import partition_longest_first, ragged_lengths
+    if scaling == "weak":
+        lengths = ragged_lengths(SEED + rank)
+        return lengths, [SEED * 1000 + rank * 100 + i for i in range(len(lengths))]
+    lengths = ragged_lengths(SEED)
+    mine = partition_longest_first(lengths, world)[rank]
+    return [lengths[i] for i in mine], [SEED * 1000 + i for i in mine]
+
+
+def make_states(lengths, seeds):
+    from straydog_b200.synthetic import q8_state
+    return [q8_state(np.random.default_rng(seed), length, KV_HEADS) for length, seed in zip(lengths, seeds)]
+
+
+def cpu_sample(lengths, seeds, budget_s, want_threads=None):
+    """Times the CPU oracle on the first sequences of the batch until about budget_s seconds are spent."""
+    import oracle
+    from straydog_b200.synthetic import queries_f16
+    spent, nbytes, used = 0.0, 0, 0
+    rng = np.random.default_rng(SEED)
+    for length, seed in zip(lengths, seeds):
+        state = make_states([length], [seed])[0]
+        q = queries_f16(rng, HEADS, DIM)
+        t0 = time.perf_counter()
+        oracle.gqa_decode_q8(state, length, length, HEADS, KV_HEADS, q, SCALE)
+        spent += time.perf_counter() - t0
+        nbytes += length * 2 * KV_HEADS * ROW
+        used += 1
+        if spent >= budget_s:
+            break
+    return nbytes / spent / 1e9, used, nbytes, spent, oracle.threads()
+
+
+def run_reference(args, rank, world):
+    """The reference's scalar host path (its CPU restatement: no part of the reference's CPU code covers attention
+    on the host beyond the scalar definition the oracle restates), on all host threads, rank 0 only."""
+    if rank != 0:
+        return
+    lengths, seeds = batch_for(0, 1, "weak")
+    per_step = max(2.0, min(20.0, 150.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_sample(lengths, seeds, per_step / 4)
+    times, total_bytes, used = [], 0, 0
+    for _ in range(args.steps):
+        gbps, used, nbytes, spent, threads = cpu_sample(lengths, seeds, per_step)
+        times.append(spent)
+        total_bytes += nbytes
+    total = sum(times)
+    value = total_bytes / total / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": total / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic (seeded)", "config": workload_config(lengths, "n/a: host memory"),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": f"first {used} of 64 sequences per step ({total_bytes // args.steps} K/V bytes)"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "tokens_per_s": used * args.steps / total}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(lengths, l2):
+    return {"workload": "config 1: ragged Q8_0 GQA decode batch, 64 sequences x 1 query token, context uniform in [1024, 32768], "
+                        "16 query / 2 K/V heads, head_dim 256, FP16 queries, softmax scale 1/16, FP32 output",
+            "sequences_per_gpu": len(lengths), "kv_bytes_per_gpu": sum(lengths) * 2 * KV_HEADS * ROW, "seed": SEED, "l2": l2}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    parser.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = parser.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    from straydog_b200.backend import Backend
+    from straydog_b200.synthetic import queries_f16
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU: the attention library has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    barrier_token = torch.zeros(1, device="cuda")
+
+    def barrier():
+        if world > 1:
+            dist.all_reduce(barrier_token)
+        torch.cuda.synchronize()
+
+    lengths, seeds = batch_for(rank, world, args.scaling)
+    kv_bytes = sum(lengths) * 2 * KV_HEADS * ROW
+    gpu = Backend(local, kv_bytes + (2 << 30))
+    states_np = make_states(lengths, seeds)
+    states = []
+    for s in states_np:
+        buffer = gpu.allocate(s.nbytes)
+        gpu.write(buffer, s)
+        states.append(buffer)
+    n = len(lengths)
+    rng = np.random.default_rng(SEED + 7 + rank)
+    q_np = queries_f16(rng, n, HEADS, DIM)
+    q = gpu.upload(q_np)
+    out = gpu.buffer(n * HEADS * DIM * 4)
+    plan = gpu.qsa_plan(states, lengths, lengths, HEADS, KV_HEADS)
+    info = gpu.qsa_plan_info(plan)
+
+    # ---- device-resident: K steps of the planned decode (two kernel launches each) ----
+    sampler = ClockSampler(local)
+    for _ in range(args.warmup):
+        gpu.qsa_plan_run(plan, SCALE, q.pointer, out.pointer)
+    gpu.synchronize()
+
+    def load_for(seconds, until_samples=None):
+        """Untimed back-to-back steps: the clock samples bracket the timed region under the same load."""
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < seconds and (until_samples is None or sampler.count() < until_samples):
+            for _ in range(20):
+                gpu.qsa_plan_run(plan, SCALE, q.pointer, out.pointer)
+            gpu.synchronize()
+    load_for(3.0, until_samples=2)
+    start, stop = gpu.event(), gpu.event()
+    marks = [(gpu.event(), gpu.event()) for _ in range(args.steps)]
+    barrier()
+    launches_before = gpu.launch_count()
+    gpu.record(start)
+    for before, after in marks:
+        gpu.qsa_plan_run_marked(plan, SCALE, q.pointer, out.pointer, before, after)
+    gpu.record(stop)
+    gpu.synchronize()
+    launches = gpu.launch_count() - launches_before
+    barrier()
+    device_ms = Backend.elapsed_ms(start, stop)
+    kernel_ms = [Backend.elapsed_ms(b, a) for b, a in marks]
+    load_for(0.5)
+    clocks = sampler.stop()
+    clocks["note"] = "nvidia-smi every 100 ms over the untimed back-to-back steps just before and after the timed region and the region itself"
+    if gpu.decode_status() != 0:
+        raise SystemExit("a bounded wait inside the decode kernel gave up: the result is invalid")
+
+    # ---- end to end: host buffers in, host buffers out, every step ----
+    q_host = torch.from_numpy(q_np.view(np.int16).copy()).pin_memory()
+    k_host = torch.from_numpy(rng.normal(0, 1, (n, KV_HEADS, DIM)).astype(np.float32)).pin_memory()
+    v_host = torch.from_numpy(rng.normal(0, 1, (n, KV_HEADS, DIM)).astype(np.float32)).pin_memory()
+    out_host = torch.empty((n, HEADS, DIM), dtype=torch.float32).pin_memory()
+    bases = [l - 1 for l in lengths]
+    import ctypes as C
+    from straydog_b200.backend import lib, _check
+    ptrs = (C.c_void_p * n)(*[s.pointer for s in states])
+    ctx = (C.c_uint64 * n)(*lengths)
+    bs = (C.c_uint64 * n)(*bases)
+
+    def e2e_step():
+        _check(lib().sdx_attention_batch(gpu.handle, ptrs, ctx, bs, n, HEADS, KV_HEADS, SCALE, q_host.data_ptr(), k_host.data_ptr(),
+                                         v_host.data_ptr(), out_host.data_ptr()))
+    for _ in range(args.warmup):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    # ---- max over ranks, sums over ranks ----
+    stats = torch.tensor([device_ms, e2e_s * 1e3, statistics.mean(kernel_ms)], device="cuda", dtype=torch.float64)
+    sums = torch.tensor([float(kv_bytes), float(n)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    device_ms_max, e2e_ms_max, kernel_ms_mean = (float(x) for x in stats.cpu())
+    total_bytes, total_sequences = (float(x) for x in sums.cpu())
+
+    if rank == 0:
+        peak, peak_source = measured_peaks()
+        value = total_bytes * args.steps / (device_ms_max / 1e3) / 1e9
+        achieved = kv_bytes / (statistics.mean(kernel_ms) / 1e3) / 1e9
+        cpu_gbps, cpu_used, cpu_bytes, cpu_spent, cpu_threads = cpu_sample(lengths, seeds, args.cpu_seconds)
+        # parity spot check of the timed output against the oracle (one short sequence), so a wrong kernel cannot post a number
+        import oracle
+        shortest = int(np.argmin(lengths))
+        want = oracle.gqa_decode_q8(states_np[shortest], lengths[shortest], lengths[shortest], HEADS, KV_HEADS, q_np[shortest], SCALE, f64=True)
+        got = gpu.read(out, np.float32, (n, HEADS, DIM))[shortest]
+        error = float(np.abs(got - want).max())
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": device_ms_max / args.steps, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+            "dtype": "f16 x int8 products, f32 accumulate", "data": "synthetic (seeded)",
+            "config": workload_config(lengths, "inputs larger than L2 (1.2 GB of K/V per step against 126 MB)"),
+            "tokens_per_s": total_sequences * args.steps / (device_ms_max / 1e3),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": peak_source, "kernel": "qsa_decode_kernel", "kernel_ms": statistics.mean(kernel_ms),
+                         "frac_of_nominal_8tbs": achieved / 8000.0},
+            "cpu_baseline": {"value": cpu_gbps, "unit": UNIT, "cores": cpu_threads, "kind": "port",
+                             "sample": f"first {cpu_used} of {n} sequences ({cpu_bytes} K/V bytes, {cpu_spent:.1f} s)"},
+            "e2e": {"value": total_bytes * args.steps / (e2e_ms_max / 1e3) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": int(q_host.nbytes + k_host.nbytes + v_host.nbytes), "d2h_bytes_per_step": int(out_host.nbytes),
+                    "ms_per_step": e2e_ms_max / args.steps, "tokens_per_s": total_sequences * args.steps / (e2e_ms_max / 1e3)},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "plan": info, "max_abs_error_vs_oracle": error,
+        }
+        print(json.dumps(line), flush=True)
+    gpu.qsa_plan_release(plan)
+    gpu.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

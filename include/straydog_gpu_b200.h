@@ -87,6 +87,11 @@ int sdx_synchronize(void* handle);
 void* sdx_stream(void* handle);
 /* Kernels launched through the handle so far. */
 uint64_t sdx_launch_count(void* handle);
+/* CUDA events on the handle's stream, for timing a region or one kernel from a host language without CUDA bindings. */
+void* sdx_event_create(void);
+int sdx_event_record(void* handle, void* event);
+int sdx_event_elapsed_ms(void* before, void* after, float* ms);
+void sdx_event_destroy(void* event);
 
 /* Appends `steps` tokens' keys and values ([steps][kv_heads][256] F32, device) to a Q8_0 state at rows
    base..: the reference's write_attention_kv (gpu/kernels.cpp:79-98) for any number of K/V heads. */
@@ -106,6 +111,8 @@ int sdx_qsa_decode(void* handle, const void* const* states, const uint64_t* cont
 void* sdx_qsa_plan(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
                    uint64_t sequences, uint64_t heads, uint64_t kv_heads);
 int sdx_qsa_plan_run(void* handle, void* plan, float scale, const void* q, float* out);
+/* sdx_qsa_plan_run with `before` recorded ahead of the streaming kernel and `after` behind it (ahead of the merge). */
+int sdx_qsa_plan_run_marked(void* handle, void* plan, float scale, const void* q, float* out, void* before, void* after);
 int sdx_qsa_plan_info(void* plan, uint64_t* kv_bytes, uint64_t* pieces, uint64_t* ctas, uint64_t* virtual_warps);
 int sdx_qsa_plan_release(void* handle, void* plan);
 /* 1 when a bounded wait inside a decode kernel gave up since the last call (cleared by the call), 0 if none. */

@@ -41,11 +41,16 @@ SIGNATURES = {
     "sdx_synchronize": ([p], i32),
     "sdx_stream": ([p], p),
     "sdx_launch_count": ([p], u64),
+    "sdx_event_create": ([], p),
+    "sdx_event_record": ([p, p], i32),
+    "sdx_event_elapsed_ms": ([p, p, C.POINTER(C.c_float)], i32),
+    "sdx_event_destroy": ([p], None),
     "sdx_kv_write": ([p, p, u64, u64, u64, u64, p, p], i32),
     "sdx_kv_decode_rows": ([p, p, u64, p], i32),
     "sdx_qsa_decode": ([p, pp, pu64, pu64, u64, u64, u64, f32, p, p], i32),
     "sdx_qsa_plan": ([p, pp, pu64, pu64, u64, u64, u64], p),
     "sdx_qsa_plan_run": ([p, p, f32, p, p], i32),
+    "sdx_qsa_plan_run_marked": ([p, p, f32, p, p, p, p], i32),
     "sdx_qsa_plan_info": ([p, pu64, pu64, pu64, pu64], i32),
     "sdx_qsa_plan_release": ([p, p], i32),
     "sdx_decode_status": ([p], i32),
@@ -53,12 +58,15 @@ SIGNATURES = {
 }
 
 
-def load() -> C.CDLL:
-    if not os.path.exists(LIB_PATH):
+def load(path: str = LIB_PATH, reference_abi_only: bool = False) -> C.CDLL:
+    """reference_abi_only: declare the sd_* entries alone (another build of the reference ABI has no sdx_* additions)."""
+    if not os.path.exists(path):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m straydog_b200.build` (needs nvcc; there is no CPU fallback)")
-    lib = C.CDLL(LIB_PATH)
+            f"{path} is missing: build it with `python -m straydog_b200.build` (needs nvcc; there is no CPU fallback)")
+    lib = C.CDLL(path)
     for name, (args, res) in SIGNATURES.items():
+        if reference_abi_only and name.startswith("sdx_"):
+            continue
         f = getattr(lib, name)   # AttributeError if the library does not export what the header declares
         f.argtypes, f.restype = args, res
     return lib

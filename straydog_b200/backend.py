@@ -26,13 +26,13 @@ class StraydogError(RuntimeError):
     pass
 
 
-def _fail():
-    raise StraydogError(lib().sd_error().decode("utf-8", "replace"))
+def _fail(library=None):
+    raise StraydogError((library or lib()).sd_error().decode("utf-8", "replace"))
 
 
-def _check(result):
+def _check(result, library=None):
     if result is None or (isinstance(result, int) and result < 0):
-        _fail()
+        _fail(library)
     return result
 
 
@@ -58,15 +58,21 @@ class Buffer:
 
 
 class Backend:
-    def __init__(self, ordinal=0, budget=1 << 30):
-        self.handle = lib().sd_create(ordinal, budget)
+    def __init__(self, ordinal=0, budget=1 << 30, library=None):
+        """library: a ctypes handle of another build of the same sd_* ABI (tests/golden drives the
+        reference's own library through this wrapper); default: libstraydog_gpu_b200.so."""
+        self.lib = library or lib()
+        self.handle = self.lib.sd_create(ordinal, budget)
         if not self.handle:
-            _fail()
+            _fail(self.lib)
         self.ordinal = ordinal
+
+    def _c(self, result):
+        return _check(result, self.lib)
 
     def close(self):
         if self.handle:
-            lib().sd_destroy(self.handle)
+            self.lib.sd_destroy(self.handle)
             self.handle = None
 
     def __enter__(self):
@@ -83,9 +89,9 @@ class Backend:
 
     # ---- memory ----
     def buffer(self, size):
-        pointer = lib().sd_buffer(self.handle, size)
+        pointer = self.lib.sd_buffer(self.handle, size)
         if not pointer:
-            _fail()
+            _fail(self.lib)
         return Buffer(self, pointer, size)
 
     def upload(self, array):
@@ -95,18 +101,18 @@ class Backend:
         return buffer
 
     def allocate(self, size):
-        pointer = lib().sd_allocate(self.handle, size)
+        pointer = self.lib.sd_allocate(self.handle, size)
         if not pointer:
-            _fail()
+            _fail(self.lib)
         return Buffer(self, pointer, size)
 
     def write_buffer(self, buffer, offset, array):
         array = np.ascontiguousarray(array)
-        _check(lib().sd_buffer_write(self.handle, buffer.pointer, offset, _host(array), array.nbytes))
+        self._c(self.lib.sd_buffer_write(self.handle, buffer.pointer, offset, _host(array), array.nbytes))
 
     def read_buffer(self, buffer, offset, out):
         assert out.flags.c_contiguous
-        _check(lib().sd_buffer_read(self.handle, buffer.pointer, offset, _host(out), out.nbytes))
+        self._c(self.lib.sd_buffer_read(self.handle, buffer.pointer, offset, _host(out), out.nbytes))
         return out
 
     def read(self, buffer, dtype, shape, offset=0):
@@ -114,58 +120,73 @@ class Backend:
 
     def write(self, buffer, array):
         array = np.ascontiguousarray(array)
-        _check(lib().sd_write(self.handle, buffer.pointer, _host(array), array.nbytes))
+        self._c(self.lib.sd_write(self.handle, buffer.pointer, _host(array), array.nbytes))
 
     def download(self, buffer, out):
-        _check(lib().sd_download(self.handle, buffer.pointer, _host(out), out.nbytes))
+        self._c(self.lib.sd_download(self.handle, buffer.pointer, _host(out), out.nbytes))
         return out
 
     def zero(self, buffer):
-        _check(lib().sd_zero(self.handle, buffer.pointer))
+        self._c(self.lib.sd_zero(self.handle, buffer.pointer))
 
     def release(self, buffer):
-        _check(lib().sd_release(self.handle, buffer.pointer))
+        self._c(self.lib.sd_release(self.handle, buffer.pointer))
         buffer.pointer = None
 
     def memory(self):
         used, budget = C.c_uint64(), C.c_uint64()
-        _check(lib().sd_memory(self.handle, C.byref(used), C.byref(budget)))
+        self._c(self.lib.sd_memory(self.handle, C.byref(used), C.byref(budget)))
         return used.value, budget.value
 
     def synchronize(self):
-        _check(lib().sdx_synchronize(self.handle))
+        self._c(self.lib.sdx_synchronize(self.handle))
 
     def stream(self):
-        return lib().sdx_stream(self.handle)
+        return self.lib.sdx_stream(self.handle)
+
+    def event(self):
+        e = self.lib.sdx_event_create()
+        if not e:
+            _fail(self.lib)
+        return e
+
+    def record(self, event):
+        self._c(self.lib.sdx_event_record(self.handle, event))
+
+    @staticmethod
+    def elapsed_ms(before, after):
+        ms = C.c_float()
+        _check(lib().sdx_event_elapsed_ms(before, after, C.byref(ms)))
+        return ms.value
 
     def launch_count(self):
-        return int(lib().sdx_launch_count(self.handle))
+        return int(self.lib.sdx_launch_count(self.handle))
 
     # ---- K/V ----
     def kv_format(self, row):
-        _check(lib().sd_kv_format(self.handle, row))
+        self._c(self.lib.sd_kv_format(self.handle, row))
 
     def kv_stage(self, buffer, rows):
-        _check(lib().sd_kv_stage(self.handle, buffer.pointer, rows))
+        self._c(self.lib.sd_kv_stage(self.handle, buffer.pointer, rows))
 
     def kv_write(self, state, context, kv_heads, base, steps, keys, values):
-        _check(lib().sdx_kv_write(self.handle, state.pointer, context, kv_heads, base, steps, keys.pointer, values.pointer))
+        self._c(self.lib.sdx_kv_write(self.handle, state.pointer, context, kv_heads, base, steps, keys.pointer, values.pointer))
 
     def kv_decode_rows(self, rows_pointer, count, out):
-        _check(lib().sdx_kv_decode_rows(self.handle, rows_pointer, count, out.pointer))
+        self._c(self.lib.sdx_kv_decode_rows(self.handle, rows_pointer, count, out.pointer))
 
     # ---- Qwen-style attention ----
     def attention_sequence(self, state, context, base, steps, selected, packed_input):
         """sd_attention_sequence: host floats in, host floats out ([steps, 24, 256])."""
         packed_input = np.ascontiguousarray(packed_input, np.float32)
         out = np.empty(steps * 24 * 256, np.float32)
-        _check(lib().sd_attention_sequence(self.handle, state.pointer, context, base, steps, selected, _host(packed_input),
+        self._c(self.lib.sd_attention_sequence(self.handle, state.pointer, context, base, steps, selected, _host(packed_input),
                                            packed_input.size, _host(out), out.size))
         return out.reshape(steps, 24, 256)
 
     def attention(self, q, keys, values, context, positions, rows, heads, kv_heads, dim, scale, gate, scratch, out):
         """sd_op_attention over device pointers (ints); gate and scratch may be None."""
-        _check(lib().sd_op_attention(self.handle, q, keys, values, context, positions, rows, heads, kv_heads, dim, scale, gate,
+        self._c(self.lib.sd_op_attention(self.handle, q, keys, values, context, positions, rows, heads, kv_heads, dim, scale, gate,
                                      scratch.pointer if scratch else None, scratch.size if scratch else 0, out))
 
     def qsa_decode(self, states, contexts, lengths, heads, kv_heads, scale, q, out):
@@ -173,47 +194,50 @@ class Backend:
         ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])
         ctx = (C.c_uint64 * n)(*contexts)
         lens = (C.c_uint64 * n)(*lengths)
-        _check(lib().sdx_qsa_decode(self.handle, ptrs, ctx, lens, n, heads, kv_heads, scale, q, out))
+        self._c(self.lib.sdx_qsa_decode(self.handle, ptrs, ctx, lens, n, heads, kv_heads, scale, q, out))
 
     def qsa_plan(self, states, contexts, lengths, heads, kv_heads):
         n = len(states)
         ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])
         ctx = (C.c_uint64 * n)(*contexts)
         lens = (C.c_uint64 * n)(*lengths)
-        plan = lib().sdx_qsa_plan(self.handle, ptrs, ctx, lens, n, heads, kv_heads)
+        plan = self.lib.sdx_qsa_plan(self.handle, ptrs, ctx, lens, n, heads, kv_heads)
         if not plan:
-            _fail()
+            _fail(self.lib)
         return plan
 
     def qsa_plan_run(self, plan, scale, q, out):
-        _check(lib().sdx_qsa_plan_run(self.handle, plan, scale, q, out))
+        self._c(self.lib.sdx_qsa_plan_run(self.handle, plan, scale, q, out))
+
+    def qsa_plan_run_marked(self, plan, scale, q, out, before, after):
+        self._c(self.lib.sdx_qsa_plan_run_marked(self.handle, plan, scale, q, out, before, after))
 
     def qsa_plan_info(self, plan):
         vals = [C.c_uint64() for _ in range(4)]
-        _check(lib().sdx_qsa_plan_info(plan, *[C.byref(v) for v in vals]))
+        self._c(self.lib.sdx_qsa_plan_info(plan, *[C.byref(v) for v in vals]))
         return dict(zip(("kv_bytes", "pieces", "ctas", "virtual_warps"), [v.value for v in vals]))
 
     def qsa_plan_release(self, plan):
-        _check(lib().sdx_qsa_plan_release(self.handle, plan))
+        self._c(self.lib.sdx_qsa_plan_release(self.handle, plan))
 
     def decode_status(self):
-        return _check(lib().sdx_decode_status(self.handle))
+        return self._c(self.lib.sdx_decode_status(self.handle))
 
     def attention_batch(self, states, contexts, bases, heads, kv_heads, scale, q_host, k_host, v_host, out_host):
         n = len(states)
         ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])
         ctx = (C.c_uint64 * n)(*contexts)
         bs = (C.c_uint64 * n)(*bases)
-        _check(lib().sdx_attention_batch(self.handle, ptrs, ctx, bs, n, heads, kv_heads, scale, _host(q_host), _host(k_host),
+        self._c(self.lib.sdx_attention_batch(self.handle, ptrs, ctx, bs, n, heads, kv_heads, scale, _host(q_host), _host(k_host),
                                          _host(v_host), _host(out_host)))
         return out_host
 
     # ---- DeepSeek-style latent attention ----
     def attention_turns_reserve(self, rows, rope_dims):
-        _check(lib().sd_attention_turns_reserve(self.handle, rows, rope_dims))
+        self._c(self.lib.sd_attention_turns_reserve(self.handle, rows, rope_dims))
 
     def attention_turns_arm(self, rows):
-        _check(lib().sd_attention_turns_arm(self.handle, rows))
+        self._c(self.lib.sd_attention_turns_arm(self.handle, rows))
 
     def sparse_attention(self, q, raw, raw_rows, positions, window, compressed, selected, sinks, rows, heads, dim, scale, rope,
                          scratch, out):
@@ -221,15 +245,15 @@ class Backend:
         c_ptr, c_rows = compressed if compressed else (None, 0)
         s_ptr, selections = selected if selected else (None, 0)
         rope_dims, freq = rope if rope else (0, None)
-        _check(lib().sd_op_sparse_attention(self.handle, q, raw, raw_rows, positions, window, c_ptr, c_rows, s_ptr, selections, sinks,
+        self._c(self.lib.sd_op_sparse_attention(self.handle, q, raw, raw_rows, positions, window, c_ptr, c_rows, s_ptr, selections, sinks,
                                             rows, heads, dim, scale, rope_dims, freq, scratch.pointer if scratch else None,
                                             scratch.size if scratch else 0, out))
 
     def top_k(self, scores, rows, groups, k, out):
-        _check(lib().sd_op_top_k(self.handle, scores, rows, groups, k, out))
+        self._c(self.lib.sd_op_top_k(self.handle, scores, rows, groups, k, out))
 
     def to_bf16(self, x, count, out):
-        _check(lib().sd_op_to_bf16(self.handle, x, count, out))
+        self._c(self.lib.sd_op_to_bf16(self.handle, x, count, out))
 
 
 def device_count():

@@ -271,6 +271,31 @@ void* sdx_stream(void* handle) {
     catch (const std::exception& e) { last_error = e.what(); return nullptr; }
 }
 
+void* sdx_event_create(void) {
+    cudaEvent_t event = nullptr;
+    const cudaError_t error = cudaEventCreate(&event);
+    if (error != cudaSuccess) { last_error = cudaGetErrorString(error); return nullptr; }
+    return event;
+}
+
+int sdx_event_record(void* handle, void* event) {
+    try {
+        auto& value = device(handle);
+        SDB_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(event), value.stream));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sdx_event_elapsed_ms(void* before, void* after, float* ms) {
+    try {
+        SDB_CHECK(cudaEventSynchronize(static_cast<cudaEvent_t>(after)));
+        SDB_CHECK(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(before), static_cast<cudaEvent_t>(after)));
+        return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+void sdx_event_destroy(void* event) { if (event) cudaEventDestroy(static_cast<cudaEvent_t>(event)); }
+
 uint64_t sdx_launch_count(void* handle) {
     try { return device(handle).launches; }
     catch (const std::exception& e) { last_error = e.what(); return 0; }

@@ -383,7 +383,8 @@ static void fill_plan(Device& d, const HostTables& host, DecodePlan& plan, uint6
     plan.table_bytes = table_bytes_of(host);
 }
 
-static void run_plan(Device& d, const DecodePlan& plan, float scale, const void* q, float* out) {
+static void run_plan(Device& d, const DecodePlan& plan, float scale, const void* q, float* out, cudaEvent_t before = nullptr,
+                     cudaEvent_t after = nullptr) {
     static bool configured[64] = {};
     if (!configured[d.ordinal & 63]) {
         SDB_CHECK(cudaFuncSetAttribute(qsa_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kDecodeSmem)));
@@ -401,7 +402,9 @@ static void run_plan(Device& d, const DecodePlan& plan, float scale, const void*
     args.group = plan.group;
     args.scale_log2 = scale * 1.4426950408889634f;
     args.status = plan.status;
+    if (before) SDB_CHECK(cudaEventRecord(before, d.stream));
     qsa_decode_kernel<<<plan.ctas, kWarps * 32, kDecodeSmem, d.stream>>>(args);
+    if (after) SDB_CHECK(cudaEventRecord(after, d.stream));
     qsa_decode_merge_kernel<<<dim3(plan.segments, plan.group), 256, 0, d.stream>>>(args.segments, plan.partial, plan.group, out);
     d.launches += 2;
 }
@@ -488,6 +491,16 @@ int sdx_qsa_plan_run(void* handle, void* plan, float scale, const void* q, float
     span(value, q, checked_product({p.sequences, p.heads, 256, 2}), "attention queries");
     span(value, out, checked_product({p.sequences, p.heads, 256, 4}), "an attention output");
     run_plan(value, p, scale, q, out);
+    SDB_OP_END
+}
+
+int sdx_qsa_plan_run_marked(void* handle, void* plan, float scale, const void* q, float* out, void* before, void* after) {
+    SDB_OP_BEGIN
+    if (!plan) throw std::runtime_error("null Straydog decode plan");
+    const auto& p = *static_cast<const DecodePlan*>(plan);
+    span(value, q, checked_product({p.sequences, p.heads, 256, 2}), "attention queries");
+    span(value, out, checked_product({p.sequences, p.heads, 256, 4}), "an attention output");
+    run_plan(value, p, scale, q, out, static_cast<cudaEvent_t>(before), static_cast<cudaEvent_t>(after));
     SDB_OP_END
 }
 

@@ -1,0 +1,179 @@
+"""Seeded synthetic inputs of the benchmark configurations, shared by the tests, the smoke test and bench.py.
+
+Q8_0 K/V rows hold int8 values uniform in [-127, 127] and one FP16 scale per 32-value block drawn as
+|N(0, 0.02)|; queries are FP16 N(0, 1); latent rows are BF16 N(0, 0.05). The xorshift generators
+restate the ones the reference's GPU tests seed their inputs with
+(crates/straydog-engine/tests/attention_gpu.rs:10-20, ds_state_bf16_gpu.rs:13-24), so that those
+tests' exact inputs can be rebuilt.
+"""
+import numpy as np
+
+ROW_Q8 = 272
+M64 = (1 << 64) - 1
+
+
+def q8_state(rng, context, kv_heads, filled=None):
+    """uint8 [2*kv_heads, context, 272]: rows 0..filled-1 random, the rest zero."""
+    filled = context if filled is None else filled
+    state = np.zeros((2 * kv_heads, context, ROW_Q8), np.uint8)
+    values = rng.integers(-127, 128, size=(2 * kv_heads, filled, 256), dtype=np.int8)
+    scales = np.abs(rng.normal(0.0, 0.02, size=(2 * kv_heads, filled, 8))).astype(np.float16)
+    state[:, :filled, :256] = values.view(np.uint8)
+    state[:, :filled, 256:] = scales.view(np.uint8).reshape(2 * kv_heads, filled, 16)
+    return state
+
+
+def queries_f16(rng, *shape):
+    return rng.normal(0.0, 1.0, size=shape).astype(np.float16)
+
+
+def bf16_round(x):
+    """float32 array -> (uint16 BF16 bits, float32 widened), round to nearest even."""
+    bits = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    halves = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+    return halves, (halves.astype(np.uint32) << 16).view(np.float32)
+
+
+def unique_sorted_indices(rng, rows, count, limit):
+    out = np.empty((rows, count), np.int32)
+    for r in range(rows):
+        out[r] = np.sort(rng.choice(limit, size=count, replace=False)).astype(np.int32)
+    return out
+
+
+class XorShift:
+    """The reference tests' xorshift64 (13, 7, 17)."""
+
+    def __init__(self, seed):
+        self.s = seed & M64
+
+    def next(self):
+        s = self.s
+        s ^= (s << 13) & M64
+        s ^= s >> 7
+        s ^= (s << 17) & M64
+        self.s = s
+        return s
+
+    def floats_unit(self, count):
+        """attention_gpu.rs: (state >> 40) / 2^23 - 1, in [-1, 1)."""
+        return np.array([np.float32(self.next() >> 40) / np.float32(1 << 23) - np.float32(1.0) for _ in range(count)], np.float32)
+
+    def floats_scaled(self, count, scale):
+        """ds_state_bf16_gpu.rs: ((next % 2e6) / 1e6 - 1) * scale."""
+        return np.array([(np.float32(self.next() % 2_000_000) / np.float32(1_000_000.0) - np.float32(1.0)) * np.float32(scale)
+                         for _ in range(count)], np.float32)
+
+
+def close(actual, expected, atol=2e-3, rtol=1e-2):
+    """The benchmark's tolerance: every output within max-abs 2e-3 or max-rel 1e-2 of the oracle."""
+    actual = np.asarray(actual, np.float64)
+    expected = np.asarray(expected, np.float64)
+    error = np.abs(actual - expected)
+    ok = (error <= atol) | (error <= rtol * np.abs(expected))
+    return bool(np.all(ok) and np.all(np.isfinite(actual))), float(error.max())
+
+
+def ragged_lengths(seed, sequences=64, low=1024, high=32768):
+    """Context lengths of the ragged decode batch: uniform in [low, high], seeded."""
+    return [int(x) for x in np.random.default_rng(seed).integers(low, high + 1, sequences)]
+
+
+def partition_longest_first(lengths, parts):
+    """Greedy longest-first bin packing of sequences over `parts` ranks; returns a list of index lists."""
+    bins = [[] for _ in range(parts)]
+    loads = [0] * parts
+    for index in sorted(range(len(lengths)), key=lambda i: -lengths[i]):
+        target = loads.index(min(loads))
+        bins[target].append(index)
+        loads[target] += lengths[index]
+    return [sorted(b) for b in bins]
+
+
+# ---- inputs of the reference's own model-free GPU tests, rebuilt from their seeds ----
+def attention_sequence_input(rng, steps, selected, base, context, kind, heads=24, kv_heads=2):
+    """The packed F32 input of sd_attention_sequence: q | k | v | positions as floats | counts as floats."""
+    q = rng.normal(0, 1, (steps, heads, 256)).astype(np.float32)
+    k = rng.normal(0, 1, (steps, kv_heads, 256)).astype(np.float32)
+    v = rng.normal(0, 1, (steps, kv_heads, 256)).astype(np.float32)
+    idx = np.zeros((steps, selected), np.float32)
+    counts = np.zeros(steps, np.float32)
+    for s in range(steps):
+        limit = base + s
+        if kind == "dense":
+            n = min(selected, limit + 1)
+            idx[s, :n] = np.arange(limit + 1 - n, limit + 1)
+        else:   # sparse: unsorted, with dead slots (negative, future, past the context)
+            n = selected
+            idx[s] = rng.integers(0, limit + 1, selected)
+            idx[s, ::7] = -1
+            idx[s, 3::11] = limit + 1 + rng.integers(0, 5)
+            idx[s, 5::13] = context + 3
+            idx[s, 0] = limit     # its own position: written by this call
+        counts[s] = n
+    return np.concatenate([q.ravel(), k.ravel(), v.ravel(), idx.ravel(), counts]).astype(np.float32)
+
+
+def op_attention_case(rows, heads, kv_heads, dim, context, zero_queries=False):
+    """crates/straydog-engine/tests/attention_gpu.rs:89-104: the inputs of check(shape, zero_queries)."""
+    random = XorShift(0x9E3779B97F4A7C15 ^ rows ^ (dim << 16))
+    q = random.floats_unit(rows * heads * dim)
+    if zero_queries:
+        q[:] = 0
+    keys = random.floats_unit(context * kv_heads * dim)
+    values = random.floats_unit(context * kv_heads * dim)
+    special = [0, 1, 15, 16, context - 1, context + 7]
+    positions = np.array([special[r] if r < len(special) else (r * 17 + 3) % context for r in range(rows)], np.int32)
+    gate = np.array([[-12.0, -1.0, 0.0, 1.0, 12.0][i % 5] for i in range(q.size)], np.float32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+    return dict(q=q, keys=keys, values=values, positions=positions, gate=gate, scale=scale)
+
+
+def sparse_attention_case(rows, heads):
+    """crates/straydog-engine/tests/ds_state_bf16_gpu.rs:66-80: the inputs of attention(rows, heads, _)."""
+    dim, window, raw_rows, compressed_rows, selections, rope_dims = 512, 128, 256, 300, 512, 64
+    random = XorShift(0x9E3779B9 ^ (rows * 131 + heads))
+    q = random.floats_scaled(rows * heads * dim, 1.0)
+    raw = random.floats_scaled(raw_rows * dim, 1.0)
+    halves, widened = bf16_round(random.floats_scaled(compressed_rows * dim, 1.0))
+    sinks = random.floats_scaled(heads, 2.0)
+    freq = np.array([np.float32(10000.0) ** np.float32(-(2.0 * i) / rope_dims) for i in range(rope_dims // 2)], np.float32)
+    positions = np.array([1000 + r for r in range(rows)], np.int32)
+    selected = np.array([-1 if at % 37 == 5 else int(random.next() % compressed_rows) for at in range(rows * selections)], np.int32)
+    return dict(q=q, raw=raw, halves=halves, widened=widened, sinks=sinks, freq=freq, positions=positions, selected=selected,
+                dim=dim, window=window, raw_rows=raw_rows, compressed_rows=compressed_rows, selections=selections, rope_dims=rope_dims,
+                rows=rows, heads=heads, scale=float(np.float32(1.0) / np.sqrt(np.float32(dim))))
+
+
+def latent_decode_case(seed, rows, heads, dim, context, selections):
+    """The benchmark's DeepSeek-style decode at any size: BF16 latent rows N(0, 0.05) per query's own cache, unique sorted
+    top-k indices, BF16-exact queries N(0, 1), window 1 (the query's own row as F32), sinks -inf, no rope."""
+    rng = np.random.default_rng(seed)
+    halves, widened = bf16_round(rng.normal(0, 0.05, (rows * context, dim)).astype(np.float32))
+    _, q = bf16_round(rng.normal(0, 1, (rows, heads, dim)).astype(np.float32))
+    raw = widened.reshape(rows, context, dim)[:, -1].copy()
+    selected = np.stack([np.sort(rng.choice(context, selections, replace=False)) + r * context for r in range(rows)]).astype(np.int32)
+    return dict(q=q, raw=raw, halves=halves, sinks=np.full(heads, -np.inf, np.float32), freq=np.zeros(1, np.float32),
+                positions=np.arange(rows, dtype=np.int32), selected=selected, dim=dim, window=1, raw_rows=rows,
+                compressed_rows=rows * context, selections=selections, rope_dims=0, rows=rows, heads=heads,
+                scale=float(np.float32(1.0) / np.sqrt(np.float32(dim))))
+
+
+def tie_scores(random, rows, groups):
+    """crates/straydog-engine/tests/fused_gpu.rs:366-377: quarter steps in [-2, 2], -0 beside +0, -inf and +inf."""
+    out = np.empty(rows * groups, np.float32)
+    for i in range(rows * groups):
+        draw = random.next()
+        if groups == 600 and draw % 8 != 0:
+            out[i] = -np.inf
+            continue
+        m = draw % 97
+        if m <= 6:
+            out[i] = -np.inf
+        elif m == 7:
+            out[i] = np.inf
+        elif m == 8:
+            out[i] = -0.0
+        else:
+            out[i] = np.float32((draw >> 8) % 17) * np.float32(0.25) - np.float32(2.0) + (np.float32(0.125) if i % 1000 == 999 else np.float32(0.0))
+    return out.reshape(rows, groups)

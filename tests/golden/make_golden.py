@@ -1,0 +1,103 @@
+"""Generates tests/golden/*.npz by running the REFERENCE's own GPU library (oracle/_ref/libstraydog_ref.so,
+built from the reference's unmodified sources by oracle/Makefile.ref) through its C ABI on a B200.
+
+    python tests/golden/make_golden.py          # on a machine with a GPU and oracle/_ref built
+
+Inputs are rebuilt from seeds by straydog_b200.synthetic (the fixtures hold outputs only, plus the few
+state rows a call writes), so the fixtures stay small. The tests compare the CPU oracle and this
+library's kernels against them.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from straydog_b200 import _lib, synthetic  # noqa: E402
+from straydog_b200.backend import Backend  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(ROOT, "oracle", "_ref", "libstraydog_ref.so")
+
+SEQUENCE_CASES = [(4, 2052, 3000, 4096, "sparse"), (3, 64, 100, 256, "dense"), (8, 513, 20, 64, "sparse")]
+ATTENTION_CASES = [(15, 16, 2, 256, 137), (1, 2, 1, 256, 137), (17, 4, 2, 256, 35), (16, 4, 2, 128, 35)]
+SPARSE_CASES = [(1, 32), (4, 32)]
+LATENT_CASES = [(11, 2, 16, 576, 1024, 256)]
+TOPK_GROUPS = [511, 512, 513, 600, 4096, 30000]
+
+
+def main():
+    gpu = Backend(0, 2 << 30, library=_lib.load(REF, reference_abi_only=True))
+    out = {}
+    for steps, selected, base, context, kind in SEQUENCE_CASES:
+        rng = np.random.default_rng(steps * 1000 + selected)
+        state_np = synthetic.q8_state(rng, context, 2, filled=base)
+        inp = synthetic.attention_sequence_input(rng, steps, selected, base, context, kind)
+        state = gpu.allocate(state_np.nbytes)
+        gpu.write(state, state_np)
+        got = gpu.attention_sequence(state, context, base, steps, selected, inp)
+        after = gpu.download(state, np.empty_like(state_np))
+        key = f"sequence_{steps}_{selected}_{base}_{context}_{kind}"
+        out[key] = got
+        out[key + "_rows"] = after[:, base:base + steps].copy()
+        gpu.release(state)
+    for rows, heads, kv_heads, dim, context in ATTENTION_CASES:
+        c = synthetic.op_attention_case(rows, heads, kv_heads, dim, context)
+        qs, ks, vs, gs, ps = (gpu.upload(c[k]) for k in ("q", "keys", "values", "gate", "positions"))
+        scratch = gpu.buffer(rows * heads * 64 * (dim + 2) * 4)
+        o = gpu.buffer(c["q"].size * 4)
+        for gated in (False, True):
+            gpu.attention(qs.pointer, ks.pointer, vs.pointer, context, ps.pointer, rows, heads, kv_heads, dim, c["scale"],
+                          gs.pointer if gated else None, scratch, o.pointer)
+            out[f"attention_{rows}_{heads}_{kv_heads}_{dim}_{context}_{int(gated)}"] = gpu.read(o, np.float32, (rows, heads, dim))
+        for b in (qs, ks, vs, gs, ps, scratch, o):
+            gpu.release(b)
+
+    def sparse(c, compressed_np, tagged):
+        bufs = {k: gpu.upload(c[k]) for k in ("q", "raw", "sinks", "freq", "positions", "selected")}
+        comp = gpu.upload(compressed_np)
+        o = gpu.buffer(c["rows"] * c["heads"] * c["dim"] * 4)
+        scratch = gpu.buffer(256 << 20)
+        gpu.attention_turns_reserve(c["rows"], c["rope_dims"])
+        gpu.sparse_attention(bufs["q"].pointer, bufs["raw"].pointer, c["raw_rows"], bufs["positions"].pointer, c["window"],
+                             (comp.tagged_bf16() if tagged else comp.pointer, c["compressed_rows"]), (bufs["selected"].pointer, c["selections"]),
+                             bufs["sinks"].pointer, c["rows"], c["heads"], c["dim"], c["scale"],
+                             (c["rope_dims"], bufs["freq"].pointer) if c["rope_dims"] else None, scratch, o.pointer)
+        got = gpu.read(o, np.float32, (c["rows"], c["heads"], c["dim"]))
+        for b in list(bufs.values()) + [comp, o, scratch]:
+            gpu.release(b)
+        return got
+    for rows, heads in SPARSE_CASES:
+        c = synthetic.sparse_attention_case(rows, heads)
+        tagged = sparse(c, c["halves"], True)
+        plain = sparse(c, c["widened"], False)
+        assert np.array_equal(tagged.view(np.uint32), plain.view(np.uint32)), "the reference's own BF16 = F32 contract"
+        out[f"sparse_{rows}_{heads}"] = tagged
+    for seed, rows, heads, dim, context, selections in LATENT_CASES:
+        c = synthetic.latent_decode_case(seed, rows, heads, dim, context, selections)
+        c["sinks"] = np.full(heads, -1e30, np.float32)   # exp(sink - top) = 0 either way
+        out[f"latent_{seed}_{rows}_{heads}_{dim}_{context}_{selections}"] = sparse(c, c["halves"], True)
+    random = synthetic.XorShift(0x2F6B91D3C0A54E77)
+    for groups in TOPK_GROUPS:
+        scores = synthetic.tie_scores(random, 2, groups)
+        dev = gpu.upload(scores)
+        o = gpu.buffer(2 * 512 * 4)
+        gpu.top_k(dev.pointer, 2, groups, 512, o.pointer)
+        out[f"topk_{groups}"] = gpu.read(o, np.int32, (2, 512))
+        gpu.release(dev)
+        gpu.release(o)
+    values = synthetic.XorShift(0x243F6A8885A308D3).floats_scaled(10_000, 1e3)
+    dev = gpu.upload(values)
+    o = gpu.buffer(values.size * 2)
+    gpu.to_bf16(dev.pointer, values.size, o.pointer)
+    out["to_bf16"] = gpu.read(o, np.uint16, (values.size,))
+    gpu.close()
+    target = os.environ.get("GOLDEN_OUT", os.path.join(HERE, "reference_b200.npz"))
+    np.savez_compressed(target, **out)
+    print(f"wrote {target}: {len(out)} arrays, {os.path.getsize(target)} bytes")
+
+
+if __name__ == "__main__":
+    main()

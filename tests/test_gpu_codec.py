@@ -1,0 +1,53 @@
+"""Q8_0 write and decode on the GPU against the oracle: bit for bit."""
+import numpy as np
+import pytest
+
+import oracle
+from util import q8_state
+
+pytestmark = pytest.mark.gpu
+
+
+def test_kv_write_is_bit_exact(gpu):
+    rng = np.random.default_rng(31)
+    context, kv_heads = 96, 2
+    for base, steps in [(0, 1), (5, 8), (40, 56), (95, 1)]:
+        keys = (rng.normal(0, 1, (steps, kv_heads, 256)) * rng.choice([1e-5, 0.02, 1.0, 40.0, 6e4], (steps, kv_heads, 1))).astype(np.float32)
+        values = rng.normal(0, 3, (steps, kv_heads, 256)).astype(np.float32)
+        keys[0, 0, 32:64] = 0.0            # an all-zero block: zero scale, zero bytes
+        values[0, 0, :3] = [np.float32(0.5), np.float32(1.5), np.float32(2.5)]   # ties
+        expect = np.zeros((2 * kv_heads, context, 272), np.uint8)
+        oracle.kv_write(expect, context, kv_heads, base, keys, values)
+        state = gpu.buffer(expect.nbytes)
+        k_dev, v_dev = gpu.upload(keys), gpu.upload(values)
+        gpu.kv_write(state, context, kv_heads, base, steps, k_dev, v_dev)
+        got = gpu.read(state, np.uint8, expect.shape)
+        assert np.array_equal(got, expect), (base, steps)
+        for b in (state, k_dev, v_dev):
+            gpu.release(b)
+
+
+def test_q8_decode_is_bit_exact(gpu):
+    rng = np.random.default_rng(32)
+    state = q8_state(rng, 500, 2)
+    rows = state.reshape(-1, 272)
+    dev = gpu.upload(rows)
+    out = gpu.buffer(rows.shape[0] * 256 * 4)
+    gpu.kv_decode_rows(dev.pointer, rows.shape[0], out)
+    got = gpu.read(out, np.float32, (rows.shape[0], 256))
+    want = oracle.q8_decode_rows(rows)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    gpu.release(dev)
+    gpu.release(out)
+
+
+def test_kv_write_rejects_bad_shapes(gpu):
+    from straydog_b200.backend import StraydogError
+    state = gpu.buffer(4 * 16 * 272)
+    rows = gpu.buffer(2 * 256 * 4)
+    with pytest.raises(StraydogError):
+        gpu.kv_write(state, 16, 2, 16, 1, rows, rows)      # past the context
+    with pytest.raises(StraydogError):
+        gpu.kv_write(state, 32, 2, 0, 1, rows, rows)       # state too small for the context
+    gpu.release(state)
+    gpu.release(rows)

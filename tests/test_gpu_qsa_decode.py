@@ -1,0 +1,154 @@
+"""Split-K Q8_0 GQA decode (sdx_qsa_decode, sdx_qsa_plan*, sdx_attention_batch) against the oracle."""
+import numpy as np
+import pytest
+
+import oracle
+from util import close, q8_state, queries_f16
+
+pytestmark = pytest.mark.gpu
+CANARY = np.float32(12345.125)
+GUARD = 7
+
+
+def run_decode(gpu, states_np, contexts, lengths, heads, kv_heads, q, scale=1 / 16, plan=False):
+    n = len(states_np)
+    states = [gpu.upload(s) for s in states_np]
+    q_dev = gpu.upload(q)
+    out = gpu.upload(np.full(n * heads * 256 + 2 * GUARD, CANARY, np.float32))
+    if plan:
+        p = gpu.qsa_plan(states, contexts, lengths, heads, kv_heads)
+        gpu.qsa_plan_run(p, scale, q_dev.pointer, out.at(GUARD * 4))
+        gpu.qsa_plan_run(p, scale, q_dev.pointer, out.at(GUARD * 4))   # a plan replays
+        gpu.qsa_plan_release(p)
+    else:
+        gpu.qsa_decode(states, contexts, lengths, heads, kv_heads, scale, q_dev.pointer, out.at(GUARD * 4))
+    got = gpu.read(out, np.float32, (n * heads * 256 + 2 * GUARD,))
+    assert gpu.decode_status() == 0
+    assert np.all(got[:GUARD] == CANARY) and np.all(got[-GUARD:] == CANARY), "output guard"
+    for b in states + [q_dev, out]:
+        gpu.release(b)
+    return got[GUARD:-GUARD].reshape(n, heads, 256)
+
+
+def expect_decode(states_np, contexts, lengths, heads, kv_heads, q, scale=1 / 16, f64=True):
+    return np.stack([oracle.gqa_decode_q8(states_np[s], contexts[s], lengths[s], heads, kv_heads, q[s], scale, f64=f64)
+                     for s in range(len(states_np))])
+
+
+def test_config0_single_sequence_4096(gpu):
+    rng = np.random.default_rng(100)
+    state = q8_state(rng, 4096, 2)
+    q = queries_f16(rng, 1, 16, 256)
+    got = run_decode(gpu, [state], [4096], [4096], 16, 2, q)
+    want = expect_decode([state], [4096], [4096], 16, 2, q)
+    ok, worst = close(got, want)
+    assert ok, worst
+    # much tighter than the stated tolerance: FP32 accumulation of exact products
+    assert worst < 2e-4, worst
+    want32 = expect_decode([state], [4096], [4096], 16, 2, q, f64=False)
+    assert close(got, want32)[0]
+
+
+@pytest.mark.parametrize("length", [1, 2, 15, 16, 17, 31, 32, 33, 127, 128, 129, 1000])
+def test_edge_lengths(gpu, length):
+    rng = np.random.default_rng(200 + length)
+    context = 1024
+    state = q8_state(rng, context, 2)
+    # rows past the length hold bytes that must not leak in (scales that are NaN/Inf as FP16)
+    state[:, length:, :] = 0xFF
+    q = queries_f16(rng, 1, 16, 256)
+    got = run_decode(gpu, [state], [context], [length], 16, 2, q)
+    want = expect_decode([state], [context], [length], 16, 2, q)
+    ok, worst = close(got, want)
+    assert ok, (length, worst)
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(1, 1), (2, 2), (4, 2), (8, 1), (16, 2), (12, 3), (32, 4)])
+def test_head_groupings(gpu, heads, kv_heads):
+    rng = np.random.default_rng(300 + heads)
+    state = q8_state(rng, 400, kv_heads)
+    q = queries_f16(rng, 1, heads, 256)
+    got = run_decode(gpu, [state], [400], [333], heads, kv_heads, q, scale=0.05)
+    want = expect_decode([state], [400], [333], heads, kv_heads, q, scale=0.05)
+    ok, worst = close(got, want)
+    assert ok, worst
+
+
+def test_ragged_batch_and_plan_replay(gpu):
+    rng = np.random.default_rng(400)
+    lengths = [int(x) for x in rng.integers(1, 3000, 12)]
+    contexts = [l + int(x) for l, x in zip(lengths, rng.integers(0, 50, 12))]
+    states = [q8_state(rng, c, 2) for c in contexts]
+    q = queries_f16(rng, 12, 16, 256)
+    want = expect_decode(states, contexts, lengths, 16, 2, q)
+    got = run_decode(gpu, states, contexts, lengths, 16, 2, q)
+    ok, worst = close(got, want)
+    assert ok, worst
+    got_plan = run_decode(gpu, states, contexts, lengths, 16, 2, q, plan=True)
+    assert np.array_equal(got_plan.view(np.uint32), got.view(np.uint32)), "a plan's run equals the direct call"
+
+
+def test_a_sequence_result_does_not_depend_on_its_batch(gpu):
+    # the reference's verification contract (docs/DESIGN.md:40-41) asks a row's bits to be those of a one-token decode; here the
+    # stream-K cut points move with the batch, so the value is the same to FP32 rounding, not bit for bit
+    rng = np.random.default_rng(500)
+    lengths = [700, 64, 1500, 333]
+    states = [q8_state(rng, l, 2) for l in lengths]
+    q = queries_f16(rng, 4, 16, 256)
+    together = run_decode(gpu, states, lengths, lengths, 16, 2, q)
+    for s in range(4):
+        alone = run_decode(gpu, [states[s]], [lengths[s]], [lengths[s]], 16, 2, q[s:s + 1])
+        ok, worst = close(alone[0], together[s], atol=5e-4, rtol=1e-3)   # same value; the split points differ with the batch
+        assert ok, (s, worst)
+
+
+def test_large_scales_and_peaked_softmax(gpu):
+    rng = np.random.default_rng(600)
+    state = q8_state(rng, 256, 2)
+    state[:, :, 256:] = np.full((4, 256, 8), 3.0, np.float16).view(np.uint8).reshape(4, 256, 16)   # values up to 381
+    q = queries_f16(rng, 1, 16, 256)
+    got = run_decode(gpu, [state], [256], [256], 16, 2, q, scale=1 / 16)
+    want = expect_decode([state], [256], [256], 16, 2, q, scale=1 / 16)
+    ok, worst = close(got, want, atol=2e-3 * 150, rtol=1e-2)   # outputs are O(300) here
+    assert ok, worst
+
+
+def test_attention_batch_from_host_buffers(gpu):
+    rng = np.random.default_rng(700)
+    n, heads, kv_heads = 5, 16, 2
+    bases = [0, 15, 16, 200, 1023]
+    contexts = [64, 64, 64, 512, 1024]
+    states_np = [q8_state(rng, c, kv_heads, filled=b) for c, b in zip(contexts, bases)]
+    states = [gpu.upload(s) for s in states_np]
+    q = queries_f16(rng, n, heads, 256)
+    k = rng.normal(0, 1, (n, kv_heads, 256)).astype(np.float32)
+    v = rng.normal(0, 1, (n, kv_heads, 256)).astype(np.float32)
+    out = np.empty((n, heads, 256), np.float32)
+    gpu.attention_batch(states, contexts, bases, heads, kv_heads, 1 / 16, q, k, v, out)
+    for s in range(n):
+        oracle.kv_write(states_np[s], contexts[s], kv_heads, bases[s], k[s:s + 1], v[s:s + 1])
+        got_state = gpu.read(states[s], np.uint8, states_np[s].shape)
+        assert np.array_equal(got_state, states_np[s]), "the new row is written bit for bit"
+        want = oracle.gqa_decode_q8(states_np[s], contexts[s], bases[s] + 1, heads, kv_heads, q[s], 1 / 16, f64=True)
+        ok, worst = close(out[s], want)
+        assert ok, (s, worst)
+    for b in states:
+        gpu.release(b)
+
+
+def test_invalid_batches_are_refused(gpu):
+    from straydog_b200.backend import StraydogError
+    state = gpu.buffer(4 * 64 * 272)
+    q = gpu.buffer(16 * 256 * 2)
+    out = gpu.buffer(16 * 256 * 4)
+    for args in [([state], [64], [65], 16, 2),      # length past the context
+                 ([state], [64], [0], 16, 2),       # no key
+                 ([state], [128], [10], 16, 2),     # state smaller than the context says
+                 ([state], [64], [10], 18, 1),      # more than 8 heads a group
+                 ([state], [64], [10], 16, 3)]:     # heads not a multiple of kv_heads
+        with pytest.raises(StraydogError):
+            gpu.qsa_decode(args[0], args[1], args[2], args[3], args[4], 1 / 16, q.pointer, out.pointer)
+    with pytest.raises(StraydogError):
+        gpu.qsa_decode([state], [64], [10], 16, 2, 1 / 16, q.pointer + 4096 * 2, out.pointer)   # queries outside their buffer
+    for b in (state, q, out):
+        gpu.release(b)

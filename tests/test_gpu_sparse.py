@@ -1,0 +1,96 @@
+"""sd_op_sparse_attention: the reference's ds_state_bf16_gpu.rs shapes (BF16-tagged rows give the bits of
+their F32 values), the oracle within tolerance, sinks, rope, empty selections, ring addressing."""
+import numpy as np
+import pytest
+
+import oracle
+from util import XorShift, bf16_round, close, sparse_attention_case
+
+pytestmark = pytest.mark.gpu
+
+
+def reference_case(rows, heads):
+    return sparse_attention_case(rows, heads)
+
+
+def run(gpu, c, compressed_np, tagged, scratch_bytes=64 << 20):
+    bufs = {k: gpu.upload(c[k]) for k in ("q", "raw", "sinks", "freq", "positions", "selected")}
+    comp = gpu.upload(compressed_np)
+    out = gpu.buffer(c["rows"] * c["heads"] * c["dim"] * 4)
+    scratch = gpu.buffer(scratch_bytes) if scratch_bytes else None
+    gpu.attention_turns_reserve(c["rows"], c["rope_dims"])
+    gpu.sparse_attention(bufs["q"].pointer, bufs["raw"].pointer, c["raw_rows"], bufs["positions"].pointer, c["window"],
+                         (comp.tagged_bf16() if tagged else comp.pointer, c["compressed_rows"]),
+                         (bufs["selected"].pointer, c["selections"]), bufs["sinks"].pointer, c["rows"], c["heads"], c["dim"],
+                         float(np.float32(1.0) / np.sqrt(np.float32(c["dim"]))),
+                         (c["rope_dims"], bufs["freq"].pointer) if c["rope_dims"] else None, scratch, out.pointer)
+    got = gpu.read(out, np.float32, (c["rows"], c["heads"], c["dim"]))
+    for b in list(bufs.values()) + [comp, out] + ([scratch] if scratch else []):
+        gpu.release(b)
+    return got
+
+
+@pytest.mark.parametrize("rows,heads", [(1, 32), (4, 32), (64, 32), (16, 64)])
+def test_the_attention_of_bf16_rows_is_that_of_their_f32_values(gpu, rows, heads):
+    c = reference_case(rows, heads)
+    from_f32 = run(gpu, c, c["widened"], tagged=False)
+    from_bf16 = run(gpu, c, c["halves"], tagged=True)
+    assert from_f32.any()
+    assert np.array_equal(from_f32.view(np.uint32), from_bf16.view(np.uint32))
+    want = oracle.sparse_attention(c["q"], c["raw"], c["raw_rows"], c["positions"], c["window"], c["halves"], c["selected"],
+                                   c["selections"], c["sinks"], rows, heads, c["dim"], float(np.float32(1.0) / np.sqrt(np.float32(c["dim"]))),
+                                   c["rope_dims"], c["freq"], f64=True)
+    ok, worst = close(from_bf16, want)
+    assert ok, worst
+
+
+def test_benchmark_shape_small(gpu):
+    # config 3's shape at a size the oracle finishes quickly: 576-wide BF16 rows N(0, 0.05), unique sorted indices,
+    # window 1 (the query's own F32 row), sinks at -inf, no rope
+    rng = np.random.default_rng(41)
+    rows, heads, dim, ctx, sel = 4, 128, 576, 4096, 512
+    halves, widened = bf16_round(rng.normal(0, 0.05, (rows * ctx, dim)).astype(np.float32))
+    _, q = bf16_round(rng.normal(0, 1, (rows, heads, dim)).astype(np.float32))
+    raw = widened.reshape(rows, ctx, dim)[:, -1].copy()
+    selected = np.stack([np.sort(rng.choice(ctx, sel, replace=False)) + r * ctx for r in range(rows)]).astype(np.int32)
+    c = dict(q=q, raw=raw, sinks=np.full(heads, -np.inf, np.float32), freq=np.zeros(1, np.float32), positions=np.arange(rows, dtype=np.int32),
+             selected=selected, dim=dim, window=1, raw_rows=rows, compressed_rows=rows * ctx, selections=sel, rope_dims=0, rows=rows, heads=heads)
+    got = run(gpu, c, halves, tagged=True)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+    want = oracle.sparse_attention(q, raw, rows, c["positions"], 1, halves, selected, sel, c["sinks"], rows, heads, dim, scale, 0, None, f64=True)
+    ok, worst = close(got, want)
+    assert ok, worst
+
+
+def test_window_ring_empty_selections_and_no_selection_list(gpu):
+    rng = np.random.default_rng(42)
+    rows, heads, dim, window, raw_rows = 5, 8, 64, 6, 8
+    q = rng.normal(0, 1, (rows, heads, dim)).astype(np.float32)
+    raw = rng.normal(0, 1, (raw_rows, dim)).astype(np.float32)
+    halves, _ = bf16_round(rng.normal(0, 1, (20, dim)).astype(np.float32))
+    positions = np.array([0, 3, 7, 8, 21], np.int32)      # before the window fills, and wrapped around the ring
+    selected = np.full((rows, 4), -1, np.int32)
+    selected[2] = [3, -1, 19, 0]
+    sinks = rng.normal(0, 1, heads).astype(np.float32)
+    c = dict(q=q, raw=raw, sinks=sinks, freq=np.zeros(1, np.float32), positions=positions, selected=selected, dim=dim, window=window,
+             raw_rows=raw_rows, compressed_rows=20, selections=4, rope_dims=0, rows=rows, heads=heads)
+    got = run(gpu, c, halves, tagged=True, scratch_bytes=0)
+    want = oracle.sparse_attention(q, raw, raw_rows, positions, window, halves, selected, 4, sinks, rows, heads, dim, 0.125, 0, None, f64=True)
+    ok, worst = close(got, want)
+    assert ok, worst
+
+
+def test_invalid_shapes_are_refused(gpu):
+    from straydog_b200.backend import StraydogError
+    b = gpu.buffer(1 << 20)
+    def call(**kw):
+        a = dict(rows=1, heads=4, dim=64, window=4, rope=None, selections=4)
+        a.update(kw)
+        gpu.sparse_attention(b.pointer, b.pointer, 8, b.pointer, a["window"], (b.pointer, 16), (b.pointer, a["selections"]), b.pointer,
+                             a["rows"], a["heads"], a["dim"], 1.0, a["rope"], None, b.pointer)
+    call()
+    for bad in (dict(rows=0), dict(rows=65536), dict(window=0), dict(rope=(3, b.pointer)), dict(rope=(130, b.pointer)), dict(dim=32, rope=(64, b.pointer)),
+                dict(selections=1 << 30)):
+        with pytest.raises(StraydogError):
+            call(**bad)
+    gpu.release(b)

@@ -1,0 +1,53 @@
+"""sd_op_top_k against the reference's rule on its own tie-heavy cases (tests/fused_gpu.rs:359-389); sd_op_to_bf16."""
+import numpy as np
+import pytest
+
+import oracle
+from util import XorShift, bf16_round, tie_scores
+
+pytestmark = pytest.mark.gpu
+
+
+def test_top_k_matches_its_reference_with_many_ties(gpu):
+    random = XorShift(0x2F6B91D3C0A54E77)
+    k = 512
+    for groups in [511, 512, 513, 600, 4096, 30000, 65536, 131072]:
+        scores = tie_scores(random, 2, groups)
+        dev = gpu.upload(scores)
+        out = gpu.buffer(2 * k * 4)
+        gpu.top_k(dev.pointer, 2, groups, k, out.pointer)
+        got = gpu.read(out, np.int32, (2, k))
+        want = oracle.top_k(scores, k)
+        assert np.array_equal(got, want), groups
+        gpu.release(dev)
+        gpu.release(out)
+
+
+@pytest.mark.parametrize("rows,groups,k", [(1, 1, 1), (3, 10, 16), (32, 65536, 2048), (5, 2049, 2048), (2, 100000, 1)])
+def test_top_k_random_scores(gpu, rows, groups, k):
+    rng = np.random.default_rng(rows * 7 + groups)
+    scores = rng.normal(0, 1, (rows, groups)).astype(np.float32)
+    scores[:, ::5] = np.round(scores[:, ::5], 1)     # ties
+    dev = gpu.upload(scores)
+    out = gpu.buffer(rows * k * 4)
+    gpu.top_k(dev.pointer, rows, groups, k, out.pointer)
+    assert np.array_equal(gpu.read(out, np.int32, (rows, k)), oracle.top_k(scores, k))
+    gpu.release(dev)
+    gpu.release(out)
+
+
+def test_rounding_into_bf16_is_to_the_nearest_even(gpu):
+    # tests/ds_state_bf16_gpu.rs:50-69
+    values = XorShift(0x243F6A8885A308D3).floats_scaled(10_000, 1e3)
+    extra = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 3.4028235e38, 1.17549435e-38, 1 + 1 / 256, 1 + 3 / 256], np.float32)
+    values = np.concatenate([values, extra, np.array([0x3F808000, 0x3F818000], np.uint32).view(np.float32)])
+    dev = gpu.upload(values)
+    out = gpu.buffer(values.size * 2)
+    gpu.to_bf16(dev.pointer, values.size, out.pointer)
+    got = gpu.read(out, np.uint16, (values.size,))
+    want, _ = bf16_round(values)
+    nan = np.isnan(values)
+    assert np.array_equal(got[~nan], want[~nan])
+    assert np.all(np.isnan((got[nan].astype(np.uint32) << 16).view(np.float32)))
+    gpu.release(dev)
+    gpu.release(out)

@@ -3,7 +3,7 @@ reference's top-k rule written out in Python (tests/fused_gpu.rs:325-357), and i
 import numpy as np
 
 import oracle
-from util import XorShift, bf16_round, q8_state, queries_f16
+from util import XorShift, bf16_round, q8_state, queries_f16, tie_scores
 
 
 def numpy_attention(q, k, v, scale):
@@ -103,26 +103,6 @@ def python_top_k(scores, k):
                 out.append(g)
                 need -= 1
     return out + [-1] * (k - len(out))
-
-
-def tie_scores(random, rows, groups):
-    # crates/straydog-engine/tests/fused_gpu.rs:366-377
-    out = np.empty(rows * groups, np.float32)
-    for i in range(rows * groups):
-        draw = random.next()
-        if groups == 600 and draw % 8 != 0:
-            out[i] = -np.inf
-            continue
-        m = draw % 97
-        if m <= 6:
-            out[i] = -np.inf
-        elif m == 7:
-            out[i] = np.inf
-        elif m == 8:
-            out[i] = -0.0
-        else:
-            out[i] = np.float32((draw >> 8) % 17) * np.float32(0.25) - np.float32(2.0) + (np.float32(0.125) if i % 1000 == 999 else np.float32(0.0))
-    return out.reshape(rows, groups)
 
 
 def test_top_k_matches_the_reference_rule_with_many_ties():
