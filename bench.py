@@ -100,13 +100,13 @@ class ClockSampler:
         return out
 
 
-def batch_for(rank, world, scaling):
+def batch_for(rank, world, scaling, sequences=64):
     """(lengths of this rank's sequences, their seeds)."""
     from straydog_b200.synthetic import partition_longest_first, ragged_lengths
     if scaling == "weak":
-        lengths = ragged_lengths(SEED + rank)
+        lengths = ragged_lengths(SEED + rank, sequences)
         return lengths, [SEED * 1000 + rank * 100 + i for i in range(len(lengths))]
-    lengths = ragged_lengths(SEED)
+    lengths = ragged_lengths(SEED, sequences)
     mine = partition_longest_first(lengths, world)[rank]
     return [lengths[i] for i in mine], [SEED * 1000 + i for i in mine]
 
@@ -175,6 +175,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
+    parser.add_argument("--sequences", type=int, default=64, help="sequences per batch (64 is the benchmark; fewer for a profiler capture)")
+    parser.add_argument("--profile", action="store_true", help="device-resident steps only, no load padding: the command an ncu capture wraps")
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -200,7 +202,7 @@ def main():
             dist.all_reduce(barrier_token)
         torch.cuda.synchronize()
 
-    lengths, seeds = batch_for(rank, world, args.scaling)
+    lengths, seeds = batch_for(rank, world, args.scaling, args.sequences)
     kv_bytes = sum(lengths) * 2 * KV_HEADS * ROW
     gpu = Backend(local, kv_bytes + (2 << 30))
     states_np = make_states(lengths, seeds)
@@ -218,6 +220,14 @@ def main():
     info = gpu.qsa_plan_info(plan)
 
     # ---- device-resident: K steps of the planned decode (two kernel launches each) ----
+    if args.profile:
+        for _ in range(args.warmup + args.steps):
+            gpu.qsa_plan_run(plan, SCALE, q.pointer, out.pointer)
+        gpu.synchronize()
+        print(json.dumps({"profile": True, "plan": info, "launches": gpu.launch_count()}))
+        gpu.qsa_plan_release(plan)
+        gpu.close()
+        return
     sampler = ClockSampler(local)
     for _ in range(args.warmup):
         gpu.qsa_plan_run(plan, SCALE, q.pointer, out.pointer)

@@ -30,6 +30,7 @@ TOPK_GROUPS = [511, 512, 513, 600, 4096, 30000]
 
 def main():
     gpu = Backend(0, 2 << 30, library=_lib.load(REF, reference_abi_only=True))
+    gpu.kv_format(272)   # the reference defaults to FP16 rows until told otherwise (gpu/core.hpp:837)
     out = {}
     for steps, selected, base, context, kind in SEQUENCE_CASES:
         rng = np.random.default_rng(steps * 1000 + selected)

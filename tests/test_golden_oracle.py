@@ -1,0 +1,67 @@
+"""Pins the CPU oracle to outputs of the reference's own GPU library (tests/golden/reference_b200.npz, made by
+tests/golden/make_golden.py on a B200): byte and index work bit for bit, attention within FP32 rounding."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from util import (XorShift, attention_sequence_input, bf16_round, latent_decode_case, op_attention_case, q8_state,
+                  sparse_attention_case, tie_scores)
+
+GOLDEN = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_b200.npz"))
+SEQUENCE_CASES = [(4, 2052, 3000, 4096, "sparse"), (3, 64, 100, 256, "dense"), (8, 513, 20, 64, "sparse")]
+ATTENTION_CASES = [(15, 16, 2, 256, 137), (1, 2, 1, 256, 137), (17, 4, 2, 256, 35), (16, 4, 2, 128, 35)]
+
+
+def worst(a, b):
+    return float(np.abs(np.asarray(a, np.float64) - np.asarray(b, np.float64)).max())
+
+
+@pytest.mark.parametrize("steps,selected,base,context,kind", SEQUENCE_CASES)
+def test_attention_sequence(steps, selected, base, context, kind):
+    rng = np.random.default_rng(steps * 1000 + selected)
+    state = q8_state(rng, context, 2, filled=base)
+    inp = attention_sequence_input(rng, steps, selected, base, context, kind)
+    got = oracle.attention_sequence(state, context, 24, 2, base, steps, selected, inp)
+    key = f"sequence_{steps}_{selected}_{base}_{context}_{kind}"
+    assert np.array_equal(state[:, base:base + steps], GOLDEN[key + "_rows"]), "the Q8_0 rows the call writes: bit for bit"
+    assert worst(got, GOLDEN[key]) < 2e-5
+
+
+@pytest.mark.parametrize("rows,heads,kv_heads,dim,context", ATTENTION_CASES)
+def test_op_attention(rows, heads, kv_heads, dim, context):
+    c = op_attention_case(rows, heads, kv_heads, dim, context)
+    for gated in (0, 1):
+        out, out64, bound = oracle.op_attention(c["q"], c["keys"], c["values"], context, c["positions"], rows, heads, kv_heads, dim, c["scale"],
+                                                c["gate"] if gated else None, want64=True)
+        ref = GOLDEN[f"attention_{rows}_{heads}_{kv_heads}_{dim}_{context}_{gated}"]
+        # the reference's own kernels sit inside the bound its test derives around the oracle's F64 values
+        assert np.all(np.abs(ref.astype(np.float64) - out64) <= bound)
+        assert worst(out, ref) < 1e-5
+
+
+@pytest.mark.parametrize("rows,heads", [(1, 32), (4, 32)])
+def test_sparse_attention(rows, heads):
+    c = sparse_attention_case(rows, heads)
+    got = oracle.sparse_attention(c["q"], c["raw"], c["raw_rows"], c["positions"], c["window"], c["halves"], c["selected"], c["selections"],
+                                  c["sinks"], rows, heads, c["dim"], c["scale"], c["rope_dims"], c["freq"])
+    assert worst(got, GOLDEN[f"sparse_{rows}_{heads}"]) < 2e-5
+
+
+def test_latent_decode_shape():
+    seed, rows, heads, dim, context, selections = 11, 2, 16, 576, 1024, 256
+    c = latent_decode_case(seed, rows, heads, dim, context, selections)
+    got = oracle.sparse_attention(c["q"], c["raw"], c["raw_rows"], c["positions"], c["window"], c["halves"], c["selected"], selections,
+                                  c["sinks"], rows, heads, dim, c["scale"], 0, None)
+    assert worst(got, GOLDEN[f"latent_{seed}_{rows}_{heads}_{dim}_{context}_{selections}"]) < 2e-6
+
+
+def test_top_k_and_bf16_bit_for_bit():
+    random = XorShift(0x2F6B91D3C0A54E77)
+    for groups in [511, 512, 513, 600, 4096, 30000]:
+        scores = tie_scores(random, 2, groups)
+        assert np.array_equal(oracle.top_k(scores, 512), GOLDEN[f"topk_{groups}"]), groups
+    values = XorShift(0x243F6A8885A308D3).floats_scaled(10_000, 1e3)
+    assert np.array_equal(oracle.to_bf16(values), GOLDEN["to_bf16"])
+    assert np.array_equal(bf16_round(values)[0], GOLDEN["to_bf16"])

@@ -62,6 +62,42 @@ def test_benchmark_shape_small(gpu):
     assert ok, worst
 
 
+@pytest.mark.parametrize("rows,heads,dim,window,selections,rope_dims,exact_q", [
+    (3, 16, 576, 8, 200, 0, True), (8, 16, 576, 8, 2048, 64, True), (2, 128, 576, 1, 96, 0, True), (5, 24, 512, 128, 31, 64, False),
+    (1, 8, 512, 3, 0, 0, False), (2, 40, 576, 40, 65, 128, False)])
+def test_tensor_core_kernel_shapes(gpu, rows, heads, dim, window, selections, rope_dims, exact_q):
+    """Head tiles of 16 and 32 with tails, spans with a causal window (config 4's layout), rope on BF16-exact and on F32 queries,
+    partial tiles, no selection at all; each against the F64 oracle and against this library's FP32 kernel."""
+    import os
+    rng = np.random.default_rng(rows * 100 + heads)
+    raw_rows, compressed_rows = max(window, 8), 5000
+    q = rng.normal(0, 1, (rows, heads, dim)).astype(np.float32)
+    if exact_q:
+        _, q = bf16_round(q)
+    raw = rng.normal(0, 0.05, (raw_rows, dim)).astype(np.float32)
+    halves, _ = bf16_round(rng.normal(0, 0.05, (compressed_rows, dim)).astype(np.float32))
+    selected = rng.integers(0, compressed_rows, (rows, max(selections, 1))).astype(np.int32)
+    selected[:, ::9] = -1
+    positions = (np.arange(rows) + (window - 1 if rows > 1 else 0)).astype(np.int32)
+    sinks = rng.normal(0, 1, heads).astype(np.float32)
+    freq = (10000.0 ** (-(2.0 * np.arange(max(rope_dims, 2) // 2)) / max(rope_dims, 2))).astype(np.float32)
+    c = dict(q=q, raw=raw, sinks=sinks, freq=freq, positions=positions, selected=selected, dim=dim, window=window, raw_rows=raw_rows,
+             compressed_rows=compressed_rows, selections=selections, rope_dims=rope_dims, rows=rows, heads=heads)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+    want = oracle.sparse_attention(q, raw, raw_rows, positions, window, halves, selected if selections else None, selections, sinks, rows, heads,
+                                   dim, scale, rope_dims, freq if rope_dims else None, f64=True)
+    got = run(gpu, c, halves, tagged=True)
+    ok, worst = close(got, want)
+    assert ok, worst
+    os.environ["SDX_SPARSE_SIMT"] = "1"
+    try:
+        simt = run(gpu, c, halves, tagged=True)
+    finally:
+        del os.environ["SDX_SPARSE_SIMT"]
+    assert close(simt, want, atol=1e-4, rtol=1e-3)[0]
+    assert close(got, simt)[0]
+
+
 def test_window_ring_empty_selections_and_no_selection_list(gpu):
     rng = np.random.default_rng(42)
     rows, heads, dim, window, raw_rows = 5, 8, 64, 6, 8
