@@ -115,6 +115,16 @@ int sdx_qsa_plan_run(void* handle, void* plan, float scale, const void* q, float
 int sdx_qsa_plan_run_marked(void* handle, void* plan, float scale, const void* q, float* out, void* before, void* after);
 int sdx_qsa_plan_info(void* plan, uint64_t* kv_bytes, uint64_t* pieces, uint64_t* ctas, uint64_t* virtual_warps);
 int sdx_qsa_plan_release(void* handle, void* plan);
+/* No counterpart in the reference. sdx_qsa_decode for hosts that may not allocate once they serve (an engine
+   whose VRAM budget is fully handed out, a loop that forbids driver allocations because they stall the
+   device): the work list and the split partials live in a 16.3 MiB array inside the library's device image,
+   held by every GPU that loads the library until exit. Limits: at most 64 sequences, 8 K/V heads and 2048
+   work-list pieces a call; a larger batch is refused with an error, nothing is truncated. The first call on a
+   device looks up the array's device address (make that call before any stream capture). Calls share the
+   array: two calls that overlap on the GPU, from any handles or threads, race; the call returns after its
+   result is complete. It calls no cudaMalloc, cudaFree or allocating library routine. */
+int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
+                          uint64_t sequences, uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out);
 /* 1 when a bounded wait inside a decode kernel gave up since the last call (cleared by the call), 0 if none. */
 int sdx_decode_status(void* handle);
 

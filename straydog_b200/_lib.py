@@ -48,6 +48,7 @@ SIGNATURES = {
     "sdx_kv_write": ([p, p, u64, u64, u64, u64, p, p], i32),
     "sdx_kv_decode_rows": ([p, p, u64, p], i32),
     "sdx_qsa_decode": ([p, pp, pu64, pu64, u64, u64, u64, f32, p, p], i32),
+    "sdx_qsa_decode_static": ([p, pp, pu64, pu64, u64, u64, u64, f32, p, p], i32),
     "sdx_qsa_plan": ([p, pp, pu64, pu64, u64, u64, u64], p),
     "sdx_qsa_plan_run": ([p, p, f32, p, p], i32),
     "sdx_qsa_plan_run_marked": ([p, p, f32, p, p, p, p], i32),

@@ -196,6 +196,14 @@ class Backend:
         lens = (C.c_uint64 * n)(*lengths)
         self._c(self.lib.sdx_qsa_decode(self.handle, ptrs, ctx, lens, n, heads, kv_heads, scale, q, out))
 
+    def qsa_decode_static(self, states, contexts, lengths, heads, kv_heads, scale, q, out):
+        """sdx_qsa_decode_static: the same decode with its scratch inside the library's device image (no allocation)."""
+        n = len(states)
+        ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])
+        ctx = (C.c_uint64 * n)(*contexts)
+        lens = (C.c_uint64 * n)(*lengths)
+        self._c(self.lib.sdx_qsa_decode_static(self.handle, ptrs, ctx, lens, n, heads, kv_heads, scale, q, out))
+
     def qsa_plan(self, states, contexts, lengths, heads, kv_heads):
         n = len(states)
         ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])

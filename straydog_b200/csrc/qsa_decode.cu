@@ -524,6 +524,68 @@ int sdx_qsa_plan_release(void* handle, void* plan) {
     SDB_OP_END
 }
 
+// ---- the decode that allocates nothing ----
+// Every other decode entry keeps its work list and its split partials in memory it allocates on demand
+// (cudaMalloc / cudaMallocHost the first time a batch of a new size arrives). Some hosts cannot allow
+// that: an engine that has handed its whole VRAM budget to weights and K/V and must never see an
+// allocation fail mid-request, or a serving loop that forbids driver allocations after start-up because
+// they synchronise the device. For them this entry keeps all of its scratch in one array that is part
+// of the library's device image: it exists on every GPU that loads the library, from load to exit,
+// whether or not the entry is ever called.
+constexpr size_t kStaticSequences = 64;                                  // sequences a call
+constexpr size_t kStaticKvHeads = 8;                                     // K/V heads
+constexpr size_t kStaticPieces = 2048;                                   // pieces a call's work list may hold
+constexpr size_t kStaticTableBytes = size_t(128) << 10;                  // segments | pieces | warp ranges
+constexpr size_t kStaticScratchBytes = kStaticTableBytes + kStaticPieces * size_t(kPartialFloats) * 4 + 256;   // about 16.3 MiB
+static __device__ __align__(256) uint8_t static_decode_scratch[kStaticScratchBytes];
+
+// The array's device address, per device. The symbol's name is only a host-side stand-in: the address a
+// kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+static uint8_t* static_scratch_address(Device& d) {
+    static std::mutex mutex;
+    static std::map<int, uint8_t*> known;
+    std::lock_guard<std::mutex> lock(mutex);
+    auto found = known.find(d.ordinal);
+    if (found != known.end()) return found->second;
+    void* address = nullptr;
+    SDB_CHECK(cudaGetSymbolAddress(&address, static_decode_scratch));   // (device(handle) made d.ordinal current)
+    known[d.ordinal] = static_cast<uint8_t*>(address);
+    return static_cast<uint8_t*>(address);
+}
+
+int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
+                          uint64_t sequences, uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out) {
+    SDB_OP_BEGIN
+    if (sequences > kStaticSequences || kv_heads > kStaticKvHeads)
+        throw std::runtime_error("sdx_qsa_decode_static holds scratch for at most 64 sequences of at most 8 K/V heads: use sdx_qsa_decode for a larger batch");
+    span(value, q, checked_product({sequences, heads, 256, 2}), "attention queries");
+    span(value, out, checked_product({sequences, heads, 256, 4}), "an attention output");
+    std::vector<const uint8_t*> checked;
+    uint64_t kv_bytes = 0;
+    validate_batch(value, states, contexts, lengths, sequences, heads, kv_heads, checked, kv_bytes);
+    HostTables host;
+    build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(value.sms) * kWarps, host);
+    DecodePlan plan;
+    fill_plan(value, host, plan, sequences, heads, kv_heads);
+    if (plan.pieces > kStaticPieces || plan.table_bytes > kStaticTableBytes)
+        throw std::runtime_error("sdx_qsa_decode_static: this batch's work list is larger than the static scratch (2048 pieces)");
+    uint8_t* scratch = static_scratch_address(value);
+    plan.partial = reinterpret_cast<float*>(scratch + kStaticTableBytes);
+    plan.status = reinterpret_cast<int*>(scratch + kStaticScratchBytes - 256);
+    // The tables travel from ordinary host memory: the copy is staged by the runtime before the call returns, so the
+    // vector may go; nothing is allocated on the device. The status word is the only part that must start at zero.
+    std::vector<uint8_t> staging(plan.table_bytes);
+    SDB_CHECK(cudaMemsetAsync(plan.status, 0, 4, value.stream));
+    upload_tables(value, host, plan, scratch, staging.data());
+    run_plan(value, plan, scale, q, out);
+    SDB_CHECK(cudaGetLastError());
+    int gave_up = 0;
+    SDB_CHECK(cudaMemcpyAsync(&gave_up, plan.status, 4, cudaMemcpyDeviceToHost, value.stream));
+    SDB_CHECK(cudaStreamSynchronize(value.stream));
+    if (gave_up) throw std::runtime_error("sdx_qsa_decode_static: a bounded wait inside the decode kernel gave up");
+    SDB_OP_END
+}
+
 // 1 when a bounded wait inside a decode kernel gave up since the last call (the word is cleared), else 0.
 int sdx_decode_status(void* handle) {
     try {
