@@ -167,12 +167,166 @@ def workload_config(lengths, l2):
             "sequences_per_gpu": len(lengths), "kv_bytes_per_gpu": sum(lengths) * 2 * KV_HEADS * ROW, "seed": SEED, "l2": l2}
 
 
+
+# ---- the other configurations (parity-test cases, measured here for DESIGN.md and profiles/; not the driver's line) ----
+def timed(gpu, fn, steps, warmup):
+    for _ in range(max(3, warmup)):
+        fn()
+    gpu.synchronize()
+    start, stop = gpu.event(), gpu.event()
+    gpu.record(start)
+    for _ in range(steps):
+        fn()
+    gpu.record(stop)
+    gpu.synchronize()
+    return gpu.elapsed_ms(start, stop) / steps
+
+
+def reference_gpu_backend(budget):
+    """The reference's own GPU library built for sm_100a (oracle/_ref): the same-box kernels to beat."""
+    from straydog_b200 import _lib
+    from straydog_b200.backend import Backend
+    path = os.path.join(ROOT, "oracle", "_ref", "libstraydog_ref.so")
+    if not os.path.exists(path):
+        return None
+    gpu = Backend(0, budget, library=_lib.load(path, reference_abi_only=True))
+    gpu.kv_format(272)
+    # event timing goes through this library's helpers on the default stream ordering of the reference's handle:
+    # the reference queues on its own stream, so its calls are timed host-side around a synchronising read instead
+    return gpu
+
+
+def run_other_config(args):
+    import torch
+    from straydog_b200.backend import Backend
+    from straydog_b200 import synthetic
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU")
+    peak_hbm, peak_source = measured_peaks()
+    peak_tensor = 1689.0
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        peak_tensor = float(json.load(open(path))["bf16_tflops"])
+    cfg = args.config
+    ref = args.impl == "reference-gpu"
+    line = {"config_id": cfg, "impl": args.impl, "steps": args.steps, "warmup": args.warmup}
+    if cfg in (0, 2):
+        heads, kv_heads = HEADS, KV_HEADS
+        context = 4096 if cfg == 0 else 16384
+        first, rows = (4095, 1) if cfg == 0 else (8192, 8192)
+        rng = np.random.default_rng(SEED + cfg)
+        state_np = synthetic.q8_state(rng, context, kv_heads)
+        q_np = synthetic.queries_f16(rng, rows, heads, DIM)
+        kv_bytes = (first + rows) * 2 * kv_heads * ROW
+        flops = 4.0 * DIM * heads * sum(first + r + 1 for r in range(rows))
+        if not ref:
+            gpu = Backend(0, 4 << 30)
+            state, q = gpu.upload(state_np), gpu.upload(q_np)
+            out = gpu.buffer(rows * heads * DIM * 4)
+            if cfg == 0:
+                plan = gpu.qsa_plan([state], [context], [context], heads, kv_heads)
+                ms = timed(gpu, lambda: gpu.qsa_plan_run(plan, SCALE, q.pointer, out.pointer), args.steps, args.warmup)
+            else:
+                ms = timed(gpu, lambda: gpu.qsa_prompt(state, context, first, rows, heads, kv_heads, SCALE, q.pointer, out.pointer), args.steps, args.warmup)
+        else:
+            # the reference's generic GQA over the dequantised F32 K/V [context][kv_heads][dim] (gpu/token_mixing.hpp:652)
+            import oracle
+            gpu = reference_gpu_backend(8 << 30)
+            planes = oracle.q8_decode_rows(state_np.reshape(-1, ROW)).reshape(2 * kv_heads, context, DIM)
+            keys = np.ascontiguousarray(planes[:kv_heads].transpose(1, 0, 2))
+            values = np.ascontiguousarray(planes[kv_heads:].transpose(1, 0, 2))
+            kb, vb, qb = gpu.upload(keys), gpu.upload(values), gpu.upload(q_np.astype(np.float32))
+            pb = gpu.upload(np.arange(first, first + rows, dtype=np.int32))
+            scratch = gpu.buffer(max(1, rows * heads * 64 * (DIM + 2) * 4) if rows < 16 else 4096)
+            out = gpu.buffer(rows * heads * DIM * 4)
+            probe = np.empty(4, np.float32)
+
+            def call():
+                gpu.attention(qb.pointer, kb.pointer, vb.pointer, context, pb.pointer, rows, heads, kv_heads, DIM, SCALE, None, scratch, out.pointer)
+            for _ in range(2):
+                call()
+            gpu.read_buffer(out, 0, probe)
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                call()
+            gpu.read_buffer(out, 0, probe)
+            ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        line.update({"workload": "config 0: 1 sequence x 4096 keys decode" if cfg == 0 else "config 2: 8192-token chunk after 8192 cached, causal prompt attention",
+                     "ms": ms, "kv_gbps": kv_bytes / ms / 1e6, "tflops": flops / ms / 1e9,
+                     "roofline": ({"bound": "hbm", "achieved": kv_bytes / ms / 1e6, "peak": peak_hbm, "unit": "GB/s", "frac": kv_bytes / ms / 1e6 / peak_hbm}
+                                  if cfg == 0 else {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": peak_tensor, "unit": "TFLOP/s",
+                                                    "frac": flops / ms / 1e9 / peak_tensor}),
+                     "tokens_per_s": rows / ms * 1e3})
+    else:
+        heads = 128 // max(1, args.head_shards)
+        dim, selections = 576, 2048
+        if cfg == 3:
+            rows, context, window, calls = 32, 65536, 1, 1
+        else:
+            rows, context, window, calls = 8, 32768, 8, 16
+        rng = np.random.default_rng(SEED + cfg)
+        total_rows = (rows if cfg == 3 else 1) * context * (1 if cfg == 3 else calls)
+        # BF16 latent rows N(0, 0.05), generated in slabs to bound host memory
+        halves = np.empty((total_rows, dim), np.uint16)
+        for at in range(0, total_rows, 1 << 18):
+            n = min(1 << 18, total_rows - at)
+            halves[at:at + n] = synthetic.bf16_round(rng.normal(0, 0.05, (n, dim)).astype(np.float32))[0]
+        _, q_np = synthetic.bf16_round(rng.normal(0, 1, (calls, rows, heads, dim)).astype(np.float32))
+        raw_np = rng.normal(0, 0.05, (calls, max(rows, window), dim)).astype(np.float32)
+        selected = np.stack([np.sort(rng.choice(context, selections, replace=False)) for _ in range(calls * rows)]).astype(np.int32)
+        if cfg == 3:
+            selected += (np.arange(rows) * context)[:, None].astype(np.int32)
+        else:
+            selected += (np.repeat(np.arange(calls), rows) * context)[:, None].astype(np.int32)
+        selected = selected.reshape(calls, rows, selections)
+        positions = np.arange(rows, dtype=np.int32) if cfg == 3 else np.arange(rows, dtype=np.int32)
+        sinks = np.full(heads, -1e30, np.float32)
+        gpu = reference_gpu_backend(16 << 30) if ref else Backend(0, 16 << 30)
+        comp = gpu.upload(halves)
+        qb = [gpu.upload(q_np[c]) for c in range(calls)]
+        rb = [gpu.upload(raw_np[c]) for c in range(calls)]
+        sb = [gpu.upload(selected[c]) for c in range(calls)]
+        pb, kb = gpu.upload(positions), gpu.upload(sinks)
+        outs = [gpu.buffer(rows * heads * dim * 4) for _ in range(calls)]
+        scratch = gpu.buffer(512 << 20)
+        scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+
+        def step():
+            for c in range(calls):
+                gpu.sparse_attention(qb[c].pointer, rb[c].pointer, raw_np.shape[1], pb.pointer, window, (comp.tagged_bf16(), total_rows),
+                                     (sb[c].pointer, selections), kb.pointer, rows, heads, dim, scale, None, scratch, outs[c].pointer)
+        if ref:
+            probe = np.empty(4, np.float32)
+            for _ in range(2):
+                step()
+            gpu.read_buffer(outs[-1], 0, probe)
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                step()
+            gpu.read_buffer(outs[-1], 0, probe)
+            ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        else:
+            ms = timed(gpu, step, args.steps, args.warmup)
+        keys_per_row = selections + (window if cfg == 3 else (window + 1) / 2)
+        nbytes = calls * rows * selections * dim * 2
+        flops = 4.0 * dim * heads * calls * rows * keys_per_row
+        line.update({"workload": ("config 3: latent sparse decode, 32 queries x top-2048 of 65536, 576-wide BF16 rows" if cfg == 3 else
+                                  "config 4: verify spans, 16 sequences x 8 draft rows (one call per sequence), top-2048 of 32768, causal window in the span"),
+                     "heads": heads, "ms": ms, "gather_gbps": nbytes / ms / 1e6, "tflops": flops / ms / 1e9,
+                     "roofline_hbm_frac": nbytes / ms / 1e6 / peak_hbm, "roofline_tensor_frac": flops / ms / 1e9 / peak_tensor,
+                     "tokens_per_s": calls * rows / ms * 1e3})
+    line["peak_source"] = peak_source
+    print(json.dumps(line), flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
-    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
+    parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4], help="1 is the benchmark line; the others are measured for the design notes")
+    parser.add_argument("--head-shards", type=int, default=1, help="configs 3/4: heads per GPU = 128 / head_shards (the per-GPU work of head sharding)")
     parser.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--sequences", type=int, default=64, help="sequences per batch (64 is the benchmark; fewer for a profiler capture)")
@@ -180,9 +334,14 @@ def main():
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.config != 1:
+        run_other_config(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
+    if args.impl == "reference-gpu":
+        raise SystemExit("--impl reference-gpu is for --config 0, 2, 3, 4")
     if args.warmup < 3:
         args.warmup = 3
 

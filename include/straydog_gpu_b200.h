@@ -128,6 +128,13 @@ int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_
 /* 1 when a bounded wait inside a decode kernel gave up since the last call (cleared by the call), 0 if none. */
 int sdx_decode_status(void* handle);
 
+/* Causal prompt attention of a chunk: `rows` new tokens at positions first .. first + rows - 1 of a Q8_0 state
+   (their K/V rows already written, e.g. by sdx_kv_write) attend positions 0 .. their own. q [rows][heads][256]
+   FP16 and out [rows][heads][256] F32 are device pointers; heads / kv_heads is 1, 2, 4 or 8. The dense causal
+   form of the reference's qsa_flash_launch (gpu/sparse_attention_compute.hpp:589-608). */
+int sdx_qsa_prompt(void* handle, const void* state, uint64_t context, uint64_t first, uint64_t rows, uint64_t heads,
+                   uint64_t kv_heads, float scale, const void* q, float* out);
+
 /* One decode step of a batch from HOST buffers (the batched twin of sd_attention_sequence): for
    sequence s the new token's keys/values (k, v: [sequences][kv_heads][256] F32, host) are written
    to row bases[s] of states[s], then its query (q: [sequences][heads][256] FP16, host) attends rows

@@ -55,6 +55,7 @@ SIGNATURES = {
     "sdx_qsa_plan_info": ([p, pu64, pu64, pu64, pu64], i32),
     "sdx_qsa_plan_release": ([p, p], i32),
     "sdx_decode_status": ([p], i32),
+    "sdx_qsa_prompt": ([p, p, u64, u64, u64, u64, u64, f32, p, p], i32),
     "sdx_attention_batch": ([p, pp, pu64, pu64, u64, u64, u64, f32, p, p, p, p], i32),
 }
 

@@ -228,6 +228,10 @@ class Backend:
     def qsa_plan_release(self, plan):
         self._c(self.lib.sdx_qsa_plan_release(self.handle, plan))
 
+    def qsa_prompt(self, state, context, first, rows, heads, kv_heads, scale, q, out):
+        self._c(self.lib.sdx_qsa_prompt(self.handle, state.pointer if isinstance(state, Buffer) else state, context, first, rows, heads,
+                                        kv_heads, scale, q, out))
+
     def decode_status(self):
         return self._c(self.lib.sdx_decode_status(self.handle))
 

@@ -62,6 +62,7 @@ void* raw_allocate(Device& d, size_t bytes, bool zero);
 void raw_release(Device& d, void* pointer);
 void span(Device& d, const void* pointer, size_t bytes, const char* what);
 void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_host = false);
+int* status_word(Device& d);   // the device's word a kernel's bounded wait sets when it gives up (read by sdx_decode_status)
 
 // a * b * c ... with overflow refusal (gpu/core.hpp:1413 region: an op_span check never passes on a wrapped size)
 inline size_t checked_product(std::initializer_list<uint64_t> factors) {

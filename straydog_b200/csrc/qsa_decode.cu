@@ -410,7 +410,7 @@ static void run_plan(Device& d, const DecodePlan& plan, float scale, const void*
 }
 
 // The status word of the device's decode kernels (a wait that gave up sets it), read after a synchronising call.
-static int* status_word(Device& d) {
+int* status_word(Device& d) {
     static std::map<int, int*> words;
     static std::mutex mutex;
     std::lock_guard<std::mutex> lock(mutex);
