@@ -102,13 +102,8 @@ class ClockSampler:
 
 def batch_for(rank, world, scaling, sequences=64):
     """(lengths of this rank's sequences, their seeds)."""
-    from straydog_b200.synthetic import partition_longest_first, ragged_lengths
-    if scaling == "weak":
-        lengths = ragged_lengths(SEED + rank, sequences)
-        return lengths, [SEED * 1000 + rank * 100 + i for i in range(len(lengths))]
-    lengths = ragged_lengths(SEED, sequences)
-    mine = partition_longest_first(lengths, world)[rank]
-    return [lengths[i] for i in mine], [SEED * 1000 + i for i in mine]
+    from straydog_b200.sharding import rank_batch
+    return rank_batch(SEED, rank, world, scaling, sequences)
 
 
 def make_states(lengths, seeds):
@@ -444,13 +439,9 @@ def main():
     e2e_s = time.perf_counter() - t0
 
     # ---- max over ranks, sums over ranks ----
-    stats = torch.tensor([device_ms, e2e_s * 1e3, statistics.mean(kernel_ms)], device="cuda", dtype=torch.float64)
-    sums = torch.tensor([float(kv_bytes), float(n)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
-    device_ms_max, e2e_ms_max, kernel_ms_mean = (float(x) for x in stats.cpu())
-    total_bytes, total_sequences = (float(x) for x in sums.cpu())
+    from straydog_b200.sharding import whole_job
+    (device_ms_max, e2e_ms_max, kernel_ms_mean), (total_bytes, total_sequences) = whole_job(
+        [device_ms, e2e_s * 1e3, statistics.mean(kernel_ms)], [float(kv_bytes), float(n)], device="cuda")
 
     if rank == 0:
         peak, peak_source = measured_peaks()
