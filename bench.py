@@ -259,6 +259,8 @@ def run_other_config(args):
             rows, context, window, calls = 32, 65536, 1, 1
         else:
             rows, context, window, calls = 8, 32768, 8, 16
+        if args.context:
+            context = args.context
         rng = np.random.default_rng(SEED + cfg)
         total_rows = (rows if cfg == 3 else 1) * context * (1 if cfg == 3 else calls)
         # BF16 latent rows N(0, 0.05), generated in slabs to bound host memory
@@ -321,6 +323,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4], help="1 is the benchmark line; the others are measured for the design notes")
+    parser.add_argument("--context", type=int, default=0, help="configs 3/4: override the per-query context (a smaller resident set for a profiler capture)")
     parser.add_argument("--head-shards", type=int, default=1, help="configs 3/4: heads per GPU = 128 / head_shards (the per-GPU work of head sharding)")
     parser.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     parser.add_argument("--cpu-seconds", type=float, default=12.0)

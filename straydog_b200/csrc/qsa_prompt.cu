@@ -17,7 +17,12 @@
 #include "common.cuh"
 #include "../../include/straydog_gpu_b200.h"
 
+#include <cstdlib>
+
 namespace sdb {
+
+void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t first, size_t rows, size_t heads, size_t kv_heads,
+                      float scale, const void* q, float* out);
 
 constexpr int kPromptKeys = 64;                    // keys a tile
 constexpr int kPromptRow = (256 + 8) * 2;          // padded FP16 row in shared memory: 528 bytes
@@ -246,6 +251,13 @@ extern "C" int sdx_qsa_prompt(void* handle, const void* state, uint64_t context,
     span(value, out, checked_product({rows, heads, 256, 4}), "an attention output");
     if (reinterpret_cast<uintptr_t>(state) % 16 || reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(out) % 8)
         throw std::runtime_error("Straydog prompt attention operands must be 16-byte aligned");
+    // SDX_PROMPT_KERNEL=tcgen05 | mma (read at each call): the tcgen05/TMEM kernel or the mma.sync kernel
+    const char* choice = std::getenv("SDX_PROMPT_KERNEL");
+    if (choice && std::string(choice) == "tcgen05") {
+        launch_prompt_tc(value, static_cast<const uint8_t*>(state), context, first, rows, heads, kv_heads, scale, q, out);
+        SDB_CHECK(cudaGetLastError());
+        return 0;
+    }
     static bool configured[64] = {};
     if (!configured[value.ordinal & 63]) {
         SDB_CHECK(cudaFuncSetAttribute(qsa_prompt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kPromptSmem)));

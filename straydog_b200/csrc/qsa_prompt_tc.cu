@@ -1,0 +1,372 @@
+// Causal prompt attention over Q8_0 K/V on the 5th-generation tensor cores (tcgen05.mma, accumulators
+// in TMEM): the Blackwell-native form of sdx_qsa_prompt.
+//
+// A CTA owns 128 M-rows: 128 / group consecutive query tokens x the `group` query heads of one K/V head.
+// It walks the causal key range in tiles of 64 keys:
+//   S[128 x 64]  = Q[128 x 256] . K_tile^T      16 x tcgen05.mma (M 128, N 64, K 16), FP16 in, FP32 in TMEM
+//   O[128 x 256] += P[128 x 64] . V_tile         4 x tcgen05.mma (M 128, N 256, K 16)
+// TMEM (512 columns): O in columns 0..255, two S buffers in 256..319 and 320..383.
+//
+// Warp roles (12 warps):
+//   warps 0-3   softmax: thread = one M-row (its TMEM lane). tcgen05.ld of the row's 64 scores, mask, running
+//               max / sum, P rounded to FP16 into shared memory in the operand's swizzled layout; O is rescaled in
+//               TMEM only when a row's maximum has grown by more than 2^8 (the stale maximum stays exact
+//               arithmetic: weights are at most 256 and the final division uses the same maximum); epilogue.
+//   warp 4      one thread issues every tcgen05.mma and commits them to mbarriers.
+//   warps 5-11  dequantisers: Q8_0 rows straight from global memory (L2-resident: a state is a few MB) as 16-byte
+//               pieces, value = FP16(int8 * scale) (the rounding of the reference's own tensor-core kernel,
+//               gpu/kernels.cpp:46-54), stored as the 128-byte-swizzled K-major / MN-major operand tiles.
+// K and V tiles are double buffered, S is double buffered, so the tensor pipe works on S(i+1) while the
+// softmax warps work on S(i). Every wait is bounded; a wait that gives up raises a flag that ends all roles,
+// frees TMEM and reports through the status word.
+#include "common.cuh"
+
+namespace sdb {
+namespace tc {
+
+constexpr int kM = 128, kN = 64, kD = 256;
+constexpr int kThreads = 384, kMmaWarp = 4, kDequantFirst = 5 * 32, kDequantThreads = 7 * 32;
+constexpr int kQBytes = kM * kD * 2, kKVBytes = kN * kD * 2, kPBytes = kM * kN * 2;
+constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kOffK + 2 * kKVBytes, kOffP = kOffV + 2 * kKVBytes, kOffBars = kOffP + kPBytes;
+constexpr size_t kSmem = kOffBars + 256 + 1024;   // + slack to align the base to 1024 bytes
+constexpr uint32_t kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;
+
+struct Args {
+    const uint8_t* keys;
+    const uint8_t* values;
+    size_t context, first, rows, heads, kv_heads, group;
+    const __half* q;
+    float* out;
+    float scale_log2;
+    int* status;
+};
+
+enum Bar { kKFull = 0, kKFree = 2, kVFull = 4, kVFree = 6, kSFull = 8, kSFree = 10, kPFull = 12, kPvDone = 13, kBars = 14 };
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
+    // start address, leading and stride byte offsets in 16-byte units; descriptor version 1; 128-byte swizzle
+    return uint64_t((address & 0x3ffffu) >> 4) | (uint64_t(leading_bytes >> 4) << 16) | (uint64_t(stride_bytes >> 4) << 32) |
+           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// kind::f16 instruction descriptor: FP32 accumulator, FP16 A and B, A K-major, B K-major or MN-major, shape M x N
+__device__ __forceinline__ uint32_t instr_desc(int m, int n, bool b_mn_major) {
+    return (1u << 4) | (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                   "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+                   "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    #pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]), "f"(v[9]),
+                   "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]), "f"(v[16]), "f"(v[17]), "f"(v[18]), "f"(v[19]),
+                   "f"(v[20]), "f"(v[21]), "f"(v[22]), "f"(v[23]), "f"(v[24]), "f"(v[25]), "f"(v[26]), "f"(v[27]), "f"(v[28]), "f"(v[29]),
+                   "f"(v[30]), "f"(v[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Sixteen consecutive Q8_0 values (16 raw bytes) of a block with FP16 scale `scale_h`, as two 16-byte pieces of FP16.
+__device__ __forceinline__ void dequant16(const uint4& bytes, __half scale_h, uint4& first, uint4& second) {
+    const __half2 scale2 = __halves2half2(scale_h, scale_h);
+    const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));   // 1152 = 1024 + 128
+    const uint32_t words[4] = {bytes.x ^ 0x80808080u, bytes.y ^ 0x80808080u, bytes.z ^ 0x80808080u, bytes.w ^ 0x80808080u};
+    uint32_t h[8];
+    #pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const uint32_t lo = prmt(words[w], 0x64646464u, 0x4140u), hi = prmt(words[w], 0x64646464u, 0x4342u);
+        const __half2 a0 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&lo), bias), scale2);
+        const __half2 a1 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&hi), bias), scale2);
+        h[2 * w] = *reinterpret_cast<const uint32_t*>(&a0);
+        h[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&a1);
+    }
+    first = make_uint4(h[0], h[1], h[2], h[3]);
+    second = make_uint4(h[4], h[5], h[6], h[7]);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const size_t tokens_per_block = kM / a.group;
+    const size_t blocks = (a.rows + tokens_per_block - 1) / tokens_per_block;
+    const size_t block = blocks - 1 - blockIdx.x, kv = blockIdx.y;   // longest blocks first
+    const size_t r0 = block * tokens_per_block;
+
+    if (tid == 0) {
+        const uint32_t counts[kBars] = {7, 7, 1, 1, 7, 7, 1, 1, 1, 1, 4, 4, 4, 1};
+        for (int i = 0; i < kBars; ++i) mbar_init(&bars[i], counts[i]);
+        *abort_flag = 0;
+    }
+    fence_barrier_init();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q -> shared memory, K-major with 128-byte swizzle: four 64-column blocks of [128 rows][128 bytes]
+    for (int i = tid; i < kM * 32; i += kThreads) {
+        const int m = i / 32, piece = i % 32;   // 16-byte piece = 8 columns
+        const size_t row = r0 + m / a.group, head = kv * a.group + m % a.group;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < a.rows) v = *reinterpret_cast<const uint4*>(a.q + (row * a.heads + head) * kD + piece * 8);
+        *reinterpret_cast<uint4*>(smem + kOffQ + (piece / 8) * (kM * 128) + m * 128 + (((piece % 8) ^ (m & 7)) << 4)) = v;
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const size_t last_row = min(a.rows, r0 + tokens_per_block) - 1;
+    const size_t keys_total = min(a.context, a.first + last_row + 1);
+    const uint32_t tiles = uint32_t((keys_total + kN - 1) / kN);
+    const uint8_t* key_plane = a.keys + kv * a.context * kv_row_q8;
+    const uint8_t* value_plane = a.values + kv * a.context * kv_row_q8;
+
+    // a bounded wait that also ends when another role has given up
+    auto wait = [&](int bar, uint32_t parity) -> bool {
+        if (mbar_try_wait(&bars[bar], parity)) return true;
+        const uint64_t start = global_timer_ns();
+        for (;;) {
+            #pragma unroll 1
+            for (int spin = 0; spin < 32; ++spin)
+                if (mbar_try_wait(&bars[bar], parity)) return true;
+            if (*abort_flag) return false;
+            if (global_timer_ns() - start > 2000000000ull) { *abort_flag = 1; atomicExch(a.status, 1); return false; }
+        }
+    };
+
+    if (warp < 4) {
+        // ================= softmax, correction, epilogue: thread = M-row =================
+        const int m = tid;
+        const size_t token = r0 + m / a.group, head = kv * a.group + m % a.group;
+        const bool valid = token < a.rows;
+        const long long limit = valid ? (long long)(a.first + token) : -1;
+        const uint32_t lane_base = uint32_t(warp * 32) << 16;
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool alive = true;
+        for (uint32_t j = 0; j < tiles && alive; ++j) {
+            const uint32_t slot = j & 1;
+            if (!wait(kSFull + slot, (j >> 1) & 1)) { alive = false; break; }
+            tc_fence_after();
+            float s[64];
+            {
+                float half0[32], half1[32];
+                tmem_ld32(tmem + lane_base + 256 + slot * 64, half0);
+                tmem_ld32(tmem + lane_base + 256 + slot * 64 + 32, half1);
+                #pragma unroll
+                for (int i = 0; i < 32; ++i) { s[i] = half0[i]; s[32 + i] = half1[i]; }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[kSFree + slot]);
+            const long long begin = (long long)j * kN;
+            const bool edge = begin + kN - 1 > (long long)(a.first + r0) || begin + kN > (long long)keys_total;
+            float top = -INFINITY;
+            #pragma unroll
+            for (int n = 0; n < 64; ++n) {
+                float x = s[n] * a.scale_log2;
+                if (edge && begin + n > limit) x = -INFINITY;
+                s[n] = x;
+                top = fmaxf(top, x);
+            }
+            const float m_new = fmaxf(m_run, top);
+            // keep the old maximum while the new one is within 2^8 of it: no pass over O in TMEM
+            const bool grow = m_new > m_run + kRescaleThreshold || m_run == -INFINITY;
+            const float m_use = grow ? m_new : m_run;
+            if (j >= 1) {
+                if (!wait(kPvDone, (j - 1) & 1)) { alive = false; break; }   // P and O are free again
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grow && m_run != -INFINITY)) {
+                    const float factor = grow && m_run != -INFINITY ? fast_exp2(m_run - m_use) : 1.0f;
+                    #pragma unroll 1
+                    for (int c = 0; c < 8; ++c) {
+                        float o[32];
+                        tmem_ld32(tmem + lane_base + c * 32, o);
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= factor;
+                        tmem_st32(tmem + lane_base + c * 32, o);
+                    }
+                    tmem_st_wait();
+                    l_run *= factor;
+                } else if (grow && m_run != -INFINITY) {
+                    l_run *= fast_exp2(m_run - m_use);
+                }
+            }
+            if (grow && m_run == -INFINITY) l_run = 0.0f;
+            m_run = m_use;
+            const float u = m_run == -INFINITY ? 0.0f : m_run;
+            // P row: 64 FP16 = 8 pieces of 16 bytes, piece c at ((c ^ (m & 7)) << 4) of the row's 128 bytes
+            uint8_t* p_row = smem + kOffP + m * 128;
+            float sum = 0.0f;
+            #pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t packed[4];
+                #pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t pair = pack_half2(fast_exp2(s[8 * c + 2 * i] - u), fast_exp2(s[8 * c + 2 * i + 1] - u));
+                    const float2 rounded = __half22float2(*reinterpret_cast<const __half2*>(&pair));
+                    sum += rounded.x + rounded.y;
+                    packed[i] = pair;
+                }
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (m & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            l_run += sum;
+            fence_proxy_async();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[kPFull]);
+        }
+        // epilogue: O / l
+        if (alive && tiles > 0 && wait(kPvDone, (tiles - 1) & 1)) {
+            tc_fence_after();
+            const float inverse = 1.0f / l_run;
+            float* mine = a.out + (token * a.heads + head) * kD;
+            #pragma unroll 1
+            for (int c = 0; c < 8; ++c) {
+                float o[32];
+                tmem_ld32(tmem + lane_base + c * 32, o);
+                if (valid) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; i += 2) *reinterpret_cast<float2*>(mine + c * 32 + i) = make_float2(o[i] * inverse, o[i + 1] * inverse);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ================= the MMA issuer =================
+        if (lane == 0) {
+            const uint32_t q_base = smem_u32(smem + kOffQ), k_base = smem_u32(smem + kOffK), v_base = smem_u32(smem + kOffV),
+                           p_base = smem_u32(smem + kOffP);
+            const uint32_t idesc_s = instr_desc(kM, kN, false), idesc_o = instr_desc(kM, kD, true);
+            bool alive = true;
+            for (uint32_t i = 0; i <= tiles && alive; ++i) {
+                if (i < tiles) {
+                    const uint32_t slot = i & 1;
+                    if (!wait(kKFull + slot, (i >> 1) & 1)) break;
+                    if (i >= 2 && !wait(kSFree + slot, ((i - 2) >> 1) & 1)) break;
+                    tc_fence_after();
+                    #pragma unroll
+                    for (int kk = 0; kk < 16; ++kk) {
+                        const uint64_t a_desc = smem_desc(q_base + (kk / 4) * (kM * 128) + (kk % 4) * 32, 16, 1024);
+                        const uint64_t b_desc = smem_desc(k_base + slot * kKVBytes + (kk / 4) * (kN * 128) + (kk % 4) * 32, 16, 1024);
+                        umma(tmem + 256 + slot * 64, a_desc, b_desc, idesc_s, kk > 0);
+                    }
+                    umma_commit(&bars[kSFull + slot]);
+                    umma_commit(&bars[kKFree + slot]);
+                }
+                if (i >= 1) {
+                    const uint32_t j = i - 1, slot = j & 1;
+                    if (!wait(kPFull, j & 1)) break;
+                    if (!wait(kVFull + slot, (j >> 1) & 1)) break;
+                    tc_fence_after();
+                    #pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const uint64_t a_desc = smem_desc(p_base + kk * 32, 16, 1024);
+                        const uint64_t b_desc = smem_desc(v_base + slot * kKVBytes + kk * (16 * 128), kN * 128, 1024);
+                        umma(tmem, a_desc, b_desc, idesc_o, j > 0 || kk > 0);
+                    }
+                    umma_commit(&bars[kPvDone]);
+                    umma_commit(&bars[kVFree + slot]);
+                }
+            }
+        }
+    } else {
+        // ================= dequantisers =================
+        const int dt = tid - kDequantFirst;
+        bool alive = true;
+        for (uint32_t i = 0; i < tiles && alive; ++i) {
+            const uint32_t slot = i & 1;
+            const size_t begin = size_t(i) * kN;
+            const uint32_t count = uint32_t(min(size_t(kN), keys_total - begin));
+            #pragma unroll 1
+            for (int plane = 0; plane < 2 && alive; ++plane) {
+                if (i >= 2 && !wait((plane ? kVFree : kKFree) + slot, ((i - 2) >> 1) & 1)) { alive = false; break; }
+                const uint8_t* source = (plane ? value_plane : key_plane) + begin * kv_row_q8;
+                uint8_t* tile = smem + (plane ? kOffV : kOffK) + slot * kKVBytes;
+                uint4 bytes[5];
+                __half scales[5];
+                #pragma unroll
+                for (int u = 0; u < 5; ++u) {
+                    const int idx = dt + u * kDequantThreads, r = idx / 16, piece = idx % 16;
+                    bytes[u] = make_uint4(0x80808080u ^ 0x80808080u, 0, 0, 0);
+                    scales[u] = __ushort_as_half(0);
+                    if (idx < kN * 16 && uint32_t(r) < count) {
+                        bytes[u] = __ldg(reinterpret_cast<const uint4*>(source + size_t(r) * kv_row_q8 + piece * 16));
+                        scales[u] = __ldg(reinterpret_cast<const __half*>(source + size_t(r) * kv_row_q8 + 256) + piece / 2);
+                    }
+                }
+                #pragma unroll
+                for (int u = 0; u < 5; ++u) {
+                    const int idx = dt + u * kDequantThreads, r = idx / 16, piece = idx % 16;
+                    if (idx >= kN * 16) continue;
+                    uint4 first, second;
+                    dequant16(bytes[u], scales[u], first, second);   // (rows past the last key: zero bytes, zero scale -> zeros)
+                    uint8_t* row = tile + (piece / 4) * (kN * 128) + r * 128;
+                    const int chunk = (piece % 4) * 2;
+                    *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) = first;
+                    *reinterpret_cast<uint4*>(row + (((chunk + 1) ^ (r & 7)) << 4)) = second;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars[(plane ? kVFull : kKFull) + slot]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace tc
+
+void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t first, size_t rows, size_t heads, size_t kv_heads,
+                      float scale, const void* q, float* out) {
+    static bool configured[64] = {};
+    if (!configured[d.ordinal & 63]) {
+        SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
+        configured[d.ordinal & 63] = true;
+    }
+    tc::Args args{};
+    args.keys = state;
+    args.values = state + kv_heads * context * kv_row_q8;
+    args.context = context; args.first = first; args.rows = rows; args.heads = heads; args.kv_heads = kv_heads; args.group = heads / kv_heads;
+    args.q = static_cast<const __half*>(q);
+    args.out = out;
+    args.scale_log2 = scale * 1.4426950408889634f;
+    args.status = status_word(d);
+    const size_t tokens_per_block = tc::kM / args.group;
+    const dim3 grid{unsigned((rows + tokens_per_block - 1) / tokens_per_block), unsigned(kv_heads)};
+    tc::qsa_prompt_tc_kernel<<<grid, tc::kThreads, tc::kSmem, d.stream>>>(args);
+    ++d.launches;
+}
+
+}  // namespace sdb

@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 import oracle
-from util import close, q8_state, queries_f16
+from util import close, q8_state, q8_value_bound, queries_f16
 
 pytestmark = pytest.mark.gpu
 GUARD, CANARY = 8, np.float32(12345.125)
@@ -31,7 +31,9 @@ def test_small_chunks_every_row(gpu, first, rows, heads, kv_heads):
     q = queries_f16(rng, rows, heads, 256)
     got = run_prompt(gpu, state, context, first, rows, heads, kv_heads, q)
     want = oracle.gqa_prompt_q8(state, context, first, heads, kv_heads, q, 1 / 16, f64=True)
-    ok, worst = close(got, want)
+    # K and V enter the tensor cores rounded to FP16 (as in the reference's own kernel): rows of a few keys whose large values
+    # cancel are held to 1e-3 of the largest value instead of to the sum's own size
+    ok, worst = close(got, want, value_bound=q8_value_bound(state))
     assert ok, worst
 
 
