@@ -35,33 +35,41 @@ __global__ void sparse_turns_kernel(const int32_t* __restrict__ positions, const
 // gpu/ops.hpp:1366-1377), as F32 and, for the tensor-core kernel, split into BF16 high and low parts
 // (q = hi + lo up to 2^-17 relative). exact_flag is cleared when any low part is non-zero outside the
 // rotated columns.
-__global__ void __launch_bounds__(256) sparse_prepare_q_kernel(const float* __restrict__ q, size_t heads, size_t dim, size_t pairs,
+__global__ void __launch_bounds__(128) sparse_prepare_q_kernel(const float* __restrict__ q, size_t heads, size_t dim, size_t pairs,
                                                                const double2* __restrict__ forward, float* __restrict__ rotated_q,
                                                                __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
                                                                int* __restrict__ inexact) {
-    const size_t row = blockIdx.x, plain = dim - 2 * pairs;
+    // block = (head, row); a thread takes adjacent column pairs (a rope pair never straddles two threads: dim and rope_dims are even)
+    const size_t head = blockIdx.x, row = blockIdx.y, plain = dim - 2 * pairs;
+    const size_t base = (row * heads + head) * dim;
     bool any = false;
-    for (size_t i = threadIdx.x; i < heads * dim; i += blockDim.x) {
-        const size_t head = i / dim, col = i % dim;
-        const float* source = q + (row * heads + head) * dim;
-        float v = source[col];
+    for (size_t col = 2 * threadIdx.x; col + 1 < dim; col += 2 * blockDim.x) {
+        float2 v = make_float2(q[base + col], q[base + col + 1]);   // (the caller's q is only known to be 4-byte aligned)
         if (col >= plain) {
-            const size_t pair = (col - plain) / 2;
-            const double2 g = forward[row * pairs + pair];
-            const double a = source[plain + 2 * pair], b = source[plain + 2 * pair + 1];
-            v = (col - plain) % 2 == 0 ? float(a * g.x - b * g.y) : float(a * g.y + b * g.x);
+            const double2 g = forward[row * pairs + (col - plain) / 2];
+            const double a = v.x, b = v.y;
+            v = make_float2(float(a * g.x - b * g.y), float(a * g.y + b * g.x));
         }
-        const size_t at = (row * heads + head) * dim + col;
-        if (rotated_q) rotated_q[at] = v;
+        if (rotated_q) { rotated_q[base + col] = v.x; rotated_q[base + col + 1] = v.y; }
         if (hi) {
-            const __nv_bfloat16 h = __float2bfloat16_rn(v);
-            const float rest = v - __bfloat162float(h);
-            hi[at] = h;
-            lo[at] = __float2bfloat16_rn(rest);
-            if (rest != 0.0f && col < plain) any = true;
+            const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
+            const float r0 = v.x - __bfloat162float(h0), r1 = v.y - __bfloat162float(h1);
+            *reinterpret_cast<__nv_bfloat162*>(hi + base + col) = __halves2bfloat162(h0, h1);
+            *reinterpret_cast<__nv_bfloat162*>(lo + base + col) = __halves2bfloat162(__float2bfloat16_rn(r0), __float2bfloat16_rn(r1));
+            if (col < plain && (r0 != 0.0f || r1 != 0.0f)) any = true;
         }
     }
-    if (inexact && any) atomicExch(inexact, 1);
+    if (dim % 2 && threadIdx.x == 0) {   // an odd last column (never rotated: rope_dims is even)
+        const float v = q[base + dim - 1];
+        if (rotated_q) rotated_q[base + dim - 1] = v;
+        if (hi) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            hi[base + dim - 1] = h;
+            lo[base + dim - 1] = __float2bfloat16_rn(v - __bfloat162float(h));
+            if (v != __bfloat162float(h)) any = true;
+        }
+    }
+    if (inexact && __syncthreads_or(any) && threadIdx.x == 0) atomicExch(inexact, 1);
 }
 
 // ---- FP32 kernel: block = (row, group of 4 heads, split); a warp per key ----
@@ -160,31 +168,55 @@ __global__ void __launch_bounds__(128) sparse_combine_kernel(const float* __rest
                                                              int log2_domain, float* __restrict__ out) {
     const size_t item = blockIdx.x, row = item / heads, head = item % heads, plain = dim - 2 * pairs;
     const float* first = partial + item * splits * (dim + 2);
-    const float unit = log2_domain ? 1.4426950408889634f : 1.0f;
-    const float sink = sinks[head] * unit;
-    float top = sink;
-    for (size_t s = 0; s < splits; ++s) top = fmaxf(top, first[s * (dim + 2) + dim]);
-    const auto weight = [&](float x) { return log2_domain ? exp2f(x) : expf(x); };
-    float denominator = weight(sink - top);   // (a sink of -inf adds 0)
-    for (size_t s = 0; s < splits; ++s) {
-        const float own = first[s * (dim + 2) + dim];
-        if (own != -INFINITY) denominator += first[s * (dim + 2) + dim + 1] * weight(own - top);
-    }
-    for (size_t pair = threadIdx.x; pair < dim / 2 + dim % 2; pair += blockDim.x) {
-        float o[2];
+    constexpr int kMaxSplits = 64;
+    __shared__ float factors[kMaxSplits];
+    __shared__ float denominator_shared;
+    if (threadIdx.x < 32) {
+        // the first warp: the head's maximum (with its sink), every split's factor and the denominator
+        const float unit = log2_domain ? 1.4426950408889634f : 1.0f;
+        const float sink = sinks[head] * unit;
+        float tops[kMaxSplits / 32], sums[kMaxSplits / 32], top = sink;
         #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const size_t d = 2 * pair + i;
-            float sum = 0.0f;
-            if (d < dim)
-                for (size_t s = 0; s < splits; ++s) {
-                    const float own = first[s * (dim + 2) + dim];
-                    if (own != -INFINITY) sum = fmaf(first[s * (dim + 2) + d], weight(own - top), sum);
-                }
-            o[i] = sum / denominator;
+        for (int i = 0; i < kMaxSplits / 32; ++i) {
+            const size_t s = threadIdx.x + 32 * i;
+            tops[i] = s < splits ? first[s * (dim + 2) + dim] : -INFINITY;
+            sums[i] = s < splits ? first[s * (dim + 2) + dim + 1] : 0.0f;
+            top = fmaxf(top, tops[i]);
         }
+        #pragma unroll
+        for (unsigned offset = 16; offset; offset /= 2) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+        float denominator = 0.0f;
+        #pragma unroll
+        for (int i = 0; i < kMaxSplits / 32; ++i) {
+            const size_t s = threadIdx.x + 32 * i;
+            const float factor = tops[i] == -INFINITY ? 0.0f : (log2_domain ? exp2f(tops[i] - top) : expf(tops[i] - top));
+            if (s < splits) factors[s] = factor;
+            denominator += factor * sums[i];
+        }
+        #pragma unroll
+        for (unsigned offset = 16; offset; offset /= 2) denominator += __shfl_xor_sync(0xffffffffu, denominator, offset);
+        // (a sink of -inf adds 0; top is finite whenever any key or the sink is)
+        if (threadIdx.x == 0) denominator_shared = denominator + (log2_domain ? exp2f(sink - top) : expf(sink - top));
+    }
+    __syncthreads();
+    const float denominator = denominator_shared;
+    for (size_t pair = threadIdx.x; pair < dim / 2 + dim % 2; pair += blockDim.x) {
         const size_t d = 2 * pair;
-        if (d >= plain && d + 1 < dim) {   // (plain is even whenever dim and rope_dims are: pairs never straddle it)
+        float o[2] = {0.0f, 0.0f};
+        if (d + 1 < dim && dim % 2 == 0) {
+            for (size_t s = 0; s < splits; ++s) {
+                const float2 x = *reinterpret_cast<const float2*>(first + s * (dim + 2) + d);   // (rows of dim + 2 floats, d even: 8-byte aligned when dim is even)
+                o[0] = fmaf(x.x, factors[s], o[0]);
+                o[1] = fmaf(x.y, factors[s], o[1]);
+            }
+        } else {
+            for (size_t s = 0; s < splits; ++s) {
+                o[0] = fmaf(first[s * (dim + 2) + d], factors[s], o[0]);
+                if (d + 1 < dim) o[1] = fmaf(first[s * (dim + 2) + d + 1], factors[s], o[1]);
+            }
+        }
+        o[0] /= denominator; o[1] /= denominator;
+        if (d >= plain && d + 1 < dim) {
             const double2 g = inverse[row * pairs + (d - plain) / 2];
             const double x = o[0], y = o[1];
             o[0] = float(x * g.x - y * g.y);
@@ -292,7 +324,7 @@ int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint6
     const float* q_used = q;
     if (pairs) {
         auto* rotated = reinterpret_cast<float*>(work);
-        sparse_prepare_q_kernel<<<unsigned(rows), 256, 0, value.stream>>>(q, heads, dim, pairs, forward, rotated, nullptr, nullptr, nullptr);
+        sparse_prepare_q_kernel<<<dim3(unsigned(heads), unsigned(rows)), 128, 0, value.stream>>>(q, heads, dim, pairs, forward, rotated, nullptr, nullptr, nullptr);
         ++value.launches;
         q_used = rotated;
     }

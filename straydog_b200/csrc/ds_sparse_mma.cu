@@ -317,7 +317,7 @@ void sparse_mma_launch(Device& d, const SparseArgs& a, const float* q, const flo
     auto* lo = reinterpret_cast<__nv_bfloat16*>(work + lo_at);
     auto* partial = reinterpret_cast<float*>(work + partial_at);
     SDB_CHECK(cudaMemsetAsync(flags, 0, 8, d.stream));
-    sparse_prepare_q_kernel<<<unsigned(rows), 256, 0, d.stream>>>(q, a.heads, a.dim, pairs, forward, nullptr, hi, lo, flags);
+    sparse_prepare_q_kernel<<<dim3(unsigned(a.heads), unsigned(rows)), 128, 0, d.stream>>>(q, a.heads, a.dim, pairs, forward, nullptr, hi, lo, flags);
     ++d.launches;
     const int lo_rope_from = pairs ? int((a.dim - 2 * pairs) / 16) : int(a.dim / 16);
     if (a.dim == 576) {

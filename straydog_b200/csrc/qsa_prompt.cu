@@ -251,9 +251,9 @@ extern "C" int sdx_qsa_prompt(void* handle, const void* state, uint64_t context,
     span(value, out, checked_product({rows, heads, 256, 4}), "an attention output");
     if (reinterpret_cast<uintptr_t>(state) % 16 || reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(out) % 8)
         throw std::runtime_error("Straydog prompt attention operands must be 16-byte aligned");
-    // SDX_PROMPT_KERNEL=tcgen05 | mma (read at each call): the tcgen05/TMEM kernel or the mma.sync kernel
+    // The tcgen05/TMEM kernel is the default; SDX_PROMPT_KERNEL=mma (read at each call) selects the mma.sync kernel for A/B runs.
     const char* choice = std::getenv("SDX_PROMPT_KERNEL");
-    if (choice && std::string(choice) == "tcgen05") {
+    if (!(choice && std::string(choice) == "mma")) {
         launch_prompt_tc(value, static_cast<const uint8_t*>(state), context, first, rows, heads, kv_heads, scale, q, out);
         SDB_CHECK(cudaGetLastError());
         return 0;

@@ -1,4 +1,5 @@
-"""Causal prompt attention over Q8_0 K/V (sdx_qsa_prompt) against the oracle."""
+"""Causal prompt attention over Q8_0 K/V (sdx_qsa_prompt) against the oracle: the mma.sync kernel (SDX_PROMPT_KERNEL=mma);
+the default tcgen05 kernel runs the same cases in test_gpu_y_prompt_tcgen05.py."""
 import numpy as np
 import pytest
 
@@ -7,6 +8,11 @@ from util import close, q8_state, q8_value_bound, queries_f16
 
 pytestmark = pytest.mark.gpu
 GUARD, CANARY = 8, np.float32(12345.125)
+
+
+@pytest.fixture(autouse=True)
+def use_mma_sync(monkeypatch):
+    monkeypatch.setenv("SDX_PROMPT_KERNEL", "mma")
 
 
 def run_prompt(gpu, state_np, context, first, rows, heads, kv_heads, q, scale=1 / 16):
