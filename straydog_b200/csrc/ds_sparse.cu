@@ -308,7 +308,10 @@ int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint6
 
     const bool force_simt = env_flag("SDX_SPARSE_SIMT");
     if (!force_simt && sparse_mma_supported(args)) {
-        sparse_mma_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        // (SDX_SPARSE_KERNEL=v1: the first form of the tensor-core kernel, two tiles in flight per CTA, kept for A/B runs)
+        const char* form = std::getenv("SDX_SPARSE_KERNEL");
+        if (form && form[0] == 'v' && form[1] == '1' && !form[2]) sparse_mma_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        else sparse_mma2_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         SDB_CHECK(cudaGetLastError());
         return 0;
     }

@@ -298,35 +298,46 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
         }
     } else {
         // ================= dequantisers =================
+        // A thread owns up to five 16-byte pieces of the K tile and five of the V tile. The raw bytes of tile i + 1 are
+        // loaded into registers before tile i is converted, so the L2 latency of a tile hides behind the arithmetic of the
+        // one before it.
         const int dt = tid - kDequantFirst;
-        bool alive = true;
-        for (uint32_t i = 0; i < tiles && alive; ++i) {
-            const uint32_t slot = i & 1;
+        uint4 bytes[2][5], next_bytes[2][5];
+        __half scales[2][5], next_scales[2][5];
+        auto load_tile = [&](uint32_t i, uint4 (&raw)[2][5], __half (&sc)[2][5]) {
             const size_t begin = size_t(i) * kN;
-            const uint32_t count = uint32_t(min(size_t(kN), keys_total - begin));
-            #pragma unroll 1
-            for (int plane = 0; plane < 2 && alive; ++plane) {
-                if (i >= 2 && !wait((plane ? kVFree : kKFree) + slot, ((i - 2) >> 1) & 1)) { alive = false; break; }
+            const uint32_t count = i < tiles ? uint32_t(min(size_t(kN), keys_total - begin)) : 0u;
+            #pragma unroll
+            for (int plane = 0; plane < 2; ++plane) {
                 const uint8_t* source = (plane ? value_plane : key_plane) + begin * kv_row_q8;
-                uint8_t* tile = smem + (plane ? kOffV : kOffK) + slot * kKVBytes;
-                uint4 bytes[5];
-                __half scales[5];
                 #pragma unroll
                 for (int u = 0; u < 5; ++u) {
                     const int idx = dt + u * kDequantThreads, r = idx / 16, piece = idx % 16;
-                    bytes[u] = make_uint4(0x80808080u ^ 0x80808080u, 0, 0, 0);
-                    scales[u] = __ushort_as_half(0);
-                    if (idx < kN * 16 && uint32_t(r) < count) {
-                        bytes[u] = __ldg(reinterpret_cast<const uint4*>(source + size_t(r) * kv_row_q8 + piece * 16));
-                        scales[u] = __ldg(reinterpret_cast<const __half*>(source + size_t(r) * kv_row_q8 + 256) + piece / 2);
+                    raw[plane][u] = make_uint4(0, 0, 0, 0);
+                    sc[plane][u] = __ushort_as_half(0);
+                    if (idx < kN * 16 && uint32_t(r) < count) {   // (rows past the last key stay zero bytes with a zero scale: zeros)
+                        raw[plane][u] = __ldg(reinterpret_cast<const uint4*>(source + size_t(r) * kv_row_q8 + piece * 16));
+                        sc[plane][u] = __ldg(reinterpret_cast<const __half*>(source + size_t(r) * kv_row_q8 + 256) + piece / 2);
                     }
                 }
+            }
+        };
+        load_tile(0, bytes, scales);
+        bool alive = true;
+        for (uint32_t i = 0; i < tiles && alive; ++i) {
+            const uint32_t slot = i & 1;
+            load_tile(i + 1, next_bytes, next_scales);
+            #pragma unroll
+            for (int plane = 0; plane < 2; ++plane) {
+                if (!alive) break;
+                if (i >= 2 && !wait((plane ? kVFree : kKFree) + slot, ((i - 2) >> 1) & 1)) { alive = false; break; }
+                uint8_t* tile = smem + (plane ? kOffV : kOffK) + slot * kKVBytes;
                 #pragma unroll
                 for (int u = 0; u < 5; ++u) {
                     const int idx = dt + u * kDequantThreads, r = idx / 16, piece = idx % 16;
                     if (idx >= kN * 16) continue;
                     uint4 first, second;
-                    dequant16(bytes[u], scales[u], first, second);   // (rows past the last key: zero bytes, zero scale -> zeros)
+                    dequant16(bytes[plane][u], scales[plane][u], first, second);
                     uint8_t* row = tile + (piece / 4) * (kN * 128) + r * 128;
                     const int chunk = (piece % 4) * 2;
                     *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) = first;
@@ -336,6 +347,10 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars[(plane ? kVFull : kKFull) + slot]);
             }
+            #pragma unroll
+            for (int plane = 0; plane < 2; ++plane)
+                #pragma unroll
+                for (int u = 0; u < 5; ++u) { bytes[plane][u] = next_bytes[plane][u]; scales[plane][u] = next_scales[plane][u]; }
         }
     }
     tc_fence_before();
