@@ -21,13 +21,17 @@
 // frees TMEM and reports through the status word.
 #include "common.cuh"
 
+#include <cstdlib>
+#include <cuda.h>   // CUtensorMap (the encode function is reached through cudaGetDriverEntryPoint: no link against the driver library)
+
 namespace sdb {
 namespace tc {
 
 constexpr int kM = 128, kN = 64, kD = 256;
 constexpr int kThreads = 384, kMmaWarp = 4, kDequantFirst = 5 * 32, kDequantThreads = 7 * 32;
+constexpr int kThreadsTma = 192, kTmaWarp = 5;   // the TMA-fed form: 4 softmax warps, the MMA warp, the copy warp
 constexpr int kQBytes = kM * kD * 2, kKVBytes = kN * kD * 2, kPBytes = kM * kN * 2;
-constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kOffK + 2 * kKVBytes, kOffP = kOffV + 2 * kKVBytes, kOffBars = kOffP + kPBytes;
+constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kOffK + 2 * kKVBytes, kOffP = kOffV + 2 * kKVBytes, kOffBars = kOffP + 2 * kPBytes;
 constexpr size_t kSmem = kOffBars + 256 + 1024;   // + slack to align the base to 1024 bytes
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
@@ -42,7 +46,7 @@ struct Args {
     int* status;
 };
 
-enum Bar { kKFull = 0, kKFree = 2, kVFull = 4, kVFree = 6, kSFull = 8, kSFree = 10, kPFull = 12, kPvDone = 13, kBars = 14 };
+enum Bar { kKFull = 0, kKFree = 2, kVFull = 4, kVFree = 6, kSFull = 8, kSFree = 10, kPFull = 12, kPFree = 14, kPvDone = 16, kBars = 17 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
     // start address, leading and stride byte offsets in 16-byte units; descriptor version 1; 128-byte swizzle
@@ -106,7 +110,11 @@ __device__ __forceinline__ void dequant16(const uint4& bytes, __half scale_h, ui
     second = make_uint4(h[4], h[5], h[6], h[7]);
 }
 
-__global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a) {
+// kTma: K and V tiles come as FP16 from a pre-dequantised workspace by tensor-map bulk copies (128-byte swizzle) instead of being
+// dequantised by seven warps of this CTA.
+template<bool kTma>
+__global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
+    constexpr int kBlockThreads = kTma ? kThreadsTma : kThreads;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
@@ -120,7 +128,8 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
     const size_t r0 = block * tokens_per_block;
 
     if (tid == 0) {
-        const uint32_t counts[kBars] = {7, 7, 1, 1, 7, 7, 1, 1, 1, 1, 4, 4, 4, 1};
+        const uint32_t fill = kTma ? 1 : 7;   // arrivals on a full barrier: the copy thread, or the seven dequantising warps
+        const uint32_t counts[kBars] = {fill, fill, 1, 1, fill, fill, 1, 1, 1, 1, 4, 4, 4, 4, 1, 1, 1};
         for (int i = 0; i < kBars; ++i) mbar_init(&bars[i], counts[i]);
         *abort_flag = 0;
     }
@@ -130,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // Q -> shared memory, K-major with 128-byte swizzle: four 64-column blocks of [128 rows][128 bytes]
-    for (int i = tid; i < kM * 32; i += kThreads) {
+    for (int i = tid; i < kM * 32; i += kBlockThreads) {
         const int m = i / 32, piece = i % 32;   // 16-byte piece = 8 columns
         const size_t row = r0 + m / a.group, head = kv * a.group + m % a.group;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -200,40 +209,39 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             // keep the old maximum while the new one is within 2^8 of it: no pass over O in TMEM
             const bool grow = m_new > m_run + kRescaleThreshold || m_run == -INFINITY;
             const float m_use = grow ? m_new : m_run;
-            if (j >= 1) {
-                if (!wait(kPvDone, (j - 1) & 1)) { alive = false; break; }   // P and O are free again
+            // The product that read this P slot two tiles ago is done. (Also: with it done, at most one product is still pending, which
+            // keeps the parity of the pv_done wait below unambiguous.)
+            if (j >= 2 && !wait(kPFree + slot, ((j - 2) >> 1) & 1)) { alive = false; break; }
+            if (j >= 1 && __any_sync(0xffffffffu, grow && m_run != -INFINITY)) {
+                // a maximum of this warp's rows has grown past the threshold: O is rescaled in TMEM once every product issued so far has landed
+                if (!wait(kPvDone, (j - 1) & 1)) { alive = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow && m_run != -INFINITY)) {
-                    const float factor = grow && m_run != -INFINITY ? fast_exp2(m_run - m_use) : 1.0f;
-                    #pragma unroll 1
-                    for (int c = 0; c < 8; ++c) {
-                        float o[32];
-                        tmem_ld32(tmem + lane_base + c * 32, o);
-                        #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= factor;
-                        tmem_st32(tmem + lane_base + c * 32, o);
-                    }
-                    tmem_st_wait();
-                    l_run *= factor;
-                } else if (grow && m_run != -INFINITY) {
-                    l_run *= fast_exp2(m_run - m_use);
+                const float factor = grow && m_run != -INFINITY ? fast_exp2(m_run - m_use) : 1.0f;
+                #pragma unroll 1
+                for (int c = 0; c < 8; ++c) {
+                    float o[32];
+                    tmem_ld32(tmem + lane_base + c * 32, o);
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] *= factor;
+                    tmem_st32(tmem + lane_base + c * 32, o);
                 }
+                tmem_st_wait();
+                l_run *= factor;
             }
             if (grow && m_run == -INFINITY) l_run = 0.0f;
             m_run = m_use;
             const float u = m_run == -INFINITY ? 0.0f : m_run;
             // P row: 64 FP16 = 8 pieces of 16 bytes, piece c at ((c ^ (m & 7)) << 4) of the row's 128 bytes
-            uint8_t* p_row = smem + kOffP + m * 128;
+            uint8_t* p_row = smem + kOffP + slot * kPBytes + m * 128;
             float sum = 0.0f;
             #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t packed[4];
                 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint32_t pair = pack_half2(fast_exp2(s[8 * c + 2 * i] - u), fast_exp2(s[8 * c + 2 * i + 1] - u));
-                    const float2 rounded = __half22float2(*reinterpret_cast<const __half2*>(&pair));
-                    sum += rounded.x + rounded.y;
-                    packed[i] = pair;
+                    const float p0 = fast_exp2(s[8 * c + 2 * i] - u), p1 = fast_exp2(s[8 * c + 2 * i + 1] - u);
+                    sum += p0 + p1;
+                    packed[i] = pack_half2(p0, p1);
                 }
                 *reinterpret_cast<uint4*>(p_row + ((c ^ (m & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
@@ -241,9 +249,10 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             fence_proxy_async();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[kPFull]);
+            if (lane == 0) mbar_arrive(&bars[kPFull + slot]);
         }
         // epilogue: O / l
+        if (alive && tiles >= 2 && !wait(kPFree + ((tiles - 2) & 1), ((tiles - 2) >> 1) & 1)) alive = false;   // (all but the last product done)
         if (alive && tiles > 0 && wait(kPvDone, (tiles - 1) & 1)) {
             tc_fence_after();
             const float inverse = 1.0f / l_run;
@@ -282,18 +291,42 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
                 }
                 if (i >= 1) {
                     const uint32_t j = i - 1, slot = j & 1;
-                    if (!wait(kPFull, j & 1)) break;
+                    if (!wait(kPFull + slot, (j >> 1) & 1)) break;
                     if (!wait(kVFull + slot, (j >> 1) & 1)) break;
                     tc_fence_after();
                     #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t a_desc = smem_desc(p_base + kk * 32, 16, 1024);
+                        const uint64_t a_desc = smem_desc(p_base + slot * kPBytes + kk * 32, 16, 1024);
                         const uint64_t b_desc = smem_desc(v_base + slot * kKVBytes + kk * (16 * 128), kN * 128, 1024);
                         umma(tmem, a_desc, b_desc, idesc_o, j > 0 || kk > 0);
                     }
                     umma_commit(&bars[kPvDone]);
                     umma_commit(&bars[kVFree + slot]);
+                    umma_commit(&bars[kPFree + slot]);
                 }
+            }
+        }
+    } else if constexpr (kTma) {
+        // ================= the copy thread: FP16 tiles by TMA =================
+        if (warp == kTmaWarp && lane == 0) {
+            const int32_t key_row0 = int32_t(kv * a.context), value_row0 = int32_t((a.kv_heads + kv) * a.context);
+            for (uint32_t i = 0; i < tiles; ++i) {
+                const uint32_t slot = i & 1;
+                const int32_t begin = int32_t(i * kN);
+                bool ok = true;
+                #pragma unroll
+                for (int plane = 0; plane < 2 && ok; ++plane) {
+                    if (i >= 2 && !wait((plane ? kVFree : kKFree) + slot, ((i - 2) >> 1) & 1)) { ok = false; break; }
+                    uint64_t* bar = &bars[(plane ? kVFull : kKFull) + slot];
+                    uint8_t* tile = smem + (plane ? kOffV : kOffK) + slot * kKVBytes;
+                    mbar_expect_tx(bar, kKVBytes);
+                    #pragma unroll
+                    for (int d = 0; d < 4; ++d)   // four 64-column blocks of [64 rows][128 bytes]
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                     ::"r"(smem_u32(tile + d * (kN * 128))), "l"(&kv_map), "r"(64 * d), "r"((plane ? value_row0 : key_row0) + begin),
+                                       "r"(smem_u32(bar)) : "memory");
+                }
+                if (!ok) break;
             }
         }
     } else {
@@ -363,13 +396,41 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
 
 }  // namespace tc
 
+// Q8_0 rows -> FP16 rows [plane][position][256] (512 bytes a row), once per call: value = FP16(int8 * scale). Positions at or past
+// `valid` (up to `padded`, the last tile's end) are written as zeros, so a tile never holds bits nobody wrote.
+__global__ void __launch_bounds__(256) prompt_dequant_kernel(const uint8_t* __restrict__ state, size_t context, size_t planes, size_t valid,
+                                                             size_t padded, __half* __restrict__ out) {
+    const size_t pieces = planes * padded * 16;   // 16-byte raw pieces
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < pieces; i += size_t(gridDim.x) * blockDim.x) {
+        const size_t piece = i % 16, position = (i / 16) % padded, plane = i / (16 * padded);
+        uint4 first = make_uint4(0, 0, 0, 0), second = first;
+        if (position < valid) {
+            const uint8_t* row = state + (plane * context + position) * kv_row_q8;
+            tc::dequant16(__ldg(reinterpret_cast<const uint4*>(row + piece * 16)), __ldg(reinterpret_cast<const __half*>(row + 256) + piece / 2), first, second);
+        }
+        uint4* target = reinterpret_cast<uint4*>(out + (plane * context + position) * 256 + piece * 16);
+        target[0] = first;
+        target[1] = second;
+    }
+}
+
+// cuTensorMapEncodeTiled through the runtime (no link against the driver library)
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        SDB_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result));
+        if (!entry || result != cudaDriverEntryPointSuccess) throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
+        fn = reinterpret_cast<EncodeTiled>(entry);
+    }
+    return fn;
+}
+
 void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t first, size_t rows, size_t heads, size_t kv_heads,
                       float scale, const void* q, float* out) {
-    static bool configured[64] = {};
-    if (!configured[d.ordinal & 63]) {
-        SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
-        configured[d.ordinal & 63] = true;
-    }
     tc::Args args{};
     args.keys = state;
     args.values = state + kv_heads * context * kv_row_q8;
@@ -380,7 +441,37 @@ void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t fi
     args.status = status_word(d);
     const size_t tokens_per_block = tc::kM / args.group;
     const dim3 grid{unsigned((rows + tokens_per_block - 1) / tokens_per_block), unsigned(kv_heads)};
-    tc::qsa_prompt_tc_kernel<<<grid, tc::kThreads, tc::kSmem, d.stream>>>(args);
+    static bool configured[64] = {};
+    if (!configured[d.ordinal & 63]) {
+        SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
+        SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
+        configured[d.ordinal & 63] = true;
+    }
+    CUtensorMap map{};
+    // SDX_PROMPT_FEED=inline (read at each call): the seven dequantising warps inside the CTA instead of the FP16 workspace + TMA
+    const char* feed = std::getenv("SDX_PROMPT_FEED");
+    if (feed && std::string(feed) == "inline") {
+        tc::qsa_prompt_tc_kernel<false><<<grid, tc::kThreads, tc::kSmem, d.stream>>>(args, map);
+        ++d.launches;
+        return;
+    }
+    // FP16 copy of the positions this chunk can see (library-owned workspace, grown on the first call of a size; L2-sized for the
+    // benchmark's chunk: 16384 positions x 4 planes x 512 bytes = 33.5 MB), then tensor-map bulk copies feed the MMA tiles
+    const size_t planes = 2 * kv_heads, valid = first + rows;
+    const size_t padded = std::min(context, (valid + tc::kN - 1) / tc::kN * tc::kN);
+    auto* fp16 = static_cast<__half*>(ensure(d, d.work, d.work_bytes, planes * context * 512));
+    const unsigned blocks = unsigned(std::min<size_t>((planes * padded * 16 + 255) / 256, size_t(d.sms) * 16));
+    prompt_dequant_kernel<<<blocks, 256, 0, d.stream>>>(state, context, planes, valid, padded, fp16);
+    ++d.launches;
+    SDB_CHECK(cudaGetLastError());
+    const cuuint64_t dims[2] = {256, cuuint64_t(planes * context)};
+    const cuuint64_t strides[1] = {512};
+    const cuuint32_t box[2] = {64, cuuint32_t(tc::kN)}, element_strides[2] = {1, 1};
+    const CUresult encoded = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, fp16, dims, strides, box, element_strides,
+                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (encoded != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(encoded)));
+    tc::qsa_prompt_tc_kernel<true><<<grid, tc::kThreadsTma, tc::kSmem, d.stream>>>(args, map);
     ++d.launches;
 }
 
