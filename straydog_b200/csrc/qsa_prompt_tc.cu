@@ -1,21 +1,28 @@
 // Causal prompt attention over Q8_0 K/V on the 5th-generation tensor cores (tcgen05.mma, accumulators
-// in TMEM): the Blackwell-native form of sdx_qsa_prompt.
+// and the A operands in TMEM): the Blackwell-native form of sdx_qsa_prompt.
+//
+// Before the attention kernel a small kernel turns the Q8_0 rows the chunk can see into FP16 rows
+// (value = FP16(int8 * scale), the rounding of the reference's own tensor-core kernel, gpu/kernels.cpp:46-54)
+// in a library-owned workspace that stays in L2 (33.5 MB for 16384 positions): every 64-key tile is then
+// dequantised once per call instead of once per 16-token block.
 //
 // A CTA owns 128 M-rows: 128 / group consecutive query tokens x the `group` query heads of one K/V head.
 // It walks the causal key range in tiles of 64 keys:
 //   S[128 x 64]  = Q[128 x 256] . K_tile^T      16 x tcgen05.mma (M 128, N 64, K 16), FP16 in, FP32 in TMEM
 //   O[128 x 256] += P[128 x 64] . V_tile         4 x tcgen05.mma (M 128, N 256, K 16)
-// TMEM (512 columns): O in columns 0..255, two S buffers in 256..319 and 320..383.
+// TMEM (all 512 columns): O in 0..255; two S buffers in 256..319 and 320..383; Q (FP16, two values a column) in
+// 384..511. P is written over the first 32 columns of the S buffer it was made from, so both products take their A
+// operand from TMEM and shared memory only holds K and V tiles.
 //
-// Warp roles (12 warps):
-//   warps 0-3   softmax: thread = one M-row (its TMEM lane). tcgen05.ld of the row's 64 scores, mask, running
-//               max / sum, P rounded to FP16 into shared memory in the operand's swizzled layout; O is rescaled in
-//               TMEM only when a row's maximum has grown by more than 2^8 (the stale maximum stays exact
-//               arithmetic: weights are at most 256 and the final division uses the same maximum); epilogue.
-//   warp 4      one thread issues every tcgen05.mma and commits them to mbarriers.
-//   warps 5-11  dequantisers: Q8_0 rows straight from global memory (L2-resident: a state is a few MB) as 16-byte
-//               pieces, value = FP16(int8 * scale) (the rounding of the reference's own tensor-core kernel,
-//               gpu/kernels.cpp:46-54), stored as the 128-byte-swizzled K-major / MN-major operand tiles.
+// Warp roles (10 warps):
+//   warps 0-7   softmax: two threads per M-row (32 of the tile's 64 columns each; warp w works on the TMEM lanes
+//               32 (w % 4).. a warp may touch). tcgen05.ld of the scores, mask, row maximum exchanged with the partner
+//               warp through shared memory, P rounded to FP16 and stored to TMEM; O is rescaled in TMEM only when a
+//               row's maximum has grown by more than 2^8 (the stale maximum stays exact arithmetic: weights are at
+//               most 256 and the final division uses the same maximum); epilogue O / l.
+//   warp 8      one thread issues every tcgen05.mma and commits them to mbarriers.
+//   warp 9      one thread feeds K and V tiles: tensor-map bulk copies (TMA, 128-byte swizzle) of four
+//               [64 rows][128 bytes] boxes per tile, which is the K-major / MN-major operand layout the MMA reads.
 // K and V tiles are double buffered, S is double buffered, so the tensor pipe works on S(i+1) while the
 // softmax warps work on S(i). Every wait is bounded; a wait that gives up raises a flag that ends all roles,
 // frees TMEM and reports through the status word.
@@ -28,11 +35,11 @@ namespace sdb {
 namespace tc {
 
 constexpr int kM = 128, kN = 64, kD = 256;
-constexpr int kThreads = 384, kMmaWarp = 4, kDequantFirst = 5 * 32, kDequantThreads = 7 * 32;
-constexpr int kThreadsTma = 192, kTmaWarp = 5;   // the TMA-fed form: 4 softmax warps, the MMA warp, the copy warp
+constexpr int kSoftmaxWarps = 8, kMmaWarp = 8, kTmaWarp = 9, kThreads = 320;   // 8 softmax warps, the MMA warp, the copy warp
 constexpr int kQBytes = kM * kD * 2, kKVBytes = kN * kD * 2, kPBytes = kM * kN * 2;
 constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kOffK + 2 * kKVBytes, kOffP = kOffV + 2 * kKVBytes, kOffBars = kOffP + 2 * kPBytes;
-constexpr size_t kSmem = kOffBars + 256 + 1024;   // + slack to align the base to 1024 bytes
+constexpr int kOffStats = kOffBars + 192;            // [2 halves][128 rows] floats exchanged between the two warps of a row block
+constexpr size_t kSmem = kOffStats + 2 * kM * 4 + 1024;   // + slack to align the base to 1024 bytes
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -62,6 +69,12 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
 }
+// the same with the A operand in TMEM (lane = row; a 32-bit column holds two consecutive K elements)
+__device__ __forceinline__ void umma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate)) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -90,6 +103,17 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
                    "f"(v[30]), "f"(v[31])
                  : "memory");
 }
+__device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t (&v)[32]) {
+    float f[32];
+    #pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+    tmem_st32(taddr, f);
+}
+__device__ __forceinline__ void tmem_st16_bits(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                   "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Sixteen consecutive Q8_0 values (16 raw bytes) of a block with FP16 scale `scale_h`, as two 16-byte pieces of FP16.
@@ -110,16 +134,17 @@ __device__ __forceinline__ void dequant16(const uint4& bytes, __half scale_h, ui
     second = make_uint4(h[4], h[5], h[6], h[7]);
 }
 
-// kTma: K and V tiles come as FP16 from a pre-dequantised workspace by tensor-map bulk copies (128-byte swizzle) instead of being
-// dequantised by seven warps of this CTA.
-template<bool kTma>
-__global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
-    constexpr int kBlockThreads = kTma ? kThreadsTma : kThreads;
+__device__ __forceinline__ void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+
+// K and V tiles come as FP16 from a pre-dequantised workspace by tensor-map bulk copies (128-byte swizzle).
+__global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
+    constexpr int kBlockThreads = kThreads;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* stats = reinterpret_cast<float*>(smem + kOffStats);
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const size_t tokens_per_block = kM / a.group;
@@ -128,8 +153,7 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
     const size_t r0 = block * tokens_per_block;
 
     if (tid == 0) {
-        const uint32_t fill = kTma ? 1 : 7;   // arrivals on a full barrier: the copy thread, or the seven dequantising warps
-        const uint32_t counts[kBars] = {fill, fill, 1, 1, fill, fill, 1, 1, 1, 1, 4, 4, 4, 4, 1, 1, 1};
+        const uint32_t counts[kBars] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, kSoftmaxWarps, kSoftmaxWarps, 1, 1, 1};   // (s_free: the product's commit)
         for (int i = 0; i < kBars; ++i) mbar_init(&bars[i], counts[i]);
         *abort_flag = 0;
     }
@@ -138,19 +162,31 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Q -> shared memory, K-major with 128-byte swizzle: four 64-column blocks of [128 rows][128 bytes]
-    for (int i = tid; i < kM * 32; i += kBlockThreads) {
-        const int m = i / 32, piece = i % 32;   // 16-byte piece = 8 columns
-        const size_t row = r0 + m / a.group, head = kv * a.group + m % a.group;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < a.rows) v = *reinterpret_cast<const uint4*>(a.q + (row * a.heads + head) * kD + piece * 8);
-        *reinterpret_cast<uint4*>(smem + kOffQ + (piece / 8) * (kM * 128) + m * 128 + (((piece % 8) ^ (m & 7)) << 4)) = v;
-    }
-    fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // Q -> TMEM columns 384..511 as the A operand of the score products (lane = M-row, a 32-bit column = two consecutive
+    // columns of Q): the tensor core then reads only K from shared memory. A softmax thread stores its half row.
+    if (warp < kSoftmaxWarps) {
+        const int rb = warp & 3, half = warp >> 2, m = rb * 32 + lane;
+        const size_t row = r0 + m / a.group, head = kv * a.group + m % a.group;
+        const uint4* source = reinterpret_cast<const uint4*>(a.q + (row * a.heads + head) * kD + half * 128);
+        #pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint32_t words[32];
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 v = row < a.rows ? __ldg(source + c * 8 + i) : make_uint4(0, 0, 0, 0);
+                words[4 * i] = v.x; words[4 * i + 1] = v.y; words[4 * i + 2] = v.z; words[4 * i + 3] = v.w;
+            }
+            tmem_st32_bits(tmem + (uint32_t(rb * 32) << 16) + 384 + half * 64 + c * 32, words);
+        }
+        tmem_st_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
 
     const size_t last_row = min(a.rows, r0 + tokens_per_block) - 1;
     const size_t keys_total = min(a.context, a.first + last_row + 1);
@@ -171,59 +207,55 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
         }
     };
 
-    if (warp < 4) {
-        // ================= softmax, correction, epilogue: thread = M-row =================
-        const int m = tid;
+    if (warp < kSoftmaxWarps) {
+        // ================= softmax, correction, epilogue: two threads per M-row, 32 of the tile's 64 columns each =================
+        // Warp w works on TMEM lanes 32 (w % 4) .. (the lanes a warp may touch) and columns 32 (w / 4) .. ; the two warps of a row
+        // block exchange their row maxima through shared memory, so both take the same decisions and keep their own partial sums.
+        const int rb = warp & 3, half = warp >> 2, m = rb * 32 + lane;
         const size_t token = r0 + m / a.group, head = kv * a.group + m % a.group;
         const bool valid = token < a.rows;
         const long long limit = valid ? (long long)(a.first + token) : -1;
-        const uint32_t lane_base = uint32_t(warp * 32) << 16;
+        const uint32_t lane_base = uint32_t(rb * 32) << 16;
+        float* mine_stat = stats + half * kM + m;
+        const float* other_stat = stats + (half ^ 1) * kM + m;
         float m_run = -INFINITY, l_run = 0.0f;
         bool alive = true;
         for (uint32_t j = 0; j < tiles && alive; ++j) {
             const uint32_t slot = j & 1;
             if (!wait(kSFull + slot, (j >> 1) & 1)) { alive = false; break; }
             tc_fence_after();
-            float s[64];
-            {
-                float half0[32], half1[32];
-                tmem_ld32(tmem + lane_base + 256 + slot * 64, half0);
-                tmem_ld32(tmem + lane_base + 256 + slot * 64 + 32, half1);
-                #pragma unroll
-                for (int i = 0; i < 32; ++i) { s[i] = half0[i]; s[32 + i] = half1[i]; }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[kSFree + slot]);
-            const long long begin = (long long)j * kN;
-            const bool edge = begin + kN - 1 > (long long)(a.first + r0) || begin + kN > (long long)keys_total;
+            float s[32];
+            tmem_ld32(tmem + lane_base + 256 + slot * 64 + half * 32, s);
+            const long long begin = (long long)j * kN + half * 32;
+            const bool edge = (long long)j * kN + kN - 1 > (long long)(a.first + r0) || (long long)j * kN + kN > (long long)keys_total;
             float top = -INFINITY;
             #pragma unroll
-            for (int n = 0; n < 64; ++n) {
+            for (int n = 0; n < 32; ++n) {
                 float x = s[n] * a.scale_log2;
                 if (edge && begin + n > limit) x = -INFINITY;
                 s[n] = x;
                 top = fmaxf(top, x);
             }
-            const float m_new = fmaxf(m_run, top);
+            *mine_stat = top;
+            pair_barrier(1 + rb);
+            const float m_new = fmaxf(m_run, fmaxf(top, *other_stat));
+            pair_barrier(1 + rb);   // (the partner has read this tile's maximum before the next one is written)
             // keep the old maximum while the new one is within 2^8 of it: no pass over O in TMEM
             const bool grow = m_new > m_run + kRescaleThreshold || m_run == -INFINITY;
             const float m_use = grow ? m_new : m_run;
-            // The product that read this P slot two tiles ago is done. (Also: with it done, at most one product is still pending, which
-            // keeps the parity of the pv_done wait below unambiguous.)
-            if (j >= 2 && !wait(kPFree + slot, ((j - 2) >> 1) & 1)) { alive = false; break; }
             if (j >= 1 && __any_sync(0xffffffffu, grow && m_run != -INFINITY)) {
-                // a maximum of this warp's rows has grown past the threshold: O is rescaled in TMEM once every product issued so far has landed
+                // a maximum of this warp's rows has grown past the threshold: O (this half's 128 columns) is rescaled in TMEM once every
+                // product issued so far has landed
                 if (!wait(kPvDone, (j - 1) & 1)) { alive = false; break; }
                 tc_fence_after();
                 const float factor = grow && m_run != -INFINITY ? fast_exp2(m_run - m_use) : 1.0f;
                 #pragma unroll 1
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     float o[32];
-                    tmem_ld32(tmem + lane_base + c * 32, o);
+                    tmem_ld32(tmem + lane_base + half * 128 + c * 32, o);
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= factor;
-                    tmem_st32(tmem + lane_base + c * 32, o);
+                    tmem_st32(tmem + lane_base + half * 128 + c * 32, o);
                 }
                 tmem_st_wait();
                 l_run *= factor;
@@ -231,36 +263,36 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
             if (grow && m_run == -INFINITY) l_run = 0.0f;
             m_run = m_use;
             const float u = m_run == -INFINITY ? 0.0f : m_run;
-            // P row: 64 FP16 = 8 pieces of 16 bytes, piece c at ((c ^ (m & 7)) << 4) of the row's 128 bytes
-            uint8_t* p_row = smem + kOffP + slot * kPBytes + m * 128;
+            // This half of the P row, 32 FP16 as 16 TMEM columns, over the first columns of the S buffer it came from (every thread of the
+            // row block has its scores in registers by now: both halves passed the barriers above). The product reads P from TMEM.
+            uint32_t packed[16];
             float sum = 0.0f;
             #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t packed[4];
-                #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float p0 = fast_exp2(s[8 * c + 2 * i] - u), p1 = fast_exp2(s[8 * c + 2 * i + 1] - u);
-                    sum += p0 + p1;
-                    packed[i] = pack_half2(p0, p1);
-                }
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (m & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            for (int i = 0; i < 16; ++i) {
+                const float p0 = fast_exp2(s[2 * i] - u), p1 = fast_exp2(s[2 * i + 1] - u);
+                sum += p0 + p1;
+                packed[i] = pack_half2(p0, p1);
             }
             l_run += sum;
-            fence_proxy_async();
+            tmem_st16_bits(tmem + lane_base + 256 + slot * 64 + half * 16, packed);
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[kPFull + slot]);
         }
-        // epilogue: O / l
-        if (alive && tiles >= 2 && !wait(kPFree + ((tiles - 2) & 1), ((tiles - 2) >> 1) & 1)) alive = false;   // (all but the last product done)
+        // epilogue: O / l, this half's 128 columns; the row's denominator is the two halves' sums
+        *mine_stat = l_run;
+        pair_barrier(1 + rb);
+        const float denominator = l_run + *other_stat;
+        if (alive && tiles >= 2 && !wait(kSFree + ((tiles - 2) & 1), ((tiles - 2) >> 1) & 1)) alive = false;   // (all but the last product done)
         if (alive && tiles > 0 && wait(kPvDone, (tiles - 1) & 1)) {
             tc_fence_after();
-            const float inverse = 1.0f / l_run;
-            float* mine = a.out + (token * a.heads + head) * kD;
+            const float inverse = 1.0f / denominator;
+            float* mine = a.out + (token * a.heads + head) * kD + half * 128;
             #pragma unroll 1
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 float o[32];
-                tmem_ld32(tmem + lane_base + c * 32, o);
+                tmem_ld32(tmem + lane_base + half * 128 + c * 32, o);
                 if (valid) {
                     #pragma unroll
                     for (int i = 0; i < 32; i += 2) *reinterpret_cast<float2*>(mine + c * 32 + i) = make_float2(o[i] * inverse, o[i + 1] * inverse);
@@ -270,8 +302,7 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
     } else if (warp == kMmaWarp) {
         // ================= the MMA issuer =================
         if (lane == 0) {
-            const uint32_t q_base = smem_u32(smem + kOffQ), k_base = smem_u32(smem + kOffK), v_base = smem_u32(smem + kOffV),
-                           p_base = smem_u32(smem + kOffP);
+            const uint32_t k_base = smem_u32(smem + kOffK), v_base = smem_u32(smem + kOffV);
             const uint32_t idesc_s = instr_desc(kM, kN, false), idesc_o = instr_desc(kM, kD, true);
             bool alive = true;
             for (uint32_t i = 0; i <= tiles && alive; ++i) {
@@ -282,9 +313,8 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
                     tc_fence_after();
                     #pragma unroll
                     for (int kk = 0; kk < 16; ++kk) {
-                        const uint64_t a_desc = smem_desc(q_base + (kk / 4) * (kM * 128) + (kk % 4) * 32, 16, 1024);
                         const uint64_t b_desc = smem_desc(k_base + slot * kKVBytes + (kk / 4) * (kN * 128) + (kk % 4) * 32, 16, 1024);
-                        umma(tmem + 256 + slot * 64, a_desc, b_desc, idesc_s, kk > 0);
+                        umma_a_tmem(tmem + 256 + slot * 64, tmem + 384 + kk * 8, b_desc, idesc_s, kk > 0);
                     }
                     umma_commit(&bars[kSFull + slot]);
                     umma_commit(&bars[kKFree + slot]);
@@ -296,17 +326,16 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
                     tc_fence_after();
                     #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t a_desc = smem_desc(p_base + slot * kPBytes + kk * 32, 16, 1024);
                         const uint64_t b_desc = smem_desc(v_base + slot * kKVBytes + kk * (16 * 128), kN * 128, 1024);
-                        umma(tmem, a_desc, b_desc, idesc_o, j > 0 || kk > 0);
+                        umma_a_tmem(tmem, tmem + 256 + slot * 64 + kk * 8, b_desc, idesc_o, j > 0 || kk > 0);
                     }
                     umma_commit(&bars[kPvDone]);
                     umma_commit(&bars[kVFree + slot]);
-                    umma_commit(&bars[kPFree + slot]);
+                    umma_commit(&bars[kSFree + slot]);   // P sat in the S buffer: free once the product has read it
                 }
             }
         }
-    } else if constexpr (kTma) {
+    } else {
         // ================= the copy thread: FP16 tiles by TMA =================
         if (warp == kTmaWarp && lane == 0) {
             const int32_t key_row0 = int32_t(kv * a.context), value_row0 = int32_t((a.kv_heads + kv) * a.context);
@@ -328,62 +357,6 @@ __global__ void __launch_bounds__(kTma ? kThreadsTma : kThreads, 1) qsa_prompt_t
                 }
                 if (!ok) break;
             }
-        }
-    } else {
-        // ================= dequantisers =================
-        // A thread owns up to five 16-byte pieces of the K tile and five of the V tile. The raw bytes of tile i + 1 are
-        // loaded into registers before tile i is converted, so the L2 latency of a tile hides behind the arithmetic of the
-        // one before it.
-        const int dt = tid - kDequantFirst;
-        uint4 bytes[2][5], next_bytes[2][5];
-        __half scales[2][5], next_scales[2][5];
-        auto load_tile = [&](uint32_t i, uint4 (&raw)[2][5], __half (&sc)[2][5]) {
-            const size_t begin = size_t(i) * kN;
-            const uint32_t count = i < tiles ? uint32_t(min(size_t(kN), keys_total - begin)) : 0u;
-            #pragma unroll
-            for (int plane = 0; plane < 2; ++plane) {
-                const uint8_t* source = (plane ? value_plane : key_plane) + begin * kv_row_q8;
-                #pragma unroll
-                for (int u = 0; u < 5; ++u) {
-                    const int idx = dt + u * kDequantThreads, r = idx / 16, piece = idx % 16;
-                    raw[plane][u] = make_uint4(0, 0, 0, 0);
-                    sc[plane][u] = __ushort_as_half(0);
-                    if (idx < kN * 16 && uint32_t(r) < count) {   // (rows past the last key stay zero bytes with a zero scale: zeros)
-                        raw[plane][u] = __ldg(reinterpret_cast<const uint4*>(source + size_t(r) * kv_row_q8 + piece * 16));
-                        sc[plane][u] = __ldg(reinterpret_cast<const __half*>(source + size_t(r) * kv_row_q8 + 256) + piece / 2);
-                    }
-                }
-            }
-        };
-        load_tile(0, bytes, scales);
-        bool alive = true;
-        for (uint32_t i = 0; i < tiles && alive; ++i) {
-            const uint32_t slot = i & 1;
-            load_tile(i + 1, next_bytes, next_scales);
-            #pragma unroll
-            for (int plane = 0; plane < 2; ++plane) {
-                if (!alive) break;
-                if (i >= 2 && !wait((plane ? kVFree : kKFree) + slot, ((i - 2) >> 1) & 1)) { alive = false; break; }
-                uint8_t* tile = smem + (plane ? kOffV : kOffK) + slot * kKVBytes;
-                #pragma unroll
-                for (int u = 0; u < 5; ++u) {
-                    const int idx = dt + u * kDequantThreads, r = idx / 16, piece = idx % 16;
-                    if (idx >= kN * 16) continue;
-                    uint4 first, second;
-                    dequant16(bytes[plane][u], scales[plane][u], first, second);
-                    uint8_t* row = tile + (piece / 4) * (kN * 128) + r * 128;
-                    const int chunk = (piece % 4) * 2;
-                    *reinterpret_cast<uint4*>(row + ((chunk ^ (r & 7)) << 4)) = first;
-                    *reinterpret_cast<uint4*>(row + (((chunk + 1) ^ (r & 7)) << 4)) = second;
-                }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars[(plane ? kVFull : kKFull) + slot]);
-            }
-            #pragma unroll
-            for (int plane = 0; plane < 2; ++plane)
-                #pragma unroll
-                for (int u = 0; u < 5; ++u) { bytes[plane][u] = next_bytes[plane][u]; scales[plane][u] = next_scales[plane][u]; }
         }
     }
     tc_fence_before();
@@ -443,18 +416,10 @@ void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t fi
     const dim3 grid{unsigned((rows + tokens_per_block - 1) / tokens_per_block), unsigned(kv_heads)};
     static bool configured[64] = {};
     if (!configured[d.ordinal & 63]) {
-        SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
-        SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
+        SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
         configured[d.ordinal & 63] = true;
     }
     CUtensorMap map{};
-    // SDX_PROMPT_FEED=inline (read at each call): the seven dequantising warps inside the CTA instead of the FP16 workspace + TMA
-    const char* feed = std::getenv("SDX_PROMPT_FEED");
-    if (feed && std::string(feed) == "inline") {
-        tc::qsa_prompt_tc_kernel<false><<<grid, tc::kThreads, tc::kSmem, d.stream>>>(args, map);
-        ++d.launches;
-        return;
-    }
     // FP16 copy of the positions this chunk can see (library-owned workspace, grown on the first call of a size; L2-sized for the
     // benchmark's chunk: 16384 positions x 4 planes x 512 bytes = 33.5 MB), then tensor-map bulk copies feed the MMA tiles
     const size_t planes = 2 * kv_heads, valid = first + rows;
@@ -471,7 +436,7 @@ void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t fi
                                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (encoded != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(encoded)));
-    tc::qsa_prompt_tc_kernel<true><<<grid, tc::kThreadsTma, tc::kSmem, d.stream>>>(args, map);
+    tc::qsa_prompt_tc_kernel<<<grid, tc::kThreads, tc::kSmem, d.stream>>>(args, map);
     ++d.launches;
 }
 

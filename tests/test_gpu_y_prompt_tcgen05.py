@@ -9,11 +9,9 @@ from util import close, q8_state, q8_value_bound, queries_f16
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["tma", "inline"])
-def use_tcgen05(request, monkeypatch):
-    """Both feeds of the tcgen05 kernel: FP16 workspace + tensor-map copies (the default), and in-CTA dequantising warps."""
+@pytest.fixture(autouse=True)
+def use_tcgen05(monkeypatch):
     monkeypatch.delenv("SDX_PROMPT_KERNEL", raising=False)
-    monkeypatch.setenv("SDX_PROMPT_FEED", request.param)
 
 
 @pytest.mark.parametrize("first,rows,heads,kv_heads", [(0, 16, 16, 2), (0, 1, 16, 2), (0, 17, 16, 2), (5, 40, 16, 2), (63, 2, 16, 2), (64, 64, 16, 2),
