@@ -6,7 +6,7 @@
 One process per GPU (torchrun sets RANK/LOCAL_RANK/WORLD_SIZE for N > 1). A step is one pass of the
 decode attention over one batch: 64 sequences with context lengths uniform in [1024, 32768], 16 query
 / 2 K/V heads of 256, Q8_0 K/V rows, FP16 queries, FP32 output. Sequences are independent, so ranks
-share no data: with --scaling weak (default) every rank decodes its own seeded 64-sequence batch; with
+share no data: with --scaling weak (default) every rank decodes a 64-sequence batch of the same seeded lengths and its own seeded contents; with
 --scaling strong the one 64-sequence batch is dealt over the ranks longest first.
 
 Prints ONE JSON line (rank 0). `value` is K/V gigabytes streamed per second by the whole job with
@@ -115,6 +115,7 @@ def cpu_sample(lengths, seeds, budget_s, want_threads=None):
     """Times the CPU oracle on the first sequences of the batch until about budget_s seconds are spent."""
     import oracle
     from straydog_b200.synthetic import queries_f16
+    oracle.set_threads(os.cpu_count() or 1)   # (torchrun exports OMP_NUM_THREADS=1 to its ranks)
     spent, nbytes, used = 0.0, 0, 0
     rng = np.random.default_rng(SEED)
     for length, seed in zip(lengths, seeds):
@@ -270,28 +271,33 @@ def run_other_config(args):
             halves[at:at + n] = synthetic.bf16_round(rng.normal(0, 0.05, (n, dim)).astype(np.float32))[0]
         _, q_np = synthetic.bf16_round(rng.normal(0, 1, (calls, rows, heads, dim)).astype(np.float32))
         raw_np = rng.normal(0, 0.05, (calls, max(rows, window), dim)).astype(np.float32)
-        selected = np.stack([np.sort(rng.choice(context, selections, replace=False)) for _ in range(calls * rows)]).astype(np.int32)
+        # config 3 touches 75.5 MB a step, which would stay in the 126 MB L2: successive steps rotate over `variants` index
+        # lists (302 MB in all); config 4's 16 calls touch 302 MB a step as it is
+        variants = 4 if cfg == 3 else 1
+        selected = np.stack([np.sort(rng.choice(context, selections, replace=False)) for _ in range(variants * calls * rows)]).astype(np.int32)
         if cfg == 3:
-            selected += (np.arange(rows) * context)[:, None].astype(np.int32)
+            selected += (np.tile(np.arange(rows), variants) * context)[:, None].astype(np.int32)
         else:
             selected += (np.repeat(np.arange(calls), rows) * context)[:, None].astype(np.int32)
-        selected = selected.reshape(calls, rows, selections)
+        selected = selected.reshape(variants * calls, rows, selections)
         positions = np.arange(rows, dtype=np.int32) if cfg == 3 else np.arange(rows, dtype=np.int32)
         sinks = np.full(heads, -1e30, np.float32)
         gpu = reference_gpu_backend(16 << 30) if ref else Backend(0, 16 << 30)
         comp = gpu.upload(halves)
         qb = [gpu.upload(q_np[c]) for c in range(calls)]
         rb = [gpu.upload(raw_np[c]) for c in range(calls)]
-        sb = [gpu.upload(selected[c]) for c in range(calls)]
+        sb = [gpu.upload(selected[c]) for c in range(variants * calls)]
+        turn = [0]
         pb, kb = gpu.upload(positions), gpu.upload(sinks)
         outs = [gpu.buffer(rows * heads * dim * 4) for _ in range(calls)]
         scratch = gpu.buffer(512 << 20)
         scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
 
         def step():
+            turn[0] = (turn[0] + 1) % variants
             for c in range(calls):
                 gpu.sparse_attention(qb[c].pointer, rb[c].pointer, raw_np.shape[1], pb.pointer, window, (comp.tagged_bf16(), total_rows),
-                                     (sb[c].pointer, selections), kb.pointer, rows, heads, dim, scale, None, scratch, outs[c].pointer)
+                                     (sb[turn[0] * calls + c].pointer, selections), kb.pointer, rows, heads, dim, scale, None, scratch, outs[c].pointer)
         if ref:
             probe = np.empty(4, np.float32)
             for _ in range(2):
@@ -309,7 +315,8 @@ def run_other_config(args):
         flops = 4.0 * dim * heads * calls * rows * keys_per_row
         line.update({"workload": ("config 3: latent sparse decode, 32 queries x top-2048 of 65536, 576-wide BF16 rows" if cfg == 3 else
                                   "config 4: verify spans, 16 sequences x 8 draft rows (one call per sequence), top-2048 of 32768, causal window in the span"),
-                     "heads": heads, "ms": ms, "gather_gbps": nbytes / ms / 1e6, "tflops": flops / ms / 1e9,
+                     "heads": heads, "l2": "steps rotate over 4 index lists (302 MB of rows against the 126 MB L2)" if cfg == 3 else "302 MB of rows a step",
+                     "ms": ms, "gather_gbps": nbytes / ms / 1e6, "tflops": flops / ms / 1e9,
                      "roofline_hbm_frac": nbytes / ms / 1e6 / peak_hbm, "roofline_tensor_frac": flops / ms / 1e9 / peak_tensor,
                      "tokens_per_s": calls * rows / ms * 1e3})
     line["peak_source"] = peak_source
@@ -450,7 +457,8 @@ def main():
         peak, peak_source = measured_peaks()
         value = total_bytes * args.steps / (device_ms_max / 1e3) / 1e9
         achieved = kv_bytes / (statistics.mean(kernel_ms) / 1e3) / 1e9
-        cpu_gbps, cpu_used, cpu_bytes, cpu_spent, cpu_threads = cpu_sample(lengths, seeds, args.cpu_seconds)
+        # the CPU baseline is timed at N = 1 only (a multi-rank run shares the host's cores with the other ranks)
+        cpu_gbps, cpu_used, cpu_bytes, cpu_spent, cpu_threads = cpu_sample(lengths, seeds, args.cpu_seconds) if world == 1 else (None, 0, 0, 0.0, 0)
         # parity spot check of the timed output against the oracle (one short sequence), so a wrong kernel cannot post a number
         import oracle
         shortest = int(np.argmin(lengths))
@@ -466,8 +474,8 @@ def main():
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                          "peak_source": peak_source, "kernel": "qsa_decode_kernel", "kernel_ms": statistics.mean(kernel_ms),
                          "frac_of_nominal_8tbs": achieved / 8000.0},
-            "cpu_baseline": {"value": cpu_gbps, "unit": UNIT, "cores": cpu_threads, "kind": "port",
-                             "sample": f"first {cpu_used} of {n} sequences ({cpu_bytes} K/V bytes, {cpu_spent:.1f} s)"},
+            "cpu_baseline": ({"value": cpu_gbps, "unit": UNIT, "cores": cpu_threads, "kind": "port",
+                              "sample": f"first {cpu_used} of {n} sequences ({cpu_bytes} K/V bytes, {cpu_spent:.1f} s)"} if world == 1 else None),
             "e2e": {"value": total_bytes * args.steps / (e2e_ms_max / 1e3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": int(q_host.nbytes + k_host.nbytes + v_host.nbytes), "d2h_bytes_per_step": int(out_host.nbytes),
                     "ms_per_step": e2e_ms_max / args.steps, "tokens_per_s": total_sequences * args.steps / (e2e_ms_max / 1e3)},

@@ -38,6 +38,7 @@ _sig("orc_sparse_attention", [_p, _p, _u64, _p, _u64, _p, _i32, _p, _u64, _p, _u
 _sig("orc_top_k", [_p, _u64, _u64, _u64, _p])
 _sig("orc_to_bf16", [_p, _u64, _p])
 _sig("orc_threads", [], _i32)
+_sig("orc_set_threads", [_i32])
 
 ROW_Q8 = 272
 DIM = 256
@@ -45,6 +46,10 @@ DIM = 256
 
 def threads() -> int:
     return int(_lib.orc_threads())
+
+
+def set_threads(n: int) -> None:
+    _lib.orc_set_threads(int(n))
 
 
 def f32_to_f16(x: float) -> int:

@@ -466,6 +466,15 @@ void orc_to_bf16(const float* x, uint64_t count, uint16_t* out) {
     for (uint64_t i = 0; i < count; ++i) out[i] = f32_to_bf16(x[i]);
 }
 
+// torchrun exports OMP_NUM_THREADS=1 to its ranks: the timed baseline asks for the host's cores explicitly.
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_threads(void) {
 #ifdef _OPENMP
     int n = 1;

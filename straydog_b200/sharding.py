@@ -10,10 +10,11 @@ from .synthetic import partition_longest_first, ragged_lengths
 def rank_batch(seed, rank, world, scaling, sequences=64):
     """(lengths, seeds) of the sequences `rank` decodes.
 
-    weak: every rank has its own seeded batch of `sequences` (per-GPU work fixed as N grows).
+    weak: every rank has a batch of `sequences` with the same seeded lengths and its own seeded contents
+    (per-GPU work fixed as N grows).
     strong: one batch of `sequences` dealt over the ranks, longest first, by K/V bytes."""
     if scaling == "weak":
-        lengths = ragged_lengths(seed + rank, sequences)
+        lengths = ragged_lengths(seed, sequences)
         return lengths, [seed * 1000 + rank * 100 + i for i in range(len(lengths))]
     if scaling != "strong":
         raise ValueError(f"unknown scaling {scaling!r}")

@@ -41,10 +41,10 @@ def test_two_ranks_shard_and_reduce():
     assert abs(loads[0] - loads[1]) <= max(everything), "longest-first packing balances to within one sequence"
     for r in range(world):
         _, weak, times, sums = results[r]
-        assert len(weak) == 64 and weak == ragged_lengths(SEED + r)
+        assert len(weak) == 64 and weak == ragged_lengths(SEED)
         assert times == [11.0, 3.0], "max over ranks"
         assert sums[0] == float(sum(everything)) and sums[1] == 64.0
-        assert sums[2] == float(sum(ragged_lengths(SEED)) + sum(ragged_lengths(SEED + 1)))
+        assert sums[2] == 2.0 * float(sum(ragged_lengths(SEED)))
 
 
 def test_partition_edge_cases():
