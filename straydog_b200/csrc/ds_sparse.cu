@@ -308,9 +308,12 @@ int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint6
 
     const bool force_simt = env_flag("SDX_SPARSE_SIMT");
     if (!force_simt && sparse_mma_supported(args)) {
-        // (SDX_SPARSE_KERNEL=v1: the first form of the tensor-core kernel, two tiles in flight per CTA, kept for A/B runs)
+        // (SDX_SPARSE_KERNEL=v1|v2|v3 forces one form of the tensor-core kernel for A/B runs; by default up to 16 heads
+        //  take the third form, sixteen warps over one head tile, and more heads the second, 32 heads a CTA)
         const char* form = std::getenv("SDX_SPARSE_KERNEL");
-        if (form && form[0] == 'v' && form[1] == '1' && !form[2]) sparse_mma_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        const char which = form && form[0] == 'v' && form[1] && !form[2] ? form[1] : (heads <= 16 ? '3' : '2');
+        if (which == '1') sparse_mma_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        else if (which == '3') sparse_mma3_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         else sparse_mma2_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         SDB_CHECK(cudaGetLastError());
         return 0;

@@ -48,6 +48,9 @@ void sparse_mma_launch(Device& d, const SparseArgs& a, const float* q, const flo
 void sparse_mma2_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
                         const double2* forward, const double2* inverse, float* out);
 
+void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
+                        const double2* forward, const double2* inverse, float* out);
+
 // kernels of ds_sparse.cu the tensor-core path reuses
 __global__ void sparse_prepare_q_kernel(const float* q, size_t heads, size_t dim, size_t pairs, const double2* forward, float* rotated_q,
                                         __nv_bfloat16* hi, __nv_bfloat16* lo, int* inexact);

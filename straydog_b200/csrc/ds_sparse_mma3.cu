@@ -1,0 +1,443 @@
+// Tensor-core kernel of the latent sparse attention (sd_op_sparse_attention) for sm_100a, third form:
+// sixteen compute warps and two copy warps a CTA; scores split by KEYS and the weighted sum split by
+// COLUMNS, so that a score is exponentiated once (not once per warp) and a warp issues about a third of
+// the instructions per key of the second form; the gather is taken off the compute warps altogether.
+// Measured on the second form and on a first draft of this one: a compute warp that issues its own
+// 16-byte cp.async copies sits in that issue for a third of a tile's time, and the index list has to be
+// read a whole tile ahead because it comes from HBM like the rows.
+//
+// What it replaces: op_attention_scores_kernel + op_attention_output_kernel + combine
+// (gpu/ops.hpp:1329-1434, 1542-1677). A CTA holds 16 heads of one query row and streams a split of that
+// row's selected compressed rows once; the queries are rotated and split into BF16 parts by the CTA itself
+// (gpu/ops.hpp:1318-1327, 1366-1377), so one launch and the combine make a call.
+//
+// CTA = 576 threads. Warps 0-15 are two groups of eight; the groups take alternate 32-key tiles of a
+// four-slot ring (group g owns slots g and g + 2), each with its own softmax state and its own partial.
+// Warp 16 + g is group g's copy warp: a lane per key, one bulk copy (TMA engine) of a whole row into a
+// padded shared-memory row, completion counted on the slot's full barrier; absent rows are zero-filled
+// by the lane itself. A slot returns through an empty barrier on which the group's warps arrive as they
+// leave the tile. Per tile a group runs three phases:
+//   scores   warp (kh, kq): keys 16 kh .. 16 kh + 15 of the tile, quarter kq of the contraction; Q and K
+//            fragments by ldmatrix, two accumulator pairs so that consecutive MMAs do not depend on each
+//            other. The four partial sums of a score go to a shared slab.                    [barrier A]
+//   softmax  warp w: heads 2w and 2w + 1, a lane per key pair: the four parts are added in part order,
+//            scaled and masked; running maximum and denominator of the head live in these lanes; the
+//            weights are rounded to BF16 once and stored with the rescale factor of the head. [barrier B]
+//   output   warp w: columns w * dim / 8 ..: O = O * factor + P V, P by ldmatrix from shared memory,
+//            V by transposing ldmatrix from the same rows that served as keys (keys are the values).
+// Exactness: as in the other forms, F32 operands are split into BF16 high and low parts and both are
+// multiplied, so BF16-tagged and F32 rows of equal values give equal bits (tests/ds_state_bf16_gpu.rs:99-102).
+// Every wait is bounded; a wait that gives up is voted through barrier A so that a group leaves together.
+#include "ds_sparse.cuh"
+
+#include <algorithm>
+#include <type_traits>
+
+namespace sdb {
+namespace v3 {
+
+constexpr int kT = 32;            // keys a tile
+constexpr int kStages = 4;        // tiles in the ring
+constexpr int kGroups = 2, kGroupWarps = 8, kGroupThreads = 32 * kGroupWarps;
+constexpr int kComputeThreads = kGroups * kGroupThreads, kThreads = kComputeThreads + 32 * kGroups;
+
+template<int DIM> struct Shape {
+    static constexpr int kRow = (DIM + 8) * 2;          // padded shared-memory row, bytes
+    static constexpr int kPlane = kT * kRow;
+    static constexpr int kKS = DIM / 64;                // k-steps (16 columns) of one contraction quarter
+    static constexpr int kCols = DIM / 8;               // output columns a warp owns
+    static constexpr int kNT = kCols / 8;               // its n-tiles (8 columns)
+    static constexpr int kSlabRow = kT + 8;             // floats
+    static constexpr int kSlab = 16 * kSlabRow;         // one contraction quarter's partial scores
+    static constexpr int kPRow = (kT + 8) * 2;          // bytes of a row of weights
+    static constexpr int kOffQhi = kStages * kPlane;
+    static constexpr int kOffQlo = kOffQhi + 16 * kRow;
+    static constexpr int kOffSlabs = kOffQlo + 16 * kRow;
+    static constexpr int kOffP = kOffSlabs + kGroups * 4 * kSlab * 4;
+    static constexpr int kOffFactors = kOffP + kGroups * 16 * kPRow;
+    static constexpr int kOffBars = kOffFactors + kGroups * 16 * 4;         // full[kStages], empty[kStages]
+    static constexpr int kOffPtrs = kOffBars + 2 * kStages * 8;             // F32 phase: a tile's key pointers
+    static constexpr int kOffMisc = kOffPtrs + kT * 8;                      // abort flag, live mask of an F32 tile
+    static constexpr size_t kSmem = kOffMisc + 16;
+    static_assert(kSmem <= 232448, "shared memory of one CTA");
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(address));
+}
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+__device__ __forceinline__ void group_barrier(int id) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kGroupThreads) : "memory");
+}
+// a group barrier that also ORs a flag over the group
+__device__ __forceinline__ bool group_barrier_or(int id, bool flag) {
+    uint32_t any;
+    asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %2, 0; bar.red.or.pred p, %1, %3, q; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(any) : "r"(id), "r"(uint32_t(flag)), "n"(kGroupThreads) : "memory");
+    return any != 0;
+}
+
+template<int DIM>
+__global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
+        const SparseArgs a, const float* __restrict__ q, size_t pairs, const double2* __restrict__ forward,
+        float scale_log2, float* __restrict__ partial, int* __restrict__ status) {
+    using S = Shape<DIM>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* planes = smem;
+    uint8_t* q_hi = smem + S::kOffQhi;
+    uint8_t* q_lo = smem + S::kOffQlo;
+    float* slabs = reinterpret_cast<float*>(smem + S::kOffSlabs);
+    uint8_t* weights = smem + S::kOffP;
+    float* factors = reinterpret_cast<float*>(smem + S::kOffFactors);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::kOffBars);
+    uint64_t* empty = full + kStages;
+    const float** key_ptrs = reinterpret_cast<const float**>(smem + S::kOffPtrs);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + S::kOffMisc);
+    uint32_t* f32_live = reinterpret_cast<uint32_t*>(smem + S::kOffMisc + 4);
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
+    const bool copier = warp >= kGroups * kGroupWarps;
+    const int group = copier ? warp - kGroups * kGroupWarps : warp / kGroupWarps, gw = warp % kGroupWarps;
+    const int kh = gw % 2, kq = gw / 2;                        // scores: key half of the tile, contraction quarter
+    const size_t split = blockIdx.x, splits = gridDim.x, row = blockIdx.z, head0 = size_t(blockIdx.y) * 16;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 32); mbar_init(&empty[s], kGroupWarps); }
+        *abort_flag = 0;
+    }
+    fence_barrier_init();
+    __syncthreads();
+
+    // a bounded wait that also ends when another warp has given up
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if (mbar_try_wait(bar, parity)) return true;
+        const uint64_t start = global_timer_ns();
+        for (;;) {
+            #pragma unroll 1
+            for (int spin = 0; spin < 32; ++spin)
+                if (mbar_try_wait(bar, parity)) return true;
+            if (*abort_flag) return false;
+            if (global_timer_ns() - start > 2000000000ull) { *abort_flag = 1; atomicExch(status, 1); return false; }
+        }
+    };
+
+    const KeyList list = key_list(a, row);
+    const bool rows_bf16 = state_is_bf16(a.compressed);
+    const size_t per_split = ((a.selections + splits - 1) / splits + kT - 1) / kT * kT;
+    const size_t sel_begin = min(a.selections, split * per_split), sel_end = min(a.selections, sel_begin + per_split);
+    const uint32_t stream_tiles = rows_bf16 ? uint32_t((sel_end - sel_begin + kT - 1) / kT) : 0u;
+    // F32 keys: the window rows (split 0) and untagged compressed rows, taken tile by tile before the stream
+    const size_t f32_begin = split == 0 ? 0 : list.raw_count + sel_begin;
+    const size_t f32_end = rows_bf16 ? (split == 0 ? list.raw_count : f32_begin) : list.raw_count + sel_end;
+    // (a CTA with F32 tiles keeps the last two slots for their high and low planes until those tiles are done)
+    uint8_t* f32_hi = planes + size_t(kStages - 2) * S::kPlane;
+    const uint32_t f32_tiles = [&] {
+        uint32_t n = 0;
+        for (size_t first = f32_begin; first < f32_end; ++n) first += min(size_t(kT), (first < list.raw_count ? list.raw_count : f32_end) - first);
+        return n;
+    }();
+
+    const int32_t* chosen = a.selected + row * a.selections;
+    auto index_of = [&](uint32_t tile) -> int32_t {   // this lane's row of `tile`
+        const size_t index = sel_begin + size_t(tile) * kT + lane;
+        return tile < stream_tiles && index < sel_end ? chosen[index] : -1;
+    };
+
+    // =========================== the copy warp of a group ===========================
+    if (copier) {
+        const uint8_t* halves = reinterpret_cast<const uint8_t*>(state_halves(a.compressed));
+        auto fill = [&](uint32_t tile, int32_t at) {
+            const int slot = int(tile % kStages);
+            uint8_t* dst = planes + size_t(slot) * S::kPlane + size_t(lane) * S::kRow;
+            if (at >= 0) {
+                mbar_expect_tx(&full[slot], DIM * 2);
+                bulk_g2s(dst, halves + size_t(at) * DIM * 2, DIM * 2, &full[slot]);
+            } else {   // an absent row: zeros, so that a zero weight never meets stale bits
+                #pragma unroll 4
+                for (int c = 0; c < DIM * 2 / 16; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0, 0, 0, 0);
+                fence_proxy_async();   // (a later bulk copy lands on the same bytes)
+                mbar_arrive(&full[slot]);
+            }
+        };
+        // indices are read two tiles before they are used: the list comes from HBM like the rows
+        int32_t next = index_of(uint32_t(group) + kGroups);
+        if (uint32_t(group) < stream_tiles) fill(uint32_t(group), index_of(uint32_t(group)));
+        __syncthreads_or(0);                                              // the queries are prepared
+        for (uint32_t i = 0; i < f32_tiles; ++i) { __syncthreads(); __syncthreads(); __syncthreads(); }
+        __syncthreads();                                                  // the last two slots join the ring
+        for (uint32_t tile = uint32_t(group) + kGroups; tile < stream_tiles; tile += kGroups) {
+            const int32_t at = next;
+            next = index_of(tile + kGroups);
+            if (tile >= uint32_t(kStages) && !wait(&empty[tile % kStages], ((tile / kStages) - 1) & 1)) break;
+            fill(tile, at);
+        }
+        return;
+    }
+
+    // =========================== the compute warps ===========================
+    // ---- the CTA's 16 query rows: rotated (double), split into BF16 high and low parts ----
+    bool any_lo = false;
+    {
+        const size_t plain = DIM - 2 * pairs;
+        constexpr int kEach = 16 * (DIM / 2) / kComputeThreads;   // column pairs a thread prepares
+        static_assert(16 * (DIM / 2) % kComputeThreads == 0, "the query rows divide evenly over the threads");
+        float2 loaded[kEach];
+        #pragma unroll
+        for (int it = 0; it < kEach; ++it) {   // (every load is asked for before the first is used)
+            const int i = threadIdx.x + it * kComputeThreads, head = i / (DIM / 2), col = 2 * (i % (DIM / 2));
+            loaded[it] = make_float2(0.0f, 0.0f);
+            if (head0 + head < a.heads) {
+                const float* src = q + (row * a.heads + head0 + head) * DIM + col;   // (only known to be 4-byte aligned)
+                loaded[it] = make_float2(src[0], src[1]);
+            }
+        }
+        #pragma unroll
+        for (int it = 0; it < kEach; ++it) {
+            const int i = threadIdx.x + it * kComputeThreads, head = i / (DIM / 2), col = 2 * (i % (DIM / 2));
+            float2 v = loaded[it];
+            if (size_t(col) >= plain && head0 + head < a.heads) {
+                const double2 turn = forward[row * pairs + (col - plain) / 2];
+                const double x = v.x, y = v.y;
+                v = make_float2(float(x * turn.x - y * turn.y), float(x * turn.y + y * turn.x));
+            }
+            const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
+            const float r0 = v.x - __bfloat162float(h0), r1 = v.y - __bfloat162float(h1);
+            *reinterpret_cast<__nv_bfloat162*>(q_hi + head * S::kRow + col * 2) = __halves2bfloat162(h0, h1);
+            *reinterpret_cast<__nv_bfloat162*>(q_lo + head * S::kRow + col * 2) = __halves2bfloat162(__float2bfloat16_rn(r0), __float2bfloat16_rn(r1));
+            if (size_t(col) < plain && (r0 != 0.0f || r1 != 0.0f)) any_lo = true;
+        }
+    }
+    // (low parts matter from the first rotated column on, or everywhere when some plain column is not a BF16 value)
+    const int lo_from = __syncthreads_or(any_lo) ? 0 : int((DIM - 2 * pairs) / 16);
+
+    float o[S::kNT][4];
+    #pragma unroll
+    for (int n = 0; n < S::kNT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    float m = -INFINITY, l = 0.0f;   // of head 2 gw + lane / 16 (the softmax phase's lanes)
+
+    // ---- lane constants of the three phases ----
+    const int frag_row = 8 * (lane / 16) + lane % 8, frag_half = (lane / 8) % 2;
+    const uint32_t k_lane = uint32_t((16 * kh + frag_row) * S::kRow + (16 * kq * S::kKS + 8 * frag_half) * 2);
+    const int a_row = lane % 8 + 8 * ((lane / 8) % 2), a_col = 8 * (lane / 16);     // A operand by ldmatrix: queries and weights
+    const uint32_t qhi_lane = smem_u32(q_hi) + uint32_t(a_row * S::kRow + (16 * kq * S::kKS + a_col) * 2);
+    const uint32_t qlo_lane = smem_u32(q_lo) + uint32_t(a_row * S::kRow + (16 * kq * S::kKS + a_col) * 2);
+    const uint32_t p_lane = smem_u32(weights) + uint32_t(group * 16 * S::kPRow + a_row * S::kPRow + a_col * 2);
+    const int v_key = 8 * ((lane / 8) % 2) + lane % 8, v_dim = 8 * (lane / 16);
+    const uint32_t v_lane = uint32_t(v_key * S::kRow + (gw * S::kCols + v_dim) * 2);
+    float* slab_out = slabs + (group * 4 + kq) * S::kSlab + g * S::kSlabRow + 16 * kh + 2 * t;
+    const int soft_head = 2 * gw + lane / 16, soft_key = 2 * (lane % 16);
+    const float* slab_in = slabs + group * 4 * S::kSlab + soft_head * S::kSlabRow + soft_key;
+    uint32_t* p_out = reinterpret_cast<uint32_t*>(weights + group * 16 * S::kPRow + soft_head * S::kPRow + soft_key * 2);
+    float* group_factors = factors + group * 16;
+
+    // ---- one tile for one group. has_lo: the tile has a low-part plane (F32 keys). failed: this warp's wait gave up.
+    //      Returns false when the group gives up. ----
+    auto compute = [&](uint32_t hi_plane, uint32_t lo_plane, uint32_t live, bool failed, auto lo_tag) -> bool {
+        constexpr bool has_lo = decltype(lo_tag)::value;
+        float s[2][2][4];   // [k-step parity][n-tile]: consecutive k-steps feed different accumulators
+        #pragma unroll
+        for (int i = 0; i < 2; ++i)
+            #pragma unroll
+            for (int j = 0; j < 2; ++j) { s[i][j][0] = s[i][j][1] = s[i][j][2] = s[i][j][3] = 0.0f; }
+        uint32_t qa[2][4], kb[2][4];
+        ldmatrix_x4(qa[0], qhi_lane);
+        ldmatrix_x4(kb[0], hi_plane + k_lane);
+        #pragma unroll
+        for (int ks = 0; ks < S::kKS; ++ks) {
+            const int cur = ks & 1, nxt = cur ^ 1;
+            if (ks + 1 < S::kKS) {   // (the next step's fragments are on their way while this step multiplies)
+                ldmatrix_x4(qa[nxt], qhi_lane + 32 * (ks + 1));
+                ldmatrix_x4(kb[nxt], hi_plane + k_lane + 32 * (ks + 1));
+            }
+            mma_bf16(s[cur][0], qa[cur], kb[cur][0], kb[cur][1]);
+            mma_bf16(s[cur][1], qa[cur], kb[cur][2], kb[cur][3]);
+            if (kq * S::kKS + ks >= lo_from) {
+                uint32_t al[4];
+                ldmatrix_x4(al, qlo_lane + 32 * ks);
+                mma_bf16(s[cur][0], al, kb[cur][0], kb[cur][1]);
+                mma_bf16(s[cur][1], al, kb[cur][2], kb[cur][3]);
+            }
+            if constexpr (has_lo) {
+                uint32_t bl[4];
+                ldmatrix_x4(bl, lo_plane + k_lane + 32 * ks);
+                mma_bf16(s[cur][0], qa[cur], bl[0], bl[1]);
+                mma_bf16(s[cur][1], qa[cur], bl[2], bl[3]);
+            }
+        }
+        #pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            *reinterpret_cast<float2*>(slab_out + 8 * j) = make_float2(s[0][j][0] + s[1][j][0], s[0][j][1] + s[1][j][1]);
+            *reinterpret_cast<float2*>(slab_out + 8 * S::kSlabRow + 8 * j) = make_float2(s[0][j][2] + s[1][j][2], s[0][j][3] + s[1][j][3]);
+        }
+        if (group_barrier_or(1 + group, failed)) return false;                         // barrier A
+        {   // softmax of heads 2 gw, 2 gw + 1: a lane per key pair
+            float2 sum = make_float2(0.0f, 0.0f);
+            #pragma unroll
+            for (int part = 0; part < 4; ++part) {
+                const float2 x = *reinterpret_cast<const float2*>(slab_in + part * S::kSlab);
+                sum.x += x.x; sum.y += x.y;
+            }
+            const float s0 = (live >> soft_key) & 1u ? sum.x * scale_log2 : -INFINITY;
+            const float s1 = (live >> (soft_key + 1)) & 1u ? sum.y * scale_log2 : -INFINITY;
+            float top = fmaxf(s0, s1);
+            #pragma unroll
+            for (int offset = 1; offset < 16; offset *= 2) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+            const float next = fmaxf(m, top);
+            const float factor = m == next ? 1.0f : (m == -INFINITY ? 0.0f : fast_exp2(m - next));
+            const float used = next == -INFINITY ? 0.0f : next;   // (no live key yet: weights 0, not NaN)
+            const uint32_t p = pack_bf16x2(fast_exp2(s0 - used), fast_exp2(s1 - used));
+            float total = bf16_lo(p) + bf16_hi(p);
+            #pragma unroll
+            for (int offset = 1; offset < 16; offset *= 2) total += __shfl_xor_sync(0xffffffffu, total, offset);
+            l = l * factor + total;
+            m = next;
+            *p_out = p;
+            if (lane % 16 == 0) group_factors[soft_head] = factor;
+        }
+        group_barrier(1 + group);                                                       // barrier B
+        {   // O = O * factor + P V over this warp's columns
+            const float f0 = group_factors[g], f1 = group_factors[g + 8];
+            if (__any_sync(0xffffffffu, f0 != 1.0f || f1 != 1.0f)) {
+                #pragma unroll
+                for (int n = 0; n < S::kNT; ++n) { o[n][0] *= f0; o[n][1] *= f0; o[n][2] *= f1; o[n][3] *= f1; }
+            }
+            #pragma unroll
+            for (int kk = 0; kk < kT / 16; ++kk) {
+                uint32_t pa[4], vb[S::kNT / 2][4], tail0 = 0, tail1 = 0;
+                ldmatrix_x4(pa, p_lane + 32 * kk);
+                #pragma unroll
+                for (int np = 0; np < S::kNT / 2; ++np) ldmatrix_x4_trans(vb[np], hi_plane + v_lane + uint32_t(16 * kk * S::kRow + 32 * np));
+                if constexpr (S::kNT % 2 == 1) ldmatrix_x2_trans(tail0, tail1, hi_plane + v_lane + uint32_t(16 * kk * S::kRow + 32 * (S::kNT / 2)));
+                #pragma unroll
+                for (int np = 0; np < S::kNT / 2; ++np) {
+                    mma_bf16(o[2 * np], pa, vb[np][0], vb[np][1]);
+                    mma_bf16(o[2 * np + 1], pa, vb[np][2], vb[np][3]);
+                }
+                if constexpr (S::kNT % 2 == 1) mma_bf16(o[S::kNT - 1], pa, tail0, tail1);
+                if constexpr (has_lo) {
+                    #pragma unroll
+                    for (int np = 0; np < S::kNT / 2; ++np) {
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, lo_plane + v_lane + uint32_t(16 * kk * S::kRow + 32 * np));
+                        mma_bf16(o[2 * np], pa, b[0], b[1]);
+                        mma_bf16(o[2 * np + 1], pa, b[2], b[3]);
+                    }
+                    if constexpr (S::kNT % 2 == 1) {
+                        ldmatrix_x2_trans(tail0, tail1, lo_plane + v_lane + uint32_t(16 * kk * S::kRow + 32 * (S::kNT / 2)));
+                        mma_bf16(o[S::kNT - 1], pa, tail0, tail1);
+                    }
+                }
+            }
+        }
+        return true;
+    };
+
+    // ---- F32 keys: converted into a high and a low plane (the last two slots), a tile at a time, by every compute thread ----
+    for (size_t first = f32_begin; first < f32_end;) {
+        // (a tile never mixes window rows with selected rows, so that the selected rows tile alike in both formats)
+        const size_t limit = first < list.raw_count ? list.raw_count : f32_end;
+        const size_t count = min(size_t(kT), limit - first);
+        __syncthreads();   // the planes' last readers are done
+        if (warp == 0) {
+            const float* key = size_t(lane) < count ? key_pointer(a, list, row, first + lane) : nullptr;
+            key_ptrs[lane] = key;
+            const uint32_t mask = __ballot_sync(0xffffffffu, key != nullptr);
+            if (lane == 0) *f32_live = mask;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < kT * (DIM / 2); i += kComputeThreads) {
+            const int r = i / (DIM / 2), c = 2 * (i % (DIM / 2));
+            const float* key = key_ptrs[r];
+            float2 v = make_float2(0.0f, 0.0f);
+            if (key) v = state_is_bf16(key) ? make_float2(__uint_as_float(uint32_t(state_halves(key)[c]) << 16), __uint_as_float(uint32_t(state_halves(key)[c + 1]) << 16))
+                                            : make_float2(key[c], key[c + 1]);
+            const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
+            *reinterpret_cast<__nv_bfloat162*>(f32_hi + r * S::kRow + c * 2) = __halves2bfloat162(h0, h1);
+            *reinterpret_cast<__nv_bfloat162*>(f32_hi + S::kPlane + r * S::kRow + c * 2) =
+                __halves2bfloat162(__float2bfloat16_rn(v.x - __bfloat162float(h0)), __float2bfloat16_rn(v.y - __bfloat162float(h1)));
+        }
+        fence_proxy_async();   // (bulk copies will land on these bytes later)
+        __syncthreads();
+        // (window tiles go to group 0; selected rows alternate between the groups exactly as the stream's tiles do, so
+        //  that F32 rows and BF16 rows of equal values are summed in the same order)
+        const int consumer = first < list.raw_count ? 0 : int(((first - list.raw_count - sel_begin) / kT) % kGroups);
+        if (group == consumer) compute(smem_u32(f32_hi), smem_u32(f32_hi) + S::kPlane, *f32_live, false, std::true_type{});
+        first += count;
+    }
+    __syncthreads();   // the F32 tiles are consumed: the last two slots join the ring
+
+    // ---- BF16 selected rows: tile t is consumed by group t % 2 from slot t % kStages ----
+    {
+        int32_t live_at = index_of(uint32_t(group));   // (read a tile ahead; the copy warp has had the same line a tile earlier still)
+        for (uint32_t tile = uint32_t(group); tile < stream_tiles; tile += kGroups) {
+            const int slot = int(tile % kStages);
+            const uint32_t live = __ballot_sync(0xffffffffu, live_at >= 0);
+            live_at = index_of(tile + kGroups);
+            const bool arrived = wait(&full[slot], (tile / kStages) & 1);
+            const uint32_t plane = smem_u32(planes) + uint32_t(slot) * S::kPlane;
+            if (!compute(plane, plane, live, !arrived, std::false_type{})) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+    }
+
+    // ---- the group's partial: [DIM sums | max (exp2 domain) | denominator] per head ----
+    #pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const size_t head = head0 + g + 8 * i;
+        if (head >= a.heads) continue;
+        float* mine = partial + ((row * a.heads + head) * (splits * kGroups) + split * kGroups + group) * (DIM + 2);
+        #pragma unroll
+        for (int n = 0; n < S::kNT; ++n)
+            *reinterpret_cast<float2*>(mine + gw * S::kCols + 8 * n + 2 * t) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+    }
+    if (lane % 16 == 0 && head0 + soft_head < a.heads) {
+        float* mine = partial + ((row * a.heads + head0 + soft_head) * (splits * kGroups) + split * kGroups + group) * (DIM + 2);
+        mine[DIM] = m; mine[DIM + 1] = l;
+    }
+}
+
+}  // namespace v3
+
+template<int DIM>
+static void launch_v3(Device& d, const SparseArgs& a, const float* q, size_t pairs, const double2* forward, size_t rows, size_t splits,
+                      float* partial, int* status) {
+    using S = v3::Shape<DIM>;
+    static bool configured[64] = {};
+    if (!configured[d.ordinal & 63]) {
+        SDB_CHECK(cudaFuncSetAttribute(v3::sparse_mma3_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(S::kSmem)));
+        configured[d.ordinal & 63] = true;
+    }
+    const dim3 grid{unsigned(splits), unsigned((a.heads + 15) / 16), unsigned(rows)};
+    v3::sparse_mma3_kernel<DIM><<<grid, v3::kThreads, S::kSmem, d.stream>>>(a, q, pairs, forward, a.scale * 1.4426950408889634f, partial, status);
+    ++d.launches;
+}
+
+void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
+                        const double2* forward, const double2* inverse, float* out) {
+    const size_t head_tiles = (a.heads + 15) / 16;
+    // one wave of CTAs (one per SM): as many splits as keep rows * head tiles * splits within the SM count,
+    // each group of a split at least two tiles
+    size_t splits = size_t(d.sms) / std::max<size_t>(1, rows * head_tiles);
+    splits = std::max<size_t>(1, std::min<size_t>({splits, size_t(16), std::max<size_t>(1, a.selections / (2 * v3::kT * v3::kGroups))}));
+    const size_t partials = splits * v3::kGroups;
+    const size_t total = 256 + checked_product({rows, a.heads, partials, a.dim + 2, 4});
+    auto* work = static_cast<uint8_t*>(ensure(d, d.partial, d.partial_bytes, total));
+    auto* partial = reinterpret_cast<float*>(work + 256);
+    int* status = status_word(d);
+    if (a.dim == 576) launch_v3<576>(d, a, q, pairs, forward, rows, splits, partial, status);
+    else launch_v3<512>(d, a, q, pairs, forward, rows, splits, partial, status);
+    SDB_CHECK(cudaGetLastError());
+    sparse_combine_kernel<<<unsigned(rows * a.heads), 128, 0, d.stream>>>(partial, partials, a.heads, a.dim, sinks, pairs, inverse, 1, out);
+    ++d.launches;
+}
+
+}  // namespace sdb

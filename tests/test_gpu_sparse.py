@@ -9,6 +9,16 @@ from util import XorShift, bf16_round, close, sparse_attention_case
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["default", "v2", "v3"])
+def form(request):
+    """Which form of the tensor-core kernel answers: the library's own choice by head count, or one form forced for every shape."""
+    import os
+    if request.param != "default":
+        os.environ["SDX_SPARSE_KERNEL"] = request.param
+    yield request.param
+    os.environ.pop("SDX_SPARSE_KERNEL", None)
+
+
 def reference_case(rows, heads):
     return sparse_attention_case(rows, heads)
 
@@ -31,7 +41,7 @@ def run(gpu, c, compressed_np, tagged, scratch_bytes=64 << 20):
 
 
 @pytest.mark.parametrize("rows,heads", [(1, 32), (4, 32), (64, 32), (16, 64)])
-def test_the_attention_of_bf16_rows_is_that_of_their_f32_values(gpu, rows, heads):
+def test_the_attention_of_bf16_rows_is_that_of_their_f32_values(gpu, form, rows, heads):
     c = reference_case(rows, heads)
     from_f32 = run(gpu, c, c["widened"], tagged=False)
     from_bf16 = run(gpu, c, c["halves"], tagged=True)
@@ -44,7 +54,7 @@ def test_the_attention_of_bf16_rows_is_that_of_their_f32_values(gpu, rows, heads
     assert ok, worst
 
 
-def test_benchmark_shape_small(gpu):
+def test_benchmark_shape_small(gpu, form):
     # config 3's shape at a size the oracle finishes quickly: 576-wide BF16 rows N(0, 0.05), unique sorted indices,
     # window 1 (the query's own F32 row), sinks at -inf, no rope
     rng = np.random.default_rng(41)
@@ -65,7 +75,7 @@ def test_benchmark_shape_small(gpu):
 @pytest.mark.parametrize("rows,heads,dim,window,selections,rope_dims,exact_q", [
     (3, 16, 576, 8, 200, 0, True), (8, 16, 576, 8, 2048, 64, True), (2, 128, 576, 1, 96, 0, True), (5, 24, 512, 128, 31, 64, False),
     (1, 8, 512, 3, 0, 0, False), (2, 40, 576, 40, 65, 128, False)])
-def test_tensor_core_kernel_shapes(gpu, rows, heads, dim, window, selections, rope_dims, exact_q):
+def test_tensor_core_kernel_shapes(gpu, form, rows, heads, dim, window, selections, rope_dims, exact_q):
     """Head tiles of 16 and 32 with tails, spans with a causal window (config 4's layout), rope on BF16-exact and on F32 queries,
     partial tiles, no selection at all; each against the F64 oracle and against this library's FP32 kernel."""
     import os
