@@ -1,5 +1,5 @@
 // Tensor-core kernel of the latent sparse attention (sd_op_sparse_attention) for sm_100a, third form:
-// sixteen compute warps and two copy warps a CTA; scores split by KEYS and the weighted sum split by
+// sixteen compute warps and four copy warps a CTA; scores split by KEYS and the weighted sum split by
 // COLUMNS, so that a score is exponentiated once (not once per warp) and a warp issues about a third of
 // the instructions per key of the second form; the gather is taken off the compute warps altogether.
 // Measured on the second form and on a first draft of this one: a compute warp that issues its own
@@ -9,11 +9,13 @@
 // What it replaces: op_attention_scores_kernel + op_attention_output_kernel + combine
 // (gpu/ops.hpp:1329-1434, 1542-1677). A CTA holds 16 heads of one query row and streams a split of that
 // row's selected compressed rows once; the queries are rotated and split into BF16 parts by the CTA itself
-// (gpu/ops.hpp:1318-1327, 1366-1377), so one launch and the combine make a call.
+// (gpu/ops.hpp:1318-1327, 1366-1377), and the CTAs of a (row, head tile) are a thread-block cluster that merges its splits through distributed
+// shared memory, so one launch makes a call and no partial goes to HBM.
 //
-// CTA = 576 threads. Warps 0-15 are two groups of eight; the groups take alternate 32-key tiles of a
+// CTA = 640 threads. Warps 0-15 are two groups of eight; the groups take alternate 32-key tiles of a
 // four-slot ring (group g owns slots g and g + 2), each with its own softmax state and its own partial.
-// Warp 16 + g is group g's copy warp: a lane per key, one bulk copy (TMA engine) of a whole row into a
+// Warps 16 + g and 18 + g are group g's copy warps (16 keys of a tile each; one warp alone needs two thirds of a
+// tile's time to issue 32 copies): a lane per key, one bulk copy (TMA engine) of a whole row into a
 // padded shared-memory row, completion counted on the slot's full barrier; absent rows are zero-filled
 // by the lane itself. A slot returns through an empty barrier on which the group's warps arrive as they
 // leave the tile. Per tile a group runs three phases:
@@ -39,7 +41,8 @@ namespace v3 {
 constexpr int kT = 32;            // keys a tile
 constexpr int kStages = 4;        // tiles in the ring
 constexpr int kGroups = 2, kGroupWarps = 8, kGroupThreads = 32 * kGroupWarps;
-constexpr int kComputeThreads = kGroups * kGroupThreads, kThreads = kComputeThreads + 32 * kGroups;
+constexpr int kCopyWarps = 2;     // copy warps a group, 16 rows of a tile each
+constexpr int kComputeThreads = kGroups * kGroupThreads, kThreads = kComputeThreads + 32 * kGroups * kCopyWarps;
 
 template<int DIM> struct Shape {
     static constexpr int kRow = (DIM + 8) * 2;          // padded shared-memory row, bytes
@@ -86,10 +89,24 @@ __device__ __forceinline__ bool group_barrier_or(int id, bool flag) {
     return any != 0;
 }
 
+// thread-block cluster: the CTAs of one (row, head tile) are a cluster, a CTA per split of the selected keys
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_address(uint32_t local, uint32_t rank) {   // the same shared-memory offset in CTA `rank`
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float2 cluster_load2(uint32_t address) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(address) : "memory");
+    return v;
+}
+
 template<int DIM>
 __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         const SparseArgs a, const float* __restrict__ q, size_t pairs, const double2* __restrict__ forward,
-        float scale_log2, float* __restrict__ partial, int* __restrict__ status) {
+        float scale_log2, int* __restrict__ status, const float* __restrict__ sinks, const double2* __restrict__ inverse, float* __restrict__ out) {
     using S = Shape<DIM>;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* planes = smem;
@@ -106,7 +123,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
     const bool copier = warp >= kGroups * kGroupWarps;
-    const int group = copier ? warp - kGroups * kGroupWarps : warp / kGroupWarps, gw = warp % kGroupWarps;
+    const int group = copier ? (warp - kGroups * kGroupWarps) % kGroups : warp / kGroupWarps, gw = warp % kGroupWarps;
+    const int copy_half = (warp - kGroups * kGroupWarps) / kGroups;   // of a copy warp: which 16 rows of a tile
     const int kh = gw % 2, kq = gw / 2;                        // scores: key half of the tile, contraction quarter
     const size_t split = blockIdx.x, splits = gridDim.x, row = blockIdx.z, head0 = size_t(blockIdx.y) * 16;
     if (threadIdx.x == 0) {
@@ -146,17 +164,20 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     }();
 
     const int32_t* chosen = a.selected + row * a.selections;
-    auto index_of = [&](uint32_t tile) -> int32_t {   // this lane's row of `tile`
-        const size_t index = sel_begin + size_t(tile) * kT + lane;
+    auto index_at = [&](uint32_t tile, int key) -> int32_t {   // row number of key `key` of `tile`, -1: none
+        const size_t index = sel_begin + size_t(tile) * kT + key;
         return tile < stream_tiles && index < sel_end ? chosen[index] : -1;
     };
 
-    // =========================== the copy warp of a group ===========================
+    // =========================== the copy warps of a group ===========================
     if (copier) {
         const uint8_t* halves = reinterpret_cast<const uint8_t*>(state_halves(a.compressed));
+        const bool active = lane < kT / kCopyWarps;
+        const int key = copy_half * (kT / kCopyWarps) + lane;
         auto fill = [&](uint32_t tile, int32_t at) {
+            if (!active) return;
             const int slot = int(tile % kStages);
-            uint8_t* dst = planes + size_t(slot) * S::kPlane + size_t(lane) * S::kRow;
+            uint8_t* dst = planes + size_t(slot) * S::kPlane + size_t(key) * S::kRow;
             if (at >= 0) {
                 mbar_expect_tx(&full[slot], DIM * 2);
                 bulk_g2s(dst, halves + size_t(at) * DIM * 2, DIM * 2, &full[slot]);
@@ -168,17 +189,20 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
             }
         };
         // indices are read two tiles before they are used: the list comes from HBM like the rows
-        int32_t next = index_of(uint32_t(group) + kGroups);
-        if (uint32_t(group) < stream_tiles) fill(uint32_t(group), index_of(uint32_t(group)));
+        int32_t next = active ? index_at(uint32_t(group) + kGroups, key) : -1;
+        if (uint32_t(group) < stream_tiles) fill(uint32_t(group), active ? index_at(uint32_t(group), key) : -1);
         __syncthreads_or(0);                                              // the queries are prepared
         for (uint32_t i = 0; i < f32_tiles; ++i) { __syncthreads(); __syncthreads(); __syncthreads(); }
         __syncthreads();                                                  // the last two slots join the ring
         for (uint32_t tile = uint32_t(group) + kGroups; tile < stream_tiles; tile += kGroups) {
             const int32_t at = next;
-            next = index_of(tile + kGroups);
+            next = active ? index_at(tile + kGroups, key) : -1;
             if (tile >= uint32_t(kStages) && !wait(&empty[tile % kStages], ((tile / kStages) - 1) & 1)) break;
             fill(tile, at);
         }
+        // (the merge at the end is the compute warps' work; every thread of the cluster meets at its two barriers)
+        cluster_arrive(); cluster_wait();
+        cluster_arrive(); cluster_wait();
         return;
     }
 
@@ -376,11 +400,11 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
 
     // ---- BF16 selected rows: tile t is consumed by group t % 2 from slot t % kStages ----
     {
-        int32_t live_at = index_of(uint32_t(group));   // (read a tile ahead; the copy warp has had the same line a tile earlier still)
+        int32_t live_at = index_at(uint32_t(group), lane);   // (read a tile ahead; the copy warp has had the same line a tile earlier still)
         for (uint32_t tile = uint32_t(group); tile < stream_tiles; tile += kGroups) {
             const int slot = int(tile % kStages);
             const uint32_t live = __ballot_sync(0xffffffffu, live_at >= 0);
-            live_at = index_of(tile + kGroups);
+            live_at = index_at(tile + kGroups, lane);
             const bool arrived = wait(&full[slot], (tile / kStages) & 1);
             const uint32_t plane = smem_u32(planes) + uint32_t(slot) * S::kPlane;
             if (!compute(plane, plane, live, !arrived, std::false_type{})) break;
@@ -389,55 +413,124 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         }
     }
 
-    // ---- the group's partial: [DIM sums | max (exp2 domain) | denominator] per head ----
-    #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const size_t head = head0 + g + 8 * i;
-        if (head >= a.heads) continue;
-        float* mine = partial + ((row * a.heads + head) * (splits * kGroups) + split * kGroups + group) * (DIM + 2);
+    // ---- the merge of the splits (gpu/ops.hpp:1561-1583, 1648-1677) runs inside the cluster: every group leaves its partial in
+    //      its CTA's shared memory (the ring is idle by now), and after a cluster barrier CTA r merges columns r * dim / splits ..
+    //      of all 16 heads, reading the other CTAs' partials through distributed shared memory: no partial goes to HBM. ----
+    constexpr int kPartRow = DIM + 8;                          // floats (a part is exactly one slot of the ring)
+    static_assert(16 * kPartRow * 4 <= S::kPlane, "a group's partial fits a slot");
+    float* parts_area = reinterpret_cast<float*>(planes);      // [group][16 heads][kPartRow]
+    float* part_stats = reinterpret_cast<float*>(weights);     // [group][16 heads][max, denominator], in the group's own weight rows
+    group_barrier(1 + group);                                  // the group's last tile has been read by all of its warps
+    {
+        float* mine = parts_area + size_t(group) * 16 * kPartRow + gw * S::kCols + 2 * t;
         #pragma unroll
-        for (int n = 0; n < S::kNT; ++n)
-            *reinterpret_cast<float2*>(mine + gw * S::kCols + 8 * n + 2 * t) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+        for (int n = 0; n < S::kNT; ++n) {
+            *reinterpret_cast<float2*>(mine + g * kPartRow + 8 * n) = make_float2(o[n][0], o[n][1]);
+            *reinterpret_cast<float2*>(mine + (g + 8) * kPartRow + 8 * n) = make_float2(o[n][2], o[n][3]);
+        }
+        if (lane % 16 == 0) { part_stats[group * (16 * S::kPRow / 4) + soft_head * 2] = m; part_stats[group * (16 * S::kPRow / 4) + soft_head * 2 + 1] = l; }
     }
-    if (lane % 16 == 0 && head0 + soft_head < a.heads) {
-        float* mine = partial + ((row * a.heads + head0 + soft_head) * (splits * kGroups) + split * kGroups + group) * (DIM + 2);
-        mine[DIM] = m; mine[DIM + 1] = l;
+    cluster_arrive(); cluster_wait();
+    const int parts = int(splits) * kGroups;                   // (at most 16: a lane each)
+    float* merge_factors = slabs;                              // [16 heads][32]
+    float* denominators = slabs + 16 * 32;
+    {   // warp = head, lane = part
+        const size_t head = head0 + warp;
+        float top_part = -INFINITY, sum_part = 0.0f, sink = -INFINITY;
+        if (head < a.heads) sink = sinks[head] * 1.4426950408889634f;
+        if (lane < parts) {
+            const float2 stats = cluster_load2(cluster_address(smem_u32(part_stats + (lane % kGroups) * (16 * S::kPRow / 4) + warp * 2), uint32_t(lane / kGroups)));
+            top_part = stats.x; sum_part = stats.y;
+        }
+        float top = fmaxf(top_part, sink);
+        #pragma unroll
+        for (int offset = 16; offset; offset /= 2) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+        const float factor = top_part == -INFINITY ? 0.0f : exp2f(top_part - top);
+        float denominator = factor * sum_part;
+        #pragma unroll
+        for (int offset = 16; offset; offset /= 2) denominator += __shfl_xor_sync(0xffffffffu, denominator, offset);
+        merge_factors[warp * 32 + lane] = factor;
+        // (a sink of -inf adds 0; top is finite whenever any key or the sink is)
+        if (lane == 0) denominators[warp] = denominator + exp2f(sink - top);
     }
+    asm volatile("bar.sync 3, %0;" ::"n"(kComputeThreads) : "memory");
+    {
+        const size_t plain = DIM - 2 * pairs;
+        const int cols = DIM / int(splits), col0 = int(split) * cols, half = cols / 2;   // this CTA's columns (splits divides dim / 2)
+        for (int i = threadIdx.x; i < 16 * half; i += kComputeThreads) {
+            const int head_local = i / half, d = col0 + 2 * (i % half);
+            const size_t head = head0 + head_local;
+            if (head >= a.heads) continue;
+            const uint32_t from = smem_u32(parts_area + head_local * kPartRow + d);
+            float2 sum = make_float2(0.0f, 0.0f);
+            #pragma unroll 1
+            for (int part0 = 0; part0 < parts; part0 += 8) {
+                float2 x[8];
+                #pragma unroll
+                for (int k = 0; k < 8; ++k) {   // (a round's loads are asked for before the first is used)
+                    const int part = part0 + k;
+                    x[k] = part < parts ? cluster_load2(cluster_address(from + uint32_t((part % kGroups) * 16 * kPartRow * 4), uint32_t(part / kGroups)))
+                                        : make_float2(0.0f, 0.0f);
+                }
+                #pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (part0 + k < parts) {
+                        const float factor = merge_factors[head_local * 32 + part0 + k];
+                        sum.x = fmaf(x[k].x, factor, sum.x); sum.y = fmaf(x[k].y, factor, sum.y);
+                    }
+                }
+            }
+            const float denominator = denominators[head_local];
+            sum.x /= denominator; sum.y /= denominator;
+            if (size_t(d) >= plain) {
+                const double2 turn = inverse[row * pairs + (d - plain) / 2];
+                const double x0 = sum.x, y0 = sum.y;
+                sum = make_float2(float(x0 * turn.x - y0 * turn.y), float(x0 * turn.y + y0 * turn.x));
+            }
+            float* to = out + (row * a.heads + head) * DIM + d;   // (only known to be 4-byte aligned)
+            to[0] = sum.x; to[1] = sum.y;
+        }
+    }
+    cluster_arrive(); cluster_wait();   // (nobody leaves while its partial may still be read)
 }
 
 }  // namespace v3
 
 template<int DIM>
 static void launch_v3(Device& d, const SparseArgs& a, const float* q, size_t pairs, const double2* forward, size_t rows, size_t splits,
-                      float* partial, int* status) {
+                      int* status, const float* sinks, const double2* inverse, float* out) {
     using S = v3::Shape<DIM>;
     static bool configured[64] = {};
     if (!configured[d.ordinal & 63]) {
         SDB_CHECK(cudaFuncSetAttribute(v3::sparse_mma3_kernel<DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(S::kSmem)));
         configured[d.ordinal & 63] = true;
     }
-    const dim3 grid{unsigned(splits), unsigned((a.heads + 15) / 16), unsigned(rows)};
-    v3::sparse_mma3_kernel<DIM><<<grid, v3::kThreads, S::kSmem, d.stream>>>(a, q, pairs, forward, a.scale * 1.4426950408889634f, partial, status);
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3{unsigned(splits), unsigned((a.heads + 15) / 16), unsigned(rows)};
+    config.blockDim = dim3{unsigned(v3::kThreads), 1, 1};
+    config.dynamicSmemBytes = S::kSmem;
+    config.stream = d.stream;
+    cudaLaunchAttribute cluster{};
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = unsigned(splits); cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster; config.numAttrs = 1;
+    SDB_CHECK(cudaLaunchKernelEx(&config, v3::sparse_mma3_kernel<DIM>, a, q, pairs, forward, a.scale * 1.4426950408889634f, status, sinks, inverse, out));
     ++d.launches;
 }
 
 void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
                         const double2* forward, const double2* inverse, float* out) {
     const size_t head_tiles = (a.heads + 15) / 16;
-    // one wave of CTAs (one per SM): as many splits as keep rows * head tiles * splits within the SM count,
-    // each group of a split at least two tiles
-    size_t splits = size_t(d.sms) / std::max<size_t>(1, rows * head_tiles);
-    splits = std::max<size_t>(1, std::min<size_t>({splits, size_t(16), std::max<size_t>(1, a.selections / (2 * v3::kT * v3::kGroups))}));
-    const size_t partials = splits * v3::kGroups;
-    const size_t total = 256 + checked_product({rows, a.heads, partials, a.dim + 2, 4});
-    auto* work = static_cast<uint8_t*>(ensure(d, d.partial, d.partial_bytes, total));
-    auto* partial = reinterpret_cast<float*>(work + 256);
+    // One wave of CTAs (one per SM). The splits of a (row, head tile) are a thread-block cluster: 1, 2, 4 or 8 of them, as many
+    // as keep rows * head tiles * splits within the SM count, each group of a split at least two tiles.
+    const size_t room = size_t(d.sms) / std::max<size_t>(1, rows * head_tiles);
+    const size_t useful = std::max<size_t>(1, a.selections / (2 * v3::kT * v3::kGroups));
+    size_t splits = 1;
+    while (splits * 2 <= std::min<size_t>({room, useful, size_t(8)})) splits *= 2;
     int* status = status_word(d);
-    if (a.dim == 576) launch_v3<576>(d, a, q, pairs, forward, rows, splits, partial, status);
-    else launch_v3<512>(d, a, q, pairs, forward, rows, splits, partial, status);
+    if (a.dim == 576) launch_v3<576>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out);
+    else launch_v3<512>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out);
     SDB_CHECK(cudaGetLastError());
-    sparse_combine_kernel<<<unsigned(rows * a.heads), 128, 0, d.stream>>>(partial, partials, a.heads, a.dim, sinks, pairs, inverse, 1, out);
-    ++d.launches;
 }
 
 }  // namespace sdb
