@@ -127,6 +127,21 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     const int copy_half = (warp - kGroups * kGroupWarps) / kGroups;   // of a copy warp: which 16 rows of a tile
     const int kh = gw % 2, kq = gw / 2;                        // scores: key half of the tile, contraction quarter
     const size_t split = blockIdx.x, splits = gridDim.x, row = blockIdx.z, head0 = size_t(blockIdx.y) * 16;
+    // (the compute threads ask for their share of the queries before anything else: the load's latency covers the set-up)
+    constexpr int kEach = 16 * (DIM / 2) / kComputeThreads;   // column pairs a thread prepares
+    static_assert(16 * (DIM / 2) % kComputeThreads == 0, "the query rows divide evenly over the threads");
+    float2 loaded[kEach];
+    if (!copier) {
+        #pragma unroll
+        for (int it = 0; it < kEach; ++it) {
+            const int i = threadIdx.x + it * kComputeThreads, head = i / (DIM / 2), col = 2 * (i % (DIM / 2));
+            loaded[it] = make_float2(0.0f, 0.0f);
+            if (head0 + head < a.heads) {
+                const float* src = q + (row * a.heads + head0 + head) * DIM + col;   // (only known to be 4-byte aligned)
+                loaded[it] = make_float2(src[0], src[1]);
+            }
+        }
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], 32); mbar_init(&empty[s], kGroupWarps); }
         *abort_flag = 0;
@@ -149,8 +164,15 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
 
     const KeyList list = key_list(a, row);
     const bool rows_bf16 = state_is_bf16(a.compressed);
-    const size_t per_split = ((a.selections + splits - 1) / splits + kT - 1) / kT * kT;
-    const size_t sel_begin = min(a.selections, split * per_split), sel_end = min(a.selections, sel_begin + per_split);
+    // The selected rows are dealt in whole tiles. Split 0 also has the window rows, an F32 tile of which costs about two
+    // streamed tiles (converted on the spot, both parts multiplied): it takes that many fewer streamed tiles.
+    const size_t all_tiles = (a.selections + kT - 1) / kT;
+    const size_t window_cost = 2 * ((list.raw_count + kT - 1) / kT);   // (the same for both row formats, so that they are dealt alike)
+    const size_t per_split = (all_tiles + window_cost + splits - 1) / splits;
+    const size_t first_share = per_split > window_cost ? per_split - window_cost : (splits == 1 ? all_tiles : 0);
+    const size_t tile_begin = split == 0 ? 0 : min(all_tiles, first_share + (split - 1) * per_split);
+    const size_t tile_end = split + 1 == splits ? all_tiles : min(all_tiles, first_share + split * per_split);
+    const size_t sel_begin = min(a.selections, tile_begin * kT), sel_end = min(a.selections, tile_end * kT);
     const uint32_t stream_tiles = rows_bf16 ? uint32_t((sel_end - sel_begin + kT - 1) / kT) : 0u;
     // F32 keys: the window rows (split 0) and untagged compressed rows, taken tile by tile before the stream
     const size_t f32_begin = split == 0 ? 0 : list.raw_count + sel_begin;
@@ -191,7 +213,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         // indices are read two tiles before they are used: the list comes from HBM like the rows
         int32_t next = active ? index_at(uint32_t(group) + kGroups, key) : -1;
         if (uint32_t(group) < stream_tiles) fill(uint32_t(group), active ? index_at(uint32_t(group), key) : -1);
-        __syncthreads_or(0);                                              // the queries are prepared
         for (uint32_t i = 0; i < f32_tiles; ++i) { __syncthreads(); __syncthreads(); __syncthreads(); }
         __syncthreads();                                                  // the last two slots join the ring
         for (uint32_t tile = uint32_t(group) + kGroups; tile < stream_tiles; tile += kGroups) {
@@ -211,18 +232,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     bool any_lo = false;
     {
         const size_t plain = DIM - 2 * pairs;
-        constexpr int kEach = 16 * (DIM / 2) / kComputeThreads;   // column pairs a thread prepares
-        static_assert(16 * (DIM / 2) % kComputeThreads == 0, "the query rows divide evenly over the threads");
-        float2 loaded[kEach];
-        #pragma unroll
-        for (int it = 0; it < kEach; ++it) {   // (every load is asked for before the first is used)
-            const int i = threadIdx.x + it * kComputeThreads, head = i / (DIM / 2), col = 2 * (i % (DIM / 2));
-            loaded[it] = make_float2(0.0f, 0.0f);
-            if (head0 + head < a.heads) {
-                const float* src = q + (row * a.heads + head0 + head) * DIM + col;   // (only known to be 4-byte aligned)
-                loaded[it] = make_float2(src[0], src[1]);
-            }
-        }
         #pragma unroll
         for (int it = 0; it < kEach; ++it) {
             const int i = threadIdx.x + it * kComputeThreads, head = i / (DIM / 2), col = 2 * (i % (DIM / 2));
@@ -240,7 +249,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         }
     }
     // (low parts matter from the first rotated column on, or everywhere when some plain column is not a BF16 value)
-    const int lo_from = __syncthreads_or(any_lo) ? 0 : int((DIM - 2 * pairs) / 16);
+    uint32_t some_lo;
+    asm volatile("{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.or.pred p, 4, %2, q; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(some_lo) : "r"(uint32_t(any_lo)), "n"(kComputeThreads) : "memory");   // (the compute threads alone: the copy warps are busy)
+    const int lo_from = some_lo ? 0 : int((DIM - 2 * pairs) / 16);
 
     float o[S::kNT][4];
     #pragma unroll
@@ -434,6 +446,19 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     const int parts = int(splits) * kGroups;                   // (at most 16: a lane each)
     float* merge_factors = slabs;                              // [16 heads][32]
     float* denominators = slabs + 16 * 32;
+    // this CTA's columns (splits divides dim / 2); all the parts of a column pair are asked for at once
+    const int cols = DIM / int(splits), col0 = int(split) * cols, half = cols / 2;
+    auto merge_pair = [&](int i, auto&& body) {
+        const int head_local = i / half, d = col0 + 2 * (i % half);
+        if (i >= 16 * half || head0 + head_local >= a.heads) return;
+        const uint32_t from = smem_u32(parts_area + head_local * kPartRow + d);
+        float2 x[16];
+        #pragma unroll
+        for (int part = 0; part < 16; ++part)
+            x[part] = part < parts ? cluster_load2(cluster_address(from + uint32_t((part % kGroups) * 16 * kPartRow * 4), uint32_t(part / kGroups)))
+                                   : make_float2(0.0f, 0.0f);
+        body(head_local, d, x);
+    };
     {   // warp = head, lane = part
         const size_t head = head0 + warp;
         float top_part = -INFINITY, sum_part = 0.0f, sink = -INFINITY;
@@ -456,39 +481,26 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     asm volatile("bar.sync 3, %0;" ::"n"(kComputeThreads) : "memory");
     {
         const size_t plain = DIM - 2 * pairs;
-        const int cols = DIM / int(splits), col0 = int(split) * cols, half = cols / 2;   // this CTA's columns (splits divides dim / 2)
         for (int i = threadIdx.x; i < 16 * half; i += kComputeThreads) {
-            const int head_local = i / half, d = col0 + 2 * (i % half);
-            const size_t head = head0 + head_local;
-            if (head >= a.heads) continue;
-            const uint32_t from = smem_u32(parts_area + head_local * kPartRow + d);
-            float2 sum = make_float2(0.0f, 0.0f);
-            #pragma unroll 1
-            for (int part0 = 0; part0 < parts; part0 += 8) {
-                float2 x[8];
+            merge_pair(i, [&](int head_local, int d, const float2 (&x)[16]) {
+                float2 sum = make_float2(0.0f, 0.0f);
                 #pragma unroll
-                for (int k = 0; k < 8; ++k) {   // (a round's loads are asked for before the first is used)
-                    const int part = part0 + k;
-                    x[k] = part < parts ? cluster_load2(cluster_address(from + uint32_t((part % kGroups) * 16 * kPartRow * 4), uint32_t(part / kGroups)))
-                                        : make_float2(0.0f, 0.0f);
-                }
-                #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    if (part0 + k < parts) {
-                        const float factor = merge_factors[head_local * 32 + part0 + k];
-                        sum.x = fmaf(x[k].x, factor, sum.x); sum.y = fmaf(x[k].y, factor, sum.y);
+                for (int part = 0; part < 16; ++part) {
+                    if (part < parts) {
+                        const float factor = merge_factors[head_local * 32 + part];
+                        sum.x = fmaf(x[part].x, factor, sum.x); sum.y = fmaf(x[part].y, factor, sum.y);
                     }
                 }
-            }
-            const float denominator = denominators[head_local];
-            sum.x /= denominator; sum.y /= denominator;
-            if (size_t(d) >= plain) {
-                const double2 turn = inverse[row * pairs + (d - plain) / 2];
-                const double x0 = sum.x, y0 = sum.y;
-                sum = make_float2(float(x0 * turn.x - y0 * turn.y), float(x0 * turn.y + y0 * turn.x));
-            }
-            float* to = out + (row * a.heads + head) * DIM + d;   // (only known to be 4-byte aligned)
-            to[0] = sum.x; to[1] = sum.y;
+                const float denominator = denominators[head_local];
+                sum.x /= denominator; sum.y /= denominator;
+                if (size_t(d) >= plain) {
+                    const double2 turn = inverse[row * pairs + (d - plain) / 2];
+                    const double x0 = sum.x, y0 = sum.y;
+                    sum = make_float2(float(x0 * turn.x - y0 * turn.y), float(x0 * turn.y + y0 * turn.x));
+                }
+                float* to = out + (row * a.heads + head0 + head_local) * DIM + d;   // (only known to be 4-byte aligned)
+                to[0] = sum.x; to[1] = sum.y;
+            });
         }
     }
     cluster_arrive(); cluster_wait();   // (nobody leaves while its partial may still be read)
