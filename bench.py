@@ -293,8 +293,19 @@ def run_other_config(args):
         scratch = gpu.buffer(512 << 20)
         scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
 
+        one_call = cfg == 4 and not ref and not args.per_call
+        if one_call:
+            # the 16 spans in one launch (sdx_sparse_attention_spans): their buffers laid end to end
+            q_all, raw_all, sel_all = gpu.upload(q_np), gpu.upload(raw_np), gpu.upload(selected)
+            pos_all = gpu.upload(np.tile(positions, calls))
+            out_all = gpu.buffer(calls * rows * heads * dim * 4)
+
         def step():
             turn[0] = (turn[0] + 1) % variants
+            if one_call:
+                gpu.sparse_attention_spans(q_all.pointer, raw_all.pointer, raw_np.shape[1], pos_all.pointer, window, (comp.tagged_bf16(), total_rows),
+                                           (sel_all.pointer, selections), kb.pointer, calls, rows, heads, dim, scale, None, out_all.pointer)
+                return
             for c in range(calls):
                 gpu.sparse_attention(qb[c].pointer, rb[c].pointer, raw_np.shape[1], pb.pointer, window, (comp.tagged_bf16(), total_rows),
                                      (sb[turn[0] * calls + c].pointer, selections), kb.pointer, rows, heads, dim, scale, None, scratch, outs[c].pointer)
@@ -314,7 +325,8 @@ def run_other_config(args):
         nbytes = calls * rows * selections * dim * 2
         flops = 4.0 * dim * heads * calls * rows * keys_per_row
         line.update({"workload": ("config 3: latent sparse decode, 32 queries x top-2048 of 65536, 576-wide BF16 rows" if cfg == 3 else
-                                  "config 4: verify spans, 16 sequences x 8 draft rows (one call per sequence), top-2048 of 32768, causal window in the span"),
+                                  "config 4: verify spans, 16 sequences x 8 draft rows, top-2048 of 32768, causal window in the span; " +
+                                  ("one launch for the 16 spans" if one_call else "one call per sequence")),
                      "heads": heads, "l2": "steps rotate over 4 index lists (302 MB of rows against the 126 MB L2)" if cfg == 3 else "302 MB of rows a step",
                      "ms": ms, "gather_gbps": nbytes / ms / 1e6, "tflops": flops / ms / 1e9,
                      "roofline_hbm_frac": nbytes / ms / 1e6 / peak_hbm, "roofline_tensor_frac": flops / ms / 1e9 / peak_tensor,
@@ -332,6 +344,7 @@ def main():
     parser.add_argument("--config", type=int, default=1, choices=[0, 1, 2, 3, 4], help="1 is the benchmark line; the others are measured for the design notes")
     parser.add_argument("--context", type=int, default=0, help="configs 3/4: override the per-query context (a smaller resident set for a profiler capture)")
     parser.add_argument("--head-shards", type=int, default=1, help="configs 3/4: heads per GPU = 128 / head_shards (the per-GPU work of head sharding)")
+    parser.add_argument("--per-call", action="store_true", help="config 4: one sd_op_sparse_attention call per sequence instead of one sdx_sparse_attention_spans launch")
     parser.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     parser.add_argument("--cpu-seconds", type=float, default=12.0)
     parser.add_argument("--sequences", type=int, default=64, help="sequences per batch (64 is the benchmark; fewer for a profiler capture)")

@@ -135,6 +135,16 @@ int sdx_decode_status(void* handle);
 int sdx_qsa_prompt(void* handle, const void* state, uint64_t context, uint64_t first, uint64_t rows, uint64_t heads,
                    uint64_t kv_heads, float scale, const void* q, float* out);
 
+/* Latent sparse attention of several spans in one call (no reference counterpart: the reference verifies one sequence per call,
+   gpu/straydog_gpu.h:398, crates/straydog-engine/src/arch/deepseek41/engine.rs:3838). Equal to `spans` calls of
+   sd_op_sparse_attention with rows = span_rows: span s takes q, positions, selected and out at row offset s * span_rows and its
+   own window ring raw + s * raw_rows * dim (positions count in that ring); `compressed`, `sinks`, `frequencies` are shared, so the
+   caller keeps the sequences' caches in one allocation and points `selected` into it. No scratch: the library owns its workspaces. */
+int sdx_sparse_attention_spans(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                               uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                               uint64_t selections, const float* sinks, uint64_t spans, uint64_t span_rows, uint64_t heads, uint64_t dim,
+                               float scale, uint64_t rope_dims, const float* frequencies, float* out);
+
 /* One decode step of a batch from HOST buffers (the batched twin of sd_attention_sequence): for
    sequence s the new token's keys/values (k, v: [sequences][kv_heads][256] F32, host) are written
    to row bases[s] of states[s], then its query (q: [sequences][heads][256] FP16, host) attends rows

@@ -261,6 +261,15 @@ class Backend:
                                             rows, heads, dim, scale, rope_dims, freq, scratch.pointer if scratch else None,
                                             scratch.size if scratch else 0, out))
 
+    def sparse_attention_spans(self, q, raw, raw_rows, positions, window, compressed, selected, sinks, spans, span_rows, heads, dim, scale,
+                               rope, out):
+        """`spans` calls of sparse_attention with rows = span_rows in one launch (an addition; every span its own window ring)."""
+        c_ptr, c_rows = compressed if compressed else (None, 0)
+        s_ptr, selections = selected if selected else (None, 0)
+        rope_dims, freq = rope if rope else (0, None)
+        self._c(self.lib.sdx_sparse_attention_spans(self.handle, q, raw, raw_rows, positions, window, c_ptr, c_rows, s_ptr, selections, sinks,
+                                                spans, span_rows, heads, dim, scale, rope_dims, freq, out))
+
     def top_k(self, scores, rows, groups, k, out):
         self._c(self.lib.sd_op_top_k(self.handle, scores, rows, groups, k, out))
 

@@ -268,17 +268,20 @@ int sd_attention_turns_arm(void* handle, uint64_t rows) {
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
 }
 
-int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
-                           uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
-                           uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
-                           uint64_t rope_dims, const float* frequencies, float* scratch, uint64_t scratch_bytes, float* out) {
+// The body of both entries. spans > 1: `rows` = spans * span_rows query rows, span s with its own window ring
+// raw + s * raw_rows * dim and positions counted in that ring; everything else as in a single call.
+static int sparse_attention_call(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                                 uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                                 uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
+                                 uint64_t rope_dims, const float* frequencies, float* scratch, uint64_t scratch_bytes, float* out,
+                                 uint64_t spans, uint64_t span_rows) {
     SDB_OP_BEGIN
     if (!rows || rows > 65535 || !heads || !dim || !window || rope_dims % 2 || rope_dims > dim || rope_dims > 128)
         throw std::runtime_error("invalid Straydog attention shape");
     if (dim > 1024 || heads > 65535 * kSimtHeads || !raw_rows) throw std::runtime_error("invalid Straydog attention shape");
     if (rope_dims) span(value, frequencies, size_t(rope_dims / 2) * 4, "rope frequencies");
     span(value, q, checked_product({rows, heads, dim, 4}), "attention queries");
-    span(value, raw, checked_product({raw_rows, dim, 4}), "window rows");
+    span(value, raw, checked_product({spans, raw_rows, dim, 4}), "window rows");
     span(value, positions, checked_product({rows, 4}), "query positions");
     if (selections) {
         if (state_is_bf16(compressed)) span(value, state_halves(compressed), checked_product({compressed_rows, dim, 2}), "compressed rows");
@@ -305,13 +308,14 @@ int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint6
     args.raw = raw; args.raw_rows = raw_rows; args.positions = positions; args.window = window; args.compressed = compressed;
     args.compressed_rows = compressed_rows; args.selected = selected; args.selections = selections; args.heads = heads; args.dim = dim;
     args.scale = scale;
+    args.span_rows = spans > 1 ? span_rows : rows;   // (one span: every row in ring 0)
 
     const bool force_simt = env_flag("SDX_SPARSE_SIMT");
     if (!force_simt && sparse_mma_supported(args)) {
-        // (SDX_SPARSE_KERNEL=v1|v2|v3 forces one form of the tensor-core kernel for A/B runs; by default up to 16 heads
-        //  take the third form, sixteen warps over one head tile, and more heads the second, 32 heads a CTA)
+        // (SDX_SPARSE_KERNEL=v1|v2|v3 picks a form of the tensor-core kernel for A/B runs; the third, sixteen compute warps over one
+        //  head tile of 16 with the merge inside a thread-block cluster, is the default: it is the fastest at every head count measured)
         const char* form = std::getenv("SDX_SPARSE_KERNEL");
-        const char which = form && form[0] == 'v' && form[1] && !form[2] ? form[1] : (heads <= 16 ? '3' : '2');
+        const char which = form && form[0] == 'v' && form[1] && !form[2] ? form[1] : '3';
         if (which == '1') sparse_mma_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         else if (which == '3') sparse_mma3_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         else sparse_mma2_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
@@ -349,6 +353,25 @@ int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint6
     sparse_combine_kernel<<<unsigned(rows * heads), 128, 0, value.stream>>>(partial, splits, heads, dim, sinks, pairs, inverse, 0, out);
     ++value.launches;
     SDB_OP_END
+}
+
+int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                           uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                           uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
+                           uint64_t rope_dims, const float* frequencies, float* scratch, uint64_t scratch_bytes, float* out) {
+    return sparse_attention_call(handle, q, raw, raw_rows, positions, window, compressed, compressed_rows, selected, selections, sinks, rows,
+                                 heads, dim, scale, rope_dims, frequencies, scratch, scratch_bytes, out, 1, rows);
+}
+
+int sdx_sparse_attention_spans(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                               uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                               uint64_t selections, const float* sinks, uint64_t spans, uint64_t span_rows, uint64_t heads, uint64_t dim,
+                               float scale, uint64_t rope_dims, const float* frequencies, float* out) {
+    try {
+        if (!spans || !span_rows || spans > 65535 || span_rows > 65535) throw std::runtime_error("invalid Straydog attention shape");
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+    return sparse_attention_call(handle, q, raw, raw_rows, positions, window, compressed, compressed_rows, selected, selections, sinks,
+                                 spans * span_rows, heads, dim, scale, rope_dims, frequencies, nullptr, 0, out, spans, span_rows);
 }
 
 }  // extern "C"

@@ -13,6 +13,7 @@ struct SparseArgs {
     const int32_t* selected; size_t selections;
     size_t heads, dim;
     float scale;
+    size_t span_rows;   // rows of one span: a call may hold several spans, each with its own window ring (never 0; one span: all the rows)
 };
 
 __host__ __device__ inline bool state_is_bf16(const void* p) { return reinterpret_cast<uintptr_t>(p) & 1u; }
@@ -31,7 +32,10 @@ __device__ __forceinline__ KeyList key_list(const SparseArgs& a, size_t row) {
 }
 // Key `index` of a row: an F32 window row, a compressed row (tagged as `compressed` is), or null for an empty selection.
 __device__ __forceinline__ const float* key_pointer(const SparseArgs& a, const KeyList& list, size_t row, size_t index) {
-    if (index < list.raw_count) return a.raw + size_t(list.first + int64_t(index)) % a.raw_rows * a.dim;
+    if (index < list.raw_count) {
+        const float* ring = a.raw + row / a.span_rows * a.raw_rows * a.dim;   // (a span's own ring)
+        return ring + size_t(list.first + int64_t(index)) % a.raw_rows * a.dim;
+    }
     if (index >= list.total) return nullptr;
     const int32_t at = a.selected[row * a.selections + (index - list.raw_count)];
     if (at < 0) return nullptr;

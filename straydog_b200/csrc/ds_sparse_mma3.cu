@@ -41,6 +41,7 @@ namespace v3 {
 constexpr int kT = 32;            // keys a tile
 constexpr int kStages = 4;        // tiles in the ring
 constexpr int kGroups = 2, kGroupWarps = 8, kGroupThreads = 32 * kGroupWarps;
+constexpr int kScalarWindow = 4;   // window rows up to which the window is taken by FP32 arithmetic, a row at a time
 constexpr int kCopyWarps = 2;     // copy warps a group, 16 rows of a tile each
 constexpr int kComputeThreads = kGroups * kGroupThreads, kThreads = kComputeThreads + 32 * kGroups * kCopyWarps;
 
@@ -164,21 +165,23 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
 
     const KeyList list = key_list(a, row);
     const bool rows_bf16 = state_is_bf16(a.compressed);
-    // The selected rows are dealt in whole tiles. Split 0 also has the window rows, an F32 tile of which costs about two
-    // streamed tiles (converted on the spot, both parts multiplied): it takes that many fewer streamed tiles.
-    const size_t all_tiles = (a.selections + kT - 1) / kT;
-    const size_t window_cost = 2 * ((list.raw_count + kT - 1) / kT);   // (the same for both row formats, so that they are dealt alike)
-    const size_t per_split = (all_tiles + window_cost + splits - 1) / splits;
-    const size_t first_share = per_split > window_cost ? per_split - window_cost : (splits == 1 ? all_tiles : 0);
-    const size_t tile_begin = split == 0 ? 0 : min(all_tiles, first_share + (split - 1) * per_split);
-    const size_t tile_end = split + 1 == splits ? all_tiles : min(all_tiles, first_share + split * per_split);
-    const size_t sel_begin = min(a.selections, tile_begin * kT), sel_end = min(a.selections, tile_end * kT);
-    const uint32_t stream_tiles = rows_bf16 ? uint32_t((sel_end - sel_begin + kT - 1) / kT) : 0u;
-    // F32 keys: the window rows (split 0) and untagged compressed rows, taken tile by tile before the stream
-    const size_t f32_begin = split == 0 ? 0 : list.raw_count + sel_begin;
-    const size_t f32_end = rows_bf16 ? (split == 0 ? list.raw_count : f32_begin) : list.raw_count + sel_end;
-    // (a CTA with F32 tiles keeps the last two slots for their high and low planes until those tiles are done)
-    uint8_t* f32_hi = planes + size_t(kStages - 2) * S::kPlane;
+    // The selected rows are dealt in whole tiles. Split 0 also has the window rows, an F32 tile of which costs one of its groups
+    // about three streamed tiles (read, converted on the spot, both parts multiplied): it takes that many fewer streamed tiles.
+    const uint32_t all_tiles = uint32_t((a.selections + kT - 1) / kT), window_tiles = uint32_t((list.raw_count + kT - 1) / kT);
+    // (a window of up to kScalarWindow rows goes through FP32 arithmetic instead: next to free)
+    const bool scalar_window = list.raw_count > 0 && list.raw_count <= size_t(kScalarWindow);
+    const uint32_t window_cost = scalar_window ? 0u : 3 * window_tiles;   // (the same for both row formats, so that they are dealt alike)
+    const uint32_t per_split = (all_tiles + window_cost + uint32_t(splits) - 1) / uint32_t(splits);
+    const uint32_t first_share = per_split > window_cost ? per_split - window_cost : (splits == 1 ? all_tiles : 0u);
+    const uint32_t tile_begin = split == 0 ? 0u : min(all_tiles, first_share + (uint32_t(split) - 1) * per_split);
+    const uint32_t tile_end = split + 1 == splits ? all_tiles : min(all_tiles, first_share + uint32_t(split) * per_split);
+    const size_t sel_begin = min(a.selections, size_t(tile_begin) * kT), sel_end = min(a.selections, size_t(tile_end) * kT);
+    const uint32_t stream_tiles = rows_bf16 ? tile_end - tile_begin : 0u;
+    // F32 keys. BF16 rows: only split 0's window rows, which its group 0 converts and consumes by itself in its own two slots
+    // while group 1 already streams. Untagged F32 rows: every key, tile by tile, by the whole CTA in the last two slots.
+    const bool window_here = rows_bf16 && split == 0 && window_tiles > 0 && !scalar_window;
+    const size_t f32_begin = rows_bf16 ? 0 : (split == 0 && !scalar_window ? 0 : list.raw_count + sel_begin);
+    const size_t f32_end = rows_bf16 ? 0 : list.raw_count + sel_end;
     const uint32_t f32_tiles = [&] {
         uint32_t n = 0;
         for (size_t first = f32_begin; first < f32_end; ++n) first += min(size_t(kT), (first < list.raw_count ? list.raw_count : f32_end) - first);
@@ -198,6 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         const int key = copy_half * (kT / kCopyWarps) + lane;
         auto fill = [&](uint32_t tile, int32_t at) {
             if (!active) return;
+            if (at >= 0 && size_t(at) >= a.compressed_rows) { atomicExch(status, 2); at = -1; }   // (a row number past the cache: taken as absent, reported)
             const int slot = int(tile % kStages);
             uint8_t* dst = planes + size_t(slot) * S::kPlane + size_t(key) * S::kRow;
             if (at >= 0) {
@@ -211,15 +215,16 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
             }
         };
         // indices are read two tiles before they are used: the list comes from HBM like the rows
-        int32_t next = active ? index_at(uint32_t(group) + kGroups, key) : -1;
-        if (uint32_t(group) < stream_tiles) fill(uint32_t(group), active ? index_at(uint32_t(group), key) : -1);
-        for (uint32_t i = 0; i < f32_tiles; ++i) { __syncthreads(); __syncthreads(); __syncthreads(); }
-        __syncthreads();                                                  // the last two slots join the ring
-        for (uint32_t tile = uint32_t(group) + kGroups; tile < stream_tiles; tile += kGroups) {
-            const int32_t at = next;
-            next = active ? index_at(tile + kGroups, key) : -1;
-            if (tile >= uint32_t(kStages) && !wait(&empty[tile % kStages], ((tile / kStages) - 1) & 1)) break;
+        int32_t at = active ? index_at(uint32_t(group), key) : -1, next = active ? index_at(uint32_t(group) + kGroups, key) : -1;
+        for (uint32_t i = 0; i < f32_tiles; ++i) { __syncthreads(); __syncthreads(); __syncthreads(); }   // (untagged rows: no stream)
+        // (group 0's slots first hold the window tiles' planes where there are any: they are released like a streamed tile)
+        const uint32_t shift = window_here && group == 0 ? 1u : 0u;
+        for (uint32_t tile = uint32_t(group); tile < stream_tiles; tile += kGroups) {
+            const uint32_t use = tile / kStages + shift;
+            if (use >= 1 && !wait(&empty[tile % kStages], (use - 1) & 1)) break;
             fill(tile, at);
+            at = next;
+            next = active ? index_at(tile + 2 * kGroups, key) : -1;
         }
         // (the merge at the end is the compute warps' work; every thread of the cluster meets at its two barriers)
         cluster_arrive(); cluster_wait();
@@ -376,39 +381,111 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         return true;
     };
 
-    // ---- F32 keys: converted into a high and a low plane (the last two slots), a tile at a time, by every compute thread ----
-    for (size_t first = f32_begin; first < f32_end;) {
-        // (a tile never mixes window rows with selected rows, so that the selected rows tile alike in both formats)
-        const size_t limit = first < list.raw_count ? list.raw_count : f32_end;
-        const size_t count = min(size_t(kT), limit - first);
-        __syncthreads();   // the planes' last readers are done
-        if (warp == 0) {
+    // ---- F32 keys: a tile at a time, converted into a high and a low plane ----
+    auto key_in_range = [&](const float* key) -> bool {
+        const size_t rings = (gridDim.z + a.span_rows - 1) / a.span_rows;
+        if (state_is_bf16(key)) {
+            const uint16_t* at = state_halves(key), *base = state_halves(a.compressed);
+            return state_is_bf16(a.compressed) && at >= base && at + DIM <= base + a.compressed_rows * DIM;
+        }
+        if (key >= a.raw && key + DIM <= a.raw + rings * a.raw_rows * DIM) return true;
+        return !state_is_bf16(a.compressed) && key >= a.compressed && key + DIM <= a.compressed + a.compressed_rows * DIM;
+    };
+    auto convert_tile = [&](size_t first, size_t count, int tid, int threads, uint8_t* hi, uint8_t* lo, auto&& barrier) {
+        barrier();   // the planes' last readers are done
+        if (tid < 32) {
             const float* key = size_t(lane) < count ? key_pointer(a, list, row, first + lane) : nullptr;
             key_ptrs[lane] = key;
             const uint32_t mask = __ballot_sync(0xffffffffu, key != nullptr);
             if (lane == 0) *f32_live = mask;
         }
-        __syncthreads();
-        for (int i = threadIdx.x; i < kT * (DIM / 2); i += kComputeThreads) {
+        barrier();
+        for (int i = tid; i < kT * (DIM / 2); i += threads) {
             const int r = i / (DIM / 2), c = 2 * (i % (DIM / 2));
             const float* key = key_ptrs[r];
+            if (key && !key_in_range(key)) { atomicExch(status, 3); key = nullptr; }   // (never expected: a corrupted pointer table is reported, not followed)
             float2 v = make_float2(0.0f, 0.0f);
             if (key) v = state_is_bf16(key) ? make_float2(__uint_as_float(uint32_t(state_halves(key)[c]) << 16), __uint_as_float(uint32_t(state_halves(key)[c + 1]) << 16))
                                             : make_float2(key[c], key[c + 1]);
             const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
-            *reinterpret_cast<__nv_bfloat162*>(f32_hi + r * S::kRow + c * 2) = __halves2bfloat162(h0, h1);
-            *reinterpret_cast<__nv_bfloat162*>(f32_hi + S::kPlane + r * S::kRow + c * 2) =
+            *reinterpret_cast<__nv_bfloat162*>(hi + r * S::kRow + c * 2) = __halves2bfloat162(h0, h1);
+            *reinterpret_cast<__nv_bfloat162*>(lo + r * S::kRow + c * 2) =
                 __halves2bfloat162(__float2bfloat16_rn(v.x - __bfloat162float(h0)), __float2bfloat16_rn(v.y - __bfloat162float(h1)));
         }
         fence_proxy_async();   // (bulk copies will land on these bytes later)
-        __syncthreads();
-        // (window tiles go to group 0; selected rows alternate between the groups exactly as the stream's tiles do, so
-        //  that F32 rows and BF16 rows of equal values are summed in the same order)
-        const int consumer = first < list.raw_count ? 0 : int(((first - list.raw_count - sel_begin) / kT) % kGroups);
-        if (group == consumer) compute(smem_u32(f32_hi), smem_u32(f32_hi) + S::kPlane, *f32_live, false, std::true_type{});
-        first += count;
+        barrier();
+    };
+    if (scalar_window && split == 0 && group == 0) {
+        // A short window (a decode step's own row, a verify span's few rows): FP32 arithmetic, a row at a time, by group 0 before its
+        // stream. A half warp forms the score of its head (the softmax phase's lanes), every warp adds the weighted row to its columns.
+        float* all_staged = slabs;                                // [rows][DIM] in group 0's slab (idle until its first tile)
+        static_assert(kScalarWindow * DIM <= 4 * S::kSlab, "the window's rows fit the group's slab");
+        float* window_weights = reinterpret_cast<float*>(weights);   // [16] in group 0's weight rows (idle too)
+        const int part = lane % 16;
+        for (size_t j = 0; j < list.raw_count; ++j) {             // (every row is asked for before the first is used)
+            const float* key = key_pointer(a, list, row, j);
+            for (int c = threadIdx.x; c < DIM; c += kGroupThreads) all_staged[j * DIM + c] = key[c];
+        }
+        group_barrier(1);
+        for (size_t j = 0; j < list.raw_count; ++j) {
+            const float* staged = all_staged + j * DIM;
+            float sum = 0.0f;
+            {
+                const uint8_t* hi = q_hi + soft_head * S::kRow, *lo = q_lo + soft_head * S::kRow;
+                #pragma unroll 4
+                for (int c = 2 * part; c < DIM; c += 32) {   // (column pairs interleaved over the 16 lanes: conflict-free)
+                    const uint32_t h = *reinterpret_cast<const uint32_t*>(hi + c * 2), w = *reinterpret_cast<const uint32_t*>(lo + c * 2);
+                    const float2 k = *reinterpret_cast<const float2*>(staged + c);
+                    sum = fmaf(bf16_lo(h) + bf16_lo(w), k.x, sum);
+                    sum = fmaf(bf16_hi(h) + bf16_hi(w), k.y, sum);
+                }
+            }
+            #pragma unroll
+            for (int offset = 1; offset < 16; offset *= 2) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+            const float score = sum * scale_log2;
+            const float next = fmaxf(m, score);
+            const float factor = m == next ? 1.0f : (m == -INFINITY ? 0.0f : fast_exp2(m - next));
+            const float weight = fast_exp2(score - next);
+            l = l * factor + weight;
+            m = next;
+            if (part == 0) { group_factors[soft_head] = factor; window_weights[soft_head] = weight; }
+            group_barrier(1);
+            {
+                const float f0 = group_factors[g], f1 = group_factors[g + 8], w0 = window_weights[g], w1 = window_weights[g + 8];
+                #pragma unroll
+                for (int n = 0; n < S::kNT; ++n) {
+                    const float2 k = *reinterpret_cast<const float2*>(staged + gw * S::kCols + 8 * n + 2 * t);
+                    o[n][0] = fmaf(w0, k.x, o[n][0] * f0); o[n][1] = fmaf(w0, k.y, o[n][1] * f0);
+                    o[n][2] = fmaf(w1, k.x, o[n][2] * f1); o[n][3] = fmaf(w1, k.y, o[n][3] * f1);
+                }
+            }
+            group_barrier(1);   // the weights have been read
+        }
     }
-    __syncthreads();   // the F32 tiles are consumed: the last two slots join the ring
+    if (window_here && group == 0) {
+        // split 0 of BF16 rows: group 0 alone, in its own slots 0 and 2; its copy warp waits for the slots' first release
+        uint8_t* hi = planes, *lo = planes + 2 * size_t(S::kPlane);
+        for (size_t first = 0; first < list.raw_count; first += kT) {
+            convert_tile(first, min(size_t(kT), list.raw_count - first), threadIdx.x, kGroupThreads, hi, lo, [&] { group_barrier(1); });
+            compute(smem_u32(hi), smem_u32(lo), *f32_live, false, std::true_type{});
+        }
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&empty[0]); mbar_arrive(&empty[2]); }
+    }
+    {
+        // untagged F32 rows: the whole CTA, the last two slots (there is no stream). A tile never mixes window rows with selected
+        // rows, and selected tiles alternate between the groups exactly as the stream's tiles do, so that F32 rows and BF16
+        // rows of equal values are summed in the same order.
+        uint8_t* hi = planes + size_t(kStages - 2) * S::kPlane, *lo = hi + S::kPlane;
+        for (size_t first = f32_begin; first < f32_end;) {
+            const size_t limit = first < list.raw_count ? list.raw_count : f32_end;
+            const size_t count = min(size_t(kT), limit - first);
+            convert_tile(first, count, threadIdx.x, kComputeThreads, hi, lo, [] { __syncthreads(); });
+            const int consumer = first < list.raw_count ? 0 : int(((first - list.raw_count - sel_begin) / kT) % kGroups);
+            if (group == consumer) compute(smem_u32(hi), smem_u32(lo), *f32_live, false, std::true_type{});
+            first += count;
+        }
+    }
 
     // ---- BF16 selected rows: tile t is consumed by group t % 2 from slot t % kStages ----
     {
@@ -446,19 +523,28 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     const int parts = int(splits) * kGroups;                   // (at most 16: a lane each)
     float* merge_factors = slabs;                              // [16 heads][32]
     float* denominators = slabs + 16 * 32;
-    // this CTA's columns (splits divides dim / 2); all the parts of a column pair are asked for at once
+    // This CTA's columns (splits divides dim / 2). A thread merges up to kWide column pairs; the first eight parts of all of
+    // them are asked for before the factors are formed, so that the two latencies overlap.
     const int cols = DIM / int(splits), col0 = int(split) * cols, half = cols / 2;
-    auto merge_pair = [&](int i, auto&& body) {
-        const int head_local = i / half, d = col0 + 2 * (i % half);
-        if (i >= 16 * half || head0 + head_local >= a.heads) return;
-        const uint32_t from = smem_u32(parts_area + head_local * kPartRow + d);
-        float2 x[16];
-        #pragma unroll
-        for (int part = 0; part < 16; ++part)
-            x[part] = part < parts ? cluster_load2(cluster_address(from + uint32_t((part % kGroups) * 16 * kPartRow * 4), uint32_t(part / kGroups)))
-                                   : make_float2(0.0f, 0.0f);
-        body(head_local, d, x);
+    constexpr int kWide = (16 * (DIM / 2) / 4 + kComputeThreads - 1) / kComputeThreads;   // pairs a thread at four or more splits
+    auto pair_source = [&](int i, int& head_local, int& d) -> bool {
+        head_local = i / half; d = col0 + 2 * (i % half);
+        return i < 16 * half && head0 + head_local < a.heads;
     };
+    auto load_parts = [&](int i, int part0, float2 (&x)[8]) {
+        int head_local, d;
+        const bool real = pair_source(i, head_local, d);
+        const uint32_t from = smem_u32(parts_area + (real ? head_local * kPartRow + d : 0));
+        #pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int part = part0 + k;
+            x[k] = real && part < parts ? cluster_load2(cluster_address(from + uint32_t((part % kGroups) * 16 * kPartRow * 4), uint32_t(part / kGroups)))
+                                        : make_float2(0.0f, 0.0f);
+        }
+    };
+    float2 early[kWide][8];
+    #pragma unroll
+    for (int w = 0; w < kWide; ++w) load_parts(threadIdx.x + w * kComputeThreads, 0, early[w]);
     {   // warp = head, lane = part
         const size_t head = head0 + warp;
         float top_part = -INFINITY, sum_part = 0.0f, sink = -INFINITY;
@@ -481,26 +567,48 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     asm volatile("bar.sync 3, %0;" ::"n"(kComputeThreads) : "memory");
     {
         const size_t plain = DIM - 2 * pairs;
-        for (int i = threadIdx.x; i < 16 * half; i += kComputeThreads) {
-            merge_pair(i, [&](int head_local, int d, const float2 (&x)[16]) {
-                float2 sum = make_float2(0.0f, 0.0f);
-                #pragma unroll
-                for (int part = 0; part < 16; ++part) {
-                    if (part < parts) {
-                        const float factor = merge_factors[head_local * 32 + part];
-                        sum.x = fmaf(x[part].x, factor, sum.x); sum.y = fmaf(x[part].y, factor, sum.y);
-                    }
+        auto add_parts = [&](float2& sum, int head_local, int part0, const float2 (&x)[8]) {
+            #pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (part0 + k < parts) {
+                    const float factor = merge_factors[head_local * 32 + part0 + k];
+                    sum.x = fmaf(x[k].x, factor, sum.x); sum.y = fmaf(x[k].y, factor, sum.y);
                 }
-                const float denominator = denominators[head_local];
-                sum.x /= denominator; sum.y /= denominator;
-                if (size_t(d) >= plain) {
-                    const double2 turn = inverse[row * pairs + (d - plain) / 2];
-                    const double x0 = sum.x, y0 = sum.y;
-                    sum = make_float2(float(x0 * turn.x - y0 * turn.y), float(x0 * turn.y + y0 * turn.x));
-                }
-                float* to = out + (row * a.heads + head0 + head_local) * DIM + d;   // (only known to be 4-byte aligned)
-                to[0] = sum.x; to[1] = sum.y;
-            });
+            }
+        };
+        auto finish = [&](float2 sum, int head_local, int d) {
+            const float denominator = denominators[head_local];
+            sum.x /= denominator; sum.y /= denominator;
+            if (size_t(d) >= plain) {
+                const double2 turn = inverse[row * pairs + (d - plain) / 2];
+                const double x0 = sum.x, y0 = sum.y;
+                sum = make_float2(float(x0 * turn.x - y0 * turn.y), float(x0 * turn.y + y0 * turn.x));
+            }
+            float* to = out + (row * a.heads + head0 + head_local) * DIM + d;   // (only known to be 4-byte aligned)
+            to[0] = sum.x; to[1] = sum.y;
+        };
+        #pragma unroll
+        for (int w = 0; w < kWide; ++w) {
+            int head_local, d;
+            if (!pair_source(threadIdx.x + w * kComputeThreads, head_local, d)) continue;
+            float2 sum = make_float2(0.0f, 0.0f);
+            add_parts(sum, head_local, 0, early[w]);
+            if (parts > 8) {
+                float2 more[8];
+                load_parts(threadIdx.x + w * kComputeThreads, 8, more);
+                add_parts(sum, head_local, 8, more);
+            }
+            finish(sum, head_local, d);
+        }
+        // (fewer than four splits: more pairs a thread than were asked for early)
+        for (int i = threadIdx.x + kWide * kComputeThreads; i < 16 * half; i += kComputeThreads) {
+            int head_local, d;
+            if (!pair_source(i, head_local, d)) continue;
+            float2 x[8];
+            load_parts(i, 0, x);
+            float2 sum = make_float2(0.0f, 0.0f);
+            add_parts(sum, head_local, 0, x);
+            finish(sum, head_local, d);
         }
     }
     cluster_arrive(); cluster_wait();   // (nobody leaves while its partial may still be read)

@@ -108,6 +108,46 @@ def test_tensor_core_kernel_shapes(gpu, form, rows, heads, dim, window, selectio
     assert close(got, simt)[0]
 
 
+@pytest.mark.parametrize("heads,window,rope_dims", [(16, 8, 64), (32, 3, 0), (8, 20, 0)])
+def test_spans_in_one_call_equal_one_call_a_span(gpu, form, heads, window, rope_dims):
+    """sdx_sparse_attention_spans: several verify spans (their own window rings, one shared cache allocation) in one launch give
+    the bits of one sd_op_sparse_attention call a span, and stay within tolerance of the oracle."""
+    rng = np.random.default_rng(7 + heads)
+    spans, span_rows, dim, selections, raw_rows, per_cache = 3, 8, 576, 96, 32, 700
+    q = rng.normal(0, 1, (spans, span_rows, heads, dim)).astype(np.float32)
+    raw = rng.normal(0, 0.05, (spans, raw_rows, dim)).astype(np.float32)
+    halves, _ = bf16_round(rng.normal(0, 0.05, (spans * per_cache, dim)).astype(np.float32))
+    selected = rng.integers(0, per_cache, (spans, span_rows, selections)).astype(np.int32)
+    selected[:, :, ::7] = -1
+    absolute = np.where(selected >= 0, selected + (np.arange(spans) * per_cache)[:, None, None], -1).astype(np.int32)
+    positions = np.stack([np.arange(span_rows) + 5 * s for s in range(spans)]).astype(np.int32)   # (span s starts at ring row 5 s)
+    sinks = rng.normal(0, 1, heads).astype(np.float32)
+    freq = (10000.0 ** (-(2.0 * np.arange(max(rope_dims, 2) // 2)) / max(rope_dims, 2))).astype(np.float32)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+    bufs = {k: gpu.upload(v) for k, v in dict(q=q, raw=raw, positions=positions, selected=absolute, sinks=sinks, freq=freq).items()}
+    comp = gpu.upload(halves)
+    out = gpu.buffer(q.nbytes)
+    rope = (rope_dims, bufs["freq"].pointer) if rope_dims else None
+    gpu.sparse_attention_spans(bufs["q"].pointer, bufs["raw"].pointer, raw_rows, bufs["positions"].pointer, window,
+                               (comp.tagged_bf16(), spans * per_cache), (bufs["selected"].pointer, selections), bufs["sinks"].pointer,
+                               spans, span_rows, heads, dim, scale, rope, out.pointer)
+    together = gpu.read(out, np.float32, q.shape)
+    one = gpu.buffer(q[0].nbytes)
+    for s in range(spans):
+        gpu.sparse_attention(bufs["q"].pointer + s * q[0].nbytes, bufs["raw"].pointer + s * raw[0].nbytes, raw_rows,
+                             bufs["positions"].pointer + s * span_rows * 4, window, (comp.tagged_bf16(), spans * per_cache),
+                             (bufs["selected"].pointer + s * span_rows * selections * 4, selections), bufs["sinks"].pointer,
+                             span_rows, heads, dim, scale, rope, None, one.pointer)
+        alone = gpu.read(one, np.float32, q[0].shape)
+        assert np.array_equal(alone.view(np.uint32), together[s].view(np.uint32)), f"span {s}"
+        want = oracle.sparse_attention(q[s], raw[s], raw_rows, positions[s], window, halves, absolute[s], selections, sinks, span_rows, heads,
+                                       dim, scale, rope_dims, freq if rope_dims else None, f64=True)
+        ok, worst = close(alone, want)
+        assert ok, worst
+    for b in list(bufs.values()) + [comp, out, one]:
+        gpu.release(b)
+
+
 def test_window_ring_empty_selections_and_no_selection_list(gpu):
     rng = np.random.default_rng(42)
     rows, heads, dim, window, raw_rows = 5, 8, 64, 6, 8
