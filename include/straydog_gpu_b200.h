@@ -145,6 +145,25 @@ int sdx_sparse_attention_spans(void* handle, const float* q, const float* raw, u
                                uint64_t selections, const float* sinks, uint64_t spans, uint64_t span_rows, uint64_t heads, uint64_t dim,
                                float scale, uint64_t rope_dims, const float* frequencies, float* out);
 
+/* Head-sharded latent attention with the all-gather inside the kernel (no reference counterpart: the reference shards by
+   pipeline stage, not by head). Rank `rank` of `world` (<= 8) GPUs of one node computes this call's `heads` heads (its share) over
+   the whole latent cache; every GPU keeps a gathered buffer [world][rows][heads][dim] F32 (rank-major). The call stores this rank's
+   outputs into slot `rank` of EVERY GPU's buffer (outs[peer]: this handle's own allocation for peer == rank, mappings made by
+   sdx_ipc_open for the others: plain stores over NVLink from the kernel's merge), then raises counter `rank` in every GPU's
+   `flags[peer]` (int32 [world], zeroed once) to `step` and waits on the stream, bounded to a second, until its own counters all
+   show `step`: work queued behind the call sees the whole gathered buffer. `step` grows by one per call. */
+int sdx_sparse_attention_gather(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                                uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                                uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
+                                uint64_t rope_dims, const float* frequencies, uint64_t world, uint64_t rank, void* const* outs,
+                                void* const* flags, int32_t step);
+/* Sharing an allocation with the other ranks' processes (CUDA IPC): export writes a 64-byte handle for an allocation's base
+   pointer; open maps another process's exported allocation of `bytes` bytes (peer access over NVLink) and lets this handle's
+   entries accept pointers into it where they say so; close unmaps. */
+int sdx_ipc_export(void* handle, const void* pointer, void* out_handle);
+void* sdx_ipc_open(void* handle, const void* in_handle, uint64_t bytes);
+int sdx_ipc_close(void* handle, void* pointer);
+
 /* One decode step of a batch from HOST buffers (the batched twin of sd_attention_sequence): for
    sequence s the new token's keys/values (k, v: [sequences][kv_heads][256] F32, host) are written
    to row bases[s] of states[s], then its query (q: [sequences][heads][256] FP16, host) attends rows

@@ -36,6 +36,10 @@ SIGNATURES = {
     "sd_attention_turns_reserve": ([p, u64, u64], i32),
     "sd_attention_turns_arm": ([p, u64], i32),
     "sd_op_sparse_attention": ([p, p, p, u64, p, u64, p, u64, p, u64, p, u64, u64, u64, f32, u64, p, p, u64, p], i32),
+    "sdx_sparse_attention_gather": ([p, p, p, u64, p, u64, p, u64, p, u64, p, u64, u64, u64, f32, u64, p, u64, u64, p, p, i32], i32),
+    "sdx_ipc_export": ([p, p, p], i32),
+    "sdx_ipc_open": ([p, p, u64], p),
+    "sdx_ipc_close": ([p, p], i32),
     "sdx_sparse_attention_spans": ([p, p, p, u64, p, u64, p, u64, p, u64, p, u64, u64, u64, u64, f32, u64, p, p], i32),
     "sd_op_top_k": ([p, p, u64, u64, u64, p], i32),
     "sd_op_to_bf16": ([p, p, u64, p], i32),

@@ -270,6 +270,33 @@ class Backend:
         self._c(self.lib.sdx_sparse_attention_spans(self.handle, q, raw, raw_rows, positions, window, c_ptr, c_rows, s_ptr, selections, sinks,
                                                 spans, span_rows, heads, dim, scale, rope_dims, freq, out))
 
+    def ipc_export(self, buffer):
+        """64 bytes another rank's process hands to ipc_open to map `buffer` (an allocation of this handle)."""
+        token = C.create_string_buffer(64)
+        self._c(self.lib.sdx_ipc_export(self.handle, buffer.pointer, token))
+        return token.raw
+
+    def ipc_open(self, token, size):
+        pointer = self.lib.sdx_ipc_open(self.handle, token, size)
+        if not pointer:
+            _fail(self.lib)
+        return pointer
+
+    def ipc_close(self, pointer):
+        self._c(self.lib.sdx_ipc_close(self.handle, pointer))
+
+    def sparse_attention_gather(self, q, raw, raw_rows, positions, window, compressed, selected, sinks, rows, heads, dim, scale, rope,
+                                rank, outs, flags, step):
+        """sparse_attention of this rank's heads with its outputs stored into slot `rank` of every rank's gathered buffer
+        (outs, flags: one device pointer per rank, the others' mapped by ipc_open)."""
+        c_ptr, c_rows = compressed if compressed else (None, 0)
+        s_ptr, selections = selected if selected else (None, 0)
+        rope_dims, freq = rope if rope else (0, None)
+        world = len(outs)
+        out_table, flag_table = (C.c_void_p * world)(*outs), (C.c_void_p * world)(*flags)
+        self._c(self.lib.sdx_sparse_attention_gather(self.handle, q, raw, raw_rows, positions, window, c_ptr, c_rows, s_ptr, selections, sinks,
+                                                 rows, heads, dim, scale, rope_dims, freq, world, rank, out_table, flag_table, step))
+
     def top_k(self, scores, rows, groups, k, out):
         self._c(self.lib.sd_op_top_k(self.handle, scores, rows, groups, k, out))
 

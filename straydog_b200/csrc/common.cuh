@@ -43,6 +43,7 @@ struct Device {
     unsigned kv_row = kv_row_q8;
     std::mutex mutex;
     std::map<const uint8_t*, size_t> allocations;   // base -> requested bytes
+    std::map<const uint8_t*, size_t> peers;         // base -> bytes of other processes' allocations mapped by sdx_ipc_open
     // staging for host-pointer entries (page-locked) and device-side workspaces, grown on demand
     void* pinned = nullptr; size_t pinned_bytes = 0;
     void* work = nullptr; size_t work_bytes = 0;        // packed inputs / outputs of host-pointer entries
@@ -61,6 +62,7 @@ Device& device(void* handle);   // sets the CUDA device; throws on a null handle
 void* raw_allocate(Device& d, size_t bytes, bool zero);
 void raw_release(Device& d, void* pointer);
 void span(Device& d, const void* pointer, size_t bytes, const char* what);
+void span_or_peer(Device& d, const void* pointer, size_t bytes, const char* what);   // also accepts a mapped peer allocation
 void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_host = false);
 int* status_word(Device& d);   // the device's word a kernel's bounded wait sets when it gives up (read by sdx_decode_status)
 

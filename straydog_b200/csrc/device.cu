@@ -4,6 +4,8 @@
 // result or a null pointer is a failure that sd_error() describes for the calling thread; the
 // library owns every allocation and each op checks that its pointers lie inside one of them.
 #include "common.cuh"
+
+#include <cstring>
 #include "../../include/straydog_gpu_b200.h"
 
 namespace sdb {
@@ -57,6 +59,19 @@ void span(Device& d, const void* pointer, size_t bytes, const char* what) {
         if (bytes <= next->second && size_t(at - next->first) <= next->second - bytes) return;
     }
     throw std::runtime_error(std::string("Straydog op: ") + what + " is outside this device's allocations");
+}
+
+void span_or_peer(Device& d, const void* pointer, size_t bytes, const char* what) {
+    const auto* at = static_cast<const uint8_t*>(pointer);
+    {
+        std::lock_guard<std::mutex> lock(d.mutex);
+        auto next = d.peers.upper_bound(at);
+        if (next != d.peers.begin()) {
+            --next;
+            if (bytes <= next->second && size_t(at - next->first) <= next->second - bytes) return;
+        }
+    }
+    span(d, pointer, bytes, what);
 }
 
 // Library-owned workspaces (not in the allocation map: callers never see them), grown on demand.
@@ -116,6 +131,7 @@ void sd_destroy(void* handle) {
     auto* value = static_cast<Device*>(handle);
     if (cudaSetDevice(value->ordinal) == cudaSuccess) {
         cudaStreamSynchronize(value->stream);
+        for (auto& entry : value->peers) cudaIpcCloseMemHandle(const_cast<uint8_t*>(entry.first));
         for (auto& entry : value->allocations) cudaFree(const_cast<uint8_t*>(entry.first));
         if (value->pinned) cudaFreeHost(value->pinned);
         if (value->append_pinned) cudaFreeHost(value->append_pinned);
@@ -299,6 +315,49 @@ void sdx_event_destroy(void* event) { if (event) cudaEventDestroy(static_cast<cu
 uint64_t sdx_launch_count(void* handle) {
     try { return device(handle).launches; }
     catch (const std::exception& e) { last_error = e.what(); return 0; }
+}
+
+
+// ---- another process's allocation on another GPU of the node, for kernels that store to peers over NVLink ----
+int sdx_ipc_export(void* handle, const void* pointer, void* out_handle) {
+    SDB_OP_BEGIN
+    {
+        std::lock_guard<std::mutex> lock(value.mutex);
+        if (!value.allocations.count(static_cast<const uint8_t*>(pointer))) throw std::runtime_error("unknown Straydog allocation");
+    }
+    if (!out_handle) throw std::runtime_error("no room for the handle");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the exported handle is 64 bytes");
+    cudaIpcMemHandle_t exported;
+    SDB_CHECK(cudaIpcGetMemHandle(&exported, const_cast<void*>(pointer)));
+    std::memcpy(out_handle, &exported, sizeof exported);
+    SDB_OP_END
+}
+
+void* sdx_ipc_open(void* handle, const void* in_handle, uint64_t bytes) {
+    try {
+        auto& value = device(handle);
+        if (!in_handle || !bytes) throw std::runtime_error("no handle to open");
+        cudaIpcMemHandle_t imported;
+        std::memcpy(&imported, in_handle, sizeof imported);
+        void* pointer = nullptr;
+        SDB_CHECK(cudaIpcOpenMemHandle(&pointer, imported, cudaIpcMemLazyEnablePeerAccess));
+        std::lock_guard<std::mutex> lock(value.mutex);
+        value.peers.emplace(static_cast<const uint8_t*>(pointer), size_t(bytes));
+        return pointer;
+    } catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+int sdx_ipc_close(void* handle, void* pointer) {
+    SDB_OP_BEGIN
+    {
+        std::lock_guard<std::mutex> lock(value.mutex);
+        auto found = value.peers.find(static_cast<const uint8_t*>(pointer));
+        if (found == value.peers.end()) throw std::runtime_error("unknown peer mapping");
+        value.peers.erase(found);
+    }
+    SDB_CHECK(cudaStreamSynchronize(value.stream));
+    SDB_CHECK(cudaIpcCloseMemHandle(pointer));
+    SDB_OP_END
 }
 
 }  // extern "C"

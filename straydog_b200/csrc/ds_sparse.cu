@@ -274,7 +274,7 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
                                  uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
                                  uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
                                  uint64_t rope_dims, const float* frequencies, float* scratch, uint64_t scratch_bytes, float* out,
-                                 uint64_t spans, uint64_t span_rows) {
+                                 uint64_t spans, uint64_t span_rows, const GatherTargets* gather = nullptr) {
     SDB_OP_BEGIN
     if (!rows || rows > 65535 || !heads || !dim || !window || rope_dims % 2 || rope_dims > dim || rope_dims > 128)
         throw std::runtime_error("invalid Straydog attention shape");
@@ -289,7 +289,7 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
         span(value, selected, checked_product({rows, selections, 4}), "selected rows");
     }
     span(value, sinks, checked_product({heads, 4}), "attention sinks");
-    span(value, out, checked_product({rows, heads, dim, 4}), "an attention output");
+    if (!gather) span(value, out, checked_product({rows, heads, dim, 4}), "an attention output");
     if (scratch && scratch_bytes) span(value, scratch, size_t(scratch_bytes), "attention scratch");
 
     const size_t pairs = size_t(rope_dims / 2);
@@ -310,6 +310,12 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
     args.scale = scale;
     args.span_rows = spans > 1 ? span_rows : rows;   // (one span: every row in ring 0)
 
+    if (gather) {   // (the gathered form exists in the third tensor-core kernel only)
+        if (!sparse_mma_supported(args)) throw std::runtime_error("the gathered latent attention needs dim 512 or 576 and 16-byte aligned rows");
+        sparse_mma3_launch(value, args, q, sinks, rows, pairs, forward, inverse, nullptr, gather);
+        SDB_CHECK(cudaGetLastError());
+        return 0;
+    }
     const bool force_simt = env_flag("SDX_SPARSE_SIMT");
     if (!force_simt && sparse_mma_supported(args)) {
         // (SDX_SPARSE_KERNEL=v1|v2|v3 picks a form of the tensor-core kernel for A/B runs; the third, sixteen compute warps over one
@@ -372,6 +378,30 @@ int sdx_sparse_attention_spans(void* handle, const float* q, const float* raw, u
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
     return sparse_attention_call(handle, q, raw, raw_rows, positions, window, compressed, compressed_rows, selected, selections, sinks,
                                  spans * span_rows, heads, dim, scale, rope_dims, frequencies, nullptr, 0, out, spans, span_rows);
+}
+
+
+int sdx_sparse_attention_gather(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
+                                uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
+                                uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
+                                uint64_t rope_dims, const float* frequencies, uint64_t world, uint64_t rank, void* const* outs,
+                                void* const* flags, int32_t step) {
+    GatherTargets gather{};
+    try {
+        auto& value = device(handle);
+        if (!world || world > uint64_t(kMaxGatherWorld) || rank >= world || !outs || !flags) throw std::runtime_error("invalid gather of Straydog attention outputs");
+        const size_t bytes = checked_product({world, rows, heads, dim, 4});
+        for (uint64_t peer = 0; peer < world; ++peer) {
+            span_or_peer(value, outs[peer], bytes, "a gathered attention output");
+            span_or_peer(value, flags[peer], size_t(world) * 4, "a gather's arrival counters");
+            if (reinterpret_cast<uintptr_t>(outs[peer]) % 8 || dim % 2) throw std::runtime_error("a gathered attention output must be 8-byte aligned");
+            gather.out[peer] = static_cast<float*>(outs[peer]);
+            gather.flags[peer] = static_cast<int*>(flags[peer]);
+        }
+        gather.world = uint32_t(world); gather.rank = uint32_t(rank); gather.step = step;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+    return sparse_attention_call(handle, q, raw, raw_rows, positions, window, compressed, compressed_rows, selected, selections, sinks, rows,
+                                 heads, dim, scale, rope_dims, frequencies, nullptr, 0, nullptr, 1, rows, &gather);
 }
 
 }  // extern "C"

@@ -16,6 +16,17 @@ struct SparseArgs {
     size_t span_rows;   // rows of one span: a call may hold several spans, each with its own window ring (never 0; one span: all the rows)
 };
 
+// Head-sharded runs: every GPU of the node keeps the gathered outputs [world][rows][heads][dim] (rank-major), and a rank's
+// kernel stores its own outputs into slot `rank` of every GPU's copy over NVLink (peer pointers), so that the all-gather
+// is part of the attention kernel's merge instead of a collective behind it.
+constexpr int kMaxGatherWorld = 8;
+struct GatherTargets {
+    float* out[kMaxGatherWorld];     // every rank's gathered buffer (this rank's own included)
+    int* flags[kMaxGatherWorld];     // every rank's arrival counters [world]
+    uint32_t world, rank;            // world == 0: no gather, plain `out`
+    int32_t step;                    // value a rank's counter takes when its outputs of this call have been stored
+};
+
 __host__ __device__ inline bool state_is_bf16(const void* p) { return reinterpret_cast<uintptr_t>(p) & 1u; }
 __host__ __device__ inline const uint16_t* state_halves(const void* p) {
     return reinterpret_cast<const uint16_t*>(reinterpret_cast<uintptr_t>(p) & ~uintptr_t(1));
@@ -53,7 +64,7 @@ void sparse_mma2_launch(Device& d, const SparseArgs& a, const float* q, const fl
                         const double2* forward, const double2* inverse, float* out);
 
 void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
-                        const double2* forward, const double2* inverse, float* out);
+                        const double2* forward, const double2* inverse, float* out, const GatherTargets* gather = nullptr);
 
 // kernels of ds_sparse.cu the tensor-core path reuses
 __global__ void sparse_prepare_q_kernel(const float* q, size_t heads, size_t dim, size_t pairs, const double2* forward, float* rotated_q,

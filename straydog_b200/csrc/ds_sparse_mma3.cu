@@ -107,7 +107,8 @@ __device__ __forceinline__ float2 cluster_load2(uint32_t address) {
 template<int DIM>
 __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         const SparseArgs a, const float* __restrict__ q, size_t pairs, const double2* __restrict__ forward,
-        float scale_log2, int* __restrict__ status, const float* __restrict__ sinks, const double2* __restrict__ inverse, float* __restrict__ out) {
+        float scale_log2, int* __restrict__ status, const float* __restrict__ sinks, const double2* __restrict__ inverse, float* __restrict__ out,
+        const GatherTargets gather) {
     using S = Shape<DIM>;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* planes = smem;
@@ -584,6 +585,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
                 const double x0 = sum.x, y0 = sum.y;
                 sum = make_float2(float(x0 * turn.x - y0 * turn.y), float(x0 * turn.y + y0 * turn.x));
             }
+            if (gather.world) {   // slot `rank` of every GPU's gathered copy (8-byte aligned: checked by the entry)
+                const size_t at = ((size_t(gather.rank) * gridDim.z + row) * a.heads + head0 + head_local) * DIM + d;
+                #pragma unroll 1
+                for (uint32_t peer = 0; peer < gather.world; ++peer) *reinterpret_cast<float2*>(gather.out[peer] + at) = sum;
+                return;
+            }
             float* to = out + (row * a.heads + head0 + head_local) * DIM + d;   // (only known to be 4-byte aligned)
             to[0] = sum.x; to[1] = sum.y;
         };
@@ -616,9 +623,29 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
 
 }  // namespace v3
 
+// After a rank's attention kernel: tell every GPU that this rank's slot of its gathered copy is written, then wait until every
+// rank has told this GPU the same. The attention kernel's peer stores are complete when this kernel starts (same stream); the
+// fence and the release store order them before the counter for a reader on another GPU. The wait is bounded: a rank that never
+// arrives ends it after a second with status 4 instead of hanging the GPU.
+__global__ void gather_signal_wait_kernel(const GatherTargets gather, int* __restrict__ status) {
+    const uint32_t peer = threadIdx.x;
+    if (peer >= gather.world) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(gather.flags[peer] + gather.rank), "r"(gather.step) : "memory");
+    const int* mine = gather.flags[gather.rank] + peer;
+    const uint64_t start = global_timer_ns();
+    for (;;) {
+        int seen;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if (seen - gather.step >= 0) break;   // (counters only grow; the difference survives a wrap)
+        if (global_timer_ns() - start > 1000000000ull) { atomicExch(status, 4); break; }
+        __nanosleep(200);
+    }
+}
+
 template<int DIM>
 static void launch_v3(Device& d, const SparseArgs& a, const float* q, size_t pairs, const double2* forward, size_t rows, size_t splits,
-                      int* status, const float* sinks, const double2* inverse, float* out) {
+                      int* status, const float* sinks, const double2* inverse, float* out, const GatherTargets& gather) {
     using S = v3::Shape<DIM>;
     static bool configured[64] = {};
     if (!configured[d.ordinal & 63]) {
@@ -634,12 +661,12 @@ static void launch_v3(Device& d, const SparseArgs& a, const float* q, size_t pai
     cluster.id = cudaLaunchAttributeClusterDimension;
     cluster.val.clusterDim.x = unsigned(splits); cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
     config.attrs = &cluster; config.numAttrs = 1;
-    SDB_CHECK(cudaLaunchKernelEx(&config, v3::sparse_mma3_kernel<DIM>, a, q, pairs, forward, a.scale * 1.4426950408889634f, status, sinks, inverse, out));
+    SDB_CHECK(cudaLaunchKernelEx(&config, v3::sparse_mma3_kernel<DIM>, a, q, pairs, forward, a.scale * 1.4426950408889634f, status, sinks, inverse, out, gather));
     ++d.launches;
 }
 
 void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
-                        const double2* forward, const double2* inverse, float* out) {
+                        const double2* forward, const double2* inverse, float* out, const GatherTargets* gather) {
     const size_t head_tiles = (a.heads + 15) / 16;
     // One wave of CTAs (one per SM). The splits of a (row, head tile) are a thread-block cluster: 1, 2, 4 or 8 of them, as many
     // as keep rows * head tiles * splits within the SM count, each group of a split at least two tiles.
@@ -648,9 +675,16 @@ void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const fl
     size_t splits = 1;
     while (splits * 2 <= std::min<size_t>({room, useful, size_t(8)})) splits *= 2;
     int* status = status_word(d);
-    if (a.dim == 576) launch_v3<576>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out);
-    else launch_v3<512>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out);
+    GatherTargets targets{};
+    if (gather) targets = *gather;
+    if (a.dim == 576) launch_v3<576>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out, targets);
+    else launch_v3<512>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out, targets);
     SDB_CHECK(cudaGetLastError());
+    if (targets.world > 1) {
+        gather_signal_wait_kernel<<<1, 32, 0, d.stream>>>(targets, status);
+        ++d.launches;
+        SDB_CHECK(cudaGetLastError());
+    }
 }
 
 }  // namespace sdb

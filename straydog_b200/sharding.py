@@ -1,6 +1,9 @@
-"""Host-side logic of running the decode path on N GPUs of one node: which sequences a rank owns and how the ranks'
-timings and byte counts become one whole-job number. Sequences are independent, so the data path has no collective;
-torch.distributed carries only the barrier and two small reductions (NCCL on GPUs, gloo in the CPU tests)."""
+"""Host-side logic of running the attention path on N GPUs of one node.
+
+GQA decode: which sequences a rank owns and how the ranks' timings and byte counts become one whole-job number. Sequences are
+independent, so that data path has no collective; torch.distributed carries only the barrier and two small reductions.
+Latent sparse attention: the heads are dealt over the ranks (the latent rows are shared by all heads, so every rank holds the
+cache); a rank's outputs [rows][heads / N][dim] are all-gathered into [N][rows][heads / N][dim] (NCCL on GPUs, gloo in the CPU tests)."""
 import torch
 import torch.distributed as dist
 
@@ -31,3 +34,29 @@ def whole_job(times_ms, sums, device=None):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(s, op=dist.ReduceOp.SUM)
     return [float(x) for x in t.cpu()], [float(x) for x in s.cpu()]
+
+
+def head_range(heads, rank, world):
+    """(first head, head count) of `rank` when `heads` are dealt evenly over `world` ranks (heads % world == 0)."""
+    if heads % world:
+        raise ValueError(f"{heads} heads do not divide over {world} ranks")
+    each = heads // world
+    return rank * each, each
+
+
+def gather_heads(shard):
+    """All-gather of a rank's outputs [rows][heads / N][dim] -> [N][rows][heads / N][dim] (rank-major, what NCCL delivers without a
+    transpose; the consumer's contraction runs over (rank, head, dim) in that order). Runs on the current stream."""
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    full = torch.empty((world,) + tuple(shard.shape), dtype=shard.dtype, device=shard.device)
+    if world == 1:
+        full[0].copy_(shard)
+    else:
+        dist.all_gather_into_tensor(full.view(-1), shard.reshape(-1))
+    return full
+
+
+def heads_from_gathered(full):
+    """[N][rows][heads / N][dim] -> [rows][heads][dim] (a view-changing copy, for checks)."""
+    world, rows, each, dim = full.shape
+    return full.permute(1, 0, 2, 3).reshape(rows, world * each, dim)

@@ -54,3 +54,42 @@ def test_partition_edge_cases():
     assert sorted(parts[0] + parts[1]) == [0, 1, 2, 3, 4] and [4] in parts
     single, _ = sharding.rank_batch(SEED, 0, 1, "strong")
     assert single == ragged_lengths(SEED)
+
+
+def head_worker(rank, world, port, results):
+    import numpy as np
+    import oracle
+    from util import sparse_attention_case
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    c = sparse_attention_case(2, 8)
+    c["q"] = c["q"].reshape(c["rows"], c["heads"], c["dim"])
+    first, each = sharding.head_range(c["heads"], rank, world)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(c["dim"])))
+    mine = oracle.sparse_attention(np.ascontiguousarray(c["q"][:, first:first + each]), c["raw"], c["raw_rows"], c["positions"], c["window"], c["halves"],
+                                   c["selected"], c["selections"], c["sinks"][first:first + each], c["rows"], each, c["dim"], scale,
+                                   c["rope_dims"], c["freq"])
+    full = sharding.gather_heads(torch.from_numpy(mine))
+    results[rank] = sharding.heads_from_gathered(full).numpy()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_head_shards_gather_to_the_unsharded_result():
+    """Heads are independent in the latent attention: a rank's slice of q and sinks gives that slice of the output bit for bit, and
+    the all-gather (rank-major) rearranges to the unsharded [rows][heads][dim]."""
+    import numpy as np
+    import oracle
+    from util import sparse_attention_case
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(head_worker, args=(world, free_port(), results), nprocs=world, join=True)
+    c = sparse_attention_case(2, 8)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(c["dim"])))
+    whole = oracle.sparse_attention(c["q"], c["raw"], c["raw_rows"], c["positions"], c["window"], c["halves"], c["selected"],
+                                    c["selections"], c["sinks"], c["rows"], c["heads"], c["dim"], scale, c["rope_dims"], c["freq"])
+    for r in range(world):
+        assert np.array_equal(results[r].view(np.uint32), whole.view(np.uint32))
+    with __import__("pytest").raises(ValueError):
+        sharding.head_range(10, 0, 4)
