@@ -125,7 +125,10 @@ int sdx_qsa_plan_release(void* handle, void* plan);
    result is complete. It calls no cudaMalloc, cudaFree or allocating library routine. */
 int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
                           uint64_t sequences, uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out);
-/* 1 when a bounded wait inside a decode kernel gave up since the last call (cleared by the call), 0 if none. */
+/* What a kernel reported instead of hanging or faulting since the last call (cleared by the call), 0 if nothing:
+   1 a bounded wait on a copy gave up (decode, prompt or latent kernel); 2 a selected row number lay past the latent cache (the
+   row was taken as absent); 3 a key pointer lay outside the call's buffers (skipped); 4 a rank of a gathered latent attention
+   never raised its counter within a second. Synchronises the handle's stream. */
 int sdx_decode_status(void* handle);
 
 /* Causal prompt attention of a chunk: `rows` new tokens at positions first .. first + rows - 1 of a Q8_0 state

@@ -586,7 +586,8 @@ int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_
     SDB_OP_END
 }
 
-// 1 when a bounded wait inside a decode kernel gave up since the last call (the word is cleared), else 0.
+// What a kernel reported since the last call (the word is cleared): 0 nothing, 1 a bounded wait on a copy gave up, 2 / 3 a row
+// number / key pointer out of range in the latent kernel, 4 a gather's peer never arrived.
 int sdx_decode_status(void* handle) {
     try {
         auto& value = device(handle);

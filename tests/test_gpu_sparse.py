@@ -148,6 +148,75 @@ def test_spans_in_one_call_equal_one_call_a_span(gpu, form, heads, window, rope_
         gpu.release(b)
 
 
+def test_gathered_form_with_one_rank_equals_the_plain_call(gpu):
+    """sdx_sparse_attention_gather at world = 1: slot 0 of the gathered buffer holds the bits of sd_op_sparse_attention; foreign
+    pointers and bad ranks are refused. (Two ranks wait on each other's counters, so they never share one GPU: the N-GPU
+    form is checked against the oracle by `bench.py --config 3` under torchrun.)"""
+    from straydog_b200.backend import StraydogError
+    rng = np.random.default_rng(11)
+    rows, heads, dim, ctx, sel = 3, 16, 576, 2048, 256
+    halves, widened = bf16_round(rng.normal(0, 0.05, (rows * ctx, dim)).astype(np.float32))
+    _, q = bf16_round(rng.normal(0, 1, (rows, heads, dim)).astype(np.float32))
+    raw = widened.reshape(rows, ctx, dim)[:, -1].copy()
+    selected = np.stack([np.sort(rng.choice(ctx, sel, replace=False)) + r * ctx for r in range(rows)]).astype(np.int32)
+    sinks = rng.normal(0, 1, heads).astype(np.float32)
+    bufs = {k: gpu.upload(v) for k, v in dict(q=q, raw=raw, positions=np.arange(rows, dtype=np.int32), selected=selected, sinks=sinks).items()}
+    comp = gpu.upload(halves)
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(dim)))
+    plain, full, flags = gpu.buffer(q.nbytes), gpu.buffer(q.nbytes), gpu.buffer(4)
+    args = (bufs["q"].pointer, bufs["raw"].pointer, rows, bufs["positions"].pointer, 1, (comp.tagged_bf16(), rows * ctx),
+            (bufs["selected"].pointer, sel), bufs["sinks"].pointer, rows, heads, dim, scale, None)
+    gpu.sparse_attention(*args, None, plain.pointer)
+    gpu.sparse_attention_gather(*args, 0, [full.pointer], [flags.pointer], 1)
+    a, b = gpu.read(plain, np.float32, q.shape), gpu.read(full, np.float32, q.shape)
+    assert a.any() and np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert gpu.decode_status() == 0
+    with pytest.raises(StraydogError):
+        gpu.sparse_attention_gather(*args, 1, [full.pointer], [flags.pointer], 2)          # rank outside the world
+    with pytest.raises(StraydogError):
+        gpu.sparse_attention_gather(*args, 0, [full.pointer + 4], [flags.pointer], 2)      # buffer too small from there, and misaligned
+    with pytest.raises(StraydogError):
+        gpu.ipc_close(full.pointer)                                                          # not a peer mapping
+    assert len(gpu.ipc_export(full)) == 64
+    for b_ in list(bufs.values()) + [comp, plain, full, flags]:
+        gpu.release(b_)
+
+
+def test_a_gather_whose_peer_never_arrives_gives_up_with_a_status(gpu):
+    """The counter wait behind the gathered form is bounded: with a second 'rank' that nothing ever runs (both buffers on this
+    GPU), the wait runs out after a second, the call returns, the status word says 4 and the handle stays usable."""
+    import time
+    rng = np.random.default_rng(12)
+    rows, heads, dim, ctx, sel = 1, 16, 512, 512, 128
+    halves, widened = bf16_round(rng.normal(0, 0.05, (ctx, dim)).astype(np.float32))
+    _, q = bf16_round(rng.normal(0, 1, (rows, heads, dim)).astype(np.float32))
+    raw = widened[-1:].copy()
+    selected = np.sort(rng.choice(ctx, sel, replace=False)).astype(np.int32).reshape(1, sel)
+    bufs = {k: gpu.upload(v) for k, v in dict(q=q, raw=raw, positions=np.zeros(1, np.int32), selected=selected,
+                                              sinks=np.zeros(heads, np.float32)).items()}
+    comp = gpu.upload(halves)
+    mine, other = gpu.buffer(2 * q.nbytes), gpu.buffer(2 * q.nbytes)
+    my_flags, other_flags = gpu.buffer(8), gpu.buffer(8)
+    args = (bufs["q"].pointer, bufs["raw"].pointer, 1, bufs["positions"].pointer, 1, (comp.tagged_bf16(), ctx),
+            (bufs["selected"].pointer, sel), bufs["sinks"].pointer, rows, heads, dim, float(dim) ** -0.5, None)
+    assert gpu.decode_status() == 0
+    started = time.perf_counter()
+    gpu.sparse_attention_gather(*args, 0, [mine.pointer, other.pointer], [my_flags.pointer, other_flags.pointer], 1)
+    gpu.synchronize()
+    waited = time.perf_counter() - started
+    assert 0.9 < waited < 5.0, waited
+    assert gpu.decode_status() == 4
+    # rank 0's slot is written in both copies, its counter raised in both; the absent rank's slot and counter are untouched
+    a, b = gpu.read(mine, np.float32, (2, rows, heads, dim)), gpu.read(other, np.float32, (2, rows, heads, dim))
+    assert a[0].any() and np.array_equal(a[0], b[0]) and not a[1].any() and not b[1].any()
+    assert gpu.read(my_flags, np.int32, (2,)).tolist() == [1, 0] and gpu.read(other_flags, np.int32, (2,)).tolist() == [1, 0]
+    plain = gpu.buffer(q.nbytes)
+    gpu.sparse_attention(*args, None, plain.pointer)   # the handle still works
+    assert np.array_equal(gpu.read(plain, np.float32, q.shape), a[0])
+    for b_ in list(bufs.values()) + [comp, mine, other, my_flags, other_flags, plain]:
+        gpu.release(b_)
+
+
 def test_window_ring_empty_selections_and_no_selection_list(gpu):
     rng = np.random.default_rng(42)
     rows, heads, dim, window, raw_rows = 5, 8, 64, 6, 8
