@@ -168,9 +168,12 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     const bool rows_bf16 = state_is_bf16(a.compressed);
     // The selected rows are dealt in whole tiles. Split 0 also has the window rows, an F32 tile of which costs one of its groups
     // about three streamed tiles (read, converted on the spot, both parts multiplied): it takes that many fewer streamed tiles.
-    const uint32_t all_tiles = uint32_t((a.selections + kT - 1) / kT), window_tiles = uint32_t((list.raw_count + kT - 1) / kT);
-    // (a window of up to kScalarWindow rows goes through FP32 arithmetic instead: next to free)
-    const bool scalar_window = list.raw_count > 0 && list.raw_count <= size_t(kScalarWindow);
+    // (a window of up to kScalarWindow rows goes through FP32 arithmetic instead: next to free. When the call's window is that
+    //  short, the dealing does not wait for the row's position to come from HBM: the copy warps start a round trip earlier.)
+    const bool short_window = a.window <= size_t(kScalarWindow);
+    const uint32_t all_tiles = uint32_t((a.selections + kT - 1) / kT);
+    const uint32_t window_tiles = short_window ? 0u : uint32_t((list.raw_count + kT - 1) / kT);
+    const bool scalar_window = short_window || (list.raw_count > 0 && list.raw_count <= size_t(kScalarWindow));
     const uint32_t window_cost = scalar_window ? 0u : 3 * window_tiles;   // (the same for both row formats, so that they are dealt alike)
     const uint32_t per_split = (all_tiles + window_cost + uint32_t(splits) - 1) / uint32_t(splits);
     const uint32_t first_share = per_split > window_cost ? per_split - window_cost : (splits == 1 ? all_tiles : 0u);
