@@ -164,7 +164,7 @@ def workload_config(lengths, l2):
 
 
 
-# ---- the other configurations (parity-test cases, measured here for DESIGN.md and profiles/; not the driver's line) ----
+# ---- the other configurations (parity-test cases, measured for the design notes and the profile summaries; not the benchmark line) ----
 def timed(gpu, fn, steps, warmup):
     for _ in range(max(3, warmup)):
         fn()
