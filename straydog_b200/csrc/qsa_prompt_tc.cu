@@ -228,14 +228,16 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             tmem_ld32(tmem + lane_base + 256 + slot * 64 + half * 32, s);
             const long long begin = (long long)j * kN + half * 32;
             const bool edge = (long long)j * kN + kN - 1 > (long long)(a.first + r0) || (long long)j * kN + kN > (long long)keys_total;
-            float top = -INFINITY;
+            // (four independent maxima, then their maximum: one chain of 32 dependent fmnmx cost a third of the tile's softmax time)
+            float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             #pragma unroll
             for (int n = 0; n < 32; ++n) {
                 float x = s[n] * a.scale_log2;
                 if (edge && begin + n > limit) x = -INFINITY;
                 s[n] = x;
-                top = fmaxf(top, x);
+                tops[n & 3] = fmaxf(tops[n & 3], x);
             }
+            const float top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
             *mine_stat = top;
             pair_barrier(1 + rb);
             const float m_new = fmaxf(m_run, fmaxf(top, *other_stat));
@@ -266,14 +268,14 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             // This half of the P row, 32 FP16 as 16 TMEM columns, over the first columns of the S buffer it came from (every thread of the
             // row block has its scores in registers by now: both halves passed the barriers above). The product reads P from TMEM.
             uint32_t packed[16];
-            float sum = 0.0f;
+            float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float p0 = fast_exp2(s[2 * i] - u), p1 = fast_exp2(s[2 * i + 1] - u);
-                sum += p0 + p1;
+                sums[i & 3] += p0 + p1;
                 packed[i] = pack_half2(p0, p1);
             }
-            l_run += sum;
+            l_run += (sums[0] + sums[1]) + (sums[2] + sums[3]);
             tmem_st16_bits(tmem + lane_base + 256 + slot * 64 + half * 16, packed);
             tmem_st_wait();
             tc_fence_before();
