@@ -615,7 +615,10 @@ def main():
             "dtype": "f16 x int8 products, f32 accumulate", "data": "synthetic (seeded)",
             "config": workload_config(lengths, "inputs larger than L2 (1.2 GB of K/V per step against 126 MB)"),
             "tokens_per_s": total_sequences * args.steps / (device_ms_max / 1e3),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         # DRAM bytes a launch: the ncu capture of a 16-sequence case read and wrote 1.022 x its algorithmic bytes
+                         # (the extra is the split partials); traffic grows with the K/V bytes, so it is scaled to this launch
+                         "traffic": kv_bytes * 1.022, "traffic_source": "ncu dram__bytes of a 16-sequence launch (226.2 MB for 220.9 MB), scaled by K/V bytes",
                          "peak_source": peak_source, "kernel": "qsa_decode_kernel", "kernel_ms": statistics.mean(kernel_ms),
                          "frac_of_nominal_8tbs": achieved / 8000.0},
             "cpu_baseline": ({"value": cpu_gbps, "unit": UNIT, "cores": cpu_threads, "kind": "port",
