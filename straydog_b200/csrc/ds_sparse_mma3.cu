@@ -664,6 +664,24 @@ static void launch_v3(Device& d, const SparseArgs& a, const float* q, size_t pai
     cluster.id = cudaLaunchAttributeClusterDimension;
     cluster.val.clusterDim.x = unsigned(splits); cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
     config.attrs = &cluster; config.numAttrs = 1;
+    // A cluster of this size must fit the device (one 640-thread CTA with all its shared memory per SM, the cluster's SMs in one
+    // GPC): asked of the driver once per device and size; a size that does not fit is halved (the kernel reads the split count
+    // from the grid, so any power of two is a valid launch).
+    static int fits[64][4] = {};   // [device][log2 size]: 0 unknown, 1 fits, -1 does not
+    for (;;) {
+        const unsigned size = config.gridDim.x;
+        const int slot = size >= 8 ? 3 : size >= 4 ? 2 : size >= 2 ? 1 : 0;
+        int& known = fits[d.ordinal & 63][slot];
+        if (size > 1 && !known) {
+            int clusters = 0;
+            const cudaError_t asked = cudaOccupancyMaxActiveClusters(&clusters, v3::sparse_mma3_kernel<DIM>, &config);
+            if (asked != cudaSuccess) cudaGetLastError();
+            known = asked == cudaSuccess && clusters > 0 ? 1 : -1;
+        }
+        if (size == 1 || known > 0) break;
+        config.gridDim.x = size / 2;
+        cluster.val.clusterDim.x = size / 2;
+    }
     SDB_CHECK(cudaLaunchKernelEx(&config, v3::sparse_mma3_kernel<DIM>, a, q, pairs, forward, a.scale * 1.4426950408889634f, status, sinks, inverse, out, gather));
     ++d.launches;
 }
