@@ -81,6 +81,10 @@ int sd_op_top_k(void* handle, const float* scores, uint64_t rows, uint64_t group
 int sd_op_to_bf16(void* handle, const float* x, uint64_t count, void* out);
 
 /* ---- additions (no counterpart in the reference) ---- */
+/* A handle over another library's CUDA stream and allocations on device `ordinal` (no counterpart in the reference: it is what the
+   reference's own build holds when its spans call this library's kernels, include/qsa_b200.hpp). Ops queue on `stream`; pointers
+   are taken as checked by the caller; sd_allocate and friends are refused. Released by sd_destroy, which leaves the stream alone. */
+void* sdx_adopt(int ordinal, void* stream);
 /* Waits for everything queued on the handle's stream. */
 int sdx_synchronize(void* handle);
 /* The handle's CUDA stream (a cudaStream_t), for timing with events on the launching stream. */
@@ -166,6 +170,19 @@ int sdx_sparse_attention_gather(void* handle, const float* q, const float* raw, 
 int sdx_ipc_export(void* handle, const void* pointer, void* out_handle);
 void* sdx_ipc_open(void* handle, const void* in_handle, uint64_t bytes);
 int sdx_ipc_close(void* handle, void* pointer);
+
+/* Selection-list decode attention of `steps` rows on the tensor cores: the reference's qsa_attention (steps = 1) and
+   qsa_attention_rows (a verification's rows) as their callers use them (gpu/sparse_attention_compute.hpp:609-647 over
+   qsa_decode_parts / qsa_decode_merge, :41-170), for any heads / kv_heads <= 16. All pointers are device pointers. `input` holds
+   the packed F32 rows in the reference's layout (gpu/core.hpp:392): [steps][heads][256] queries | [steps][kv_heads][256] keys |
+   [steps][kv_heads][256] values | [steps][selected] key positions as floats | [steps] counts as floats. Row r sits at position
+   positions[r] (or base + r when positions is null); slot s of a row is live when s < count, 0 <= position <= the row's own and
+   position < context. `mirror` (or null) is the ring of the newest mirror_rows positions of a host-resident state, read as
+   gpu/sparse_attention_compute.hpp:65-68 does. `gates` (or null): out is multiplied by sigmoid(gates[r * gate_stride + head * 512
+   + 256 + column]) (:168). out [steps][heads][256] F32. A row's result has the same bits whatever `steps` is. selected <= 8192. */
+int sdx_qsa_attention_rows(void* handle, const void* state, uint64_t context, uint64_t base, const uint32_t* positions,
+                           uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float scale, const float* input,
+                           const void* mirror, uint64_t mirror_rows, const float* gates, uint64_t gate_stride, float* out);
 
 /* One decode step of a batch from HOST buffers (the batched twin of sd_attention_sequence): for
    sequence s the new token's keys/values (k, v: [sequences][kv_heads][256] F32, host) are written

@@ -43,6 +43,7 @@ SIGNATURES = {
     "sdx_sparse_attention_spans": ([p, p, p, u64, p, u64, p, u64, p, u64, p, u64, u64, u64, u64, f32, u64, p, p], i32),
     "sd_op_top_k": ([p, p, u64, u64, u64, p], i32),
     "sd_op_to_bf16": ([p, p, u64, p], i32),
+    "sdx_adopt": ([i32, p], p),
     "sdx_synchronize": ([p], i32),
     "sdx_stream": ([p], p),
     "sdx_launch_count": ([p], u64),
@@ -61,6 +62,7 @@ SIGNATURES = {
     "sdx_qsa_plan_release": ([p, p], i32),
     "sdx_decode_status": ([p], i32),
     "sdx_qsa_prompt": ([p, p, u64, u64, u64, u64, u64, f32, p, p], i32),
+    "sdx_qsa_attention_rows": ([p, p, u64, u64, p, u64, u64, u64, u64, f32, p, p, u64, p, u64, p], i32),
     "sdx_attention_batch": ([p, pp, pu64, pu64, u64, u64, u64, f32, p, p, p, p], i32),
 }
 

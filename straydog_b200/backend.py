@@ -232,6 +232,15 @@ class Backend:
         self._c(self.lib.sdx_qsa_prompt(self.handle, state.pointer if isinstance(state, Buffer) else state, context, first, rows, heads,
                                         kv_heads, scale, q, out))
 
+    def qsa_attention_rows(self, state, context, base, positions, steps, selected, heads, kv_heads, scale, packed, out, mirror=None,
+                           gates=None):
+        """sdx_qsa_attention_rows: the reference's qsa_attention / qsa_attention_rows over device pointers. positions: device pointer
+        or None; mirror: (pointer, rows) or None; gates: (pointer, row stride in floats) or None."""
+        m_ptr, m_rows = mirror if mirror else (None, 0)
+        g_ptr, g_stride = gates if gates else (None, 0)
+        self._c(self.lib.sdx_qsa_attention_rows(self.handle, state.pointer if isinstance(state, Buffer) else state, context, base, positions,
+                                                steps, selected, heads, kv_heads, scale, packed, m_ptr, m_rows, g_ptr, g_stride, out))
+
     def decode_status(self):
         return self._c(self.lib.sdx_decode_status(self.handle))
 

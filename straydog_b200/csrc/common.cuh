@@ -55,6 +55,7 @@ struct Device {
     bool turns_ready = false; size_t turns_ready_rows = 0, turns_ready_pairs = 0;
     void* kv_stage = nullptr; uint64_t kv_stage_rows = 0;
     uint64_t launches = 0;   // kernels launched through this handle (the benchmark's gpu_launches)
+    bool adopted = false;    // made by sdx_adopt over another library's stream and allocations: no range checks, nothing owned but workspaces
     explicit Device(int o) : ordinal(o) {}
 };
 
@@ -63,6 +64,7 @@ void* raw_allocate(Device& d, size_t bytes, bool zero);
 void raw_release(Device& d, void* pointer);
 void span(Device& d, const void* pointer, size_t bytes, const char* what);
 void span_or_peer(Device& d, const void* pointer, size_t bytes, const char* what);   // also accepts a mapped peer allocation
+size_t allocation_bytes(Device& d, const void* base);   // requested bytes of the allocation that starts at `base`, 0 if none (takes the lock)
 void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_host = false);
 int* status_word(Device& d);   // the device's word a kernel's bounded wait sets when it gives up (read by sdx_decode_status)
 

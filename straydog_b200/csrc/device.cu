@@ -51,6 +51,10 @@ void raw_release(Device& d, void* pointer) {
 
 // The range [pointer, pointer + bytes) lies inside one allocation of this device (gpu/ops.hpp:8-26).
 void span(Device& d, const void* pointer, size_t bytes, const char* what) {
+    if (d.adopted) {   // the adopting library has checked its own pointers (gpu/ops.hpp:8-26 runs before any kernel of its ops)
+        if (!pointer) throw std::runtime_error(std::string("Straydog op: ") + what + " is null");
+        return;
+    }
     const auto* at = static_cast<const uint8_t*>(pointer);
     std::lock_guard<std::mutex> lock(d.mutex);
     auto next = d.allocations.upper_bound(at);
@@ -72,6 +76,12 @@ void span_or_peer(Device& d, const void* pointer, size_t bytes, const char* what
         }
     }
     span(d, pointer, bytes, what);
+}
+
+size_t allocation_bytes(Device& d, const void* base) {
+    std::lock_guard<std::mutex> lock(d.mutex);
+    auto found = d.allocations.find(static_cast<const uint8_t*>(base));
+    return found == d.allocations.end() ? 0 : found->second;
 }
 
 // Library-owned workspaces (not in the allocation map: callers never see them), grown on demand.
@@ -126,6 +136,27 @@ void* sd_create(int ordinal, uint64_t budget) {
     } catch (const std::exception& e) { last_error = e.what(); return nullptr; }
 }
 
+// A handle over another library's device state: its stream (work is queued there, in order with that library's own kernels) and
+// its allocations (pointers are taken as that library checked them). For the reference's own build when it calls this library's
+// kernels from inside its spans (include/qsa_b200.hpp). Owns only this library's workspaces; sd_destroy frees those.
+void* sdx_adopt(int ordinal, void* stream) {
+    try {
+        int count = 0;
+        SDB_CHECK(cudaGetDeviceCount(&count));
+        if (ordinal < 0 || ordinal >= count) throw std::runtime_error("unknown Straydog device ordinal");
+        auto value = std::make_unique<Device>(ordinal);
+        SDB_CHECK(cudaSetDevice(ordinal));
+        cudaDeviceProp prop{};
+        SDB_CHECK(cudaGetDeviceProperties(&prop, ordinal));
+        if (prop.major != 10)
+            throw std::runtime_error(std::string("this Straydog build holds code for B200-class GPUs (sm_100a) only, not for ") + prop.name);
+        value->sms = prop.multiProcessorCount;
+        value->stream = static_cast<cudaStream_t>(stream);
+        value->adopted = true;
+        return value.release();
+    } catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
 void sd_destroy(void* handle) {
     if (!handle) return;
     auto* value = static_cast<Device*>(handle);
@@ -136,7 +167,7 @@ void sd_destroy(void* handle) {
         if (value->pinned) cudaFreeHost(value->pinned);
         if (value->append_pinned) cudaFreeHost(value->append_pinned);
         for (void* p : {value->work, value->partial, value->tables, value->append, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
-        cudaStreamDestroy(value->stream);
+        if (!value->adopted) cudaStreamDestroy(value->stream);
         cudaGetLastError();
     }
     delete value;
@@ -170,8 +201,7 @@ void* sd_upload(void* handle, const void* data, uint64_t bytes) {
 int sd_write(void* handle, void* pointer, const void* data, uint64_t bytes) {
     try {
         auto& value = device(handle);
-        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
-        if (!data || found == value.allocations.end() || found->second != bytes) throw std::runtime_error("invalid Straydog write");
+        if (!data || !bytes || allocation_bytes(value, pointer) != bytes) throw std::runtime_error("invalid Straydog write");
         copy_in(value, pointer, data, bytes);
         SDB_CHECK(cudaStreamSynchronize(value.stream));
         return 0;
@@ -190,9 +220,9 @@ int sd_release(void* handle, void* pointer) {
 int sd_allocation_bytes(void* handle, const void* pointer, uint64_t* bytes) {
     try {
         auto& value = device(handle);
-        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
-        if (!bytes || found == value.allocations.end()) throw std::runtime_error("unknown Straydog allocation");
-        *bytes = found->second + allocation_tail;
+        const size_t requested = allocation_bytes(value, pointer);
+        if (!bytes || !requested) throw std::runtime_error("unknown Straydog allocation");
+        *bytes = requested + allocation_tail;
         return 0;
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
 }
@@ -200,9 +230,9 @@ int sd_allocation_bytes(void* handle, const void* pointer, uint64_t* bytes) {
 int sd_zero(void* handle, void* pointer) {
     try {
         auto& value = device(handle);
-        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
-        if (found == value.allocations.end()) throw std::runtime_error("unknown Straydog state allocation");
-        SDB_CHECK(cudaMemsetAsync(pointer, 0, found->second, value.stream));
+        const size_t requested = allocation_bytes(value, pointer);
+        if (!requested) throw std::runtime_error("unknown Straydog state allocation");
+        SDB_CHECK(cudaMemsetAsync(pointer, 0, requested, value.stream));
         SDB_CHECK(cudaStreamSynchronize(value.stream));
         return 0;
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
@@ -211,8 +241,7 @@ int sd_zero(void* handle, void* pointer) {
 int sd_download(void* handle, void* pointer, void* output, uint64_t bytes) {
     try {
         auto& value = device(handle);
-        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
-        if (!output || found == value.allocations.end() || found->second != bytes)
+        if (!output || !bytes || allocation_bytes(value, pointer) != bytes)
             throw std::runtime_error("Straydog state readback size mismatch");
         SDB_CHECK(cudaMemcpyAsync(output, pointer, bytes, cudaMemcpyDeviceToHost, value.stream));
         SDB_CHECK(cudaStreamSynchronize(value.stream));
@@ -265,8 +294,7 @@ int sd_kv_format(void* handle, uint32_t row) {
 int sd_kv_stage(void* handle, void* pointer, uint64_t rows) {
     try {
         auto& value = device(handle);
-        auto found = value.allocations.find(static_cast<const uint8_t*>(pointer));
-        if (!rows || rows > (uint64_t(1) << 22) || found == value.allocations.end() || found->second != size_t(rows) * 1024 * 4)
+        if (!rows || rows > (uint64_t(1) << 22) || allocation_bytes(value, pointer) != size_t(rows) * 1024 * 4)
             throw std::runtime_error("invalid Straydog K/V stage");
         value.kv_stage = pointer;
         value.kv_stage_rows = rows;
@@ -341,6 +369,23 @@ void* sdx_ipc_open(void* handle, const void* in_handle, uint64_t bytes) {
         std::memcpy(&imported, in_handle, sizeof imported);
         void* pointer = nullptr;
         SDB_CHECK(cudaIpcOpenMemHandle(&pointer, imported, cudaIpcMemLazyEnablePeerAccess));
+        // the size the caller states must fit the range that was mapped: a kernel given this pointer stores into another GPU
+        size_t mapped = 0;
+        {
+            using Range = int (*)(unsigned long long*, size_t*, unsigned long long);
+            void* entry = nullptr;
+            cudaDriverEntryPointQueryResult found;
+            if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &entry, cudaEnableDefault, &found) == cudaSuccess && entry &&
+                found == cudaDriverEntryPointSuccess) {
+                unsigned long long base = 0;
+                if (reinterpret_cast<Range>(entry)(&base, &mapped, reinterpret_cast<unsigned long long>(pointer)) != 0) mapped = 0;
+                else mapped -= size_t(reinterpret_cast<unsigned long long>(pointer) - base);
+            }
+        }
+        if (mapped && bytes > mapped) {   // (a driver that cannot answer leaves the stated size as it is)
+            cudaIpcCloseMemHandle(pointer);
+            throw std::runtime_error("the mapped peer allocation is smaller than the size stated for it");
+        }
         std::lock_guard<std::mutex> lock(value.mutex);
         value.peers.emplace(static_cast<const uint8_t*>(pointer), size_t(bytes));
         return pointer;

@@ -1,18 +1,22 @@
 // Causal prompt attention over Q8_0 K/V on the 5th-generation tensor cores (tcgen05.mma, accumulators
 // and the A operands in TMEM): the Blackwell-native form of sdx_qsa_prompt.
 //
-// Before the attention kernel a small kernel turns the Q8_0 rows the chunk can see into FP16 rows
-// (value = FP16(int8 * scale), the rounding of the reference's own tensor-core kernel, gpu/kernels.cpp:46-54)
-// in a library-owned workspace that stays in L2 (33.5 MB for 16384 positions): every 64-key tile is then
-// dequantised once per call instead of once per 16-token block.
+// Before the attention kernel a small kernel turns the Q8_0 rows the chunk can see into two FP16 planes in a
+// library-owned workspace that stays in L2 (67 MB for 16384 positions): hi = FP16(int8 * scale), the rounding of the
+// reference's own tensor-core kernel (gpu/kernels.cpp:46-54), and lo = int8 * scale - hi, the part that rounding drops
+// (an int8 times an FP16 scale has at most 18 significant bits, so hi + lo is the value itself). Every product is issued
+// twice, once per plane, into the same FP32 accumulator: K and V enter the tensor cores exactly, as they enter the
+// reference's FP32 kernels (gpu/sparse_attention_compute.hpp:177-415), and only the softmax weights are rounded to FP16.
+// Every 64-key tile is dequantised once per call instead of once per 16-token block.
 //
 // A CTA owns 128 M-rows: 128 / group consecutive query tokens x the `group` query heads of one K/V head.
 // It walks the causal key range in tiles of 64 keys:
-//   S[128 x 64]  = Q[128 x 256] . K_tile^T      16 x tcgen05.mma (M 128, N 64, K 16), FP16 in, FP32 in TMEM
-//   O[128 x 256] += P[128 x 64] . V_tile         4 x tcgen05.mma (M 128, N 256, K 16)
+//   S[128 x 64]  = Q[128 x 256] . (K_hi + K_lo)^T   2 x 16 tcgen05.mma (M 128, N 64, K 16), FP16 in, FP32 in TMEM
+//   O[128 x 256] += P[128 x 64] . (V_hi + V_lo)     2 x 4 tcgen05.mma (M 128, N 256, K 16)
 // TMEM (all 512 columns): O in 0..255; two S buffers in 256..319 and 320..383; Q (FP16, two values a column) in
 // 384..511. P is written over the first 32 columns of the S buffer it was made from, so both products take their A
-// operand from TMEM and shared memory only holds K and V tiles.
+// operand from TMEM and shared memory only holds K and V tiles: one ring of six 32 KB slots that the copy thread fills
+// and the MMA thread drains in the same fixed order (K_hi, K_lo of tile i, then V_hi, V_lo of tile i - 1).
 //
 // Warp roles (10 warps):
 //   warps 0-7   softmax: two threads per M-row (32 of the tile's 64 columns each; warp w works on the TMEM lanes
@@ -21,14 +25,14 @@
 //               row's maximum has grown by more than 2^8 (the stale maximum stays exact arithmetic: weights are at
 //               most 256 and the final division uses the same maximum); epilogue O / l.
 //   warp 8      one thread issues every tcgen05.mma and commits them to mbarriers.
-//   warp 9      one thread feeds K and V tiles: tensor-map bulk copies (TMA, 128-byte swizzle) of four
-//               [64 rows][128 bytes] boxes per tile, which is the K-major / MN-major operand layout the MMA reads.
-// K and V tiles are double buffered, S is double buffered, so the tensor pipe works on S(i+1) while the
-// softmax warps work on S(i). Every wait is bounded; a wait that gives up raises a flag that ends all roles,
+//   warp 9      one thread feeds the ring: tensor-map bulk copies (TMA, 128-byte swizzle) of four
+//               [64 rows][128 bytes] boxes per slot, which is the K-major / MN-major operand layout the MMA reads.
+// S is double buffered, so the tensor pipe works on S(i+1) while the softmax warps work on S(i). Every wait is bounded; a wait that gives up raises a flag that ends all roles,
 // frees TMEM and reports through the status word.
 #include "common.cuh"
+#include "../../include/straydog_gpu_b200.h"
 
-#include <cstdlib>
+#include <algorithm>
 #include <cuda.h>   // CUtensorMap (the encode function is reached through cudaGetDriverEntryPoint: no link against the driver library)
 
 namespace sdb {
@@ -36,24 +40,24 @@ namespace tc {
 
 constexpr int kM = 128, kN = 64, kD = 256;
 constexpr int kSoftmaxWarps = 8, kMmaWarp = 8, kTmaWarp = 9, kThreads = 320;   // 8 softmax warps, the MMA warp, the copy warp
-constexpr int kQBytes = kM * kD * 2, kKVBytes = kN * kD * 2, kPBytes = kM * kN * 2;
-constexpr int kOffQ = 0, kOffK = kQBytes, kOffV = kOffK + 2 * kKVBytes, kOffP = kOffV + 2 * kKVBytes, kOffBars = kOffP + 2 * kPBytes;
-constexpr int kOffStats = kOffBars + 192;            // [2 halves][128 rows] floats exchanged between the two warps of a row block
+constexpr int kKVBytes = kN * kD * 2;               // one operand tile: 64 positions x 256 FP16
+constexpr int kSlots = 6;                            // the operand ring
+constexpr int kOffRing = 0, kOffBars = kOffRing + kSlots * kKVBytes;
+constexpr int kOffStats = kOffBars + 256;            // [2 halves][128 rows] floats exchanged between the two warps of a row block
 constexpr size_t kSmem = kOffStats + 2 * kM * 4 + 1024;   // + slack to align the base to 1024 bytes
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
 
 struct Args {
-    const uint8_t* keys;
-    const uint8_t* values;
-    size_t context, first, rows, heads, kv_heads, group;
+    size_t padded;      // positions a plane of the FP16 workspace holds (a multiple of 64)
+    size_t first, rows, heads, kv_heads, group;
     const __half* q;
     float* out;
     float scale_log2;
     int* status;
 };
 
-enum Bar { kKFull = 0, kKFree = 2, kVFull = 4, kVFree = 6, kSFull = 8, kSFree = 10, kPFull = 12, kPFree = 14, kPvDone = 16, kBars = 17 };
+enum Bar { kFull = 0, kFree = kSlots, kSFull = 2 * kSlots, kSFree = kSFull + 2, kPFull = kSFree + 2, kPvDone = kPFull + 2, kBars = kPvDone + 1 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
     // start address, leading and stride byte offsets in 16-byte units; descriptor version 1; 128-byte swizzle
@@ -116,24 +120,6 @@ __device__ __forceinline__ void tmem_st16_bits(uint32_t taddr, const uint32_t (&
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Sixteen consecutive Q8_0 values (16 raw bytes) of a block with FP16 scale `scale_h`, as two 16-byte pieces of FP16.
-__device__ __forceinline__ void dequant16(const uint4& bytes, __half scale_h, uint4& first, uint4& second) {
-    const __half2 scale2 = __halves2half2(scale_h, scale_h);
-    const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));   // 1152 = 1024 + 128
-    const uint32_t words[4] = {bytes.x ^ 0x80808080u, bytes.y ^ 0x80808080u, bytes.z ^ 0x80808080u, bytes.w ^ 0x80808080u};
-    uint32_t h[8];
-    #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        const uint32_t lo = prmt(words[w], 0x64646464u, 0x4140u), hi = prmt(words[w], 0x64646464u, 0x4342u);
-        const __half2 a0 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&lo), bias), scale2);
-        const __half2 a1 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&hi), bias), scale2);
-        h[2 * w] = *reinterpret_cast<const uint32_t*>(&a0);
-        h[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&a1);
-    }
-    first = make_uint4(h[0], h[1], h[2], h[3]);
-    second = make_uint4(h[4], h[5], h[6], h[7]);
-}
-
 __device__ __forceinline__ void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
 // K and V tiles come as FP16 from a pre-dequantised workspace by tensor-map bulk copies (128-byte swizzle).
@@ -153,8 +139,8 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
     const size_t r0 = block * tokens_per_block;
 
     if (tid == 0) {
-        const uint32_t counts[kBars] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, kSoftmaxWarps, kSoftmaxWarps, 1, 1, 1};   // (s_free: the product's commit)
-        for (int i = 0; i < kBars; ++i) mbar_init(&bars[i], counts[i]);
+        // (every barrier is completed by one arrival - a copy's byte count or an MMA commit - except p_full: one arrival per softmax warp)
+        for (int i = 0; i < kBars; ++i) mbar_init(&bars[i], i == kPFull || i == kPFull + 1 ? kSoftmaxWarps : 1);
         *abort_flag = 0;
     }
     fence_barrier_init();
@@ -189,10 +175,8 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
     tc_fence_after();
 
     const size_t last_row = min(a.rows, r0 + tokens_per_block) - 1;
-    const size_t keys_total = min(a.context, a.first + last_row + 1);
+    const size_t keys_total = a.first + last_row + 1;
     const uint32_t tiles = uint32_t((keys_total + kN - 1) / kN);
-    const uint8_t* key_plane = a.keys + kv * a.context * kv_row_q8;
-    const uint8_t* value_plane = a.values + kv * a.context * kv_row_q8;
 
     // a bounded wait that also ends when another role has given up
     auto wait = [&](int bar, uint32_t parity) -> bool {
@@ -229,15 +213,16 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             const long long begin = (long long)j * kN + half * 32;
             const bool edge = (long long)j * kN + kN - 1 > (long long)(a.first + r0) || (long long)j * kN + kN > (long long)keys_total;
             // (four independent maxima, then their maximum: one chain of 32 dependent fmnmx cost a third of the tile's softmax time)
+            // the scores stay unscaled: the scale (positive) is applied to the maximum once and folded into each exponent's argument
             float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            #pragma unroll
-            for (int n = 0; n < 32; ++n) {
-                float x = s[n] * a.scale_log2;
-                if (edge && begin + n > limit) x = -INFINITY;
-                s[n] = x;
-                tops[n & 3] = fmaxf(tops[n & 3], x);
+            if (edge) {
+                #pragma unroll
+                for (int n = 0; n < 32; ++n)
+                    if (begin + n > limit) s[n] = -INFINITY;
             }
-            const float top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
+            #pragma unroll
+            for (int n = 0; n < 32; ++n) tops[n & 3] = fmaxf(tops[n & 3], s[n]);
+            const float top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3])) * a.scale_log2;
             *mine_stat = top;
             pair_barrier(1 + rb);
             const float m_new = fmaxf(m_run, fmaxf(top, *other_stat));
@@ -271,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float p0 = fast_exp2(s[2 * i] - u), p1 = fast_exp2(s[2 * i + 1] - u);
+                const float p0 = fast_exp2(fmaf(s[2 * i], a.scale_log2, -u)), p1 = fast_exp2(fmaf(s[2 * i + 1], a.scale_log2, -u));
                 sums[i & 3] += p0 + p1;
                 packed[i] = pack_half2(p0, p1);
             }
@@ -303,61 +288,78 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
         }
     } else if (warp == kMmaWarp) {
         // ================= the MMA issuer =================
+        // The ring is drained in the order the copy thread fills it: item t sits in slot t % 6, in its (t / 6)-th use.
         if (lane == 0) {
-            const uint32_t k_base = smem_u32(smem + kOffK), v_base = smem_u32(smem + kOffV);
+            const uint32_t ring = smem_u32(smem + kOffRing);
             const uint32_t idesc_s = instr_desc(kM, kN, false), idesc_o = instr_desc(kM, kD, true);
+            uint32_t item = 0;
             bool alive = true;
             for (uint32_t i = 0; i <= tiles && alive; ++i) {
                 if (i < tiles) {
-                    const uint32_t slot = i & 1;
-                    if (!wait(kKFull + slot, (i >> 1) & 1)) break;
-                    if (i >= 2 && !wait(kSFree + slot, ((i - 2) >> 1) & 1)) break;
-                    tc_fence_after();
-                    #pragma unroll
-                    for (int kk = 0; kk < 16; ++kk) {
-                        const uint64_t b_desc = smem_desc(k_base + slot * kKVBytes + (kk / 4) * (kN * 128) + (kk % 4) * 32, 16, 1024);
-                        umma_a_tmem(tmem + 256 + slot * 64, tmem + 384 + kk * 8, b_desc, idesc_s, kk > 0);
+                    const uint32_t buffer = i & 1;
+                    if (i >= 2 && !wait(kSFree + buffer, ((i - 2) >> 1) & 1)) break;
+                    #pragma unroll 1
+                    for (int part = 0; part < 2 && alive; ++part, ++item) {   // K_hi, then K_lo into the same accumulator
+                        const uint32_t slot = item % kSlots;
+                        if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
+                        tc_fence_after();
+                        #pragma unroll
+                        for (int kk = 0; kk < 16; ++kk) {
+                            const uint64_t b_desc = smem_desc(ring + slot * kKVBytes + (kk / 4) * (kN * 128) + (kk % 4) * 32, 16, 1024);
+                            umma_a_tmem(tmem + 256 + buffer * 64, tmem + 384 + kk * 8, b_desc, idesc_s, part > 0 || kk > 0);
+                        }
+                        umma_commit(&bars[kFree + slot]);
                     }
-                    umma_commit(&bars[kSFull + slot]);
-                    umma_commit(&bars[kKFree + slot]);
+                    if (!alive) break;
+                    umma_commit(&bars[kSFull + buffer]);
                 }
                 if (i >= 1) {
-                    const uint32_t j = i - 1, slot = j & 1;
-                    if (!wait(kPFull + slot, (j >> 1) & 1)) break;
-                    if (!wait(kVFull + slot, (j >> 1) & 1)) break;
-                    tc_fence_after();
-                    #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint64_t b_desc = smem_desc(v_base + slot * kKVBytes + kk * (16 * 128), kN * 128, 1024);
-                        umma_a_tmem(tmem, tmem + 256 + slot * 64 + kk * 8, b_desc, idesc_o, j > 0 || kk > 0);
+                    const uint32_t j = i - 1, buffer = j & 1;
+                    if (!wait(kPFull + buffer, (j >> 1) & 1)) break;
+                    #pragma unroll 1
+                    for (int part = 0; part < 2 && alive; ++part, ++item) {   // V_hi, then V_lo
+                        const uint32_t slot = item % kSlots;
+                        if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
+                        tc_fence_after();
+                        #pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint64_t b_desc = smem_desc(ring + slot * kKVBytes + kk * (16 * 128), kN * 128, 1024);
+                            umma_a_tmem(tmem, tmem + 256 + buffer * 64 + kk * 8, b_desc, idesc_o, j > 0 || part > 0 || kk > 0);
+                        }
+                        umma_commit(&bars[kFree + slot]);
                     }
+                    if (!alive) break;
                     umma_commit(&bars[kPvDone]);
-                    umma_commit(&bars[kVFree + slot]);
-                    umma_commit(&bars[kSFree + slot]);   // P sat in the S buffer: free once the product has read it
+                    umma_commit(&bars[kSFree + buffer]);   // P sat in the S buffer: free once the product has read it
                 }
             }
         }
     } else {
         // ================= the copy thread: FP16 tiles by TMA =================
+        // Workspace rows: [hi | lo][plane][padded positions]; a tile never leaves its plane because `padded` is a multiple of 64.
         if (warp == kTmaWarp && lane == 0) {
-            const int32_t key_row0 = int32_t(kv * a.context), value_row0 = int32_t((a.kv_heads + kv) * a.context);
-            for (uint32_t i = 0; i < tiles; ++i) {
-                const uint32_t slot = i & 1;
-                const int32_t begin = int32_t(i * kN);
-                bool ok = true;
-                #pragma unroll
-                for (int plane = 0; plane < 2 && ok; ++plane) {
-                    if (i >= 2 && !wait((plane ? kVFree : kKFree) + slot, ((i - 2) >> 1) & 1)) { ok = false; break; }
-                    uint64_t* bar = &bars[(plane ? kVFull : kKFull) + slot];
-                    uint8_t* tile = smem + (plane ? kOffV : kOffK) + slot * kKVBytes;
+            const size_t planes = 2 * a.kv_heads;
+            uint32_t item = 0;
+            bool ok = true;
+            for (uint32_t i = 0; i <= tiles && ok; ++i) {
+                #pragma unroll 1
+                for (int which = 0; which < 4 && ok; ++which) {   // K_hi, K_lo of tile i; V_hi, V_lo of tile i - 1
+                    const bool value = which >= 2;
+                    if (value ? i == 0 : i == tiles) continue;
+                    const uint32_t tile_index = value ? i - 1 : i, part = which & 1;
+                    const size_t plane = value ? a.kv_heads + kv : kv;
+                    const int32_t row0 = int32_t((part * planes + plane) * a.padded + size_t(tile_index) * kN);
+                    const uint32_t slot = item % kSlots;
+                    if (item >= uint32_t(kSlots) && !wait(kFree + slot, (item / kSlots - 1) & 1)) { ok = false; break; }
+                    uint64_t* bar = &bars[kFull + slot];
+                    uint8_t* tile = smem + kOffRing + slot * kKVBytes;
                     mbar_expect_tx(bar, kKVBytes);
                     #pragma unroll
                     for (int d = 0; d < 4; ++d)   // four 64-column blocks of [64 rows][128 bytes]
                         asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                     ::"r"(smem_u32(tile + d * (kN * 128))), "l"(&kv_map), "r"(64 * d), "r"((plane ? value_row0 : key_row0) + begin),
-                                       "r"(smem_u32(bar)) : "memory");
+                                     ::"r"(smem_u32(tile + d * (kN * 128))), "l"(&kv_map), "r"(64 * d), "r"(row0), "r"(smem_u32(bar)) : "memory");
+                    ++item;
                 }
-                if (!ok) break;
             }
         }
     }
@@ -371,21 +373,42 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
 
 }  // namespace tc
 
-// Q8_0 rows -> FP16 rows [plane][position][256] (512 bytes a row), once per call: value = FP16(int8 * scale). Positions at or past
-// `valid` (up to `padded`, the last tile's end) are written as zeros, so a tile never holds bits nobody wrote.
+// Q8_0 rows -> two FP16 planes of rows [hi | lo][plane][position][256] (512 bytes a row), once per call: hi = FP16(int8 * scale),
+// lo = FP16(int8 * scale - hi) (the FP32 product is exact: 7 x 11 significant bits). Positions at or past `valid` (up to `padded`,
+// the last tile's end) are written as zeros, so a tile never holds bits nobody wrote.
 __global__ void __launch_bounds__(256) prompt_dequant_kernel(const uint8_t* __restrict__ state, size_t context, size_t planes, size_t valid,
                                                              size_t padded, __half* __restrict__ out) {
     const size_t pieces = planes * padded * 16;   // 16-byte raw pieces
+    const size_t lo_offset = planes * padded * 256;
     for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < pieces; i += size_t(gridDim.x) * blockDim.x) {
         const size_t piece = i % 16, position = (i / 16) % padded, plane = i / (16 * padded);
-        uint4 first = make_uint4(0, 0, 0, 0), second = first;
+        uint32_t hi[8] = {0, 0, 0, 0, 0, 0, 0, 0}, lo[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (position < valid) {
             const uint8_t* row = state + (plane * context + position) * kv_row_q8;
-            tc::dequant16(__ldg(reinterpret_cast<const uint4*>(row + piece * 16)), __ldg(reinterpret_cast<const __half*>(row + 256) + piece / 2), first, second);
+            const uint4 bytes = __ldg(reinterpret_cast<const uint4*>(row + piece * 16));
+            const float scale = __half2float(__ldg(reinterpret_cast<const __half*>(row + 256) + piece / 2));
+            const uint32_t words[4] = {bytes.x, bytes.y, bytes.z, bytes.w};
+            #pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                __half h[4], l[4];
+                #pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const float x = __fmul_rn(float(int8_t(words[w] >> (8 * b))), scale);
+                    h[b] = __float2half_rn(x);
+                    l[b] = __float2half_rn(__fsub_rn(x, __half2float(h[b])));
+                }
+                hi[2 * w] = uint32_t(__half_as_ushort(h[0])) | uint32_t(__half_as_ushort(h[1])) << 16;
+                hi[2 * w + 1] = uint32_t(__half_as_ushort(h[2])) | uint32_t(__half_as_ushort(h[3])) << 16;
+                lo[2 * w] = uint32_t(__half_as_ushort(l[0])) | uint32_t(__half_as_ushort(l[1])) << 16;
+                lo[2 * w + 1] = uint32_t(__half_as_ushort(l[2])) | uint32_t(__half_as_ushort(l[3])) << 16;
+            }
         }
-        uint4* target = reinterpret_cast<uint4*>(out + (plane * context + position) * 256 + piece * 16);
-        target[0] = first;
-        target[1] = second;
+        uint4* target = reinterpret_cast<uint4*>(out + (plane * padded + position) * 256 + piece * 16);
+        target[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        target[1] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+        uint4* low = reinterpret_cast<uint4*>(out + lo_offset + (plane * padded + position) * 256 + piece * 16);
+        low[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        low[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
     }
 }
 
@@ -404,12 +427,10 @@ static EncodeTiled encode_tiled() {
     return fn;
 }
 
-void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t first, size_t rows, size_t heads, size_t kv_heads,
-                      float scale, const void* q, float* out) {
+static void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t first, size_t rows, size_t heads, size_t kv_heads,
+                             float scale, const void* q, float* out) {
     tc::Args args{};
-    args.keys = state;
-    args.values = state + kv_heads * context * kv_row_q8;
-    args.context = context; args.first = first; args.rows = rows; args.heads = heads; args.kv_heads = kv_heads; args.group = heads / kv_heads;
+    args.first = first; args.rows = rows; args.heads = heads; args.kv_heads = kv_heads; args.group = heads / kv_heads;
     args.q = static_cast<const __half*>(q);
     args.out = out;
     args.scale_log2 = scale * 1.4426950408889634f;
@@ -422,16 +443,18 @@ void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t fi
         configured[d.ordinal & 63] = true;
     }
     CUtensorMap map{};
-    // FP16 copy of the positions this chunk can see (library-owned workspace, grown on the first call of a size; L2-sized for the
-    // benchmark's chunk: 16384 positions x 4 planes x 512 bytes = 33.5 MB), then tensor-map bulk copies feed the MMA tiles
+    // FP16 hi and lo copies of the positions this chunk can see, in a library-owned workspace that is grown on the first call of
+    // a size and sits outside the handle's budget (16384 positions x 4 planes x 2 x 512 bytes = 67 MB for the benchmark's chunk:
+    // L2-sized). Its extent follows the positions the chunk sees, rounded up to whole tiles, not the state's context.
     const size_t planes = 2 * kv_heads, valid = first + rows;
-    const size_t padded = std::min(context, (valid + tc::kN - 1) / tc::kN * tc::kN);
-    auto* fp16 = static_cast<__half*>(ensure(d, d.work, d.work_bytes, planes * context * 512));
+    const size_t padded = (valid + tc::kN - 1) / tc::kN * tc::kN;
+    args.padded = padded;
+    auto* fp16 = static_cast<__half*>(ensure(d, d.work, d.work_bytes, 2 * planes * padded * 512));
     const unsigned blocks = unsigned(std::min<size_t>((planes * padded * 16 + 255) / 256, size_t(d.sms) * 16));
     prompt_dequant_kernel<<<blocks, 256, 0, d.stream>>>(state, context, planes, valid, padded, fp16);
     ++d.launches;
     SDB_CHECK(cudaGetLastError());
-    const cuuint64_t dims[2] = {256, cuuint64_t(planes * context)};
+    const cuuint64_t dims[2] = {256, cuuint64_t(2 * planes * padded)};
     const cuuint64_t strides[1] = {512};
     const cuuint32_t box[2] = {64, cuuint32_t(tc::kN)}, element_strides[2] = {1, 1};
     const CUresult encoded = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, fp16, dims, strides, box, element_strides,
@@ -443,3 +466,27 @@ void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t fi
 }
 
 }  // namespace sdb
+
+using namespace sdb;
+
+// Causal prompt attention over a Q8_0 K/V state: a chunk of `rows` new tokens at positions first .. first + rows - 1 attends every
+// cached position up to its own. What it replaces in the reference: qsa_flash / qsa_flash_wide (FP32,
+// gpu/sparse_attention_compute.hpp:177-415) and qsa_flash_mma (mma.sync per token, :416-584) behind qsa_flash_launch (:589-608), in
+// their dense causal form. The reference walks one token per block, so sixteen neighbouring tokens that share almost all their
+// keys each read and dequantise them again; here a CTA takes 128 / group consecutive tokens for all the query heads of one K/V head.
+extern "C" int sdx_qsa_prompt(void* handle, const void* state, uint64_t context, uint64_t first, uint64_t rows, uint64_t heads,
+                              uint64_t kv_heads, float scale, const void* q, float* out) {
+    SDB_OP_BEGIN
+    if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
+    const uint64_t group = kv_heads ? heads / kv_heads : 0;
+    if (!context || context > (uint64_t(1) << 24) || !rows || first > context || rows > context - first || !heads || !kv_heads ||
+        heads % kv_heads || (group != 1 && group != 2 && group != 4 && group != 8) || kv_heads > 65535 || !(scale > 0.0f) || !(scale < 1e30f))
+        throw std::runtime_error("invalid Straydog attention dimensions");
+    span(value, state, checked_product({context, 2 * kv_heads, kv_row_q8}), "a K/V state");
+    span(value, q, checked_product({rows, heads, 256, 2}), "attention queries");
+    span(value, out, checked_product({rows, heads, 256, 4}), "an attention output");
+    if (reinterpret_cast<uintptr_t>(state) % 16 || reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(out) % 8)
+        throw std::runtime_error("Straydog prompt attention operands must be 16-byte aligned");
+    launch_prompt_tc(value, static_cast<const uint8_t*>(state), context, first, rows, heads, kv_heads, scale, q, out);
+    SDB_OP_END
+}

@@ -137,8 +137,7 @@ int sd_attention_sequence(void* handle, void* state, uint64_t context, uint64_t 
             steps > context - base || !selected || selected > kMaxSelected)
             throw std::runtime_error("invalid Straydog attention dimensions");
         if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
-        auto found = value.allocations.find(static_cast<const uint8_t*>(state));
-        if (found == value.allocations.end() || found->second != context * 4 * value.kv_row)
+        if (allocation_bytes(value, state) != context * 4 * value.kv_row)
             throw std::runtime_error("Straydog attention state size mismatch");
         if (input_count != steps * (heads * 256 + kv_heads * 512 + selected + 1) || output_count != steps * heads * 256)
             throw std::runtime_error("Straydog attention workspace mismatch");

@@ -22,6 +22,18 @@ def compile_program():
     return PROGRAM
 
 
+def test_the_seam_header_instantiates_with_the_references_call_shapes():
+    # include/qsa_b200.hpp: qsa_attention<P> / qsa_attention_rows<P> with the reference's signatures, over stand-in declarations
+    from straydog_b200 import build
+    library_dir = os.path.dirname(build.build())
+    os.makedirs(BUILD, exist_ok=True)
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    done = subprocess.run(["g++", "-std=c++17", "-O1", "-Wall", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp", "seam_compile.cpp"),
+                           "-o", os.path.join(BUILD, "seam_compile"), "-L", library_dir, "-lstraydog_gpu_b200", f"-Wl,-rpath,{library_dir}",
+                           f"-Wl,-rpath-link,{cuda}/lib64"], capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
+
+
 def test_the_cpp_mirror_compiles_and_links():
     assert os.path.exists(compile_program())
 
