@@ -119,12 +119,26 @@ int sdx_qsa_plan_run(void* handle, void* plan, float scale, const void* q, float
 int sdx_qsa_plan_run_marked(void* handle, void* plan, float scale, const void* q, float* out, void* before, void* after);
 int sdx_qsa_plan_info(void* plan, uint64_t* kv_bytes, uint64_t* pieces, uint64_t* ctas, uint64_t* virtual_warps);
 int sdx_qsa_plan_release(void* handle, void* plan);
+/* How the batched decode entries of this handle (sdx_qsa_decode, sdx_qsa_plan, sdx_attention_batch) cut a batch into pieces.
+   fixed = 0 (the default), moving cuts: the batch's 16-key tiles laid end to end and cut into equal runs, one per warp: the fewest
+   partials and an even load whatever the batch, but where a sequence is cut depends on its batch, so its result is the same
+   value to FP32 rounding, not bit for bit. fixed = 1: a sequence is cut at places that depend on its own length only (chunks of
+   512 keys and a halving tail, 128 keys for sequences under 8192) and its chunks are merged in order: the same bits in any batch,
+   at the cost of more partials and of an uneven load when a batch is small. (The reference's own bit-for-bit contract, verification
+   rows = one-token decodes, is the selection-list entry's, sdx_qsa_attention_rows, which keeps it always.) */
+int sdx_decode_cuts(void* handle, int fixed);
+/* The cuts of a batch for `warps` warps, without a device (host arithmetic): fixed as above. Returns the number of pieces of sequence `probe`'s first K/V head and writes where they begin to begins[0 ..
+   capacity); stats (or null) = {pieces in all, warps used, most 16-key tiles a warp got, tiles in all}. */
+int sdx_qsa_cuts(const uint64_t* lengths, uint64_t sequences, uint64_t kv_heads, uint64_t warps, int fixed, uint64_t probe,
+                 uint32_t* begins, uint64_t capacity, uint64_t* stats);
 /* No counterpart in the reference. sdx_qsa_decode for hosts that may not allocate once they serve (an engine
    whose VRAM budget is fully handed out, a loop that forbids driver allocations because they stall the
    device): the work list and the split partials live in a 16.3 MiB array inside the library's device image,
    held by every GPU that loads the library until exit. Limits: at most 64 sequences, 8 K/V heads and 2048
    work-list pieces a call; a larger batch is refused with an error, nothing is truncated. The first call on a
-   device looks up the array's device address (make that call before any stream capture). Calls share the
+   device looks up the array's device address and, under the CUDA runtime's default lazy loading, is also when the GPU takes the
+   library's device image with the array in it: make that call at start-up (before any stream capture); it is every later call
+   that touches no allocator. Calls share the
    array: two calls that overlap on the GPU, from any handles or threads, race; the call returns after its
    result is complete. It calls no cudaMalloc, cudaFree or allocating library routine. */
 int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
@@ -156,9 +170,13 @@ int sdx_sparse_attention_spans(void* handle, const float* q, const float* raw, u
    pipeline stage, not by head). Rank `rank` of `world` (<= 8) GPUs of one node computes this call's `heads` heads (its share) over
    the whole latent cache; every GPU keeps a gathered buffer [world][rows][heads][dim] F32 (rank-major). The call stores this rank's
    outputs into slot `rank` of EVERY GPU's buffer (outs[peer]: this handle's own allocation for peer == rank, mappings made by
-   sdx_ipc_open for the others: plain stores over NVLink from the kernel's merge), then raises counter `rank` in every GPU's
-   `flags[peer]` (int32 [world], zeroed once) to `step` and waits on the stream, bounded to a second, until its own counters all
-   show `step`: work queued behind the call sees the whole gathered buffer. `step` grows by one per call. */
+   sdx_ipc_open for the others: plain stores over NVLink from the kernel's merge); the last CTA of the kernel then raises counter
+   `rank` in every GPU's `flags[peer]` (int32 [world], zeroed once) to `step` and waits, bounded to a second, until its own
+   counters all show `step`: work queued behind the call sees the whole gathered buffer. `step` grows by one per call.
+   The caller keeps TWO gathered buffers per GPU and passes them in turn (step odd / even): a rank may run one call ahead of
+   its peers, never two (it cannot leave call n + 1 before every peer has entered its own call n + 1, which the peer's stream
+   orders behind the peer's readers of call n), so with two buffers a store never lands in a buffer a peer still reads; with one
+   buffer it could. */
 int sdx_sparse_attention_gather(void* handle, const float* q, const float* raw, uint64_t raw_rows, const int32_t* positions,
                                 uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
                                 uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,

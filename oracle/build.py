@@ -18,11 +18,12 @@ def build(force: bool = False) -> str:
 
 
 def build_reference() -> str | None:
-    """The reference's own GPU library for sm_100a (oracle/_ref/libstraydog_ref.so), when its sources are present."""
-    ref = os.environ.get("STRAYDOG_REFERENCE", "/root/reference")
+    """The reference's own GPU library for sm_100a (oracle/_ref/libstraydog_ref.so), when its sources are present: the checkout
+    STRAYDOG_REFERENCE names, else a `reference` directory beside this repository."""
     out = os.path.join(HERE, "_ref", "libstraydog_ref.so")
     if os.path.exists(out):
         return out
+    ref = os.environ.get("STRAYDOG_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     if not os.path.isdir(os.path.join(ref, "gpu")):
         return None
     subprocess.run(["make", "-f", os.path.join(HERE, "Makefile.ref"), f"REF={ref}", "-j5"], check=True, cwd=os.path.dirname(HERE))

@@ -204,6 +204,10 @@ class Backend:
         lens = (C.c_uint64 * n)(*lengths)
         self._c(self.lib.sdx_qsa_decode_static(self.handle, ptrs, ctx, lens, n, heads, kv_heads, scale, q, out))
 
+    def decode_cuts(self, fixed):
+        """sdx_decode_cuts: fixed cuts (a sequence's bits do not depend on its batch) or the default moving cuts."""
+        self._c(self.lib.sdx_decode_cuts(self.handle, int(bool(fixed))))
+
     def qsa_plan(self, states, contexts, lengths, heads, kv_heads):
         n = len(states)
         ptrs = (C.c_void_p * n)(*[s.pointer if isinstance(s, Buffer) else s for s in states])

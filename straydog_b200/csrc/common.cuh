@@ -35,6 +35,14 @@ inline void check_at(cudaError_t error, const char* file, int line) {
 
 struct DecodePlan;
 
+// One (sequence, K/V head) of a decode batch: the work list's unit, also what a batched K/V append addresses.
+struct Segment {
+    const uint8_t* keys;    // plane base
+    const uint8_t* values;
+    uint32_t q_offset;      // (sequence * heads + kv_head * group) * 256, in query elements
+    uint32_t first_piece, pieces, length;
+};
+
 struct Device {
     int ordinal = 0;
     int sms = 0;
@@ -49,8 +57,7 @@ struct Device {
     void* work = nullptr; size_t work_bytes = 0;        // packed inputs / outputs of host-pointer entries
     void* partial = nullptr; size_t partial_bytes = 0;  // split partials of the decode kernels
     void* tables = nullptr; size_t tables_bytes = 0;    // work lists of the decode kernels
-    void* append = nullptr; size_t append_bytes = 0;    // plane table of a batched K/V append
-    void* append_pinned = nullptr; size_t append_pinned_bytes = 0;
+    bool fixed_cuts = false;                            // the decode work list's cuts (sdx_decode_cuts)
     double* turns = nullptr; size_t turns_rows = 0, turns_pairs = 0;   // rope sincos table (forward, inverse)
     bool turns_ready = false; size_t turns_ready_rows = 0, turns_ready_pairs = 0;
     void* kv_stage = nullptr; uint64_t kv_stage_rows = 0;

@@ -165,8 +165,7 @@ void sd_destroy(void* handle) {
         for (auto& entry : value->peers) cudaIpcCloseMemHandle(const_cast<uint8_t*>(entry.first));
         for (auto& entry : value->allocations) cudaFree(const_cast<uint8_t*>(entry.first));
         if (value->pinned) cudaFreeHost(value->pinned);
-        if (value->append_pinned) cudaFreeHost(value->append_pinned);
-        for (void* p : {value->work, value->partial, value->tables, value->append, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
+        for (void* p : {value->work, value->partial, value->tables, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
         if (!value->adopted) cudaStreamDestroy(value->stream);
         cudaGetLastError();
     }

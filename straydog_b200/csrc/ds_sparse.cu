@@ -5,9 +5,9 @@
 // Reference: gpu/kernels.cpp:5311-5476 (entry, validation), gpu/ops.hpp:1203-1235 (BF16-tagged rows),
 // :1240-1297 (definition), :1309-1327 (key order, rope table), :1528-1538 (inverse rope), :1561-1583 (sink).
 //
-// This file holds the entry, the rope table, the query preparation and the FP32 CUDA-core kernel
-// (exact FP32 products for any operand values); ds_sparse_mma.cu holds the tensor-core kernel the
-// entry prefers when the shape allows it.
+// This file holds the entries, the rope table and the FP32 CUDA-core kernel (exact FP32 products for any
+// operand values and any dim); ds_sparse_mma3.cu holds the tensor-core kernel the entries prefer when the
+// shape allows it (dim 512 or 576).
 #include "common.cuh"
 #include "ds_sparse.cuh"
 #include "../../include/straydog_gpu_b200.h"
@@ -31,45 +31,21 @@ __global__ void sparse_turns_kernel(const int32_t* __restrict__ positions, const
     }
 }
 
-// q with its last 2 * pairs columns rotated in adjacent pairs (double arithmetic, rounded to F32:
-// gpu/ops.hpp:1366-1377), as F32 and, for the tensor-core kernel, split into BF16 high and low parts
-// (q = hi + lo up to 2^-17 relative). exact_flag is cleared when any low part is non-zero outside the
-// rotated columns.
-__global__ void __launch_bounds__(128) sparse_prepare_q_kernel(const float* __restrict__ q, size_t heads, size_t dim, size_t pairs,
-                                                               const double2* __restrict__ forward, float* __restrict__ rotated_q,
-                                                               __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
-                                                               int* __restrict__ inexact) {
-    // block = (head, row); a thread takes adjacent column pairs (a rope pair never straddles two threads: dim and rope_dims are even)
+// q with its last 2 * pairs columns rotated in adjacent pairs (double arithmetic, rounded to F32: gpu/ops.hpp:1366-1377), for the
+// FP32 kernel (the tensor-core kernel rotates its own queries).
+__global__ void __launch_bounds__(128) sparse_rotate_q_kernel(const float* __restrict__ q, size_t heads, size_t dim, size_t pairs,
+                                                              const double2* __restrict__ forward, float* __restrict__ rotated_q) {
+    // block = (head, row); a thread takes adjacent column pairs (a rope pair never straddles two threads: dim - 2 * pairs columns come first)
     const size_t head = blockIdx.x, row = blockIdx.y, plain = dim - 2 * pairs;
     const size_t base = (row * heads + head) * dim;
-    bool any = false;
-    for (size_t col = 2 * threadIdx.x; col + 1 < dim; col += 2 * blockDim.x) {
-        float2 v = make_float2(q[base + col], q[base + col + 1]);   // (the caller's q is only known to be 4-byte aligned)
-        if (col >= plain) {
-            const double2 g = forward[row * pairs + (col - plain) / 2];
-            const double a = v.x, b = v.y;
-            v = make_float2(float(a * g.x - b * g.y), float(a * g.y + b * g.x));
-        }
-        if (rotated_q) { rotated_q[base + col] = v.x; rotated_q[base + col + 1] = v.y; }
-        if (hi) {
-            const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
-            const float r0 = v.x - __bfloat162float(h0), r1 = v.y - __bfloat162float(h1);
-            *reinterpret_cast<__nv_bfloat162*>(hi + base + col) = __halves2bfloat162(h0, h1);
-            *reinterpret_cast<__nv_bfloat162*>(lo + base + col) = __halves2bfloat162(__float2bfloat16_rn(r0), __float2bfloat16_rn(r1));
-            if (col < plain && (r0 != 0.0f || r1 != 0.0f)) any = true;
-        }
+    for (size_t col = threadIdx.x; col < plain; col += blockDim.x) rotated_q[base + col] = q[base + col];
+    for (size_t pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+        const size_t col = plain + 2 * pair;
+        const double2 g = forward[row * pairs + pair];
+        const double a = q[base + col], b = q[base + col + 1];
+        rotated_q[base + col] = float(a * g.x - b * g.y);
+        rotated_q[base + col + 1] = float(a * g.y + b * g.x);
     }
-    if (dim % 2 && threadIdx.x == 0) {   // an odd last column (never rotated: rope_dims is even)
-        const float v = q[base + dim - 1];
-        if (rotated_q) rotated_q[base + dim - 1] = v;
-        if (hi) {
-            const __nv_bfloat16 h = __float2bfloat16_rn(v);
-            hi[base + dim - 1] = h;
-            lo[base + dim - 1] = __float2bfloat16_rn(v - __bfloat162float(h));
-            if (v != __bfloat162float(h)) any = true;
-        }
-    }
-    if (inexact && __syncthreads_or(any) && threadIdx.x == 0) atomicExch(inexact, 1);
 }
 
 // ---- FP32 kernel: block = (row, group of 4 heads, split); a warp per key ----
@@ -162,10 +138,9 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sparse_simt_kernel(const Spar
 
 // The splits of a (row, head) combined with the head's sink (in the max and the denominator,
 // gpu/ops.hpp:1561-1583), divided, and the rotated columns turned back (gpu/ops.hpp:1528-1538).
-// `log2_domain`: the partial maxima are in the exp2 domain (the tensor-core kernel's), the sink then scaled to it.
 __global__ void __launch_bounds__(128) sparse_combine_kernel(const float* __restrict__ partial, size_t splits, size_t heads, size_t dim,
                                                              const float* __restrict__ sinks, size_t pairs, const double2* __restrict__ inverse,
-                                                             int log2_domain, float* __restrict__ out) {
+                                                             float* __restrict__ out) {
     const size_t item = blockIdx.x, row = item / heads, head = item % heads, plain = dim - 2 * pairs;
     const float* first = partial + item * splits * (dim + 2);
     constexpr int kMaxSplits = 64;
@@ -173,8 +148,7 @@ __global__ void __launch_bounds__(128) sparse_combine_kernel(const float* __rest
     __shared__ float denominator_shared;
     if (threadIdx.x < 32) {
         // the first warp: the head's maximum (with its sink), every split's factor and the denominator
-        const float unit = log2_domain ? 1.4426950408889634f : 1.0f;
-        const float sink = sinks[head] * unit;
+        const float sink = sinks[head];
         float tops[kMaxSplits / 32], sums[kMaxSplits / 32], top = sink;
         #pragma unroll
         for (int i = 0; i < kMaxSplits / 32; ++i) {
@@ -189,14 +163,14 @@ __global__ void __launch_bounds__(128) sparse_combine_kernel(const float* __rest
         #pragma unroll
         for (int i = 0; i < kMaxSplits / 32; ++i) {
             const size_t s = threadIdx.x + 32 * i;
-            const float factor = tops[i] == -INFINITY ? 0.0f : (log2_domain ? exp2f(tops[i] - top) : expf(tops[i] - top));
+            const float factor = tops[i] == -INFINITY ? 0.0f : expf(tops[i] - top);
             if (s < splits) factors[s] = factor;
             denominator += factor * sums[i];
         }
         #pragma unroll
         for (unsigned offset = 16; offset; offset /= 2) denominator += __shfl_xor_sync(0xffffffffu, denominator, offset);
         // (a sink of -inf adds 0; top is finite whenever any key or the sink is)
-        if (threadIdx.x == 0) denominator_shared = denominator + (log2_domain ? exp2f(sink - top) : expf(sink - top));
+        if (threadIdx.x == 0) denominator_shared = denominator + expf(sink - top);
     }
     __syncthreads();
     const float denominator = denominator_shared;
@@ -235,6 +209,13 @@ static void turns_reserve(Device& d, size_t rows, size_t pairs) {
     d.turns = nullptr;
     SDB_CHECK(cudaMalloc(reinterpret_cast<void**>(&d.turns), rows * pairs * 2 * sizeof(double2)));
     d.turns_rows = rows; d.turns_pairs = pairs;
+}
+
+// The tensor-core kernel holds dim 512 and 576 and needs 16-byte aligned BF16 rows (whole rows travel by bulk copies).
+bool sparse_mma_supported(const SparseArgs& a) {
+    if (a.dim != 512 && a.dim != 576) return false;
+    if (a.selections && state_is_bf16(a.compressed) && reinterpret_cast<uintptr_t>(state_halves(a.compressed)) % 16) return false;
+    return true;
 }
 
 static bool env_flag(const char* name) {
@@ -318,13 +299,7 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
     }
     const bool force_simt = env_flag("SDX_SPARSE_SIMT");
     if (!force_simt && sparse_mma_supported(args)) {
-        // (SDX_SPARSE_KERNEL=v1|v2|v3 picks a form of the tensor-core kernel for A/B runs; the third, sixteen compute warps over one
-        //  head tile of 16 with the merge inside a thread-block cluster, is the default: it is the fastest at every head count measured)
-        const char* form = std::getenv("SDX_SPARSE_KERNEL");
-        const char which = form && form[0] == 'v' && form[1] && !form[2] ? form[1] : '3';
-        if (which == '1') sparse_mma_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
-        else if (which == '3') sparse_mma3_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
-        else sparse_mma2_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        sparse_mma3_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         SDB_CHECK(cudaGetLastError());
         return 0;
     }
@@ -340,7 +315,7 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
     const float* q_used = q;
     if (pairs) {
         auto* rotated = reinterpret_cast<float*>(work);
-        sparse_prepare_q_kernel<<<dim3(unsigned(heads), unsigned(rows)), 128, 0, value.stream>>>(q, heads, dim, pairs, forward, rotated, nullptr, nullptr, nullptr);
+        sparse_rotate_q_kernel<<<dim3(unsigned(heads), unsigned(rows)), 128, 0, value.stream>>>(q, heads, dim, pairs, forward, rotated);
         ++value.launches;
         q_used = rotated;
     }
@@ -356,7 +331,7 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
     #undef SDB_SIMT
     ++value.launches;
     SDB_CHECK(cudaGetLastError());
-    sparse_combine_kernel<<<unsigned(rows * heads), 128, 0, value.stream>>>(partial, splits, heads, dim, sinks, pairs, inverse, 0, out);
+    sparse_combine_kernel<<<unsigned(rows * heads), 128, 0, value.stream>>>(partial, splits, heads, dim, sinks, pairs, inverse, out);
     ++value.launches;
     SDB_OP_END
 }

@@ -25,6 +25,7 @@ struct GatherTargets {
     int* flags[kMaxGatherWorld];     // every rank's arrival counters [world]
     uint32_t world, rank;            // world == 0: no gather, plain `out`
     int32_t step;                    // value a rank's counter takes when its outputs of this call have been stored
+    unsigned* arrivals;              // this GPU's count of the grid's finished CTAs (zero at rest: the last CTA wraps it)
 };
 
 __host__ __device__ inline bool state_is_bf16(const void* p) { return reinterpret_cast<uintptr_t>(p) & 1u; }
@@ -57,19 +58,7 @@ __device__ __forceinline__ const float* key_pointer(const SparseArgs& a, const K
 #endif
 
 bool sparse_mma_supported(const SparseArgs& a);
-void sparse_mma_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
-                       const double2* forward, const double2* inverse, float* out);
-
-void sparse_mma2_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
-                        const double2* forward, const double2* inverse, float* out);
-
 void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
                         const double2* forward, const double2* inverse, float* out, const GatherTargets* gather = nullptr);
-
-// kernels of ds_sparse.cu the tensor-core path reuses
-__global__ void sparse_prepare_q_kernel(const float* q, size_t heads, size_t dim, size_t pairs, const double2* forward, float* rotated_q,
-                                        __nv_bfloat16* hi, __nv_bfloat16* lo, int* inexact);
-__global__ void sparse_combine_kernel(const float* partial, size_t splits, size_t heads, size_t dim, const float* sinks, size_t pairs,
-                                      const double2* inverse, int log2_domain, float* out);
 
 }  // namespace sdb

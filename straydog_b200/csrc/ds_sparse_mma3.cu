@@ -622,29 +622,36 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
         }
     }
     cluster_arrive(); cluster_wait();   // (nobody leaves while its partial may still be read)
+    if (gather.world > 1) {
+        // The gathered form's hand-over, by the last CTA of the grid to finish: every thread's peer stores are ordered before its
+        // CTA's arrival, the arrivals before the counters this rank raises on every GPU (release, system scope); then the same
+        // thread waits, bounded to a second, until every rank has raised this GPU's counters to `step`: work queued behind this
+        // kernel sees the whole gathered buffer. A rank that never arrives ends the wait with status 4 instead of hanging the GPU.
+        __threadfence_system();
+        asm volatile("bar.sync 3, %0;" ::"n"(kComputeThreads) : "memory");
+        if (threadIdx.x == 0) {
+            const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+            if (atomicInc(gather.arrivals, total - 1) == total - 1) {   // (wraps to zero: ready for the next call)
+                __threadfence_system();
+                for (uint32_t peer = 0; peer < gather.world; ++peer)
+                    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(gather.flags[peer] + gather.rank), "r"(gather.step) : "memory");
+                const uint64_t start = global_timer_ns();
+                for (uint32_t peer = 0; peer < gather.world; ++peer) {
+                    const int* mine = gather.flags[gather.rank] + peer;
+                    for (;;) {
+                        int seen;
+                        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                        if (seen - gather.step >= 0) break;   // (counters only grow; the difference survives a wrap)
+                        if (global_timer_ns() - start > 1000000000ull) { atomicExch(status, 4); peer = gather.world; break; }
+                        __nanosleep(100);
+                    }
+                }
+            }
+        }
+    }
 }
 
 }  // namespace v3
-
-// After a rank's attention kernel: tell every GPU that this rank's slot of its gathered copy is written, then wait until every
-// rank has told this GPU the same. The attention kernel's peer stores are complete when this kernel starts (same stream); the
-// fence and the release store order them before the counter for a reader on another GPU. The wait is bounded: a rank that never
-// arrives ends it after a second with status 4 instead of hanging the GPU.
-__global__ void gather_signal_wait_kernel(const GatherTargets gather, int* __restrict__ status) {
-    const uint32_t peer = threadIdx.x;
-    if (peer >= gather.world) return;
-    __threadfence_system();
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(gather.flags[peer] + gather.rank), "r"(gather.step) : "memory");
-    const int* mine = gather.flags[gather.rank] + peer;
-    const uint64_t start = global_timer_ns();
-    for (;;) {
-        int seen;
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-        if (seen - gather.step >= 0) break;   // (counters only grow; the difference survives a wrap)
-        if (global_timer_ns() - start > 1000000000ull) { atomicExch(status, 4); break; }
-        __nanosleep(200);
-    }
-}
 
 template<int DIM>
 static void launch_v3(Device& d, const SparseArgs& a, const float* q, size_t pairs, const double2* forward, size_t rows, size_t splits,
@@ -697,15 +704,10 @@ void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const fl
     while (splits * 2 <= std::min<size_t>({room, useful, size_t(8)})) splits *= 2;
     int* status = status_word(d);
     GatherTargets targets{};
-    if (gather) targets = *gather;
+    if (gather) { targets = *gather; targets.arrivals = reinterpret_cast<unsigned*>(status) + 16; }   // (a word of the status block, zero at rest)
     if (a.dim == 576) launch_v3<576>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out, targets);
     else launch_v3<512>(d, a, q, pairs, forward, rows, splits, status, sinks, inverse, out, targets);
     SDB_CHECK(cudaGetLastError());
-    if (targets.world > 1) {
-        gather_signal_wait_kernel<<<1, 32, 0, d.stream>>>(targets, status);
-        ++d.launches;
-        SDB_CHECK(cudaGetLastError());
-    }
 }
 
 }  // namespace sdb

@@ -11,6 +11,19 @@
 
 namespace sdb {
 
+// kv_encode (gpu/kernels.cpp:58-69) for one 32-value block held by a warp, a value a lane: the block's scale is
+// FP16(max |v| / 127), a value is v / scale rounded to nearest even and clamped to +-127, 0 under a zero scale.
+__device__ __forceinline__ int8_t q8_encode(float value, __half& scale_h) {
+    float top = fabsf(value);
+    #pragma unroll
+    for (unsigned offset = 16; offset; offset /= 2) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
+    scale_h = __float2half_rn(__fdiv_rn(top, 127.0f));
+    const float scale = __half2float(scale_h);
+    int q = scale > 0.0f ? __float2int_rn(__fdiv_rn(value, scale)) : 0;
+    q = q > 127 ? 127 : q < -127 ? -127 : q;
+    return int8_t(q);
+}
+
 // One warp encodes one 32-value block: lane = column % 32. Grid-stride over blocks so that any
 // number of rows runs in one launch sized to the SM count.
 __global__ void __launch_bounds__(256) kv_write_kernel(uint8_t* __restrict__ state, size_t context, size_t kv_heads, size_t base,
@@ -24,16 +37,28 @@ __global__ void __launch_bounds__(256) kv_write_kernel(uint8_t* __restrict__ sta
         const bool is_value = block >= blocks / 2;
         const size_t index = (is_value ? block - blocks / 2 : block) * 32 + lane;   // into [steps][kv_heads][256]
         const size_t step = index / width, head = (index % width) / 256, column = index % 256;
-        const float value = (is_value ? values : keys)[index];
-        float top = fabsf(value);
-        #pragma unroll
-        for (unsigned offset = 16; offset; offset /= 2) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
-        const __half scale_h = __float2half_rn(__fdiv_rn(top, 127.0f));
-        const float scale = __half2float(scale_h);
-        int q = scale > 0.0f ? __float2int_rn(__fdiv_rn(value, scale)) : 0;
-        q = q > 127 ? 127 : q < -127 ? -127 : q;
+        __half scale_h;
+        const int8_t q = q8_encode((is_value ? values : keys)[index], scale_h);
         uint8_t* row = state + (((is_value ? kv_heads : 0) + head) * context + base + step) * kv_row_q8;
-        reinterpret_cast<int8_t*>(row)[column] = int8_t(q);
+        reinterpret_cast<int8_t*>(row)[column] = q;
+        if (lane == 0) reinterpret_cast<__half*>(row + 256)[column / 32] = scale_h;
+    }
+}
+
+// The same encode for a batch of sequences, one new token each: segment i (a sequence's K/V head) takes keys / values
+// [i][256] into row `length - 1` of its planes.
+__global__ void __launch_bounds__(256) kv_append_kernel(const Segment* __restrict__ segments, size_t count,
+                                                         const float* __restrict__ keys, const float* __restrict__ values) {
+    const unsigned lane = threadIdx.x % 32;
+    const size_t blocks = count * 8 * 2;
+    for (size_t block = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) / 32; block < blocks; block += size_t(gridDim.x) * blockDim.x / 32) {
+        const bool is_value = block >= blocks / 2;
+        const size_t index = (is_value ? block - blocks / 2 : block) * 32 + lane, segment = index / 256, column = index % 256;
+        __half scale_h;
+        const int8_t q = q8_encode((is_value ? values : keys)[index], scale_h);
+        const Segment s = segments[segment];
+        uint8_t* row = const_cast<uint8_t*>(is_value ? s.values : s.keys) + size_t(s.length - 1) * kv_row_q8;
+        reinterpret_cast<int8_t*>(row)[column] = q;
         if (lane == 0) reinterpret_cast<__half*>(row + 256)[column / 32] = scale_h;
     }
 }
@@ -53,6 +78,12 @@ void launch_kv_write(Device& d, uint8_t* state, size_t context, size_t kv_heads,
     const size_t warps = steps * kv_heads * 8 * 2;
     const unsigned grid = unsigned(std::min<size_t>((warps + 7) / 8, size_t(d.sms) * 8));
     kv_write_kernel<<<grid, 256, 0, d.stream>>>(state, context, kv_heads, base, position, steps, keys, values);
+    ++d.launches;
+}
+
+void launch_kv_append(Device& d, const Segment* segments, size_t count, const float* keys, const float* values) {
+    const unsigned grid = unsigned(std::min<size_t>((count * 16 + 7) / 8, size_t(d.sms) * 8));
+    kv_append_kernel<<<grid, 256, 0, d.stream>>>(segments, count, keys, values);
     ++d.launches;
 }
 

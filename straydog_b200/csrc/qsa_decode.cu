@@ -25,6 +25,8 @@
 #include "../../include/straydog_gpu_b200.h"
 
 #include <algorithm>
+#include <cstdlib>
+#include <utility>
 
 namespace sdb {
 
@@ -33,13 +35,7 @@ constexpr int kTileBytes = 2 * kTileKeys * int(kv_row_q8);   // K rows then V ro
 constexpr int kPartialFloats = 8 * 258;                      // per piece: 8 heads x (256 sums, max, denominator)
 constexpr size_t kDecodeSmem = size_t(kWarps) * kStages * kTileBytes + size_t(kWarps) * kStages * 8 + 16;
 
-struct Segment {            // one (sequence, KV head)
-    const uint8_t* keys;    // plane base
-    const uint8_t* values;
-    uint32_t q_offset;      // (sequence * heads + kv_head * group) * 256, in query elements
-    uint32_t first_piece, pieces, length;
-};
-struct Piece { uint32_t segment, begin, end, pad; };
+struct Piece { uint32_t segment, begin, end, slot; };   // slot: the piece's partial, counted in the segment's own order
 
 struct DecodeArgs {
     const Segment* segments;
@@ -84,7 +80,7 @@ struct Cursor {
         if (piece >= piece_end) return;
         const Piece p = a.pieces[piece];
         const Segment s = a.segments[p.segment];
-        key = p.begin; key_end = p.end; keys = s.keys; values = s.values;
+        key = p.begin; key_end = min(p.end, s.length); keys = s.keys; values = s.values;
     }
     __device__ __forceinline__ bool done() const { return piece >= piece_end; }
 };
@@ -98,6 +94,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const Decode
         for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
     fence_barrier_init();
     __syncthreads();
+    // the merge launched behind this kernel may take its place on the SMs now: it waits for this grid's end before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // virtual warp v runs on CTA v % ctas: few warps spread over many SMs rather than filling one
     const uint32_t vwarp = uint32_t(warp) * a.ctas + blockIdx.x;
     if (vwarp >= a.virtual_warps) return;
@@ -246,7 +244,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const Decode
             l0 += __shfl_xor_sync(0xffffffffu, l0, offset);
             l1 += __shfl_xor_sync(0xffffffffu, l1, offset);
         }
-        float* mine = a.partial + size_t(use.piece) * kPartialFloats;
+        float* mine = a.partial + size_t(piece.slot) * kPartialFloats;
         #pragma unroll
         for (int b = 0; b < 8; ++b)
             #pragma unroll
@@ -269,8 +267,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const Decode
 // exp2: the maxima are kept in the exp2 domain), out = sum factor * acc / sum factor * denominator.
 __global__ void __launch_bounds__(256) qsa_decode_merge_kernel(const Segment* __restrict__ segments, const float* __restrict__ partial,
                                                                uint32_t group, float* __restrict__ out) {
-    const Segment segment = segments[blockIdx.x];
+    const Segment segment = segments[blockIdx.x];   // (the work list: written before the streaming kernel was launched)
     const uint32_t head = blockIdx.y, column = threadIdx.x;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the streaming kernel's partials are complete and visible from here on
     const float* first = partial + size_t(segment.first_piece) * kPartialFloats + head * 258;
     float top = -INFINITY;
     for (uint32_t piece = 0; piece < segment.pieces; ++piece) top = fmaxf(top, first[size_t(piece) * kPartialFloats + 256]);
@@ -304,31 +303,96 @@ struct HostTables {
     std::vector<uint32_t> warp_piece;
 };
 
-// Cuts the segments' tiles into equal runs, one per virtual warp (at least `min_tiles` each).
+// The work list in its two forms.
+//
+// Fixed cuts (the default): a segment is cut at places that depend on its own length only - chunks of 32 tiles (512 keys; 8 tiles
+// for a segment shorter than 512 tiles) and a tail that halves down to single tiles - and a chunk is never shared by two warps.
+// The chunks are dealt to the warps longest first, each to the warp with the least work so far; the halving tails are what lets
+// that come out even. A segment's partials are merged in chunk order, so a sequence's result has the same bits in any batch (the
+// reference's verification contract, docs/DESIGN.md:40-41, kept for this library's own batched decode).
+//
+// Moving cuts: the segments' tiles laid end to end and cut into equal runs, one per warp. Fewer partials (one per warp and one
+// per segment border), but where a segment is cut depends on what else is in the batch. Kept for sdx_qsa_decode_static, whose
+// fixed scratch bounds the number of partials.
+static void chunk_sizes(uint64_t tiles, std::vector<uint32_t>& out) {
+    const uint64_t chunk = tiles >= 512 ? 32 : 8;
+    out.clear();
+    while (tiles >= 2 * chunk) { out.push_back(uint32_t(chunk)); tiles -= chunk; }
+    while (tiles > 2) { const uint64_t take = (tiles + 1) / 2; out.push_back(uint32_t(take)); tiles -= take; }
+    if (tiles) out.push_back(uint32_t(tiles));
+}
+
 static void build_tables(const std::vector<const uint8_t*>& states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
-                         uint64_t heads, uint64_t kv_heads, uint32_t warps_available, HostTables& out) {
+                         uint64_t heads, uint64_t kv_heads, uint32_t warps_available, HostTables& out, bool fixed_cuts = true) {
     const uint64_t group = heads / kv_heads;
     uint64_t total_tiles = 0;
     for (uint64_t s = 0; s < sequences; ++s) total_tiles += (lengths[s] + kTileKeys - 1) / kTileKeys * kv_heads;
     constexpr uint64_t min_tiles = 8;
-    const uint64_t per_warp = std::max<uint64_t>(min_tiles, (total_tiles + warps_available - 1) / warps_available);
     out.segments.clear(); out.pieces.clear(); out.warp_piece.clear();
+    auto segment_of = [&](uint64_t s, uint64_t kv) {
+        Segment segment{};
+        segment.keys = states[s] + kv * contexts[s] * kv_row_q8;
+        segment.values = states[s] + (kv_heads + kv) * contexts[s] * kv_row_q8;
+        segment.q_offset = uint32_t((s * heads + kv * group) * 256);
+        segment.length = uint32_t(lengths[s]);
+        return segment;
+    };
+    if (fixed_cuts) {
+        struct Chunk { uint32_t segment, begin, end, slot, tiles; };
+        std::vector<Chunk> chunks;
+        std::vector<uint32_t> sizes;
+        for (uint64_t s = 0; s < sequences; ++s)
+            for (uint64_t kv = 0; kv < kv_heads; ++kv) {
+                Segment segment = segment_of(s, kv);
+                segment.first_piece = uint32_t(chunks.size());
+                chunk_sizes((lengths[s] + kTileKeys - 1) / kTileKeys, sizes);
+                uint64_t key = 0;
+                for (uint32_t tiles : sizes) {
+                    // (a chunk ends at a tile border; the kernel stops at the segment's length, so a work list stays valid while
+                    // its segments keep their tile counts)
+                    const uint64_t end = key + uint64_t(tiles) * kTileKeys;
+                    chunks.push_back(Chunk{uint32_t(out.segments.size()), uint32_t(key), uint32_t(end), uint32_t(chunks.size()), tiles});
+                    key = end;
+                }
+                segment.pieces = uint32_t(chunks.size()) - segment.first_piece;
+                out.segments.push_back(segment);
+            }
+        const uint32_t warps = uint32_t(std::max<uint64_t>(1, std::min<uint64_t>(warps_available, total_tiles / min_tiles)));
+        std::vector<uint32_t> order(chunks.size());
+        for (uint32_t i = 0; i < order.size(); ++i) order[i] = i;
+        std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return chunks[a].tiles > chunks[b].tiles; });
+        // least-loaded warp first: a heap of (tiles so far, warp)
+        std::vector<std::pair<uint64_t, uint32_t>> heap(warps);
+        for (uint32_t w = 0; w < warps; ++w) heap[w] = {0, w};
+        auto later = [](const std::pair<uint64_t, uint32_t>& a, const std::pair<uint64_t, uint32_t>& b) { return a > b; };
+        std::vector<std::vector<uint32_t>> dealt(warps);
+        for (uint32_t index : order) {
+            std::pop_heap(heap.begin(), heap.end(), later);
+            auto& least = heap.back();
+            dealt[least.second].push_back(index);
+            least.first += chunks[index].tiles;
+            std::push_heap(heap.begin(), heap.end(), later);
+        }
+        for (uint32_t w = 0; w < warps; ++w) {
+            out.warp_piece.push_back(uint32_t(out.pieces.size()));
+            for (uint32_t index : dealt[w]) out.pieces.push_back(Piece{chunks[index].segment, chunks[index].begin, chunks[index].end, chunks[index].slot});
+        }
+        out.warp_piece.push_back(uint32_t(out.pieces.size()));
+        return;
+    }
+    const uint64_t per_warp = std::max<uint64_t>(min_tiles, (total_tiles + warps_available - 1) / warps_available);
     out.warp_piece.push_back(0);
     uint64_t room = per_warp;   // tiles the current warp may still take
     for (uint64_t s = 0; s < sequences; ++s)
         for (uint64_t kv = 0; kv < kv_heads; ++kv) {
-            Segment segment{};
-            segment.keys = states[s] + kv * contexts[s] * kv_row_q8;
-            segment.values = states[s] + (kv_heads + kv) * contexts[s] * kv_row_q8;
-            segment.q_offset = uint32_t((s * heads + kv * group) * 256);
+            Segment segment = segment_of(s, kv);
             segment.first_piece = uint32_t(out.pieces.size());
-            segment.length = uint32_t(lengths[s]);
             uint64_t key = 0;
             while (key < lengths[s]) {
                 if (!room) { out.warp_piece.push_back(uint32_t(out.pieces.size())); room = per_warp; }
                 const uint64_t tiles_left = (lengths[s] - key + kTileKeys - 1) / kTileKeys, take = std::min(room, tiles_left);
                 const uint64_t end = std::min<uint64_t>(lengths[s], key + take * kTileKeys);
-                out.pieces.push_back(Piece{uint32_t(out.segments.size()), uint32_t(key), uint32_t(end), 0});
+                out.pieces.push_back(Piece{uint32_t(out.segments.size()), uint32_t(key), uint32_t(end), uint32_t(out.pieces.size())});
                 room -= take;
                 key = end;
             }
@@ -405,7 +469,17 @@ static void run_plan(Device& d, const DecodePlan& plan, float scale, const void*
     if (before) SDB_CHECK(cudaEventRecord(before, d.stream));
     qsa_decode_kernel<<<plan.ctas, kWarps * 32, kDecodeSmem, d.stream>>>(args);
     if (after) SDB_CHECK(cudaEventRecord(after, d.stream));
-    qsa_decode_merge_kernel<<<dim3(plan.segments, plan.group), 256, 0, d.stream>>>(args.segments, plan.partial, plan.group, out);
+    // programmatic dependent launch: the merge's blocks are placed while the streaming kernel drains and start at its end
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(plan.segments, plan.group);
+    config.blockDim = dim3(256);
+    config.stream = d.stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = after ? 0 : 1;   // (an event recorded between the two launches keeps the plain order)
+    SDB_CHECK(cudaLaunchKernelEx(&config, qsa_decode_merge_kernel, args.segments, static_cast<const float*>(plan.partial), plan.group, out));
     d.launches += 2;
 }
 
@@ -423,13 +497,15 @@ int* status_word(Device& d) {
     return word;
 }
 
+void launch_kv_append(Device& d, const Segment* segments, size_t count, const float* keys, const float* values);
+
 void qsa_decode_dense(Device& d, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
                       uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out) {
     std::vector<const uint8_t*> checked;
     uint64_t kv_bytes = 0;
     validate_batch(d, states, contexts, lengths, sequences, heads, kv_heads, checked, kv_bytes);
     HostTables host;
-    build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(d.sms) * kWarps, host);
+    build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(d.sms) * kWarps, host, d.fixed_cuts);
     DecodePlan plan;
     fill_plan(d, host, plan, sequences, heads, kv_heads);
     ensure(d, d.pinned, d.pinned_bytes, plan.table_bytes, true);
@@ -441,6 +517,57 @@ void qsa_decode_dense(Device& d, const void* const* states, const uint64_t* cont
     SDB_CHECK(cudaStreamSynchronize(d.stream));
     upload_tables(d, host, plan, d.tables, d.pinned);
     run_plan(d, plan, scale, q, out);
+}
+
+// One decode step of a batch from host buffers: the new rows are appended and the batch is decoded by one pass over one work
+// list. The host builds the list while the copies of the queries and the new rows are in flight.
+void attention_batch(Device& d, void* const* states, const uint64_t* contexts, const uint64_t* bases, uint64_t sequences, uint64_t heads,
+                     uint64_t kv_heads, float scale, const void* q, const float* k, const float* v, float* out) {
+    // everything is checked before anything is queued: a refused call leaves the K/V states as they were
+    if (!states || !contexts || !bases || !q || !k || !v || !out || !sequences || sequences > 65535)
+        throw std::runtime_error("invalid Straydog attention dimensions");
+    std::vector<uint64_t> lengths(sequences);
+    for (uint64_t s = 0; s < sequences; ++s) {
+        if (!contexts[s] || bases[s] >= contexts[s]) throw std::runtime_error("invalid Straydog attention dimensions");
+        lengths[s] = bases[s] + 1;
+    }
+    std::vector<const uint8_t*> checked;
+    uint64_t kv_bytes = 0;
+    validate_batch(d, reinterpret_cast<const void* const*>(states), contexts, lengths.data(), sequences, heads, kv_heads, checked, kv_bytes);
+    {
+        std::vector<const uint8_t*> sorted(checked);
+        std::sort(sorted.begin(), sorted.end());
+        if (std::adjacent_find(sorted.begin(), sorted.end()) != sorted.end())
+            throw std::runtime_error("a Straydog K/V state is listed twice in one batch: its new row would be written twice");
+    }
+    // device work buffer: q (FP16) | k | v | out
+    const size_t q_bytes = size_t(sequences * heads) * 256 * 2, new_bytes = size_t(sequences * kv_heads) * 256 * 4,
+                 out_bytes = size_t(sequences * heads) * 256 * 4;
+    const size_t k_at = (q_bytes + 255) / 256 * 256, v_at = k_at + (new_bytes + 255) / 256 * 256,
+                 out_at = v_at + (new_bytes + 255) / 256 * 256, total = out_at + out_bytes;
+    auto* work = static_cast<uint8_t*>(ensure(d, d.work, d.work_bytes, total));
+    SDB_CHECK(cudaMemcpyAsync(work, q, q_bytes, cudaMemcpyHostToDevice, d.stream));
+    SDB_CHECK(cudaMemcpyAsync(work + k_at, k, new_bytes, cudaMemcpyHostToDevice, d.stream));
+    SDB_CHECK(cudaMemcpyAsync(work + v_at, v, new_bytes, cudaMemcpyHostToDevice, d.stream));
+    HostTables host;
+    build_tables(checked, contexts, lengths.data(), sequences, heads, kv_heads, uint32_t(d.sms) * kWarps, host, d.fixed_cuts);
+    DecodePlan plan;
+    fill_plan(d, host, plan, sequences, heads, kv_heads);
+    // (these grow on the first call of a size only; the previous call ended with a synchronisation, so the staging area is free)
+    ensure(d, d.pinned, d.pinned_bytes, plan.table_bytes, true);
+    ensure(d, d.tables, d.tables_bytes, plan.table_bytes);
+    ensure(d, d.partial, d.partial_bytes, size_t(plan.pieces) * kPartialFloats * 4);
+    plan.partial = static_cast<float*>(d.partial);
+    plan.status = status_word(d);
+    upload_tables(d, host, plan, d.tables, d.pinned);
+    // the new rows, appended by one launch over the work list's segments (plane bases and lengths)
+    launch_kv_append(d, reinterpret_cast<const Segment*>(static_cast<uint8_t*>(d.tables) + plan.segment_offset), host.segments.size(),
+                     reinterpret_cast<const float*>(work + k_at), reinterpret_cast<const float*>(work + v_at));
+    SDB_CHECK(cudaGetLastError());
+    run_plan(d, plan, scale, work, reinterpret_cast<float*>(work + out_at));
+    SDB_CHECK(cudaGetLastError());
+    SDB_CHECK(cudaMemcpyAsync(out, work + out_at, out_bytes, cudaMemcpyDeviceToHost, d.stream));
+    SDB_CHECK(cudaStreamSynchronize(d.stream));
 }
 
 }  // namespace sdb
@@ -458,6 +585,54 @@ int sdx_qsa_decode(void* handle, const void* const* states, const uint64_t* cont
     SDB_OP_END
 }
 
+int sdx_attention_batch(void* handle, void* const* states, const uint64_t* contexts, const uint64_t* bases, uint64_t sequences,
+                        uint64_t heads, uint64_t kv_heads, float scale, const void* q, const float* k, const float* v, float* out) {
+    SDB_OP_BEGIN
+    attention_batch(value, states, contexts, bases, sequences, heads, kv_heads, scale, q, k, v, out);
+    SDB_OP_END
+}
+
+// The work list's cuts without a device (host arithmetic only): stats = {pieces, warps used, most tiles a warp got, tiles in all};
+// begins[0 .. result) = where the pieces of sequence `probe`'s first K/V head start. For tests and for a caller that sizes scratch.
+int sdx_qsa_cuts(const uint64_t* lengths, uint64_t sequences, uint64_t kv_heads, uint64_t warps, int fixed, uint64_t probe,
+                 uint32_t* begins, uint64_t capacity, uint64_t* stats) {
+    try {
+        if (!lengths || !sequences || !kv_heads || !warps || probe >= sequences) throw std::runtime_error("invalid Straydog attention dimensions");
+        std::vector<const uint8_t*> states(sequences, nullptr);
+        std::vector<uint64_t> contexts(lengths, lengths + sequences);
+        for (uint64_t s = 0; s < sequences; ++s)
+            if (!lengths[s] || lengths[s] > (uint64_t(1) << 24)) throw std::runtime_error("invalid Straydog attention dimensions");
+        HostTables host;
+        build_tables(states, contexts.data(), lengths, sequences, kv_heads, kv_heads, uint32_t(warps), host, fixed != 0);
+        if (stats) {
+            uint64_t most = 0, total = 0;
+            for (size_t w = 0; w + 1 < host.warp_piece.size(); ++w) {
+                uint64_t tiles = 0;
+                for (uint32_t i = host.warp_piece[w]; i < host.warp_piece[w + 1]; ++i) {
+                    const Piece& piece = host.pieces[i];
+                    tiles += (std::min(piece.end, host.segments[piece.segment].length) - piece.begin + kTileKeys - 1) / kTileKeys;
+                }
+                most = std::max(most, tiles);
+                total += tiles;
+            }
+            stats[0] = host.pieces.size(); stats[1] = host.warp_piece.size() - 1; stats[2] = most; stats[3] = total;
+        }
+        std::vector<uint32_t> mine;
+        for (const Piece& piece : host.pieces)
+            if (piece.segment == probe * kv_heads) mine.push_back(piece.begin);
+        std::sort(mine.begin(), mine.end());
+        if (begins)
+            for (size_t i = 0; i < mine.size() && i < capacity; ++i) begins[i] = mine[i];
+        return int(mine.size());
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+int sdx_decode_cuts(void* handle, int fixed) {
+    SDB_OP_BEGIN
+    value.fixed_cuts = fixed != 0;
+    SDB_OP_END
+}
+
 void* sdx_qsa_plan(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
                    uint64_t heads, uint64_t kv_heads) {
     try {
@@ -466,7 +641,7 @@ void* sdx_qsa_plan(void* handle, const void* const* states, const uint64_t* cont
         uint64_t kv_bytes = 0;
         validate_batch(value, states, contexts, lengths, sequences, heads, kv_heads, checked, kv_bytes);
         HostTables host;
-        build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(value.sms) * kWarps, host);
+        build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(value.sms) * kWarps, host, value.fixed_cuts);
         auto plan = std::make_unique<DecodePlan>();
         fill_plan(value, host, *plan, sequences, heads, kv_heads);
         plan->kv_bytes = kv_bytes;
@@ -530,8 +705,10 @@ int sdx_qsa_plan_release(void* handle, void* plan) {
 // that: an engine that has handed its whole VRAM budget to weights and K/V and must never see an
 // allocation fail mid-request, or a serving loop that forbids driver allocations after start-up because
 // they synchronise the device. For them this entry keeps all of its scratch in one array that is part
-// of the library's device image: it exists on every GPU that loads the library, from load to exit,
-// whether or not the entry is ever called.
+// of the library's device image: every GPU that loads the image holds it until exit. The CUDA runtime
+// loads a library's device image lazily by default (at the first use of one of its kernels or symbols, which
+// is when the array's 16.3 MiB are taken), so the call that must never allocate is any call AFTER the first
+// one on that device: make one warm-up call at start-up, or run with CUDA_MODULE_LOADING=EAGER.
 constexpr size_t kStaticSequences = 64;                                  // sequences a call
 constexpr size_t kStaticKvHeads = 8;                                     // K/V heads
 constexpr size_t kStaticPieces = 2048;                                   // pieces a call's work list may hold
@@ -564,7 +741,7 @@ int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_
     uint64_t kv_bytes = 0;
     validate_batch(value, states, contexts, lengths, sequences, heads, kv_heads, checked, kv_bytes);
     HostTables host;
-    build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(value.sms) * kWarps, host);
+    build_tables(checked, contexts, lengths, sequences, heads, kv_heads, uint32_t(value.sms) * kWarps, host, false);   // (moving cuts: fewest partials)
     DecodePlan plan;
     fill_plan(value, host, plan, sequences, heads, kv_heads);
     if (plan.pieces > kStaticPieces || plan.table_bytes > kStaticTableBytes)

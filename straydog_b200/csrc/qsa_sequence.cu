@@ -1,6 +1,5 @@
 // sd_attention_sequence: the reference's standalone selection-attention entry (host floats in,
-// host floats out; gpu/kernels.cpp:4387-4419 over attention_scores / attention_reduce, :100-165),
-// and sdx_attention_batch, its batched dense-causal twin over the tensor-core decode kernel.
+// host floats out; gpu/kernels.cpp:4387-4419 over attention_scores / attention_reduce, :100-165).
 //
 // The selection kernel keeps FP32 arithmetic throughout (queries arrive as F32 and the reference
 // computes in F32): one block per (step, query head), a warp per selected key for the scores
@@ -13,8 +12,6 @@ namespace sdb {
 
 void launch_kv_write(Device& d, uint8_t* state, size_t context, size_t kv_heads, size_t base, const uint32_t* position, size_t steps,
                      const float* keys, const float* values);
-void qsa_decode_dense(Device& d, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
-                      uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out);
 
 constexpr int kMaxSelected = 2052;   // gpu/kernels.cpp:4392
 
@@ -97,31 +94,6 @@ __global__ void __launch_bounds__(256) selection_attention_kernel(const uint8_t*
     output[item * 256 + t] = result;
 }
 
-// The new token's keys and values of every segment (sequence, K/V head) of a batch, quantised into
-// row `length - 1` of the segment's planes: kv_encode per 32-value block, a warp each.
-struct SegmentView { const uint8_t* keys; const uint8_t* values; uint32_t q_offset, first_piece, pieces, length; };
-__global__ void __launch_bounds__(256) kv_append_kernel(const SegmentView* __restrict__ segments, size_t count,
-                                                         const float* __restrict__ keys, const float* __restrict__ values) {
-    const unsigned lane = threadIdx.x % 32;
-    const size_t blocks = count * 8 * 2;
-    for (size_t block = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) / 32; block < blocks; block += size_t(gridDim.x) * blockDim.x / 32) {
-        const bool is_value = block >= blocks / 2;
-        const size_t index = (is_value ? block - blocks / 2 : block) * 32 + lane, segment = index / 256, column = index % 256;
-        const float value = (is_value ? values : keys)[index];
-        float top = fabsf(value);
-        #pragma unroll
-        for (unsigned offset = 16; offset; offset /= 2) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
-        const __half scale_h = __float2half_rn(__fdiv_rn(top, 127.0f));
-        const float scale = __half2float(scale_h);
-        int q = scale > 0.0f ? __float2int_rn(__fdiv_rn(value, scale)) : 0;
-        q = q > 127 ? 127 : q < -127 ? -127 : q;
-        const SegmentView s = segments[segment];
-        uint8_t* row = const_cast<uint8_t*>(is_value ? s.values : s.keys) + size_t(s.length - 1) * kv_row_q8;
-        reinterpret_cast<int8_t*>(row)[column] = int8_t(q);
-        if (lane == 0) reinterpret_cast<__half*>(row + 256)[column / 32] = scale_h;
-    }
-}
-
 }  // namespace sdb
 
 using namespace sdb;
@@ -159,55 +131,6 @@ int sd_attention_sequence(void* handle, void* state, uint64_t context, uint64_t 
         ++value.launches;
         SDB_CHECK(cudaGetLastError());
         SDB_CHECK(cudaMemcpyAsync(output, device_out, out_bytes, cudaMemcpyDeviceToHost, value.stream));
-        SDB_CHECK(cudaStreamSynchronize(value.stream));
-        return 0;
-    } catch (const std::exception& e) { last_error = e.what(); return -1; }
-}
-
-int sdx_attention_batch(void* handle, void* const* states, const uint64_t* contexts, const uint64_t* bases, uint64_t sequences,
-                        uint64_t heads, uint64_t kv_heads, float scale, const void* q, const float* k, const float* v, float* out) {
-    try {
-        auto& value = device(handle);
-        if (!states || !contexts || !bases || !q || !k || !v || !out || !sequences || sequences > 65535 || !heads || !kv_heads ||
-            heads % kv_heads)
-            throw std::runtime_error("invalid Straydog attention dimensions");
-        if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
-        std::vector<uint64_t> lengths(sequences);
-        std::vector<SegmentView> views(sequences * kv_heads);
-        for (uint64_t s = 0; s < sequences; ++s) {
-            if (!contexts[s] || bases[s] >= contexts[s]) throw std::runtime_error("invalid Straydog attention dimensions");
-            span(value, states[s], checked_product({contexts[s], 2 * kv_heads, kv_row_q8}), "a K/V state");
-            lengths[s] = bases[s] + 1;
-            auto* planes = static_cast<const uint8_t*>(states[s]);
-            for (uint64_t h = 0; h < kv_heads; ++h)
-                views[s * kv_heads + h] = SegmentView{planes + h * contexts[s] * kv_row_q8, planes + (kv_heads + h) * contexts[s] * kv_row_q8,
-                                                      0, 0, 0, uint32_t(lengths[s])};
-        }
-        // device work buffer: q (FP16) | k | v | out
-        const size_t q_bytes = size_t(sequences * heads) * 256 * 2, kv_bytes = size_t(sequences * kv_heads) * 256 * 4,
-                     out_bytes = size_t(sequences * heads) * 256 * 4;
-        const size_t k_at = (q_bytes + 255) / 256 * 256, v_at = k_at + (kv_bytes + 255) / 256 * 256,
-                     out_at = v_at + (kv_bytes + 255) / 256 * 256, total = out_at + out_bytes;
-        auto* work = static_cast<uint8_t*>(ensure(value, value.work, value.work_bytes, total));
-        SDB_CHECK(cudaMemcpyAsync(work, q, q_bytes, cudaMemcpyHostToDevice, value.stream));
-        SDB_CHECK(cudaMemcpyAsync(work + k_at, k, kv_bytes, cudaMemcpyHostToDevice, value.stream));
-        SDB_CHECK(cudaMemcpyAsync(work + v_at, v, kv_bytes, cudaMemcpyHostToDevice, value.stream));
-        // the new rows, appended by one launch over a table of the batch's planes
-        const size_t view_bytes = views.size() * sizeof(SegmentView);
-        auto* staged = static_cast<uint8_t*>(ensure(value, value.append_pinned, value.append_pinned_bytes, view_bytes, true));
-        ensure(value, value.append, value.append_bytes, view_bytes);
-        SDB_CHECK(cudaStreamSynchronize(value.stream));   // (a previous call's table has left the staging area)
-        std::memcpy(staged, views.data(), view_bytes);
-        SDB_CHECK(cudaMemcpyAsync(value.append, staged, view_bytes, cudaMemcpyHostToDevice, value.stream));
-        const unsigned grid = unsigned(std::min<size_t>((views.size() * 16 + 7) / 8, size_t(value.sms) * 8));
-        kv_append_kernel<<<grid, 256, 0, value.stream>>>(static_cast<const SegmentView*>(value.append), views.size(),
-                                                         reinterpret_cast<const float*>(work + k_at), reinterpret_cast<const float*>(work + v_at));
-        ++value.launches;
-        SDB_CHECK(cudaGetLastError());
-        qsa_decode_dense(value, reinterpret_cast<const void* const*>(states), contexts, lengths.data(), sequences, heads, kv_heads, scale,
-                         work, reinterpret_cast<float*>(work + out_at));
-        SDB_CHECK(cudaGetLastError());
-        SDB_CHECK(cudaMemcpyAsync(out, work + out_at, out_bytes, cudaMemcpyDeviceToHost, value.stream));
         SDB_CHECK(cudaStreamSynchronize(value.stream));
         return 0;
     } catch (const std::exception& e) { last_error = e.what(); return -1; }

@@ -60,3 +60,12 @@ def heads_from_gathered(full):
     """[N][rows][heads / N][dim] -> [rows][heads][dim] (a view-changing copy, for checks)."""
     world, rows, each, dim = full.shape
     return full.permute(1, 0, 2, 3).reshape(rows, world * each, dim)
+
+
+def gathered_buffer_of(step):
+    """Which of a rank's TWO gathered buffers call number `step` of sdx_sparse_attention_gather stores into (steps count from 1).
+
+    A rank leaves call n only when every peer's counter shows n, i.e. when every peer has finished the attention kernel of its own
+    call n; a peer's stream runs that kernel behind its readers of call n - 1. So while a rank stores call n + 1 into buffer
+    (n + 1) % 2 a slow peer may still read buffer n % 2 (call n), and nothing of call n - 1 is read any more anywhere."""
+    return step % 2

@@ -51,3 +51,38 @@ def test_kv_write_rejects_bad_shapes(gpu):
         gpu.kv_write(state, 32, 2, 0, 1, rows, rows)       # state too small for the context
     gpu.release(state)
     gpu.release(rows)
+
+
+def test_kv_stage_registration_is_validated(gpu):
+    # gpu/kernels.cpp:4277-4290: the stage is one allocation of exactly rows * 4096 bytes; it is dropped when that allocation is released
+    from straydog_b200.backend import StraydogError
+    stage = gpu.buffer(8 * 4096)
+    gpu.kv_stage(stage, 8)
+    for rows in (0, 7, 9):
+        with pytest.raises(StraydogError, match="K/V stage"):
+            gpu.kv_stage(stage, rows)
+    other = gpu.buffer(64)
+    with pytest.raises(StraydogError):
+        gpu.kv_stage(other, 8)
+    gpu.release(other)
+    gpu.release(stage)
+
+
+def test_fp16_rows_are_a_known_format_that_the_attention_refuses():
+    # gpu/kernels.cpp:4266-4275 takes 512 (FP16 rows) and 272 (Q8_0 rows); this library's attention reads Q8_0 rows only and
+    # says so at the call instead of misreading FP16 rows
+    from straydog_b200.backend import Backend, StraydogError
+    with Backend(0, 1 << 28) as gpu:
+        with pytest.raises(StraydogError, match="K/V format"):
+            gpu.kv_format(100)
+        gpu.kv_format(512)
+        state = gpu.buffer(4 * 16 * 512)
+        q, out = gpu.buffer(16 * 256 * 2), gpu.buffer(16 * 256 * 4)
+        with pytest.raises(StraydogError, match="Q8_0"):
+            gpu.qsa_decode([state], [16], [16], 16, 2, 1 / 16, q.pointer, out.pointer)
+        with pytest.raises(StraydogError, match="Q8_0"):
+            gpu.qsa_prompt(state, 16, 0, 4, 16, 2, 1 / 16, q.pointer, out.pointer)
+        with pytest.raises(StraydogError, match="Q8_0"):
+            gpu.kv_write(state, 16, 2, 0, 1, q, q)
+        gpu.kv_format(272)
+        gpu.qsa_decode([state], [16], [16], 16, 2, 1 / 16, q.pointer, out.pointer)

@@ -89,17 +89,49 @@ def test_ragged_batch_and_plan_replay(gpu):
 
 
 def test_a_sequence_result_does_not_depend_on_its_batch(gpu):
-    # the reference's verification contract (docs/DESIGN.md:40-41) asks a row's bits to be those of a one-token decode; here the
-    # stream-K cut points move with the batch, so the value is the same to FP32 rounding, not bit for bit
+    # the reference's verification contract (docs/DESIGN.md:40-41) asks a row's bits to be those of a one-token decode. With the
+    # default moving cuts the split points move with the batch, so the value is the same to FP32 rounding; with fixed cuts
+    # (sdx_decode_cuts) a sequence is cut by its own length alone and the bits are the same in any batch.
     rng = np.random.default_rng(500)
-    lengths = [700, 64, 1500, 333]
+    lengths = [700, 64, 9000, 333, 1]
     states = [q8_state(rng, l, 2) for l in lengths]
-    q = queries_f16(rng, 4, 16, 256)
-    together = run_decode(gpu, states, lengths, lengths, 16, 2, q)
-    for s in range(4):
-        alone = run_decode(gpu, [states[s]], [lengths[s]], [lengths[s]], 16, 2, q[s:s + 1])
-        ok, worst = close(alone[0], together[s], atol=5e-4, rtol=1e-3)   # same value; the split points differ with the batch
-        assert ok, (s, worst)
+    q = queries_f16(rng, len(lengths), 16, 256)
+    want = expect_decode(states, lengths, lengths, 16, 2, q)
+    for fixed in (False, True):
+        gpu.decode_cuts(fixed)
+        try:
+            together = run_decode(gpu, states, lengths, lengths, 16, 2, q)
+            ok, worst = close(together, want)
+            assert ok and worst < 5e-4, (fixed, worst)
+            for s in range(len(lengths)):
+                alone = run_decode(gpu, [states[s]], [lengths[s]], [lengths[s]], 16, 2, q[s:s + 1])
+                pair = run_decode(gpu, [states[s], states[2]], [lengths[s], lengths[2]], [lengths[s], lengths[2]], 16, 2, q[[s, 2]], plan=True)
+                if fixed:
+                    assert np.array_equal(alone[0].view(np.uint32), together[s].view(np.uint32)), s
+                    assert np.array_equal(pair[0].view(np.uint32), together[s].view(np.uint32)), s
+                else:
+                    ok, worst = close(alone[0], together[s], atol=5e-4, rtol=1e-3)
+                    assert ok, (s, worst)
+        finally:
+            gpu.decode_cuts(False)
+
+
+@pytest.mark.parametrize("fixed", [False, True])
+def test_the_benchmarks_longest_contexts(gpu, fixed):
+    # the metric is quoted at 32 K context: sequences at and just under it, beside the shortest the batch may hold
+    rng = np.random.default_rng(501)
+    lengths = [32768, 32767, 1024, 20001]
+    contexts = [32768, 32768, 1024, 20480]
+    states = [q8_state(rng, c, 2) for c in contexts]
+    q = queries_f16(rng, len(lengths), 16, 256)
+    gpu.decode_cuts(fixed)
+    try:
+        got = run_decode(gpu, states, contexts, lengths, 16, 2, q, plan=True)
+    finally:
+        gpu.decode_cuts(False)
+    want = expect_decode(states, contexts, lengths, 16, 2, q)
+    ok, worst = close(got, want)
+    assert ok and worst < 5e-4, worst
 
 
 def test_large_scales_and_peaked_softmax(gpu):
@@ -134,6 +166,25 @@ def test_attention_batch_from_host_buffers(gpu):
         assert ok, (s, worst)
     for b in states:
         gpu.release(b)
+
+
+def test_a_refused_batch_step_leaves_the_states_untouched(gpu):
+    # every check runs before the new rows are written: too many heads a group, and one state listed twice
+    from straydog_b200.backend import StraydogError
+    rng = np.random.default_rng(701)
+    state_np = q8_state(rng, 64, 2, filled=10)
+    a, b = gpu.upload(state_np), gpu.upload(state_np)
+    q = queries_f16(rng, 2, 18, 256)
+    k = rng.normal(0, 1, (2, 1, 256)).astype(np.float32)
+    out = np.empty((2, 18, 256), np.float32)
+    with pytest.raises(StraydogError):
+        gpu.attention_batch([a, b], [64, 64], [10, 10], 18, 1, 1 / 16, q, k, k, out)       # 18 heads on one K/V head
+    q16, k2, out16 = queries_f16(rng, 2, 16, 256), rng.normal(0, 1, (2, 2, 256)).astype(np.float32), np.empty((2, 16, 256), np.float32)
+    with pytest.raises(StraydogError, match="listed twice"):
+        gpu.attention_batch([a, a], [64, 64], [10, 10], 16, 2, 1 / 16, q16, k2, k2, out16)
+    for buffer in (a, b):
+        assert np.array_equal(gpu.read(buffer, np.uint8, state_np.shape), state_np)
+        gpu.release(buffer)
 
 
 def test_invalid_batches_are_refused(gpu):

@@ -9,14 +9,10 @@ from util import XorShift, bf16_round, close, sparse_attention_case
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["default", "v2", "v3"])
-def form(request):
-    """Which form of the tensor-core kernel answers: the library's own choice by head count, or one form forced for every shape."""
-    import os
-    if request.param != "default":
-        os.environ["SDX_SPARSE_KERNEL"] = request.param
-    yield request.param
-    os.environ.pop("SDX_SPARSE_KERNEL", None)
+@pytest.fixture
+def form():
+    """The library's own choice of kernel (the tensor-core kernel wherever the shape allows it)."""
+    yield "default"
 
 
 def reference_case(rows, heads):

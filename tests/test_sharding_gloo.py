@@ -93,3 +93,38 @@ def test_head_shards_gather_to_the_unsharded_result():
         assert np.array_equal(results[r].view(np.uint32), whole.view(np.uint32))
     with __import__("pytest").raises(ValueError):
         sharding.head_range(10, 0, 4)
+
+
+def test_two_gathered_buffers_are_enough_and_one_is_not():
+    """sdx_sparse_attention_gather's buffer rule, as a schedule on CPU: every rank runs, per call n, [kernel: store its slot of call n
+    into every rank's gathered buffer, raise its counters to n, wait until its own counters all show n] and then [consumer: read its
+    own gathered buffer of call n], each rank's phases in stream order, the ranks interleaved at random. With two buffers taken in
+    turn (sharding.gathered_buffer_of) a consumer always finds call n in every slot; with one buffer some interleaving lets a rank
+    that is a call ahead overwrite what a slow peer has not read yet."""
+    import random
+
+    def run(world, calls, buffers, seed):
+        random.seed(seed)
+        store = [[[0] * world for _ in range(buffers)] for _ in range(world)]     # store[gpu][buffer][slot] = call whose data sits there
+        counters = [[0] * world for _ in range(world)]                            # counters[gpu][peer]
+        call, phase = [1] * world, ["store"] * world                              # store -> wait -> read
+        while any(c <= calls for c in call):
+            rank = random.choice([r for r in range(world) if call[r] <= calls])
+            n = call[rank]
+            which = sharding.gathered_buffer_of(n) if buffers == 2 else 0
+            if phase[rank] == "store":
+                for gpu in range(world):
+                    store[gpu][which][rank] = n
+                    counters[gpu][rank] = n
+                phase[rank] = "wait"
+            elif phase[rank] == "wait":
+                if all(seen >= n for seen in counters[rank]):
+                    phase[rank] = "read"
+            else:
+                if any(slot != n for slot in store[rank][which]):
+                    return False
+                call[rank], phase[rank] = n + 1, "store"
+        return True
+
+    assert all(run(world, 40, 2, seed) for world in (2, 4, 8) for seed in range(30))
+    assert not all(run(4, 40, 1, seed) for seed in range(30))

@@ -3,7 +3,9 @@ allocate while they serve. Collected last on purpose (a failure here stops nothi
 
 Checks, through the C ABI: two calls in a row (different batches, so the second must not see the first one's
 leftovers in the shared array) give what sdx_qsa_decode gives for the same inputs, and what the CPU oracle
-gives within the decode tests' tolerance; a batch beyond the stated limits is refused with an error.
+gives within the decode tests' tolerance; a batch beyond the stated limits is refused with an error; once a
+first call has made the library's device image resident, a further call on a new batch shape leaves the
+GPU's free memory where it was.
 """
 import numpy as np
 import pytest
@@ -51,4 +53,37 @@ def test_a_batch_beyond_the_static_scratch_is_refused(gpu):
     with pytest.raises(StraydogError, match="at most 64 sequences"):
         gpu.qsa_decode_static([state] * 65, [16] * 65, [16] * 65, 16, 2, 1 / 16, q.pointer, out.pointer)
     for b in (state, q, out):
+        gpu.release(b)
+
+
+def test_the_largest_batch_the_limits_allow_fits_the_static_scratch(gpu):
+    # 64 sequences on 8 K/V heads is the most segments a call may hold (512); its work list has at most one piece per warp of the
+    # GPU plus one per segment, 8 * 148 + 512 = 1696 on a B200, inside the 2048 the scratch holds (the refusal beyond 2048 pieces
+    # guards a GPU with more SMs): the call is accepted and gives the allocating entry's bits
+    rng = np.random.default_rng(10)
+    length = 3001
+    state_np = q8_state(rng, length, 8)
+    state = gpu.upload(state_np)
+    q = gpu.upload(queries_f16(rng, 64, 8, 256))
+    out_static, out_plain = gpu.buffer(64 * 8 * 256 * 4), gpu.buffer(64 * 8 * 256 * 4)
+    gpu.qsa_decode_static([state] * 64, [length] * 64, [length] * 64, 8, 8, 1 / 16, q.pointer, out_static.pointer)
+    gpu.qsa_decode([state] * 64, [length] * 64, [length] * 64, 8, 8, 1 / 16, q.pointer, out_plain.pointer)
+    a, b = gpu.read(out_static, np.uint32, (64 * 8 * 256,)), gpu.read(out_plain, np.uint32, (64 * 8 * 256,))
+    assert np.array_equal(a, b)
+    assert gpu.decode_status() == 0
+    for buffer in (state, q, out_static, out_plain):
+        gpu.release(buffer)
+
+
+def test_after_the_first_call_a_call_leaves_free_memory_unchanged(gpu):
+    import torch
+    rng = np.random.default_rng(9)
+    states = [gpu.upload(q8_state(rng, l, 2)) for l in (700, 1300, 90)]
+    q = gpu.upload(queries_f16(rng, 3, 16, 256))
+    out = gpu.buffer(3 * 16 * 256 * 4)
+    gpu.qsa_decode_static(states[:1], [700], [700], 16, 2, 1 / 16, q.pointer, out.pointer)   # the first call: the image is resident after it
+    free_before = torch.cuda.mem_get_info(0)[0]
+    gpu.qsa_decode_static(states, [700, 1300, 90], [700, 1300, 90], 16, 2, 1 / 16, q.pointer, out.pointer)   # a batch shape not seen before
+    assert torch.cuda.mem_get_info(0)[0] == free_before
+    for b in states + [q, out]:
         gpu.release(b)
