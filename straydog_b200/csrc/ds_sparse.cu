@@ -51,12 +51,15 @@ __global__ void __launch_bounds__(128) sparse_rotate_q_kernel(const float* __res
 // ---- FP32 kernel: block = (row, group of 4 heads, split); a warp per key ----
 constexpr int kSimtHeads = 4, kSimtWarps = 8;
 
+// The partial of split s of (row, head) goes to slot part0 + s of that pair's `parts` slots (parts == 0: one slot per split).
 template<int PER_LANE>
-__global__ void __launch_bounds__(kSimtWarps * 32) sparse_simt_kernel(const SparseArgs a, const float* __restrict__ q, float* __restrict__ partial) {
+__global__ void __launch_bounds__(kSimtWarps * 32) sparse_simt_kernel(const SparseArgs a, const float* __restrict__ q, float* __restrict__ partial,
+                                                                      size_t parts, size_t part0) {
     const size_t row = blockIdx.x, head0 = size_t(blockIdx.y) * kSimtHeads, split = blockIdx.z, splits = gridDim.z;
     const unsigned lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     const KeyList list = key_list(a, row);
     const size_t share = (list.total + splits - 1) / splits, begin = min(list.total, split * share), end = min(list.total, begin + share);
+    if (!parts) parts = splits;
     extern __shared__ float shared[];
     float* qs = shared;                                  // [kSimtHeads][dim]
     float* merged = shared + kSimtHeads * a.dim;         // [kSimtHeads][dim]
@@ -128,10 +131,10 @@ __global__ void __launch_bounds__(kSimtWarps * 32) sparse_simt_kernel(const Spar
     // the split's partial: [dim sums | max | denominator] per (row, head, split)
     for (size_t i = threadIdx.x; i < kSimtHeads * a.dim; i += blockDim.x) {
         const size_t h = i / a.dim, head = head0 + h;
-        if (head < a.heads) partial[((row * a.heads + head) * splits + split) * (a.dim + 2) + i % a.dim] = merged[i];
+        if (head < a.heads) partial[((row * a.heads + head) * parts + part0 + split) * (a.dim + 2) + i % a.dim] = merged[i];
     }
     if (threadIdx.x < kSimtHeads && head0 + threadIdx.x < a.heads) {
-        float* at = partial + ((row * a.heads + head0 + threadIdx.x) * splits + split) * (a.dim + 2) + a.dim;
+        float* at = partial + ((row * a.heads + head0 + threadIdx.x) * parts + part0 + split) * (a.dim + 2) + a.dim;
         at[0] = top[threadIdx.x]; at[1] = total[threadIdx.x];
     }
 }
@@ -209,6 +212,42 @@ static void turns_reserve(Device& d, size_t rows, size_t pairs) {
     d.turns = nullptr;
     SDB_CHECK(cudaMalloc(reinterpret_cast<void**>(&d.turns), rows * pairs * 2 * sizeof(double2)));
     d.turns_rows = rows; d.turns_pairs = pairs;
+}
+
+static void launch_simt(Device& d, const SparseArgs& args, const float* q_used, float* partial, size_t rows, size_t splits, size_t parts, size_t part0) {
+    const size_t groups = (args.heads + kSimtHeads - 1) / kSimtHeads;
+    const dim3 grid{unsigned(rows), unsigned(groups), unsigned(splits)};
+    const size_t shared = 2 * kSimtHeads * size_t(args.dim) * 4;
+    const int per_lane = int((args.dim + 31) / 32);
+    #define SDB_SIMT(N) do { \
+        SDB_CHECK(cudaFuncSetAttribute(sparse_simt_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared))); \
+        sparse_simt_kernel<N><<<grid, kSimtWarps * 32, shared, d.stream>>>(args, q_used, partial, parts, part0); } while (0)
+    if (per_lane <= 4) SDB_SIMT(4); else if (per_lane <= 8) SDB_SIMT(8); else if (per_lane <= 16) SDB_SIMT(16);
+    else if (per_lane <= 18) SDB_SIMT(18); else SDB_SIMT(32);
+    #undef SDB_SIMT
+    ++d.launches;
+    SDB_CHECK(cudaGetLastError());
+}
+
+// For the tcgen05 kernel: the window rows' share of every (row, head) as slot 0 of its `parts` partials, in exact FP32 arithmetic.
+void sparse_window_partial(Device& d, const SparseArgs& a, const float* q, size_t rows, size_t pairs, const double2* forward, float* rotated,
+                           float* partial, size_t parts) {
+    const float* q_used = q;
+    if (pairs) {
+        sparse_rotate_q_kernel<<<dim3(unsigned(a.heads), unsigned(rows)), 128, 0, d.stream>>>(q, a.heads, a.dim, pairs, forward, rotated);
+        ++d.launches;
+        q_used = rotated;
+    }
+    SparseArgs window = a;
+    window.selections = 0;   // (the key list of a row is then its window rows alone)
+    launch_simt(d, window, q_used, partial, rows, 1, parts, 0);
+}
+
+void sparse_combine(Device& d, const float* partial, size_t parts, size_t rows, size_t heads, size_t dim, const float* sinks, size_t pairs,
+                    const double2* inverse, float* out) {
+    sparse_combine_kernel<<<unsigned(rows * heads), 128, 0, d.stream>>>(partial, parts, heads, dim, sinks, pairs, inverse, out);
+    ++d.launches;
+    SDB_CHECK(cudaGetLastError());
 }
 
 // The tensor-core kernel holds dim 512 and 576 and needs 16-byte aligned BF16 rows (whole rows travel by bulk copies).
@@ -298,6 +337,13 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
         return 0;
     }
     const bool force_simt = env_flag("SDX_SPARSE_SIMT");
+    // (SDX_SPARSE_KERNEL=mma3, read at each call, keeps the mma.sync kernel where the tcgen05 kernel would run: the in-library A/B)
+    const char* form = std::getenv("SDX_SPARSE_KERNEL");
+    if (!force_simt && sparse_tc_supported(args) && !(form && std::string(form) == "mma3")) {
+        sparse_tc_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        SDB_CHECK(cudaGetLastError());
+        return 0;
+    }
     if (!force_simt && sparse_mma_supported(args)) {
         sparse_mma3_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         SDB_CHECK(cudaGetLastError());
@@ -320,17 +366,7 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
         q_used = rotated;
     }
     auto* partial = reinterpret_cast<float*>(work + q_bytes);
-    const dim3 grid{unsigned(rows), unsigned(groups), unsigned(splits)};
-    const size_t shared = 2 * kSimtHeads * size_t(dim) * 4;
-    const int per_lane = int((dim + 31) / 32);
-    #define SDB_SIMT(N) do { \
-        SDB_CHECK(cudaFuncSetAttribute(sparse_simt_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared))); \
-        sparse_simt_kernel<N><<<grid, kSimtWarps * 32, shared, value.stream>>>(args, q_used, partial); } while (0)
-    if (per_lane <= 4) SDB_SIMT(4); else if (per_lane <= 8) SDB_SIMT(8); else if (per_lane <= 16) SDB_SIMT(16);
-    else if (per_lane <= 18) SDB_SIMT(18); else SDB_SIMT(32);
-    #undef SDB_SIMT
-    ++value.launches;
-    SDB_CHECK(cudaGetLastError());
+    launch_simt(value, args, q_used, partial, rows, splits, 0, 0);
     sparse_combine_kernel<<<unsigned(rows * heads), 128, 0, value.stream>>>(partial, splits, heads, dim, sinks, pairs, inverse, out);
     ++value.launches;
     SDB_OP_END

@@ -9,10 +9,15 @@ from util import XorShift, bf16_round, close, sparse_attention_case
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture
-def form():
-    """The library's own choice of kernel (the tensor-core kernel wherever the shape allows it)."""
-    yield "default"
+@pytest.fixture(params=["default", "mma3"])
+def form(request):
+    """Which tensor-core kernel answers where both can: the library's own choice (the tcgen05 kernel for BF16 rows, head counts that
+    are multiples of 16 and short windows) or the mma.sync kernel for every shape."""
+    import os
+    if request.param != "default":
+        os.environ["SDX_SPARSE_KERNEL"] = request.param
+    yield request.param
+    os.environ.pop("SDX_SPARSE_KERNEL", None)
 
 
 def reference_case(rows, heads):
@@ -70,7 +75,8 @@ def test_benchmark_shape_small(gpu, form):
 
 @pytest.mark.parametrize("rows,heads,dim,window,selections,rope_dims,exact_q", [
     (3, 16, 576, 8, 200, 0, True), (8, 16, 576, 8, 2048, 64, True), (2, 128, 576, 1, 96, 0, True), (5, 24, 512, 128, 31, 64, False),
-    (1, 8, 512, 3, 0, 0, False), (2, 40, 576, 40, 65, 128, False)])
+    (1, 8, 512, 3, 0, 0, False), (2, 40, 576, 40, 65, 128, False), (4, 32, 576, 4, 300, 64, False), (2, 64, 512, 1, 128, 0, False),
+    (3, 48, 576, 2, 100, 128, True), (2, 80, 576, 16, 64, 0, True), (1, 16, 512, 1, 4000, 0, True)])
 def test_tensor_core_kernel_shapes(gpu, form, rows, heads, dim, window, selections, rope_dims, exact_q):
     """Head tiles of 16 and 32 with tails, spans with a causal window (config 4's layout), rope on BF16-exact and on F32 queries,
     partial tiles, no selection at all; each against the F64 oracle and against this library's FP32 kernel."""
