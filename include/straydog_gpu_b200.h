@@ -149,6 +149,12 @@ int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_
    never raised its counter within a second. Synchronises the handle's stream. */
 int sdx_decode_status(void* handle);
 
+/* For builds of the library with -DSDX_TRACE (python -m straydog_b200.build --define SDX_TRACE --out <path>): the cycle counters the
+   latent tcgen05 kernel's last launch on this handle left, eight int64 per CTA (total, the MMA thread's waits for a tile, for the
+   weights and for a free score buffer, the copy thread's wait for a free slot, tiles, 0, 0). Returns the number of CTAs written
+   (0 in an ordinary build). */
+int sdx_trace_read(void* handle, int64_t* out, uint64_t capacity);
+
 /* Causal prompt attention of a chunk: `rows` new tokens at positions first .. first + rows - 1 of a Q8_0 state
    (their K/V rows already written, e.g. by sdx_kv_write) attend positions 0 .. their own. q [rows][heads][256]
    FP16 and out [rows][heads][256] F32 are device pointers; heads / kv_heads is 1, 2, 4 or 8. The dense causal

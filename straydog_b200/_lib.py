@@ -63,6 +63,7 @@ SIGNATURES = {
     "sdx_decode_cuts": ([p, i32], i32),
     "sdx_qsa_cuts": ([pu64, u64, u64, u64, i32, u64, C.POINTER(C.c_uint32), u64, pu64], i32),
     "sdx_decode_status": ([p], i32),
+    "sdx_trace_read": ([p, C.POINTER(C.c_int64), u64], i32),
     "sdx_qsa_prompt": ([p, p, u64, u64, u64, u64, u64, f32, p, p], i32),
     "sdx_qsa_attention_rows": ([p, p, u64, u64, p, u64, u64, u64, u64, f32, p, p, u64, p, u64, p], i32),
     "sdx_attention_batch": ([p, pp, pu64, pu64, u64, u64, u64, f32, p, p, p, p], i32),

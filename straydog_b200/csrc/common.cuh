@@ -57,6 +57,7 @@ struct Device {
     void* work = nullptr; size_t work_bytes = 0;        // packed inputs / outputs of host-pointer entries
     void* partial = nullptr; size_t partial_bytes = 0;  // split partials of the decode kernels
     void* tables = nullptr; size_t tables_bytes = 0;    // work lists of the decode kernels
+    long long* trace = nullptr; size_t trace_ctas = 0;   // -DSDX_TRACE builds: the last traced launch's counters
     bool fixed_cuts = false;                            // the decode work list's cuts (sdx_decode_cuts)
     double* turns = nullptr; size_t turns_rows = 0, turns_pairs = 0;   // rope sincos table (forward, inverse)
     bool turns_ready = false; size_t turns_ready_rows = 0, turns_ready_pairs = 0;

@@ -214,13 +214,48 @@ static void turns_reserve(Device& d, size_t rows, size_t pairs) {
     d.turns_rows = rows; d.turns_pairs = pairs;
 }
 
+// The window rows' share of one (row, head), for the tcgen05 kernel: a warp walks the row's few window keys (lanes over the
+// columns), exact FP32 arithmetic, online softmax in the natural domain; the result is slot 0 of the pair's `parts` partials.
+template<int PER_LANE>
+__global__ void __launch_bounds__(256) sparse_window_kernel(const SparseArgs a, const float* __restrict__ q, float* __restrict__ partial, size_t rows, size_t parts) {
+    const size_t pair = size_t(blockIdx.x) * 8 + threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (pair >= rows * a.heads) return;
+    const size_t row = pair / a.heads;
+    const KeyList list = key_list(a, row);
+    float qv[PER_LANE], acc[PER_LANE];
+    #pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) { const size_t d = lane + 32 * j; qv[j] = d < a.dim ? q[pair * a.dim + d] : 0.0f; acc[j] = 0.0f; }
+    float m = -INFINITY, l = 0.0f;
+    for (size_t index = 0; index < list.raw_count; ++index) {
+        const float* key = key_pointer(a, list, row, index);
+        float k[PER_LANE], dot = 0.0f;
+        #pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) { const size_t d = lane + 32 * j; k[j] = d < a.dim ? key[d] : 0.0f; dot = fmaf(qv[j], k[j], dot); }
+        #pragma unroll
+        for (unsigned offset = 16; offset; offset /= 2) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+        const float score = dot * a.scale, next = fmaxf(m, score), correction = expf(m - next), p = expf(score - next);
+        l = fmaf(l, correction, p);
+        #pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) acc[j] = fmaf(acc[j], correction, p * k[j]);
+        m = next;
+    }
+    float* mine = partial + pair * parts * (a.dim + 2);
+    #pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) { const size_t d = lane + 32 * j; if (d < a.dim) mine[d] = acc[j]; }
+    if (lane == 0) { mine[a.dim] = m; mine[a.dim + 1] = l; }
+}
+
 static void launch_simt(Device& d, const SparseArgs& args, const float* q_used, float* partial, size_t rows, size_t splits, size_t parts, size_t part0) {
     const size_t groups = (args.heads + kSimtHeads - 1) / kSimtHeads;
     const dim3 grid{unsigned(rows), unsigned(groups), unsigned(splits)};
     const size_t shared = 2 * kSimtHeads * size_t(args.dim) * 4;
     const int per_lane = int((args.dim + 31) / 32);
+    // (the opt-in for more than 48 KB of dynamic shared memory is asked once per device and kernel, not per launch: a driver call)
     #define SDB_SIMT(N) do { \
-        SDB_CHECK(cudaFuncSetAttribute(sparse_simt_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared))); \
+        static size_t allowed[64] = {}; \
+        if (allowed[d.ordinal & 63] < shared) { \
+            SDB_CHECK(cudaFuncSetAttribute(sparse_simt_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(shared))); \
+            allowed[d.ordinal & 63] = shared; } \
         sparse_simt_kernel<N><<<grid, kSimtWarps * 32, shared, d.stream>>>(args, q_used, partial, parts, part0); } while (0)
     if (per_lane <= 4) SDB_SIMT(4); else if (per_lane <= 8) SDB_SIMT(8); else if (per_lane <= 16) SDB_SIMT(16);
     else if (per_lane <= 18) SDB_SIMT(18); else SDB_SIMT(32);
@@ -240,7 +275,11 @@ void sparse_window_partial(Device& d, const SparseArgs& a, const float* q, size_
     }
     SparseArgs window = a;
     window.selections = 0;   // (the key list of a row is then its window rows alone)
-    launch_simt(d, window, q_used, partial, rows, 1, parts, 0);
+    const unsigned blocks = unsigned((rows * a.heads + 7) / 8);
+    if (a.dim <= 512) sparse_window_kernel<16><<<blocks, 256, 0, d.stream>>>(window, q_used, partial, rows, parts);
+    else sparse_window_kernel<18><<<blocks, 256, 0, d.stream>>>(window, q_used, partial, rows, parts);
+    ++d.launches;
+    SDB_CHECK(cudaGetLastError());
 }
 
 void sparse_combine(Device& d, const float* partial, size_t parts, size_t rows, size_t heads, size_t dim, const float* sinks, size_t pairs,

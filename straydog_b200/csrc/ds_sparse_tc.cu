@@ -47,6 +47,15 @@ template<int DIM> struct Shape {
 
 enum Bar { kFull = 0, kFree = kSlots, kSFull = 2 * kSlots, kSFree = kSFull + 2, kPFull = kSFree + 2, kPFree = kPFull + 2, kDone = kPFree + 2, kBars = kDone + 1 };
 
+// Built with -DSDX_TRACE the kernel adds up, per CTA, the cycles its MMA thread and its first copy thread spend in each wait, and
+// leaves them behind the partials (eight 64-bit counters a CTA: total, wait for a tile, for the weights, for a free score buffer,
+// copy thread's wait for a free slot, tiles): the figures the profile summary of this kernel quotes.
+#if defined(SDX_TRACE)
+#define SDX_TRACE_ADD(slot, since) trace[slot] += clock64() - (since)
+#else
+#define SDX_TRACE_ADD(slot, since) ((void)0)
+#endif
+
 struct Args {
     SparseArgs a;
     const float* q;
@@ -56,11 +65,22 @@ struct Args {
     int* status;
     float* partial;          // [(row * heads + head) * parts + 1 + split][dim + 2]
     uint32_t parts, splits;
+    long long* trace;        // -DSDX_TRACE only
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
     return uint64_t((address & 0x3ffffu) >> 4) | (uint64_t(leading_bytes >> 4) << 16) | (uint64_t(stride_bytes >> 4) << 32) |
            (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+// The same descriptor from its two words: the high word (stride 1024 bytes between 8-row groups, version 1, 128-byte swizzle) never
+// changes, and the low word is (address >> 4) | (leading offset >> 4) << 16, so a descriptor a few bytes further on is one 32-bit add
+// away (the issuing thread does nothing else, and a descriptor built from scratch costs it a dozen dependent instructions).
+constexpr uint32_t kDescHigh = 0x40004040u;
+__device__ __forceinline__ uint32_t desc_low(uint32_t address, uint32_t leading_bytes) { return ((address & 0x3ffffu) >> 4) | ((leading_bytes >> 4) << 16); }
+__device__ __forceinline__ uint64_t desc_of(uint32_t low) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(low), "r"(kDescHigh));
+    return d;
 }
 // kind::f16 instruction descriptor: FP32 accumulator, BF16 A and B, each K-major or MN-major, shape M x N
 __device__ __forceinline__ uint32_t instr_desc(int m, int n, bool a_mn, bool b_mn) {
@@ -172,28 +192,46 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc_kernel(const Args g) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // ---- the CTA's 64 query rows: rotated (double), BF16, in the swizzled K-major layout; the low parts of the tail blocks ----
+    // ---- the CTA's 64 query rows: rotated (double), BF16, in the swizzled K-major layout; the low parts of the tail blocks. Only the
+    //      real head rows are read (four column pairs a thread in flight at a time); the others are zeros. ----
     {
         uint8_t* q_hi = smem + S::kOffQ;
         uint8_t* q_lo = smem + S::kOffQlo;
         const size_t plain = DIM - 2 * g.pairs, lo_from = DIM - 64 * nlo_blocks;
-        for (int i = tid; i < kRows * (DIM / 2); i += kThreads) {
-            const int h = i / (DIM / 2), col = 2 * (i % (DIM / 2));
-            float2 v = make_float2(0.0f, 0.0f);
-            if (h < nheads) {
-                const float* src = g.q + (row * a.heads + head0 + h) * DIM + col;   // (only known to be 4-byte aligned)
-                v = make_float2(src[0], src[1]);
-                if (size_t(col) >= plain) {
-                    const double2 turn = g.forward[row * g.pairs + (col - plain) / 2];
-                    const double x = v.x, y = v.y;
-                    v = make_float2(float(x * turn.x - y * turn.y), float(x * turn.y + y * turn.x));
+        for (int i = tid; i < (kRows - nheads) * kChunks; i += kThreads) {   // 16-byte pieces of the empty rows (all zeros: the swizzle does not matter)
+            const int piece = i % kChunks, empty_row = nheads + i / kChunks;
+            *reinterpret_cast<uint4*>(q_hi + (piece / 8) * (kRows * 128) + empty_row * 128 + (piece % 8) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        for (int i = tid; i < kRows * int(nlo_blocks) * 8; i += kThreads)
+            *reinterpret_cast<uint4*>(q_lo + i * 16) = make_uint4(0, 0, 0, 0);
+        __syncthreads();
+        const int real = nheads * (DIM / 2);
+        for (int base = 0; base < real; base += 4 * kThreads) {
+            float2 v[4];
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = base + k * kThreads + tid, h = i / (DIM / 2), col = 2 * (i % (DIM / 2));
+                v[k] = make_float2(0.0f, 0.0f);
+                if (i < real) {
+                    const float* src = g.q + (row * a.heads + head0 + h) * DIM + col;   // (only known to be 4-byte aligned)
+                    v[k] = make_float2(src[0], src[1]);
                 }
             }
-            const __nv_bfloat16 h0 = __float2bfloat16_rn(v.x), h1 = __float2bfloat16_rn(v.y);
-            *reinterpret_cast<__nv_bfloat162*>(q_hi + swizzled(kRows, h, col)) = __halves2bfloat162(h0, h1);
-            if (size_t(col) >= lo_from)
-                *reinterpret_cast<__nv_bfloat162*>(q_lo + swizzled(kRows, h, col - lo_from)) =
-                    __halves2bfloat162(__float2bfloat16_rn(v.x - __bfloat162float(h0)), __float2bfloat16_rn(v.y - __bfloat162float(h1)));
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = base + k * kThreads + tid, h = i / (DIM / 2), col = 2 * (i % (DIM / 2));
+                if (i >= real) continue;
+                if (size_t(col) >= plain) {
+                    const double2 turn = g.forward[row * g.pairs + (col - plain) / 2];
+                    const double x = v[k].x, y = v[k].y;
+                    v[k] = make_float2(float(x * turn.x - y * turn.y), float(x * turn.y + y * turn.x));
+                }
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(v[k].x), h1 = __float2bfloat16_rn(v[k].y);
+                *reinterpret_cast<__nv_bfloat162*>(q_hi + swizzled(kRows, h, col)) = __halves2bfloat162(h0, h1);
+                if (size_t(col) >= lo_from)
+                    *reinterpret_cast<__nv_bfloat162*>(q_lo + swizzled(kRows, h, col - lo_from)) =
+                        __halves2bfloat162(__float2bfloat16_rn(v[k].x - __bfloat162float(h0)), __float2bfloat16_rn(v[k].y - __bfloat162float(h1)));
+            }
         }
     }
     fence_proxy_async();   // (the tensor core reads these bytes through the async proxy)
@@ -320,45 +358,64 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc_kernel(const Args g) {
     } else if (warp == kMmaWarp) {
         // ================= the MMA issuer =================
         if (lane == 0) {
-            const uint32_t ring = smem_u32(smem + S::kOffRing), q_hi = smem_u32(smem + S::kOffQ), q_lo = smem_u32(smem + S::kOffQlo);
-            const uint32_t p_base = smem_u32(smem + S::kOffP);
+            long long trace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long started = clock64();
+            (void)started;
+            const uint32_t ring = smem_u32(smem + S::kOffRing);
+            const uint32_t q_hi = desc_low(smem_u32(smem + S::kOffQ), 16), q_lo = desc_low(smem_u32(smem + S::kOffQlo), 16);
+            const uint32_t p_low = desc_low(smem_u32(smem + S::kOffP), 16);
             const uint32_t idesc_s = instr_desc(kRows, kKeys, false, false), idesc_o = instr_desc(128, nh, true, false);
+            const int lo_first = S::kBlocks - int(nlo_blocks);
             for (uint32_t i = 0; i <= tiles; ++i) {
                 if (i < tiles) {
-                    const uint32_t b = i & 1, slot = i % kSlots, tile = ring + slot * S::kTile;
+                    const uint32_t b = i & 1, slot = i % kSlots, tile = desc_low(ring + slot * S::kTile, 16), s_tmem = tmem + 320 + b * 32;
+                    long long since = clock64();
                     if (i >= 2 && !wait(kSFree + b, ((i - 2) >> 1) & 1)) break;
+                    SDX_TRACE_ADD(3, since);
+                    since = clock64();
                     if (!wait(kFull + slot, (i / kSlots) & 1)) break;
+                    SDX_TRACE_ADD(1, since);
                     fence_proxy_async();   // (the copies wrote through the generic proxy)
                     tc_fence_after();
-                    #pragma unroll 1
+                    #pragma unroll
                     for (int blk = 0; blk < S::kBlocks; ++blk)
                         #pragma unroll
                         for (int kk = 0; kk < 4; ++kk)
-                            umma(tmem + 320 + b * 32, smem_desc(q_hi + blk * (kRows * 128) + kk * 32, 16, 1024),
-                                 smem_desc(tile + blk * (kKeys * 128) + kk * 32, 16, 1024), idesc_s, blk > 0 || kk > 0);
-                    #pragma unroll 1
-                    for (int lb = 0; lb < int(nlo_blocks); ++lb)
+                            umma(s_tmem, desc_of(q_hi + ((blk * (kRows * 128) + kk * 32) >> 4)), desc_of(tile + ((blk * (kKeys * 128) + kk * 32) >> 4)),
+                                 idesc_s, blk > 0 || kk > 0);
+                    #pragma unroll
+                    for (int lb = 0; lb < 2; ++lb) {
+                        if (lb >= int(nlo_blocks)) break;
                         #pragma unroll
                         for (int kk = 0; kk < 4; ++kk)
-                            umma(tmem + 320 + b * 32, smem_desc(q_lo + lb * (kRows * 128) + kk * 32, 16, 1024),
-                                 smem_desc(tile + (S::kBlocks - int(nlo_blocks) + lb) * (kKeys * 128) + kk * 32, 16, 1024), idesc_s, true);
+                            umma(s_tmem, desc_of(q_lo + ((lb * (kRows * 128) + kk * 32) >> 4)),
+                                 desc_of(tile + (((lo_first + lb) * (kKeys * 128) + kk * 32) >> 4)), idesc_s, true);
+                    }
                     umma_commit(&bars[kSFull + b]);
                 }
                 if (i >= 1) {
-                    const uint32_t j = i - 1, b = j & 1, slot = j % kSlots, tile = ring + slot * S::kTile;
+                    const uint32_t j = i - 1, b = j & 1, slot = j % kSlots;
+                    const uint32_t tile = desc_low(ring + slot * S::kTile, kKeys * 128), p_tile = p_low + ((b * (kRows * 128)) >> 4);
+                    const long long since = clock64();
                     if (!wait(kPFull + b, (j >> 1) & 1)) break;
+                    SDX_TRACE_ADD(2, since);
                     tc_fence_after();
-                    #pragma unroll 1
+                    #pragma unroll
                     for (int mt = 0; mt < S::kMTiles; ++mt)
                         #pragma unroll
                         for (int ks = 0; ks < kKeys / 16; ++ks)
-                            umma(tmem + mt * 64, smem_desc(tile + 2 * mt * (kKeys * 128) + ks * (16 * 128), kKeys * 128, 1024),
-                                 smem_desc(p_base + b * (kRows * 128) + ks * 32, 16, 1024), idesc_o, j > 0 || ks > 0);
+                            umma(tmem + mt * 64, desc_of(tile + ((2 * mt * (kKeys * 128) + ks * (16 * 128)) >> 4)), desc_of(p_tile + ((ks * 32) >> 4)),
+                                 idesc_o, j > 0 || ks > 0);
                     umma_commit(&bars[kFree + slot]);
                     umma_commit(&bars[kPFree + b]);
                     umma_commit(&bars[kDone]);
                 }
             }
+#if defined(SDX_TRACE)
+            trace[0] = clock64() - started; trace[5] = tiles;
+            long long* mine = g.trace + ((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+            for (int i = 0; i < 8; ++i) if (i != 4) mine[i] = trace[i];
+#endif
         }
     } else {
         // ================= the copy warps: 16-byte copies into the swizzled tile, a warp instruction = 512 bytes of one row =================
@@ -375,7 +432,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc_kernel(const Args g) {
         for (uint32_t t = 0; t < tiles; ++t) {
             const uint32_t slot = t % kSlots;
             const int32_t next = index_at(t + 1);   // (the list comes from HBM like the rows: asked for a tile ahead)
+            const long long since = clock64();
+            (void)since;
             if (t >= uint32_t(kSlots) && !wait(kFree + slot, (t / kSlots - 1) & 1)) break;
+#if defined(SDX_TRACE)
+            if (ctid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(g.trace + ((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + 4),
+                                     (unsigned long long)(clock64() - since));
+#endif
             const uint32_t live = __ballot_sync(0xffffffffu, at >= 0);
             if (ctid == 0) masks[slot] = live;
             const uint32_t tile = smem_u32(smem + S::kOffRing + slot * S::kTile);
@@ -407,9 +470,14 @@ void sparse_window_partial(Device& d, const SparseArgs& a, const float* q, size_
 void sparse_combine(Device& d, const float* partial, size_t parts, size_t rows, size_t heads, size_t dim, const float* sinks, size_t pairs,
                     const double2* inverse, float* out);
 
+// Where the tcgen05 kernel is the faster one: 128 heads or more a call, BF16 rows, a short window. Measured on a B200 (32 rows x
+// top-2048, dim 576): 128 heads 114 us against the mma.sync kernel's 146 us (which reads every row once per 16 heads: eight times);
+// 64 heads 74 us against 75 us; 16 heads 73 us against 29 us. The kernel is bound by the tensor pipe's instruction rate, not its
+// arithmetic: an instruction of 64 x 32 x 16 or 128 x 64 x 16 costs the pipe about as long as one four times its size (48 cycles at
+// the least, about 70 with these operands), and dim 576 leaves shared memory for tiles of 32 keys only.
 bool sparse_tc_supported(const SparseArgs& a) {
-    return (a.dim == 512 || a.dim == 576) && a.heads % 16 == 0 && a.selections >= 64 && a.window <= 16 && state_is_bf16(a.compressed) &&
-           reinterpret_cast<uintptr_t>(state_halves(a.compressed)) % 16 == 0;
+    return (a.dim == 512 || a.dim == 576) && a.heads % 16 == 0 && a.heads >= 128 && a.selections >= 64 && a.window <= 16 &&
+           state_is_bf16(a.compressed) && reinterpret_cast<uintptr_t>(state_halves(a.compressed)) % 16 == 0;
 }
 
 template<int DIM>
@@ -434,7 +502,12 @@ void sparse_tc_launch(Device& d, const SparseArgs& a, const float* q, const floa
     const size_t parts = splits + 1;   // part 0: the window rows (FP32 kernel)
     const size_t partial_bytes = checked_product({rows, a.heads, parts, a.dim + 2, 4});
     const size_t q_bytes = pairs ? (checked_product({rows, a.heads, a.dim, 4}) + 255) / 256 * 256 : 0;
-    auto* work = static_cast<uint8_t*>(ensure(d, d.partial, d.partial_bytes, q_bytes + partial_bytes));
+    size_t trace_bytes = 0;
+#if defined(SDX_TRACE)
+    const size_t trace_at = (q_bytes + partial_bytes + 255) / 256 * 256;
+    trace_bytes = 256 + splits * head_tiles * rows * 64;   // the counters follow the partials in the workspace
+#endif
+    auto* work = static_cast<uint8_t*>(ensure(d, d.partial, d.partial_bytes, q_bytes + partial_bytes + trace_bytes));
     auto* partial = reinterpret_cast<float*>(work + q_bytes);
     sparse_window_partial(d, a, q, rows, pairs, forward, reinterpret_cast<float*>(work), partial, parts);
     tcl::Args args{};
@@ -443,9 +516,25 @@ void sparse_tc_launch(Device& d, const SparseArgs& a, const float* q, const floa
     args.status = status_word(d);
     args.partial = partial;
     args.parts = uint32_t(parts); args.splits = uint32_t(splits);
+#if defined(SDX_TRACE)
+    args.trace = reinterpret_cast<long long*>(work + trace_at);
+    SDB_CHECK(cudaMemsetAsync(args.trace, 0, splits * head_tiles * rows * 64, d.stream));
+    d.trace = args.trace; d.trace_ctas = splits * head_tiles * rows;
+#endif
     if (a.dim == 576) launch_tc<576>(d, args, rows, head_tiles); else launch_tc<512>(d, args, rows, head_tiles);
     SDB_CHECK(cudaGetLastError());
     sparse_combine(d, partial, parts, rows, a.heads, a.dim, sinks, pairs, inverse, out);
 }
 
 }  // namespace sdb
+
+// The counters of the last traced launch on this handle (eight per CTA), for builds with -DSDX_TRACE; 0 CTAs in any other build.
+extern "C" int sdx_trace_read(void* handle, int64_t* out, uint64_t capacity) {
+    try {
+        auto& value = sdb::device(handle);
+        SDB_CHECK(cudaStreamSynchronize(value.stream));
+        const size_t ctas = std::min<size_t>(value.trace_ctas, size_t(capacity / 8));
+        if (ctas) SDB_CHECK(cudaMemcpy(out, value.trace, ctas * 64, cudaMemcpyDeviceToHost));
+        return int(ctas);
+    } catch (const std::exception& e) { sdb::last_error = e.what(); return -1; }
+}
