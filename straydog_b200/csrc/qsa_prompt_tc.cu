@@ -1,13 +1,13 @@
 // Causal prompt attention over Q8_0 K/V on the 5th-generation tensor cores (tcgen05.mma, accumulators
 // and the A operands in TMEM): the Blackwell-native form of sdx_qsa_prompt.
 //
-// Before the attention kernel a small kernel turns the Q8_0 rows the chunk can see into two FP16 planes in a
-// library-owned workspace that stays in L2 (67 MB for 16384 positions): hi = FP16(int8 * scale), the rounding of the
-// reference's own tensor-core kernel (gpu/kernels.cpp:46-54), and lo = int8 * scale - hi, the part that rounding drops
-// (an int8 times an FP16 scale has at most 18 significant bits, so hi + lo is the value itself). Every product is issued
-// twice, once per plane, into the same FP32 accumulator: K and V enter the tensor cores exactly, as they enter the
-// reference's FP32 kernels (gpu/sparse_attention_compute.hpp:177-415), and only the softmax weights are rounded to FP16.
-// Every 64-key tile is dequantised once per call instead of once per 16-token block.
+// K and V enter the tensor cores as two FP16 planes: hi = FP16(int8 * scale), the rounding of the reference's own tensor-core kernel
+// (gpu/kernels.cpp:46-54), and lo = int8 * scale - hi, the part that rounding drops (an int8 times an FP16 scale has at most 18
+// significant bits, so hi + lo is the value itself and one FP16 fused multiply-add gives lo exactly). Every product is issued
+// twice, once per plane, into the same FP32 accumulator: K and V enter exactly, as they enter the reference's FP32 kernels
+// (gpu/sparse_attention_compute.hpp:177-415), and only the softmax weights are rounded to FP16. The planes are made inside the
+// kernel from the raw Q8_0 rows: a CTA streams 272 bytes a row from L2, not the 1024 bytes of two FP16 planes (with the planes
+// prepared in memory by a kernel of their own, this kernel was bound by the L2's bandwidth at about 7 TB/s over all SMs).
 //
 // A CTA owns 128 M-rows: 128 / group consecutive query tokens x the `group` query heads of one K/V head.
 // It walks the causal key range in tiles of 64 keys:
@@ -15,55 +15,73 @@
 //   O[128 x 256] += P[128 x 64] . (V_hi + V_lo)     2 x 4 tcgen05.mma (M 128, N 256, K 16)
 // TMEM (all 512 columns): O in 0..255; two S buffers in 256..319 and 320..383; Q (FP16, two values a column) in
 // 384..511. P is written over the first 32 columns of the S buffer it was made from, so both products take their A
-// operand from TMEM and shared memory only holds K and V tiles: one ring of six 32 KB slots that the copy thread fills
+// operand from TMEM and shared memory only holds K and V tiles: one ring of five 32 KB slots that the dequantising warps fill
 // and the MMA thread drains in the same fixed order (K_hi, K_lo of tile i, then V_hi, V_lo of tile i - 1).
 //
-// Warp roles (10 warps):
+// Warp roles (14 warps):
 //   warps 0-7   softmax: two threads per M-row (32 of the tile's 64 columns each; warp w works on the TMEM lanes
 //               32 (w % 4).. a warp may touch). tcgen05.ld of the scores, mask, row maximum exchanged with the partner
 //               warp through shared memory, P rounded to FP16 and stored to TMEM; O is rescaled in TMEM only when a
 //               row's maximum has grown by more than 2^8 (the stale maximum stays exact arithmetic: weights are at
 //               most 256 and the final division uses the same maximum); epilogue O / l.
 //   warp 8      one thread issues every tcgen05.mma and commits them to mbarriers.
-//   warp 9      one thread feeds the ring: tensor-map bulk copies (TMA, 128-byte swizzle) of four
-//               [64 rows][128 bytes] boxes per slot, which is the K-major / MN-major operand layout the MMA reads.
-// S is double buffered, so the tensor pipe works on S(i+1) while the softmax warps work on S(i). Every wait is bounded; a wait that gives up raises a flag that ends all roles,
-// frees TMEM and reports through the status word.
+//   warp 9      one thread brings the raw rows: a bulk copy (TMA engine) of a tile's 64 consecutive rows of one plane
+//               (17408 contiguous bytes) into a ring of three raw slots.
+//   warps 10-13 dequantise a raw slot into an FP16 hi tile and an FP16 lo tile, written in the 128-byte-swizzled
+//               [64 rows][128 bytes] blocks that are the K-major / MN-major operand layout the MMA's descriptors read.
+// S is double buffered, so the tensor pipe works on S(i+1) while the softmax warps work on S(i). Every wait is bounded; a wait
+// that gives up raises a flag that ends all roles, frees TMEM and reports through the status word.
 #include "common.cuh"
 #include "../../include/straydog_gpu_b200.h"
 
 #include <algorithm>
-#include <cuda.h>   // CUtensorMap (the encode function is reached through cudaGetDriverEntryPoint: no link against the driver library)
 
 namespace sdb {
 namespace tc {
 
 constexpr int kM = 128, kN = 64, kD = 256;
-constexpr int kSoftmaxWarps = 8, kMmaWarp = 8, kTmaWarp = 9, kThreads = 320;   // 8 softmax warps, the MMA warp, the copy warp
+constexpr int kSoftmaxWarps = 8, kMmaWarp = 8, kTmaWarp = 9, kDequantWarp0 = 10, kDequantWarps = 4;
+constexpr int kThreads = 32 * (kDequantWarp0 + kDequantWarps);   // 8 softmax warps, the MMA warp, the copy warp, 4 dequantising warps
 constexpr int kKVBytes = kN * kD * 2;               // one operand tile: 64 positions x 256 FP16
-constexpr int kSlots = 6;                            // the operand ring
-constexpr int kOffRing = 0, kOffBars = kOffRing + kSlots * kKVBytes;
+constexpr int kSlots = 5;                            // the operand ring (FP16 tiles)
+constexpr int kRawSlots = 3, kRawBytes = kN * int(kv_row_q8);   // raw Q8_0 tiles: 64 rows of one plane, 17408 contiguous bytes
+constexpr int kOffRing = 0, kOffRaw = kOffRing + kSlots * kKVBytes, kOffBars = kOffRaw + kRawSlots * kRawBytes + 256;
 constexpr int kOffStats = kOffBars + 256;            // [2 halves][128 rows] floats exchanged between the two warps of a row block
 constexpr size_t kSmem = kOffStats + 2 * kM * 4 + 1024;   // + slack to align the base to 1024 bytes
 constexpr uint32_t kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;
 
 struct Args {
-    size_t padded;      // positions a plane of the FP16 workspace holds (a multiple of 64)
-    size_t first, rows, heads, kv_heads, group;
+    const uint8_t* state;   // 2 * kv_heads planes of `context` Q8_0 rows
+    size_t context, first, rows, heads, kv_heads, group;
     const __half* q;
     float* out;
     float scale_log2;
     int* status;
+    long long* trace;   // -DSDX_TRACE only
 };
 
-enum Bar { kFull = 0, kFree = kSlots, kSFull = 2 * kSlots, kSFree = kSFull + 2, kPFull = kSFree + 2, kPvDone = kPFull + 2, kBars = kPvDone + 1 };
+enum Bar { kFull = 0, kFree = kSlots, kSFull = 2 * kSlots, kSFree = kSFull + 2, kPFull = kSFree + 2, kPvDone = kPFull + 2,
+           kRawFull = kPvDone + 1, kRawFree = kRawFull + kRawSlots, kBars = kRawFree + kRawSlots };
 
-__device__ __forceinline__ uint64_t smem_desc(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
-    // start address, leading and stride byte offsets in 16-byte units; descriptor version 1; 128-byte swizzle
-    return uint64_t((address & 0x3ffffu) >> 4) | (uint64_t(leading_bytes >> 4) << 16) | (uint64_t(stride_bytes >> 4) << 32) |
-           (uint64_t(1) << 46) | (uint64_t(2) << 61);
+// A shared-memory operand descriptor: start address, leading and stride byte offsets in 16-byte units; descriptor version 1;
+// 128-byte swizzle. Its high word (stride 1024 bytes between 8-row groups, version, swizzle) never changes here and its low word is
+// (address >> 4) | (leading offset >> 4) << 16, so the descriptor a few bytes further on is one 32-bit add away: the issuing thread
+// does nothing else, and a descriptor built from scratch costs it a dozen dependent instructions per MMA.
+constexpr uint32_t kDescHigh = 0x40004040u;
+__device__ __forceinline__ uint32_t desc_low(uint32_t address, uint32_t leading_bytes) { return ((address & 0x3ffffu) >> 4) | ((leading_bytes >> 4) << 16); }
+__device__ __forceinline__ uint64_t desc_of(uint32_t low) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(low), "r"(kDescHigh));
+    return d;
 }
+// Built with -DSDX_TRACE the MMA thread adds up the cycles it spends in each of its waits (eight 64-bit counters a CTA: total, wait
+// for a tile, for the weights, for a free score buffer, 0, tiles): the figures the profile summary of this kernel quotes.
+#if defined(SDX_TRACE)
+#define SDX_TRACE_ADD(slot, since) trace[slot] += clock64() - (since)
+#else
+#define SDX_TRACE_ADD(slot, since) ((void)0)
+#endif
 // kind::f16 instruction descriptor: FP32 accumulator, FP16 A and B, A K-major, B K-major or MN-major, shape M x N
 __device__ __forceinline__ uint32_t instr_desc(int m, int n, bool b_mn_major) {
     return (1u << 4) | (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
@@ -122,8 +140,7 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 
 __device__ __forceinline__ void pair_barrier(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
 
-// K and V tiles come as FP16 from a pre-dequantised workspace by tensor-map bulk copies (128-byte swizzle).
-__global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a, const __grid_constant__ CUtensorMap kv_map) {
+__global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a) {
     constexpr int kBlockThreads = kThreads;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -139,8 +156,12 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
     const size_t r0 = block * tokens_per_block;
 
     if (tid == 0) {
-        // (every barrier is completed by one arrival - a copy's byte count or an MMA commit - except p_full: one arrival per softmax warp)
-        for (int i = 0; i < kBars; ++i) mbar_init(&bars[i], i == kPFull || i == kPFull + 1 ? kSoftmaxWarps : 1);
+        // (a barrier is completed by one arrival - a copy's byte count or an MMA commit - except p_full, one arrival per softmax warp, and
+        //  the barriers the dequantising warps arrive on, one arrival per such warp)
+        for (int i = 0; i < kBars; ++i) {
+            const bool by_dequant = (i >= kFull && i < kFull + kSlots) || (i >= kRawFree && i < kRawFree + kRawSlots);
+            mbar_init(&bars[i], i == kPFull || i == kPFull + 1 ? kSoftmaxWarps : by_dequant ? kDequantWarps : 1);
+        }
         *abort_flag = 0;
     }
     fence_barrier_init();
@@ -288,44 +309,51 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
         }
     } else if (warp == kMmaWarp) {
         // ================= the MMA issuer =================
-        // The ring is drained in the order the copy thread fills it: item t sits in slot t % 6, in its (t / 6)-th use.
+        // The ring is drained in the order the dequantising warps fill it: item t sits in slot t % 5, in its (t / 5)-th use.
         if (lane == 0) {
+            long long trace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long started = clock64();
+            (void)started;
             const uint32_t ring = smem_u32(smem + kOffRing);
             const uint32_t idesc_s = instr_desc(kM, kN, false), idesc_o = instr_desc(kM, kD, true);
             uint32_t item = 0;
             bool alive = true;
             for (uint32_t i = 0; i <= tiles && alive; ++i) {
                 if (i < tiles) {
-                    const uint32_t buffer = i & 1;
+                    const uint32_t buffer = i & 1, s_tmem = tmem + 256 + buffer * 64;
+                    long long since = clock64();
                     if (i >= 2 && !wait(kSFree + buffer, ((i - 2) >> 1) & 1)) break;
+                    SDX_TRACE_ADD(3, since);
                     #pragma unroll 1
                     for (int part = 0; part < 2 && alive; ++part, ++item) {   // K_hi, then K_lo into the same accumulator
-                        const uint32_t slot = item % kSlots;
+                        const uint32_t slot = item % kSlots, tile = desc_low(ring + slot * kKVBytes, 16);
+                        since = clock64();
                         if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
+                        SDX_TRACE_ADD(1, since);
                         tc_fence_after();
                         #pragma unroll
-                        for (int kk = 0; kk < 16; ++kk) {
-                            const uint64_t b_desc = smem_desc(ring + slot * kKVBytes + (kk / 4) * (kN * 128) + (kk % 4) * 32, 16, 1024);
-                            umma_a_tmem(tmem + 256 + buffer * 64, tmem + 384 + kk * 8, b_desc, idesc_s, part > 0 || kk > 0);
-                        }
+                        for (int kk = 0; kk < 16; ++kk)
+                            umma_a_tmem(s_tmem, tmem + 384 + kk * 8, desc_of(tile + (((kk / 4) * (kN * 128) + (kk % 4) * 32) >> 4)), idesc_s, part > 0 || kk > 0);
                         umma_commit(&bars[kFree + slot]);
                     }
                     if (!alive) break;
                     umma_commit(&bars[kSFull + buffer]);
                 }
                 if (i >= 1) {
-                    const uint32_t j = i - 1, buffer = j & 1;
+                    const uint32_t j = i - 1, buffer = j & 1, p_tmem = tmem + 256 + buffer * 64;
+                    long long since = clock64();
                     if (!wait(kPFull + buffer, (j >> 1) & 1)) break;
+                    SDX_TRACE_ADD(2, since);
                     #pragma unroll 1
                     for (int part = 0; part < 2 && alive; ++part, ++item) {   // V_hi, then V_lo
-                        const uint32_t slot = item % kSlots;
+                        const uint32_t slot = item % kSlots, tile = desc_low(ring + slot * kKVBytes, kN * 128);
+                        since = clock64();
                         if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
+                        SDX_TRACE_ADD(1, since);
                         tc_fence_after();
                         #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const uint64_t b_desc = smem_desc(ring + slot * kKVBytes + kk * (16 * 128), kN * 128, 1024);
-                            umma_a_tmem(tmem, tmem + 256 + buffer * 64 + kk * 8, b_desc, idesc_o, j > 0 || part > 0 || kk > 0);
-                        }
+                        for (int kk = 0; kk < 4; ++kk)
+                            umma_a_tmem(tmem, p_tmem + kk * 8, desc_of(tile + ((kk * (16 * 128)) >> 4)), idesc_o, j > 0 || part > 0 || kk > 0);
                         umma_commit(&bars[kFree + slot]);
                     }
                     if (!alive) break;
@@ -333,34 +361,82 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
                     umma_commit(&bars[kSFree + buffer]);   // P sat in the S buffer: free once the product has read it
                 }
             }
+#if defined(SDX_TRACE)
+            trace[0] = clock64() - started; trace[5] = tiles;
+            long long* mine = a.trace + (size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+            for (int c = 0; c < 8; ++c) mine[c] = trace[c];
+#endif
         }
-    } else {
-        // ================= the copy thread: FP16 tiles by TMA =================
-        // Workspace rows: [hi | lo][plane][padded positions]; a tile never leaves its plane because `padded` is a multiple of 64.
-        if (warp == kTmaWarp && lane == 0) {
-            const size_t planes = 2 * a.kv_heads;
+    } else if (warp == kTmaWarp) {
+        // ================= the copy thread: raw Q8_0 rows by bulk copies =================
+        // Raw item r is the K rows of tile i or the V rows of tile i - 1, in the order the MMA thread wants them: K(0), K(1), V(0), K(2), ...
+        if (lane == 0) {
             uint32_t item = 0;
             bool ok = true;
             for (uint32_t i = 0; i <= tiles && ok; ++i) {
                 #pragma unroll 1
-                for (int which = 0; which < 4 && ok; ++which) {   // K_hi, K_lo of tile i; V_hi, V_lo of tile i - 1
-                    const bool value = which >= 2;
+                for (int which = 0; which < 2 && ok; ++which) {
+                    const bool value = which == 1;
                     if (value ? i == 0 : i == tiles) continue;
-                    const uint32_t tile_index = value ? i - 1 : i, part = which & 1;
-                    const size_t plane = value ? a.kv_heads + kv : kv;
-                    const int32_t row0 = int32_t((part * planes + plane) * a.padded + size_t(tile_index) * kN);
-                    const uint32_t slot = item % kSlots;
-                    if (item >= uint32_t(kSlots) && !wait(kFree + slot, (item / kSlots - 1) & 1)) { ok = false; break; }
-                    uint64_t* bar = &bars[kFull + slot];
-                    uint8_t* tile = smem + kOffRing + slot * kKVBytes;
-                    mbar_expect_tx(bar, kKVBytes);
-                    #pragma unroll
-                    for (int d = 0; d < 4; ++d)   // four 64-column blocks of [64 rows][128 bytes]
-                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                     ::"r"(smem_u32(tile + d * (kN * 128))), "l"(&kv_map), "r"(64 * d), "r"(row0), "r"(smem_u32(bar)) : "memory");
+                    const uint32_t tile_index = value ? i - 1 : i, slot = item % kRawSlots;
+                    const size_t plane = value ? a.kv_heads + kv : kv, begin = size_t(tile_index) * kN;
+                    const uint32_t rows = uint32_t(min(size_t(kN), keys_total - begin));
+                    if (item >= uint32_t(kRawSlots) && !wait(kRawFree + slot, (item / kRawSlots - 1) & 1)) { ok = false; break; }
+                    mbar_expect_tx(&bars[kRawFull + slot], rows * kv_row_q8);
+                    bulk_g2s(smem + kOffRaw + slot * kRawBytes, a.state + (plane * a.context + begin) * kv_row_q8, rows * kv_row_q8, &bars[kRawFull + slot]);
                     ++item;
                 }
             }
+        }
+    } else {
+        // ================= the dequantising warps: a raw slot -> an FP16 hi tile and an FP16 lo tile =================
+        // Thread t takes half a row (row t / 2, columns 128 (t % 2) ..): eight 16-byte pieces of raw values, four block scales.
+        const int dt = tid - 32 * kDequantWarp0, row = dt / 2, half = dt % 2;
+        const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));   // 1152 = 1024 + 128
+        const uint32_t total_items = 2 * tiles;
+        for (uint32_t item = 0; item < total_items; ++item) {
+            const uint32_t raw_slot = item % kRawSlots, hi_slot = (2 * item) % kSlots, lo_slot = (2 * item + 1) % kSlots;
+            // which tile the item is (K(0), K(1), V(0), K(2), V(1), ..., V(tiles - 1)) and how many of its 64 rows exist
+            const uint32_t tile_index = item == 0 ? 0u : item + 1 == total_items ? tiles - 1 : (item & 1 ? (item + 1) / 2 : item / 2 - 1);
+            const uint32_t rows = uint32_t(min(size_t(kN), keys_total - size_t(tile_index) * kN));
+            if (!wait(kRawFull + raw_slot, (item / kRawSlots) & 1)) break;
+            if (2 * item >= uint32_t(kSlots) && !wait(kFree + hi_slot, ((2 * item) / kSlots - 1) & 1)) break;
+            if (2 * item + 1 >= uint32_t(kSlots) && !wait(kFree + lo_slot, ((2 * item + 1) / kSlots - 1) & 1)) break;
+            const uint8_t* raw = smem + kOffRaw + raw_slot * kRawBytes + row * kv_row_q8;
+            uint8_t* hi_tile = smem + kOffRing + hi_slot * kKVBytes;
+            uint8_t* lo_tile = smem + kOffRing + lo_slot * kKVBytes;
+            const bool exists = uint32_t(row) < rows;   // (rows past the chunk's last position: zeros, never stale bytes)
+            uint2 scales = make_uint2(0, 0);
+            if (exists) scales = *reinterpret_cast<const uint2*>(raw + 256 + half * 8);
+            #pragma unroll
+            for (int piece = 0; piece < 8; ++piece) {
+                uint4 bytes = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+                if (exists) bytes = *reinterpret_cast<const uint4*>(raw + half * 128 + piece * 16);
+                const uint32_t scale_word = piece < 4 ? scales.x : scales.y;
+                const __half scale_h = __ushort_as_half(uint16_t((piece / 2) & 1 ? scale_word >> 16 : scale_word & 0xffffu));
+                const __half2 scale2 = __halves2half2(scale_h, scale_h);
+                const uint32_t words[4] = {bytes.x ^ 0x80808080u, bytes.y ^ 0x80808080u, bytes.z ^ 0x80808080u, bytes.w ^ 0x80808080u};
+                uint32_t hi[8], lo[8];
+                #pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t pair0 = prmt(words[w], 0x64646464u, 0x4140u), pair1 = prmt(words[w], 0x64646464u, 0x4342u);
+                    const __half2 v0 = __hsub2(*reinterpret_cast<const __half2*>(&pair0), bias), v1 = __hsub2(*reinterpret_cast<const __half2*>(&pair1), bias);
+                    const __half2 h0 = __hmul2(v0, scale2), h1 = __hmul2(v1, scale2);
+                    const __half2 l0 = __hfma2(v0, scale2, __hneg2(h0)), l1 = __hfma2(v1, scale2, __hneg2(h1));   // exact: the product has 18 bits at most
+                    hi[2 * w] = *reinterpret_cast<const uint32_t*>(&h0); hi[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&h1);
+                    lo[2 * w] = *reinterpret_cast<const uint32_t*>(&l0); lo[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&l1);
+                }
+                // 16 values = two 16-byte pieces of the row's 128-byte segment in block (column / 64), swizzled by the row
+                const int column = half * 128 + piece * 16, block = column / 64, c0 = (column % 64) / 8;
+                const uint32_t at0 = block * (kN * 128) + row * 128 + (((c0) ^ (row % 8)) * 16), at1 = block * (kN * 128) + row * 128 + (((c0 + 1) ^ (row % 8)) * 16);
+                *reinterpret_cast<uint4*>(hi_tile + at0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(hi_tile + at1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                *reinterpret_cast<uint4*>(lo_tile + at0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4*>(lo_tile + at1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+            }
+            fence_proxy_async();   // (the tensor core reads the tiles through the async proxy)
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&bars[kFull + hi_slot]); mbar_arrive(&bars[kFull + lo_slot]); mbar_arrive(&bars[kRawFree + raw_slot]); }
         }
     }
     tc_fence_before();
@@ -373,63 +449,10 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
 
 }  // namespace tc
 
-// Q8_0 rows -> two FP16 planes of rows [hi | lo][plane][position][256] (512 bytes a row), once per call: hi = FP16(int8 * scale),
-// lo = FP16(int8 * scale - hi) (the FP32 product is exact: 7 x 11 significant bits). Positions at or past `valid` (up to `padded`,
-// the last tile's end) are written as zeros, so a tile never holds bits nobody wrote.
-__global__ void __launch_bounds__(256) prompt_dequant_kernel(const uint8_t* __restrict__ state, size_t context, size_t planes, size_t valid,
-                                                             size_t padded, __half* __restrict__ out) {
-    const size_t pieces = planes * padded * 16;   // 16-byte raw pieces
-    const size_t lo_offset = planes * padded * 256;
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < pieces; i += size_t(gridDim.x) * blockDim.x) {
-        const size_t piece = i % 16, position = (i / 16) % padded, plane = i / (16 * padded);
-        uint32_t hi[8] = {0, 0, 0, 0, 0, 0, 0, 0}, lo[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (position < valid) {
-            const uint8_t* row = state + (plane * context + position) * kv_row_q8;
-            const uint4 bytes = __ldg(reinterpret_cast<const uint4*>(row + piece * 16));
-            const float scale = __half2float(__ldg(reinterpret_cast<const __half*>(row + 256) + piece / 2));
-            const uint32_t words[4] = {bytes.x, bytes.y, bytes.z, bytes.w};
-            #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                __half h[4], l[4];
-                #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    const float x = __fmul_rn(float(int8_t(words[w] >> (8 * b))), scale);
-                    h[b] = __float2half_rn(x);
-                    l[b] = __float2half_rn(__fsub_rn(x, __half2float(h[b])));
-                }
-                hi[2 * w] = uint32_t(__half_as_ushort(h[0])) | uint32_t(__half_as_ushort(h[1])) << 16;
-                hi[2 * w + 1] = uint32_t(__half_as_ushort(h[2])) | uint32_t(__half_as_ushort(h[3])) << 16;
-                lo[2 * w] = uint32_t(__half_as_ushort(l[0])) | uint32_t(__half_as_ushort(l[1])) << 16;
-                lo[2 * w + 1] = uint32_t(__half_as_ushort(l[2])) | uint32_t(__half_as_ushort(l[3])) << 16;
-            }
-        }
-        uint4* target = reinterpret_cast<uint4*>(out + (plane * padded + position) * 256 + piece * 16);
-        target[0] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        target[1] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-        uint4* low = reinterpret_cast<uint4*>(out + lo_offset + (plane * padded + position) * 256 + piece * 16);
-        low[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        low[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-    }
-}
-
-// cuTensorMapEncodeTiled through the runtime (no link against the driver library)
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiled encode_tiled() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* entry = nullptr;
-        cudaDriverEntryPointQueryResult result;
-        SDB_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result));
-        if (!entry || result != cudaDriverEntryPointSuccess) throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
-        fn = reinterpret_cast<EncodeTiled>(entry);
-    }
-    return fn;
-}
-
 static void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, size_t first, size_t rows, size_t heads, size_t kv_heads,
                              float scale, const void* q, float* out) {
     tc::Args args{};
+    args.state = state; args.context = context;
     args.first = first; args.rows = rows; args.heads = heads; args.kv_heads = kv_heads; args.group = heads / kv_heads;
     args.q = static_cast<const __half*>(q);
     args.out = out;
@@ -442,26 +465,15 @@ static void launch_prompt_tc(Device& d, const uint8_t* state, size_t context, si
         SDB_CHECK(cudaFuncSetAttribute(tc::qsa_prompt_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(tc::kSmem)));
         configured[d.ordinal & 63] = true;
     }
-    CUtensorMap map{};
-    // FP16 hi and lo copies of the positions this chunk can see, in a library-owned workspace that is grown on the first call of
-    // a size and sits outside the handle's budget (16384 positions x 4 planes x 2 x 512 bytes = 67 MB for the benchmark's chunk:
-    // L2-sized). Its extent follows the positions the chunk sees, rounded up to whole tiles, not the state's context.
-    const size_t planes = 2 * kv_heads, valid = first + rows;
-    const size_t padded = (valid + tc::kN - 1) / tc::kN * tc::kN;
-    args.padded = padded;
-    auto* fp16 = static_cast<__half*>(ensure(d, d.work, d.work_bytes, 2 * planes * padded * 512));
-    const unsigned blocks = unsigned(std::min<size_t>((planes * padded * 16 + 255) / 256, size_t(d.sms) * 16));
-    prompt_dequant_kernel<<<blocks, 256, 0, d.stream>>>(state, context, planes, valid, padded, fp16);
-    ++d.launches;
-    SDB_CHECK(cudaGetLastError());
-    const cuuint64_t dims[2] = {256, cuuint64_t(2 * planes * padded)};
-    const cuuint64_t strides[1] = {512};
-    const cuuint32_t box[2] = {64, cuuint32_t(tc::kN)}, element_strides[2] = {1, 1};
-    const CUresult encoded = encode_tiled()(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, fp16, dims, strides, box, element_strides,
-                                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (encoded != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string(int(encoded)));
-    tc::qsa_prompt_tc_kernel<<<grid, tc::kThreads, tc::kSmem, d.stream>>>(args, map);
+#if defined(SDX_TRACE)
+    {
+        const size_t ctas = size_t(grid.x) * grid.y;
+        args.trace = static_cast<long long*>(ensure(d, d.work, d.work_bytes, ctas * 64));
+        SDB_CHECK(cudaMemsetAsync(args.trace, 0, ctas * 64, d.stream));
+        d.trace = args.trace; d.trace_ctas = ctas;
+    }
+#endif
+    tc::qsa_prompt_tc_kernel<<<grid, tc::kThreads, tc::kSmem, d.stream>>>(args);
     ++d.launches;
 }
 
