@@ -75,6 +75,35 @@ int sd_op_sparse_attention(void* handle, const float* q, const float* raw, uint6
                            uint64_t window, const float* compressed, uint64_t compressed_rows, const int32_t* selected,
                            uint64_t selections, const float* sinks, uint64_t rows, uint64_t heads, uint64_t dim, float scale,
                            uint64_t rope_dims, const float* frequencies, float* scratch, uint64_t scratch_bytes, float* out);
+/* gpu/straydog_gpu.h:399-406. The drafter's noncausal block attention: q / out [slots][heads][512] (1..5 slots, 1..64 heads), K = V ring
+   [128][512], the block's keys [slots][512], sinks [heads]; rope already applied. Every query sees history positions
+   [anchor - history, anchor) of the ring and ALL block keys; history 0..128 <= anchor <= INT32_MAX; anchor_at (device, or null)
+   overrides `anchor` at run time; scale 1 / sqrt(512); the sink enters the maximum and the denominator only. */
+int sd_op_dspark_attention(void* handle, const float* q, const float* ring, const float* block, const float* sinks, uint64_t heads,
+                           uint64_t slots, uint32_t anchor, const int32_t* anchor_at, uint64_t history, float* out);
+/* ---- the producers of the latent attention's rows and index lists (DeepSeek-V4.1's indexer) ---- */
+/* gpu/straydog_gpu.h:271. The last rope_dims values of each of rows x vectors vectors of `width`, rotated in adjacent pairs by
+   positions[row] * frequencies[pair] (the angle times -1.0 with `inverse`), in double, in place. */
+int sd_op_rope(void* handle, float* x, uint64_t rows, uint64_t vectors, uint64_t width, uint64_t rope_dims, const int32_t* positions,
+               const float* frequencies, int inverse);
+/* gpu/straydog_gpu.h:407. `ratio` consecutive rows pooled into one per group by a per-channel softmax of the gate (no gate: ratio 1). */
+int sd_op_compress(void* handle, const float* kv, const float* gate, uint64_t groups, uint64_t ratio, uint64_t dim, float* out);
+/* gpu/straydog_gpu.h:408. scores[row][g] = scale * sum_h relu(q[row][h] . keys[g]) * weights[row][h] for g < visible[row], -inf beyond;
+   heads <= 64; `keys` may carry the BF16 tag in bit 0. */
+int sd_op_index_scores(void* handle, const float* q, const float* keys, const float* weights, const int32_t* visible, uint64_t rows,
+                       uint64_t groups, uint64_t heads, uint64_t dim, float scale, float* scores);
+/* gpu/straydog_gpu.h:410-414. Each row's `blocks` blocks of `block` groups whose highest score is highest (the block of the row's last
+   visible group always kept, blocks of only -inf never), in index order, -1 past the last; scratch holds rows * ceil(groups / block)
+   floats. */
+int sd_op_index_candidates(void* handle, const float* scores, const int32_t* visible, uint64_t rows, uint64_t groups, uint64_t blocks,
+                           uint64_t block, int32_t* out, float* scratch, uint64_t scratch_bytes);
+/* gpu/straydog_gpu.h:415-419. sd_op_rope of q (q itself unchanged), sd_op_index_scores and sd_op_top_k in one call: the same scores and
+   indices. With candidates (rows x blocks) a row's groups scored and chosen are its candidates' (scores rows x blocks * block in
+   candidate order), the indices the groups'. */
+int sd_op_index_select(void* handle, const float* q, const float* keys, const float* weights, const int32_t* visible, uint64_t rows,
+                       uint64_t groups, uint64_t heads, uint64_t dim, float scale, uint64_t rope_dims, const int32_t* positions,
+                       const float* frequencies, float* scores, uint64_t k, int32_t* out, const int32_t* candidates, uint64_t blocks,
+                       uint64_t block);
 /* gpu/straydog_gpu.h:409 */
 int sd_op_top_k(void* handle, const float* scores, uint64_t rows, uint64_t groups, uint64_t k, int32_t* out);
 /* gpu/straydog_gpu.h:459 */

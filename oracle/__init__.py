@@ -35,6 +35,11 @@ _sig("orc_gqa_decode_q8", [_p, _u64, _u64, _u64, _u64, _p, _f32, _i32, _p])
 _sig("orc_gqa_prompt_q8", [_p, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _p, _f32, _i32, _p])
 _sig("orc_op_attention", [_p, _p, _p, _u64, _p, _u64, _u64, _u64, _u64, _f32, _p, _p, _p, _p])
 _sig("orc_sparse_attention", [_p, _p, _u64, _p, _u64, _p, _i32, _p, _u64, _p, _u64, _u64, _u64, _f32, _u64, _p, _i32, _p])
+_sig("orc_dspark_attention", [_p, _p, _p, _p, _u64, _u64, _u64, _u64, _i32, _p])
+_sig("orc_rope", [_p, _u64, _u64, _u64, _u64, _p, _p, _i32])
+_sig("orc_compress", [_p, _p, _u64, _u64, _u64, _p])
+_sig("orc_index_scores", [_p, _p, _i32, _p, _p, _u64, _u64, _u64, _u64, _f32, _p, _u64, _u64, _p])
+_sig("orc_index_block_tops", [_p, _p, _u64, _u64, _u64, _p])
 _sig("orc_top_k", [_p, _u64, _u64, _u64, _p])
 _sig("orc_to_bf16", [_p, _u64, _p])
 _sig("orc_threads", [], _i32)
@@ -142,6 +147,71 @@ def sparse_attention(q, raw, raw_rows, positions, window, compressed, selected, 
     _lib.orc_sparse_attention(_ptr(q), _ptr(raw), raw_rows, _ptr(positions), window, _ptr(compressed), int(bf16), _ptr(selected),
                               selections, _ptr(sinks), rows, heads, dim, scale, rope_dims, _ptr(frequencies), int(f64), _ptr(out))
     return out
+
+
+def dspark_attention(q, ring, block, sinks, heads, slots, anchor, history, f64=False):
+    """q [slots, heads, 512], ring [128, 512], block [>= slots, 512], sinks [>= heads] F32 -> out [slots, heads, 512]."""
+    q, ring, block, sinks = (np.ascontiguousarray(x, np.float32) for x in (q, ring, block, sinks))
+    out = np.empty((slots, heads, 512), np.float32)
+    _lib.orc_dspark_attention(_ptr(q), _ptr(ring), _ptr(block), _ptr(sinks), heads, slots, anchor, history, int(f64), _ptr(out))
+    return out
+
+
+def rope(x, positions, frequencies, inverse=False):
+    """x [rows, vectors, width] F32 (a rotated copy is returned), rope over the last 2 * len(frequencies) columns."""
+    x = np.array(x, np.float32, order="C")
+    rows, vectors, width = x.shape
+    positions, frequencies = np.ascontiguousarray(positions, np.int32), np.ascontiguousarray(frequencies, np.float32)
+    _lib.orc_rope(_ptr(x), rows, vectors, width, 2 * frequencies.size, _ptr(positions), _ptr(frequencies), int(inverse))
+    return x
+
+
+def compress(kv, gate, ratio):
+    """kv, gate [groups * ratio, dim] F32 -> [groups, dim]."""
+    kv = np.ascontiguousarray(kv, np.float32)
+    gate = None if gate is None else np.ascontiguousarray(gate, np.float32)
+    groups, dim = kv.shape[0] // ratio, kv.shape[1]
+    out = np.empty((groups, dim), np.float32)
+    _lib.orc_compress(_ptr(kv), _ptr(gate), groups, ratio, dim, _ptr(out))
+    return out
+
+
+def index_scores(q, keys, weights, visible, scale, candidates=None, block=1):
+    """q [rows, heads, dim] F32, keys [groups, dim] F32 or BF16 halves (uint16), weights [rows, heads], visible [rows] ->
+    scores [rows, groups], or [rows, blocks * block] in candidate order with candidates [rows, blocks]."""
+    q, weights, visible = np.ascontiguousarray(q, np.float32), np.ascontiguousarray(weights, np.float32), np.ascontiguousarray(visible, np.int32)
+    bf16 = keys.dtype == np.uint16
+    keys = np.ascontiguousarray(keys, np.uint16 if bf16 else np.float32)
+    rows, heads, dim = q.shape
+    groups = keys.shape[0]
+    blocks = 0
+    if candidates is not None:
+        candidates = np.ascontiguousarray(candidates, np.int32)
+        blocks = candidates.shape[1]
+    out = np.empty((rows, blocks * block if blocks else groups), np.float32)
+    _lib.orc_index_scores(_ptr(q), _ptr(keys), int(bf16), _ptr(weights), _ptr(visible), rows, groups, heads, dim, scale, _ptr(candidates), blocks, block, _ptr(out))
+    return out
+
+
+def index_candidates(scores, visible, blocks, block):
+    """scores [rows, groups] -> candidates [rows, blocks]: the top blocks by their highest score, in index order, -1 past the last."""
+    scores, visible = np.ascontiguousarray(scores, np.float32), np.ascontiguousarray(visible, np.int32)
+    rows, groups = scores.shape
+    tops = np.empty((rows, (groups + block - 1) // block), np.float32)
+    _lib.orc_index_block_tops(_ptr(scores), _ptr(visible), rows, groups, block, _ptr(tops))
+    return top_k(tops, blocks)
+
+
+def index_select(q, keys, weights, visible, scale, positions, frequencies, k, candidates=None, block=1):
+    """gpu/ops.hpp:1978-2300 by its contract (crates/straydog-engine/tests/fused_gpu.rs:391-431): rope, scores, top k -> (scores, indices);
+    with candidates the indices are the groups' (gpu/ops.hpp:1967-1975)."""
+    rotated = rope(q, positions, frequencies) if len(frequencies) else np.ascontiguousarray(q, np.float32)
+    scores = index_scores(rotated, keys, weights, visible, scale, candidates, block)
+    picked = top_k(scores, k)
+    if candidates is not None:
+        c = np.take_along_axis(np.asarray(candidates, np.int64), np.maximum(picked, 0) // block, axis=1)
+        picked = np.where(picked < 0, -1, c * block + np.maximum(picked, 0) % block).astype(np.int32)
+    return scores, picked
 
 
 def top_k(scores, k):

@@ -461,6 +461,132 @@ void orc_top_k(const float* scores, uint64_t rows, uint64_t groups, uint64_t k, 
     }
 }
 
+// gpu/ops.hpp:107-120 (op_rope_kernel): the last 2 * pairs values of each of rows x vectors vectors of `width`, rotated in adjacent
+// pairs by positions[row] * frequencies[pair] (times -1.0 with `inverse`), angle and rotation in double, in place.
+void orc_rope(float* x, uint64_t rows, uint64_t vectors, uint64_t width, uint64_t rope_dims, const int32_t* positions,
+              const float* frequencies, int inverse) {
+    const uint64_t pairs = rope_dims / 2;
+    for (uint64_t row = 0; row < rows; ++row)
+        for (uint64_t vector = 0; vector < vectors; ++vector)
+            for (uint64_t pair = 0; pair < pairs; ++pair) {
+                float* v = x + (row * vectors + vector) * width + (width - rope_dims) + 2 * pair;
+                const double angle = double(positions[row]) * double(frequencies[pair]) * (inverse ? -1.0 : 1.0);
+                const double s = std::sin(angle), c = std::cos(angle), a = v[0], b = v[1];
+                v[0] = float(a * c - b * s);
+                v[1] = float(a * s + b * c);
+            }
+}
+
+// gpu/ops.hpp:1679-1695 (op_compress_kernel): `ratio` rows pooled per group and channel by the softmax of the gate; the weighted sum
+// one chain of fused multiply-adds over the rows in order (what the kernel's `acc += w * kv` compiles to), the weights' sum plain adds.
+void orc_compress(const float* kv, const float* gate, uint64_t groups, uint64_t ratio, uint64_t dim, float* out) {
+    for (uint64_t group = 0; group < groups; ++group)
+        for (uint64_t col = 0; col < dim; ++col) {
+            if (!gate) { out[group * dim + col] = kv[group * dim + col]; continue; }
+            float top = -INFINITY;
+            for (uint64_t r = 0; r < ratio; ++r) top = std::fmax(top, gate[(group * ratio + r) * dim + col]);
+            float sum = 0.0f, acc = 0.0f;
+            for (uint64_t r = 0; r < ratio; ++r) {
+                const float w = std::exp(gate[(group * ratio + r) * dim + col] - top);
+                sum += w;
+                acc = std::fmaf(w, kv[(group * ratio + r) * dim + col], acc);
+            }
+            out[group * dim + col] = acc / sum;
+        }
+}
+
+// gpu/ops.hpp:1697-1745 (op_index_scores_kernel), with gpu/ops.hpp:1942-1951 (index_candidate) when `candidates` is given (then the
+// scores are rows x blocks * block in candidate order, as gpu/ops.hpp:1978-2075 stores them). A dot is one chain of fused multiply-adds
+// over the columns in order from 0; a head's term relu(dot) * weight, one rounded product; the terms added in head order; then * scale.
+// keys_bf16: the keys are BF16 halves (widened exactly).
+void orc_index_scores(const float* q, const void* keys, int keys_bf16, const float* weights, const int32_t* visible, uint64_t rows, uint64_t groups,
+                      uint64_t heads, uint64_t dim, float scale, const int32_t* candidates, uint64_t blocks, uint64_t block, float* scores) {
+    const uint64_t scored = candidates ? blocks * block : groups;
+    #pragma omp parallel for collapse(2) schedule(static)
+    for (uint64_t row = 0; row < rows; ++row)
+        for (uint64_t place = 0; place < scored; ++place) {
+            const uint64_t limit = std::min<uint64_t>(groups, uint64_t(std::max(visible[row], 0)));
+            uint64_t g = place;
+            if (candidates) { const int32_t b = candidates[row * blocks + place / block]; g = b < 0 ? groups : uint64_t(b) * block + place % block; }
+            if (g >= limit) { scores[row * scored + place] = -INFINITY; continue; }
+            float total = 0.0f;
+            for (uint64_t h = 0; h < heads; ++h) {
+                const float* qv = q + (row * heads + h) * dim;
+                float acc = 0.0f;
+                for (uint64_t d = 0; d < dim; ++d) {
+                    float k;
+                    if (keys_bf16) { const uint32_t bits = uint32_t(static_cast<const uint16_t*>(keys)[g * dim + d]) << 16; std::memcpy(&k, &bits, 4); }
+                    else k = static_cast<const float*>(keys)[g * dim + d];
+                    acc = std::fmaf(qv[d], k, acc);
+                }
+                const float term = std::fmax(acc, 0.0f) * weights[row * heads + h];
+                total += term;
+            }
+            scores[row * scored + place] = total * scale;
+        }
+}
+
+// gpu/ops.hpp:1952-1966 (op_index_block_tops_kernel): a block's highest score, +inf for the block of the row's last visible group.
+void orc_index_block_tops(const float* scores, const int32_t* visible, uint64_t rows, uint64_t groups, uint64_t block, float* tops) {
+    const uint64_t count = (groups + block - 1) / block;
+    for (uint64_t row = 0; row < rows; ++row) {
+        const uint64_t seen = std::min<uint64_t>(groups, uint64_t(std::max(visible[row], 0)));
+        for (uint64_t b = 0; b < count; ++b) {
+            float top = seen && b == (seen - 1) / block ? INFINITY : -INFINITY;
+            for (uint64_t g = b * block, end = std::min(groups, g + block); g < end; ++g) top = std::fmax(top, scores[row * groups + g]);
+            tops[row * count + b] = top;
+        }
+    }
+}
+
+// gpu/dspark_attention.hpp:9-100 (dspark_attention_kernel) and crates/straydog-engine/tests/dspark_attention_gpu.rs:25-39 (its F64
+// oracle): every query row [slots][heads][512] attends the ring's history positions [anchor - history, anchor) (ring of 128 rows,
+// K = V) and all `slots` block keys; scale 1 / sqrt(512); the head's sink in the maximum and in the denominator.
+// accumulate64 = 0: the kernel's FP32 arithmetic (a score one chain of fused multiply-adds over the columns in order, an output
+// column one chain over the keys in order); 1: F64 throughout.
+void orc_dspark_attention(const float* q, const float* ring, const float* block, const float* sinks, uint64_t heads, uint64_t slots,
+                          uint64_t anchor, uint64_t history, int accumulate64, float* out) {
+    constexpr uint64_t dim = 512, ring_rows = 128;
+    const uint64_t first = anchor >= history ? anchor - history : 0, raw_count = anchor - first, total = raw_count + slots;
+    auto key = [&](uint64_t index) { return index < raw_count ? ring + (first + index) % ring_rows * dim : block + (index - raw_count) * dim; };
+    #pragma omp parallel for schedule(dynamic)
+    for (uint64_t item = 0; item < slots * heads; ++item) {
+        const float* query = q + item * dim;
+        const double sink = sinks[item % heads];
+        std::vector<double> scores(total);
+        double top = sink;
+        for (uint64_t i = 0; i < total; ++i) {
+            if (accumulate64) {
+                double dot = 0;
+                for (uint64_t d = 0; d < dim; ++d) dot += double(query[d]) * double(key(i)[d]);
+                scores[i] = dot / std::sqrt(double(dim));
+            } else {
+                float dot = 0;
+                for (uint64_t d = 0; d < dim; ++d) dot = std::fmaf(query[d], key(i)[d], dot);
+                scores[i] = dot * (1.0f / std::sqrt(float(dim)));
+            }
+            top = std::max(top, scores[i]);
+        }
+        double denominator = 0;
+        for (uint64_t i = 0; i < total; ++i) {
+            scores[i] = accumulate64 ? std::exp(scores[i] - top) : double(std::exp(float(scores[i]) - float(top)));
+            denominator = accumulate64 ? denominator + scores[i] : double(float(denominator) + float(scores[i]));
+        }
+        denominator = accumulate64 ? denominator + std::exp(sink - top) : double(float(denominator) + std::exp(float(sink) - float(top)));
+        for (uint64_t d = 0; d < dim; ++d) {
+            if (accumulate64) {
+                double sum = 0;
+                for (uint64_t i = 0; i < total; ++i) sum += scores[i] * double(key(i)[d]);
+                out[item * dim + d] = float(sum / denominator);
+            } else {
+                float sum = 0;
+                for (uint64_t i = 0; i < total; ++i) sum = std::fmaf(float(scores[i]), key(i)[d], sum);
+                out[item * dim + d] = sum / float(denominator);
+            }
+        }
+    }
+}
+
 // gpu/straydog_gpu.h:458-459 (sd_op_to_bf16: nearest, ties to even); tests/ds_state_bf16_gpu.rs:27-37.
 void orc_to_bf16(const float* x, uint64_t count, uint16_t* out) {
     for (uint64_t i = 0; i < count; ++i) out[i] = f32_to_bf16(x[i]);

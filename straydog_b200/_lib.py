@@ -41,6 +41,12 @@ SIGNATURES = {
     "sdx_ipc_open": ([p, p, u64], p),
     "sdx_ipc_close": ([p, p], i32),
     "sdx_sparse_attention_spans": ([p, p, p, u64, p, u64, p, u64, p, u64, p, u64, u64, u64, u64, f32, u64, p, p], i32),
+    "sd_op_dspark_attention": ([p, p, p, p, p, u64, u64, u32, p, u64, p], i32),
+    "sd_op_rope": ([p, p, u64, u64, u64, u64, p, p, i32], i32),
+    "sd_op_compress": ([p, p, p, u64, u64, u64, p], i32),
+    "sd_op_index_scores": ([p, p, p, p, p, u64, u64, u64, u64, f32, p], i32),
+    "sd_op_index_candidates": ([p, p, p, u64, u64, u64, u64, p, p, u64], i32),
+    "sd_op_index_select": ([p, p, p, p, p, u64, u64, u64, u64, f32, u64, p, p, p, u64, p, p, u64, u64], i32),
     "sd_op_top_k": ([p, p, u64, u64, u64, p], i32),
     "sd_op_to_bf16": ([p, p, u64, p], i32),
     "sdx_adopt": ([i32, p], p),

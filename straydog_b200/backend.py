@@ -310,6 +310,31 @@ class Backend:
         self._c(self.lib.sdx_sparse_attention_gather(self.handle, q, raw, raw_rows, positions, window, c_ptr, c_rows, s_ptr, selections, sinks,
                                                  rows, heads, dim, scale, rope_dims, freq, world, rank, out_table, flag_table, step))
 
+    def dspark_attention(self, q, ring, block, sinks, heads, slots, anchor, anchor_at, history, out):
+        """sd_op_dspark_attention over device pointers (crates/straydog-engine/src/ops.rs:232-237); anchor_at: device pointer or None."""
+        self._c(self.lib.sd_op_dspark_attention(self.handle, q, ring.pointer if isinstance(ring, Buffer) else ring, block,
+                                                sinks.pointer if isinstance(sinks, Buffer) else sinks, heads, slots, anchor, anchor_at, history, out))
+
+    # ---- the indexer (crates/straydog-engine/src/ops.rs:1173-1222); device pointers (ints) throughout ----
+    def rope(self, x, rows, vectors, width, rope_dims, positions, frequencies, inverse=False):
+        self._c(self.lib.sd_op_rope(self.handle, x, rows, vectors, width, rope_dims, positions, frequencies, int(inverse)))
+
+    def compress(self, kv, gate, groups, ratio, dim, out):
+        self._c(self.lib.sd_op_compress(self.handle, kv, gate, groups, ratio, dim, out))
+
+    def index_scores(self, q, keys, weights, visible, rows, groups, heads, dim, scale, scores):
+        self._c(self.lib.sd_op_index_scores(self.handle, q, keys, weights, visible, rows, groups, heads, dim, scale, scores))
+
+    def index_candidates(self, scores, visible, rows, groups, blocks, block, out, scratch):
+        self._c(self.lib.sd_op_index_candidates(self.handle, scores, visible, rows, groups, blocks, block, out, scratch.pointer, scratch.size))
+
+    def index_select(self, q, keys, weights, visible, rows, groups, heads, dim, scale, rope, scores, k, out, candidates=None):
+        """rope: (rope_dims, positions pointer, frequencies pointer); candidates: (pointer, blocks, block) or None."""
+        rope_dims, positions, frequencies = rope
+        c_ptr, blocks, block = candidates if candidates else (None, 0, 0)
+        self._c(self.lib.sd_op_index_select(self.handle, q, keys, weights, visible, rows, groups, heads, dim, scale, rope_dims, positions,
+                                            frequencies, scores, k, out, c_ptr, blocks, block))
+
     def top_k(self, scores, rows, groups, k, out):
         self._c(self.lib.sd_op_top_k(self.handle, scores, rows, groups, k, out))
 

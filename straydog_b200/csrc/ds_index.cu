@@ -1,0 +1,236 @@
+// The producers of the latent attention's index lists (DeepSeek-V4.1's indexer) and its compressed rows:
+//   sd_op_rope              gpu/straydog_gpu.h:271, gpu/ops.hpp:107-120, entry gpu/kernels.cpp:4942-4956
+//   sd_op_compress          gpu/straydog_gpu.h:407, gpu/ops.hpp:1679-1695, entry gpu/kernels.cpp:5478-5485
+//   sd_op_index_scores      gpu/straydog_gpu.h:408, gpu/ops.hpp:1697-1745, entry gpu/kernels.cpp:5487-5499
+//   sd_op_index_candidates  gpu/straydog_gpu.h:410-414, gpu/ops.hpp:1942-1966, entry gpu/kernels.cpp:5546-5566
+//   sd_op_index_select      gpu/straydog_gpu.h:415-419, gpu/ops.hpp:1978-2300, entry gpu/kernels.cpp:5568-5667
+// The contract is bit-exact: a score is scale * sum over heads in order of relu(q_h . key) * weight_h, each dot one chain of fused
+// multiply-adds over the columns in order, each term one rounded product, the terms added in head order; sd_op_index_select gives
+// the scores and indices that sd_op_rope, sd_op_index_scores and sd_op_top_k give one after the other
+// (crates/straydog-engine/tests/fused_gpu.rs:391-431). The kernels here keep that order of operations with another division of
+// the work: a thread owns one group's key and all the heads' running dots, the queries (up to 64 heads x 32 columns at a time) and a
+// tile of 128 keys x 32 columns go through shared memory with coalesced loads, BF16-tagged keys are widened as they land.
+#include "common.cuh"
+#include "ds_sparse.cuh"
+#include "../../include/straydog_gpu_b200.h"
+
+#include <algorithm>
+
+namespace sdb {
+
+void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block);
+
+__global__ void __launch_bounds__(256) rope_kernel(float* __restrict__ x, size_t count, size_t vectors, size_t width, size_t pairs,
+                                                   const int32_t* __restrict__ positions, const float* __restrict__ frequencies, int inverse) {
+    const size_t index = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= count) return;
+    const size_t pair = index % pairs, vector = index / pairs % vectors, row = index / (pairs * vectors);
+    float* v = x + (row * vectors + vector) * width + (width - 2 * pairs) + 2 * pair;
+    double s, c;
+    sincos(double(positions[row]) * double(frequencies[pair]) * (inverse ? -1.0 : 1.0), &s, &c);   // (the angle times -1.0: its own sincos)
+    const double a = v[0], b = v[1];
+    v[0] = float(a * c - b * s);
+    v[1] = float(a * s + b * c);
+}
+
+// out[group][col] = sum_r softmax_r(gate[group * ratio + r][col]) * kv[group * ratio + r][col]; no gate: the row itself
+__global__ void __launch_bounds__(256) compress_kernel(const float* __restrict__ kv, const float* __restrict__ gate, size_t groups, size_t ratio,
+                                                       size_t dim, float* __restrict__ out) {
+    const size_t index = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (index >= groups * dim) return;
+    const size_t group = index / dim, col = index % dim;
+    if (!gate) { out[index] = kv[group * dim + col]; return; }
+    const float* g = gate + group * ratio * dim + col;
+    const float* v = kv + group * ratio * dim + col;
+    float top = -INFINITY;
+    for (size_t r = 0; r < ratio; ++r) top = fmaxf(top, g[r * dim]);
+    float sum = 0.0f, acc = 0.0f;
+    for (size_t r = 0; r < ratio; ++r) {
+        const float w = expf(g[r * dim] - top);
+        sum = __fadd_rn(sum, w);
+        acc = fmaf(w, v[r * dim], acc);   // (what the reference's `acc += w * kv` compiles to)
+    }
+    out[index] = __fdiv_rn(acc, sum);
+}
+
+constexpr int kIndexGroups = 128, kIndexCols = 32, kIndexHeads = 64;
+
+// A block scores `kIndexGroups` places of one row; a thread a place. With candidates, place v of a row stands for group
+// candidates[v / block] * block + v % block (none where the slot is -1) and the scores are stored in candidate order.
+__global__ void __launch_bounds__(kIndexGroups) index_scores_kernel(const float* __restrict__ q, const float* keys, const float* __restrict__ weights,
+                                                                    const int32_t* __restrict__ visible, size_t groups, size_t heads, size_t dim,
+                                                                    float scale, float* __restrict__ scores, const int32_t* __restrict__ candidates,
+                                                                    size_t blocks, size_t block) {
+    const size_t row = blockIdx.y, scored = candidates ? blocks * block : groups, place = size_t(blockIdx.x) * kIndexGroups + threadIdx.x;
+    const unsigned t = threadIdx.x;
+    const size_t limit = min(groups, size_t(max(visible[row], 0)));
+    size_t g = groups;
+    if (place < scored) {
+        if (!candidates) g = place;
+        else { const int32_t b = candidates[row * blocks + place / block]; g = b < 0 ? groups : size_t(b) * block + place % block; }
+    }
+    __shared__ float qs[kIndexHeads][kIndexCols + 1];
+    __shared__ float ks[kIndexGroups][kIndexCols + 1];
+    __shared__ size_t tile_groups[kIndexGroups];
+    tile_groups[t] = g;
+    float acc[kIndexHeads];
+    #pragma unroll
+    for (int h = 0; h < kIndexHeads; ++h) acc[h] = 0.0f;
+    const float* row_q = q + row * heads * dim;
+    const bool bf16 = state_is_bf16(keys);
+    for (size_t d0 = 0; d0 < dim; d0 += kIndexCols) {
+        __syncthreads();
+        for (unsigned i = t; i < kIndexHeads * kIndexCols; i += kIndexGroups) {
+            const size_t h = i / kIndexCols, col = d0 + i % kIndexCols;
+            qs[h][i % kIndexCols] = h < heads && col < dim ? row_q[h * dim + col] : 0.0f;
+        }
+        for (unsigned i = t; i < kIndexGroups * kIndexCols; i += kIndexGroups) {
+            const size_t at = tile_groups[i / kIndexCols], col = d0 + i % kIndexCols;
+            float value = 0.0f;
+            if (at < limit && col < dim)
+                value = bf16 ? __uint_as_float(uint32_t(state_halves(keys)[at * dim + col]) << 16) : keys[at * dim + col];
+            ks[i / kIndexCols][i % kIndexCols] = value;
+        }
+        __syncthreads();
+        const int width = int(min(size_t(kIndexCols), dim - d0));
+        for (int c = 0; c < width; ++c) {
+            const float k = ks[t][c];
+            #pragma unroll
+            for (int h = 0; h < kIndexHeads; ++h) acc[h] = fmaf(qs[h][c], k, acc[h]);
+        }
+    }
+    if (place >= scored) return;
+    float total = 0.0f;
+    #pragma unroll
+    for (int h = 0; h < kIndexHeads; ++h)
+        if (size_t(h) < heads) total = __fadd_rn(total, __fmul_rn(fmaxf(acc[h], 0.0f), weights[row * heads + h]));
+    scores[row * scored + place] = g < limit ? __fmul_rn(total, scale) : -INFINITY;
+}
+
+// A block's highest score, a thread a block; the block of the row's last visible group +inf (always kept), blocks of only -inf stay -inf.
+__global__ void __launch_bounds__(256) index_block_tops_kernel(const float* __restrict__ scores, const int32_t* __restrict__ visible, size_t groups,
+                                                               size_t block, size_t count, float* __restrict__ tops) {
+    const size_t row = blockIdx.y, b = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (b >= count) return;
+    const float* s = scores + row * groups;
+    const size_t seen = min(groups, size_t(max(visible[row], 0)));
+    float top = seen && b == (seen - 1) / block ? INFINITY : -INFINITY;
+    for (size_t g = b * block, end = min(groups, g + block); g < end; ++g) top = fmaxf(top, s[g]);
+    tops[row * count + b] = top;
+}
+
+static void launch_index_scores(Device& d, const float* q, const float* keys, const float* weights, const int32_t* visible, size_t rows, size_t groups,
+                                size_t heads, size_t dim, float scale, float* scores, const int32_t* candidates, size_t blocks, size_t block) {
+    const size_t scored = candidates ? blocks * block : groups;
+    index_scores_kernel<<<dim3(unsigned((scored + kIndexGroups - 1) / kIndexGroups), unsigned(rows)), kIndexGroups, 0, d.stream>>>(
+        q, keys, weights, visible, groups, heads, dim, scale, scores, candidates, blocks, block);
+    ++d.launches;
+    SDB_CHECK(cudaGetLastError());
+}
+
+static void keys_span(Device& d, const float* keys, size_t values) {
+    if (state_is_bf16(keys)) span(d, state_halves(keys), values * 2, "index keys");
+    else span(d, keys, values * 4, "index keys");
+}
+
+}  // namespace sdb
+
+using namespace sdb;
+
+extern "C" {
+
+int sd_op_rope(void* handle, float* x, uint64_t rows, uint64_t vectors, uint64_t width, uint64_t rope_dims, const int32_t* positions,
+               const float* frequencies, int inverse) {
+    SDB_OP_BEGIN
+    if (!rows || !vectors || !rope_dims || rope_dims % 2 || rope_dims > width) throw std::runtime_error("invalid Straydog rope shape");
+    span(value, x, checked_product({rows, vectors, width, 4}), "a rotated buffer");
+    span(value, positions, checked_product({rows, 4}), "rope positions");
+    span(value, frequencies, checked_product({rope_dims / 2, 4}), "rope frequencies");
+    const size_t count = checked_product({rows, vectors, rope_dims / 2});
+    rope_kernel<<<unsigned((count + 255) / 256), 256, 0, value.stream>>>(x, count, size_t(vectors), size_t(width), size_t(rope_dims / 2), positions, frequencies, inverse);
+    ++value.launches;
+    SDB_OP_END
+}
+
+int sd_op_compress(void* handle, const float* kv, const float* gate, uint64_t groups, uint64_t ratio, uint64_t dim, float* out) {
+    SDB_OP_BEGIN
+    if (!groups || !ratio || !dim) throw std::runtime_error("invalid Straydog compression shape");
+    span(value, kv, checked_product({groups, ratio, dim, 4}), "rows to compress");
+    if (gate) span(value, gate, checked_product({groups, ratio, dim, 4}), "a compression gate");
+    span(value, out, checked_product({groups, dim, 4}), "compressed rows");
+    const size_t count = checked_product({groups, dim});
+    compress_kernel<<<unsigned((count + 255) / 256), 256, 0, value.stream>>>(kv, gate, size_t(groups), size_t(ratio), size_t(dim), out);
+    ++value.launches;
+    SDB_OP_END
+}
+
+int sd_op_index_scores(void* handle, const float* q, const float* keys, const float* weights, const int32_t* visible, uint64_t rows, uint64_t groups,
+                       uint64_t heads, uint64_t dim, float scale, float* scores) {
+    SDB_OP_BEGIN
+    if (!rows || rows > 65535 || !groups || !heads || heads > uint64_t(kIndexHeads) || !dim) throw std::runtime_error("invalid Straydog index shape");
+    span(value, q, checked_product({rows, heads, dim, 4}), "index queries");
+    keys_span(value, keys, checked_product({groups, dim}));
+    span(value, weights, checked_product({rows, heads, 4}), "index weights");
+    span(value, visible, checked_product({rows, 4}), "visible counts");
+    span(value, scores, checked_product({rows, groups, 4}), "index scores");
+    launch_index_scores(value, q, keys, weights, visible, size_t(rows), size_t(groups), size_t(heads), size_t(dim), scale, scores, nullptr, 0, 1);
+    SDB_OP_END
+}
+
+int sd_op_index_candidates(void* handle, const float* scores, const int32_t* visible, uint64_t rows, uint64_t groups, uint64_t blocks, uint64_t block,
+                           int32_t* out, float* scratch, uint64_t scratch_bytes) {
+    SDB_OP_BEGIN
+    if (!rows || rows > 65535 || !groups || groups > (uint64_t(1) << 31) || !blocks || blocks > (uint64_t(1) << 20) || !block || block > 4096)
+        throw std::runtime_error("invalid Straydog index candidates");
+    const uint64_t count = (groups + block - 1) / block;
+    span(value, scores, checked_product({rows, groups, 4}), "index scores");
+    span(value, visible, checked_product({rows, 4}), "visible counts");
+    span(value, out, checked_product({rows, blocks, 4}), "index candidates");
+    if (checked_product({rows, count, 4}) > scratch_bytes) throw std::runtime_error("Straydog index candidates need more scratch");
+    span(value, scratch, checked_product({rows, count, 4}), "index candidates' scratch");
+    index_block_tops_kernel<<<dim3(unsigned((count + 255) / 256), unsigned(rows)), 256, 0, value.stream>>>(scores, visible, size_t(groups), size_t(block), size_t(count), scratch);
+    ++value.launches;
+    SDB_CHECK(cudaGetLastError());
+    launch_top_k(value, scratch, size_t(rows), size_t(count), size_t(blocks), out, nullptr, 0, 1);
+    SDB_OP_END
+}
+
+int sd_op_index_select(void* handle, const float* q, const float* keys, const float* weights, const int32_t* visible, uint64_t rows, uint64_t groups,
+                       uint64_t heads, uint64_t dim, float scale, uint64_t rope_dims, const int32_t* positions, const float* frequencies, float* scores,
+                       uint64_t k, int32_t* out, const int32_t* candidates, uint64_t blocks, uint64_t block) {
+    SDB_OP_BEGIN
+    if (!rows || rows > 65535 || !groups || groups > (uint64_t(1) << 31) || !heads || heads > uint64_t(kIndexHeads) || !dim || !k ||
+        k > (uint64_t(1) << 31) || rope_dims % 2 || rope_dims > dim || rope_dims > 128)
+        throw std::runtime_error("invalid Straydog index shape");
+    uint64_t scored = groups;
+    if (candidates) {
+        if (!blocks || !block || blocks > (uint64_t(1) << 20) || block > 4096) throw std::runtime_error("invalid Straydog index candidates");
+        span(value, candidates, checked_product({rows, blocks, 4}), "index candidates");
+        scored = blocks * block;
+    }
+    span(value, q, checked_product({rows, heads, dim, 4}), "index queries");
+    keys_span(value, keys, checked_product({groups, dim}));
+    span(value, weights, checked_product({rows, heads, 4}), "index weights");
+    span(value, visible, checked_product({rows, 4}), "visible counts");
+    span(value, positions, checked_product({rows, 4}), "query positions");
+    if (rope_dims) span(value, frequencies, checked_product({rope_dims / 2, 4}), "rope frequencies");
+    span(value, scores, checked_product({rows, std::max(groups, scored), 4}), "index scores");
+    span(value, out, checked_product({rows, k, 4}), "top-k indices");
+    // q rotated into a workspace of the library (q itself stays as it is), then the scores and the top k over them
+    const float* q_used = q;
+    if (rope_dims) {
+        const size_t bytes = checked_product({rows, heads, dim, 4});
+        auto* rotated = static_cast<float*>(ensure(value, value.work, value.work_bytes, bytes));
+        SDB_CHECK(cudaMemcpyAsync(rotated, q, bytes, cudaMemcpyDeviceToDevice, value.stream));
+        const size_t count = checked_product({rows, heads, rope_dims / 2});
+        rope_kernel<<<unsigned((count + 255) / 256), 256, 0, value.stream>>>(rotated, count, size_t(heads), size_t(dim), size_t(rope_dims / 2), positions, frequencies, 0);
+        ++value.launches;
+        SDB_CHECK(cudaGetLastError());
+        q_used = rotated;
+    }
+    launch_index_scores(value, q_used, keys, weights, visible, size_t(rows), size_t(groups), size_t(heads), size_t(dim), scale, scores, candidates, size_t(blocks), size_t(block ? block : 1));
+    launch_top_k(value, scores, size_t(rows), size_t(scored), size_t(k), out, candidates, size_t(blocks), size_t(block ? block : 1));
+    SDB_OP_END
+}
+
+}  // extern "C"

@@ -89,7 +89,11 @@ __device__ __forceinline__ void find_band(const uint32_t* hist, uint32_t bins, u
     __syncthreads();
 }
 
-__global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict__ scores, size_t groups, size_t k, int32_t* __restrict__ out) {
+// With `candidates` (a row's `blocks` block numbers in index order, -1 past the last; gpu/ops.hpp:1942-1951) the row's scores are
+// those of its candidate groups in candidate order, and a kept place v is written as the group it stands for,
+// candidates[v / block] * block + v % block: index order both ways, so the list still ascends.
+__global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict__ scores, size_t groups, size_t k, int32_t* __restrict__ out,
+                                                         const int32_t* __restrict__ candidates, size_t blocks, size_t block) {
     extern __shared__ __align__(16) uint32_t dynamic[];
     uint32_t* hist = dynamic;
     uint32_t* sure = hist + kBins;              // indices kept for sure, ascending
@@ -100,6 +104,8 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
     const float* row = scores + size_t(blockIdx.x) * groups;
     int32_t* mine = out + size_t(blockIdx.x) * k;
     const unsigned t = threadIdx.x;
+    const int32_t* mapped = candidates ? candidates + size_t(blockIdx.x) * blocks : nullptr;
+    const auto group_of = [&](uint32_t place) { return mapped ? int32_t(size_t(mapped[place / block]) * block + place % block) : int32_t(place); };
 
     // ---- read 1: the top 11 key bits ----
     for (uint32_t i = t; i < kBins; i += kThreads) hist[i] = 0;
@@ -199,8 +205,8 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
             while (low < high) { const uint32_t mid = (low + high) / 2; if (list[mid] < index) low = mid + 1; else high = mid; }
             return low;
         };
-        for (uint32_t i = t; i < sure_count; i += kThreads) mine[i + before_in(chosen, chosen_count, sure[i])] = int32_t(sure[i]);
-        for (uint32_t i = t; i < chosen_count; i += kThreads) mine[i + before_in(sure, sure_count, chosen[i])] = int32_t(chosen[i]);
+        for (uint32_t i = t; i < sure_count; i += kThreads) mine[i + before_in(chosen, chosen_count, sure[i])] = group_of(sure[i]);
+        for (uint32_t i = t; i < chosen_count; i += kThreads) mine[i + before_in(sure, sure_count, chosen[i])] = group_of(chosen[i]);
         for (size_t i = size_t(sure_count) + chosen_count + t; i < k; i += kThreads) mine[i] = -1;
         return;
     }
@@ -251,7 +257,7 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
         size_t at = written + prefix_before(kept, sh, tile_kept);
         #pragma unroll
         for (int i = 0; i < kPerThread; ++i)
-            if (keep[i] && at < k) mine[at++] = int32_t(first + i);
+            if (keep[i] && at < k) mine[at++] = group_of(uint32_t(first + i));
         written += tile_kept;
         ties_seen += tile_ties;
     }
@@ -259,6 +265,18 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
 }
 
 }  // namespace topk
+
+// rows x groups scores -> rows x k indices (with candidates: see top_k_kernel)
+void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block) {
+    static bool configured[64] = {};
+    if (!configured[d.ordinal & 63]) {
+        SDB_CHECK(cudaFuncSetAttribute(topk::top_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(topk::kSmem)));
+        configured[d.ordinal & 63] = true;
+    }
+    topk::top_k_kernel<<<unsigned(rows), topk::kThreads, topk::kSmem, d.stream>>>(scores, groups, k, out, candidates, blocks, block);
+    ++d.launches;
+    SDB_CHECK(cudaGetLastError());
+}
 
 // out[i] = x[i] as BF16: nearest, ties to even; a NaN stays a NaN (gpu/token_mixing.hpp:728-735).
 __global__ void __launch_bounds__(256) to_bf16_kernel(const float* __restrict__ x, size_t count, uint16_t* __restrict__ out) {
@@ -280,13 +298,7 @@ int sd_op_top_k(void* handle, const float* scores, uint64_t rows, uint64_t group
         throw std::runtime_error("invalid Straydog top-k shape");
     span(value, scores, checked_product({rows, groups, 4}), "scores");
     span(value, out, checked_product({rows, k, 4}), "top-k indices");
-    static bool configured[64] = {};
-    if (!configured[value.ordinal & 63]) {
-        SDB_CHECK(cudaFuncSetAttribute(topk::top_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(topk::kSmem)));
-        configured[value.ordinal & 63] = true;
-    }
-    topk::top_k_kernel<<<unsigned(rows), topk::kThreads, topk::kSmem, value.stream>>>(scores, size_t(groups), size_t(k), out);
-    ++value.launches;
+    launch_top_k(value, scores, size_t(rows), size_t(groups), size_t(k), out, nullptr, 0, 1);
     SDB_OP_END
 }
 

@@ -159,6 +159,41 @@ def latent_decode_case(seed, rows, heads, dim, context, selections):
                 scale=float(np.float32(1.0) / np.sqrt(np.float32(dim))))
 
 
+def dspark_case():
+    """crates/straydog-engine/tests/dspark_attention_gpu.rs:56-63: the inputs of its main test (xorshift64 floats in [-scale, scale))."""
+    random = XorShift(0x9E3779B97F4A7C15)
+
+    def floats(count, scale):
+        return np.array([(np.float32(random.next() >> 40) / np.float32(1 << 24) - np.float32(0.5)) * np.float32(2.0) * np.float32(scale)
+                         for _ in range(count)], np.float32)
+    q, ring, block, sinks = floats(5 * 64 * 512, 0.3), floats(128 * 512, 0.4), floats(5 * 512, 0.6), floats(64, 2.0)
+    sinks[0::16] = 30.0
+    sinks[1::16] = -30.0
+    return dict(q=q.reshape(5, 64, 512), ring=ring.reshape(128, 512), block=block.reshape(5, 512), sinks=sinks)
+
+
+INDEX_CASES = [(1, 3000), (4, 2000), (1, 300)]          # crates/straydog-engine/tests/fused_gpu.rs:399
+TWO_LEVEL_CASES = [(1, 6000, 256, 8), (3, 5001, 1024, 8)]   # (rows, groups, blocks, block): the second keeps every block (626 < 1024)
+
+
+def index_case(rows, groups, heads=32, dim=128, rope_dims=64, spread=3, seed=0):
+    """crates/straydog-engine/tests/fused_gpu.rs:391-412 in shape and value ranges (q in [-2, 2), keys and weights in [-1, 1), rope
+    frequencies 1.6e5 ^ (-2 i / rope), visible = groups - spread * row, positions 20000 + 7 * row, scale 1 / (sqrt(dim) sqrt(heads))),
+    seeded here."""
+    rng = np.random.default_rng([rows, groups, heads, dim, seed])
+    frequencies = np.array([np.float32(1.6e5) ** (np.float32(-2.0 * i) / np.float32(rope_dims)) for i in range(rope_dims // 2)], np.float32)
+    return dict(q=rng.uniform(-2, 2, (rows, heads, dim)).astype(np.float32), keys=rng.uniform(-1, 1, (groups, dim)).astype(np.float32),
+                weights=rng.uniform(-1, 1, (rows, heads)).astype(np.float32), visible=np.array([groups - spread * r for r in range(rows)], np.int32),
+                positions=np.array([20000 + 7 * r for r in range(rows)], np.int32), frequencies=frequencies, rows=rows, groups=groups, heads=heads,
+                dim=dim, rope_dims=rope_dims, scale=float(np.float32(1.0) / (np.sqrt(np.float32(dim)) * np.sqrt(np.float32(heads)))))
+
+
+def compress_case(groups=37, ratio=4, dim=128, seed=5):
+    rng = np.random.default_rng(seed)
+    return dict(kv=rng.uniform(-1, 1, (groups * ratio, dim)).astype(np.float32), gate=rng.uniform(-4, 4, (groups * ratio, dim)).astype(np.float32),
+                groups=groups, ratio=ratio, dim=dim)
+
+
 def tie_scores(random, rows, groups):
     """crates/straydog-engine/tests/fused_gpu.rs:366-377: quarter steps in [-2, 2], -0 beside +0, -inf and +inf."""
     out = np.empty(rows * groups, np.float32)

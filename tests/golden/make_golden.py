@@ -25,6 +25,7 @@ SEQUENCE_CASES = [(4, 2052, 3000, 4096, "sparse"), (3, 64, 100, 256, "dense"), (
 ATTENTION_CASES = [(15, 16, 2, 256, 137), (1, 2, 1, 256, 137), (17, 4, 2, 256, 35), (16, 4, 2, 128, 35)]
 SPARSE_CASES = [(1, 32), (4, 32)]
 LATENT_CASES = [(11, 2, 16, 576, 1024, 256)]
+DSPARK_CASES = [(1, 0, 0), (5, 37, 149), (3, 128, 389)]
 TOPK_GROUPS = [511, 512, 513, 600, 4096, 30000]
 
 
@@ -89,6 +90,52 @@ def main():
         out[f"topk_{groups}"] = gpu.read(o, np.int32, (2, 512))
         gpu.release(dev)
         gpu.release(o)
+    c = synthetic.dspark_case()
+    q, ring, block, sinks = (gpu.upload(c[k]) for k in ("q", "ring", "block", "sinks"))
+    o = gpu.buffer(c["q"].nbytes)
+    for slots, history, anchor in DSPARK_CASES:
+        gpu.dspark_attention(q.pointer, ring, block.pointer, sinks, 64, slots, anchor, None, history, o.pointer)
+        out[f"dspark_{slots}_{history}_{anchor}"] = gpu.read(o, np.float32, (slots, 64, 512))[:, ::8].copy()   # every eighth head keeps the file small
+    for b in (q, ring, block, sinks, o):
+        gpu.release(b)
+
+    def index_select(c, k, candidates=None):
+        bufs = {name: gpu.upload(c[name]) for name in ("q", "keys", "weights", "visible", "positions", "frequencies")}
+        scored = c["groups"] if candidates is None else candidates[1] * candidates[2]
+        scores, picked = gpu.buffer(c["rows"] * max(scored, c["groups"]) * 4), gpu.buffer(c["rows"] * k * 4)
+        gpu.index_select(bufs["q"].pointer, bufs["keys"].pointer, bufs["weights"].pointer, bufs["visible"].pointer, c["rows"], c["groups"],
+                         c["heads"], c["dim"], c["scale"], (c["rope_dims"], bufs["positions"].pointer, bufs["frequencies"].pointer),
+                         scores.pointer, k, picked.pointer, candidates)
+        got = gpu.read(scores, np.float32, (c["rows"], scored)), gpu.read(picked, np.int32, (c["rows"], k))
+        for b in list(bufs.values()) + [picked]:
+            gpu.release(b)
+        return got + (scores,)
+    for rows, groups in synthetic.INDEX_CASES:
+        c = synthetic.index_case(rows, groups)
+        scores, picked, held = index_select(c, 512)
+        gpu.release(held)
+        out[f"index_scores_{rows}_{groups}"], out[f"index_top_{rows}_{groups}"] = scores, picked
+    for rows, groups, blocks, block in synthetic.TWO_LEVEL_CASES:
+        source = synthetic.index_case(rows, groups, spread=13)
+        _, _, scores = index_select(source, 512)
+        visible, chosen = gpu.upload(source["visible"]), gpu.buffer(rows * blocks * 4)
+        scratch = gpu.buffer(rows * -(-groups // block) * 4)
+        gpu.index_candidates(scores.pointer, visible.pointer, rows, groups, blocks, block, chosen.pointer, scratch)
+        out[f"candidates_{rows}_{groups}_{blocks}_{block}"] = gpu.read(chosen, np.int32, (rows, blocks))
+        later = synthetic.index_case(rows, groups, spread=13, seed=1)
+        later["keys"] = source["keys"]
+        _, picked, held = index_select(later, 512, (chosen.pointer, blocks, block))
+        out[f"index_within_{rows}_{groups}_{blocks}_{block}"] = picked
+        for b in (scores, visible, chosen, scratch, held):
+            gpu.release(b)
+    c = synthetic.compress_case()
+    kv, gate, o = gpu.upload(c["kv"]), gpu.upload(c["gate"]), gpu.buffer(c["groups"] * c["dim"] * 4)
+    gpu.compress(kv.pointer, gate.pointer, c["groups"], c["ratio"], c["dim"], o.pointer)
+    out["compress"] = gpu.read(o, np.float32, (c["groups"], c["dim"]))
+    c = synthetic.index_case(3, 1)
+    x, at, fr = gpu.upload(c["q"]), gpu.upload(c["positions"]), gpu.upload(c["frequencies"])
+    gpu.rope(x.pointer, 3, c["heads"], c["dim"], c["rope_dims"], at.pointer, fr.pointer)
+    out["rope"] = gpu.read(x, np.float32, c["q"].shape)
     values = synthetic.XorShift(0x243F6A8885A308D3).floats_scaled(10_000, 1e3)
     dev = gpu.upload(values)
     o = gpu.buffer(values.size * 2)

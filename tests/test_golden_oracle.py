@@ -65,3 +65,42 @@ def test_top_k_and_bf16_bit_for_bit():
     values = XorShift(0x243F6A8885A308D3).floats_scaled(10_000, 1e3)
     assert np.array_equal(oracle.to_bf16(values), GOLDEN["to_bf16"])
     assert np.array_equal(bf16_round(values)[0], GOLDEN["to_bf16"])
+
+
+def test_dspark_attention():
+    from util import dspark_case
+    c = dspark_case()
+    for slots, history, anchor in [(1, 0, 0), (5, 37, 149), (3, 128, 389)]:
+        got = oracle.dspark_attention(c["q"][:slots], c["ring"], c["block"], c["sinks"], 64, slots, anchor, history)
+        assert worst(got[:, ::8], GOLDEN[f"dspark_{slots}_{history}_{anchor}"]) < 2e-6   # (the fixture holds every eighth head)
+
+
+def test_the_indexer():
+    """Scores within the rope's sin and cos of the reference library's (the CPU's libm against the device's); everything after the scores
+    (the choice of indices, the candidate blocks, the choice among them) bit for bit from the library's own scores."""
+    from util import INDEX_CASES, TWO_LEVEL_CASES, compress_case, index_case
+    for rows, groups in INDEX_CASES:
+        c = index_case(rows, groups)
+        scores, picked = oracle.index_select(c["q"], c["keys"], c["weights"], c["visible"], c["scale"], c["positions"], c["frequencies"], 512)
+        want = GOLDEN[f"index_scores_{rows}_{groups}"]
+        seen = np.isfinite(want)
+        assert np.array_equal(seen, np.isfinite(scores)) and worst(scores[seen], want[seen]) <= 1e-5
+        assert np.array_equal(oracle.top_k(want, 512), GOLDEN[f"index_top_{rows}_{groups}"])
+    for rows, groups, blocks, block in TWO_LEVEL_CASES:
+        source = index_case(rows, groups, spread=13)
+        scores, _ = oracle.index_select(source["q"], source["keys"], source["weights"], source["visible"], source["scale"], source["positions"],
+                                        source["frequencies"], 512)
+        chosen = GOLDEN[f"candidates_{rows}_{groups}_{blocks}_{block}"]
+        mine = oracle.index_candidates(scores, source["visible"], blocks, block)
+        # a block's highest score an ulp apart could swap two blocks at the cut: allow a few, demand the rest
+        assert np.mean(mine == chosen) > 0.99
+        later = index_case(rows, groups, spread=13, seed=1)
+        _, picked = oracle.index_select(later["q"], source["keys"], later["weights"], later["visible"], later["scale"], later["positions"],
+                                        later["frequencies"], 512, candidates=chosen, block=block)
+        want = GOLDEN[f"index_within_{rows}_{groups}_{blocks}_{block}"]
+        assert np.mean(picked == want) > 0.98
+        assert np.all(np.diff(picked.astype(np.int64), axis=1)[picked[:, 1:] >= 0] > 0), "ascending group indices"
+    c = compress_case()
+    assert worst(oracle.compress(c["kv"], c["gate"], c["ratio"]), GOLDEN["compress"]) <= 1e-6
+    r = index_case(3, 1)
+    assert worst(oracle.rope(r["q"], r["positions"], r["frequencies"]), GOLDEN["rope"]) <= 1e-6

@@ -76,7 +76,10 @@ def test_benchmark_shape_small(gpu, form):
 @pytest.mark.parametrize("rows,heads,dim,window,selections,rope_dims,exact_q", [
     (3, 16, 576, 8, 200, 0, True), (8, 16, 576, 8, 2048, 64, True), (2, 128, 576, 1, 96, 0, True), (5, 24, 512, 128, 31, 64, False),
     (1, 8, 512, 3, 0, 0, False), (2, 40, 576, 40, 65, 128, False), (4, 32, 576, 4, 300, 64, False), (2, 64, 512, 1, 128, 0, False),
-    (3, 48, 576, 2, 100, 128, True), (2, 80, 576, 16, 64, 0, True), (1, 16, 512, 1, 4000, 0, True)])
+    (3, 48, 576, 2, 100, 128, True), (2, 80, 576, 16, 64, 0, True), (1, 16, 512, 1, 4000, 0, True),
+    # 128 heads and more: the shapes the tcgen05 kernel takes by the library's own choice (rope on F32 queries, a head tile that is
+    # half padding, 512-wide rows, the longest window it accepts, a ragged last tile of selections)
+    (2, 128, 576, 8, 200, 64, False), (1, 144, 512, 2, 100, 0, True), (3, 128, 512, 16, 1000, 128, False), (1, 192, 576, 1, 64, 64, True)])
 def test_tensor_core_kernel_shapes(gpu, form, rows, heads, dim, window, selections, rope_dims, exact_q):
     """Head tiles of 16 and 32 with tails, spans with a causal window (config 4's layout), rope on BF16-exact and on F32 queries,
     partial tiles, no selection at all; each against the F64 oracle and against this library's FP32 kernel."""
