@@ -18,16 +18,18 @@
 // operand from TMEM and shared memory only holds K and V tiles: one ring of five 32 KB slots that the dequantising warps fill
 // and the MMA thread drains in the same fixed order (K_hi, K_lo of tile i, then V_hi, V_lo of tile i - 1).
 //
-// Warp roles (14 warps):
+// Warp roles (19 warps):
 //   warps 0-7   softmax: two threads per M-row (32 of the tile's 64 columns each; warp w works on the TMEM lanes
 //               32 (w % 4).. a warp may touch). tcgen05.ld of the scores, mask, row maximum exchanged with the partner
 //               warp through shared memory, P rounded to FP16 and stored to TMEM; O is rescaled in TMEM only when a
 //               row's maximum has grown by more than 2^8 (the stale maximum stays exact arithmetic: weights are at
 //               most 256 and the final division uses the same maximum); epilogue O / l.
-//   warp 8      one thread issues every tcgen05.mma and commits them to mbarriers.
-//   warp 9      one thread brings the raw rows: a bulk copy (TMA engine) of a tile's 64 consecutive rows of one plane
+//   warp 8      one thread issues the score products' tcgen05.mma and commits them to mbarriers.
+//   warp 9      one thread issues the value products' (a thread each: the tensor pipe's queue is short, and one issuer's waits
+//               for tiles, weights and buffers let it run dry; with two, one's waits pass while the other issues).
+//   warp 10     one thread brings the raw rows: a bulk copy (TMA engine) of a tile's 64 consecutive rows of one plane
 //               (17408 contiguous bytes) into a ring of three raw slots.
-//   warps 10-13 dequantise a raw slot into an FP16 hi tile and an FP16 lo tile, written in the 128-byte-swizzled
+//   warps 11-18 dequantise a raw slot into an FP16 hi tile and an FP16 lo tile, written in the 128-byte-swizzled
 //               [64 rows][128 bytes] blocks that are the K-major / MN-major operand layout the MMA's descriptors read.
 // S is double buffered, so the tensor pipe works on S(i+1) while the softmax warps work on S(i). Every wait is bounded; a wait
 // that gives up raises a flag that ends all roles, frees TMEM and reports through the status word.
@@ -40,8 +42,8 @@ namespace sdb {
 namespace tc {
 
 constexpr int kM = 128, kN = 64, kD = 256;
-constexpr int kSoftmaxWarps = 8, kMmaWarp = 8, kTmaWarp = 9, kDequantWarp0 = 10, kDequantWarps = 4;
-constexpr int kThreads = 32 * (kDequantWarp0 + kDequantWarps);   // 8 softmax warps, the MMA warp, the copy warp, 4 dequantising warps
+constexpr int kSoftmaxWarps = 8, kScoreWarp = 8, kValueWarp = 9, kTmaWarp = 10, kDequantWarp0 = 11, kDequantWarps = 8;
+constexpr int kThreads = 32 * (kDequantWarp0 + kDequantWarps);   // 8 softmax warps, two MMA warps, the copy warp, 8 dequantising warps
 constexpr int kKVBytes = kN * kD * 2;               // one operand tile: 64 positions x 256 FP16
 constexpr int kSlots = 5;                            // the operand ring (FP16 tiles)
 constexpr int kRawSlots = 3, kRawBytes = kN * int(kv_row_q8);   // raw Q8_0 tiles: 64 rows of one plane, 17408 contiguous bytes
@@ -307,64 +309,80 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
                 }
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ================= the MMA issuer =================
-        // The ring is drained in the order the dequantising warps fill it: item t sits in slot t % 5, in its (t / 5)-th use.
+    } else if (warp == kScoreWarp) {
+        // ================= the score products' issuer =================
+        // The ring is drained in the order the dequantising warps fill it: plane tile t sits in slot t % 5, in its (t / 5)-th use. The
+        // planes of K(i) are tiles 4 i - 2 and 4 i - 1 (0 and 1 for the first tile), those of V(j) 4 j + 4 and 4 j + 5 (4 j + 2 and
+        // 4 j + 3 for the last tile, which no K follows). Scores and values have a thread each, so that one's waits pass while the
+        // other issues: the tensor pipe's queue is short, and a single issuer let it run dry at every wait.
         if (lane == 0) {
             long long trace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             const long long started = clock64();
             (void)started;
             const uint32_t ring = smem_u32(smem + kOffRing);
-            const uint32_t idesc_s = instr_desc(kM, kN, false), idesc_o = instr_desc(kM, kD, true);
-            uint32_t item = 0;
+            const uint32_t idesc_s = instr_desc(kM, kN, false);
             bool alive = true;
-            for (uint32_t i = 0; i <= tiles && alive; ++i) {
-                if (i < tiles) {
-                    const uint32_t buffer = i & 1, s_tmem = tmem + 256 + buffer * 64;
-                    long long since = clock64();
-                    if (i >= 2 && !wait(kSFree + buffer, ((i - 2) >> 1) & 1)) break;
-                    SDX_TRACE_ADD(3, since);
-                    #pragma unroll 1
-                    for (int part = 0; part < 2 && alive; ++part, ++item) {   // K_hi, then K_lo into the same accumulator
-                        const uint32_t slot = item % kSlots, tile = desc_low(ring + slot * kKVBytes, 16);
-                        since = clock64();
-                        if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
-                        SDX_TRACE_ADD(1, since);
-                        tc_fence_after();
-                        #pragma unroll
-                        for (int kk = 0; kk < 16; ++kk)
-                            umma_a_tmem(s_tmem, tmem + 384 + kk * 8, desc_of(tile + (((kk / 4) * (kN * 128) + (kk % 4) * 32) >> 4)), idesc_s, part > 0 || kk > 0);
-                        umma_commit(&bars[kFree + slot]);
-                    }
-                    if (!alive) break;
-                    umma_commit(&bars[kSFull + buffer]);
+            for (uint32_t i = 0; i < tiles && alive; ++i) {
+                const uint32_t buffer = i & 1, s_tmem = tmem + 256 + buffer * 64;
+                long long since = clock64();
+                if (i >= 2 && !wait(kSFree + buffer, ((i - 2) >> 1) & 1)) break;
+                SDX_TRACE_ADD(3, since);
+                uint32_t item = i == 0 ? 0u : 4 * i - 2;
+                #pragma unroll 1
+                for (int part = 0; part < 2 && alive; ++part, ++item) {   // K_hi, then K_lo into the same accumulator
+                    const uint32_t slot = item % kSlots, tile = desc_low(ring + slot * kKVBytes, 16);
+                    since = clock64();
+                    if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
+                    SDX_TRACE_ADD(1, since);
+                    #pragma unroll
+                    for (int kk = 0; kk < 16; ++kk)
+                        umma_a_tmem(s_tmem, tmem + 384 + kk * 8, desc_of(tile + (((kk / 4) * (kN * 128) + (kk % 4) * 32) >> 4)), idesc_s, part > 0 || kk > 0);
+                    umma_commit(&bars[kFree + slot]);
                 }
-                if (i >= 1) {
-                    const uint32_t j = i - 1, buffer = j & 1, p_tmem = tmem + 256 + buffer * 64;
-                    long long since = clock64();
-                    if (!wait(kPFull + buffer, (j >> 1) & 1)) break;
-                    SDX_TRACE_ADD(2, since);
-                    #pragma unroll 1
-                    for (int part = 0; part < 2 && alive; ++part, ++item) {   // V_hi, then V_lo
-                        const uint32_t slot = item % kSlots, tile = desc_low(ring + slot * kKVBytes, kN * 128);
-                        since = clock64();
-                        if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
-                        SDX_TRACE_ADD(1, since);
-                        tc_fence_after();
-                        #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk)
-                            umma_a_tmem(tmem, p_tmem + kk * 8, desc_of(tile + ((kk * (16 * 128)) >> 4)), idesc_o, j > 0 || part > 0 || kk > 0);
-                        umma_commit(&bars[kFree + slot]);
-                    }
-                    if (!alive) break;
-                    umma_commit(&bars[kPvDone]);
-                    umma_commit(&bars[kSFree + buffer]);   // P sat in the S buffer: free once the product has read it
-                }
+                if (!alive) break;
+                umma_commit(&bars[kSFull + buffer]);
             }
 #if defined(SDX_TRACE)
             trace[0] = clock64() - started; trace[5] = tiles;
             long long* mine = a.trace + (size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 8;
-            for (int c = 0; c < 8; ++c) mine[c] = trace[c];
+            mine[0] = trace[0]; mine[1] = trace[1]; mine[3] = trace[3]; mine[5] = trace[5];
+#endif
+        }
+    } else if (warp == kValueWarp) {
+        // ================= the value products' issuer =================
+        if (lane == 0) {
+            long long trace[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long started = clock64();
+            (void)started;
+            const uint32_t ring = smem_u32(smem + kOffRing);
+            const uint32_t idesc_o = instr_desc(kM, kD, true);
+            bool alive = true;
+            for (uint32_t j = 0; j < tiles && alive; ++j) {
+                const uint32_t buffer = j & 1, p_tmem = tmem + 256 + buffer * 64;
+                long long since = clock64();
+                if (!wait(kPFull + buffer, (j >> 1) & 1)) break;
+                SDX_TRACE_ADD(2, since);
+                tc_fence_after();
+                uint32_t item = j + 1 == tiles ? 4 * j + 2 : 4 * j + 4;
+                #pragma unroll 1
+                for (int part = 0; part < 2 && alive; ++part, ++item) {   // V_hi, then V_lo
+                    const uint32_t slot = item % kSlots, tile = desc_low(ring + slot * kKVBytes, kN * 128);
+                    since = clock64();
+                    if (!wait(kFull + slot, (item / kSlots) & 1)) { alive = false; break; }
+                    SDX_TRACE_ADD(4, since);
+                    #pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_a_tmem(tmem, p_tmem + kk * 8, desc_of(tile + ((kk * (16 * 128)) >> 4)), idesc_o, j > 0 || part > 0 || kk > 0);
+                    umma_commit(&bars[kFree + slot]);
+                }
+                if (!alive) break;
+                umma_commit(&bars[kPvDone]);
+                umma_commit(&bars[kSFree + buffer]);   // P sat in the S buffer: free once the product has read it
+            }
+#if defined(SDX_TRACE)
+            trace[6] = clock64() - started;
+            long long* mine = a.trace + (size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+            mine[2] = trace[2]; mine[4] = trace[4]; mine[6] = trace[6];
 #endif
         }
     } else if (warp == kTmaWarp) {
@@ -390,8 +408,10 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
         }
     } else {
         // ================= the dequantising warps: a raw slot -> an FP16 hi tile and an FP16 lo tile =================
-        // Thread t takes half a row (row t / 2, columns 128 (t % 2) ..): eight 16-byte pieces of raw values, four block scales.
-        const int dt = tid - 32 * kDequantWarp0, row = dt / 2, half = dt % 2;
+        // Thread t takes a quarter of a row (row t % 64, columns 64 (t / 64) ..: one 128-byte segment of the operand tile): four 16-byte
+        // pieces of raw values, two block scales. A warp's 32 rows are 272 bytes apart in the raw slot and 128 bytes apart, swizzled, in
+        // the tile: neither its loads nor its stores meet in a bank.
+        const int dt = tid - 32 * kDequantWarp0, row = dt % kN, quarter = dt / kN;
         const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));   // 1152 = 1024 + 128
         const uint32_t total_items = 2 * tiles;
         for (uint32_t item = 0; item < total_items; ++item) {
@@ -403,17 +423,15 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             if (2 * item >= uint32_t(kSlots) && !wait(kFree + hi_slot, ((2 * item) / kSlots - 1) & 1)) break;
             if (2 * item + 1 >= uint32_t(kSlots) && !wait(kFree + lo_slot, ((2 * item + 1) / kSlots - 1) & 1)) break;
             const uint8_t* raw = smem + kOffRaw + raw_slot * kRawBytes + row * kv_row_q8;
-            uint8_t* hi_tile = smem + kOffRing + hi_slot * kKVBytes;
-            uint8_t* lo_tile = smem + kOffRing + lo_slot * kKVBytes;
+            uint8_t* hi_row = smem + kOffRing + hi_slot * kKVBytes + quarter * (kN * 128) + row * 128;
+            uint8_t* lo_row = smem + kOffRing + lo_slot * kKVBytes + quarter * (kN * 128) + row * 128;
             const bool exists = uint32_t(row) < rows;   // (rows past the chunk's last position: zeros, never stale bytes)
-            uint2 scales = make_uint2(0, 0);
-            if (exists) scales = *reinterpret_cast<const uint2*>(raw + 256 + half * 8);
+            const uint32_t scales = exists ? *reinterpret_cast<const uint32_t*>(raw + 256 + quarter * 4) : 0u;
             #pragma unroll
-            for (int piece = 0; piece < 8; ++piece) {
+            for (int piece = 0; piece < 4; ++piece) {
                 uint4 bytes = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
-                if (exists) bytes = *reinterpret_cast<const uint4*>(raw + half * 128 + piece * 16);
-                const uint32_t scale_word = piece < 4 ? scales.x : scales.y;
-                const __half scale_h = __ushort_as_half(uint16_t((piece / 2) & 1 ? scale_word >> 16 : scale_word & 0xffffu));
+                if (exists) bytes = *reinterpret_cast<const uint4*>(raw + quarter * 64 + piece * 16);
+                const __half scale_h = __ushort_as_half(uint16_t(piece / 2 ? scales >> 16 : scales & 0xffffu));
                 const __half2 scale2 = __halves2half2(scale_h, scale_h);
                 const uint32_t words[4] = {bytes.x ^ 0x80808080u, bytes.y ^ 0x80808080u, bytes.z ^ 0x80808080u, bytes.w ^ 0x80808080u};
                 uint32_t hi[8], lo[8];
@@ -426,13 +444,12 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
                     hi[2 * w] = *reinterpret_cast<const uint32_t*>(&h0); hi[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&h1);
                     lo[2 * w] = *reinterpret_cast<const uint32_t*>(&l0); lo[2 * w + 1] = *reinterpret_cast<const uint32_t*>(&l1);
                 }
-                // 16 values = two 16-byte pieces of the row's 128-byte segment in block (column / 64), swizzled by the row
-                const int column = half * 128 + piece * 16, block = column / 64, c0 = (column % 64) / 8;
-                const uint32_t at0 = block * (kN * 128) + row * 128 + (((c0) ^ (row % 8)) * 16), at1 = block * (kN * 128) + row * 128 + (((c0 + 1) ^ (row % 8)) * 16);
-                *reinterpret_cast<uint4*>(hi_tile + at0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(hi_tile + at1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
-                *reinterpret_cast<uint4*>(lo_tile + at0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                *reinterpret_cast<uint4*>(lo_tile + at1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                // 16 values = two 16-byte pieces of the row's 128-byte segment, swizzled by the row
+                const uint32_t at0 = ((2 * piece) ^ (row % 8)) * 16, at1 = ((2 * piece + 1) ^ (row % 8)) * 16;
+                *reinterpret_cast<uint4*>(hi_row + at0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(hi_row + at1) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                *reinterpret_cast<uint4*>(lo_row + at0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4*>(lo_row + at1) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
             }
             fence_proxy_async();   // (the tensor core reads the tiles through the async proxy)
             __syncwarp();
