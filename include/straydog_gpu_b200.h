@@ -49,9 +49,16 @@ int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* outp
 /* ---- K/V format and staging ---- */
 /* gpu/straydog_gpu.h:113. row: 272 (Q8_0) or 512 (FP16). The attention kernels of this build read Q8_0 rows. */
 int sd_kv_format(void* handle, uint32_t row);
-/* gpu/straydog_gpu.h:114. The VRAM stage of host-resident K/V. With K/V resident in HBM the stage is
-   registered and validated but never needed. */
+/* gpu/straydog_gpu.h:114. The VRAM stage of host-resident K/V: an allocation of rows * 4096 bytes. With K/V resident in HBM the
+   stage is registered and validated but never needed; sdx_qsa_attention_gathered copies a host-resident state's selected blocks
+   into it. */
 int sd_kv_stage(void* handle, void* pointer, uint64_t rows);
+/* gpu/straydog_gpu.h:100. A zeroed state of `bytes` in page-locked host memory that the GPU reads in place (a K/V beyond the VRAM
+   budget): the pointer returned is the device's view of it and an allocation of the handle like any other (sd_write, sd_download,
+   sd_release; outside the VRAM budget). Null on failure. */
+void* sd_host_state(void* handle, uint64_t bytes);
+/* gpu/straydog_gpu.h:112. 1 when the device reads mapped host memory. */
+int sd_host_state_supported(void* handle);
 
 /* ---- Qwen3.8-style grouped-query attention over Q8_0 K/V ---- */
 /* gpu/straydog_gpu.h:528. Host pointers. The reference's own shapes: 24 query / 2 K/V heads of 256,
@@ -236,6 +243,16 @@ int sdx_ipc_close(void* handle, void* pointer);
 int sdx_qsa_attention_rows(void* handle, const void* state, uint64_t context, uint64_t base, const uint32_t* positions,
                            uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float scale, const float* input,
                            const void* mirror, uint64_t mirror_rows, const float* gates, uint64_t gate_stride, float* out);
+
+/* sdx_qsa_attention_rows over a state in host memory (sd_host_state), through the stage registered with sd_kv_stage: the union of
+   the rows' selected 4-position blocks is copied into the stage once, in block order, and the selections are renumbered to it
+   (the reference's qsa_attention_gathered, gpu/prefill_batch.hpp:227-252 over gpu/sparse_attention_compute.hpp:680-734), as many
+   rows at a time as the stage holds the union of; one host read of the union's size per attempt; a stage that cannot hold one
+   row's selection (4 * selected positions always do) is refused. The same bits as
+   sdx_qsa_attention_rows over the same state. `input` is left as it is. passes (or null): the groups of rows the call made. */
+int sdx_qsa_attention_gathered(void* handle, const void* state, uint64_t context, uint64_t base, const uint32_t* positions,
+                               uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float scale, const float* input,
+                               const float* gates, uint64_t gate_stride, float* out, uint64_t* passes);
 
 /* One decode step of a batch from HOST buffers (the batched twin of sd_attention_sequence): for
    sequence s the new token's keys/values (k, v: [sequences][kv_heads][256] F32, host) are written

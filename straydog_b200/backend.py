@@ -245,6 +245,22 @@ class Backend:
         self._c(self.lib.sdx_qsa_attention_rows(self.handle, state.pointer if isinstance(state, Buffer) else state, context, base, positions,
                                                 steps, selected, heads, kv_heads, scale, packed, m_ptr, m_rows, g_ptr, g_stride, out))
 
+    def host_state(self, size):
+        """sd_host_state: a zeroed state in page-locked host memory the GPU reads in place (outside the VRAM budget)."""
+        pointer = self.lib.sd_host_state(self.handle, size)
+        if not pointer:
+            _fail(self.lib)
+        return Buffer(self, pointer, size)
+
+    def qsa_attention_gathered(self, state, context, base, positions, steps, selected, heads, kv_heads, scale, packed, out, gates=None):
+        """sdx_qsa_attention_gathered: sdx_qsa_attention_rows over a host-resident state through the registered K/V stage; returns the
+        number of row groups the call made."""
+        g_ptr, g_stride = gates if gates else (None, 0)
+        passes = C.c_uint64(0)
+        self._c(self.lib.sdx_qsa_attention_gathered(self.handle, state.pointer if isinstance(state, Buffer) else state, context, base, positions,
+                                                    steps, selected, heads, kv_heads, scale, packed, g_ptr, g_stride, out, C.byref(passes)))
+        return passes.value
+
     def decode_status(self):
         return self._c(self.lib.sdx_decode_status(self.handle))
 

@@ -51,12 +51,14 @@ struct Device {
     unsigned kv_row = kv_row_q8;
     std::mutex mutex;
     std::map<const uint8_t*, size_t> allocations;   // base -> requested bytes
+    std::map<const uint8_t*, void*> host_states;    // device pointer -> the page-locked host allocation behind it (sd_host_state)
     std::map<const uint8_t*, size_t> peers;         // base -> bytes of other processes' allocations mapped by sdx_ipc_open
     // staging for host-pointer entries (page-locked) and device-side workspaces, grown on demand
     void* pinned = nullptr; size_t pinned_bytes = 0;
     void* work = nullptr; size_t work_bytes = 0;        // packed inputs / outputs of host-pointer entries
     void* partial = nullptr; size_t partial_bytes = 0;  // split partials of the decode kernels
     void* tables = nullptr; size_t tables_bytes = 0;    // work lists of the decode kernels
+    void* unions = nullptr; size_t unions_bytes = 0;    // places and blocks of a gathered selection union, the renumbered rows
     long long* trace = nullptr; size_t trace_ctas = 0;   // -DSDX_TRACE builds: the last traced launch's counters
     bool fixed_cuts = false;                            // the decode work list's cuts (sdx_decode_cuts)
     double* turns = nullptr; size_t turns_rows = 0, turns_pairs = 0;   // rope sincos table (forward, inverse)

@@ -44,6 +44,13 @@ void raw_release(Device& d, void* pointer) {
     auto found = d.allocations.find(static_cast<const uint8_t*>(pointer));
     if (found == d.allocations.end()) throw std::runtime_error("unknown Straydog allocation");
     SDB_CHECK(cudaStreamSynchronize(d.stream));
+    auto host = d.host_states.find(found->first);
+    if (host != d.host_states.end()) {   // a host-resident state: page-locked host memory, outside the VRAM budget
+        SDB_CHECK(cudaFreeHost(host->second));
+        d.host_states.erase(host);
+        d.allocations.erase(found);
+        return;
+    }
     SDB_CHECK(cudaFree(pointer));
     d.used -= found->second + allocation_tail;
     d.allocations.erase(found);
@@ -96,7 +103,7 @@ void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_hos
 }
 
 static void copy_in(Device& d, void* target, const void* data, size_t bytes) {
-    SDB_CHECK(cudaMemcpyAsync(target, data, bytes, cudaMemcpyHostToDevice, d.stream));
+    SDB_CHECK(cudaMemcpyAsync(target, data, bytes, cudaMemcpyDefault, d.stream));   // (the target may be a host-resident state)
 }
 
 }  // namespace sdb
@@ -163,9 +170,13 @@ void sd_destroy(void* handle) {
     if (cudaSetDevice(value->ordinal) == cudaSuccess) {
         cudaStreamSynchronize(value->stream);
         for (auto& entry : value->peers) cudaIpcCloseMemHandle(const_cast<uint8_t*>(entry.first));
-        for (auto& entry : value->allocations) cudaFree(const_cast<uint8_t*>(entry.first));
+        for (auto& entry : value->allocations) {
+            auto host = value->host_states.find(entry.first);
+            if (host != value->host_states.end()) cudaFreeHost(host->second);
+            else cudaFree(const_cast<uint8_t*>(entry.first));
+        }
         if (value->pinned) cudaFreeHost(value->pinned);
-        for (void* p : {value->work, value->partial, value->tables, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
+        for (void* p : {value->work, value->partial, value->tables, value->unions, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
         if (!value->adopted) cudaStreamDestroy(value->stream);
         cudaGetLastError();
     }
@@ -242,7 +253,7 @@ int sd_download(void* handle, void* pointer, void* output, uint64_t bytes) {
         auto& value = device(handle);
         if (!output || !bytes || allocation_bytes(value, pointer) != bytes)
             throw std::runtime_error("Straydog state readback size mismatch");
-        SDB_CHECK(cudaMemcpyAsync(output, pointer, bytes, cudaMemcpyDeviceToHost, value.stream));
+        SDB_CHECK(cudaMemcpyAsync(output, pointer, bytes, cudaMemcpyDefault, value.stream));
         SDB_CHECK(cudaStreamSynchronize(value.stream));
         return 0;
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
@@ -270,7 +281,7 @@ int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* outp
         auto& value = device(handle);
         if (!output || offset > UINT64_MAX - bytes) throw std::runtime_error("invalid Straydog buffer read");
         span(value, static_cast<const uint8_t*>(buffer) + offset, bytes, "a read buffer");
-        SDB_CHECK(cudaMemcpyAsync(output, static_cast<const uint8_t*>(buffer) + offset, bytes, cudaMemcpyDeviceToHost, value.stream));
+        SDB_CHECK(cudaMemcpyAsync(output, static_cast<const uint8_t*>(buffer) + offset, bytes, cudaMemcpyDefault, value.stream));
         SDB_CHECK(cudaStreamSynchronize(value.stream));
         return 0;
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
@@ -298,6 +309,36 @@ int sd_kv_stage(void* handle, void* pointer, uint64_t rows) {
         value.kv_stage = pointer;
         value.kv_stage_rows = rows;
         return 0;
+    } catch (const std::exception& e) { last_error = e.what(); return -1; }
+}
+
+// gpu/kernels.cpp:3876-3902: a zeroed state in page-locked host memory the GPU reads in place (a K/V that does not fit the VRAM budget);
+// the pointer returned is the device's view of it, an allocation of the handle like any other (sd_release frees it).
+void* sd_host_state(void* handle, uint64_t bytes) {
+    try {
+        auto& value = device(handle);
+        if (!bytes) throw std::runtime_error("invalid Straydog host state");
+        void* host = nullptr;
+        SDB_CHECK(cudaHostAlloc(&host, size_t(bytes) + allocation_tail, cudaHostAllocMapped));
+        void* pointer = nullptr;
+        try {
+            std::memset(host, 0, size_t(bytes) + allocation_tail);
+            SDB_CHECK(cudaHostGetDevicePointer(&pointer, host, 0));
+            std::lock_guard<std::mutex> lock(value.mutex);
+            value.host_states.emplace(static_cast<const uint8_t*>(pointer), host);
+            value.allocations.emplace(static_cast<const uint8_t*>(pointer), size_t(bytes));
+        } catch (...) { cudaFreeHost(host); throw; }
+        return pointer;
+    } catch (const std::exception& e) { last_error = e.what(); return nullptr; }
+}
+
+// gpu/kernels.cpp (sd_host_state_supported): whether the device reads mapped host memory (every B200 does: unified addressing)
+int sd_host_state_supported(void* handle) {
+    try {
+        auto& value = device(handle);
+        int can = 0;
+        SDB_CHECK(cudaDeviceGetAttribute(&can, cudaDevAttrCanMapHostMemory, value.ordinal));
+        return can ? 1 : 0;
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
 }
 

@@ -30,6 +30,7 @@ struct SelectArgs {
     const uint8_t* state;      // 2 * kv_heads planes of `context` rows
     const uint8_t* mirror;     // ring of the newest rows (2 * kv_heads planes of mirror_rows), or null
     size_t context, mirror_rows, base, steps, selected, heads, kv_heads, group, chunks;
+    size_t row0;               // the launch's first row (a launch may take a part of the packed rows)
     const uint32_t* position;  // a row's own position, or null: base + row
     const float* input;        // the packed rows
     float* partial;            // [row][head][chunk][258]
@@ -64,7 +65,7 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kSelTiles) * kSelTileBytes);
     int* tokens = reinterpret_cast<int*>(bars + kSelTiles);
-    const size_t chunk = blockIdx.x, kv = blockIdx.y, row = blockIdx.z;
+    const size_t chunk = blockIdx.x, kv = blockIdx.y, row = a.row0 + blockIdx.z;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
     const size_t index_start = a.steps * (a.heads * 256 + a.kv_heads * 512);
     const size_t count = size_t(a.input[index_start + a.steps * a.selected + row]);
@@ -245,7 +246,7 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
 // chunk without a live key, out = sum factor * acc / sum factor * denominator, times sigmoid(gate) when gates are given (:168).
 __global__ void __launch_bounds__(256) qsa_select_merge_kernel(const SelectArgs a, const float* __restrict__ gates, size_t gate_stride,
                                                                float* __restrict__ out) {
-    const size_t head = blockIdx.x, row = blockIdx.y, column = threadIdx.x;
+    const size_t head = blockIdx.x, row = a.row0 + blockIdx.y, column = threadIdx.x;
     const size_t index_start = a.steps * (a.heads * 256 + a.kv_heads * 512);
     const size_t count = size_t(a.input[index_start + a.steps * a.selected + row]);
     const size_t used = min((count + kSelChunk - 1) / kSelChunk, a.chunks);
@@ -266,6 +267,106 @@ __global__ void __launch_bounds__(256) qsa_select_merge_kernel(const SelectArgs 
         value *= x >= 0 ? 1.0f / (1.0f + e) : e / (1.0f + e);   // gpu/core.hpp:1108-1111
     }
     out[(row * a.heads + head) * 256 + column] = value;
+}
+
+// Rows [row0, row0 + rows) of the packed rows: the chunks' kernel, then the merge.
+static void launch_select(Device& value, SelectArgs& args, size_t row0, size_t rows, float scale, const float* gates, size_t gate_stride, float* out) {
+    args.row0 = row0;
+    // the chunks' partials: a library-owned workspace, grown on the first call of a size (make that call outside a stream capture)
+    args.partial = static_cast<float*>(ensure(value, value.partial, value.partial_bytes, checked_product({args.steps, args.heads, args.chunks, 258, 4})));
+    args.scale_log2 = scale * 1.4426950408889634f;
+    args.status = status_word(value);
+    static bool configured[64] = {};
+    if (!configured[value.ordinal & 63]) {
+        SDB_CHECK(cudaFuncSetAttribute(qsa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSelSmem)));
+        configured[value.ordinal & 63] = true;
+    }
+    const unsigned warps = unsigned((args.group + 7) / 8);
+    qsa_select_kernel<<<dim3(unsigned(args.chunks), unsigned(args.kv_heads), unsigned(rows)), 32 * warps, kSelSmem, value.stream>>>(args);
+    qsa_select_merge_kernel<<<dim3(unsigned(args.heads), unsigned(rows)), 256, 0, value.stream>>>(args, gates, gate_stride, out);
+    value.launches += 2;
+}
+
+// ---- a batch's selections over a K/V in host memory: the union of the selected 4-row blocks copied into the VRAM stage once ----
+// What it replaces in the reference: qsa_mark_selection, qsa_place_union, qsa_gather_union, qsa_renumber_selection
+// (gpu/sparse_attention_compute.hpp:680-734) under qsa_attention_gathered (gpu/prefill_batch.hpp:227-252). Nearby tokens select
+// overlapping blocks; read over the bus once per token they would cost the bus many times over, so the union goes to the stage in
+// block order and every selection is renumbered to it: a row reads the same keys and values in the same order, so the same bits.
+// marks[block] = 1 for every block a live slot of rows [first, first + gridDim.x) names (a live slot: the chunks' kernel's rule).
+__global__ void __launch_bounds__(256) union_mark_kernel(const SelectArgs a, size_t first, uint32_t* __restrict__ marks) {
+    const size_t row = first + blockIdx.x, index_start = a.steps * (a.heads * 256 + a.kv_heads * 512);
+    const float* indices = a.input + index_start + row * a.selected;
+    const size_t count = min(a.selected, size_t(a.input[index_start + a.steps * a.selected + row]));
+    const float limit = float(a.position ? size_t(a.position[row]) : a.base + row);
+    for (size_t i = threadIdx.x; i < count; i += 256) {
+        const float raw = indices[i];
+        if (raw >= 0 && raw <= limit && raw < float(a.context)) marks[size_t(raw) / 4] = 1u;
+    }
+}
+// marks[block] becomes the number of marked blocks before it, blocks[place] the block in that place, marks[end] the count: one
+// CTA of 1024 threads, each a run of blocks, the runs' counts scanned by warp shuffles.
+__global__ void __launch_bounds__(1024) union_place_kernel(uint32_t* __restrict__ marks, size_t end, uint32_t* __restrict__ blocks) {
+    __shared__ unsigned warp_totals[32];
+    const unsigned t = threadIdx.x, lane = t % 32, warp = t / 32;
+    const size_t per = (end + 1023) / 1024, from = min(end, size_t(t) * per), to = min(end, from + per);
+    unsigned own = 0;
+    for (size_t block = from; block < to; ++block) own += marks[block] != 0;
+    unsigned inclusive = own;
+    #pragma unroll
+    for (int offset = 1; offset < 32; offset *= 2) {
+        const unsigned other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+        if (lane >= unsigned(offset)) inclusive += other;
+    }
+    if (lane == 31) warp_totals[warp] = inclusive;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned total = warp_totals[lane], scanned = total;
+        #pragma unroll
+        for (int offset = 1; offset < 32; offset *= 2) {
+            const unsigned other = __shfl_up_sync(0xffffffffu, scanned, offset);
+            if (lane >= unsigned(offset)) scanned += other;
+        }
+        warp_totals[lane] = scanned - total;   // exclusive
+        if (lane == 31) marks[end] = scanned;
+    }
+    __syncthreads();
+    unsigned at = warp_totals[warp] + inclusive - own;
+    for (size_t block = from; block < to; ++block) {
+        const bool marked = marks[block] != 0;
+        marks[block] = at;
+        if (marked) blocks[at++] = uint32_t(block);
+    }
+}
+// Union place p's four rows of every plane, from the K/V into rows 4 p .. 4 p + 3 of the stage; a CTA per place, 16-byte pieces.
+__global__ void __launch_bounds__(256) union_gather_kernel(const uint8_t* __restrict__ state, size_t context, size_t planes,
+                                                           const uint32_t* __restrict__ blocks, const uint32_t* __restrict__ total,
+                                                           uint8_t* __restrict__ stage, size_t capacity) {
+    constexpr size_t pieces = kv_row_q8 / 16;
+    const size_t place = blockIdx.x;
+    if (place >= *total) return;
+    const size_t block = blocks[place];
+    for (size_t i = threadIdx.x; i < planes * 4 * pieces; i += 256) {
+        const size_t plane = i / (4 * pieces), row = i / pieces % 4, piece = i % pieces, position = block * 4 + row;
+        if (position >= context) continue;
+        reinterpret_cast<uint4*>(stage + (plane * capacity + place * 4 + row) * kv_row_q8)[piece] =
+            __ldg(reinterpret_cast<const uint4*>(state + (plane * context + position) * kv_row_q8) + piece);
+    }
+}
+// Rows [first, first + gridDim.x)'s selections renumbered to the union's places, into the library's copy of the packed rows (the
+// caller's stay as they are); a slot that was not live becomes -1, which no rule makes live.
+__global__ void __launch_bounds__(256) union_renumber_kernel(const SelectArgs a, size_t first, const uint32_t* __restrict__ places,
+                                                             float* __restrict__ renumbered) {
+    const size_t row = first + blockIdx.x, index_start = a.steps * (a.heads * 256 + a.kv_heads * 512);
+    const float* indices = a.input + index_start + row * a.selected;
+    float* target = renumbered + index_start + row * a.selected;
+    const size_t count = min(a.selected, size_t(a.input[index_start + a.steps * a.selected + row]));
+    const float limit = float(a.position ? size_t(a.position[row]) : a.base + row);
+    for (size_t i = threadIdx.x; i < count; i += 256) {
+        const float raw = indices[i];
+        const bool live = raw >= 0 && raw <= limit && raw < float(a.context);
+        const size_t index = live ? size_t(raw) : 0;
+        target[i] = live ? float(size_t(places[index / 4]) * 4 + index % 4) : -1.0f;
+    }
 }
 
 }  // namespace sdb
@@ -298,18 +399,78 @@ extern "C" int sdx_qsa_attention_rows(void* handle, const void* state, uint64_t 
     args.chunks = (selected + kSelChunk - 1) / kSelChunk;
     args.position = positions;
     args.input = input;
-    // the chunks' partials: a library-owned workspace, grown on the first call of a size (make that call outside a stream capture)
-    args.partial = static_cast<float*>(ensure(value, value.partial, value.partial_bytes, checked_product({steps, heads, args.chunks, 258, 4})));
-    args.scale_log2 = scale * 1.4426950408889634f;
-    args.status = status_word(value);
-    static bool configured[64] = {};
-    if (!configured[value.ordinal & 63]) {
-        SDB_CHECK(cudaFuncSetAttribute(qsa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSelSmem)));
-        configured[value.ordinal & 63] = true;
+    launch_select(value, args, 0, steps, scale, gates, gate_stride, out);
+    SDB_OP_END
+}
+
+// Selection-list attention over a K/V that lies in host memory (sd_host_state), through the VRAM stage registered with sd_kv_stage:
+// as many rows at a time as the stage holds the union of (halved until it does, one host read of the union's size per attempt, as
+// gpu/prefill_batch.hpp:232-250 does); a stage that cannot hold one row's selection is refused. The result is
+// sdx_qsa_attention_rows' over the same state bit for bit. `passes` (optional) receives how many groups of rows the call made.
+extern "C" int sdx_qsa_attention_gathered(void* handle, const void* state, uint64_t context, uint64_t base, const uint32_t* positions,
+                                          uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float scale, const float* input,
+                                          const float* gates, uint64_t gate_stride, float* out, uint64_t* passes) {
+    SDB_OP_BEGIN
+    if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
+    const uint64_t group = kv_heads ? heads / kv_heads : 0;
+    if (!context || context > (uint64_t(1) << 24) || !steps || steps > max_batch || !selected || selected > 8192 || !heads || !kv_heads ||
+        heads % kv_heads || group > 16 || kv_heads > 65535 || base > context)
+        throw std::runtime_error("invalid Straydog attention dimensions");
+    if (!value.kv_stage) throw std::runtime_error("no Straydog K/V stage is registered");
+    const size_t planes = 2 * kv_heads, capacity = size_t(value.kv_stage_rows) * 4096 / (kv_row_q8 * planes);
+    if (capacity < 4) throw std::runtime_error("invalid Straydog K/V stage");
+    const size_t packed = checked_product({steps, heads * 256 + kv_heads * 512 + selected + 1, 4});
+    span(value, state, checked_product({context, planes, kv_row_q8}), "a K/V state");
+    span(value, input, packed, "packed attention rows");
+    span(value, out, checked_product({steps, heads, 256, 4}), "an attention output");
+    if (positions) span(value, positions, steps * 4, "attention positions");
+    if (gates) span(value, gates, checked_product({(steps - 1) * gate_stride + heads * 512, 4}), "attention gates");
+    if (reinterpret_cast<uintptr_t>(state) % 16 || reinterpret_cast<uintptr_t>(input) % 16)
+        throw std::runtime_error("Straydog attention operands must be 16-byte aligned");
+    SelectArgs args{};
+    args.state = static_cast<const uint8_t*>(state);
+    args.context = context; args.base = base; args.steps = steps; args.selected = selected;
+    args.heads = heads; args.kv_heads = kv_heads; args.group = group;
+    args.chunks = (selected + kSelChunk - 1) / kSelChunk;
+    args.position = positions;
+    args.input = input;
+    // the workspace: places (end + 1 words), blocks (end words), then the renumbered copy of the packed rows
+    const size_t end = (context + 3) / 4, words = (2 * end + 1 + 3) / 4 * 4;
+    auto* places = static_cast<uint32_t*>(ensure(value, value.unions, value.unions_bytes, words * 4 + packed));
+    uint32_t* blocks = places + end + 1;
+    float* renumbered = reinterpret_cast<float*>(places + words);
+    SDB_CHECK(cudaMemcpyAsync(renumbered, input, packed, cudaMemcpyDeviceToDevice, value.stream));
+    auto* stage = static_cast<uint8_t*>(value.kv_stage);
+    uint64_t made = 0;
+    for (size_t first = 0; first < steps; ++made) {
+        size_t count = steps - first;
+        uint32_t total = 0;
+        for (;;) {
+            SDB_CHECK(cudaMemsetAsync(places, 0, (end + 1) * 4, value.stream));
+            union_mark_kernel<<<unsigned(count), 256, 0, value.stream>>>(args, first, places);
+            union_place_kernel<<<1, 1024, 0, value.stream>>>(places, end, blocks);
+            value.launches += 2;
+            SDB_CHECK(cudaMemcpyAsync(&total, places + end, 4, cudaMemcpyDeviceToHost, value.stream));
+            SDB_CHECK(cudaStreamSynchronize(value.stream));
+            if (size_t(total) * 4 <= capacity || count == 1) break;
+            count = (count + 1) / 2;
+        }
+        if (size_t(total) * 4 <= capacity) {
+            if (total) {
+                union_gather_kernel<<<total, 256, 0, value.stream>>>(args.state, context, planes, blocks, places + end, stage, capacity);
+                ++value.launches;
+            }
+            union_renumber_kernel<<<unsigned(count), 256, 0, value.stream>>>(args, first, places, renumbered);
+            ++value.launches;
+            SelectArgs staged = args;
+            staged.state = stage; staged.context = capacity; staged.input = renumbered;
+            launch_select(value, staged, first, count, scale, gates, gate_stride, out);
+        } else
+            // (the reference lets such a row read the host rows directly; the chunks' kernel fetches rows with the bulk-copy engine, which is
+            //  kept to device memory here, so a stage that cannot hold one row's selection is refused: 4 * selected positions always do)
+            throw std::runtime_error("the Straydog K/V stage is too small for one row's selection");
+        first += count;
     }
-    const unsigned warps = unsigned((group + 7) / 8);
-    qsa_select_kernel<<<dim3(unsigned(args.chunks), unsigned(kv_heads), unsigned(steps)), 32 * warps, kSelSmem, value.stream>>>(args);
-    qsa_select_merge_kernel<<<dim3(unsigned(heads), unsigned(steps)), 256, 0, value.stream>>>(args, gates, gate_stride, out);
-    value.launches += 2;
+    if (passes) *passes = made;
     SDB_OP_END
 }

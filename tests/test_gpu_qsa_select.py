@@ -127,3 +127,43 @@ def test_invalid_shapes_are_refused(gpu):
             gpu.qsa_attention_rows(state, context, 0, None, steps, selected, heads, kv_heads, 0.0625, packed.pointer, out.pointer)
     for b in (state, packed, out):
         gpu.release(b)
+
+
+@pytest.mark.parametrize("stage_rows,expect_passes", [(4096, 1), (700, None), (24, 0)])
+def test_a_host_resident_state_is_attended_through_the_gathered_union(gpu, stage_rows, expect_passes):
+    # the K/V lies in page-locked host memory (sd_host_state); the union of the rows' selected 4-position blocks is copied into the
+    # VRAM stage and the selections renumbered to it: the bits of the plain entry over a VRAM copy of the same state. Stages that hold
+    # the whole batch's union, a few rows' at a time, and not even one row's (refused).
+    rng = np.random.default_rng(77)
+    steps, selected, base, context, heads, kv_heads = 8, 600, 3000, 4096, 16, 2
+    state_np = q8_state(rng, context, kv_heads, filled=base + steps)
+    packed = attention_sequence_input(rng, steps, selected, base, context, "sparse", heads, kv_heads)
+    positions = np.arange(base, base + steps, dtype=np.uint32)
+    device_state = gpu.allocate(state_np.nbytes)
+    gpu.write(device_state, state_np)
+    want = attend(gpu, device_state, context, base, steps, selected, heads, kv_heads, packed, positions=positions)
+    assert gpu.lib.sd_host_state_supported(gpu.handle) == 1
+    host_state = gpu.host_state(state_np.nbytes)
+    gpu.write(host_state, state_np)
+    assert np.array_equal(gpu.download(host_state, np.empty_like(state_np)), state_np)
+    stage = gpu.allocate(stage_rows * 4096)
+    gpu.kv_stage(stage, stage_rows)
+    inp, pos = gpu.upload(packed), gpu.upload(positions)
+    out = gpu.upload(np.full(steps * heads * 256 + 2 * GUARD, CANARY, np.float32))
+    if expect_passes == 0:   # a stage that does not hold even one row's selection
+        from straydog_b200.backend import StraydogError
+        with pytest.raises(StraydogError, match="too small for one row"):
+            gpu.qsa_attention_gathered(host_state, context, base, pos.pointer, steps, selected, heads, kv_heads, 0.0625, inp.pointer, out.at(GUARD * 4))
+    for run in range(2 if expect_passes != 0 else 0):
+        passes = gpu.qsa_attention_gathered(host_state, context, base, pos.pointer, steps, selected, heads, kv_heads, 0.0625, inp.pointer, out.at(GUARD * 4))
+        got = gpu.read(out, np.float32, (steps * heads * 256 + 2 * GUARD,))
+        assert np.all(got[:GUARD] == CANARY) and np.all(got[-GUARD:] == CANARY), "output guard"
+        assert np.array_equal(got[GUARD:-GUARD].view(np.uint32), want.reshape(-1).view(np.uint32)), run
+        assert passes == expect_passes if expect_passes else passes > 1
+    assert gpu.decode_status() == 0
+    assert np.array_equal(gpu.read(inp, np.float32, packed.shape), packed), "the caller's rows stay as they are"
+    for b in (device_state, inp, pos, out, stage, host_state):   # (releasing the stage unregisters it)
+        gpu.release(b)
+    from straydog_b200.backend import StraydogError
+    with pytest.raises(StraydogError, match="no Straydog K/V stage"):
+        gpu.qsa_attention_gathered(device_state.pointer, context, base, None, steps, selected, heads, kv_heads, 0.0625, inp.pointer, out.pointer)
