@@ -40,11 +40,16 @@ METRIC, UNIT = "decode_attn_kv_gbps", "GB/s"
 TOLERANCE = (2e-3, 1e-2)   # max-abs or max-rel per element: the tests' tolerance
 
 
+TENSOR_SUSTAINED = 1400.0   # dense BF16 over seconds under the power cap (the fallback; the measured file overrides it)
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             peaks = json.load(f)
+        global TENSOR_SUSTAINED
+        TENSOR_SUSTAINED = float(peaks.get("bf16_tflops_sustained", TENSOR_SUSTAINED))
         return float(peaks["hbm_gbs"]), float(peaks["bf16_tflops"]), "measured (MEASURED_PEAKS.json)"
     return 6650.0, 1590.0, "fallback (6.65 TB/s, 1.59 PFLOP/s: earlier measurements on this pool)"
 
@@ -299,9 +304,11 @@ def run_qsa_config(cfg, args, local, gpu=None):
                   "roofline": ({"bound": "hbm", "achieved": kv_bytes / ms / 1e6, "peak": peak_hbm, "unit": "GB/s", "frac": kv_bytes / ms / 1e6 / peak_hbm,
                                 "note": "two launches of a few microseconds: launch-bound, the state (4.5 MB) stays in L2"}
                                if cfg == 0 else
-                               {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": peak_tensor, "unit": "TFLOP/s", "frac": flops / ms / 1e9 / peak_tensor,
+                               {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": TENSOR_SUSTAINED, "unit": "TFLOP/s",
+                                "frac": flops / ms / 1e9 / TENSOR_SUSTAINED, "frac_of_burst_peak": flops / ms / 1e9 / peak_tensor, "burst_peak": peak_tensor,
                                 "note": "algorithmic flops 4 * 256 * 16 * sum of visible keys; the kernel issues every product twice (FP16 hi and lo "
-                                        "planes of K and V), which the figure does not count"}),
+                                        "planes of K and V), which the figure does not count. The steps run back to back for about a second under the "
+                                        "power cap, so the peak is the sustained cuBLAS figure; the burst one is beside it"}),
                   "peak_source": peak_source})
     if own or ref:
         gpu.close()

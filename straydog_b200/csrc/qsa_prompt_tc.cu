@@ -280,8 +280,12 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
             #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float p0 = fast_exp2(fmaf(s[2 * i], a.scale_log2, -u)), p1 = fast_exp2(fmaf(s[2 * i + 1], a.scale_log2, -u));
-                sums[i & 3] += p0 + p1;
                 packed[i] = pack_half2(p0, p1);
+                // the denominator adds the weights as the product sees them, rounded to FP16: the output stays a convex combination of the
+                // values, and a rounding of a weight moves it by (value - output), not by the value (the worst errors, rows that one or two
+                // keys of large values dominate, shrink two to three times)
+                const float2 seen = __half22float2(*reinterpret_cast<const __half2*>(&packed[i]));
+                sums[i & 3] += seen.x + seen.y;
             }
             l_run += (sums[0] + sums[1]) + (sums[2] + sums[3]);
             tmem_st16_bits(tmem + lane_base + 256 + slot * 64 + half * 16, packed);
