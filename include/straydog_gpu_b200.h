@@ -244,6 +244,16 @@ int sdx_qsa_attention_rows(void* handle, const void* state, uint64_t context, ui
                            uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float scale, const float* input,
                            const void* mirror, uint64_t mirror_rows, const float* gates, uint64_t gate_stride, float* out);
 
+/* Qwen's indexer, the producer of the lists above (the reference's qsa_block_scores[_tiled] and qsa_select[_rows],
+   gpu/sparse_attention.hpp:141-157, 172-243, 247-296, 307-395, as qsa_index_exact launches them, :398-410; the reference has no entry of
+   its own for them). queries: `steps` rows of 4 index heads x 128 F32, query_stride floats apart (>= 512); blocks: the pooled index keys,
+   [128 columns][pool] F32. Row r at position positions[r] (or base + r) has complete = (position + 1) / 4 whole blocks: up to 512, every
+   position 0 .. position is listed; more, the 512 blocks of highest score = sum over the heads of max(0, query . key) are listed in block
+   order (equal scores by lowest block), four positions each, then the positions of the incomplete block. The lists and counts are
+   written into `packed` (the layout of sdx_qsa_attention_rows, whose queries, keys and values this call leaves alone); selected >= 2052. */
+int sdx_qsa_index_select(void* handle, const float* queries, uint64_t query_stride, const float* blocks, uint64_t pool, uint64_t base,
+                         const uint32_t* positions, uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float* packed);
+
 /* sdx_qsa_attention_rows over a state in host memory (sd_host_state), through the stage registered with sd_kv_stage: the union of
    the rows' selected 4-position blocks is copied into the stage once, in block order, and the selections are renumbered to it
    (the reference's qsa_attention_gathered, gpu/prefill_batch.hpp:227-252 over gpu/sparse_attention_compute.hpp:680-734), as many

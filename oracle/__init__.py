@@ -40,6 +40,7 @@ _sig("orc_rope", [_p, _u64, _u64, _u64, _u64, _p, _p, _i32])
 _sig("orc_compress", [_p, _p, _u64, _u64, _u64, _p])
 _sig("orc_index_scores", [_p, _p, _i32, _p, _p, _u64, _u64, _u64, _u64, _f32, _p, _u64, _u64, _p])
 _sig("orc_index_block_tops", [_p, _p, _u64, _u64, _u64, _p])
+_sig("orc_qsa_index_select", [_p, _u64, _p, _u64, _u64, _p, _u64, _u64, _u64, _p])
 _sig("orc_top_k", [_p, _u64, _u64, _u64, _p])
 _sig("orc_to_bf16", [_p, _u64, _p])
 _sig("orc_threads", [], _i32)
@@ -212,6 +213,15 @@ def index_select(q, keys, weights, visible, scale, positions, frequencies, k, ca
         c = np.take_along_axis(np.asarray(candidates, np.int64), np.maximum(picked, 0) // block, axis=1)
         picked = np.where(picked < 0, -1, c * block + np.maximum(picked, 0) % block).astype(np.int32)
     return scores, picked
+
+
+def qsa_index_select(queries, blocks, base, steps, selected, row_floats, packed, positions=None):
+    """queries [steps, 512] F32, blocks [128, pool] F32; writes the lists and counts into `packed` (float32, in place) and returns it."""
+    queries, blocks = np.ascontiguousarray(queries, np.float32), np.ascontiguousarray(blocks, np.float32)
+    positions = None if positions is None else np.ascontiguousarray(positions, np.uint32)
+    assert packed.dtype == np.float32 and packed.flags.c_contiguous and packed.size == steps * (row_floats + selected + 1)
+    _lib.orc_qsa_index_select(_ptr(queries), queries.shape[1], _ptr(blocks), blocks.shape[1], base, _ptr(positions), steps, selected, row_floats, _ptr(packed))
+    return packed
 
 
 def top_k(scores, k):

@@ -539,6 +539,43 @@ void orc_index_block_tops(const float* scores, const int32_t* visible, uint64_t 
     }
 }
 
+// gpu/sparse_attention.hpp:141-157 (qsa_block_scores; :247-296 its tiled twin with the same bits) and :172-243 (qsa_select): a row at
+// position p has complete = (p + 1) / 4 whole blocks; up to 512, every position 0 .. p; more, the 512 blocks of highest score (a dot =
+// one chain of fused multiply-adds over the 128 columns, the four heads' positive parts added in head order), equal scores by lowest
+// block, in block order, four positions each, then the positions of the incomplete block. Lists and counts go into `packed`.
+void orc_qsa_index_select(const float* queries, uint64_t query_stride, const float* blocks, uint64_t pool, uint64_t base, const uint32_t* positions,
+                          uint64_t steps, uint64_t selected, uint64_t row_floats, float* packed) {
+    const uint64_t index_start = steps * row_floats;
+    #pragma omp parallel for schedule(dynamic)
+    for (uint64_t token = 0; token < steps; ++token) {
+        const uint64_t position = positions ? positions[token] : base + token, complete = (position + 1) / 4;
+        float* indices = packed + index_start + token * selected;
+        if (complete <= 512) {
+            for (uint64_t i = 0; i <= position; ++i) indices[i] = float(i);
+            packed[index_start + steps * selected + token] = float(position + 1);
+            continue;
+        }
+        std::vector<float> scores(complete);
+        for (uint64_t block = 0; block < complete; ++block) {
+            float sums[4] = {0, 0, 0, 0};
+            for (uint64_t col = 0; col < 128; ++col) {
+                const float key = blocks[col * pool + block];
+                for (int h = 0; h < 4; ++h) sums[h] = std::fmaf(key, queries[token * query_stride + h * 128 + col], sums[h]);
+            }
+            scores[block] = std::fmax(sums[0], 0.0f) + std::fmax(sums[1], 0.0f) + std::fmax(sums[2], 0.0f) + std::fmax(sums[3], 0.0f);
+        }
+        std::vector<uint32_t> order(complete);
+        for (uint64_t i = 0; i < complete; ++i) order[i] = uint32_t(i);
+        std::stable_sort(order.begin(), order.end(), [&](uint32_t x, uint32_t y) { return scores[x] > scores[y]; });   // (stable: equal scores by block)
+        std::vector<uint32_t> kept(order.begin(), order.begin() + 512);
+        std::sort(kept.begin(), kept.end());
+        for (uint64_t j = 0; j < 512; ++j)
+            for (uint64_t tap = 0; tap < 4; ++tap) indices[4 * j + tap] = float(uint64_t(kept[j]) * 4 + tap);
+        for (uint64_t i = 0; complete * 4 + i <= position; ++i) indices[2048 + i] = float(complete * 4 + i);
+        packed[index_start + steps * selected + token] = float(2048 + position + 1 - complete * 4);
+    }
+}
+
 // gpu/dspark_attention.hpp:9-100 (dspark_attention_kernel) and crates/straydog-engine/tests/dspark_attention_gpu.rs:25-39 (its F64
 // oracle): every query row [slots][heads][512] attends the ring's history positions [anchor - history, anchor) (ring of 128 rows,
 // K = V) and all `slots` block keys; scale 1 / sqrt(512); the head's sink in the maximum and in the denominator.

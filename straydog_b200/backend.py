@@ -261,6 +261,10 @@ class Backend:
                                                     steps, selected, heads, kv_heads, scale, packed, g_ptr, g_stride, out, C.byref(passes)))
         return passes.value
 
+    def qsa_index_select(self, queries, query_stride, blocks, pool, base, positions, steps, selected, heads, kv_heads, packed):
+        """sdx_qsa_index_select: Qwen's block scores and exact top-512 block choice, written into the packed rows (device pointers)."""
+        self._c(self.lib.sdx_qsa_index_select(self.handle, queries, query_stride, blocks, pool, base, positions, steps, selected, heads, kv_heads, packed))
+
     def decode_status(self):
         return self._c(self.lib.sdx_decode_status(self.handle))
 

@@ -1,0 +1,109 @@
+// Qwen's indexer, the producer of the selection lists sdx_qsa_attention_rows consumes: block scores and the exact choice of the 512
+// best 4-position blocks of every row, written into the packed rows in the reference's layout.
+//
+// What it replaces in the reference: qsa_block_scores / qsa_block_scores_tiled (gpu/sparse_attention.hpp:141-157, 247-296) and
+// qsa_select / qsa_select_rows (:172-243, 307-395) as qsa_index_exact launches them (:398-410). The reference reaches them only from
+// inside sd_qsa_sequence and its spans, so there is no entry of its library to hold this one to: parity here rests on the oracle's
+// restatement of those lines (bit for bit: the scores are chains of fused multiply-adds in column order, the choice is integer work).
+//
+// Contract kept: a row at position p has complete = (p + 1) / 4 whole blocks. Up to 512 of them: every position 0 .. p is selected, in
+// order. More: score(block) = sum over the four index heads of max(0, sum_col key[col][block] * query[head][col]) (each dot one chain
+// of fused multiply-adds over the 128 columns in order, the four terms added in head order); the 512 blocks of highest score are
+// kept, equal scores by lowest block, listed in block order, four positions each; then the positions of the incomplete block,
+// 4 * complete .. p; the count is 2048 + (p + 1 - 4 * complete).
+//
+// Here: one scores kernel for any number of rows (a thread owns a block and eight rows' four running dots, so a key column value is
+// loaded once for 32 fused multiply-adds; the rows' queries sit in shared memory), then the library's top-k kernel (two reads of a
+// row, ties by lowest index, ascending output: the same rule) and a kernel that expands the chosen blocks into the packed rows.
+#include "common.cuh"
+#include "../../include/straydog_gpu_b200.h"
+
+namespace sdb {
+
+void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block);
+
+constexpr int kIndexRows = 8, kIndexBlocks = 128, kIndexKeep = 512;
+
+// grid (ceil(pool / 128), ceil(steps / 8)); scores [steps][pool], -inf from a row's first incomplete block on
+__global__ void __launch_bounds__(kIndexBlocks) qsa_block_scores_kernel(const float* __restrict__ queries, size_t query_stride, const float* __restrict__ blocks,
+                                                                        size_t pool, size_t base, const uint32_t* __restrict__ positions, size_t steps,
+                                                                        float* __restrict__ scores) {
+    __shared__ float q[kIndexRows][512];
+    const size_t row0 = size_t(blockIdx.y) * kIndexRows, block = size_t(blockIdx.x) * kIndexBlocks + threadIdx.x;
+    const int rows = int(min(size_t(kIndexRows), steps - row0));
+    size_t most = 0;   // the most whole blocks a row of this CTA has
+    for (int r = 0; r < rows; ++r) most = max(most, (size_t(positions ? positions[row0 + r] : base + row0 + r) + 1) / 4);
+    const bool wanted = most > size_t(kIndexKeep) && size_t(blockIdx.x) * kIndexBlocks < most;
+    if (wanted) {
+        for (int i = threadIdx.x; i < kIndexRows * 512; i += kIndexBlocks)
+            q[i / 512][i % 512] = i / 512 < rows ? queries[(row0 + i / 512) * query_stride + i % 512] : 0.0f;
+    }
+    __syncthreads();
+    float acc[kIndexRows][4];
+    #pragma unroll
+    for (int r = 0; r < kIndexRows; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+    if (wanted && block < pool) {
+        #pragma unroll 4
+        for (int col = 0; col < 128; ++col) {
+            const float key = blocks[size_t(col) * pool + block];
+            #pragma unroll
+            for (int r = 0; r < kIndexRows; ++r)
+                #pragma unroll
+                for (int h = 0; h < 4; ++h) acc[r][h] = fmaf(key, q[r][h * 128 + col], acc[r][h]);
+        }
+    }
+    if (block >= pool) return;
+    #pragma unroll
+    for (int r = 0; r < kIndexRows; ++r) {
+        if (r >= rows) break;
+        const size_t complete = (size_t(positions ? positions[row0 + r] : base + row0 + r) + 1) / 4;
+        const float score = __fadd_rn(__fadd_rn(__fadd_rn(fmaxf(acc[r][0], 0.0f), fmaxf(acc[r][1], 0.0f)), fmaxf(acc[r][2], 0.0f)), fmaxf(acc[r][3], 0.0f));
+        scores[(row0 + r) * pool + block] = complete > size_t(kIndexKeep) && block < complete ? score : -INFINITY;
+    }
+}
+
+// grid steps: the row's list and count into the packed rows
+__global__ void __launch_bounds__(256) qsa_expand_selection_kernel(const int32_t* __restrict__ picked, size_t base, const uint32_t* __restrict__ positions,
+                                                                   size_t steps, size_t selected, size_t row_floats, float* __restrict__ packed) {
+    const size_t row = blockIdx.x, position = positions ? positions[row] : base + row, complete = (position + 1) / 4;
+    const size_t index_start = steps * row_floats;
+    float* indices = packed + index_start + row * selected;
+    if (complete <= size_t(kIndexKeep)) {
+        for (size_t i = threadIdx.x; i <= position; i += 256) indices[i] = float(i);
+        if (threadIdx.x == 0) packed[index_start + steps * selected + row] = float(position + 1);
+        return;
+    }
+    for (size_t i = threadIdx.x; i < size_t(kIndexKeep) * 4; i += 256) indices[i] = float(size_t(picked[row * kIndexKeep + i / 4]) * 4 + i % 4);
+    const size_t head = size_t(kIndexKeep) * 4;
+    for (size_t i = threadIdx.x; complete * 4 + i <= position; i += 256) indices[head + i] = float(complete * 4 + i);
+    if (threadIdx.x == 0) packed[index_start + steps * selected + row] = float(head + position + 1 - complete * 4);
+}
+
+}  // namespace sdb
+
+using namespace sdb;
+
+extern "C" int sdx_qsa_index_select(void* handle, const float* queries, uint64_t query_stride, const float* blocks, uint64_t pool, uint64_t base,
+                                    const uint32_t* positions, uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float* packed) {
+    SDB_OP_BEGIN
+    if (!steps || steps > 65535 || !pool || pool > (uint64_t(1) << 22) || query_stride < 512 || selected < 2052 || selected > 8192 || !heads || !kv_heads ||
+        (!positions && (base + steps - 1) / 4 >= pool))
+        throw std::runtime_error("invalid Straydog indexer dimensions");
+    const size_t row_floats = heads * 256 + kv_heads * 512;
+    span(value, queries, checked_product({steps - 1, query_stride, 4}) + 512 * 4, "index queries");
+    span(value, blocks, checked_product({128, pool, 4}), "pooled index keys");
+    span(value, packed, checked_product({steps, row_floats + selected + 1, 4}), "packed attention rows");
+    if (positions) span(value, positions, steps * 4, "attention positions");
+    // scores [steps][pool] and the chosen blocks [steps][512]: a library-owned workspace (make the first call of a size outside a capture)
+    const size_t scores_bytes = checked_product({steps, pool, 4});
+    auto* scores = static_cast<float*>(ensure(value, value.work, value.work_bytes, scores_bytes + checked_product({steps, size_t(kIndexKeep), 4})));
+    auto* picked = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(scores) + scores_bytes);
+    qsa_block_scores_kernel<<<dim3(unsigned((pool + kIndexBlocks - 1) / kIndexBlocks), unsigned((steps + kIndexRows - 1) / kIndexRows)), kIndexBlocks, 0, value.stream>>>(
+        queries, size_t(query_stride), blocks, size_t(pool), size_t(base), positions, size_t(steps), scores);
+    ++value.launches;
+    SDB_CHECK(cudaGetLastError());
+    launch_top_k(value, scores, size_t(steps), size_t(pool), size_t(kIndexKeep), picked, nullptr, 0, 1);
+    qsa_expand_selection_kernel<<<unsigned(steps), 256, 0, value.stream>>>(picked, size_t(base), positions, size_t(steps), size_t(selected), row_floats, packed);
+    ++value.launches;
+    SDB_OP_END
+}

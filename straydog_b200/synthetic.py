@@ -212,3 +212,18 @@ def tie_scores(random, rows, groups):
         else:
             out[i] = np.float32((draw >> 8) % 17) * np.float32(0.25) - np.float32(2.0) + (np.float32(0.125) if i % 1000 == 999 else np.float32(0.0))
     return out.reshape(rows, groups)
+
+
+def qsa_index_case(steps, base, pool, heads=16, kv_heads=2, selected=2052, seed=0, integers=False):
+    """Inputs of Qwen's indexer: `steps` rows of four 128-wide index queries, the pooled index keys [128][pool], and packed rows
+    (gpu/core.hpp:392) whose list and count parts are to be written. integers: small whole numbers, so that every sum is exact in any
+    order and equal scores are common (the tie rule shows)."""
+    rng = np.random.default_rng([steps, base, pool, seed])
+    if integers:
+        queries, blocks = rng.integers(-3, 4, (steps, 512)).astype(np.float32), rng.integers(-2, 3, (128, pool)).astype(np.float32)
+    else:
+        queries, blocks = rng.normal(0, 1, (steps, 512)).astype(np.float32), rng.normal(0, 1, (128, pool)).astype(np.float32)
+    row_floats = heads * 256 + kv_heads * 512
+    packed = rng.normal(0, 1, steps * (row_floats + selected + 1)).astype(np.float32)
+    return dict(queries=queries, blocks=blocks, packed=packed, row_floats=row_floats, steps=steps, base=base, pool=pool, selected=selected,
+                heads=heads, kv_heads=kv_heads)
