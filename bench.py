@@ -315,6 +315,69 @@ def run_qsa_config(cfg, args, local, gpu=None):
     return entry
 
 
+# ---- the index producers: top-k of a row of scores, and the fused index select (scores + top-k) ----
+def run_index_ops(args, local, gpu):
+    """sd_op_top_k on (32 rows, 65 536 groups, k 2048) and sd_op_index_select on (32 rows, 16 384 groups of BF16 keys, 64 heads x 128, rope 64,
+    k 2048), each timed with device events, checked against the oracle bit for bit, and timed on the reference's own library beside it
+    when that library is present (host-timed around a synchronising read, as its calls queue on its own stream)."""
+    from straydog_b200.backend import Backend
+    from straydog_b200 import synthetic
+    import oracle
+    peak_hbm, _, peak_source = measured_peaks()
+    rng = np.random.default_rng(SEED + 9)
+    rows, groups, k = 32, 65536, 2048
+    scores_np = rng.normal(0, 1, (rows, groups)).astype(np.float32)
+    scores_np[:, ::97] = scores_np[:, 5::97]          # equal scores, so the tie rule takes part
+    c = synthetic.index_case(rows, 16384, heads=64, dim=128, rope_dims=64, spread=0)
+    halves = oracle.to_bf16(c["keys"])
+
+    def measure(lib_gpu, device_events):
+        scores, picked = lib_gpu.upload(scores_np), lib_gpu.buffer(rows * k * 4)
+        bufs = {name: lib_gpu.upload(c[name]) for name in ("q", "weights", "visible", "positions", "frequencies")}
+        keys = lib_gpu.upload(halves)
+        index_scores, index_picked = lib_gpu.buffer(rows * c["groups"] * 4), lib_gpu.buffer(rows * k * 4)
+        steps_top = lambda: lib_gpu.top_k(scores.pointer, rows, groups, k, picked.pointer)
+        steps_select = lambda: lib_gpu.index_select(bufs["q"].pointer, keys.tagged_bf16(), bufs["weights"].pointer, bufs["visible"].pointer, rows,
+                                                    c["groups"], c["heads"], c["dim"], c["scale"],
+                                                    (c["rope_dims"], bufs["positions"].pointer, bufs["frequencies"].pointer),
+                                                    index_scores.pointer, k, index_picked.pointer)
+        times = {}
+        for name, step, probe in (("top_k", steps_top, picked), ("index_select", steps_select, index_picked)):
+            if device_events:
+                for _ in range(5):
+                    step()
+                start, stop = lib_gpu.event(), lib_gpu.event()
+                lib_gpu.record(start)
+                for _ in range(200):
+                    step()
+                lib_gpu.record(stop)
+                lib_gpu.synchronize()
+                times[name] = Backend.elapsed_ms(start, stop) / 200
+            else:
+                times[name] = host_timed(lib_gpu, step, probe, 50)
+        got = lib_gpu.read(picked, np.int32, (rows, k)), lib_gpu.read(index_scores, np.float32, (rows, c["groups"])), lib_gpu.read(index_picked, np.int32, (rows, k))
+        for b in [scores, picked, keys, index_scores, index_picked] + list(bufs.values()):
+            lib_gpu.release(b)
+        return times, got
+    times, (picked, index_scores, index_picked) = measure(gpu, True)
+    if not np.array_equal(picked, oracle.top_k(scores_np, k)) or not np.array_equal(index_picked, oracle.top_k(index_scores, k)):
+        raise SystemExit("index ops: the chosen indices differ from the oracle's")
+    entry = {"workload": "sd_op_top_k (32 x 65536 scores, k 2048) and sd_op_index_select (32 rows, 16384 BF16 keys of 128, 64 heads, rope 64, k 2048)",
+             "top_k_ms": times["top_k"], "index_select_ms": times["index_select"], "indices_equal_oracle": True,
+             "top_k_roofline": {"bound": "hbm", "achieved": rows * groups * 4 / times["top_k"] / 1e6, "peak": peak_hbm, "unit": "GB/s",
+                                "frac": rows * groups * 4 / times["top_k"] / 1e6 / peak_hbm,
+                                "note": "algorithmic bytes = the scores once (8.4 MB: they fit L2, and the kernel reads them twice); a row is one CTA, so 32 rows use 32 SMs"},
+             "peak_source": peak_source}
+    if os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libstraydog_ref.so")):
+        ref = reference_gpu_backend(1 << 30)
+        ref_times, (ref_picked, ref_scores, ref_index) = measure(ref, False)
+        ref.close()
+        entry.update({"reference_top_k_ms": ref_times["top_k"], "reference_index_select_ms": ref_times["index_select"],
+                      "equal_to_reference_library": bool(np.array_equal(picked, ref_picked) and np.array_equal(index_picked, ref_index) and
+                                                         np.array_equal(index_scores.view(np.uint32), ref_scores.view(np.uint32)))})
+    return entry
+
+
 # ---- configurations 3 and 4: latent sparse attention, decode rows and verify spans ----
 def latent_inputs(gpu, cfg, heads, context, local, device_rows=True):
     """Seeded inputs of configurations 3 / 4. The BF16 latent rows (2.4 GB / 0.6 GB) are drawn on the device by torch's seeded
@@ -845,6 +908,7 @@ def main():
                 "3_128_heads": run_latent_config(3, args, local, gpu, head_shards=1),
                 "4": run_latent_config(4, args, local, gpu, head_shards=shards),
                 "4_128_heads": run_latent_config(4, args, local, gpu, head_shards=1),
+                "index_ops": run_index_ops(args, local, gpu),
             }
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -8,8 +8,9 @@
 // multiply-adds over the columns in order, each term one rounded product, the terms added in head order; sd_op_index_select gives
 // the scores and indices that sd_op_rope, sd_op_index_scores and sd_op_top_k give one after the other
 // (crates/straydog-engine/tests/fused_gpu.rs:391-431). The kernels here keep that order of operations with another division of
-// the work: a thread owns one group's key and all the heads' running dots, the queries (up to 64 heads x 32 columns at a time) and a
-// tile of 128 keys x 32 columns go through shared memory with coalesced loads, BF16-tagged keys are widened as they land.
+// the work: a thread owns a 4 x 4 register tile of (place, head) running dots fed by 16-byte shared-memory reads (see
+// index_scores_kernel), BF16-tagged keys are widened as they land. The tensor cores are not used: their summation order is not the
+// contract's.
 #include "common.cuh"
 #include "ds_sparse.cuh"
 #include "../../include/straydog_gpu_b200.h"
@@ -53,58 +54,78 @@ __global__ void __launch_bounds__(256) compress_kernel(const float* __restrict__
     out[index] = __fdiv_rn(acc, sum);
 }
 
-constexpr int kIndexGroups = 128, kIndexCols = 32, kIndexHeads = 64;
+constexpr int kIndexGroups = 64, kIndexCols = 32, kIndexHeads = 64, kIndexThreads = 256, kIndexStride = 68;   // (68 floats: 16-byte aligned rows)
 
-// A block scores `kIndexGroups` places of one row; a thread a place. With candidates, place v of a row stands for group
-// candidates[v / block] * block + v % block (none where the slot is -1) and the scores are stored in candidate order.
-__global__ void __launch_bounds__(kIndexGroups) index_scores_kernel(const float* __restrict__ q, const float* keys, const float* __restrict__ weights,
-                                                                    const int32_t* __restrict__ visible, size_t groups, size_t heads, size_t dim,
-                                                                    float scale, float* __restrict__ scores, const int32_t* __restrict__ candidates,
-                                                                    size_t blocks, size_t block) {
-    const size_t row = blockIdx.y, scored = candidates ? blocks * block : groups, place = size_t(blockIdx.x) * kIndexGroups + threadIdx.x;
-    const unsigned t = threadIdx.x;
+// A CTA scores 64 places of one row against all (<= 64) heads: thread (tg, th) = (t % 16, t / 16) owns places 4 tg .. 4 tg + 3 and heads
+// 4 th .. 4 th + 3, sixteen running dots, and per column reads one 16-byte piece of the key tile and one of the query tile (both kept
+// column-major in shared memory) for sixteen fused multiply-adds: the arithmetic pipe, not the shared-memory pipe, sets the pace. The
+// order of operations is the reference's: a dot is one chain over the columns in order, a head's term one rounded product, the terms
+// are added in head order by one thread a place. With candidates, place v of a row stands for group candidates[v / block] * block +
+// v % block (none where the slot is -1) and the scores are stored in candidate order.
+__global__ void __launch_bounds__(kIndexThreads) index_scores_kernel(const float* __restrict__ q, const float* keys, const float* __restrict__ weights,
+                                                                     const int32_t* __restrict__ visible, size_t groups, size_t heads, size_t dim,
+                                                                     float scale, float* __restrict__ scores, const int32_t* __restrict__ candidates,
+                                                                     size_t blocks, size_t block) {
+    const size_t row = blockIdx.y, scored = candidates ? blocks * block : groups, place0 = size_t(blockIdx.x) * kIndexGroups;
+    const unsigned t = threadIdx.x, tg = t % 16, th = t / 16;
     const size_t limit = min(groups, size_t(max(visible[row], 0)));
-    size_t g = groups;
-    if (place < scored) {
-        if (!candidates) g = place;
-        else { const int32_t b = candidates[row * blocks + place / block]; g = b < 0 ? groups : size_t(b) * block + place % block; }
-    }
-    __shared__ float qs[kIndexHeads][kIndexCols + 1];
-    __shared__ float ks[kIndexGroups][kIndexCols + 1];
+    __shared__ __align__(16) float tiles[2 * kIndexCols * kIndexStride];   // keys [column][place] | queries [column][head]; then the terms [head][place]
     __shared__ size_t tile_groups[kIndexGroups];
-    tile_groups[t] = g;
-    float acc[kIndexHeads];
+    float* ks = tiles;
+    float* qs = tiles + kIndexCols * kIndexStride;
+    if (t < kIndexGroups) {
+        const size_t place = place0 + t;
+        size_t g = groups;
+        if (place < scored) {
+            if (!candidates) g = place;
+            else { const int32_t b = candidates[row * blocks + place / block]; g = b < 0 ? groups : size_t(b) * block + place % block; }
+        }
+        tile_groups[t] = g;
+    }
+    float acc[4][4];   // [place][head]
     #pragma unroll
-    for (int h = 0; h < kIndexHeads; ++h) acc[h] = 0.0f;
+    for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
     const float* row_q = q + row * heads * dim;
     const bool bf16 = state_is_bf16(keys);
     for (size_t d0 = 0; d0 < dim; d0 += kIndexCols) {
         __syncthreads();
-        for (unsigned i = t; i < kIndexHeads * kIndexCols; i += kIndexGroups) {
-            const size_t h = i / kIndexCols, col = d0 + i % kIndexCols;
-            qs[h][i % kIndexCols] = h < heads && col < dim ? row_q[h * dim + col] : 0.0f;
-        }
-        for (unsigned i = t; i < kIndexGroups * kIndexCols; i += kIndexGroups) {
-            const size_t at = tile_groups[i / kIndexCols], col = d0 + i % kIndexCols;
+        // (a warp reads 32 consecutive columns of one key or one head's query, and writes them down a column of the tile)
+        for (unsigned i = t; i < kIndexGroups * kIndexCols; i += kIndexThreads) {
+            const unsigned r = i / kIndexCols, c = i % kIndexCols;
+            const size_t at = tile_groups[r], col = d0 + c;
             float value = 0.0f;
             if (at < limit && col < dim)
                 value = bf16 ? __uint_as_float(uint32_t(state_halves(keys)[at * dim + col]) << 16) : keys[at * dim + col];
-            ks[i / kIndexCols][i % kIndexCols] = value;
+            ks[c * kIndexStride + r] = value;
+            qs[c * kIndexStride + r] = r < heads && col < dim ? row_q[r * dim + col] : 0.0f;
         }
         __syncthreads();
         const int width = int(min(size_t(kIndexCols), dim - d0));
+        #pragma unroll 8
         for (int c = 0; c < width; ++c) {
-            const float k = ks[t][c];
+            const float4 k4 = *reinterpret_cast<const float4*>(ks + c * kIndexStride + 4 * tg);
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + c * kIndexStride + 4 * th);
+            const float k[4] = {k4.x, k4.y, k4.z, k4.w}, qv[4] = {q4.x, q4.y, q4.z, q4.w};
             #pragma unroll
-            for (int h = 0; h < kIndexHeads; ++h) acc[h] = fmaf(qs[h][c], k, acc[h]);
+            for (int i = 0; i < 4; ++i)
+                #pragma unroll
+                for (int h = 0; h < 4; ++h) acc[i][h] = fmaf(qv[h], k[i], acc[i][h]);
         }
     }
-    if (place >= scored) return;
-    float total = 0.0f;
+    __syncthreads();
+    float* terms = tiles;   // [head][place], 64 x 68 floats
     #pragma unroll
-    for (int h = 0; h < kIndexHeads; ++h)
-        if (size_t(h) < heads) total = __fadd_rn(total, __fmul_rn(fmaxf(acc[h], 0.0f), weights[row * heads + h]));
-    scores[row * scored + place] = g < limit ? __fmul_rn(total, scale) : -INFINITY;
+    for (int h = 0; h < 4; ++h) {
+        const size_t head = 4 * th + h;
+        const float w = head < heads ? weights[row * heads + head] : 0.0f;
+        *reinterpret_cast<float4*>(terms + head * kIndexStride + 4 * tg) =
+            make_float4(__fmul_rn(fmaxf(acc[0][h], 0.0f), w), __fmul_rn(fmaxf(acc[1][h], 0.0f), w), __fmul_rn(fmaxf(acc[2][h], 0.0f), w), __fmul_rn(fmaxf(acc[3][h], 0.0f), w));
+    }
+    __syncthreads();
+    if (t >= kIndexGroups || place0 + t >= scored) return;
+    float total = 0.0f;
+    for (size_t h = 0; h < heads; ++h) total = __fadd_rn(total, terms[h * kIndexStride + t]);
+    scores[row * scored + place0 + t] = tile_groups[t] < limit ? __fmul_rn(total, scale) : -INFINITY;
 }
 
 // A block's highest score, a thread a block; the block of the row's last visible group +inf (always kept), blocks of only -inf stay -inf.
@@ -122,7 +143,7 @@ __global__ void __launch_bounds__(256) index_block_tops_kernel(const float* __re
 static void launch_index_scores(Device& d, const float* q, const float* keys, const float* weights, const int32_t* visible, size_t rows, size_t groups,
                                 size_t heads, size_t dim, float scale, float* scores, const int32_t* candidates, size_t blocks, size_t block) {
     const size_t scored = candidates ? blocks * block : groups;
-    index_scores_kernel<<<dim3(unsigned((scored + kIndexGroups - 1) / kIndexGroups), unsigned(rows)), kIndexGroups, 0, d.stream>>>(
+    index_scores_kernel<<<dim3(unsigned((scored + kIndexGroups - 1) / kIndexGroups), unsigned(rows)), kIndexThreads, 0, d.stream>>>(
         q, keys, weights, visible, groups, heads, dim, scale, scores, candidates, blocks, block);
     ++d.launches;
     SDB_CHECK(cudaGetLastError());
