@@ -379,7 +379,9 @@ static int sparse_attention_call(void* handle, const float* q, const float* raw,
     // (SDX_SPARSE_KERNEL=mma3, read at each call, keeps the mma.sync kernel where the tcgen05 kernel would run: the in-library A/B)
     const char* form = std::getenv("SDX_SPARSE_KERNEL");
     if (!force_simt && sparse_tc_supported(args) && !(form && std::string(form) == "mma3")) {
-        sparse_tc_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        // (SDX_SPARSE_KERNEL=tc1 keeps the single-CTA tcgen05 kernel where the pair kernel would run)
+        if (form && std::string(form) == "tc1") sparse_tc_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
+        else sparse_tc2_launch(value, args, q, sinks, rows, pairs, forward, inverse, out);
         SDB_CHECK(cudaGetLastError());
         return 0;
     }

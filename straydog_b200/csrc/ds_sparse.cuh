@@ -61,6 +61,8 @@ bool sparse_mma_supported(const SparseArgs& a);
 bool sparse_tc_supported(const SparseArgs& a);
 void sparse_tc_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
                       const double2* forward, const double2* inverse, float* out);
+void sparse_tc2_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
+                       const double2* forward, const double2* inverse, float* out);
 void sparse_mma3_launch(Device& d, const SparseArgs& a, const float* q, const float* sinks, size_t rows, size_t pairs,
                         const double2* forward, const double2* inverse, float* out, const GatherTargets* gather = nullptr);
 

@@ -334,6 +334,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc_kernel(const Args g) {
             if (lane == 0) mbar_arrive(&bars[kPFull + b]);
         }
         // ---- epilogue: a thread per output column (TMEM lane), the heads along the columns ----
+        // (first the product before the last: a barrier that every product commits to may otherwise be read a phase early)
+        if (alive && tiles >= 2 && !wait(kPFree + ((tiles - 2) & 1), ((tiles - 2) >> 1) & 1)) alive = false;
         if (alive && wait(kDone, (tiles - 1) & 1)) {
             tc_fence_after();
             #pragma unroll 1
