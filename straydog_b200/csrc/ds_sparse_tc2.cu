@@ -20,16 +20,18 @@
 // heads the pair issues 96 instructions where the single-CTA kernel (ds_sparse_tc.cu: 64 heads, 32 keys, O transposed) issues 184;
 // tiles of 64 keys would halve that again, but their exchange buffers (four of 32 KB) do not fit beside Q and the ring.
 //
-// Warps (10): 0-3 softmax and epilogue (thread = head = TMEM lane), 4 issues the score products, 5 the output products (a thread
-// each, so that one's waits pass while the other issues), 6-9 gather the tile's half rows with 16-byte cp.async copies written where
+// Warps (14): 0-3 softmax and epilogue (thread = head = TMEM lane), 4-7 take the partial scores out of TMEM and send them to the
+// partner, 8 issues the score products, 9 the output products (a thread each, so that one's waits pass while the other issues),
+// 10-13 gather the tile's half rows with 16-byte cp.async copies written where
 // the 128-byte swizzle of the tensor core's shared-memory descriptors expects them (a ring of four tiles; four score buffers in
 // TMEM). The CTA leaves a partial (its columns' sums; the maximum and the denominator by CTA 0) per head for its split; the window
 // rows' partial comes from the FP32 kernel and sparse_combine_kernel merges them with the sink and turns the rotated columns back
 // (gpu/ops.hpp:1561-1583, 1528-1538). Every wait is bounded and reports through the status word; nobody leaves before the pair
 // has met at a cluster barrier.
 //
-// Measured on a B200 (32 rows x top-2048, dim 576, 128 heads): 105 us a call against the single-CTA kernel's 115 us and the
-// mma.sync kernel's 146 us; 16 spans x 8 rows in one launch 352 us against 401 us and 534 us. Of the pair kernel's 80 us a CTA
+// Measured on a B200 (32 rows x top-2048, dim 576, 128 heads): 104 us a call against the single-CTA kernel's 115 us and the
+// mma.sync kernel's 146 us; 16 spans x 8 rows in one launch 349 us against 401 us and 534 us. (Asking a tile's rows into L2
+// several tiles ahead made both slower; so did tiles of 48 keys in a ring of three.) Of the pair kernel's 80 us a CTA
 // spends 7 us preparing Q, 54 us in its 32 tiles (the softmax warps are the busy ones: 2600 of a tile's 3200 cycles, most of it the
 // fixed cost of a tile - TMEM load and store with their waits, the proxy fence, the copy's issue - not its 32 exponentials) and 9 us
 // writing its partial.
@@ -41,7 +43,7 @@ namespace sdb {
 namespace tc2 {
 
 constexpr int kHeads = 128, kKeys = 32, kSlots = 4;   // heads a CTA, keys a tile, tiles in the ring
-constexpr int kSoftmaxWarps = 4, kScoreWarp = 4, kValueWarp = 5, kCopyWarp0 = 6, kCopyWarps = 4, kThreads = 32 * (kCopyWarp0 + kCopyWarps);
+constexpr int kSoftmaxWarps = 4, kSendWarp0 = 4, kScoreWarp = 8, kValueWarp = 9, kCopyWarp0 = 10, kCopyWarps = 4, kThreads = 32 * (kCopyWarp0 + kCopyWarps);
 constexpr int kSCol = 320, kSStride = kKeys, kScoreBuffers = (512 - kSCol) / kSStride >= 4 ? 4 : 3, kExchange = kHeads * kKeys * 4;   // the score buffers' first TMEM column and their distance; bytes of one exchange buffer
 static_assert(kKeys == 32 || kKeys == 48 || kKeys == 64, "a tile: whole 16-key steps of the output product, at most two words of indices a lane");
 constexpr float kRescaleThreshold = 8.0f;
@@ -55,7 +57,7 @@ template<int DIM> struct Shape {
     static_assert(kSmem <= 232448, "shared memory of one CTA");
 };
 
-enum Bar { kFull = 0, kFree = kSlots, kSFull = 2 * kSlots, kSFree = kSFull + kScoreBuffers, kPFull = kSFree + kScoreBuffers, kRecv = kPFull + kScoreBuffers, kAck = kRecv + 8, kBars = kAck + 8 };   // kRecv, kAck: [buffer][softmax warp]   // kRecv: [buffer][softmax warp]
+enum Bar { kFull = 0, kFree = kSlots, kSFull = 2 * kSlots, kSFree = kSFull + kScoreBuffers, kPFull = kSFree + kScoreBuffers, kRecv = kPFull + kScoreBuffers, kAck = kRecv + 8, kStaged = kAck + 8, kRead = kStaged + 8, kBars = kRead + 8 };   // kRecv, kAck: [buffer][softmax warp]   // kRecv: [buffer][softmax warp]
 
 struct Args {
     SparseArgs a;
@@ -69,9 +71,9 @@ struct Args {
     long long* trace;        // -DSDX_TRACE only
 };
 
-// Built with -DSDX_TRACE: eight 64-bit counters a CTA (0 the score thread's cycles in all, 1 its wait for a tile, 3 for a free score
-// buffer, 5 tiles; 2 the output thread's wait for the weights; of head 0's softmax thread: 6 its wait for the scores, 4 for the
-// partner's partial sums, 7 its cycles in all).
+// Built with -DSDX_TRACE: eight 64-bit counters a CTA (0 the score thread's cycles in its loop, 1 of them waiting for a tile, 5 tiles;
+// of head 0's softmax thread: 3 the cycles before its loop (Q's preparation), 7 in its loop, 4 of them waiting for the two halves'
+// rows, 2 after it (the last products and the partial's stores); 6 head 0's sender's wait for the scores).
 #if defined(SDX_TRACE)
 #define SDX_TRACE_ADD(slot, since) trace[slot] += clock64() - (since)
 #define SDX_TRACE_OUT(slot) g.trace[((size_t(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8 + (slot)] = trace[slot]
@@ -295,21 +297,23 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
     };
     const int32_t* chosen = a.selected + row * a.selections;
 
-    if (warp < kSoftmaxWarps) {
-        // ================= softmax and epilogue: a thread per head (TMEM lane 32 warp + lane) =================
-        // A tile's work comes in two halves, and the first half of tile j + 1 runs before the second half of tile j, so that the
-        // exchange of one tile's partial sums is under way while the other tile's weights are formed:
-        //   send(j)   the warp's 32 rows of S_h leave TMEM for the local send buffer j % 2 ([warp][piece][lane]: neither these stores nor the
-        //             loads later meet in a bank) and lane 0 sends them (one bulk copy, TMA engine, through distributed shared memory) to the
-        //             same place of the partner's receive buffer j % 2, completing on the mbarrier the partner's same warp waits on (a
-        //             warp needs its own heads' sums only). Before that, for j >= 2, it waits for the partner's word that it has read
-        //             tile j - 2's rows: then this CTA's copy of tile j - 2 has landed (the send buffer is free) and the partner's receive
-        //             buffer may be overwritten.
-        //   finish(j) waits for the partner's rows, adds them to its own (read back from the send buffer), tells the partner that they
-        //             are read, and forms the weights.
-        const int head = 32 * warp + lane;
-        const uint32_t lane_base = uint32_t(warp * 32) << 16;
-        const uint32_t at = uint32_t(warp) * (kExchange / 4) + uint32_t(lane) * 16;   // + piece * 512, within one exchange buffer
+    if (warp < kSendWarp0 + kSoftmaxWarps) {
+        // ================= softmax and epilogue (warps 0-3) and their senders (warps 4-7): a thread per head (TMEM lane 32 (warp % 4) + lane) =================
+        const int quad = warp % 4;
+        const bool sender = warp >= kSendWarp0;
+        // A tile's work comes in two halves with a warp each, so that the exchange of one tile's partial sums is under way while an earlier
+        // tile's weights are formed:
+        //   send(j)   (warps 4-7) the quadrant's 32 rows of S_h leave TMEM for the local send buffer j % 2 ([quadrant][piece][lane]: neither
+        //             these stores nor the loads later meet in a bank) and lane 0 sends them (one bulk copy, TMA engine, through distributed
+        //             shared memory) to the same place of the partner's receive buffer j % 2, completing on the mbarrier the partner's
+        //             same quadrant waits on (it needs its own heads' sums only). Before that, for j >= 2, it waits for the partner's word
+        //             that it has read tile j - 2's rows (then this CTA's copy of tile j - 2 has landed and the partner's receive buffer may
+        //             be overwritten) and for this CTA's softmax warp to have read its own rows of tile j - 2 back.
+        //   finish(j) (warps 0-3) waits for this CTA's rows to be laid down and for the partner's to arrive, adds them, tells both senders
+        //             that they are read, and forms the weights.
+        const int head = 32 * quad + lane;
+        const uint32_t lane_base = uint32_t(quad * 32) << 16;
+        const uint32_t at = uint32_t(quad) * (kExchange / 4) + uint32_t(lane) * 16;   // + piece * 512, within one exchange buffer
         uint8_t* send_buffers = exchange;                     // [2]
         uint8_t* receive_buffers = exchange + 2 * kExchange;  // [2]
         const uint32_t their_receive = cluster_address(smem_u32(receive_buffers), partner);
@@ -334,9 +338,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
             if (kKeys == 64) tmem_ld32(tmem + lane_base + kSCol + sb * kSStride + 32, s + 32);
             else if (kKeys == 48) tmem_ld16(tmem + lane_base + kSCol + sb * kSStride + 32, s + 32);
             since = clock64();
-            if (j >= 2 && __any_sync(0xffffffffu, !wait(kAck + 4 * b + warp, ((j - 2) >> 1) & 1))) { alive = false; return; }
-            SDX_TRACE_ADD(3, since);
-            since = clock64();
+            // (the partner has read tile j - 2's rows: this CTA's copy of them has landed and the partner's receive buffer is free; and this
+            //  CTA's softmax warp has read its own rows of tile j - 2 back from the send buffer)
+            if (j >= 2 && __any_sync(0xffffffffu, !wait(kAck + 4 * b + quad, ((j - 2) >> 1) & 1) || !wait(kRead + 4 * b + quad, ((j - 2) >> 1) & 1))) { alive = false; return; }
             uint8_t* mine = send_buffers + b * kExchange + at;
             #pragma unroll
             for (int piece = 0; piece < kKeys / 4; ++piece)
@@ -344,21 +348,24 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-                mbar_expect_tx(&bars[kRecv + 4 * b + warp], kExchange / 4);   // (the partner's copy into this CTA)
+                mbar_arrive(&bars[kStaged + 4 * b + quad]);                   // (this CTA's softmax warp may read the rows back)
+                mbar_expect_tx(&bars[kRecv + 4 * b + quad], kExchange / 4);   // (the partner's copy into this CTA)
                 asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(their_receive + b * kExchange + uint32_t(warp) * (kExchange / 4)), "r"(smem_u32(mine)), "r"(uint32_t(kExchange / 4)),
-                               "r"(their_recv_bar + (4 * b + warp) * 8) : "memory");
+                             ::"r"(their_receive + b * kExchange + uint32_t(quad) * (kExchange / 4)), "r"(smem_u32(mine)), "r"(uint32_t(kExchange / 4)),
+                               "r"(their_recv_bar + (4 * b + quad) * 8) : "memory");
             }
-            SDX_TRACE_ADD(2, since);
         };
-        if (tiles) send(0);
-        for (uint32_t j = 0; j < tiles && alive; ++j) {
+        if (sender) {
+            for (uint32_t j = 0; j < tiles && alive; ++j) send(j);
+#if defined(SDX_TRACE)
+            if (head == 0) SDX_TRACE_OUT(6);
+#endif
+        }
+        for (uint32_t j = 0; j < tiles && alive && !sender; ++j) {
             const uint32_t b = j & 1;
-            if (j + 1 < tiles) send(j + 1);
-            if (!alive) break;
             long long since = clock64();
             (void)since;
-            if (__any_sync(0xffffffffu, !wait(kRecv + 4 * b + warp, (j >> 1) & 1))) { alive = false; break; }
+            if (__any_sync(0xffffffffu, !wait(kStaged + 4 * b + quad, (j >> 1) & 1) || !wait(kRecv + 4 * b + quad, (j >> 1) & 1))) { alive = false; break; }
             SDX_TRACE_ADD(4, since);
             float s[kKeys];
             #pragma unroll
@@ -368,8 +375,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
                 s[4 * piece] = own.x + other.x; s[4 * piece + 1] = own.y + other.y; s[4 * piece + 2] = own.z + other.z; s[4 * piece + 3] = own.w + other.w;
             }
             __syncwarp();
-            if (lane == 0)   // (release at cluster scope, after the warp's loads: the partner may now overwrite the receive buffer and reuse its send buffer)
-                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(their_ack_bar + (4 * b + warp) * 8) : "memory");
+            if (lane == 0) {   // (release at cluster scope, after the warp's loads: the partner may now overwrite the receive buffer and reuse its send buffer)
+                asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(their_ack_bar + (4 * b + quad) * 8) : "memory");
+                mbar_arrive(&bars[kRead + 4 * b + quad]);
+            }
             const unsigned long long mask = masks[j % kSlots];
             const uint32_t mask_lo = uint32_t(mask), mask_hi = uint32_t(mask >> 32);
             (void)mask_hi;
@@ -435,10 +444,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
         }
 #if defined(SDX_TRACE)
         const long long loop_ended = clock64();
-        if (head == 0) { trace[7] = loop_ended - started; trace[3] = prologue_cycles; SDX_TRACE_OUT(4); SDX_TRACE_OUT(6); SDX_TRACE_OUT(7); SDX_TRACE_OUT(3); }
+        if (head == 0 && !sender) { trace[7] = loop_ended - started; trace[3] = prologue_cycles; SDX_TRACE_OUT(4); SDX_TRACE_OUT(6); SDX_TRACE_OUT(7); SDX_TRACE_OUT(3); }
 #endif
         // ---- epilogue: the head's row of O, this half's columns ----
-        if (alive && wait(kSFree + (tiles - 1) % kScoreBuffers, ((tiles - 1) / kScoreBuffers) & 1)) {   // (the last product, so every product, is done)
+        if (!sender && alive && wait(kSFree + (tiles - 1) % kScoreBuffers, ((tiles - 1) / kScoreBuffers) & 1)) {   // (the last product, so every product, is done)
             tc_fence_after();
             // 32 heads x 32 columns at a time through a padded tile of the (idle) ring, so that a store instruction writes 128 consecutive
             // bytes of one head's partial instead of 8 bytes of each of 32 heads'
@@ -461,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
             }
         }
 #if defined(SDX_TRACE)
-        if (head == 0) { trace[2] = clock64() - loop_ended; SDX_TRACE_OUT(2); }
+        if (head == 0 && !sender) { trace[2] = clock64() - loop_ended; SDX_TRACE_OUT(2); }
 #endif
     } else if (warp == kScoreWarp) {
         // ================= the score products' issuer =================
@@ -477,7 +486,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
                 long long since = clock64();
                 (void)since;
                 if (i >= uint32_t(kScoreBuffers) && !wait(kSFree + b, (i / kScoreBuffers - 1) & 1)) break;
-                SDX_TRACE_ADD(3, since);
                 since = clock64();
                 if (!wait(kFull + slot, (i / kSlots) & 1)) break;
                 SDX_TRACE_ADD(1, since);

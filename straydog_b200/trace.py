@@ -1,7 +1,7 @@
 """Cycle counters of the MMA-issuing threads of the two tcgen05 kernels, from a build with -DSDX_TRACE.
 
     python -m straydog_b200.trace prompt [context first rows]      # qsa_prompt_tc_kernel (default 16384 8192 8192)
-    python -m straydog_b200.trace latent [heads rows context]      # sparse_tc_kernel (default 128 32 16384)
+    python -m straydog_b200.trace latent [heads rows context]      # sparse_tc2_kernel (default 128 32 16384; SDX_SPARSE_KERNEL=tc1: sparse_tc_kernel)
 
 Builds the traced variant of the library beside the product one (libstraydog_gpu_b200_trace.so; the product build holds no
 counters), runs a few calls on cuda:0 and prints, per 64-key (prompt) or 32-key (latent) tile, the cycles each issuing thread spent in
@@ -64,12 +64,19 @@ def latent(lib, heads=128, rows=32, context=16384):
                              kb.pointer, rows, heads, dim, float(dim) ** -0.5, None, None, out.pointer)
     t = counters(gpu, lib)
     if not len(t):
-        print("the call did not take the tcgen05 kernel (it needs 128 heads or more): no counters")
-    else:
+        print("the call did not take a tcgen05 kernel (it needs 128 heads or more): no counters")
+    elif os.environ.get("SDX_SPARSE_KERNEL") == "tc1":
         per = lambda i: float((t[:, i] / t[:, 5]).mean())   # noqa: E731
         print(f"sparse_tc_kernel, {heads} heads, {rows} rows x {sel} selected: {len(t)} CTAs, {t[:, 5].mean():.0f} tiles each")
         print(f"  per 32-key tile: issuing thread {per(0):.0f} cycles (waiting for a tile {per(1):.0f}, for the weights {per(2):.0f}, "
               f"for a free score buffer {per(3):.0f}); a copy warp waiting for a free slot {per(4):.0f}")
+    else:
+        per = lambda i: float((t[:, i] / t[:, 5]).mean())   # noqa: E731
+        print(f"sparse_tc2_kernel (pairs of CTAs), {heads} heads, {rows} rows x {sel} selected: {len(t)} CTAs, {t[:, 5].mean():.0f} tiles each")
+        print(f"  a CTA: {t[:, 3].mean():.0f} cycles before the first tile (Q's preparation), {t[:, 7].mean():.0f} in the tiles, {t[:, 2].mean():.0f} after "
+              f"(the last products, the partial's stores)")
+        print(f"  per 32-key tile: score thread {per(0):.0f} cycles (waiting for a tile {per(1):.0f}); softmax thread {per(7):.0f} "
+              f"(waiting for the two halves' rows {per(4):.0f})")
     gpu.close()
 
 

@@ -9,10 +9,10 @@ from util import XorShift, bf16_round, close, sparse_attention_case
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["default", "mma3"])
+@pytest.fixture(params=["default", "mma3", "tc1"])
 def form(request):
-    """Which tensor-core kernel answers where both can: the library's own choice (the tcgen05 kernel for BF16 rows, head counts that
-    are multiples of 16 and short windows) or the mma.sync kernel for every shape."""
+    """Which tensor-core kernel answers where several can: the library's own choice (at 128 heads and more, BF16 rows and short windows
+    the pair-of-CTAs tcgen05 kernel), the mma.sync kernel for every shape, or the single-CTA tcgen05 kernel in the pair kernel's place."""
     import os
     if request.param != "default":
         os.environ["SDX_SPARSE_KERNEL"] = request.param
