@@ -47,6 +47,7 @@ struct Device {
     int ordinal = 0;
     int sms = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t side = nullptr; cudaEvent_t side_fork = nullptr, side_join = nullptr;   // a second stream for work that may run beside a kernel of `stream` (made on first use)
     uint64_t budget = 0, used = 0;
     unsigned kv_row = kv_row_q8;
     std::mutex mutex;
@@ -76,7 +77,9 @@ void span(Device& d, const void* pointer, size_t bytes, const char* what);
 void span_or_peer(Device& d, const void* pointer, size_t bytes, const char* what);   // also accepts a mapped peer allocation
 size_t allocation_bytes(Device& d, const void* base);   // requested bytes of the allocation that starts at `base`, 0 if none (takes the lock)
 void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_host = false);
-int* status_word(Device& d);   // the device's word a kernel's bounded wait sets when it gives up (read by sdx_decode_status)
+int* status_word(Device& d);
+cudaStream_t side_stream_begin(Device& d);   // the side stream, made to wait for everything queued on d.stream so far
+void side_stream_end(Device& d);             // d.stream made to wait for everything queued on the side stream so far   // the device's word a kernel's bounded wait sets when it gives up (read by sdx_decode_status)
 
 // a * b * c ... with overflow refusal (gpu/core.hpp:1413 region: an op_span check never passes on a wrapped size)
 inline size_t checked_product(std::initializer_list<uint64_t> factors) {

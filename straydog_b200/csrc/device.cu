@@ -102,6 +102,22 @@ void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_hos
     return slot;
 }
 
+cudaStream_t side_stream_begin(Device& d) {
+    if (!d.side) {
+        SDB_CHECK(cudaStreamCreateWithFlags(&d.side, cudaStreamNonBlocking));
+        SDB_CHECK(cudaEventCreateWithFlags(&d.side_fork, cudaEventDisableTiming));
+        SDB_CHECK(cudaEventCreateWithFlags(&d.side_join, cudaEventDisableTiming));
+    }
+    SDB_CHECK(cudaEventRecord(d.side_fork, d.stream));
+    SDB_CHECK(cudaStreamWaitEvent(d.side, d.side_fork, 0));
+    return d.side;
+}
+
+void side_stream_end(Device& d) {
+    SDB_CHECK(cudaEventRecord(d.side_join, d.side));
+    SDB_CHECK(cudaStreamWaitEvent(d.stream, d.side_join, 0));
+}
+
 static void copy_in(Device& d, void* target, const void* data, size_t bytes) {
     SDB_CHECK(cudaMemcpyAsync(target, data, bytes, cudaMemcpyDefault, d.stream));   // (the target may be a host-resident state)
 }
@@ -177,6 +193,7 @@ void sd_destroy(void* handle) {
         }
         if (value->pinned) cudaFreeHost(value->pinned);
         for (void* p : {value->work, value->partial, value->tables, value->unions, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
+        if (value->side) { cudaStreamDestroy(value->side); cudaEventDestroy(value->side_fork); cudaEventDestroy(value->side_join); }
         if (!value->adopted) cudaStreamDestroy(value->stream);
         cudaGetLastError();
     }

@@ -149,6 +149,20 @@ __global__ void __launch_bounds__(128) sparse_combine_kernel(const float* __rest
     constexpr int kMaxSplits = 64;
     __shared__ float factors[kMaxSplits];
     __shared__ float denominator_shared;
+    // (the usual shape - an even dim of at most 768, at most four partials - has its sums on their way from memory before the first
+    //  warp has the factors: the kernel is a chain of two round trips to memory otherwise)
+    constexpr int kEarlyPairs = 3, kEarlySplits = 4;
+    const bool early = dim % 2 == 0 && dim / 2 <= size_t(kEarlyPairs) * 128 && splits <= size_t(kEarlySplits) && blockDim.x == 128;
+    float2 sums_early[kEarlyPairs][kEarlySplits];
+    if (early) {
+        #pragma unroll
+        for (int k = 0; k < kEarlyPairs; ++k)
+            #pragma unroll
+            for (int sp = 0; sp < kEarlySplits; ++sp) {
+                const size_t pair = threadIdx.x + 128 * k;
+                sums_early[k][sp] = pair < dim / 2 && size_t(sp) < splits ? *reinterpret_cast<const float2*>(first + sp * (dim + 2) + 2 * pair) : make_float2(0.0f, 0.0f);
+            }
+    }
     if (threadIdx.x < 32) {
         // the first warp: the head's maximum (with its sink), every split's factor and the denominator
         const float sink = sinks[head];
@@ -180,7 +194,16 @@ __global__ void __launch_bounds__(128) sparse_combine_kernel(const float* __rest
     for (size_t pair = threadIdx.x; pair < dim / 2 + dim % 2; pair += blockDim.x) {
         const size_t d = 2 * pair;
         float o[2] = {0.0f, 0.0f};
-        if (d + 1 < dim && dim % 2 == 0) {
+        if (early) {
+            const int k = int(pair / 128);
+            #pragma unroll
+            for (int kk = 0; kk < kEarlyPairs; ++kk)
+                if (kk == k) {
+                    #pragma unroll
+                    for (int sp = 0; sp < kEarlySplits; ++sp)
+                        if (size_t(sp) < splits) { o[0] = fmaf(sums_early[kk][sp].x, factors[sp], o[0]); o[1] = fmaf(sums_early[kk][sp].y, factors[sp], o[1]); }
+                }
+        } else if (d + 1 < dim && dim % 2 == 0) {
             for (size_t s = 0; s < splits; ++s) {
                 const float2 x = *reinterpret_cast<const float2*>(first + s * (dim + 2) + d);   // (rows of dim + 2 floats, d even: 8-byte aligned when dim is even)
                 o[0] = fmaf(x.x, factors[s], o[0]);
@@ -266,18 +289,19 @@ static void launch_simt(Device& d, const SparseArgs& args, const float* q_used, 
 
 // For the tcgen05 kernel: the window rows' share of every (row, head) as slot 0 of its `parts` partials, in exact FP32 arithmetic.
 void sparse_window_partial(Device& d, const SparseArgs& a, const float* q, size_t rows, size_t pairs, const double2* forward, float* rotated,
-                           float* partial, size_t parts) {
+                           float* partial, size_t parts, cudaStream_t stream) {
+    if (!stream) stream = d.stream;
     const float* q_used = q;
     if (pairs) {
-        sparse_rotate_q_kernel<<<dim3(unsigned(a.heads), unsigned(rows)), 128, 0, d.stream>>>(q, a.heads, a.dim, pairs, forward, rotated);
+        sparse_rotate_q_kernel<<<dim3(unsigned(a.heads), unsigned(rows)), 128, 0, stream>>>(q, a.heads, a.dim, pairs, forward, rotated);
         ++d.launches;
         q_used = rotated;
     }
     SparseArgs window = a;
     window.selections = 0;   // (the key list of a row is then its window rows alone)
     const unsigned blocks = unsigned((rows * a.heads + 7) / 8);
-    if (a.dim <= 512) sparse_window_kernel<16><<<blocks, 256, 0, d.stream>>>(window, q_used, partial, rows, parts);
-    else sparse_window_kernel<18><<<blocks, 256, 0, d.stream>>>(window, q_used, partial, rows, parts);
+    if (a.dim <= 512) sparse_window_kernel<16><<<blocks, 256, 0, stream>>>(window, q_used, partial, rows, parts);
+    else sparse_window_kernel<18><<<blocks, 256, 0, stream>>>(window, q_used, partial, rows, parts);
     ++d.launches;
     SDB_CHECK(cudaGetLastError());
 }

@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc_kernel(const Args g) {
 
 // The FP32 kernel and the combine of ds_sparse.cu: the window rows' partial and the merge of all partials.
 void sparse_window_partial(Device& d, const SparseArgs& a, const float* q, size_t rows, size_t pairs, const double2* forward, float* rotated,
-                           float* partial, size_t parts);
+                           float* partial, size_t parts, cudaStream_t stream = nullptr);
 void sparse_combine(Device& d, const float* partial, size_t parts, size_t rows, size_t heads, size_t dim, const float* sinks, size_t pairs,
                     const double2* inverse, float* out);
 

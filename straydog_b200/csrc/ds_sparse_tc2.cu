@@ -575,7 +575,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_tc2_kernel(const Args g) {
 }  // namespace tc2
 
 void sparse_window_partial(Device& d, const SparseArgs& a, const float* q, size_t rows, size_t pairs, const double2* forward, float* rotated,
-                           float* partial, size_t parts);
+                           float* partial, size_t parts, cudaStream_t stream = nullptr);
 void sparse_combine(Device& d, const float* partial, size_t parts, size_t rows, size_t heads, size_t dim, const float* sinks, size_t pairs,
                     const double2* inverse, float* out);
 
@@ -618,7 +618,9 @@ void sparse_tc2_launch(Device& d, const SparseArgs& a, const float* q, const flo
 #endif
     auto* work = static_cast<uint8_t*>(ensure(d, d.partial, d.partial_bytes, q_bytes + partial_bytes + trace_bytes));
     auto* partial = reinterpret_cast<float*>(work + q_bytes);
-    sparse_window_partial(d, a, q, rows, pairs, forward, reinterpret_cast<float*>(work), partial, parts);
+    // the window rows' partial (slot 0 of every head's partials) has nothing to do with the selected rows' (slots 1 ..): it runs on the
+    // handle's side stream beside the pair kernel (whose grid leaves SMs idle when a call is small), and the combine waits for both
+    sparse_window_partial(d, a, q, rows, pairs, forward, reinterpret_cast<float*>(work), partial, parts, side_stream_begin(d));
     tc2::Args args{};
 #if defined(SDX_TRACE)
     args.trace = reinterpret_cast<long long*>(work + trace_at);
@@ -632,6 +634,7 @@ void sparse_tc2_launch(Device& d, const SparseArgs& a, const float* q, const flo
     args.parts = uint32_t(parts); args.splits = uint32_t(splits);
     if (a.dim == 576) launch_tc2<576>(d, args, rows, head_tiles); else launch_tc2<512>(d, args, rows, head_tiles);
     SDB_CHECK(cudaGetLastError());
+    side_stream_end(d);
     sparse_combine(d, partial, parts, rows, a.heads, a.dim, sinks, pairs, inverse, out);
 }
 
