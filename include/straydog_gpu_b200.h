@@ -29,6 +29,8 @@ const char* sd_error(void);
 /* gpu/straydog_gpu.h:18 */
 int sd_device_count(void);
 /* gpu/straydog_gpu.h:33-34. budget: bytes this handle may allocate, at most the free memory. */
+/* (the budget bounds what sd_allocate / sd_buffer / sd_upload hand out; the library's own workspaces - split partials, work lists,
+   staging of host-pointer entries - are grown beside it on the first call of a size.) */
 void* sd_create(int ordinal, uint64_t budget);
 void sd_destroy(void* handle);
 /* gpu/straydog_gpu.h:35 */
