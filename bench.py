@@ -378,6 +378,56 @@ def run_index_ops(args, local, gpu):
     return entry
 
 
+# ---- the Qwen seam: the indexer's block choice, then selection-list attention over the lists it wrote (a verification's rows) ----
+def run_qsa_rows(args, local, gpu):
+    """sdx_qsa_index_select (8 rows at positions near 32 768: 8192 blocks scored, 512 chosen, 2048 + tail positions listed) followed by
+    sdx_qsa_attention_rows over those lists (16 query / 2 K/V heads, Q8_0 state of 32 768 positions): each timed with device events,
+    the attention checked against the oracle's scalar selection attention over the oracle's lists."""
+    from straydog_b200.backend import Backend
+    from straydog_b200 import synthetic
+    import oracle
+    peak_hbm, _, peak_source = measured_peaks()
+    steps, context, selected = 8, 32768, 2052
+    base = context - steps
+    rng = np.random.default_rng(SEED + 11)
+    c = synthetic.qsa_index_case(steps, base, context // 4, HEADS, KV_HEADS, selected)
+    state_np = synthetic.q8_state(rng, context, KV_HEADS)
+    q, blocks, packed, state = gpu.upload(c["queries"]), gpu.upload(c["blocks"]), gpu.upload(c["packed"]), gpu.upload(state_np)
+    out = gpu.buffer(steps * HEADS * DIM * 4)
+    index = lambda: gpu.qsa_index_select(q.pointer, 512, blocks.pointer, c["pool"], base, None, steps, selected, HEADS, KV_HEADS, packed.pointer)
+    attend = lambda: gpu.qsa_attention_rows(state, context, base, None, steps, selected, HEADS, KV_HEADS, SCALE, packed.pointer, out.pointer)
+    # (the rows' own keys and values are appended first, as the reference's span does before it attends)
+    gpu._c(gpu.lib.sdx_kv_write(gpu.handle, state.pointer, context, KV_HEADS, base, steps, packed.at(steps * HEADS * DIM * 4), packed.at(steps * (HEADS + KV_HEADS) * DIM * 4)))
+    times = {}
+    for name, step in (("index_select_ms", index), ("attention_rows_ms", attend)):
+        for _ in range(5):
+            step()
+        start, stop = gpu.event(), gpu.event()
+        gpu.record(start)
+        for _ in range(200):
+            step()
+        gpu.record(stop)
+        gpu.synchronize()
+        times[name] = Backend.elapsed_ms(start, stop) / 200
+    got_lists, got = gpu.read(packed, np.float32, c["packed"].shape), gpu.read(out, np.float32, (steps, HEADS, DIM))
+    want_lists = oracle.qsa_index_select(c["queries"], c["blocks"], base, steps, selected, c["row_floats"], c["packed"].copy())
+    want = oracle.attention_sequence(state_np.copy(), context, HEADS, KV_HEADS, base, steps, selected, want_lists, scale=SCALE)
+    ok, error = within_tolerance(got, want)
+    if not np.array_equal(got_lists.view(np.uint32), want_lists.view(np.uint32)) or not ok or gpu.decode_status() != 0:
+        raise SystemExit(f"qsa rows: lists or outputs differ from the oracle (max abs error {error})")
+    listed = int(sum(want_lists[steps * c["row_floats"] + steps * selected + r] for r in range(steps)))
+    nbytes = listed * 2 * KV_HEADS * ROW
+    for b in (q, blocks, packed, state, out):
+        gpu.release(b)
+    return {"workload": "Qwen's indexer (8 rows, 8192 blocks, 512 chosen) and selection-list attention of the 8 rows over the lists it wrote (32768-position Q8_0 state)",
+            **times, "lists_equal_oracle": True, "max_abs_error_vs_oracle": error,
+            "attention_rows_roofline": {"bound": "hbm", "achieved": nbytes / times["attention_rows_ms"] / 1e6, "peak": peak_hbm, "unit": "GB/s",
+                                        "frac": nbytes / times["attention_rows_ms"] / 1e6 / peak_hbm,
+                                        "note": f"algorithmic bytes = {listed} listed positions x 2 K/V heads x (K row + V row) x 272 B; a call of 8 rows is "
+                                                "528 small CTAs of gathered 272-byte rows and two launches: latency, not bandwidth"},
+            "peak_source": peak_source}
+
+
 # ---- configurations 3 and 4: latent sparse attention, decode rows and verify spans ----
 def latent_inputs(gpu, cfg, heads, context, local, device_rows=True):
     """Seeded inputs of configurations 3 / 4. The BF16 latent rows (2.4 GB / 0.6 GB) are drawn on the device by torch's seeded
@@ -909,6 +959,7 @@ def main():
                 "4": run_latent_config(4, args, local, gpu, head_shards=shards),
                 "4_128_heads": run_latent_config(4, args, local, gpu, head_shards=1),
                 "index_ops": run_index_ops(args, local, gpu),
+                "qsa_rows": run_qsa_rows(args, local, gpu),
             }
     if rank == 0:
         print(json.dumps(line), flush=True)
