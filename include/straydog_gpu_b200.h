@@ -184,7 +184,8 @@ int sdx_qsa_decode_static(void* handle, const void* const* states, const uint64_
 /* What a kernel reported instead of hanging or faulting since the last call (cleared by the call), 0 if nothing:
    1 a bounded wait on a copy gave up (decode, prompt or latent kernel); 2 a selected row number lay past the latent cache (the
    row was taken as absent); 3 a key pointer lay outside the call's buffers (skipped); 4 a rank of a gathered latent attention
-   never raised its counter within a second. Synchronises the handle's stream. */
+   never raised its counter within a second; 5 a row of sdx_qsa_normalize_rows sat at a position past the K/V state (nothing of the
+   row was written). Synchronises the handle's stream. */
 int sdx_decode_status(void* handle);
 
 /* For builds of the library with -DSDX_TRACE (python -m straydog_b200.build --define SDX_TRACE --out <path>): the cycle counters the
@@ -255,6 +256,25 @@ int sdx_qsa_attention_rows(void* handle, const void* state, uint64_t context, ui
    written into `packed` (the layout of sdx_qsa_attention_rows, whose queries, keys and values this call leaves alone); selected >= 2052. */
 int sdx_qsa_index_select(void* handle, const float* queries, uint64_t query_stride, const float* blocks, uint64_t pool, uint64_t base,
                          const uint32_t* positions, uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float* packed);
+
+/* The front of Qwen's decode and verification attention in one launch, for `rows` <= 256 rows: the reference's qsa_normalize_rows
+   (gpu/qsa_decode.hpp:86-111; for one row qsa_normalize_decode + qsa_pool_one + write_attention_kv as qsa_decode_attend launches
+   them, :5-23, 28-44; the rotation and normalisation of gpu/sparse_attention.hpp:2-6, 55-71), for any heads and kv_heads. Row r of
+   `projections` (stride floats apart, stride >= heads * 512 + kv_heads * 512 + 640) holds  qgate [heads][query 256 | gate 256] |
+   key [kv_heads][256] | value [kv_heads][256] | index query [4][128] | index key [128].  The call writes the RMS-normalised, rotated
+   queries and keys into `packed` (the layout of sdx_qsa_attention_rows for `rows` rows and `selected` slots; its values, lists and
+   counts are left alone), encodes each row's normalised keys and its values into row positions[r] of the Q8_0 `state` (and of
+   `mirror`, the ring of mirror_rows positions of a host-resident state, or null / 0), normalises and rotates the four index-query
+   heads in place, and passes the rows' index keys through the history ring: a row whose position completes a 4-position block
+   pools it into index_state ([128][context / 4 + 1] pooled blocks followed by the ring of 16 x 128, gpu/sparse_attention.hpp:462).
+   positions: the rows' K/V positions; ropes: their rotation positions (the same numbers unless the sequence holds images). Then
+   sdx_qsa_index_select (queries = projections + heads * 512 + kv_heads * 512, blocks = index_state) and sdx_qsa_attention_rows
+   (gates = projections) finish what the reference's qsa_decode_attend_rows does (gpu/qsa_decode.hpp:113-129). A position past the
+   state writes nothing and reports status 5. */
+int sdx_qsa_normalize_rows(void* handle, float* projections, uint64_t stride, uint64_t rows, uint64_t heads, uint64_t kv_heads,
+                           const float* qnorm, const float* knorm, const float* iqnorm, const float* pool_norm,
+                           const uint32_t* positions, const uint32_t* ropes, float* packed, uint64_t selected, void* state,
+                           uint64_t context, void* mirror, uint64_t mirror_rows, float* index_state);
 
 /* sdx_qsa_attention_rows over a state in host memory (sd_host_state), through the stage registered with sd_kv_stage: the union of
    the rows' selected 4-position blocks is copied into the stage once, in block order, and the selections are renumbered to it

@@ -41,6 +41,7 @@ _sig("orc_compress", [_p, _p, _u64, _u64, _u64, _p])
 _sig("orc_index_scores", [_p, _p, _i32, _p, _p, _u64, _u64, _u64, _u64, _f32, _p, _u64, _u64, _p])
 _sig("orc_index_block_tops", [_p, _p, _u64, _u64, _u64, _p])
 _sig("orc_qsa_index_select", [_p, _u64, _p, _u64, _u64, _p, _u64, _u64, _u64, _p])
+_sig("orc_qsa_normalize_rows", [_p, _u64, _u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _p, _p, _u64, _p])
 _sig("orc_top_k", [_p, _u64, _u64, _u64, _p])
 _sig("orc_to_bf16", [_p, _u64, _p])
 _sig("orc_threads", [], _i32)
@@ -222,6 +223,19 @@ def qsa_index_select(queries, blocks, base, steps, selected, row_floats, packed,
     assert packed.dtype == np.float32 and packed.flags.c_contiguous and packed.size == steps * (row_floats + selected + 1)
     _lib.orc_qsa_index_select(_ptr(queries), queries.shape[1], _ptr(blocks), blocks.shape[1], base, _ptr(positions), steps, selected, row_floats, _ptr(packed))
     return packed
+
+
+def qsa_normalize_rows(projections, heads, kv_heads, qnorm, knorm, iqnorm, pool_norm, positions, ropes, packed, state, context, index_state):
+    """projections [rows, stride] F32 (the index queries are normalised in place); packed (float32), state (uint8 Q8_0 planes) and
+    index_state ([128 * pool + 16 * 128] float32: pooled blocks, then the history ring) are written in place."""
+    assert projections.dtype == np.float32 and projections.flags.c_contiguous and packed.dtype == np.float32 and packed.flags.c_contiguous
+    assert state.dtype == np.uint8 and state.flags.c_contiguous and index_state.dtype == np.float32 and index_state.flags.c_contiguous
+    assert index_state.size == (context // 4 + 1 + 16) * 128 and state.size == context * 2 * kv_heads * ROW_Q8
+    rows, stride = projections.shape
+    norms = [np.ascontiguousarray(n, np.float32) for n in (qnorm, knorm, iqnorm, pool_norm)]
+    positions, ropes = np.ascontiguousarray(positions, np.uint32), np.ascontiguousarray(ropes, np.uint32)
+    _lib.orc_qsa_normalize_rows(_ptr(projections), stride, rows, heads, kv_heads, *[_ptr(n) for n in norms], _ptr(positions), _ptr(ropes),
+                                _ptr(packed), _ptr(state), context, _ptr(index_state))
 
 
 def top_k(scores, k):

@@ -576,6 +576,74 @@ void orc_qsa_index_select(const float* queries, uint64_t query_stride, const flo
     }
 }
 
+// gpu/sparse_attention.hpp:2-6 (qsa_rope): column c < 64 turns with its partner (c + 32) % 64 by position / 1e7^((c % 32) / 32);
+// columns from 64 on pass. (The kernel's own * cos + partner * sin is written out as the two products and their sum.)
+static float qsa_rope(float own, float partner, uint64_t column, uint64_t position) {
+    if (column >= 64) return own;
+    const float angle = float(position) / std::pow(1e7f, float(column % 32) / 32.0f);
+    return own * std::cos(angle) + (column < 32 ? -partner : partner) * std::sin(angle);
+}
+// The sum of width squares as the reference's shared-memory loop forms it: column c takes c + width / 2, then c + width / 4, ...
+static float qsa_halving_sum(float* sums, uint64_t width) {
+    for (uint64_t offset = width / 2; offset; offset /= 2)
+        for (uint64_t c = 0; c < offset; ++c) sums[c] += sums[c + offset];
+    return sums[0];
+}
+// gpu/sparse_attention.hpp:55-71 (qsa_normalize_block): one head of `width` columns, RMS-normalised, scaled by `norm`, rotated.
+static void qsa_normalize_head(const float* source, const float* norm, uint64_t width, uint64_t position, float* target) {
+    float values[256], sums[256];
+    for (uint64_t c = 0; c < width; ++c) { values[c] = source[c] * norm[c]; sums[c] = source[c] * source[c]; }
+    const float denominator = std::sqrt(qsa_halving_sum(sums, width) / float(width) + 1e-6f);
+    float result[256];
+    for (uint64_t c = 0; c < width; ++c) {
+        const float own = values[c] / denominator, partner = c < 64 ? values[(c + 32) % 64] / denominator : 0.0f;
+        result[c] = qsa_rope(own, partner, c, position);
+    }
+    std::memcpy(target, result, width * sizeof(float));   // (the index queries are normalised in place)
+}
+// gpu/qsa_decode.hpp:86-111 (qsa_normalize_rows) with :51-83 (qsa_pool_rows_block; for one row :5-23, qsa_pool_one): the rows'
+// queries and keys normalised and rotated into `packed` ([rows][heads][256] | [rows][kv_heads][256] | ...), the keys (normalised)
+// and values encoded into row positions[r] of the Q8_0 state, the four index-query heads normalised in place, the index keys passed
+// through the history ring (16 positions) and pooled four by four into blocks[column][position / 4]. index_state: [128][pool]
+// blocks, then the ring [16][128]. A projections row: qgate [heads][512] | key [kv][256] | value [kv][256] | index query [4][128] |
+// index key [128].
+void orc_qsa_normalize_rows(float* projections, uint64_t stride, uint64_t rows, uint64_t heads, uint64_t kv_heads, const float* qnorm,
+                            const float* knorm, const float* iqnorm, const float* pool_norm, const uint32_t* positions,
+                            const uint32_t* ropes, float* packed, uint8_t* state, uint64_t context, float* index_state) {
+    const uint64_t keys = heads * 512, values = keys + kv_heads * 256, index = keys + kv_heads * 512, pool = context / 4 + 1;
+    for (uint64_t row = 0; row < rows; ++row) {
+        float* own = projections + row * stride;
+        for (uint64_t head = 0; head < heads; ++head)
+            qsa_normalize_head(own + head * 512, qnorm, 256, ropes[row], packed + (row * heads + head) * 256);
+        for (uint64_t head = 0; head < kv_heads; ++head) {
+            float* normalized = packed + rows * heads * 256 + (row * kv_heads + head) * 256;
+            qsa_normalize_head(own + keys + head * 256, knorm, 256, ropes[row], normalized);
+            q8_encode_row(normalized, state + (head * context + positions[row]) * kRowQ8);
+            q8_encode_row(own + values + head * 256, state + ((kv_heads + head) * context + positions[row]) * kRowQ8);
+        }
+        for (uint64_t head = 0; head < 4; ++head)
+            qsa_normalize_head(own + index + head * 128, iqnorm, 128, ropes[row], own + index + head * 128);
+    }
+    float* history = index_state + pool * 128;
+    for (uint64_t row = 0; row < rows; ++row) {
+        const uint64_t pos = positions[row];
+        for (uint64_t c = 0; c < 128; ++c) history[(pos % 16) * 128 + c] = projections[row * stride + index + 512 + c];
+        if ((pos + 1) % 4) continue;
+        float vals[128], sums[128];
+        for (uint64_t c = 0; c < 128; ++c) {
+            float x = 0.0f;
+            for (uint64_t tap = 0; tap < 4; ++tap) x += history[((pos - 3 + tap) % 16) * 128 + c];
+            x /= 4.0f;
+            vals[c] = x * pool_norm[c]; sums[c] = x * x;
+        }
+        const float denominator = std::sqrt(qsa_halving_sum(sums, 128) / 128.0f + 1e-6f);
+        for (uint64_t c = 0; c < 128; ++c) {
+            const float value = vals[c] / denominator, partner = c < 64 ? vals[(c + 32) % 64] / denominator : 0.0f;
+            index_state[c * pool + pos / 4] = qsa_rope(value, partner, c, uint64_t(ropes[row]) - 3);
+        }
+    }
+}
+
 // gpu/dspark_attention.hpp:9-100 (dspark_attention_kernel) and crates/straydog-engine/tests/dspark_attention_gpu.rs:25-39 (its F64
 // oracle): every query row [slots][heads][512] attends the ring's history positions [anchor - history, anchor) (ring of 128 rows,
 // K = V) and all `slots` block keys; scale 1 / sqrt(512); the head's sink in the maximum and in the denominator.

@@ -265,6 +265,14 @@ class Backend:
         """sdx_qsa_index_select: Qwen's block scores and exact top-512 block choice, written into the packed rows (device pointers)."""
         self._c(self.lib.sdx_qsa_index_select(self.handle, queries, query_stride, blocks, pool, base, positions, steps, selected, heads, kv_heads, packed))
 
+    def qsa_normalize_rows(self, projections, stride, rows, heads, kv_heads, qnorm, knorm, iqnorm, pool_norm, positions, ropes, packed,
+                           selected, state, context, index_state, mirror=None, mirror_rows=0):
+        """sdx_qsa_normalize_rows: normalisation and rotation of the rows' queries, keys and index queries, their K/V rows written,
+        their index keys pooled (device pointers)."""
+        state = state.pointer if isinstance(state, Buffer) else state
+        self._c(self.lib.sdx_qsa_normalize_rows(self.handle, projections, stride, rows, heads, kv_heads, qnorm, knorm, iqnorm, pool_norm,
+                                                positions, ropes, packed, selected, state, context, mirror, mirror_rows, index_state))
+
     def decode_status(self):
         return self._c(self.lib.sdx_decode_status(self.handle))
 

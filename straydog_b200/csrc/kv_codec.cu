@@ -11,19 +11,6 @@
 
 namespace sdb {
 
-// kv_encode (gpu/kernels.cpp:58-69) for one 32-value block held by a warp, a value a lane: the block's scale is
-// FP16(max |v| / 127), a value is v / scale rounded to nearest even and clamped to +-127, 0 under a zero scale.
-__device__ __forceinline__ int8_t q8_encode(float value, __half& scale_h) {
-    float top = fabsf(value);
-    #pragma unroll
-    for (unsigned offset = 16; offset; offset /= 2) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, offset));
-    scale_h = __float2half_rn(__fdiv_rn(top, 127.0f));
-    const float scale = __half2float(scale_h);
-    int q = scale > 0.0f ? __float2int_rn(__fdiv_rn(value, scale)) : 0;
-    q = q > 127 ? 127 : q < -127 ? -127 : q;
-    return int8_t(q);
-}
-
 // One warp encodes one 32-value block: lane = column % 32. Grid-stride over blocks so that any
 // number of rows runs in one launch sized to the SM count.
 __global__ void __launch_bounds__(256) kv_write_kernel(uint8_t* __restrict__ state, size_t context, size_t kv_heads, size_t base,

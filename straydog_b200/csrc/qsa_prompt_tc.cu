@@ -78,7 +78,7 @@ __device__ __forceinline__ uint64_t desc_of(uint32_t low) {
     return d;
 }
 // Built with -DSDX_TRACE the MMA thread adds up the cycles it spends in each of its waits (eight 64-bit counters a CTA: total, wait
-// for a tile, for the weights, for a free score buffer, 0, tiles): the figures the profile summary of this kernel quotes.
+// for a tile, for the weights, for a free score buffer, the value thread's wait for a tile, tiles, the value thread's total, softmax thread 0's wait for the scores): the figures the profile summary of this kernel quotes.
 #if defined(SDX_TRACE)
 #define SDX_TRACE_ADD(slot, since) trace[slot] += clock64() - (since)
 #else
@@ -229,7 +229,13 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
         bool alive = true;
         for (uint32_t j = 0; j < tiles && alive; ++j) {
             const uint32_t slot = j & 1;
+#if defined(SDX_TRACE)
+            const long long since = clock64();
+#endif
             if (!wait(kSFull + slot, (j >> 1) & 1)) { alive = false; break; }
+#if defined(SDX_TRACE)
+            if (tid == 0) a.trace[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * 8 + 7] += clock64() - since;
+#endif
             tc_fence_after();
             float s[32];
             tmem_ld32(tmem + lane_base + 256 + slot * 64 + half * 32, s);

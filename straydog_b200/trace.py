@@ -42,7 +42,7 @@ def prompt(lib, context=16384, first=8192, rows=8192):
     per = lambda i: float((t[:, i] / t[:, 5]).mean())   # noqa: E731
     print(f"qsa_prompt_tc_kernel, {rows} rows after {first}: {min(times) * 1e3:.3f} ms a call (traced build), {len(t)} CTAs")
     print(f"  per 64-key tile: scores thread {per(0):.0f} cycles (waiting for a tile {per(1):.0f}, for a free score buffer {per(3):.0f}); "
-          f"values thread {per(6):.0f} (waiting for the weights {per(2):.0f}, for a tile {per(4):.0f})")
+          f"values thread {per(6):.0f} (waiting for the weights {per(2):.0f}, for a tile {per(4):.0f}); softmax thread 0 waiting for the scores {per(7):.0f}")
     gpu.close()
 
 

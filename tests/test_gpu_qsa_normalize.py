@@ -1,0 +1,193 @@
+"""sdx_qsa_normalize_rows (the fused front of Qwen's decode and verification attention: gpu/qsa_decode.hpp:86-111) against the
+oracle's restatement. The normalised and rotated values go through powf, cosf and sinf, whose device and host forms differ in
+the last place (and a last place of 1e7^(c/32) moves the angle by position * 6e-8), so they are compared within 2e-4 at positions
+below 4096; everything behind them is integer or codec work and is held bit for bit: the K rows are the codec's encoding of the
+keys the call itself wrote, the V rows and the history ring equal the oracle's. Then the call feeds the indexer and the attention
+as the reference's qsa_decode_attend_rows chains them (gpu/qsa_decode.hpp:113-129)."""
+import numpy as np
+import pytest
+
+import oracle
+from straydog_b200.backend import StraydogError
+
+pytestmark = pytest.mark.gpu
+SELECTED = 2052
+
+
+def case(seed, heads, kv_heads, context, positions, ropes=None, pad=0):
+    rng = np.random.default_rng(seed)
+    positions = np.asarray(positions, np.uint32)
+    rows, stride, pool = len(positions), heads * 512 + kv_heads * 512 + 640 + pad, context // 4 + 1
+    c = dict(heads=heads, kv_heads=kv_heads, context=context, rows=rows, stride=stride, pool=pool, positions=positions,
+             ropes=positions.copy() if ropes is None else np.asarray(ropes, np.uint32))
+    c["proj"] = rng.normal(0, 1, (rows, stride)).astype(np.float32)
+    c["norms"] = [rng.normal(1, 0.1, n).astype(np.float32) for n in (256, 256, 128, 128)]
+    c["packed"] = np.zeros(rows * (heads * 256 + kv_heads * 512 + SELECTED + 1), np.float32)
+    c["state"] = rng.integers(0, 256, context * 2 * kv_heads * 272, dtype=np.uint8)
+    index_state = np.zeros((pool + 16) * 128, np.float32)
+    index_state[pool * 128:] = rng.normal(0, 1, 16 * 128).astype(np.float32)
+    c["index_state"] = index_state
+    return c
+
+
+def run(gpu, c, mirror_rows=0):
+    bufs = dict(proj=gpu.upload(c["proj"]), packed=gpu.upload(c["packed"]), state=gpu.upload(c["state"]), index=gpu.upload(c["index_state"]),
+                positions=gpu.upload(c["positions"]), ropes=gpu.upload(c["ropes"]))
+    norms = [gpu.upload(n) for n in c["norms"]]
+    mirror = gpu.buffer(mirror_rows * 2 * c["kv_heads"] * 272) if mirror_rows else None
+    gpu.qsa_normalize_rows(bufs["proj"].pointer, c["stride"], c["rows"], c["heads"], c["kv_heads"], *[n.pointer for n in norms],
+                           bufs["positions"].pointer, bufs["ropes"].pointer, bufs["packed"].pointer, SELECTED, bufs["state"], c["context"],
+                           bufs["index"].pointer, mirror.pointer if mirror else None, mirror_rows)
+    got = dict(proj=gpu.read(bufs["proj"], np.float32, c["proj"].shape), packed=gpu.read(bufs["packed"], np.float32, c["packed"].shape),
+               state=gpu.read(bufs["state"], np.uint8, c["state"].shape), index=gpu.read(bufs["index"], np.float32, c["index_state"].shape))
+    if mirror:
+        got["mirror"] = gpu.read(mirror, np.uint8, (2 * c["kv_heads"], mirror_rows, 272))
+        gpu.release(mirror)
+    for b in norms:
+        gpu.release(b)
+    return got, bufs
+
+
+def reference(c):
+    want = dict(proj=c["proj"].copy(), packed=c["packed"].copy(), state=c["state"].copy(), index=c["index_state"].copy())
+    oracle.qsa_normalize_rows(want["proj"], c["heads"], c["kv_heads"], *c["norms"], c["positions"], c["ropes"], want["packed"], want["state"],
+                              c["context"], want["index"])
+    return want
+
+
+@pytest.mark.parametrize("heads,kv_heads,context,positions,pad", [
+    (24, 2, 4096, [2041, 2042, 2043, 2044, 2045, 2046, 2047, 2048], 0),    # the reference's layer, a full verification span
+    (12, 1, 512, [7], 0),                                                  # half a layer (one GPU of two), one decode token that completes a block
+    (16, 2, 1024, [0, 1, 2, 3, 4], 24),                                    # the benchmark's heads, the sequence's first rows, a padded stride
+    (16, 2, 4096, [3001], 0),
+])
+def test_rows_equal_the_oracles(gpu, heads, kv_heads, context, positions, pad):
+    c = case(1 + heads, heads, kv_heads, context, positions, pad=pad)
+    want = reference(c)
+    got, bufs = run(gpu, c)
+    assert gpu.decode_status() == 0
+    rows, pool = c["rows"], c["pool"]
+    live = rows * (heads + kv_heads) * 256
+    assert np.abs(got["packed"][:live] - want["packed"][:live]).max() < 2e-4
+    assert np.array_equal(got["packed"][live:], c["packed"][live:]), "values, lists and counts stay"
+    index_at = heads * 512 + kv_heads * 512
+    assert np.abs(got["proj"][:, index_at:index_at + 512] - want["proj"][:, index_at:index_at + 512]).max() < 2e-4
+    keep = np.ones(c["stride"], bool)
+    keep[index_at:index_at + 512] = False
+    for h in range(heads):
+        keep[h * 512:h * 512 + 256] = True   # (the queries themselves are not rewritten, only read)
+    assert np.array_equal(got["proj"][:, keep], c["proj"][:, keep])
+    # K/V rows: positions of the rows only; V rows and the ring bit for bit; K rows = the codec over the keys the call wrote
+    mine, theirs, before = (x.reshape(2 * kv_heads, context, 272) for x in (got["state"], want["state"], c["state"]))
+    untouched = np.ones(context, bool)
+    untouched[c["positions"]] = False
+    assert np.array_equal(mine[:, untouched], before[:, untouched])
+    keys = got["packed"][rows * heads * 256:live].reshape(rows, kv_heads, 256)
+    for r, p in enumerate(c["positions"]):
+        for h in range(kv_heads):
+            assert np.array_equal(mine[kv_heads + h, p], theirs[kv_heads + h, p])
+            assert np.array_equal(mine[h, p], oracle.q8_encode_rows(keys[r, h][None])[0])
+            assert np.abs(oracle.q8_decode_rows(mine[h, p][None]) - oracle.q8_decode_rows(theirs[h, p][None])).max() < 0.05
+    assert np.array_equal(got["index"][pool * 128:], want["index"][pool * 128:]), "the history ring"
+    assert np.abs(got["index"][:pool * 128] - want["index"][:pool * 128]).max() < 2e-4
+    done = [int(p) // 4 for p in c["positions"] if (int(p) + 1) % 4 == 0]
+    others = np.ones(pool, bool)
+    others[done] = False
+    assert not got["index"][:pool * 128].reshape(128, pool)[:, others].any(), "only completed blocks are written"
+    for b in bufs.values():
+        gpu.release(b)
+
+
+def test_rotation_positions_of_their_own_and_the_mirror(gpu):
+    # a sequence with an image before the rows: the rotations run ahead of the K/V positions; the mirror ring takes the same rows
+    c = case(5, 16, 2, 2048, [1030, 1031, 1032], ropes=[1100, 1101, 1102])
+    want = reference(c)
+    got, bufs = run(gpu, c, mirror_rows=64)
+    live = c["rows"] * 18 * 256
+    assert np.abs(got["packed"][:live] - want["packed"][:live]).max() < 2e-4
+    planes = got["state"].reshape(4, 2048, 272)
+    for p in c["positions"]:
+        assert np.array_equal(got["mirror"][:, p % 64], planes[:, p])
+    assert not got["mirror"][:, :6].any() and not got["mirror"][:, 9:].any()
+    assert np.abs(got["index"][:c["pool"] * 128] - want["index"][:c["pool"] * 128]).max() < 2e-4
+    for b in bufs.values():
+        gpu.release(b)
+
+
+def test_the_call_feeds_the_indexer_and_the_attention(gpu):
+    # qsa_decode_attend_rows' chain (gpu/qsa_decode.hpp:113-129) out of this library's entries: front, block choice, attention with
+    # the output gate; against the same chain through the oracle
+    heads, kv_heads, context = 16, 2, 4096
+    positions = np.arange(2300, 2306, dtype=np.uint32)
+    c = case(9, heads, kv_heads, context, positions)
+    rows, pool, row_floats = c["rows"], c["pool"], heads * 256 + kv_heads * 512
+    rng = np.random.default_rng(10)
+    from util import q8_state
+    c["state"] = q8_state(rng, context, kv_heads).view(np.uint8).ravel().copy()
+    c["index_state"][:pool * 128] = rng.normal(0, 1, pool * 128).astype(np.float32)   # the blocks pooled so far
+    got, bufs = run(gpu, c)
+    index_at = heads * 512 + kv_heads * 512
+    gpu.qsa_index_select(bufs["proj"].pointer + index_at * 4, c["stride"], bufs["index"].pointer, pool, 0, bufs["positions"].pointer, rows, SELECTED,
+                         heads, kv_heads, bufs["packed"].pointer)
+    out = gpu.buffer(rows * heads * 256 * 4)
+    gpu.qsa_attention_rows(bufs["state"], context, 0, bufs["positions"].pointer, rows, SELECTED, heads, kv_heads, 0.0625, bufs["packed"].pointer,
+                           out.pointer, gates=(bufs["proj"].pointer, c["stride"]))
+    mine = gpu.read(out, np.float32, (rows, heads, 256))
+    packed = gpu.read(bufs["packed"], np.float32, c["packed"].shape)
+    assert gpu.decode_status() == 0
+    # the oracle's chain over the GPU's own front (the rotation's last places would otherwise move a block choice at a tie)
+    state_np, proj_np = gpu.read(bufs["state"], np.uint8, c["state"].shape), gpu.read(bufs["proj"], np.float32, c["proj"].shape)
+    blocks_np = gpu.read(bufs["index"], np.float32, c["index_state"].shape)[:pool * 128].reshape(128, pool)
+    lists = oracle.qsa_index_select(proj_np[:, index_at:index_at + 512], blocks_np, 0, rows, SELECTED, row_floats, got["packed"].copy(),
+                                    positions=positions)
+    assert np.array_equal(packed, lists)
+    start = rows * row_floats
+    counts = packed[start + rows * SELECTED:]
+    want = np.zeros((rows, heads, 256))
+    planes = oracle.q8_decode_rows(state_np.reshape(-1, 272)).reshape(2 * kv_heads, context, 256).astype(np.float64)
+    for r in range(rows):
+        chosen = packed[start + r * SELECTED:start + r * SELECTED + int(counts[r])].astype(np.int64)
+        assert chosen.max() == positions[r], "a row sees its own position, written by the front"
+        for h in range(heads):
+            kv = h // (heads // kv_heads)
+            scores = planes[kv, chosen] @ packed[(r * heads + h) * 256:(r * heads + h + 1) * 256].astype(np.float64) * 0.0625
+            w = np.exp(scores - scores.max())
+            gate = proj_np[r, h * 512 + 256:h * 512 + 512].astype(np.float64)
+            want[r, h] = (w / w.sum()) @ planes[kv_heads + kv, chosen] / (1 + np.exp(-gate))
+    assert np.abs(mine - want).max() < 1e-4
+    for b in list(bufs.values()) + [out]:
+        gpu.release(b)
+
+
+def test_a_position_past_the_state_writes_nothing_and_is_reported(gpu):
+    c = case(3, 16, 2, 256, [100, 300])
+    got, bufs = run(gpu, c)
+    assert gpu.decode_status() == 5
+    mine, before = got["state"].reshape(4, 256, 272), c["state"].reshape(4, 256, 272)
+    untouched = np.ones(256, bool)
+    untouched[100] = False
+    assert np.array_equal(mine[:, untouched], before[:, untouched]) and not np.array_equal(mine[:, 100], before[:, 100])
+    assert gpu.decode_status() == 0
+    for b in bufs.values():
+        gpu.release(b)
+
+
+def test_invalid_front_shapes_are_refused(gpu):
+    c = case(4, 16, 2, 256, [10, 11])
+    bufs = dict(proj=gpu.upload(c["proj"]), packed=gpu.upload(c["packed"]), state=gpu.upload(c["state"]), index=gpu.upload(c["index_state"]),
+                positions=gpu.upload(c["positions"]), ropes=gpu.upload(c["ropes"]))
+    norms = [gpu.upload(n) for n in c["norms"]]
+
+    def call(stride=c["stride"], rows=2, heads=16, kv_heads=2, context=256, mirror_rows=0, state=None):
+        gpu.qsa_normalize_rows(bufs["proj"].pointer, stride, rows, heads, kv_heads, *[n.pointer for n in norms], bufs["positions"].pointer,
+                               bufs["ropes"].pointer, bufs["packed"].pointer, SELECTED, state or bufs["state"], context, bufs["index"].pointer, None, mirror_rows)
+    for kwargs in (dict(stride=c["stride"] - 1), dict(rows=0), dict(rows=257), dict(heads=0), dict(kv_heads=0), dict(context=0), dict(mirror_rows=8)):
+        with pytest.raises(StraydogError, match="invalid Straydog attention dimensions"):
+            call(**kwargs)
+    for kwargs in (dict(context=260), dict(rows=3), dict(state=bufs["packed"].pointer + 4)):   # a state, rows or an index state the buffers do not hold
+        with pytest.raises(StraydogError, match="outside|allocation|range"):
+            call(**kwargs)
+    call()
+    assert gpu.decode_status() == 0
+    for b in list(bufs.values()) + norms:
+        gpu.release(b)
