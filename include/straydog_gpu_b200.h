@@ -276,6 +276,20 @@ int sdx_qsa_normalize_rows(void* handle, float* projections, uint64_t stride, ui
                            const uint32_t* positions, const uint32_t* ropes, float* packed, uint64_t selected, void* state,
                            uint64_t context, void* mirror, uint64_t mirror_rows, float* index_state);
 
+/* The same front for a prompt chunk: `count` consecutive tokens from `position` (a token turns at its own position), as the
+   reference's prefill runs it in seven launches (gpu/prefill_batch.hpp:342-370, gpu/sparse_attention.hpp:493-506: qsa_normalize of the
+   queries, keys and index queries, the values' copy, qsa_pool :87-106, qsa_save_history :135-139, write_attention_kv), here in two.
+   The projections come in five arrays: qgate [count][heads][512] (query 256 | gate 256 a head), key and value_rows
+   [count][kv_heads][256], iq [count][4][128] (normalised and rotated in place), ik [count][128]. Queries, keys and values go into
+   `packed` (all three: the layout sd_attention_sequence and sdx_qsa_attention_rows read, for `count` rows), keys and values into rows
+   position .. position + count - 1 of the Q8_0 state (and the mirror ring), every 4-position block the chunk completes is pooled into
+   index_state (positions before the chunk from the ring), and the chunk's last four index keys enter the ring. The same bits as
+   sdx_qsa_normalize_rows over the same tokens. */
+int sdx_qsa_normalize_chunk(void* handle, const float* qgate, const float* key, const float* value_rows, float* iq, const float* ik,
+                            uint64_t count, uint64_t position, uint64_t heads, uint64_t kv_heads, const float* qnorm,
+                            const float* knorm, const float* iqnorm, const float* pool_norm, float* packed, uint64_t selected,
+                            void* state, uint64_t context, void* mirror, uint64_t mirror_rows, float* index_state);
+
 /* sdx_qsa_attention_rows over a state in host memory (sd_host_state), through the stage registered with sd_kv_stage: the union of
    the rows' selected 4-position blocks is copied into the stage once, in block order, and the selections are renumbered to it
    (the reference's qsa_attention_gathered, gpu/prefill_batch.hpp:227-252 over gpu/sparse_attention_compute.hpp:680-734), as many

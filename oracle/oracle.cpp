@@ -644,6 +644,51 @@ void orc_qsa_normalize_rows(float* projections, uint64_t stride, uint64_t rows, 
     }
 }
 
+// A prompt chunk's front (gpu/prefill_batch.hpp:342-370 and gpu/sparse_attention.hpp:493-506: qsa_normalize of the queries, keys and
+// index queries, the values copied into the packed rows, qsa_pool :87-106 over the blocks the chunk completes, qsa_save_history
+// :135-139, write_attention_kv): `count` tokens from `position`, a token's rotation position its own. The arrays: qgate
+// [count][heads][512], key and value [count][kv_heads][256], iq [count][4][128] (normalised in place), ik [count][128].
+void orc_qsa_normalize_chunk(const float* qgate, const float* key, const float* value, float* iq, const float* ik, uint64_t count,
+                             uint64_t position, uint64_t heads, uint64_t kv_heads, const float* qnorm, const float* knorm,
+                             const float* iqnorm, const float* pool_norm, float* packed, uint8_t* state, uint64_t context,
+                             float* index_state) {
+    const uint64_t pool = context / 4 + 1, Q = heads * 256, K = kv_heads * 256;
+    for (uint64_t t = 0; t < count; ++t) {
+        for (uint64_t head = 0; head < heads; ++head)
+            qsa_normalize_head(qgate + (t * heads + head) * 512, qnorm, 256, position + t, packed + t * Q + head * 256);
+        for (uint64_t head = 0; head < kv_heads; ++head) {
+            float* normalized = packed + count * Q + t * K + head * 256;
+            qsa_normalize_head(key + t * K + head * 256, knorm, 256, position + t, normalized);
+            std::memcpy(packed + count * (Q + K) + t * K + head * 256, value + t * K + head * 256, 256 * sizeof(float));
+            q8_encode_row(normalized, state + (head * context + position + t) * kRowQ8);
+            q8_encode_row(value + t * K + head * 256, state + ((kv_heads + head) * context + position + t) * kRowQ8);
+        }
+        for (uint64_t head = 0; head < 4; ++head)
+            qsa_normalize_head(iq + t * 512 + head * 128, iqnorm, 128, position + t, iq + t * 512 + head * 128);
+    }
+    float* history = index_state + pool * 128;
+    for (uint64_t block = position / 4; block < (position + count) / 4; ++block) {
+        const uint64_t begin = block * 4;
+        float vals[128], sums[128];
+        for (uint64_t c = 0; c < 128; ++c) {
+            float x = 0.0f;
+            for (uint64_t tap = 0; tap < 4; ++tap) {
+                const uint64_t pos = begin + tap;
+                x += pos < position ? history[(pos % 16) * 128 + c] : ik[(pos - position) * 128 + c];
+            }
+            x /= 4.0f;
+            vals[c] = x * pool_norm[c]; sums[c] = x * x;
+        }
+        const float denominator = std::sqrt(qsa_halving_sum(sums, 128) / 128.0f + 1e-6f);
+        for (uint64_t c = 0; c < 128; ++c) {
+            const float own = vals[c] / denominator, partner = c < 64 ? vals[(c + 32) % 64] / denominator : 0.0f;
+            index_state[c * pool + block] = qsa_rope(own, partner, c, begin);
+        }
+    }
+    const uint64_t kept = count < 4 ? count : 4;
+    for (uint64_t t = count - kept; t < count; ++t) std::memcpy(history + ((position + t) % 16) * 128, ik + t * 128, 128 * sizeof(float));
+}
+
 // gpu/dspark_attention.hpp:9-100 (dspark_attention_kernel) and crates/straydog-engine/tests/dspark_attention_gpu.rs:25-39 (its F64
 // oracle): every query row [slots][heads][512] attends the ring's history positions [anchor - history, anchor) (ring of 128 rows,
 // K = V) and all `slots` block keys; scale 1 / sqrt(512); the head's sink in the maximum and in the denominator.

@@ -273,6 +273,13 @@ class Backend:
         self._c(self.lib.sdx_qsa_normalize_rows(self.handle, projections, stride, rows, heads, kv_heads, qnorm, knorm, iqnorm, pool_norm,
                                                 positions, ropes, packed, selected, state, context, mirror, mirror_rows, index_state))
 
+    def qsa_normalize_chunk(self, qgate, key, value, iq, ik, count, position, heads, kv_heads, qnorm, knorm, iqnorm, pool_norm, packed, selected,
+                            state, context, index_state, mirror=None, mirror_rows=0):
+        """sdx_qsa_normalize_chunk: the same front for a prompt chunk of `count` tokens from `position` (device pointers)."""
+        state = state.pointer if isinstance(state, Buffer) else state
+        self._c(self.lib.sdx_qsa_normalize_chunk(self.handle, qgate, key, value, iq, ik, count, position, heads, kv_heads, qnorm, knorm, iqnorm,
+                                                 pool_norm, packed, selected, state, context, mirror, mirror_rows, index_state))
+
     def decode_status(self):
         return self._c(self.lib.sdx_decode_status(self.handle))
 

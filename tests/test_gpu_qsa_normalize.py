@@ -191,3 +191,83 @@ def test_invalid_front_shapes_are_refused(gpu):
     assert gpu.decode_status() == 0
     for b in list(bufs.values()) + norms:
         gpu.release(b)
+
+
+# ---- sdx_qsa_normalize_chunk: the same front for a prompt chunk (gpu/prefill_batch.hpp:342-370, gpu/sparse_attention.hpp:87-106, 135-139) ----
+def chunk_case(seed, heads, kv_heads, context, position, count):
+    rng = np.random.default_rng(seed)
+    c = dict(heads=heads, kv_heads=kv_heads, context=context, position=position, count=count, pool=context // 4 + 1)
+    c["qgate"] = rng.normal(0, 1, (count, heads, 512)).astype(np.float32)
+    c["key"], c["value"] = (rng.normal(0, 1, (count, kv_heads, 256)).astype(np.float32) for _ in range(2))
+    c["iq"], c["ik"] = rng.normal(0, 1, (count, 4, 128)).astype(np.float32), rng.normal(0, 1, (count, 128)).astype(np.float32)
+    c["norms"] = [rng.normal(1, 0.1, n).astype(np.float32) for n in (256, 256, 128, 128)]
+    c["packed"] = np.zeros(count * (heads * 256 + kv_heads * 512 + SELECTED + 1), np.float32)
+    c["state"] = rng.integers(0, 256, context * 2 * kv_heads * 272, dtype=np.uint8)
+    c["index_state"] = np.zeros((c["pool"] + 16) * 128, np.float32)
+    c["index_state"][c["pool"] * 128:] = rng.normal(0, 1, 16 * 128).astype(np.float32)
+    return c
+
+
+def run_chunk(gpu, c):
+    names = ("qgate", "key", "value", "iq", "ik", "packed", "state", "index_state")
+    bufs = {n: gpu.upload(c[n]) for n in names}
+    norms = [gpu.upload(n) for n in c["norms"]]
+    try:
+        gpu.qsa_normalize_chunk(bufs["qgate"].pointer, bufs["key"].pointer, bufs["value"].pointer, bufs["iq"].pointer, bufs["ik"].pointer, c["count"],
+                                c["position"], c["heads"], c["kv_heads"], *[n.pointer for n in norms], bufs["packed"].pointer, SELECTED, bufs["state"],
+                                c["context"], bufs["index_state"].pointer)
+        return {n: gpu.read(bufs[n], c[n].dtype, c[n].shape) for n in ("iq", "packed", "state", "index_state")}
+    finally:
+        for b in list(bufs.values()) + norms:
+            gpu.release(b)
+
+
+@pytest.mark.parametrize("heads,kv_heads,context,position,count", [(24, 2, 4096, 0, 300), (16, 2, 2048, 1021, 70), (12, 1, 512, 7, 1), (16, 2, 512, 6, 1),
+                                                                   (16, 2, 1024, 509, 16)])
+def test_a_chunks_front_equals_the_oracles_and_its_tokens_taken_as_rows(gpu, heads, kv_heads, context, position, count):
+    c = chunk_case(position + count, heads, kv_heads, context, position, count)
+    got = run_chunk(gpu, c)
+    assert gpu.decode_status() == 0
+    want = {n: c[n].copy() for n in ("iq", "packed", "state", "index_state")}
+    oracle.qsa_normalize_chunk(c["qgate"], c["key"], c["value"], want["iq"], c["ik"], position, heads, kv_heads, *c["norms"], want["packed"],
+                               want["state"], context, want["index_state"])
+    live, pool = count * (heads + kv_heads) * 256, c["pool"]
+    assert np.abs(got["packed"][:live] - want["packed"][:live]).max() < 2e-4
+    assert np.array_equal(got["packed"][live:], want["packed"][live:]), "the values' copy; lists and counts stay"
+    assert np.abs(got["iq"] - want["iq"]).max() < 2e-4
+    assert np.abs(got["index_state"][:pool * 128] - want["index_state"][:pool * 128]).max() < 2e-4
+    assert np.array_equal(got["index_state"][pool * 128:], want["index_state"][pool * 128:]), "the history ring"
+    mine, theirs, before = (x.reshape(2 * kv_heads, context, 272) for x in (got["state"], want["state"], c["state"]))
+    assert np.array_equal(mine[kv_heads:], theirs[kv_heads:]), "value rows"
+    assert np.array_equal(mine[:, :position], before[:, :position]) and np.array_equal(mine[:, position + count:], before[:, position + count:])
+    keys = got["packed"][count * heads * 256:live].reshape(count, kv_heads, 256)
+    for h in range(kv_heads):
+        assert np.array_equal(mine[h, position:position + count], oracle.q8_encode_rows(keys[:, h]))
+    # the same tokens as decode rows (<= 256 a call): the same bits everywhere both forms write
+    if count <= 256:
+        proj = np.ascontiguousarray(np.concatenate([c["qgate"].reshape(count, -1), c["key"].reshape(count, -1), c["value"].reshape(count, -1),
+                                                    c["iq"].reshape(count, -1), c["ik"]], axis=1))
+        positions = np.arange(position, position + count, dtype=np.uint32)
+        r = dict(heads=heads, kv_heads=kv_heads, context=context, rows=count, stride=proj.shape[1], pool=pool, positions=positions, ropes=positions,
+                 proj=proj, norms=c["norms"], packed=c["packed"], state=c["state"], index_state=c["index_state"])
+        rows, bufs = run(gpu, r)
+        for b in bufs.values():
+            gpu.release(b)
+        assert np.array_equal(rows["packed"][:live].view(np.uint32), got["packed"][:live].view(np.uint32))
+        assert np.array_equal(rows["state"], got["state"])
+        index_at = heads * 512 + kv_heads * 512
+        assert np.array_equal(rows["proj"][:, index_at:index_at + 512].view(np.uint32), got["iq"].reshape(count, 512).view(np.uint32))
+        assert np.array_equal(rows["index"][:pool * 128].view(np.uint32), got["index_state"][:pool * 128].view(np.uint32))
+
+
+def test_invalid_chunk_shapes_are_refused(gpu):
+    c = chunk_case(2, 16, 2, 256, 100, 8)
+    for kwargs in (dict(count=0), dict(position=250), dict(heads=0), dict(context=0)):
+        d = dict(c)
+        d.update(kwargs)
+        with pytest.raises(StraydogError, match="invalid Straydog attention dimensions"):
+            run_chunk(gpu, d)
+    d = dict(c)
+    d["count"] = 9   # more tokens than the arrays hold
+    with pytest.raises(StraydogError, match="outside"):
+        run_chunk(gpu, d)

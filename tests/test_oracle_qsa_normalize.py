@@ -2,6 +2,7 @@
 independent numpy statement of the same rule in float64. Parity unpinned: the reference's library reaches this kernel only inside
 sd_qsa_sequence, which needs a layer's weights."""
 import numpy as np
+import pytest
 
 import oracle
 
@@ -88,3 +89,54 @@ def test_one_row_is_the_decode_steps_front():
     oracle.qsa_normalize_rows(proj, heads, kv_heads, *norms, [5], [5], packed, state, context, index_state)
     assert np.abs(packed[:256] - want).max() < 2e-5
     assert not index_state[:(context // 4 + 1) * 128].any()   # position 5 completes no block
+
+
+def chunk_case(seed, heads, kv_heads, context, position, count):
+    rng = np.random.default_rng(seed)
+    c = dict(heads=heads, kv_heads=kv_heads, context=context, position=position, count=count, pool=context // 4 + 1)
+    c["qgate"] = rng.normal(0, 1, (count, heads, 512)).astype(np.float32)
+    c["key"], c["value"] = (rng.normal(0, 1, (count, kv_heads, 256)).astype(np.float32) for _ in range(2))
+    c["iq"], c["ik"] = rng.normal(0, 1, (count, 4, 128)).astype(np.float32), rng.normal(0, 1, (count, 128)).astype(np.float32)
+    c["norms"] = [rng.normal(1, 0.1, n).astype(np.float32) for n in (256, 256, 128, 128)]
+    c["packed"] = np.zeros(count * (heads * 256 + kv_heads * 512 + 2052 + 1), np.float32)
+    c["state"] = np.zeros(context * 2 * kv_heads * 272, np.uint8)
+    c["index_state"] = np.zeros((c["pool"] + 16) * 128, np.float32)
+    c["index_state"][c["pool"] * 128:] = rng.normal(0, 1, 16 * 128).astype(np.float32)
+    return c
+
+
+def as_rows(c):
+    """The chunk's tokens as decode rows: one projections row a token, positions and rotation positions position + t."""
+    heads, kv_heads, count = c["heads"], c["kv_heads"], c["count"]
+    proj = np.concatenate([c["qgate"].reshape(count, -1), c["key"].reshape(count, -1), c["value"].reshape(count, -1),
+                           c["iq"].reshape(count, -1), c["ik"]], axis=1).astype(np.float32)
+    assert proj.shape[1] == heads * 512 + kv_heads * 512 + 640
+    return np.ascontiguousarray(proj), np.arange(c["position"], c["position"] + count, dtype=np.uint32)
+
+
+@pytest.mark.parametrize("position,count", [(0, 9), (6, 1), (7, 1), (10, 14), (13, 30), (21, 3)])
+def test_a_prompt_chunks_front_equals_its_tokens_taken_as_rows(position, count):
+    # qsa_pool takes a block's positions before the chunk from the ring and the rest from the chunk (gpu/sparse_attention.hpp:87-106);
+    # the rows' form passes every token through the ring (gpu/qsa_decode.hpp:51-83): the same numbers, so the same bits
+    c = chunk_case(position * 100 + count, 4, 2, 64, position, count)
+    iq = c["iq"].copy()
+    packed, state, index_state = c["packed"].copy(), c["state"].copy(), c["index_state"].copy()
+    oracle.qsa_normalize_chunk(c["qgate"], c["key"], c["value"], iq, c["ik"], position, 4, 2, *c["norms"], packed, state, 64, index_state)
+    proj, positions = as_rows(c)
+    packed_r, state_r, index_r = c["packed"].copy(), c["state"].copy(), c["index_state"].copy()
+    oracle.qsa_normalize_rows(proj, 4, 2, *c["norms"], positions, positions, packed_r, state_r, 64, index_r)
+    live = count * (4 + 2) * 256
+    assert np.array_equal(packed[:live].view(np.uint32), packed_r[:live].view(np.uint32))
+    assert np.array_equal(packed[live:live + count * 512].reshape(count, 2, 256), c["value"]), "a chunk's values are copied into the packed rows"
+    assert not packed_r[live:].any() and not packed[live + count * 512:].any()
+    assert np.array_equal(state, state_r)
+    assert np.array_equal(iq.reshape(count, 512).view(np.uint32), proj[:, 4 * 512 + 2 * 512:4 * 512 + 2 * 512 + 512].view(np.uint32))
+    pool = c["pool"]
+    assert np.array_equal(index_state[:pool * 128].view(np.uint32), index_r[:pool * 128].view(np.uint32)), "the pooled blocks"
+    # the ring: a chunk saves its last four tokens, the rows every token; the slots both wrote agree and hold the index keys
+    ring, ring_r = index_state[pool * 128:].reshape(16, 128), index_r[pool * 128:].reshape(16, 128)
+    for t in range(max(0, count - 4), count):
+        assert np.array_equal(ring[(position + t) % 16], c["ik"][t]) and np.array_equal(ring_r[(position + t) % 16], c["ik"][t])
+    done = list(range(position // 4, (position + count) // 4))
+    blocks = index_state[:pool * 128].reshape(128, pool)
+    assert all(blocks[:, b].any() for b in done) and not np.delete(blocks, done, axis=1).any()
