@@ -381,8 +381,9 @@ def run_index_ops(args, local, gpu):
 # ---- the Qwen seam: the indexer's block choice, then selection-list attention over the lists it wrote (a verification's rows) ----
 def run_qsa_rows(args, local, gpu):
     """sdx_qsa_index_select (8 rows at positions near 32 768: 8192 blocks scored, 512 chosen, 2048 + tail positions listed) followed by
-    sdx_qsa_attention_rows over those lists (16 query / 2 K/V heads, Q8_0 state of 32 768 positions): each timed with device events,
-    the attention checked against the oracle's scalar selection attention over the oracle's lists."""
+    sdx_qsa_attention_rows over those lists (16 query / 2 K/V heads, Q8_0 state of 32 768 positions), and the fused front of 8 rows
+    (sdx_qsa_normalize_rows): each timed with device events, the attention checked against the oracle's scalar selection attention over
+    the oracle's lists, the front against the oracle's restatement."""
     from straydog_b200.backend import Backend
     from straydog_b200 import synthetic
     import oracle
@@ -417,10 +418,38 @@ def run_qsa_rows(args, local, gpu):
         raise SystemExit(f"qsa rows: lists or outputs differ from the oracle (max abs error {error})")
     listed = int(sum(want_lists[steps * c["row_floats"] + steps * selected + r] for r in range(steps)))
     nbytes = listed * 2 * KV_HEADS * ROW
-    for b in (q, blocks, packed, state, out):
+    # the fused front of the same 8 rows (sdx_qsa_normalize_rows: norm, rotation, Q8_0 K/V write, index-key pooling), behind the checks
+    # above because it writes the state; its rows sit at positions 2040..2047, where the host's and the device's powf / cosf / sinf
+    # agree to 2e-4 (a last place of 1e7^(c/32) moves the angle by position * 6e-8)
+    stride, pool = HEADS * 512 + KV_HEADS * 512 + 640, context // 4 + 1
+    positions = np.arange(2040, 2040 + steps, dtype=np.uint32)
+    proj_np = rng.normal(0, 1, (steps, stride)).astype(np.float32)
+    norms_np = [rng.normal(1, 0.1, n).astype(np.float32) for n in (256, 256, 128, 128)]
+    index_np = np.zeros((pool + 16) * 128, np.float32)
+    proj, index_state, pos = gpu.upload(proj_np), gpu.upload(index_np), gpu.upload(positions)
+    norms = [gpu.upload(n) for n in norms_np]
+    front = lambda: gpu.qsa_normalize_rows(proj.pointer, stride, steps, HEADS, KV_HEADS, *[n.pointer for n in norms], pos.pointer, pos.pointer,
+                                           packed.pointer, selected, state, context, index_state.pointer)
+    front()
+    front_packed = gpu.read(packed, np.float32, c["packed"].shape)[:steps * (HEADS + KV_HEADS) * DIM]
+    start, stop = gpu.event(), gpu.event()
+    for _ in range(5):
+        front()
+    gpu.record(start)
+    for _ in range(200):
+        front()
+    gpu.record(stop)
+    gpu.synchronize()
+    times["normalize_rows_ms"] = Backend.elapsed_ms(start, stop) / 200
+    want_packed, want_state = c["packed"].copy(), state_np.view(np.uint8).ravel().copy()
+    oracle.qsa_normalize_rows(proj_np.copy(), HEADS, KV_HEADS, *norms_np, positions, positions, want_packed, want_state, context, index_np.copy())
+    front_error = float(np.abs(front_packed - want_packed[:front_packed.size]).max())
+    if front_error > 2e-4 or gpu.decode_status() != 0:
+        raise SystemExit(f"qsa rows: the fused front differs from the oracle (max abs error {front_error})")
+    for b in (q, blocks, packed, state, out, proj, index_state, pos, *norms):
         gpu.release(b)
     return {"workload": "Qwen's indexer (8 rows, 8192 blocks, 512 chosen) and selection-list attention of the 8 rows over the lists it wrote (32768-position Q8_0 state)",
-            **times, "lists_equal_oracle": True, "max_abs_error_vs_oracle": error,
+            **times, "lists_equal_oracle": True, "max_abs_error_vs_oracle": error, "normalize_rows_max_abs_error_vs_oracle": front_error,
             "attention_rows_roofline": {"bound": "hbm", "achieved": nbytes / times["attention_rows_ms"] / 1e6, "peak": peak_hbm, "unit": "GB/s",
                                         "frac": nbytes / times["attention_rows_ms"] / 1e6 / peak_hbm,
                                         "note": f"algorithmic bytes = {listed} listed positions x 2 K/V heads x (K row + V row) x 272 B; a call of 8 rows is "
