@@ -49,7 +49,9 @@ int sd_buffer_write(void* handle, void* buffer, uint64_t offset, const void* dat
 int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* output, uint64_t bytes);
 
 /* ---- K/V format and staging ---- */
-/* gpu/straydog_gpu.h:113. row: 272 (Q8_0) or 512 (FP16). The attention kernels of this build read Q8_0 rows. */
+/* gpu/straydog_gpu.h:113. row: 272 (Q8_0) or 512 (FP16: a value's nearest FP16). FP16 rows are written (sdx_kv_write, the fused
+   fronts), decoded, grown and attended by sd_attention_sequence; the tensor-core kernels (sdx_qsa_decode*, sdx_attention_batch,
+   sdx_qsa_attention_rows, sdx_qsa_attention_gathered, sdx_qsa_prompt) read Q8_0 rows only and refuse a handle set to FP16 rows. */
 int sd_kv_format(void* handle, uint32_t row);
 /* gpu/straydog_gpu.h:114. The VRAM stage of host-resident K/V: an allocation of rows * 4096 bytes. With K/V resident in HBM the
    stage is registered and validated but never needed; sdx_qsa_attention_gathered copies a host-resident state's selected blocks
@@ -61,6 +63,17 @@ int sd_kv_stage(void* handle, void* pointer, uint64_t rows);
 void* sd_host_state(void* handle, uint64_t bytes);
 /* gpu/straydog_gpu.h:112. 1 when the device reads mapped host memory. */
 int sd_host_state_supported(void* handle);
+/* The data movement of sd_kv_grow (gpu/straydog_gpu.h:109, gpu/kernels.cpp:4048-4203): a sequence's K/V state of `from` positions and
+   its indexer state grown to `to` positions (from < to <= 262144; valid <= from positions written). The reference's entry looks the
+   two up in its decoder-layer registry and rewires the registry afterwards; the registry is the engine's, so here the caller passes
+   the two pointers and gets the new ones back in their place. *state: 2 * kv_heads planes of `from` rows, an allocation of exactly
+   that size in VRAM, or a host-resident state (sd_host_state). In VRAM the new state is a new zeroed allocation with every plane's
+   `from` positions copied on the device, and the old one is released; a host-resident state is grown in host memory and its `valid`
+   positions copied by the CPU. *index_state: [128][from / 4 + 1] pooled blocks + the 16 x 128 ring; the blocks take the pitch
+   to / 4 + 1 (the first min(from / 4 + 1, valid / 4 + 1) of every column, the rest zeros), the ring follows; it is replaced by a
+   new allocation only when the old one is too small (then the old one is released). A growth the budget refuses leaves both states
+   as they were. Returns after the copies are complete. */
+int sdx_kv_grow(void* handle, uint64_t kv_heads, uint64_t from, uint64_t to, uint64_t valid, void** state, void** index_state);
 
 /* ---- Qwen3.8-style grouped-query attention over Q8_0 K/V ---- */
 /* gpu/straydog_gpu.h:528. Host pointers. The reference's own shapes: 24 query / 2 K/V heads of 256,

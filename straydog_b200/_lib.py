@@ -46,6 +46,7 @@ SIGNATURES = {
     "sd_host_state_supported": ([p], i32),
     "sdx_qsa_attention_gathered": ([p, p, u64, u64, p, u64, u64, u64, u64, f32, p, p, u64, p, p], i32),
     "sdx_qsa_index_select": ([p, p, u64, p, u64, u64, p, u64, u64, u64, u64, p], i32),
+    "sdx_kv_grow": ([p, u64, u64, u64, u64, p, p], i32),
     "sdx_qsa_normalize_rows": ([p, p, u64, u64, u64, u64, p, p, p, p, p, p, p, u64, p, u64, p, u64, p], i32),
     "sdx_qsa_normalize_chunk": ([p, p, p, p, p, p, u64, u64, u64, u64, p, p, p, p, p, u64, p, u64, p, u64, p], i32),
     "sd_op_rope": ([p, p, u64, u64, u64, u64, p, p, i32], i32),

@@ -280,6 +280,18 @@ class Backend:
         self._c(self.lib.sdx_qsa_normalize_chunk(self.handle, qgate, key, value, iq, ik, count, position, heads, kv_heads, qnorm, knorm, iqnorm,
                                                  pool_norm, packed, selected, state, context, mirror, mirror_rows, index_state))
 
+    def kv_grow(self, kv_heads, from_context, to_context, valid, state, index_state, row=272):
+        """sdx_kv_grow: the state and the index state (Buffers) grown to `to_context` positions; returns the two new Buffers. The library
+        has released the old state (and the old index state unless it was large enough: then the same Buffer comes back)."""
+        s, i = C.c_void_p(state.pointer), C.c_void_p(index_state.pointer)
+        self._c(self.lib.sdx_kv_grow(self.handle, kv_heads, from_context, to_context, valid, C.byref(s), C.byref(i)))
+        grown = Buffer(self, s.value, to_context * 2 * kv_heads * row)
+        index = index_state
+        if i.value != index_state.pointer:
+            index, index_state.pointer = Buffer(self, i.value, ((to_context // 4 + 1) * 128 + 2048) * 4), None
+        state.pointer = None
+        return grown, index
+
     def decode_status(self):
         return self._c(self.lib.sdx_decode_status(self.handle))
 

@@ -304,8 +304,8 @@ int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* outp
     } catch (const std::exception& e) { last_error = e.what(); return -1; }
 }
 
-// gpu/kernels.cpp:4266-4275: 512 (FP16 rows) or 272 (Q8_0 rows). This library's attention kernels
-// read Q8_0 rows only; FP16 rows are accepted as a format and refused by the kernels that cannot read them.
+// gpu/kernels.cpp:4266-4275: 512 (FP16 rows) or 272 (Q8_0 rows). The codec, the fused fronts and the FP32 check path
+// (sd_attention_sequence) handle both; the tensor-core kernels stream Q8_0 rows only and refuse FP16 rows at the call.
 int sd_kv_format(void* handle, uint32_t row) {
     try {
         auto& value = device(handle);

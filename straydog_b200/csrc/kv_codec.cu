@@ -4,7 +4,8 @@
 // crates/straydog-engine/src/gpu.rs:536-561.
 //
 // Row layout (gpu/core.hpp:398-403): 256 int8 values, then the 8 FP16 scales of their 32-value
-// blocks, 272 bytes. State layout: 2 * kv_heads planes of `context` rows, keys of head 0.., then
+// blocks, 272 bytes; or, under sd_kv_format(512), 256 FP16 values (the nearest FP16 of each value,
+// gpu/kernels.cpp:42, 70). State layout: 2 * kv_heads planes of `context` rows, keys of head 0.., then
 // values of head 0...
 #include "common.cuh"
 #include "../../include/straydog_gpu_b200.h"
@@ -13,9 +14,11 @@ namespace sdb {
 
 // One warp encodes one 32-value block: lane = column % 32. Grid-stride over blocks so that any
 // number of rows runs in one launch sized to the SM count.
+template<bool F16>
 __global__ void __launch_bounds__(256) kv_write_kernel(uint8_t* __restrict__ state, size_t context, size_t kv_heads, size_t base,
                                                         const uint32_t* __restrict__ position, size_t steps,
                                                         const float* __restrict__ keys, const float* __restrict__ values) {
+    constexpr size_t kRow = F16 ? kv_row_f16 : kv_row_q8;
     if (position) base = *position;
     const size_t width = kv_heads * 256, blocks = steps * width / 32 * 2;   // key blocks, then value blocks
     const unsigned lane = threadIdx.x % 32;
@@ -24,11 +27,15 @@ __global__ void __launch_bounds__(256) kv_write_kernel(uint8_t* __restrict__ sta
         const bool is_value = block >= blocks / 2;
         const size_t index = (is_value ? block - blocks / 2 : block) * 32 + lane;   // into [steps][kv_heads][256]
         const size_t step = index / width, head = (index % width) / 256, column = index % 256;
-        __half scale_h;
-        const int8_t q = q8_encode((is_value ? values : keys)[index], scale_h);
-        uint8_t* row = state + (((is_value ? kv_heads : 0) + head) * context + base + step) * kv_row_q8;
-        reinterpret_cast<int8_t*>(row)[column] = q;
-        if (lane == 0) reinterpret_cast<__half*>(row + 256)[column / 32] = scale_h;
+        uint8_t* row = state + (((is_value ? kv_heads : 0) + head) * context + base + step) * kRow;
+        if constexpr (F16) {
+            reinterpret_cast<__half*>(row)[column] = __float2half_rn((is_value ? values : keys)[index]);
+        } else {
+            __half scale_h;
+            const int8_t q = q8_encode((is_value ? values : keys)[index], scale_h);
+            reinterpret_cast<int8_t*>(row)[column] = q;
+            if (lane == 0) reinterpret_cast<__half*>(row + 256)[column / 32] = scale_h;
+        }
     }
 }
 
@@ -50,13 +57,18 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const Segment* __restric
     }
 }
 
-// rows of 272 bytes -> rows of 256 F32: value = float(int8) * float(scale), one FP32 multiply.
+// rows of 272 bytes -> rows of 256 F32: value = float(int8) * float(scale), one FP32 multiply; rows of 512 bytes: the FP16 values widened.
+template<bool F16>
 __global__ void __launch_bounds__(256) kv_decode_rows_kernel(const uint8_t* __restrict__ rows, size_t count, float* __restrict__ out) {
     for (size_t index = size_t(blockIdx.x) * blockDim.x + threadIdx.x; index < count * 256; index += size_t(gridDim.x) * blockDim.x) {
-        const uint8_t* row = rows + index / 256 * kv_row_q8;
+        const uint8_t* row = rows + index / 256 * (F16 ? kv_row_f16 : kv_row_q8);
         const size_t column = index % 256;
-        const float scale = __half2float(reinterpret_cast<const __half*>(row + 256)[column / 32]);
-        out[index] = __fmul_rn(float(reinterpret_cast<const int8_t*>(row)[column]), scale);
+        if constexpr (F16) {
+            out[index] = __half2float(reinterpret_cast<const __half*>(row)[column]);
+        } else {
+            const float scale = __half2float(reinterpret_cast<const __half*>(row + 256)[column / 32]);
+            out[index] = __fmul_rn(float(reinterpret_cast<const int8_t*>(row)[column]), scale);
+        }
     }
 }
 
@@ -64,7 +76,8 @@ void launch_kv_write(Device& d, uint8_t* state, size_t context, size_t kv_heads,
                      const float* keys, const float* values) {
     const size_t warps = steps * kv_heads * 8 * 2;
     const unsigned grid = unsigned(std::min<size_t>((warps + 7) / 8, size_t(d.sms) * 8));
-    kv_write_kernel<<<grid, 256, 0, d.stream>>>(state, context, kv_heads, base, position, steps, keys, values);
+    if (d.kv_row == kv_row_f16) kv_write_kernel<true><<<grid, 256, 0, d.stream>>>(state, context, kv_heads, base, position, steps, keys, values);
+    else kv_write_kernel<false><<<grid, 256, 0, d.stream>>>(state, context, kv_heads, base, position, steps, keys, values);
     ++d.launches;
 }
 
@@ -83,9 +96,8 @@ extern "C" {
 int sdx_kv_write(void* handle, void* state, uint64_t context, uint64_t kv_heads, uint64_t base, uint64_t steps, const float* keys,
                  const float* values) {
     SDB_OP_BEGIN
-    if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build writes Q8_0 K/V rows only");
     if (!context || !kv_heads || !steps || base > context || steps > context - base) throw std::runtime_error("invalid Straydog K/V write");
-    span(value, state, checked_product({2, kv_heads, context, kv_row_q8}), "a K/V state");
+    span(value, state, checked_product({2, kv_heads, context, value.kv_row}), "a K/V state");
     span(value, keys, checked_product({steps, kv_heads, 256, 4}), "new keys");
     span(value, values, checked_product({steps, kv_heads, 256, 4}), "new values");
     launch_kv_write(value, static_cast<uint8_t*>(state), context, kv_heads, base, nullptr, steps, keys, values);
@@ -95,10 +107,11 @@ int sdx_kv_write(void* handle, void* state, uint64_t context, uint64_t kv_heads,
 int sdx_kv_decode_rows(void* handle, const void* rows, uint64_t count, float* out) {
     SDB_OP_BEGIN
     if (!count) throw std::runtime_error("invalid Straydog K/V row count");
-    span(value, rows, checked_product({count, kv_row_q8}), "K/V rows");
+    span(value, rows, checked_product({count, value.kv_row}), "K/V rows");
     span(value, out, checked_product({count, 256, 4}), "decoded K/V rows");
     const unsigned grid = unsigned(std::min<size_t>((count * 256 + 255) / 256, size_t(value.sms) * 16));
-    kv_decode_rows_kernel<<<grid, 256, 0, value.stream>>>(static_cast<const uint8_t*>(rows), count, out);
+    if (value.kv_row == kv_row_f16) kv_decode_rows_kernel<true><<<grid, 256, 0, value.stream>>>(static_cast<const uint8_t*>(rows), count, out);
+    else kv_decode_rows_kernel<false><<<grid, 256, 0, value.stream>>>(static_cast<const uint8_t*>(rows), count, out);
     ++value.launches;
     SDB_OP_END
 }

@@ -43,7 +43,7 @@ struct NormalizeArgs {
     const float* qnorm; const float* knorm; const float* iqnorm; const float* pool_norm;
     const uint32_t* positions; const uint32_t* ropes;
     float* packed;
-    uint8_t* state; size_t context;
+    uint8_t* state; size_t context; unsigned kv_row;
     uint8_t* mirror; size_t mirror_rows;
     float* blocks; size_t pool;   // [128][pool], then the history ring [16][128]
     int* status;
@@ -109,8 +109,13 @@ __global__ void __launch_bounds__(256) qsa_normalize_rows_kernel(const Normalize
         __half key_scale, value_scale;
         const int8_t k8 = q8_encode(key, key_scale), v8 = q8_encode(value, value_scale);
         auto put = [&](uint8_t* planes, size_t rows_of_plane, size_t at) {
-            uint8_t* k_row = planes + (head * rows_of_plane + at) * kv_row_q8;
-            uint8_t* v_row = planes + ((a.kv_heads + head) * rows_of_plane + at) * kv_row_q8;
+            uint8_t* k_row = planes + (head * rows_of_plane + at) * a.kv_row;
+            uint8_t* v_row = planes + ((a.kv_heads + head) * rows_of_plane + at) * a.kv_row;
+            if (a.kv_row == kv_row_f16) {   // FP16 rows: the nearest FP16 of each value (gpu/kernels.cpp:70)
+                reinterpret_cast<__half*>(k_row)[column] = __float2half_rn(key);
+                reinterpret_cast<__half*>(v_row)[column] = __float2half_rn(value);
+                return;
+            }
             reinterpret_cast<int8_t*>(k_row)[column] = k8;
             reinterpret_cast<int8_t*>(v_row)[column] = v8;
             if (column % 32 == 0) {
@@ -197,7 +202,6 @@ extern "C" int sdx_qsa_normalize_rows(void* handle, float* projections, uint64_t
                                       const uint32_t* positions, const uint32_t* ropes, float* packed, uint64_t selected, void* state,
                                       uint64_t context, void* mirror, uint64_t mirror_rows, float* index_state) {
     SDB_OP_BEGIN
-    if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build writes Q8_0 K/V rows only");
     if (!rows || rows > max_batch || !heads || !kv_heads || heads > 65535 || kv_heads > heads || !context || context > (uint64_t(1) << 24) ||
         stride < heads * 512 + kv_heads * 512 + 640 || (mirror_rows && !mirror) || mirror_rows > context)
         throw std::runtime_error("invalid Straydog attention dimensions");
@@ -207,8 +211,8 @@ extern "C" int sdx_qsa_normalize_rows(void* handle, float* projections, uint64_t
     span(value, iqnorm, 128 * 4, "an index-query norm"); span(value, pool_norm, 128 * 4, "an index-key norm");
     span(value, positions, rows * 4, "row positions"); span(value, ropes, rows * 4, "rotation positions");
     span(value, packed, checked_product({rows, heads * 256 + kv_heads * 512 + selected + 1, 4}), "packed attention rows");
-    span(value, state, checked_product({context, 2 * kv_heads, kv_row_q8}), "a K/V state");
-    if (mirror_rows) span(value, mirror, checked_product({mirror_rows, 2 * kv_heads, kv_row_q8}), "a K/V mirror");
+    span(value, state, checked_product({context, 2 * kv_heads, value.kv_row}), "a K/V state");
+    if (mirror_rows) span(value, mirror, checked_product({mirror_rows, 2 * kv_heads, value.kv_row}), "a K/V mirror");
     span(value, index_state, checked_product({pool + 16, 128, 4}), "an index state");
     NormalizeArgs a{};
     const size_t keys_at = heads * 512, values_at = keys_at + kv_heads * 256, index_at = keys_at + kv_heads * 512;
@@ -217,7 +221,7 @@ extern "C" int sdx_qsa_normalize_rows(void* handle, float* projections, uint64_t
     a.rows = rows; a.heads = heads; a.kv_heads = kv_heads;
     a.qnorm = qnorm; a.knorm = knorm; a.iqnorm = iqnorm; a.pool_norm = pool_norm; a.positions = positions; a.ropes = ropes;
     a.packed = packed; a.state = static_cast<uint8_t*>(state); a.context = context;
-    a.mirror = static_cast<uint8_t*>(mirror); a.mirror_rows = mirror_rows; a.blocks = index_state; a.pool = pool; a.status = status_word(value);
+    a.mirror = static_cast<uint8_t*>(mirror); a.mirror_rows = mirror_rows; a.blocks = index_state; a.pool = pool; a.status = status_word(value); a.kv_row = value.kv_row;
     qsa_normalize_rows_kernel<<<dim3(unsigned(heads + kv_heads + 5), unsigned(rows)), 256, 0, value.stream>>>(a);
     ++value.launches;
     SDB_OP_END
@@ -231,7 +235,6 @@ extern "C" int sdx_qsa_normalize_chunk(void* handle, const float* qgate, const f
                                        const float* knorm, const float* iqnorm, const float* pool_norm, float* packed, uint64_t selected,
                                        void* state, uint64_t context, void* mirror, uint64_t mirror_rows, float* index_state) {
     SDB_OP_BEGIN
-    if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build writes Q8_0 K/V rows only");
     if (!count || count > 65535 || !heads || !kv_heads || heads > 65535 || kv_heads > heads || !context || context > (uint64_t(1) << 24) ||
         position > context || count > context - position || (mirror_rows && !mirror) || mirror_rows > context)
         throw std::runtime_error("invalid Straydog attention dimensions");
@@ -244,8 +247,8 @@ extern "C" int sdx_qsa_normalize_chunk(void* handle, const float* qgate, const f
     span(value, qnorm, 256 * 4, "a query norm"); span(value, knorm, 256 * 4, "a key norm");
     span(value, iqnorm, 128 * 4, "an index-query norm"); span(value, pool_norm, 128 * 4, "an index-key norm");
     span(value, packed, checked_product({count, heads * 256 + kv_heads * 512 + selected + 1, 4}), "packed attention rows");
-    span(value, state, checked_product({context, 2 * kv_heads, kv_row_q8}), "a K/V state");
-    if (mirror_rows) span(value, mirror, checked_product({mirror_rows, 2 * kv_heads, kv_row_q8}), "a K/V mirror");
+    span(value, state, checked_product({context, 2 * kv_heads, value.kv_row}), "a K/V state");
+    if (mirror_rows) span(value, mirror, checked_product({mirror_rows, 2 * kv_heads, value.kv_row}), "a K/V mirror");
     span(value, index_state, checked_product({pool + 16, 128, 4}), "an index state");
     NormalizeArgs a{};
     a.qgate = qgate; a.qgate_stride = heads * 512; a.key = key; a.key_stride = kv_heads * 256; a.value = value_rows; a.value_stride = kv_heads * 256;
@@ -253,7 +256,7 @@ extern "C" int sdx_qsa_normalize_chunk(void* handle, const float* qgate, const f
     a.rows = count; a.heads = heads; a.kv_heads = kv_heads; a.base = position; a.copy_values = true;
     a.qnorm = qnorm; a.knorm = knorm; a.iqnorm = iqnorm; a.pool_norm = pool_norm;
     a.packed = packed; a.state = static_cast<uint8_t*>(state); a.context = context;
-    a.mirror = static_cast<uint8_t*>(mirror); a.mirror_rows = mirror_rows; a.blocks = index_state; a.pool = pool; a.status = status_word(value);
+    a.mirror = static_cast<uint8_t*>(mirror); a.mirror_rows = mirror_rows; a.blocks = index_state; a.pool = pool; a.status = status_word(value); a.kv_row = value.kv_row;
     qsa_normalize_rows_kernel<<<dim3(unsigned(heads + kv_heads + 4), unsigned(count)), 256, 0, value.stream>>>(a);
     const uint64_t completed = (position + count) / 4 - position / 4;
     qsa_pool_chunk_kernel<<<unsigned(std::max<uint64_t>(completed, 1)), 128, 0, value.stream>>>(a, completed);

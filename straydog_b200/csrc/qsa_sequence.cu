@@ -1,7 +1,8 @@
 // sd_attention_sequence: the reference's standalone selection-attention entry (host floats in,
 // host floats out; gpu/kernels.cpp:4387-4419 over attention_scores / attention_reduce, :100-165).
 //
-// The selection kernel keeps FP32 arithmetic throughout (queries arrive as F32 and the reference
+// Both K/V row formats (sd_kv_format: Q8_0 rows of 272 bytes, FP16 rows of 512, gpu/kernels.cpp:36-43): this entry is the check path,
+// and the FP16 rows are what the Q8_0 rows are checked against. The selection kernel keeps FP32 arithmetic throughout (queries arrive as F32 and the reference
 // computes in F32): one block per (step, query head), a warp per selected key for the scores
 // (lanes over the 256 columns, 8 consecutive columns each), the probabilities in shared memory, then
 // a thread per output column summing p * v in slot order, as attention_reduce does.
@@ -15,11 +16,15 @@ void launch_kv_write(Device& d, uint8_t* state, size_t context, size_t kv_heads,
 
 constexpr int kMaxSelected = 2052;   // gpu/kernels.cpp:4392
 
-__device__ __forceinline__ float q8_at(const uint8_t* row, unsigned column) {
+// kv_load (gpu/kernels.cpp:40-43): a row's value as it is read, Q8_0 (one FP32 multiply) or FP16
+template<bool F16>
+__device__ __forceinline__ float kv_at(const uint8_t* row, unsigned column) {
+    if constexpr (F16) return __half2float(reinterpret_cast<const __half*>(row)[column]);
     return __fmul_rn(float(reinterpret_cast<const int8_t*>(row)[column]),
                      __half2float(reinterpret_cast<const __half*>(row + 256)[column / 32]));
 }
 
+template<bool F16>
 __global__ void __launch_bounds__(256) selection_attention_kernel(const uint8_t* __restrict__ state, size_t context, size_t base,
                                                                   size_t steps, size_t selected, size_t heads, size_t kv_heads,
                                                                   float scale, const float* __restrict__ input, float* __restrict__ output) {
@@ -35,7 +40,8 @@ __global__ void __launch_bounds__(256) selection_attention_kernel(const uint8_t*
     query[t] = input[item * 256 + t];
     __syncthreads();
     // scores: a warp per slot
-    const uint8_t* keys = state + kv * context * kv_row_q8;
+    constexpr size_t kRow = F16 ? kv_row_f16 : kv_row_q8;
+    const uint8_t* keys = state + kv * context * kRow;
     for (size_t slot = warp; slot < selected; slot += 8) {
         int token = -1;
         if (slot < count) {
@@ -44,14 +50,24 @@ __global__ void __launch_bounds__(256) selection_attention_kernel(const uint8_t*
         }
         float sum = 0.0f;
         if (token >= 0) {
-            const uint8_t* row = keys + size_t(token) * kv_row_q8;
-            const uint2 bytes = *reinterpret_cast<const uint2*>(row + 8 * lane);
-            const float block_scale = __half2float(reinterpret_cast<const __half*>(row + 256)[lane / 4]);
-            #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t word = i < 4 ? bytes.x : bytes.y;
-                const float k = __fmul_rn(float(int8_t(word >> (8 * (i & 3)))), block_scale);
-                sum = fmaf(k, query[8 * lane + i], sum);
+            const uint8_t* row = keys + size_t(token) * kRow;
+            if constexpr (F16) {
+                const uint4 halves = *reinterpret_cast<const uint4*>(row + 16 * lane);
+                const uint32_t words[4] = {halves.x, halves.y, halves.z, halves.w};
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float k = __half2float(__ushort_as_half(uint16_t(i & 1 ? words[i / 2] >> 16 : words[i / 2] & 0xffffu)));
+                    sum = fmaf(k, query[8 * lane + i], sum);
+                }
+            } else {
+                const uint2 bytes = *reinterpret_cast<const uint2*>(row + 8 * lane);
+                const float block_scale = __half2float(reinterpret_cast<const __half*>(row + 256)[lane / 4]);
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t word = i < 4 ? bytes.x : bytes.y;
+                    const float k = __fmul_rn(float(int8_t(word >> (8 * (i & 3)))), block_scale);
+                    sum = fmaf(k, query[8 * lane + i], sum);
+                }
             }
             #pragma unroll
             for (unsigned offset = 16; offset; offset /= 2) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
@@ -84,12 +100,12 @@ __global__ void __launch_bounds__(256) selection_attention_kernel(const uint8_t*
     for (int w = 0; w < 8; ++w) total += reduce[w];
     for (size_t slot = t; slot < selected; slot += 256) weights[slot] = __fdiv_rn(weights[slot], total);
     __syncthreads();
-    const uint8_t* values = state + (kv_heads + kv) * context * kv_row_q8;
+    const uint8_t* values = state + (kv_heads + kv) * context * kRow;
     float result = 0.0f;
     const size_t live = count < selected ? count : selected;
     for (size_t slot = 0; slot < live; ++slot) {
         const int token = tokens[slot];
-        if (token >= 0) result = fmaf(weights[slot], q8_at(values + size_t(token) * kv_row_q8, t), result);
+        if (token >= 0) result = fmaf(weights[slot], kv_at<F16>(values + size_t(token) * kRow, t), result);
     }
     output[item * 256 + t] = result;
 }
@@ -108,7 +124,6 @@ int sd_attention_sequence(void* handle, void* state, uint64_t context, uint64_t 
         if (!input || !output || !context || context > 262144 || !steps || steps > max_batch || base > context ||
             steps > context - base || !selected || selected > kMaxSelected)
             throw std::runtime_error("invalid Straydog attention dimensions");
-        if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
         if (allocation_bytes(value, state) != context * 4 * value.kv_row)
             throw std::runtime_error("Straydog attention state size mismatch");
         if (input_count != steps * (heads * 256 + kv_heads * 512 + selected + 1) || output_count != steps * heads * 256)
@@ -126,8 +141,12 @@ int sd_attention_sequence(void* handle, void* state, uint64_t context, uint64_t 
         SDB_CHECK(cudaMemcpyAsync(work, input, in_bytes, cudaMemcpyHostToDevice, value.stream));
         launch_kv_write(value, static_cast<uint8_t*>(state), context, kv_heads, base, nullptr, steps, work + steps * heads * 256,
                         work + steps * (heads + kv_heads) * 256);
-        selection_attention_kernel<<<unsigned(steps * heads), 256, 0, value.stream>>>(
-            static_cast<const uint8_t*>(state), context, base, steps, selected, heads, kv_heads, 0.0625f, work, device_out);
+        if (value.kv_row == kv_row_f16)
+            selection_attention_kernel<true><<<unsigned(steps * heads), 256, 0, value.stream>>>(
+                static_cast<const uint8_t*>(state), context, base, steps, selected, heads, kv_heads, 0.0625f, work, device_out);
+        else
+            selection_attention_kernel<false><<<unsigned(steps * heads), 256, 0, value.stream>>>(
+                static_cast<const uint8_t*>(state), context, base, steps, selected, heads, kv_heads, 0.0625f, work, device_out);
         ++value.launches;
         SDB_CHECK(cudaGetLastError());
         SDB_CHECK(cudaMemcpyAsync(output, device_out, out_bytes, cudaMemcpyDeviceToHost, value.stream));

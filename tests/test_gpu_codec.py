@@ -68,21 +68,53 @@ def test_kv_stage_registration_is_validated(gpu):
     gpu.release(stage)
 
 
-def test_fp16_rows_are_a_known_format_that_the_attention_refuses():
-    # gpu/kernels.cpp:4266-4275 takes 512 (FP16 rows) and 272 (Q8_0 rows); this library's attention reads Q8_0 rows only and
-    # says so at the call instead of misreading FP16 rows
+def test_fp16_rows_are_written_decoded_and_attended_by_the_check_path():
+    # gpu/kernels.cpp:4266-4275 takes 512 (FP16 rows) and 272 (Q8_0 rows). FP16 rows (a value's nearest FP16, gpu/kernels.cpp:42, 70)
+    # are written, decoded and attended by sd_attention_sequence, the path Q8_0 results are checked against; the tensor-core decode
+    # and prompt kernels read Q8_0 rows only and say so at the call instead of misreading FP16 rows
     from straydog_b200.backend import Backend, StraydogError
+    from util import attention_sequence_input
+    rng = np.random.default_rng(21)
     with Backend(0, 1 << 28) as gpu:
         with pytest.raises(StraydogError, match="K/V format"):
             gpu.kv_format(100)
         gpu.kv_format(512)
-        state = gpu.buffer(4 * 16 * 512)
-        q, out = gpu.buffer(16 * 256 * 2), gpu.buffer(16 * 256 * 4)
+        context, base, steps, selected = 96, 40, 5, 64
+        filled = rng.normal(0, 1, (4, context, 256)).astype(np.float16)
+        filled[:, base:] = 0
+        state = gpu.allocate(filled.nbytes)
+        gpu.write(state, filled)
+        inp = attention_sequence_input(rng, steps, selected, base, context, "sparse")
+        got = gpu.attention_sequence(state, context, base, steps, selected, inp)
+        rows = gpu.download(state, np.empty_like(filled))
+        q = inp[:steps * 24 * 256].reshape(steps, 24, 256).astype(np.float64)
+        k = inp[steps * 24 * 256:steps * 26 * 256].reshape(steps, 2, 256)
+        v = inp[steps * 26 * 256:steps * 28 * 256].reshape(steps, 2, 256)
+        want_rows = filled.copy()
+        want_rows[:2, base:base + steps] = k.transpose(1, 0, 2).astype(np.float16)
+        want_rows[2:, base:base + steps] = v.transpose(1, 0, 2).astype(np.float16)
+        assert np.array_equal(rows.view(np.uint16), want_rows.view(np.uint16)), "rows base.. hold the nearest FP16 of the new keys and values"
+        lists = inp[steps * 28 * 256:steps * 28 * 256 + steps * selected].reshape(steps, selected)
+        counts = inp[steps * 28 * 256 + steps * selected:]
+        planes = want_rows.astype(np.float64)
+        for r in range(steps):
+            live = [int(x) for x in lists[r, :int(counts[r])] if 0 <= x <= base + r and x < context]
+            for h in range(24):
+                scores = planes[h // 12, live] @ q[r, h] * 0.0625
+                w = np.exp(scores - scores.max())
+                assert np.abs(got[r, h] - (w / w.sum()) @ planes[2 + h // 12, live]).max() < 1e-4
+        # the codec's two entries in the same format
+        keys, values = rng.normal(0, 2, (3, 2, 256)).astype(np.float32), rng.normal(0, 2, (3, 2, 256)).astype(np.float32)
+        kb, vb = gpu.upload(keys), gpu.upload(values)
+        gpu.kv_write(state, context, 2, 7, 3, kb, vb)
+        out = gpu.buffer(3 * 256 * 4)
+        gpu._c(gpu.lib.sdx_kv_decode_rows(gpu.handle, state.pointer + (1 * context + 7) * 512, 3, out.pointer))
+        assert np.array_equal(gpu.read(out, np.float32, (3, 256)), keys[:, 1].astype(np.float16).astype(np.float32))
+        q16, o = gpu.buffer(16 * 256 * 2), gpu.buffer(16 * 256 * 4)
         with pytest.raises(StraydogError, match="Q8_0"):
-            gpu.qsa_decode([state], [16], [16], 16, 2, 1 / 16, q.pointer, out.pointer)
+            gpu.qsa_decode([state], [context], [16], 16, 2, 1 / 16, q16.pointer, o.pointer)
         with pytest.raises(StraydogError, match="Q8_0"):
-            gpu.qsa_prompt(state, 16, 0, 4, 16, 2, 1 / 16, q.pointer, out.pointer)
-        with pytest.raises(StraydogError, match="Q8_0"):
-            gpu.kv_write(state, 16, 2, 0, 1, q, q)
+            gpu.qsa_prompt(state, context, 0, 4, 16, 2, 1 / 16, q16.pointer, o.pointer)
         gpu.kv_format(272)
-        gpu.qsa_decode([state], [16], [16], 16, 2, 1 / 16, q.pointer, out.pointer)
+        small = gpu.buffer(4 * 16 * 272)
+        gpu.qsa_decode([small], [16], [16], 16, 2, 1 / 16, q16.pointer, o.pointer)

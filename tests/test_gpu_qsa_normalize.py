@@ -271,3 +271,19 @@ def test_invalid_chunk_shapes_are_refused(gpu):
     d["count"] = 9   # more tokens than the arrays hold
     with pytest.raises(StraydogError, match="outside"):
         run_chunk(gpu, d)
+
+
+def test_fp16_rows_take_the_nearest_fp16_of_the_keys_and_values():
+    # sd_kv_format(512): the front writes FP16 rows (gpu/kernels.cpp:70), both forms
+    from straydog_b200.backend import Backend
+    with Backend(0, 1 << 29) as fp16:
+        fp16.kv_format(512)
+        c = case(8, 16, 2, 128, [60, 61, 62, 63])
+        c["state"] = np.zeros(128 * 4 * 512, np.uint8)
+        got, bufs = run(fp16, c)
+        rows = got["state"].view(np.float16).reshape(4, 128, 256)
+        keys = got["packed"][4 * 16 * 256:4 * 18 * 256].reshape(4, 2, 256)
+        values = c["proj"][:, 16 * 512 + 512:16 * 512 + 1024].reshape(4, 2, 256)
+        assert np.array_equal(rows[:2, 60:64].view(np.uint16), keys.transpose(1, 0, 2).astype(np.float16).view(np.uint16))
+        assert np.array_equal(rows[2:, 60:64].view(np.uint16), values.transpose(1, 0, 2).astype(np.float16).view(np.uint16))
+        assert not rows[:, :60].any() and not rows[:, 64:].any()
