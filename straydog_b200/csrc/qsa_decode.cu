@@ -65,6 +65,23 @@ __device__ __forceinline__ uint32_t bytes23_to_half2(uint32_t x) {
     const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
+// Bytes 0 and 2 (or 1 and 3) of a word (already xor 0x80808080) -> an FP16 pair, exactly.
+__device__ __forceinline__ uint32_t bytes02_to_half2(uint32_t x) {
+    const uint32_t h = prmt(x, 0x64646464u, 0x4240u);
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bytes13_to_half2(uint32_t x) {
+    const uint32_t h = prmt(x, 0x64646464u, 0x4341u);
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+// Four 8 x 8 matrices of 16-bit units, transposed on the way: lane i gives the address of row i % 8 of matrix i / 8, and lane (g, t)
+// receives, per matrix, unit g of rows 2t (low half) and 2t + 1 (high half).
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
 __device__ __forceinline__ float half_at(const uint4& v, int i) {
     const uint32_t w = i < 2 ? v.x : i < 4 ? v.y : i < 6 ? v.z : v.w;
     return __half2float(__ushort_as_half(uint16_t(i & 1 ? w >> 16 : w & 0xffffu)));
@@ -124,6 +141,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const Decode
 
     const int r0 = tile_row(g), r1 = r0 + 8;
     const int ka = tile_row(2 * t), kb = tile_row(2 * t + 1);   // the keys whose P this lane holds after the transpose
+    // The value bytes of a 32-column block reach the lanes through one transposing ldmatrix: a 16-bit unit is two columns of one key,
+    // matrix m holds keys (k-index j -> key tile_row(j) + 8 (m & 1)) and the units of columns 16 (m >> 1) ..: lane (g, t) then has,
+    // per matrix, columns 2g and 2g + 1 of the keys ka (+8) and kb (+8), the k-indices 2t and 2t + 1 its weights sit at.
+    const uint32_t v_lane = uint32_t((tile_row(lane % 8) + 8 * ((lane / 8) & 1)) * int(kv_row_q8) + 16 * (lane / 16));
     uint32_t slot = 0, phase = 0, fill = kStages - 1;
 
     while (!use.done()) {
@@ -158,6 +179,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const Decode
             if (!mbar_wait(&bars[slot], phase)) { if (lane == 0) atomicExch(a.status, 1); drain_delay(); return; }
             const uint8_t* kt = ring + slot * kTileBytes;
             const uint8_t* vt = kt + kTileKeys * kv_row_q8;
+            const uint32_t vt_address = smem_u32(vt);
 
             // ---- S = K Q^T: per 32-column block two MMAs into a fresh accumulator, then the block's scale ----
             const uint4 ks0 = *reinterpret_cast<const uint4*>(kt + r0 * kv_row_q8 + 256);
@@ -223,22 +245,19 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const Decode
             for (int b = 0; b < 8; ++b) {
                 const uint32_t pb0 = pack_half2(pa * half_at(va, b), pb * half_at(vb, b));
                 const uint32_t pb1 = pack_half2(pc * half_at(vc, b), pd * half_at(vd, b));
-                uint32_t wa = *reinterpret_cast<const uint32_t*>(vt + ka * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-                uint32_t wb = *reinterpret_cast<const uint32_t*>(vt + kb * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-                uint32_t wc = *reinterpret_cast<const uint32_t*>(vt + (ka + 8) * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-                uint32_t wd = *reinterpret_cast<const uint32_t*>(vt + (kb + 8) * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-                // interleave the two keys' bytes: (a.b0, b.b0, a.b1, b.b1) and (a.b2, b.b2, a.b3, b.b3)
-                const uint32_t u = prmt(wa, wb, 0x5140u), v = prmt(wa, wb, 0x7362u);
-                const uint32_t u2 = prmt(wc, wd, 0x5140u), v2 = prmt(wc, wd, 0x7362u);
-                uint32_t af[4] = {bytes01_to_half2(u), bytes23_to_half2(u), bytes01_to_half2(u2), bytes23_to_half2(u2)};
+                // w[0], w[1]: columns 32b + 2g, + 1 of keys (ka, kb) and (ka + 8, kb + 8); w[2], w[3]: columns 32b + 16 + 2g, + 1
+                uint32_t w[4];
+                ldmatrix_x4_trans(w, vt_address + v_lane + 32 * b);
+                w[0] ^= 0x80808080u; w[1] ^= 0x80808080u; w[2] ^= 0x80808080u; w[3] ^= 0x80808080u;
+                uint32_t af[4] = {bytes02_to_half2(w[0]), bytes13_to_half2(w[0]), bytes02_to_half2(w[1]), bytes13_to_half2(w[1])};
                 mma_f16(o[b][0], af, pb0, pb1);
-                uint32_t ag[4] = {bytes01_to_half2(v), bytes23_to_half2(v), bytes01_to_half2(v2), bytes23_to_half2(v2)};
+                uint32_t ag[4] = {bytes02_to_half2(w[2]), bytes13_to_half2(w[2]), bytes02_to_half2(w[3]), bytes13_to_half2(w[3])};
                 mma_f16(o[b][1], ag, pb0, pb1);
             }
             use.key += rows;
             if (++slot == kStages) { slot = 0; phase ^= 1; }
         }
-        // ---- the piece's partial: o[b][i][c] is head 2t + (c & 1), column 32b + 4g + 2i + (c >> 1) ----
+        // ---- the piece's partial: o[b][i][c] is head 2t + (c & 1), column 32b + 16i + 2g + (c >> 1) ----
         #pragma unroll
         for (int offset = 4; offset < 32; offset *= 2) {
             l0 += __shfl_xor_sync(0xffffffffu, l0, offset);
@@ -249,7 +268,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) qsa_decode_kernel(const Decode
         for (int b = 0; b < 8; ++b)
             #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const int column = 32 * b + 4 * g + 2 * i;
+                const int column = 32 * b + 16 * i + 2 * g;
                 *reinterpret_cast<float2*>(mine + (2 * t) * 258 + column) = make_float2(o[b][i][0], o[b][i][2]);
                 *reinterpret_cast<float2*>(mine + (2 * t + 1) * 258 + column) = make_float2(o[b][i][1], o[b][i][3]);
             }
