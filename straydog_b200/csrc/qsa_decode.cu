@@ -65,23 +65,6 @@ __device__ __forceinline__ uint32_t bytes23_to_half2(uint32_t x) {
     const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
-// Bytes 0 and 2 (or 1 and 3) of a word (already xor 0x80808080) -> an FP16 pair, exactly.
-__device__ __forceinline__ uint32_t bytes02_to_half2(uint32_t x) {
-    const uint32_t h = prmt(x, 0x64646464u, 0x4240u);
-    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
-__device__ __forceinline__ uint32_t bytes13_to_half2(uint32_t x) {
-    const uint32_t h = prmt(x, 0x64646464u, 0x4341u);
-    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&h), __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480)));
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
-// Four 8 x 8 matrices of 16-bit units, transposed on the way: lane i gives the address of row i % 8 of matrix i / 8, and lane (g, t)
-// receives, per matrix, unit g of rows 2t (low half) and 2t + 1 (high half).
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
-}
 __device__ __forceinline__ float half_at(const uint4& v, int i) {
     const uint32_t w = i < 2 ? v.x : i < 4 ? v.y : i < 6 ? v.z : v.w;
     return __half2float(__ushort_as_half(uint16_t(i & 1 ? w >> 16 : w & 0xffffu)));

@@ -131,6 +131,9 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // heads 2t and 2t+1 of this warp's eight
     const int r0 = sel_tile_row(g), r1 = r0 + 8;
     const int ka = sel_tile_row(2 * t), kb = sel_tile_row(2 * t + 1);
+    // (a block's value bytes come through one transposing ldmatrix, as in the dense decode kernel: matrix m holds the keys
+    //  k-index j -> sel_tile_row(j) + 8 (m & 1) and the 16-bit units of columns 16 (m >> 1) ..)
+    const uint32_t v_lane = uint32_t((sel_tile_row(lane % 8) + 8 * ((lane / 8) & 1)) * int(kv_row_q8) + 16 * (lane / 16));
 
     #pragma unroll 1
     for (int tile = 0; tile < kSelTiles; ++tile) {
@@ -141,6 +144,7 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
         if (!mbar_wait(&bars[tile], 0)) { if (lane == 0) atomicExch(a.status, 1); drain_delay(); return; }
         const uint8_t* kt = smem + size_t(tile) * kSelTileBytes;
         const uint8_t* vt = kt + kSelTile * kv_row_q8;
+        const uint32_t vt_address = smem_u32(vt);
         // ---- S = K Q^T per 32-column block, then the block's scale (rows nobody fetched hold stale bytes: masked below) ----
         const uint4 ks0 = *reinterpret_cast<const uint4*>(kt + r0 * kv_row_q8 + 256);
         const uint4 ks1 = *reinterpret_cast<const uint4*>(kt + r1 * kv_row_q8 + 256);
@@ -205,21 +209,19 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
             uint32_t ph0, pl0, ph1, pl1;
             split_pair(pa * sel_half_at(va, b), pb * sel_half_at(vb, b), ph0, pl0);
             split_pair(pc * sel_half_at(vc, b), pd * sel_half_at(vd, b), ph1, pl1);
-            const uint32_t wa = *reinterpret_cast<const uint32_t*>(vt + ka * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-            const uint32_t wb = *reinterpret_cast<const uint32_t*>(vt + kb * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-            const uint32_t wc = *reinterpret_cast<const uint32_t*>(vt + (ka + 8) * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-            const uint32_t wd = *reinterpret_cast<const uint32_t*>(vt + (kb + 8) * kv_row_q8 + 32 * b + 4 * g) ^ 0x80808080u;
-            const uint32_t u = prmt(wa, wb, 0x5140u), v = prmt(wa, wb, 0x7362u);
-            const uint32_t u2 = prmt(wc, wd, 0x5140u), v2 = prmt(wc, wd, 0x7362u);
-            const uint32_t af[4] = {sel_bytes01(u), sel_bytes23(u), sel_bytes01(u2), sel_bytes23(u2)};
+            // w[0], w[1]: columns 32b + 2g, + 1 of keys (ka, kb) and (ka + 8, kb + 8); w[2], w[3]: columns 32b + 16 + 2g, + 1
+            uint32_t w[4];
+            ldmatrix_x4_trans(w, vt_address + v_lane + 32 * b);
+            w[0] ^= 0x80808080u; w[1] ^= 0x80808080u; w[2] ^= 0x80808080u; w[3] ^= 0x80808080u;
+            const uint32_t af[4] = {bytes02_to_half2(w[0]), bytes13_to_half2(w[0]), bytes02_to_half2(w[1]), bytes13_to_half2(w[1])};
             mma_f16(o[b][0], af, pl0, pl1);
             mma_f16(o[b][0], af, ph0, ph1);
-            const uint32_t ag[4] = {sel_bytes01(v), sel_bytes23(v), sel_bytes01(v2), sel_bytes23(v2)};
+            const uint32_t ag[4] = {bytes02_to_half2(w[2]), bytes13_to_half2(w[2]), bytes02_to_half2(w[3]), bytes13_to_half2(w[3])};
             mma_f16(o[b][1], ag, pl0, pl1);
             mma_f16(o[b][1], ag, ph0, ph1);
         }
     }
-    // ---- the chunk's partial: o[b][i][c] is head 2t + (c & 1) of this warp's eight, column 32b + 4g + 2i + (c >> 1) ----
+    // ---- the chunk's partial: o[b][i][c] is head 2t + (c & 1) of this warp's eight, column 32b + 16i + 2g + (c >> 1) ----
     #pragma unroll
     for (int offset = 4; offset < 32; offset *= 2) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, offset);
@@ -234,7 +236,7 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
         for (int b = 0; b < 8; ++b)
             #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const int column = 32 * b + 4 * g + 2 * i;
+                const int column = 32 * b + 16 * i + 2 * g;
                 *reinterpret_cast<float2*>(mine + column) = make_float2(o[b][i][which], o[b][i][2 + which]);
             }
         if (g == 0) { mine[256] = which ? m1 : m0; mine[257] = which ? l1 : l0; }
