@@ -958,7 +958,7 @@ def main():
             "e2e": {"value": total_e2e_bytes * args.steps / (e2e_ms_max / 1e3) / 1e9, "unit": UNIT,
                     "h2d_bytes_per_step": int(q_host.nbytes + k_host.nbytes + v_host.nbytes), "d2h_bytes_per_step": int(out_host.nbytes),
                     "ms_per_step": e2e_ms_max / args.steps, "tokens_per_s": total_sequences * args.steps / (e2e_ms_max / 1e3),
-                    "note": "sdx_attention_batch from pinned host buffers; every step appends a row at a new position and rebuilds its work list"},
+                    "note": "sdx_attention_batch from pinned host buffers; every step appends a row at a new position; the entry keeps its work list from step to step (new tiles join a sequence's last piece, a new list every 8 tiles of growth)"},
             "gpu_launches": int(launches), "clocks": clocks, "plan": info, "cuts": "fixed" if args.fixed_cuts else "moving",
             "max_abs_error_vs_oracle": error, "sequences_checked": n,
             "step_ms_percentiles": {"p10": pick(0.10), "p50": pick(0.50), "p90": pick(0.90), "steps": len(per_step),

@@ -59,6 +59,7 @@ struct Device {
     void* work = nullptr; size_t work_bytes = 0;        // packed inputs / outputs of host-pointer entries
     void* partial = nullptr; size_t partial_bytes = 0;  // split partials of the decode kernels
     void* tables = nullptr; size_t tables_bytes = 0;    // work lists of the decode kernels
+    std::shared_ptr<void> batch_cache;                  // sdx_attention_batch's last work list, kept while the batch keeps its tile counts
     void* unions = nullptr; size_t unions_bytes = 0;    // places and blocks of a gathered selection union, the renumbered rows
     long long* trace = nullptr; size_t trace_ctas = 0;   // -DSDX_TRACE builds: the last traced launch's counters
     bool fixed_cuts = false;                            // the decode work list's cuts (sdx_decode_cuts)

@@ -393,7 +393,9 @@ static void build_tables(const std::vector<const uint8_t*>& states, const uint64
             while (key < lengths[s]) {
                 if (!room) { out.warp_piece.push_back(uint32_t(out.pieces.size())); room = per_warp; }
                 const uint64_t tiles_left = (lengths[s] - key + kTileKeys - 1) / kTileKeys, take = std::min(room, tiles_left);
-                const uint64_t end = std::min<uint64_t>(lengths[s], key + take * kTileKeys);
+                // (a piece ends at a tile border; the kernel stops at the segment's length, so a work list stays valid while its
+                // segments keep their tile counts)
+                const uint64_t end = key + take * kTileKeys;
                 out.pieces.push_back(Piece{uint32_t(out.segments.size()), uint32_t(key), uint32_t(end), uint32_t(out.pieces.size())});
                 room -= take;
                 key = end;
@@ -521,8 +523,30 @@ void qsa_decode_dense(Device& d, const void* const* states, const uint64_t* cont
     run_plan(d, plan, scale, q, out);
 }
 
+// sdx_attention_batch's work list, kept from call to call. A decode step makes every sequence one position longer, and the cuts
+// lie at tile borders: the list of the step before serves this step with the segments' new lengths, and a sequence that has crossed
+// into a new 16-key tile gets that tile added to its last piece (moving cuts only: the fixed cuts are a function of the length and
+// are rebuilt). The host builds a new list when the batch changes or once a sequence has grown by more than kCacheGrowth tiles since
+// the list was built (the warps that hold last pieces would otherwise drift ahead of the others); in between, the segments and the
+// pieces go to the device as they are (a few tens of KB) and the host builds nothing.
+constexpr uint32_t kCacheGrowth = 8;
+struct BatchCache {
+    std::vector<const uint8_t*> states;
+    std::vector<uint64_t> contexts;
+    std::vector<uint32_t> built, tiles;   // a sequence's tiles when the list was built, and now
+    uint64_t heads = 0, kv_heads = 0;
+    bool fixed = false;
+    HostTables host;
+    DecodePlan plan;
+    // the list on the device and its page-locked staging area: allocations of the cache's own (the other decode entries use the handle's,
+    // and may still be copying out of theirs when this entry is called; this entry ends with a synchronisation, so its own are free)
+    void* tables = nullptr; size_t tables_bytes = 0;
+    void* staging = nullptr; size_t staging_bytes = 0;
+    ~BatchCache() { if (tables) cudaFree(tables); if (staging) cudaFreeHost(staging); }
+};
+
 // One decode step of a batch from host buffers: the new rows are appended and the batch is decoded by one pass over one work
-// list. The host builds the list while the copies of the queries and the new rows are in flight.
+// list. The host builds the list (when the step before's does not serve) while the copies of the queries and the new rows are in flight.
 void attention_batch(Device& d, void* const* states, const uint64_t* contexts, const uint64_t* bases, uint64_t sequences, uint64_t heads,
                      uint64_t kv_heads, float scale, const void* q, const float* k, const float* v, float* out) {
     // everything is checked before anything is queued: a refused call leaves the K/V states as they were
@@ -551,19 +575,47 @@ void attention_batch(Device& d, void* const* states, const uint64_t* contexts, c
     SDB_CHECK(cudaMemcpyAsync(work, q, q_bytes, cudaMemcpyHostToDevice, d.stream));
     SDB_CHECK(cudaMemcpyAsync(work + k_at, k, new_bytes, cudaMemcpyHostToDevice, d.stream));
     SDB_CHECK(cudaMemcpyAsync(work + v_at, v, new_bytes, cudaMemcpyHostToDevice, d.stream));
-    HostTables host;
-    build_tables(checked, contexts, lengths.data(), sequences, heads, kv_heads, uint32_t(d.sms) * kWarps, host, d.fixed_cuts);
-    DecodePlan plan;
-    fill_plan(d, host, plan, sequences, heads, kv_heads);
-    // (these grow on the first call of a size only; the previous call ended with a synchronisation, so the staging area is free)
-    ensure(d, d.pinned, d.pinned_bytes, plan.table_bytes, true);
-    ensure(d, d.tables, d.tables_bytes, plan.table_bytes);
+    if (!d.batch_cache) d.batch_cache = std::make_shared<BatchCache>();
+    BatchCache& cache = *static_cast<BatchCache*>(d.batch_cache.get());
+    std::vector<uint32_t> tiles(sequences);
+    for (uint64_t s = 0; s < sequences; ++s) tiles[s] = uint32_t((lengths[s] + kTileKeys - 1) / kTileKeys);
+    bool serves = cache.tables && cache.heads == heads && cache.kv_heads == kv_heads && cache.fixed == d.fixed_cuts && cache.states == checked &&
+                  std::equal(cache.contexts.begin(), cache.contexts.end(), contexts);
+    for (uint64_t s = 0; serves && s < sequences; ++s)
+        serves = tiles[s] == cache.tiles[s] || (!d.fixed_cuts && tiles[s] > cache.tiles[s] && tiles[s] - cache.built[s] <= kCacheGrowth);
+    HostTables& host = cache.host;
+    DecodePlan& plan = cache.plan;
+    // (the buffers grow on the first call of a size only)
+    if (serves) {
+        for (size_t i = 0; i < host.segments.size(); ++i) {
+            Segment& segment = host.segments[i];
+            const uint64_t sequence = i / kv_heads;
+            segment.length = uint32_t(lengths[sequence]);
+            // (moving cuts: a segment's pieces lie one behind the other in the list, its last piece ends where its last tile does)
+            if (tiles[sequence] != cache.tiles[sequence]) host.pieces[segment.first_piece + segment.pieces - 1].end = tiles[sequence] * kTileKeys;
+        }
+        cache.tiles = tiles;
+        const size_t bytes = plan.piece_offset + host.pieces.size() * sizeof(Piece);   // segments | pieces, as upload_tables lays them out
+        auto* stage = static_cast<uint8_t*>(cache.staging);
+        std::memcpy(stage + plan.segment_offset, host.segments.data(), host.segments.size() * sizeof(Segment));
+        std::memcpy(stage + plan.piece_offset, host.pieces.data(), host.pieces.size() * sizeof(Piece));
+        SDB_CHECK(cudaMemcpyAsync(static_cast<uint8_t*>(cache.tables), stage, bytes, cudaMemcpyHostToDevice, d.stream));
+    } else {
+        cache.states.clear();   // (not a valid list until the new one is in place)
+        build_tables(checked, contexts, lengths.data(), sequences, heads, kv_heads, uint32_t(d.sms) * kWarps, host, d.fixed_cuts);
+        plan = DecodePlan{};
+        fill_plan(d, host, plan, sequences, heads, kv_heads);
+        ensure(d, cache.staging, cache.staging_bytes, plan.table_bytes, true);
+        ensure(d, cache.tables, cache.tables_bytes, plan.table_bytes);
+        upload_tables(d, host, plan, cache.tables, cache.staging);
+        cache.states = checked; cache.contexts.assign(contexts, contexts + sequences); cache.tiles = tiles; cache.built = tiles;
+        cache.heads = heads; cache.kv_heads = kv_heads; cache.fixed = d.fixed_cuts;
+    }
     ensure(d, d.partial, d.partial_bytes, size_t(plan.pieces) * kPartialFloats * 4);
     plan.partial = static_cast<float*>(d.partial);
     plan.status = status_word(d);
-    upload_tables(d, host, plan, d.tables, d.pinned);
     // the new rows, appended by one launch over the work list's segments (plane bases and lengths)
-    launch_kv_append(d, reinterpret_cast<const Segment*>(static_cast<uint8_t*>(d.tables) + plan.segment_offset), host.segments.size(),
+    launch_kv_append(d, reinterpret_cast<const Segment*>(static_cast<uint8_t*>(cache.tables) + plan.segment_offset), host.segments.size(),
                      reinterpret_cast<const float*>(work + k_at), reinterpret_cast<const float*>(work + v_at));
     SDB_CHECK(cudaGetLastError());
     run_plan(d, plan, scale, work, reinterpret_cast<float*>(work + out_at));

@@ -168,6 +168,45 @@ def test_attention_batch_from_host_buffers(gpu):
         gpu.release(b)
 
 
+def test_batch_steps_reuse_the_work_list_until_a_sequence_enters_a_new_tile(gpu):
+    # a run of decode steps: the entry keeps the step before's work list while no sequence crosses into a new 16-key tile and builds a
+    # new one when one does (positions 15 -> 16, 31 -> 32 ...); another batch, another entry of the handle and a changed batch in
+    # between must not leave a stale list behind. Every step is held to the oracle and to the rows the codec writes.
+    rng = np.random.default_rng(702)
+    heads, kv_heads = 16, 2
+    contexts = [96, 2048, 512]
+    bases = [12, 1000, 29]
+    states_np = [q8_state(rng, c, kv_heads, filled=b) for c, b in zip(contexts, bases)]
+    states = [gpu.upload(s) for s in states_np]
+    other_np = q8_state(rng, 64, kv_heads, filled=40)
+    other, q_dev, out_dev = gpu.upload(other_np), gpu.buffer(heads * 256 * 2), gpu.buffer(heads * 256 * 4)
+
+    def step(order):
+        n = len(order)
+        q = queries_f16(rng, n, heads, 256)
+        k, v = (rng.normal(0, 1, (n, kv_heads, 256)).astype(np.float32) for _ in range(2))
+        out = np.empty((n, heads, 256), np.float32)
+        gpu.attention_batch([states[i] for i in order], [contexts[i] for i in order], [bases[i] for i in order], heads, kv_heads, 1 / 16, q, k, v, out)
+        for j, i in enumerate(order):
+            oracle.kv_write(states_np[i], contexts[i], kv_heads, bases[i], k[j:j + 1], v[j:j + 1])
+            want = oracle.gqa_decode_q8(states_np[i], contexts[i], bases[i] + 1, heads, kv_heads, q[j], 1 / 16, f64=True)
+            ok, worst = close(out[j], want)
+            assert ok, (i, bases[i], worst)
+            bases[i] += 1
+
+    for _ in range(7):           # positions 12..18, 1000..1006, 29..35: two tile crossings on the way
+        step([0, 1, 2])
+    step([2, 0])                 # a different batch
+    gpu.qsa_decode([other], [64], [41], heads, kv_heads, 1 / 16, q_dev.pointer, out_dev.pointer)   # another entry of the handle, not waited for
+    for _ in range(3):
+        step([0, 1, 2])
+    for i in range(3):
+        assert np.array_equal(gpu.read(states[i], np.uint8, states_np[i].shape), states_np[i]), "every appended row, bit for bit"
+    assert gpu.decode_status() == 0
+    for b in states + [other, q_dev, out_dev]:
+        gpu.release(b)
+
+
 def test_a_refused_batch_step_leaves_the_states_untouched(gpu):
     # every check runs before the new rows are written: too many heads a group, and one state listed twice
     from straydog_b200.backend import StraydogError
