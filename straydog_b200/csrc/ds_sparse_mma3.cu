@@ -623,13 +623,15 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mma3_kernel(
     }
     cluster_arrive(); cluster_wait();   // (nobody leaves while its partial may still be read)
     if (gather.world > 1) {
-        // The gathered form's hand-over, by the last CTA of the grid to finish: every thread's peer stores are ordered before its
-        // CTA's arrival, the arrivals before the counters this rank raises on every GPU (release, system scope); then the same
-        // thread waits, bounded to a second, until every rank has raised this GPU's counters to `step`: work queued behind this
-        // kernel sees the whole gathered buffer. A rank that never arrives ends the wait with status 4 instead of hanging the GPU.
-        __threadfence_system();
+        // The gathered form's hand-over, by the last CTA of the grid to finish: a CTA's peer stores are ordered before its arrival
+        // (the barrier orders every thread's stores before thread 0's system-scope fence, which is cumulative: one fence a CTA, not
+        // one a thread, each of which would wait on seven links), the arrivals before the counters this rank raises on every GPU
+        // (release, system scope); then the same thread waits, bounded to a second, until every rank has raised this GPU's counters
+        // to `step`: work queued behind this kernel sees the whole gathered buffer. A rank that never arrives ends the wait with
+        // status 4 instead of hanging the GPU.
         asm volatile("bar.sync 3, %0;" ::"n"(kComputeThreads) : "memory");
         if (threadIdx.x == 0) {
+            __threadfence_system();
             const unsigned total = gridDim.x * gridDim.y * gridDim.z;
             if (atomicInc(gather.arrivals, total - 1) == total - 1) {   // (wraps to zero: ready for the next call)
                 __threadfence_system();
