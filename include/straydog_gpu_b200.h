@@ -126,6 +126,13 @@ int sd_op_index_select(void* handle, const float* q, const float* keys, const fl
                        uint64_t groups, uint64_t heads, uint64_t dim, float scale, uint64_t rope_dims, const int32_t* positions,
                        const float* frequencies, float* scores, uint64_t k, int32_t* out, const int32_t* candidates, uint64_t blocks,
                        uint64_t block);
+/* gpu/straydog_gpu.h:422. sd_op_index_select for one row whose head weights are projected first: weights = W . x, W [heads][proj_cols]
+   row-major of kind 0 (F32), 1 (F16) or 30 (BF16), summed in the reference GEMV's order (bit-equal weights); `weights` receives them. The
+   reference's quantised GGML kinds are refused ("unsupported Straydog GPU matrix format"): its GEMV family is outside this library. */
+int sd_op_index_select_proj(void* handle, const void* proj_weights, int proj_kind, uint64_t proj_cols, const float* x, const float* q,
+                            const float* keys, float* weights, const int32_t* visible, uint64_t groups, uint64_t heads, uint64_t dim,
+                            float scale, uint64_t rope_dims, const int32_t* positions, const float* frequencies, float* scores, uint64_t k,
+                            int32_t* out, const int32_t* candidates, uint64_t blocks, uint64_t block);
 /* gpu/straydog_gpu.h:409 */
 int sd_op_top_k(void* handle, const float* scores, uint64_t rows, uint64_t groups, uint64_t k, int32_t* out);
 /* gpu/straydog_gpu.h:459 */

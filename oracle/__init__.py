@@ -43,6 +43,7 @@ _sig("orc_index_block_tops", [_p, _p, _u64, _u64, _u64, _p])
 _sig("orc_qsa_index_select", [_p, _u64, _p, _u64, _u64, _p, _u64, _u64, _u64, _p])
 _sig("orc_qsa_normalize_rows", [_p, _u64, _u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _p, _p, _u64, _p])
 _sig("orc_qsa_normalize_chunk", [_p, _p, _p, _p, _p, _u64, _u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _u64, _p])
+_sig("orc_index_proj", [_p, _i32, _u64, _u64, _p, _i32, _p])
 _sig("orc_top_k", [_p, _u64, _u64, _u64, _p])
 _sig("orc_to_bf16", [_p, _u64, _p])
 _sig("orc_threads", [], _i32)
@@ -250,6 +251,16 @@ def qsa_normalize_chunk(qgate, key, value, iq, ik, position, heads, kv_heads, qn
     norms = [np.ascontiguousarray(n, np.float32) for n in (qnorm, knorm, iqnorm, pool_norm)]
     _lib.orc_qsa_normalize_chunk(_ptr(qgate), _ptr(key), _ptr(value), _ptr(iq), _ptr(ik), count, position, heads, kv_heads, *[_ptr(n) for n in norms],
                                  _ptr(packed), _ptr(state), context, _ptr(index_state))
+
+
+def index_proj(w, kind, x, units=True):
+    """The head weights sd_op_index_select_proj projects: w [heads, cols] (kind 0: float32; 1 / 30: uint16 F16 / BF16 bits), x [cols] F32.
+    units: the 16-byte unit path (aligned operands, a width of whole units), else the element path."""
+    w, x = np.ascontiguousarray(w), np.ascontiguousarray(x, np.float32)
+    assert w.dtype == (np.float32 if kind == 0 else np.uint16)
+    out = np.empty(w.shape[0], np.float32)
+    _lib.orc_index_proj(_ptr(w), kind, w.shape[0], w.shape[1], _ptr(x), int(units), _ptr(out))
+    return out
 
 
 def top_k(scores, k):

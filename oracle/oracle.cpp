@@ -526,6 +526,51 @@ void orc_index_scores(const float* q, const void* keys, int keys_bf16, const flo
         }
 }
 
+// The projection of sd_op_index_select_proj (gpu/kernels.cpp:5620-5667): out[h] = W[h] . x, W [rows][cols] of kind 0 (F32), 1 (F16) or 30
+// (BF16), in the order the reference's GEMV sums a matrix of so few rows (gpu/gemv.hpp:24-36: 32 lanes a row; gpu/gemv_common.hpp:42-86,
+// 784-812): lane l takes the units l, l + 32, ... (4 F32 values: a chain from the last inwards; 8 halves: a chain from the first), adds them
+// in order, and the lanes meet in a butterfly (xor 16 .. 1). `units` = 0: the element path of gpu/gemv_common.hpp:814-836 (a matrix or an
+// input off 16-byte alignment, or a width that is no whole number of units): lane l takes the columns l, l + 32, ... in one chain.
+void orc_index_proj(const void* w, int kind, uint64_t rows, uint64_t cols, const float* x, int units, float* out) {
+    auto at = [&](uint64_t row, uint64_t col) -> float {
+        if (kind == 0) return static_cast<const float*>(w)[row * cols + col];
+        const uint16_t bits = static_cast<const uint16_t*>(w)[row * cols + col];
+        if (kind == 1) return f16_to_f32(bits);
+        uint32_t wide = uint32_t(bits) << 16;
+        float value;
+        std::memcpy(&value, &wide, 4);
+        return value;
+    };
+    for (uint64_t row = 0; row < rows; ++row) {
+        float lanes[32];
+        for (uint64_t lane = 0; lane < 32; ++lane) {
+            float sum = 0.0f;
+            if (!units) {
+                for (uint64_t col = lane; col < cols; col += 32) sum = std::fmaf(at(row, col), x[col], sum);
+            } else if (kind == 0) {
+                for (uint64_t unit = lane; unit < cols / 4; unit += 32) {
+                    const uint64_t c = unit * 4;
+                    sum += std::fmaf(at(row, c), x[c], std::fmaf(at(row, c + 1), x[c + 1], std::fmaf(at(row, c + 2), x[c + 2], at(row, c + 3) * x[c + 3])));
+                }
+            } else {
+                for (uint64_t unit = lane; unit < cols / 8; unit += 32) {
+                    const uint64_t c = unit * 8;
+                    float dot = at(row, c) * x[c];
+                    for (uint64_t i = 1; i < 8; ++i) dot = std::fmaf(at(row, c + i), x[c + i], dot);
+                    sum += dot;
+                }
+            }
+            lanes[lane] = sum;
+        }
+        for (uint64_t offset = 16; offset; offset /= 2) {
+            float next[32];
+            for (uint64_t lane = 0; lane < 32; ++lane) next[lane] = lanes[lane] + lanes[lane ^ offset];
+            std::memcpy(lanes, next, sizeof(lanes));
+        }
+        out[row] = lanes[0];
+    }
+}
+
 // gpu/ops.hpp:1952-1966 (op_index_block_tops_kernel): a block's highest score, +inf for the block of the row's last visible group.
 void orc_index_block_tops(const float* scores, const int32_t* visible, uint64_t rows, uint64_t groups, uint64_t block, float* tops) {
     const uint64_t count = (groups + block - 1) / block;

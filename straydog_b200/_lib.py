@@ -54,6 +54,7 @@ SIGNATURES = {
     "sd_op_index_scores": ([p, p, p, p, p, u64, u64, u64, u64, f32, p], i32),
     "sd_op_index_candidates": ([p, p, p, u64, u64, u64, u64, p, p, u64], i32),
     "sd_op_index_select": ([p, p, p, p, p, u64, u64, u64, u64, f32, u64, p, p, p, u64, p, p, u64, u64], i32),
+    "sd_op_index_select_proj": ([p, p, i32, u64, p, p, p, p, p, u64, u64, u64, f32, u64, p, p, p, u64, p, p, u64, u64], i32),
     "sd_op_top_k": ([p, p, u64, u64, u64, p], i32),
     "sd_op_to_bf16": ([p, p, u64, p], i32),
     "sdx_adopt": ([i32, p], p),

@@ -382,6 +382,14 @@ class Backend:
         self._c(self.lib.sd_op_index_select(self.handle, q, keys, weights, visible, rows, groups, heads, dim, scale, rope_dims, positions,
                                             frequencies, scores, k, out, c_ptr, blocks, block))
 
+    def index_select_proj(self, proj_weights, proj_kind, proj_cols, x, q, keys, weights, visible, groups, heads, dim, scale, rope, scores, k, out,
+                          candidates=None):
+        """sd_op_index_select_proj: one row; weights = W . x first (W of kind 0 F32, 1 F16, 30 BF16). rope and candidates as index_select."""
+        rope_dims, positions, frequencies = rope
+        c_ptr, blocks, block = candidates if candidates else (None, 0, 0)
+        self._c(self.lib.sd_op_index_select_proj(self.handle, proj_weights, proj_kind, proj_cols, x, q, keys, weights, visible, groups, heads, dim,
+                                                 scale, rope_dims, positions, frequencies, scores, k, out, c_ptr, blocks, block))
+
     def top_k(self, scores, rows, groups, k, out):
         self._c(self.lib.sd_op_top_k(self.handle, scores, rows, groups, k, out))
 

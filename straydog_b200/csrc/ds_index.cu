@@ -3,7 +3,8 @@
 //   sd_op_compress          gpu/straydog_gpu.h:407, gpu/ops.hpp:1679-1695, entry gpu/kernels.cpp:5478-5485
 //   sd_op_index_scores      gpu/straydog_gpu.h:408, gpu/ops.hpp:1697-1745, entry gpu/kernels.cpp:5487-5499
 //   sd_op_index_candidates  gpu/straydog_gpu.h:410-414, gpu/ops.hpp:1942-1966, entry gpu/kernels.cpp:5546-5566
-//   sd_op_index_select      gpu/straydog_gpu.h:415-419, gpu/ops.hpp:1978-2300, entry gpu/kernels.cpp:5568-5667
+//   sd_op_index_select      gpu/straydog_gpu.h:415-419, gpu/ops.hpp:1978-2300, entry gpu/kernels.cpp:5568-5618
+//   sd_op_index_select_proj gpu/straydog_gpu.h:422, entry gpu/kernels.cpp:5620-5667 (plain weight kinds)
 // The contract is bit-exact: a score is scale * sum over heads in order of relu(q_h . key) * weight_h, each dot one chain of fused
 // multiply-adds over the columns in order, each term one rounded product, the terms added in head order; sd_op_index_select gives
 // the scores and indices that sd_op_rope, sd_op_index_scores and sd_op_top_k give one after the other
@@ -52,6 +53,49 @@ __global__ void __launch_bounds__(256) compress_kernel(const float* __restrict__
         acc = fmaf(w, v[r * dim], acc);   // (what the reference's `acc += w * kv` compiles to)
     }
     out[index] = __fdiv_rn(acc, sum);
+}
+
+// The projection in front of sd_op_index_select_proj: weights[h] = W[h] . x for the (<= 64) index heads, W a row-major matrix of the
+// reference's plain kinds (0: F32, 1: F16, 30: BF16). The sum's order is the reference GEMV's for such a matrix (gpu/gemv_common.hpp:42-86,
+// 784-812 with the lanes gpu/gemv.hpp:24-36 gives a matrix of so few rows: a warp a row): lane l takes the units l, l + 32, ... (a unit
+// = 4 F32 or 8 half values), a unit's dot is one chain (F32: from the last value inwards; halves: from the first), the lane adds
+// its units in order, the lanes' sums meet in a butterfly (xor 16, 8, 4, 2, 1). Rows or inputs that are not 16-byte aligned take
+// the reference's element path (gpu/gemv_common.hpp:814-836): lane l takes the columns l, l + 32, ... in one chain.
+__device__ __forceinline__ float proj_half(uint32_t bits, int kind) {
+    return kind == 1 ? __half2float(__ushort_as_half(uint16_t(bits))) : __uint_as_float(bits << 16);
+}
+__global__ void __launch_bounds__(256) index_proj_kernel(const uint8_t* __restrict__ w, int kind, size_t row_bytes, size_t rows, size_t cols,
+                                                         const float* __restrict__ x, bool units_path, float* __restrict__ out) {
+    const size_t row = size_t(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    const unsigned lane = threadIdx.x % 32;
+    if (row >= rows) return;
+    const uint8_t* data = w + row * row_bytes;
+    float sum = 0.0f;
+    if (units_path && kind == 0) {
+        for (size_t unit = lane; unit < cols / 4; unit += 32) {
+            const float4 m = reinterpret_cast<const float4*>(data)[unit], a = reinterpret_cast<const float4*>(x)[unit];
+            sum = __fadd_rn(sum, fmaf(m.x, a.x, fmaf(m.y, a.y, fmaf(m.z, a.z, __fmul_rn(m.w, a.w)))));
+        }
+    } else if (units_path) {
+        for (size_t unit = lane; unit < cols / 8; unit += 32) {
+            const uint4 q = reinterpret_cast<const uint4*>(data)[unit];
+            const float4 a = reinterpret_cast<const float4*>(x)[2 * unit], b = reinterpret_cast<const float4*>(x)[2 * unit + 1];
+            float dot = __fmul_rn(proj_half(q.x & 0xffffu, kind), a.x);
+            dot = fmaf(proj_half(q.x >> 16, kind), a.y, dot); dot = fmaf(proj_half(q.y & 0xffffu, kind), a.z, dot);
+            dot = fmaf(proj_half(q.y >> 16, kind), a.w, dot); dot = fmaf(proj_half(q.z & 0xffffu, kind), b.x, dot);
+            dot = fmaf(proj_half(q.z >> 16, kind), b.y, dot); dot = fmaf(proj_half(q.w & 0xffffu, kind), b.z, dot);
+            dot = fmaf(proj_half(q.w >> 16, kind), b.w, dot);
+            sum = __fadd_rn(sum, dot);
+        }
+    } else {
+        for (size_t col = lane; col < cols; col += 32) {
+            const float m = kind == 0 ? reinterpret_cast<const float*>(data)[col] : proj_half(reinterpret_cast<const uint16_t*>(data)[col], kind);
+            sum = fmaf(m, x[col], sum);
+        }
+    }
+    #pragma unroll
+    for (unsigned offset = 16; offset; offset /= 2) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, offset));
+    if (lane == 0) out[row] = sum;
 }
 
 constexpr int kIndexGroups = 64, kIndexCols = 32, kIndexHeads = 64, kIndexThreads = 256, kIndexStride = 68;   // (68 floats: 16-byte aligned rows)
@@ -251,6 +295,34 @@ int sd_op_index_select(void* handle, const float* q, const float* keys, const fl
     }
     launch_index_scores(value, q_used, keys, weights, visible, size_t(rows), size_t(groups), size_t(heads), size_t(dim), scale, scores, candidates, size_t(blocks), size_t(block ? block : 1));
     launch_top_k(value, scores, size_t(rows), size_t(scored), size_t(k), out, candidates, size_t(blocks), size_t(block ? block : 1));
+    SDB_OP_END
+}
+
+// gpu/straydog_gpu.h:422, entry gpu/kernels.cpp:5620-5667: sd_op_index_select for one row whose head weights are first projected from the
+// row's input, weights = W . x (written to `weights`), W [heads][proj_cols] of a plain kind: 0 (F32), 1 (F16), 30 (BF16). The reference
+// also takes its quantised GGML kinds there; those belong to its GEMV family and are refused here by name.
+int sd_op_index_select_proj(void* handle, const void* proj_weights, int proj_kind, uint64_t proj_cols, const float* x, const float* q,
+                            const float* keys, float* weights, const int32_t* visible, uint64_t groups, uint64_t heads, uint64_t dim,
+                            float scale, uint64_t rope_dims, const int32_t* positions, const float* frequencies, float* scores, uint64_t k,
+                            int32_t* out, const int32_t* candidates, uint64_t blocks, uint64_t block) {
+    SDB_OP_BEGIN
+    if (!proj_weights || !proj_cols || proj_cols > 8192 || !groups || groups > (uint64_t(1) << 31) || !heads || heads > uint64_t(kIndexHeads) ||
+        !dim || !k || k > (uint64_t(1) << 31) || rope_dims % 2 || rope_dims > dim || rope_dims > 128)
+        throw std::runtime_error("invalid Straydog index shape");
+    if (proj_kind != 0 && proj_kind != 1 && proj_kind != 30) throw std::runtime_error("unsupported Straydog GPU matrix format");
+    const size_t row_bytes = size_t(proj_cols) * (proj_kind == 0 ? 4 : 2), unit = proj_kind == 0 ? 4 : 8;
+    span(value, proj_weights, checked_product({heads, row_bytes}), "a weight matrix");
+    span(value, x, checked_product({proj_cols, 4}), "a linear input");
+    span(value, weights, checked_product({heads, 4}), "index weights");
+    const bool units_path = proj_cols % unit == 0 && reinterpret_cast<uintptr_t>(proj_weights) % 16 == 0 && row_bytes % 16 == 0 &&
+                            reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    index_proj_kernel<<<unsigned((heads + 7) / 8), 256, 0, value.stream>>>(static_cast<const uint8_t*>(proj_weights), proj_kind, row_bytes,
+                                                                            size_t(heads), size_t(proj_cols), x, units_path, weights);
+    ++value.launches;
+    SDB_CHECK(cudaGetLastError());
+    if (sd_op_index_select(handle, q, keys, weights, visible, 1, groups, heads, dim, scale, rope_dims, positions, frequencies, scores, k, out,
+                           candidates, blocks, block))
+        throw std::runtime_error(last_error);
     SDB_OP_END
 }
 

@@ -188,6 +188,26 @@ def index_case(rows, groups, heads=32, dim=128, rope_dims=64, spread=3, seed=0):
                 dim=dim, rope_dims=rope_dims, scale=float(np.float32(1.0) / (np.sqrt(np.float32(dim)) * np.sqrt(np.float32(heads)))))
 
 
+# (weight kind, columns, heads, groups, bytes the input is pushed off 16-byte alignment): F32, F16 and BF16 matrices whose rows a warp sums in
+# 16-byte units, a width that is no whole number of units and an input off alignment (both take the element path)
+INDEX_PROJ_CASES = [(30, 4096, 64, 4096, 0), (30, 2560, 32, 1000, 0), (0, 2560, 32, 4096, 0), (1, 4096, 64, 1000, 0), (30, 2052, 32, 600, 0),
+                    (0, 514, 32, 600, 0), (1, 1024, 32, 600, 4)]
+
+
+def index_proj_case(kind, cols, heads, groups, seed=0):
+    """sd_op_index_select_proj's inputs: index_case of one row plus the projection W [heads][cols] (kind 0: F32; 1: F16 bits; 30: BF16 bits, both
+    as uint16) and its input x [cols]; the head weights are what the call computes."""
+    c = index_case(1, groups, heads=heads, seed=seed + 100)
+    rng = np.random.default_rng([kind, cols, heads, groups, seed])
+    w = rng.uniform(-1, 1, (heads, cols)).astype(np.float32)
+    if kind == 1:
+        w = w.astype(np.float16).view(np.uint16)
+    elif kind == 30:
+        w = bf16_round(w)[0]
+    c.update(proj=np.ascontiguousarray(w), proj_kind=kind, proj_cols=cols, x=rng.uniform(-1, 1, cols).astype(np.float32))
+    return c
+
+
 def compress_case(groups=37, ratio=4, dim=128, seed=5):
     rng = np.random.default_rng(seed)
     return dict(kv=rng.uniform(-1, 1, (groups * ratio, dim)).astype(np.float32), gate=rng.uniform(-4, 4, (groups * ratio, dim)).astype(np.float32),

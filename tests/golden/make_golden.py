@@ -2,6 +2,7 @@
 built from the reference's unmodified sources by oracle/Makefile.ref) through its C ABI on a B200.
 
     python tests/golden/make_golden.py          # on a machine with a GPU and oracle/_ref built
+    python tests/golden/make_golden.py --proj   # reference_b200_proj.npz alone: sd_op_index_select_proj over plain weight kinds
 
 Inputs are rebuilt from seeds by straydog_b200.synthetic (the fixtures hold outputs only, plus the few
 state rows a call writes), so the fixtures stay small. The tests compare the CPU oracle and this
@@ -27,6 +28,32 @@ SPARSE_CASES = [(1, 32), (4, 32)]
 LATENT_CASES = [(11, 2, 16, 576, 1024, 256)]
 DSPARK_CASES = [(1, 0, 0), (5, 37, 149), (3, 128, 389)]
 TOPK_GROUPS = [511, 512, 513, 600, 4096, 30000]
+
+
+def proj_main():
+    """sd_op_index_select_proj of the reference's library for synthetic.INDEX_PROJ_CASES: the projected head weights, the scores and the
+    chosen indices (k = 512) of one row each."""
+    gpu = Backend(0, 2 << 30, library=_lib.load(REF, reference_abi_only=True))
+    out = {}
+    for kind, cols, heads, groups, off in synthetic.INDEX_PROJ_CASES:
+        c = synthetic.index_proj_case(kind, cols, heads, groups)
+        bufs = {name: gpu.upload(c[name]) for name in ("q", "keys", "visible", "positions", "frequencies", "proj")}
+        x = gpu.buffer(cols * 4 + 16)
+        gpu.write_buffer(x, off, c["x"])
+        weights, scores, picked = gpu.buffer(heads * 4), gpu.buffer(groups * 4), gpu.buffer(512 * 4)
+        gpu.index_select_proj(bufs["proj"].pointer, kind, cols, x.pointer + off, bufs["q"].pointer, bufs["keys"].pointer, weights.pointer,
+                              bufs["visible"].pointer, groups, heads, c["dim"], c["scale"],
+                              (c["rope_dims"], bufs["positions"].pointer, bufs["frequencies"].pointer), scores.pointer, 512, picked.pointer)
+        key = f"proj_{kind}_{cols}_{heads}_{groups}_{off}"
+        out[key + "_weights"] = gpu.read(weights, np.float32, (heads,))
+        out[key + "_scores"] = gpu.read(scores, np.float32, (groups,))
+        out[key + "_top"] = gpu.read(picked, np.int32, (512,))
+        for b in list(bufs.values()) + [x, weights, scores, picked]:
+            gpu.release(b)
+    gpu.close()
+    target = os.environ.get("GOLDEN_OUT", os.path.join(HERE, "reference_b200_proj.npz"))
+    np.savez_compressed(target, **out)
+    print(f"wrote {target}: {len(out)} arrays, {os.path.getsize(target)} bytes")
 
 
 def main():
@@ -148,4 +175,4 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    proj_main() if "--proj" in sys.argv else main()

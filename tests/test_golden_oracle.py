@@ -104,3 +104,16 @@ def test_the_indexer():
     assert worst(oracle.compress(c["kv"], c["gate"], c["ratio"]), GOLDEN["compress"]) <= 1e-6
     r = index_case(3, 1)
     assert worst(oracle.rope(r["q"], r["positions"], r["frequencies"]), GOLDEN["rope"]) <= 1e-6
+
+
+def test_the_projection_of_index_select_proj():
+    # the head weights sd_op_index_select_proj projects (the reference GEMV's order of summation), bit for bit the reference library's
+    # on a B200; then the scores and indices from them as in test_the_indexer
+    from straydog_b200.synthetic import INDEX_PROJ_CASES, index_proj_case
+    golden = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_b200_proj.npz"))
+    for kind, cols, heads, groups, off in INDEX_PROJ_CASES:
+        c = index_proj_case(kind, cols, heads, groups)
+        key = f"proj_{kind}_{cols}_{heads}_{groups}_{off}"
+        got = oracle.index_proj(c["proj"], kind, c["x"], units=(cols % (4 if kind == 0 else 8) == 0 and off == 0))
+        assert np.array_equal(got.view(np.uint32), golden[key + "_weights"].view(np.uint32)), key
+        assert np.array_equal(oracle.top_k(golden[key + "_scores"][None], 512)[0], golden[key + "_top"]), key

@@ -1,4 +1,4 @@
-"""The indexer's entries (sd_op_rope, sd_op_index_scores, sd_op_top_k, sd_op_index_select, sd_op_index_candidates, sd_op_compress) in the
+"""The indexer's entries (sd_op_rope, sd_op_index_scores, sd_op_top_k, sd_op_index_select, sd_op_index_select_proj, sd_op_index_candidates, sd_op_compress) in the
 manner of the reference's own tests (crates/straydog-engine/tests/fused_gpu.rs:391-431 and :477-545): the fused call gives the separate
 calls' scores and indices bit for bit and leaves q as it was; the two-level pick is the top k over every group with the groups outside
 the candidate blocks at -inf; and each against the reference library's own outputs and the CPU oracle."""
@@ -9,7 +9,7 @@ import pytest
 
 import oracle
 from straydog_b200.backend import StraydogError
-from util import INDEX_CASES, TWO_LEVEL_CASES, compress_case, index_case
+from util import INDEX_CASES, INDEX_PROJ_CASES, TWO_LEVEL_CASES, compress_case, index_case, index_proj_case
 
 pytestmark = pytest.mark.gpu
 GOLDEN = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_b200.npz"))
@@ -164,6 +164,54 @@ def test_compress_and_rope_against_the_reference_library_and_the_oracle(gpu):
     gpu.rope(x.pointer, 3, r["heads"], r["dim"], r["rope_dims"], at.pointer, fr.pointer, inverse=True)
     assert np.abs(gpu.read(x, np.float32, r["q"].shape) - r["q"]).max() <= 1e-6
     for b in (kv, gate, out, x, at, fr):
+        gpu.release(b)
+
+
+@pytest.mark.parametrize("kind,cols,heads,groups,off", INDEX_PROJ_CASES)
+def test_index_select_proj_equals_the_reference_librarys(gpu, kind, cols, heads, groups, off):
+    # sd_op_index_select_proj (gpu/kernels.cpp:5620-5667): the head weights projected from the row's input in the reference GEMV's order, then
+    # sd_op_index_select; weights, scores and indices bit for bit those the reference's own library gave on a B200 (tests/golden/make_golden.py --proj)
+    golden = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_b200_proj.npz"))
+    c = index_proj_case(kind, cols, heads, groups)
+    bufs = {name: gpu.upload(c[name]) for name in ("q", "keys", "visible", "positions", "frequencies", "proj")}
+    x = gpu.buffer(cols * 4 + 16)
+    gpu.write_buffer(x, off, c["x"])
+    weights, scores, picked = gpu.buffer(heads * 4), gpu.buffer(groups * 4), gpu.buffer(512 * 4)
+    gpu.index_select_proj(bufs["proj"].pointer, kind, cols, x.pointer + off, bufs["q"].pointer, bufs["keys"].pointer, weights.pointer,
+                          bufs["visible"].pointer, groups, heads, c["dim"], c["scale"],
+                          (c["rope_dims"], bufs["positions"].pointer, bufs["frequencies"].pointer), scores.pointer, 512, picked.pointer)
+    key = f"proj_{kind}_{cols}_{heads}_{groups}_{off}"
+    got_weights = gpu.read(weights, np.float32, (heads,))
+    assert np.array_equal(bits(got_weights), bits(golden[key + "_weights"]))
+    assert np.array_equal(bits(gpu.read(scores, np.float32, (groups,))), bits(golden[key + "_scores"]))
+    assert np.array_equal(gpu.read(picked, np.int32, (512,)), golden[key + "_top"])
+    # the same call as sd_op_index_select over the projected weights
+    scores_2, picked_2 = gpu.buffer(groups * 4), gpu.buffer(512 * 4)
+    gpu.index_select(bufs["q"].pointer, bufs["keys"].pointer, weights.pointer, bufs["visible"].pointer, 1, groups, heads, c["dim"], c["scale"],
+                     (c["rope_dims"], bufs["positions"].pointer, bufs["frequencies"].pointer), scores_2.pointer, 512, picked_2.pointer)
+    assert np.array_equal(gpu.read(picked_2, np.int32, (512,)), golden[key + "_top"])
+    for b in list(bufs.values()) + [x, weights, scores, picked, scores_2, picked_2]:
+        gpu.release(b)
+
+
+def test_a_quantised_projection_kind_is_refused_by_name(gpu):
+    c = index_proj_case(30, 256, 32, 600)
+    bufs = {name: gpu.upload(c[name]) for name in ("q", "keys", "visible", "positions", "frequencies", "proj", "x")}
+    weights, scores, picked = gpu.buffer(32 * 4), gpu.buffer(600 * 4), gpu.buffer(512 * 4)
+
+    def call(kind=30, cols=256):
+        gpu.index_select_proj(bufs["proj"].pointer, kind, cols, bufs["x"].pointer, bufs["q"].pointer, bufs["keys"].pointer, weights.pointer,
+                              bufs["visible"].pointer, 600, 32, c["dim"], c["scale"], (c["rope_dims"], bufs["positions"].pointer, bufs["frequencies"].pointer),
+                              scores.pointer, 512, picked.pointer)
+    for kind in (8, 12, 13, 42):   # GGML's quantised kinds: the reference's GEMV family, not this library's
+        with pytest.raises(StraydogError, match="unsupported Straydog GPU matrix format"):
+            call(kind=kind)
+    with pytest.raises(StraydogError, match="invalid Straydog index shape"):
+        call(cols=8200)
+    with pytest.raises(StraydogError, match="outside"):
+        call(cols=512)      # a matrix and an input the buffers do not hold
+    call()
+    for b in list(bufs.values()) + [weights, scores, picked]:
         gpu.release(b)
 
 
