@@ -8,7 +8,8 @@
 // F64 error-bound test (crates/straydog-engine/tests/attention_gpu.rs); top-k by its rule
 // (tests/fused_gpu.rs top_k_reference); the latent sparse attention by
 // tests/ds_state_bf16_gpu.rs shapes. Golden fixtures produced by the reference's own GPU library
-// (tests/golden/) pin the restatement where a GPU run of the reference was available.
+// (tests/golden/) pin the restatement where a GPU run of the reference was available: its sd_* entries directly, and Qwen's front,
+// indexer and selection-list decode through sd_qsa_sequence over selection matrices (tests/golden/make_golden.py --qsa).
 //
 // Build: g++ -O3 -march=native -fopenmp -shared -fPIC (see oracle/build.py). -ffast-math is never used.
 #include <algorithm>

@@ -208,6 +208,46 @@ def index_proj_case(kind, cols, heads, groups, seed=0):
     return c
 
 
+# (context, position, steps, seed): a prompt's first chunk (every position listed); a decode step that completes a block with 751 blocks to
+# choose from; a chunk of five tokens across a block's end with the choice running; a decode step in the middle of a block
+QSA_SEQUENCE_CASES = [(256, 0, 7, 1), (4096, 3003, 1, 2), (4096, 3001, 5, 3), (8192, 5001, 1, 4)]
+QSA_HIDDEN, QSA_HEADS, QSA_KV_HEADS = 2560, 24, 2
+# a projection's row r reads input column (r * a + b) % 2560 (weight 1, the rest of the row 0): the reference's own layer call
+# (sd_qsa_sequence) then projects exactly, whatever order its GEMV sums in, and everything behind the projections is its kernels' arithmetic
+QSA_SELECTORS = dict(qgate=(12288, 7, 3), key=(512, 11, 5), value=(512, 13, 17), iq=(512, 17, 29), ik=(128, 19, 31))
+
+
+def qsa_selection_matrix(name):
+    rows, a, b = QSA_SELECTORS[name]
+    w = np.zeros((rows, QSA_HIDDEN), np.float32)
+    w[np.arange(rows), (np.arange(rows) * a + b) % QSA_HIDDEN] = 1.0
+    return w
+
+
+def qsa_output_matrix():
+    """[2560][6144]: output i = attended value i (the first ten heads' 256 columns each)."""
+    w = np.zeros((QSA_HIDDEN, QSA_HEADS * 256), np.float32)
+    w[np.arange(QSA_HIDDEN), np.arange(QSA_HIDDEN)] = 1.0
+    return w
+
+
+def qsa_sequence_case(context, position, steps, seed):
+    """The inputs of one sd_qsa_sequence call over selection matrices: the layer input x [steps][2560], the four norm vectors, the K/V state
+    and the indexer state as the positions before `position` left them (seeded), and the five projections the selection matrices give."""
+    rng = np.random.default_rng([context, position, steps, seed])
+    pool = context // 4 + 1
+    c = dict(context=context, position=position, steps=steps, pool=pool, x=rng.normal(0, 1, (steps, QSA_HIDDEN)).astype(np.float32))
+    c["norms"] = [rng.normal(1, 0.1, n).astype(np.float32) for n in (256, 256, 128, 128)]
+    c["state"] = q8_state(rng, context, QSA_KV_HEADS, filled=position)
+    index_state = np.zeros((pool + 16) * 128, np.float32)
+    index_state[:pool * 128].reshape(128, pool)[:, :position // 4] = rng.normal(0, 1, (128, position // 4)).astype(np.float32)
+    index_state[pool * 128:] = rng.normal(0, 1, 16 * 128).astype(np.float32)
+    c["index_state"] = index_state
+    for name, (rows, a, b) in QSA_SELECTORS.items():
+        c[name] = np.ascontiguousarray(c["x"][:, (np.arange(rows) * a + b) % QSA_HIDDEN])
+    return c
+
+
 def compress_case(groups=37, ratio=4, dim=128, seed=5):
     rng = np.random.default_rng(seed)
     return dict(kv=rng.uniform(-1, 1, (groups * ratio, dim)).astype(np.float32), gate=rng.uniform(-4, 4, (groups * ratio, dim)).astype(np.float32),

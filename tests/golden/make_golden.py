@@ -3,6 +3,7 @@ built from the reference's unmodified sources by oracle/Makefile.ref) through it
 
     python tests/golden/make_golden.py          # on a machine with a GPU and oracle/_ref built
     python tests/golden/make_golden.py --proj   # reference_b200_proj.npz alone: sd_op_index_select_proj over plain weight kinds
+    python tests/golden/make_golden.py --qsa    # reference_b200_qsa.npz alone: sd_qsa_sequence (a whole Qwen attention layer) over selection matrices
 
 Inputs are rebuilt from seeds by straydog_b200.synthetic (the fixtures hold outputs only, plus the few
 state rows a call writes), so the fixtures stay small. The tests compare the CPU oracle and this
@@ -52,6 +53,53 @@ def proj_main():
             gpu.release(b)
     gpu.close()
     target = os.environ.get("GOLDEN_OUT", os.path.join(HERE, "reference_b200_proj.npz"))
+    np.savez_compressed(target, **out)
+    print(f"wrote {target}: {len(out)} arrays, {os.path.getsize(target)} bytes")
+
+
+def qsa_main():
+    """sd_qsa_sequence of the reference's library (gpu/sparse_attention.hpp:441-512: projections, normalisation, pooling, block scores, block
+    choice, K/V write, selection attention, gate, output projection) for synthetic.QSA_SEQUENCE_CASES. The six weight matrices are F32
+    selection matrices (a 1 a row), so the projections are exact copies of input columns and the output is the first ten heads' gated
+    attention: what the fixture holds is the reference's kernels' arithmetic behind the projections: the K/V rows the call wrote, the indexer
+    state's new columns and its ring, the block scores of the rows (where the choice ran) and the output."""
+    import ctypes as C
+    lib = _lib.load(REF, reference_abi_only=True)
+    lib.sd_qsa_sequence.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64,
+                                    C.c_uint64, C.c_void_p, C.c_void_p]
+    lib.sd_qsa_sequence.restype = C.c_int
+    gpu = Backend(0, 6 << 30, library=lib)
+    gpu.kv_format(272)
+    matrices = [gpu.upload(synthetic.qsa_selection_matrix(name)) for name in ("qgate", "key", "value", "iq", "ik")] + [gpu.upload(synthetic.qsa_output_matrix())]
+    out = {}
+    for context, position, steps, seed in synthetic.QSA_SEQUENCE_CASES:
+        c = synthetic.qsa_sequence_case(context, position, steps, seed)
+        norms = [gpu.upload(n) for n in c["norms"]]
+        state = gpu.allocate(c["state"].nbytes)
+        gpu.write(state, c["state"])
+        index, scratch = gpu.upload(c["index_state"]), gpu.buffer(256 * c["pool"] * 4)
+        pointers = (C.c_void_p * 10)(*[b.pointer for b in matrices + norms])
+        kinds = (C.c_int * 10)(*([0] * 10))
+        result = np.empty((steps, synthetic.QSA_HIDDEN), np.float32)
+        gpu._c(lib.sd_qsa_sequence(gpu.handle, pointers, kinds, state.pointer, index.pointer, scratch.pointer, context, position, steps,
+                                   c["x"].ctypes.data_as(C.c_void_p), result.ctypes.data_as(C.c_void_p)))
+        key = f"qsa_{context}_{position}_{steps}_{seed}"
+        after = gpu.download(state, np.empty_like(c["state"])).reshape(4, context, 272)
+        out[key + "_rows"] = after[:, position:position + steps].copy()
+        untouched = np.ones(context, bool)
+        untouched[position:position + steps] = False
+        assert np.array_equal(after[:, untouched], c["state"].reshape(4, context, 272)[:, untouched])
+        index_after = gpu.read(index, np.float32, c["index_state"].shape)
+        first, last = position // 4, (position + steps) // 4
+        out[key + "_blocks"] = index_after[:c["pool"] * 128].reshape(128, c["pool"])[:, first:last].copy()
+        out[key + "_ring"] = index_after[c["pool"] * 128:].copy()
+        if (position + steps) // 4 > 512:   # the block choice ran: the rows' block scores (a row's first (its position + 1) / 4 entries count)
+            out[key + "_scores"] = gpu.read(scratch, np.float32, (steps, c["pool"]))[:, :(position + steps) // 4].copy()
+        out[key + "_out"] = result
+        for b in norms + [state, index, scratch]:
+            gpu.release(b)
+    gpu.close()
+    target = os.environ.get("GOLDEN_OUT", os.path.join(HERE, "reference_b200_qsa.npz"))
     np.savez_compressed(target, **out)
     print(f"wrote {target}: {len(out)} arrays, {os.path.getsize(target)} bytes")
 
@@ -175,4 +223,4 @@ def main():
 
 
 if __name__ == "__main__":
-    proj_main() if "--proj" in sys.argv else main()
+    proj_main() if "--proj" in sys.argv else qsa_main() if "--qsa" in sys.argv else main()

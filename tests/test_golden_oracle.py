@@ -117,3 +117,45 @@ def test_the_projection_of_index_select_proj():
         got = oracle.index_proj(c["proj"], kind, c["x"], units=(cols % (4 if kind == 0 else 8) == 0 and off == 0))
         assert np.array_equal(got.view(np.uint32), golden[key + "_weights"].view(np.uint32)), key
         assert np.array_equal(oracle.top_k(golden[key + "_scores"][None], 512)[0], golden[key + "_top"]), key
+
+
+def test_the_qwen_layer_behind_its_projections():
+    # tests/golden/reference_b200_qsa.npz: what the reference's sd_qsa_sequence left behind over selection matrices (make_golden.py --qsa).
+    # The oracle's restatement of the front and of the indexer against it: the value rows and the ring bit for bit; the key rows and the
+    # pooled blocks through the host's powf / cosf / sinf (a last place of theirs moves a rotated value by position * 6e-8); the lists the
+    # rule gives over the reference's block scores equal the oracle's
+    from straydog_b200.synthetic import QSA_SEQUENCE_CASES, qsa_sequence_case
+    golden = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_b200_qsa.npz"))
+    for context, position, steps, seed in QSA_SEQUENCE_CASES:
+        c = qsa_sequence_case(context, position, steps, seed)
+        key = f"qsa_{context}_{position}_{steps}_{seed}"
+        selected, row_floats = 2052, 24 * 256 + 2 * 512
+        packed = np.zeros(steps * (row_floats + selected + 1), np.float32)
+        state, index_state, iq = c["state"].view(np.uint8).ravel().copy(), c["index_state"].copy(), c["iq"].copy()
+        oracle.qsa_normalize_chunk(c["qgate"], c["key"], c["value"], iq, c["ik"], position, 24, 2, *c["norms"], packed, state, context, index_state)
+        rows, want = state.reshape(4, context, 272)[:, position:position + steps], golden[key + "_rows"]
+        assert np.array_equal(rows[2:], want[2:]), "value rows"
+        mine = oracle.q8_decode_rows(np.ascontiguousarray(rows[:2]).reshape(-1, 272))
+        theirs = oracle.q8_decode_rows(np.ascontiguousarray(want[:2]).reshape(-1, 272))
+        assert np.abs(mine - theirs).max() < 0.06, "key rows: a quantisation step apart at most"
+        pool = c["pool"]
+        assert np.array_equal(index_state[pool * 128:].view(np.uint32), golden[key + "_ring"].view(np.uint32))
+        blocks = index_state[:pool * 128].reshape(128, pool)[:, position // 4:(position + steps) // 4]
+        assert blocks.shape == golden[key + "_blocks"].shape and (not blocks.size or np.abs(blocks - golden[key + "_blocks"]).max() < 5e-3)
+        if key + "_scores" in golden:
+            # the oracle's choice over the reference's own blocks (so that the scores are the same numbers): its lists are the rule's over the
+            # reference's scores
+            index_ref = c["index_state"].copy()
+            index_ref[:pool * 128].reshape(128, pool)[:, position // 4:(position + steps) // 4] = golden[key + "_blocks"]
+            queries_ref = iq.reshape(steps, 512)
+            lists = oracle.qsa_index_select(queries_ref, index_ref[:pool * 128].reshape(128, pool), position, steps, selected, row_floats, packed.copy())
+            start = steps * row_floats
+            for t in range(steps):
+                complete = (position + t + 1) // 4
+                scores = golden[key + "_scores"][t, :complete].astype(np.float64)
+                kept = np.sort(np.argsort(-scores, kind="stable")[:512])
+                listed = np.concatenate([(kept[:, None] * 4 + np.arange(4)).ravel(), np.arange(complete * 4, position + t + 1)])
+                count = int(lists[start + steps * selected + t])
+                got = lists[start + t * selected:start + t * selected + count]
+                # (the oracle's index queries went through the host's cosf: a block at the 512th score may change places with its neighbour)
+                assert count == len(listed) and len(set(got.astype(np.int64)) ^ set(listed)) <= 16, t

@@ -1,6 +1,6 @@
 """The oracle's restatement of qsa_normalize_rows (gpu/qsa_decode.hpp:86-111, gpu/sparse_attention.hpp:2-6, 55-71) against an
-independent numpy statement of the same rule in float64. Parity unpinned: the reference's library reaches this kernel only inside
-sd_qsa_sequence, which needs a layer's weights."""
+independent numpy statement of the same rule in float64. (The pin to the reference's own library: tests/test_golden_oracle.py and
+tests/test_gpu_qsa_layer.py, over what sd_qsa_sequence leaves behind when its weight matrices are selection matrices.)"""
 import numpy as np
 import pytest
 
