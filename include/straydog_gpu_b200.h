@@ -165,7 +165,8 @@ int sdx_kv_decode_rows(void* handle, const void* rows, uint64_t count, float* ou
 /* Ragged batch of one-token decodes: sequence s attends rows 0..lengths[s]-1 of states[s] (a Q8_0
    state of contexts[s] positions, 2 * kv_heads planes). states/contexts/lengths are HOST arrays;
    q ([sequences][heads][256] FP16) and out ([sequences][heads][256] F32) are device pointers.
-   heads / kv_heads <= 8. */
+   heads / kv_heads <= 8, or an even number up to 16 (the reference's own 24 / 2 among them: a K/V head's rows are then streamed
+   once for each half of its query heads). */
 int sdx_qsa_decode(void* handle, const void* const* states, const uint64_t* contexts, const uint64_t* lengths,
                    uint64_t sequences, uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out);
 /* The same in two steps: the plan holds the batch's work list on the device, so that a run is

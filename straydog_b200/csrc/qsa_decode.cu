@@ -3,7 +3,8 @@
 // What it replaces in the reference: qsa_decode_parts + qsa_decode_merge
 // (gpu/sparse_attention_compute.hpp:41-170) behind qsa_attention / qsa_attention_rows (:609-647),
 // generalised from "24 query / 2 KV heads, <= 2052 selected keys of one sequence" to any group of
-// <= 8 query heads per KV head, dense causal key ranges and many sequences in one launch.
+// <= 8 query heads per KV head (an even group of up to 16, the reference's own 12 among them, as two halves that stream
+// the K/V head's rows once each), dense causal key ranges and many sequences in one launch.
 //
 // Design (one persistent CTA per SM, 8 independent warps):
 //   * The batch's (sequence, KV head) segments are laid end to end as a sequence of 16-key tiles and
@@ -44,7 +45,7 @@ struct DecodeArgs {
     const __half* q;
     float* partial;
     uint32_t virtual_warps, ctas;
-    uint32_t group;               // query heads per KV head (<= 8)
+    uint32_t group;               // query heads a segment (<= 8)
     float scale_log2;             // softmax scale * log2(e)
     int* status;                  // set to 1 when a bounded wait gave up
 };
@@ -324,27 +325,33 @@ static void chunk_sizes(uint64_t tiles, std::vector<uint32_t>& out) {
     if (tiles) out.push_back(uint32_t(tiles));
 }
 
+// Segments a (sequence, K/V head): 1 for a group of up to eight query heads, 2 for a larger one (even, up to 16).
+static uint64_t group_parts(uint64_t heads, uint64_t kv_heads) { return heads / kv_heads > 8 ? 2 : 1; }
+
 static void build_tables(const std::vector<const uint8_t*>& states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
                          uint64_t heads, uint64_t kv_heads, uint32_t warps_available, HostTables& out, bool fixed_cuts = true) {
-    const uint64_t group = heads / kv_heads;
+    // A warp holds eight query heads: a larger (even) group is two segments a (sequence, K/V head), half the group's heads each.
+    const uint64_t group = heads / kv_heads, parts = group_parts(heads, kv_heads), part_heads = group / parts;
     uint64_t total_tiles = 0;
-    for (uint64_t s = 0; s < sequences; ++s) total_tiles += (lengths[s] + kTileKeys - 1) / kTileKeys * kv_heads;
+    for (uint64_t s = 0; s < sequences; ++s) total_tiles += (lengths[s] + kTileKeys - 1) / kTileKeys * kv_heads * parts;
     constexpr uint64_t min_tiles = 8;
     out.segments.clear(); out.pieces.clear(); out.warp_piece.clear();
-    auto segment_of = [&](uint64_t s, uint64_t kv) {
+    auto segment_of = [&](uint64_t s, uint64_t unit) {   // unit = kv * parts + part
+        const uint64_t kv = unit / parts, part = unit % parts;
         Segment segment{};
         segment.keys = states[s] + kv * contexts[s] * kv_row_q8;
         segment.values = states[s] + (kv_heads + kv) * contexts[s] * kv_row_q8;
-        segment.q_offset = uint32_t((s * heads + kv * group) * 256);
+        segment.q_offset = uint32_t((s * heads + kv * group + part * part_heads) * 256);
         segment.length = uint32_t(lengths[s]);
         return segment;
     };
+    const uint64_t units = kv_heads * parts;
     if (fixed_cuts) {
         struct Chunk { uint32_t segment, begin, end, slot, tiles; };
         std::vector<Chunk> chunks;
         std::vector<uint32_t> sizes;
         for (uint64_t s = 0; s < sequences; ++s)
-            for (uint64_t kv = 0; kv < kv_heads; ++kv) {
+            for (uint64_t kv = 0; kv < units; ++kv) {
                 Segment segment = segment_of(s, kv);
                 segment.first_piece = uint32_t(chunks.size());
                 chunk_sizes((lengths[s] + kTileKeys - 1) / kTileKeys, sizes);
@@ -386,7 +393,7 @@ static void build_tables(const std::vector<const uint8_t*>& states, const uint64
     out.warp_piece.push_back(0);
     uint64_t room = per_warp;   // tiles the current warp may still take
     for (uint64_t s = 0; s < sequences; ++s)
-        for (uint64_t kv = 0; kv < kv_heads; ++kv) {
+        for (uint64_t kv = 0; kv < units; ++kv) {
             Segment segment = segment_of(s, kv);
             segment.first_piece = uint32_t(out.pieces.size());
             uint64_t key = 0;
@@ -410,7 +417,7 @@ static void validate_batch(Device& d, const void* const* states, const uint64_t*
                            uint64_t heads, uint64_t kv_heads, std::vector<const uint8_t*>& checked, uint64_t& kv_bytes) {
     if (d.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's decode attention reads Q8_0 K/V rows only");
     if (!states || !contexts || !lengths || !sequences || sequences > 65535 || !heads || !kv_heads || heads % kv_heads ||
-        heads / kv_heads > 8 || heads > 1024)
+        heads / kv_heads > 16 || (heads / kv_heads > 8 && heads / kv_heads % 2) || heads > 1024)
         throw std::runtime_error("invalid Straydog attention dimensions");
     checked.resize(sequences);
     kv_bytes = 0;
@@ -446,7 +453,7 @@ static void fill_plan(Device& d, const HostTables& host, DecodePlan& plan, uint6
     plan.pieces = uint32_t(host.pieces.size());
     plan.virtual_warps = uint32_t(host.warp_piece.size() - 1);
     plan.ctas = std::min<uint32_t>(uint32_t(d.sms), plan.virtual_warps);
-    plan.group = uint32_t(heads / kv_heads);
+    plan.group = uint32_t(heads / kv_heads / group_parts(heads, kv_heads));   // query heads a segment
     plan.sequences = sequences; plan.heads = heads; plan.kv_heads = kv_heads;
     plan.table_bytes = table_bytes_of(host);
 }
@@ -557,6 +564,8 @@ void attention_batch(Device& d, void* const* states, const uint64_t* contexts, c
         if (!contexts[s] || bases[s] >= contexts[s]) throw std::runtime_error("invalid Straydog attention dimensions");
         lengths[s] = bases[s] + 1;
     }
+    // (the append runs over the work list's segments, one a (sequence, K/V head): groups of up to eight query heads here)
+    if (kv_heads && heads / kv_heads > 8) throw std::runtime_error("invalid Straydog attention dimensions");
     std::vector<const uint8_t*> checked;
     uint64_t kv_bytes = 0;
     validate_batch(d, reinterpret_cast<const void* const*>(states), contexts, lengths.data(), sequences, heads, kv_heads, checked, kv_bytes);

@@ -145,6 +145,31 @@ def test_large_scales_and_peaked_softmax(gpu):
     assert ok, worst
 
 
+@pytest.mark.parametrize("heads,kv_heads,plan", [(24, 2, False), (24, 2, True), (12, 1, False), (16, 1, False), (20, 2, True)])
+def test_groups_of_more_than_eight_heads_are_taken_as_two_halves(gpu, heads, kv_heads, plan):
+    # the reference's own layer has 24 query heads on 2 K/V heads (gpu/core.hpp:384-392; 12 on 1 for a GPU's half): an even group of up
+    # to 16 is two segments a (sequence, K/V head), each streaming the head's rows for half of its query heads
+    rng = np.random.default_rng(heads * 7 + kv_heads)
+    lengths, contexts = [1, 17, 700, 2049], [16, 64, 1024, 4096]
+    states = [q8_state(rng, c, kv_heads) for c in contexts]
+    q = queries_f16(rng, len(lengths), heads, 256)
+    got = run_decode(gpu, states, contexts, lengths, heads, kv_heads, q, plan=plan)
+    want = expect_decode(states, contexts, lengths, heads, kv_heads, q)
+    ok, worst = close(got, want)
+    assert ok and worst < 1e-3, worst   # (a sequence of a few keys has nothing to average the FP16 rounding of its weights over)
+
+
+def test_an_odd_group_of_more_than_eight_heads_is_refused(gpu):
+    from straydog_b200.backend import StraydogError
+    state, q, out = gpu.buffer(2 * 64 * 272), gpu.buffer(18 * 256 * 2), gpu.buffer(18 * 256 * 4)
+    for heads in (9, 11, 17, 18):
+        with pytest.raises(StraydogError, match="invalid Straydog attention dimensions"):
+            gpu.qsa_decode([state], [64], [10], heads, 1, 1 / 16, q.pointer, out.pointer)
+    gpu.qsa_decode([state], [64], [10], 10, 1, 1 / 16, q.pointer, out.pointer)
+    for b in (state, q, out):
+        gpu.release(b)
+
+
 def test_attention_batch_from_host_buffers(gpu):
     rng = np.random.default_rng(700)
     n, heads, kv_heads = 5, 16, 2
@@ -234,7 +259,7 @@ def test_invalid_batches_are_refused(gpu):
     for args in [([state], [64], [65], 16, 2),      # length past the context
                  ([state], [64], [0], 16, 2),       # no key
                  ([state], [128], [10], 16, 2),     # state smaller than the context says
-                 ([state], [64], [10], 18, 1),      # more than 8 heads a group
+                 ([state], [64], [10], 18, 1),      # more than 16 heads a group
                  ([state], [64], [10], 16, 3)]:     # heads not a multiple of kv_heads
         with pytest.raises(StraydogError):
             gpu.qsa_decode(args[0], args[1], args[2], args[3], args[4], 1 / 16, q.pointer, out.pointer)

@@ -63,3 +63,27 @@ def test_the_layer_behind_its_projections_equals_the_reference_librarys(gpu, con
     assert ok and worst < (1e-4 if steps == 1 else 1e-3), worst
     for b in list(bufs.values()) + norms + [packed, out]:
         gpu.release(b)
+
+
+def test_the_dense_decode_at_the_reference_layers_heads_equals_its_output(gpu):
+    # sdx_qsa_decode at Qwen's own geometry (24 query / 2 K/V heads: groups of 12, taken as two halves of six) over every position of a
+    # sequence is the layer's decode step while it lists every position (up to 512 blocks): the reference's output for such a step, after
+    # the front has written the token's row; the queries reach the dense kernel as FP16, which is what separates the two
+    context, position, steps, seed = 2048, 1500, 1, 5
+    c = qsa_sequence_case(context, position, steps, seed)
+    key = f"qsa_{context}_{position}_{steps}_{seed}"
+    bufs = {n: gpu.upload(c[n]) for n in ("qgate", "key", "value", "iq", "ik", "state", "index_state")}
+    norms = [gpu.upload(n) for n in c["norms"]]
+    packed = gpu.buffer((HEADS * 256 + KV_HEADS * 512 + SELECTED + 1) * 4)
+    gpu.qsa_normalize_chunk(bufs["qgate"].pointer, bufs["key"].pointer, bufs["value"].pointer, bufs["iq"].pointer, bufs["ik"].pointer, 1, position,
+                            HEADS, KV_HEADS, *[n.pointer for n in norms], packed.pointer, SELECTED, bufs["state"], context, bufs["index_state"].pointer)
+    queries = gpu.read(packed, np.float32, (HEADS * 256,))
+    q16, out = gpu.upload(queries.astype(np.float16)), gpu.buffer(HEADS * 256 * 4)
+    gpu.qsa_decode([bufs["state"]], [context], [position + 1], HEADS, KV_HEADS, 0.0625, q16.pointer, out.pointer)
+    assert gpu.decode_status() == 0
+    gate = c["qgate"].reshape(HEADS, 512)[:, 256:].astype(np.float64)
+    got = (gpu.read(out, np.float32, (HEADS, 256)) / (1 + np.exp(-gate)))[:10].reshape(1, 2560)
+    ok, worst = close(got, GOLDEN[key + "_out"])
+    assert ok and worst < 5e-4, worst
+    for b in list(bufs.values()) + norms + [packed, q16, out]:
+        gpu.release(b)
