@@ -217,7 +217,7 @@ int sdx_trace_read(void* handle, int64_t* out, uint64_t capacity);
 
 /* Causal prompt attention of a chunk: `rows` new tokens at positions first .. first + rows - 1 of a Q8_0 state
    (their K/V rows already written, e.g. by sdx_kv_write) attend positions 0 .. their own. q [rows][heads][256]
-   FP16 and out [rows][heads][256] F32 are device pointers; heads / kv_heads is 1, 2, 4 or 8. The dense causal
+   FP16 and out [rows][heads][256] F32 are device pointers; heads / kv_heads is at most 16 (a group that does not divide 128, like the reference's own 12, leaves some of a block's 128 rows idle). The dense causal
    form of the reference's qsa_flash_launch (gpu/sparse_attention_compute.hpp:589-608). */
 int sdx_qsa_prompt(void* handle, const void* state, uint64_t context, uint64_t first, uint64_t rows, uint64_t heads,
                    uint64_t kv_heads, float scale, const void* q, float* out);

@@ -9,7 +9,8 @@
 // kernel from the raw Q8_0 rows: a CTA streams 272 bytes a row from L2, not the 1024 bytes of two FP16 planes (with the planes
 // prepared in memory by a kernel of their own, this kernel was bound by the L2's bandwidth at about 7 TB/s over all SMs).
 //
-// A CTA owns 128 M-rows: 128 / group consecutive query tokens x the `group` query heads of one K/V head.
+// A CTA owns 128 M-rows: 128 / group consecutive query tokens x the `group` (<= 16) query heads of one K/V head (a group that does not
+// divide 128 leaves the last rows idle: the reference's own 12 heads a K/V head use 120 of them).
 // It walks the causal key range in tiles of 64 keys:
 //   S[128 x 64]  = Q[128 x 256] . (K_hi + K_lo)^T   2 x 16 tcgen05.mma (M 128, N 64, K 16), FP16 in, FP32 in TMEM
 //   O[128 x 256] += P[128 x 64] . (V_hi + V_lo)     2 x 4 tcgen05.mma (M 128, N 256, K 16)
@@ -179,7 +180,8 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
     // columns of Q): the tensor core then reads only K from shared memory. A softmax thread stores its half row.
     if (warp < kSoftmaxWarps) {
         const int rb = warp & 3, half = warp >> 2, m = rb * 32 + lane;
-        const size_t row = r0 + m / a.group, head = kv * a.group + m % a.group;
+        // (a group that does not divide 128, the reference's own 12 among them, leaves the block's last M-rows without a token: zeros)
+        const size_t row = size_t(m) < tokens_per_block * a.group ? r0 + m / a.group : a.rows, head = kv * a.group + m % a.group;
         const uint4* source = reinterpret_cast<const uint4*>(a.q + (row * a.heads + head) * kD + half * 128);
         #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -220,7 +222,7 @@ __global__ void __launch_bounds__(kThreads, 1) qsa_prompt_tc_kernel(const Args a
         // block exchange their row maxima through shared memory, so both take the same decisions and keep their own partial sums.
         const int rb = warp & 3, half = warp >> 2, m = rb * 32 + lane;
         const size_t token = r0 + m / a.group, head = kv * a.group + m % a.group;
-        const bool valid = token < a.rows;
+        const bool valid = token < a.rows && size_t(m) < tokens_per_block * a.group;
         const long long limit = valid ? (long long)(a.first + token) : -1;
         const uint32_t lane_base = uint32_t(rb * 32) << 16;
         float* mine_stat = stats + half * kM + m;
@@ -519,7 +521,7 @@ extern "C" int sdx_qsa_prompt(void* handle, const void* state, uint64_t context,
     if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
     const uint64_t group = kv_heads ? heads / kv_heads : 0;
     if (!context || context > (uint64_t(1) << 24) || !rows || first > context || rows > context - first || !heads || !kv_heads ||
-        heads % kv_heads || (group != 1 && group != 2 && group != 4 && group != 8) || kv_heads > 65535 || !(scale > 0.0f) || !(scale < 1e30f))
+        heads % kv_heads || group > 16 || kv_heads > 65535 || !(scale > 0.0f) || !(scale < 1e30f))
         throw std::runtime_error("invalid Straydog attention dimensions");
     span(value, state, checked_product({context, 2 * kv_heads, kv_row_q8}), "a K/V state");
     span(value, q, checked_product({rows, heads, 256, 2}), "attention queries");

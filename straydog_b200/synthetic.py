@@ -210,8 +210,9 @@ def index_proj_case(kind, cols, heads, groups, seed=0):
 
 # (context, position, steps, seed): a prompt's first chunk (every position listed); a decode step that completes a block with 751 blocks to
 # choose from; a chunk of five tokens across a block's end with the choice running; a decode step in the middle of a block; a decode step that
-# lists every position (375 blocks): the dense decode of 1501 positions
-QSA_SEQUENCE_CASES = [(256, 0, 7, 1), (4096, 3003, 1, 2), (4096, 3001, 5, 3), (8192, 5001, 1, 4), (2048, 1500, 1, 5)]
+# lists every position (375 blocks): the dense decode of 1501 positions; a prompt chunk of 60 tokens after 100 cached (every position listed: the
+# dense causal prompt attention)
+QSA_SEQUENCE_CASES = [(256, 0, 7, 1), (4096, 3003, 1, 2), (4096, 3001, 5, 3), (8192, 5001, 1, 4), (2048, 1500, 1, 5), (1024, 100, 60, 6)]
 QSA_HIDDEN, QSA_HEADS, QSA_KV_HEADS = 2560, 24, 2
 # a projection's row r reads input column (r * a + b) % 2560 (weight 1, the rest of the row 0): the reference's own layer call
 # (sd_qsa_sequence) then projects exactly, whatever order its GEMV sums in, and everything behind the projections is its kernels' arithmetic

@@ -60,7 +60,7 @@ def test_the_layer_behind_its_projections_equals_the_reference_librarys(gpu, con
     # K, V and the weights to FP16 (qsa_flash_mma, gpu/sparse_attention_compute.hpp:416-584; its own figure: 4.8e-4 at worst), this
     # library's selection kernel does not
     ok, worst = close(got, GOLDEN[key + "_out"])
-    assert ok and worst < (1e-4 if steps == 1 else 1e-3), worst
+    assert ok and worst < (1e-4 if steps == 1 else 2e-3), worst
     for b in list(bufs.values()) + norms + [packed, out]:
         gpu.release(b)
 
@@ -85,5 +85,29 @@ def test_the_dense_decode_at_the_reference_layers_heads_equals_its_output(gpu):
     got = (gpu.read(out, np.float32, (HEADS, 256)) / (1 + np.exp(-gate)))[:10].reshape(1, 2560)
     ok, worst = close(got, GOLDEN[key + "_out"])
     assert ok and worst < 5e-4, worst
+    for b in list(bufs.values()) + norms + [packed, q16, out]:
+        gpu.release(b)
+
+
+def test_the_prompt_kernel_at_the_reference_layers_heads_equals_its_output(gpu):
+    # sdx_qsa_prompt (tcgen05) at 24 query / 2 K/V heads (groups of 12: ten tokens a block of 120 rows) over a chunk whose every position is
+    # listed is the layer's prompt attention: the reference's output for the chunk, after the front has written the chunk's rows. Both sides
+    # round on the way (the reference's prompt kernel K, V and the weights to FP16; this one the queries and the weights)
+    context, position, steps, seed = 1024, 100, 60, 6
+    c = qsa_sequence_case(context, position, steps, seed)
+    key = f"qsa_{context}_{position}_{steps}_{seed}"
+    bufs = {n: gpu.upload(c[n]) for n in ("qgate", "key", "value", "iq", "ik", "state", "index_state")}
+    norms = [gpu.upload(n) for n in c["norms"]]
+    packed = gpu.buffer(steps * (HEADS * 256 + KV_HEADS * 512 + SELECTED + 1) * 4)
+    gpu.qsa_normalize_chunk(bufs["qgate"].pointer, bufs["key"].pointer, bufs["value"].pointer, bufs["iq"].pointer, bufs["ik"].pointer, steps, position,
+                            HEADS, KV_HEADS, *[n.pointer for n in norms], packed.pointer, SELECTED, bufs["state"], context, bufs["index_state"].pointer)
+    queries = gpu.read(packed, np.float32, (steps * HEADS * 256,))
+    q16, out = gpu.upload(queries.astype(np.float16)), gpu.buffer(steps * HEADS * 256 * 4)
+    gpu.qsa_prompt(bufs["state"], context, position, steps, HEADS, KV_HEADS, 0.0625, q16.pointer, out.pointer)
+    assert gpu.decode_status() == 0
+    gate = c["qgate"].reshape(steps, HEADS, 512)[:, :, 256:].astype(np.float64)
+    got = (gpu.read(out, np.float32, (steps, HEADS, 256)) / (1 + np.exp(-gate)))[:, :10].reshape(steps, 2560)
+    ok, worst = close(got, GOLDEN[key + "_out"])
+    assert ok and worst < 2e-3, worst
     for b in list(bufs.values()) + norms + [packed, q16, out]:
         gpu.release(b)

@@ -27,7 +27,9 @@ def run_prompt(gpu, state_np, context, first, rows, heads, kv_heads, q, scale=1 
 
 
 @pytest.mark.parametrize("first,rows,heads,kv_heads", [(0, 1, 16, 2), (0, 16, 16, 2), (0, 17, 16, 2), (5, 40, 16, 2), (63, 2, 16, 2), (64, 64, 16, 2),
-                                                       (100, 33, 8, 2), (30, 50, 4, 2), (7, 130, 2, 2), (200, 70, 8, 1), (1000, 300, 16, 2)])
+                                                       (100, 33, 8, 2), (30, 50, 4, 2), (7, 130, 2, 2), (200, 70, 8, 1), (1000, 300, 16, 2),
+                                                       # groups that do not divide a block's 128 rows (the reference's own 24 / 2 and 12 / 1), and one of 16
+                                                       (37, 45, 24, 2), (0, 21, 12, 1), (10, 30, 6, 2), (50, 20, 16, 1), (3, 26, 10, 2), (500, 64, 24, 2)])
 def test_small_chunks_every_row(gpu, first, rows, heads, kv_heads):
     rng = np.random.default_rng(first * 131 + rows)
     context = first + rows + 3
@@ -104,7 +106,7 @@ def test_invalid_chunks_are_refused(gpu):
     state = gpu.buffer(4 * 64 * 272)
     q = gpu.buffer(64 * 16 * 256 * 2)
     out = gpu.buffer(64 * 16 * 256 * 4)
-    for first, rows, heads, kv_heads, scale in [(60, 5, 16, 2, 1 / 16), (0, 0, 16, 2, 1 / 16), (0, 4, 24, 2, 1 / 16), (0, 4, 16, 3, 1 / 16),
+    for first, rows, heads, kv_heads, scale in [(60, 5, 16, 2, 1 / 16), (0, 0, 16, 2, 1 / 16), (0, 4, 34, 2, 1 / 16), (0, 4, 16, 3, 1 / 16),
                                                 (0, 4, 16, 2, 0.0), (0, 4, 16, 2, -1.0), (0, 4, 16, 2, float("nan"))]:
         with pytest.raises(StraydogError):
             gpu.qsa_prompt(state, 64, first, rows, heads, kv_heads, scale, q.pointer, out.pointer)
