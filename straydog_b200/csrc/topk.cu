@@ -5,9 +5,9 @@
 // kept; -0 ties +0; unused slots hold -1. All integer work, bit-exact.
 //
 // Kernel: one block of 1024 threads a row, built around reading the row from memory twice.
-//   read 1   a 2048-bin histogram of the top 11 bits of every live score's sortable key (warp-aggregated shared-memory
-//            atomics, so a row of equal scores costs no more than a row of distinct ones). The bin in which the running
-//            count from the top reaches k is the band: everything above it is kept for sure, everything below is dropped.
+//   read 1   a 2048-bin histogram of the top 11 bits of every live score's sortable key (sixteen private histograms filled by
+//            plain shared-memory atomics and added up). The bin in which the running count from the top reaches k is the
+//            band: everything above it is kept for sure, everything below is dropped.
 //   read 2   in index order: the sure indices go to one shared list, the band's (key, index) pairs to another.
 //   then, in shared memory only: the band's next 11 and last 10 key bits are histogrammed the same way, which gives the k-th
 //            key itself and how many of its equals are wanted; the band's chosen entries are compacted in index order; the
@@ -20,7 +20,7 @@
 namespace sdb {
 namespace topk {
 
-constexpr int kThreads = 1024, kWarps = kThreads / 32, kPerThread = 4;
+constexpr int kThreads = 1024, kWarps = kThreads / 32, kPerThread = 8;
 constexpr uint32_t kBins = 2048, kBandCap = 8192, kKeepCap = 4096;
 constexpr size_t kSmem = (kBins + kKeepCap + 2 * kBandCap + kKeepCap) * 4;   // histogram | sure | band keys | band indices | chosen
 
@@ -110,10 +110,42 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
     // ---- read 1: the top 11 key bits ----
     for (uint32_t i = t; i < kBins; i += kThreads) hist[i] = 0;
     __syncthreads();
-    for (size_t base = 0; base < groups; base += kThreads) {
-        const size_t g = base + t;
-        const uint32_t key = g < groups ? sortable(row[g]) : kDead;
-        count_in(hist, key >> 21, key > kDead);
+    // Rows of up to a million scores: sixteen private histograms (a pair of warps each), two 16-bit counts a word (bins b and b + 1024),
+    // filled by plain shared-memory atomics and added up afterwards. A warp-wide match (one add per distinct bin of a warp) cost three
+    // fifths of the whole kernel; an atomic's worst case, a warp of equal scores, is 32 adds to one word, still a fraction of a match,
+    // and the copies (a word apart in the banks) keep the warps off each other's words. Longer rows keep the matching count.
+    constexpr int kAhead = 8;
+    constexpr uint32_t kCopies = 16, kCopyWords = kBins / 2 + 1;
+    static_assert(kCopies * kCopyWords <= 2 * kBandCap + kKeepCap, "the private histograms fit the lists' area, idle during the first read");
+    if (groups <= (size_t(1) << 20) - 1024) {
+        uint32_t* copies = band_key;   // (band_key, band_index and chosen lie one behind the other)
+        for (uint32_t i = t; i < kCopies * kCopyWords; i += kThreads) copies[i] = 0;
+        __syncthreads();
+        uint32_t* my_copy = copies + (t / 64) * kCopyWords;
+        for (size_t base = 0; base < groups; base += size_t(kThreads) * kAhead) {
+            uint32_t keys[kAhead];
+            #pragma unroll
+            for (int i = 0; i < kAhead; ++i) {
+                const size_t g = base + size_t(i) * kThreads + t;
+                keys[i] = g < groups ? sortable(row[g]) : kDead;
+            }
+            #pragma unroll
+            for (int i = 0; i < kAhead; ++i)
+                if (keys[i] > kDead) atomicAdd(&my_copy[(keys[i] >> 21) & 1023u], keys[i] >> 31 ? 65536u : 1u);
+        }
+        __syncthreads();
+        for (uint32_t bin = t; bin < kBins; bin += kThreads) {
+            uint32_t sum = 0;
+            #pragma unroll
+            for (uint32_t c = 0; c < kCopies; ++c) sum += (copies[c * kCopyWords + (bin & 1023u)] >> (bin >> 10 ? 16 : 0)) & 0xffffu;
+            hist[bin] = sum;
+        }
+    } else {
+        for (size_t base = 0; base < groups; base += kThreads) {
+            const size_t g = base + t;
+            const uint32_t key = g < groups ? sortable(row[g]) : kDead;
+            count_in(hist, key >> 21, key > kDead);
+        }
     }
     __syncthreads();
     const uint32_t wanted = uint32_t(min(k, size_t(0xffffffffu)));
@@ -129,12 +161,19 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
     if (in_shared) {
         // ---- read 2: the sure indices and the band, both in index order ----
         uint32_t sure_count = 0, band_seen = 0;
+        // (the next iteration's scores are asked for before this iteration's scan: the scan's two barriers then cover the load)
+        float ahead[kPerThread];
+        #pragma unroll
+        for (int i = 0; i < kPerThread; ++i) { const size_t g = size_t(t) * kPerThread + i; ahead[i] = g < groups ? row[g] : -INFINITY; }
         for (size_t base = 0; base < groups; base += size_t(kThreads) * kPerThread) {
             const size_t first = base + size_t(t) * kPerThread;
             uint32_t keys[kPerThread], packed = 0;
             #pragma unroll
+            for (int i = 0; i < kPerThread; ++i) keys[i] = first + i < groups ? sortable(ahead[i]) : kDead;
+            #pragma unroll
+            for (int i = 0; i < kPerThread; ++i) { const size_t g = first + size_t(kThreads) * kPerThread + i; ahead[i] = g < groups ? row[g] : -INFINITY; }
+            #pragma unroll
             for (int i = 0; i < kPerThread; ++i) {
-                keys[i] = first + i < groups ? sortable(row[first + i]) : kDead;
                 const uint32_t top = keys[i] >> 21;
                 packed += keys[i] > kDead ? (top > (prefix >> 21) ? 1u : top == (prefix >> 21) ? 0x10000u : 0u) : 0u;
             }
