@@ -366,7 +366,7 @@ def run_index_ops(args, local, gpu):
              "top_k_ms": times["top_k"], "index_select_ms": times["index_select"], "indices_equal_oracle": True,
              "top_k_roofline": {"bound": "hbm", "achieved": rows * groups * 4 / times["top_k"] / 1e6, "peak": peak_hbm, "unit": "GB/s",
                                 "frac": rows * groups * 4 / times["top_k"] / 1e6 / peak_hbm,
-                                "note": "algorithmic bytes = the scores once (8.4 MB: they fit L2, and the kernel reads them twice); a row is one CTA, so 32 rows use 32 SMs"},
+                                "note": "algorithmic bytes = the scores once (8.4 MB: they fit L2, and the kernel reads them twice); a row is a cluster of 4 CTAs (128 SMs), a launch a chain of block and cluster barriers: latency-bound"},
              "peak_source": peak_source}
     if os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libstraydog_ref.so")):
         ref = reference_gpu_backend(1 << 30)

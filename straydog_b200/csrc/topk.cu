@@ -4,7 +4,10 @@
 // row the k highest scores' indices in ascending index order; scores equal to the k-th keep the lowest indices; -inf is never
 // kept; -0 ties +0; unused slots hold -1. All integer work, bit-exact.
 //
-// Kernel: one block of 1024 threads a row, built around reading the row from memory twice.
+// Kernel: blocks of 1024 threads, built around reading the row from memory twice. A row belongs to a thread-block cluster of 1, 2, 4
+// or 8 blocks (as many as keep rows x blocks within the SM count, each block at least 8192 scores): block r takes the r-th
+// contiguous slice of the row, every histogram is the sum of the blocks' histograms read through distributed shared memory, and
+// block r writes its kept indices behind those of the blocks before it, so the list still ascends.
 //   read 1   a 2048-bin histogram of the top 11 bits of every live score's sortable key (sixteen private histograms filled by
 //            plain shared-memory atomics and added up). The bin in which the running count from the top reaches k is the
 //            band: everything above it is kept for sure, everything below is dropped.
@@ -13,7 +16,8 @@
 //            key itself and how many of its equals are wanted; the band's chosen entries are compacted in index order; the
 //            two ascending lists are merged by rank (each entry's place = its own rank + a binary search in the other list).
 // A row whose band (or k) does not fit the shared lists - more than 8192 scores sharing their top 11 bits with the k-th, k over
-// 4096 - takes the general path: the two refinements read the row again, then one ordered pass compacts straight to the output.
+// 4096 - takes the general path in the cluster's first block alone: the two refinements read the row again, then one ordered pass
+// compacts straight to the output.
 #include "common.cuh"
 #include "../../include/straydog_gpu_b200.h"
 
@@ -22,7 +26,7 @@ namespace topk {
 
 constexpr int kThreads = 1024, kWarps = kThreads / 32, kPerThread = 8;
 constexpr uint32_t kBins = 2048, kBandCap = 8192, kKeepCap = 4096;
-constexpr size_t kSmem = (kBins + kKeepCap + 2 * kBandCap + kKeepCap) * 4;   // histogram | sure | band keys | band indices | chosen
+constexpr size_t kSmem = (2 * kBins + kKeepCap + 2 * kBandCap + kKeepCap) * 4;   // two histograms | sure | band keys | band indices | chosen
 
 // Order-preserving map of a score to an unsigned key; the two zeros share a key.
 __device__ __forceinline__ uint32_t sortable(float score) {
@@ -35,7 +39,28 @@ constexpr uint32_t kDead = 0x007fffffu;   // sortable(-inf): nothing at or below
 struct Shared {
     uint32_t warp_totals[kWarps];
     uint32_t found_bin, found_above, found_count, live;
+    uint32_t kept;   // this block's share of the row's list
 };
+
+// The row's cluster. Both barrier halves are executed by every thread of every block of the cluster, the same number of times.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_blocks() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+// the word / the four words at this shared-memory address in block `rank` of the cluster
+__device__ __forceinline__ uint32_t word_of(const uint32_t* local, uint32_t rank) {
+    uint32_t remote, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 words_of(const uint32_t* local, uint32_t rank) {
+    uint32_t remote;
+    uint4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(remote) : "memory");
+    return v;
+}
 
 // Exclusive prefix of `mine` over the block in thread order; `total` = the block's sum.
 __device__ __forceinline__ uint32_t prefix_before(uint32_t mine, Shared& sh, uint32_t& total) {
@@ -70,12 +95,29 @@ __device__ __forceinline__ void count_in(uint32_t* bins, uint32_t bin, bool coun
 
 // From the highest bin down: the bin in which the running count reaches `wanted` (found_bin, the count above it, its own count), and
 // the count of all bins (live). When all bins together hold fewer than `wanted`, found_bin stays at `bins` (no such bin).
-__device__ __forceinline__ void find_band(const uint32_t* hist, uint32_t bins, uint32_t wanted, Shared& sh) {
+// With `blocks` > 1 a bin's count is the sum over the cluster's blocks of their `hist` (every block finds the same band); the
+// caller does not touch this `hist` again before the cluster's next barrier. The sums are made four bins a load (a load from
+// another block's shared memory costs the same for 16 bytes as for 4): the threads' lower half adds the even blocks', the upper
+// half the odd blocks' into `scratch` (2 x bins words of this block), and a thread's bins are the two halves' sum.
+__device__ __forceinline__ void find_band(const uint32_t* hist, uint32_t bins, uint32_t wanted, Shared& sh, uint32_t blocks, uint32_t* scratch) {
     const uint32_t each = (bins + kThreads - 1) / kThreads;   // bins a thread, taken from the top
     uint32_t counts[2] = {0, 0}, sum = 0;
+    if (blocks > 1) {
+        cluster_arrive(); cluster_wait();                     // every block's histogram is complete
+        const uint32_t half = threadIdx.x / (kThreads / 2), four = threadIdx.x % (kThreads / 2);
+        if (four < bins / 4) {
+            uint4 total = make_uint4(0, 0, 0, 0);
+            for (uint32_t r = half; r < blocks; r += 2) {
+                const uint4 theirs = words_of(&hist[4 * four], r);
+                total.x += theirs.x; total.y += theirs.y; total.z += theirs.z; total.w += theirs.w;
+            }
+            *reinterpret_cast<uint4*>(&scratch[half * bins + 4 * four]) = total;
+        }
+        __syncthreads();
+    }
     for (uint32_t i = 0; i < each; ++i) {
         const uint32_t at = threadIdx.x * each + i;
-        counts[i] = at < bins ? hist[bins - 1 - at] : 0u;
+        if (at < bins) counts[i] = blocks == 1 ? hist[bins - 1 - at] : scratch[bins - 1 - at] + scratch[bins + bins - 1 - at];
         sum += counts[i];
     }
     if (threadIdx.x == 0) sh.found_bin = bins;
@@ -95,39 +137,47 @@ __device__ __forceinline__ void find_band(const uint32_t* hist, uint32_t bins, u
 __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict__ scores, size_t groups, size_t k, int32_t* __restrict__ out,
                                                          const int32_t* __restrict__ candidates, size_t blocks, size_t block) {
     extern __shared__ __align__(16) uint32_t dynamic[];
-    uint32_t* hist = dynamic;
-    uint32_t* sure = hist + kBins;              // indices kept for sure, ascending
+    uint32_t* hist_a = dynamic;                 // the histograms of the first read and of the band's last bits
+    uint32_t* hist_b = hist_a + kBins;          // the histogram between them: a block may still be reading the one before in another block
+    uint32_t* sure = hist_b + kBins;            // indices kept for sure, ascending
     uint32_t* band_key = sure + kKeepCap;       // the band in index order
     uint32_t* band_index = band_key + kBandCap;
     uint32_t* chosen = band_index + kBandCap;   // the band's kept indices, ascending
     __shared__ Shared sh;
-    const float* row = scores + size_t(blockIdx.x) * groups;
-    int32_t* mine = out + size_t(blockIdx.x) * k;
+    const uint32_t ranks = cluster_blocks(), rank = cluster_rank();
+    const size_t row_number = blockIdx.x / ranks;
+    const float* row = scores + row_number * groups;
+    int32_t* mine = out + row_number * k;
     const unsigned t = threadIdx.x;
-    const int32_t* mapped = candidates ? candidates + size_t(blockIdx.x) * blocks : nullptr;
+    const int32_t* mapped = candidates ? candidates + row_number * blocks : nullptr;
     const auto group_of = [&](uint32_t place) { return mapped ? int32_t(size_t(mapped[place / block]) * block + place % block) : int32_t(place); };
+    // this block's slice of the row
+    const size_t slice = ((groups + ranks - 1) / ranks + 3) & ~size_t(3);
+    const size_t low = min(groups, size_t(rank) * slice), high = min(groups, low + slice);
 
     // ---- read 1: the top 11 key bits ----
-    for (uint32_t i = t; i < kBins; i += kThreads) hist[i] = 0;
+    for (uint32_t i = t; i < kBins; i += kThreads) hist_a[i] = 0;
     __syncthreads();
-    // Rows of up to a million scores: sixteen private histograms (a pair of warps each), two 16-bit counts a word (bins b and b + 1024),
+    // Slices of up to a million scores: sixteen private histograms (a pair of warps each), two 16-bit counts a word (bins b and b + 1024),
     // filled by plain shared-memory atomics and added up afterwards. A warp-wide match (one add per distinct bin of a warp) cost three
     // fifths of the whole kernel; an atomic's worst case, a warp of equal scores, is 32 adds to one word, still a fraction of a match,
-    // and the copies (a word apart in the banks) keep the warps off each other's words. Longer rows keep the matching count.
-    constexpr int kAhead = 8;
+    // and the copies (a word apart in the banks) keep the warps off each other's words. Longer slices keep the matching count.
+    constexpr int kAhead = 16;
     constexpr uint32_t kCopies = 16, kCopyWords = kBins / 2 + 1;
     static_assert(kCopies * kCopyWords <= 2 * kBandCap + kKeepCap, "the private histograms fit the lists' area, idle during the first read");
-    if (groups <= (size_t(1) << 20) - 1024) {
+    static_assert(2 * kBins <= kKeepCap, "find_band's two halves fit the chosen list's area");
+    if (high - low <= (size_t(1) << 20) - 1024) {
         uint32_t* copies = band_key;   // (band_key, band_index and chosen lie one behind the other)
-        for (uint32_t i = t; i < kCopies * kCopyWords; i += kThreads) copies[i] = 0;
+        static_assert(kCopies * kCopyWords % 4 == 0, "zeroed 16 bytes a store");
+        for (uint32_t i = t; i < kCopies * kCopyWords / 4; i += kThreads) reinterpret_cast<uint4*>(copies)[i] = make_uint4(0, 0, 0, 0);
         __syncthreads();
         uint32_t* my_copy = copies + (t / 64) * kCopyWords;
-        for (size_t base = 0; base < groups; base += size_t(kThreads) * kAhead) {
+        for (size_t base = low; base < high; base += size_t(kThreads) * kAhead) {
             uint32_t keys[kAhead];
             #pragma unroll
             for (int i = 0; i < kAhead; ++i) {
                 const size_t g = base + size_t(i) * kThreads + t;
-                keys[i] = g < groups ? sortable(row[g]) : kDead;
+                keys[i] = g < high ? sortable(row[g]) : kDead;
             }
             #pragma unroll
             for (int i = 0; i < kAhead; ++i)
@@ -138,85 +188,101 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
             uint32_t sum = 0;
             #pragma unroll
             for (uint32_t c = 0; c < kCopies; ++c) sum += (copies[c * kCopyWords + (bin & 1023u)] >> (bin >> 10 ? 16 : 0)) & 0xffffu;
-            hist[bin] = sum;
+            hist_a[bin] = sum;
         }
     } else {
-        for (size_t base = 0; base < groups; base += kThreads) {
+        for (size_t base = low; base < high; base += kThreads) {
             const size_t g = base + t;
-            const uint32_t key = g < groups ? sortable(row[g]) : kDead;
-            count_in(hist, key >> 21, key > kDead);
+            const uint32_t key = g < high ? sortable(row[g]) : kDead;
+            count_in(hist_a, key >> 21, key > kDead);
         }
     }
     __syncthreads();
     const uint32_t wanted = uint32_t(min(k, size_t(0xffffffffu)));
-    find_band(hist, kBins, wanted, sh);
+    find_band(hist_a, kBins, wanted, sh, ranks, chosen);   // (chosen: idle until the band's entries are picked)
     const bool keep_all_live = sh.found_bin == kBins;          // fewer live scores than k: every one of them is kept
     uint32_t prefix = keep_all_live ? 0u : sh.found_bin << 21;  // the k-th key's bits so far
     uint32_t above = keep_all_live ? 0u : sh.found_above;       // scores above the band
-    const uint32_t band_count = keep_all_live ? 0u : sh.found_count;
+    const uint32_t band_count = keep_all_live ? 0u : sh.found_count;   // the band over the whole row
     const bool in_shared = !keep_all_live && band_count <= kBandCap && k <= kKeepCap;
     __syncthreads();
 
     uint32_t threshold = kDead, need = 0;   // kept: key > threshold, and the first `need` (by index) of key == threshold
     if (in_shared) {
-        // ---- read 2: the sure indices and the band, both in index order ----
+        // ---- read 2: the slice's sure indices and its part of the band, both in index order ----
         uint32_t sure_count = 0, band_seen = 0;
+        const uint32_t count = uint32_t(high - low), first_index = uint32_t(low);
+        const float* part = row + low;
+        // a key above band_top is kept for sure; the band's keys are band_low .. band_top (one unsigned compare of key - band_low)
+        const uint32_t band_top = prefix | 0x1fffffu, band_low = max(prefix, kDead + 1), band_width = band_top - band_low;
         // (the next iteration's scores are asked for before this iteration's scan: the scan's two barriers then cover the load)
         float ahead[kPerThread];
-        #pragma unroll
-        for (int i = 0; i < kPerThread; ++i) { const size_t g = size_t(t) * kPerThread + i; ahead[i] = g < groups ? row[g] : -INFINITY; }
-        for (size_t base = 0; base < groups; base += size_t(kThreads) * kPerThread) {
-            const size_t first = base + size_t(t) * kPerThread;
+        const bool whole = (reinterpret_cast<uintptr_t>(part) & 15) == 0;   // a thread's eight scores are two 16-byte loads
+        const auto fetch = [&](uint32_t first, float* v) {
+            if (whole && first + kPerThread <= count) {
+                #pragma unroll
+                for (int i = 0; i < kPerThread; i += 4) {
+                    const float4 x = __ldg(reinterpret_cast<const float4*>(part + first + i));
+                    v[i] = x.x; v[i + 1] = x.y; v[i + 2] = x.z; v[i + 3] = x.w;
+                }
+            } else {
+                #pragma unroll
+                for (int i = 0; i < kPerThread; ++i) v[i] = first + i < count ? part[first + i] : -INFINITY;   // (-inf: neither sure nor band)
+            }
+        };
+        fetch(t * kPerThread, ahead);
+        for (uint32_t base = 0; base < count; base += kThreads * kPerThread) {
+            const uint32_t first = base + t * kPerThread;
             uint32_t keys[kPerThread], packed = 0;
             #pragma unroll
-            for (int i = 0; i < kPerThread; ++i) keys[i] = first + i < groups ? sortable(ahead[i]) : kDead;
+            for (int i = 0; i < kPerThread; ++i) keys[i] = sortable(ahead[i]);
+            fetch(first + kThreads * kPerThread, ahead);
             #pragma unroll
-            for (int i = 0; i < kPerThread; ++i) { const size_t g = first + size_t(kThreads) * kPerThread + i; ahead[i] = g < groups ? row[g] : -INFINITY; }
-            #pragma unroll
-            for (int i = 0; i < kPerThread; ++i) {
-                const uint32_t top = keys[i] >> 21;
-                packed += keys[i] > kDead ? (top > (prefix >> 21) ? 1u : top == (prefix >> 21) ? 0x10000u : 0u) : 0u;
-            }
+            for (int i = 0; i < kPerThread; ++i) packed += (keys[i] > band_top ? 1u : 0u) + (keys[i] - band_low <= band_width ? 0x10000u : 0u);
             uint32_t tile_total;
             const uint32_t before = prefix_before(packed, sh, tile_total);   // (two counts in one scan: neither passes 16 bits)
             uint32_t sure_at = sure_count + (before & 0xffffu), band_at = band_seen + (before >> 16);
             #pragma unroll
             for (int i = 0; i < kPerThread; ++i) {
-                if (keys[i] <= kDead) continue;
-                const uint32_t top = keys[i] >> 21;
-                if (top > (prefix >> 21)) sure[sure_at++] = uint32_t(first + i);
-                else if (top == (prefix >> 21)) { band_key[band_at] = keys[i]; band_index[band_at] = uint32_t(first + i); ++band_at; }
+                if (keys[i] > band_top) sure[sure_at++] = first_index + first + i;
+                else if (keys[i] - band_low <= band_width) { band_key[band_at] = keys[i]; band_index[band_at] = first_index + first + i; ++band_at; }
             }
             sure_count += tile_total & 0xffffu;
             band_seen += tile_total >> 16;
         }
         __syncthreads();
-        // ---- the band's remaining 21 bits, in shared memory ----
+        // ---- the band's remaining 21 bits, in shared memory (band_seen: this block's part of the band) ----
         for (int round = 0; round < 2; ++round) {
             const int shift = round == 0 ? 10 : 0;
             const uint32_t bins = round == 0 ? 2048u : 1024u, decided = round == 0 ? 21u : 10u;
+            uint32_t* hist = round == 0 ? hist_b : hist_a;   // (hist_a: every block has passed the barrier of the round before, so has read it)
             for (uint32_t i = t; i < bins; i += kThreads) hist[i] = 0;
             __syncthreads();
-            for (uint32_t base = 0; base < band_count; base += kThreads) {
-                const uint32_t key = base + t < band_count ? band_key[base + t] : 0u;
-                count_in(hist, (key >> shift) & (bins - 1), base + t < band_count && (key >> decided) == (prefix >> decided));
+            for (uint32_t i = t; i < band_seen; i += kThreads) {   // (a band is a few thousand keys over 2048 bins: plain atomics)
+                const uint32_t key = band_key[i];
+                if ((key >> decided) == (prefix >> decided)) atomicAdd(&hist[(key >> shift) & (bins - 1)], 1u);
             }
             __syncthreads();
-            find_band(hist, bins, wanted - above, sh);
+            find_band(hist, bins, wanted - above, sh, ranks, chosen);
             prefix |= sh.found_bin << shift;
             above += sh.found_above;
             __syncthreads();
         }
         threshold = prefix;
         need = wanted - above;
+        // Of the `need` equals of the k-th key the blocks before this one take theirs first (hist_a holds every block's count of them).
+        for (uint32_t r = 0; r < rank; ++r) {
+            const uint32_t theirs = word_of(&hist_a[threshold & 1023u], r);
+            need -= min(need, theirs);
+        }
         // ---- the band's kept entries, in index order ----
         uint32_t chosen_count = 0, ties_seen = 0;
-        for (uint32_t base = 0; base < band_count; base += kThreads * kPerThread) {
+        for (uint32_t base = 0; base < band_seen; base += kThreads * kPerThread) {
             const uint32_t first = base + t * kPerThread;
             uint32_t keys[kPerThread], ties = 0;
             #pragma unroll
             for (int i = 0; i < kPerThread; ++i) {
-                keys[i] = first + i < band_count ? band_key[first + i] : kDead;
+                keys[i] = first + i < band_seen ? band_key[first + i] : kDead;
                 ties += keys[i] == threshold;
             }
             uint32_t tile_ties;
@@ -238,32 +304,50 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
             ties_seen += tile_ties;
         }
         __syncthreads();
+        // ---- where this block's entries start in the row's list: behind those of the blocks before it ----
+        uint32_t start = 0, total = sure_count + chosen_count;
+        if (ranks > 1) {
+            if (t == 0) sh.kept = sure_count + chosen_count;
+            cluster_arrive(); cluster_wait();
+            total = 0;
+            for (uint32_t r = 0; r < ranks; ++r) {
+                const uint32_t theirs = word_of(&sh.kept, r);
+                start += r < rank ? theirs : 0u;
+                total += theirs;
+            }
+            cluster_arrive();   // (this block has read what it needs of the others; the wait is at the end)
+        }
         // ---- two ascending lists into one: an entry's place is its own rank plus the other list's entries before it ----
         auto before_in = [](const uint32_t* list, uint32_t count, uint32_t index) {
             uint32_t low = 0, high = count;
             while (low < high) { const uint32_t mid = (low + high) / 2; if (list[mid] < index) low = mid + 1; else high = mid; }
             return low;
         };
-        for (uint32_t i = t; i < sure_count; i += kThreads) mine[i + before_in(chosen, chosen_count, sure[i])] = group_of(sure[i]);
-        for (uint32_t i = t; i < chosen_count; i += kThreads) mine[i + before_in(sure, sure_count, chosen[i])] = group_of(chosen[i]);
-        for (size_t i = size_t(sure_count) + chosen_count + t; i < k; i += kThreads) mine[i] = -1;
+        for (uint32_t i = t; i < sure_count; i += kThreads) mine[start + i + before_in(chosen, chosen_count, sure[i])] = group_of(sure[i]);
+        for (uint32_t i = t; i < chosen_count; i += kThreads) mine[start + i + before_in(sure, sure_count, chosen[i])] = group_of(chosen[i]);
+        for (size_t i = size_t(total) + rank * kThreads + t; i < k; i += size_t(ranks) * kThreads) mine[i] = -1;
+        if (ranks > 1) cluster_wait();   // nobody leaves while its shared memory may still be read
         return;
     }
 
-    // ---- the general path: refinements over the row itself, then one ordered pass ----
+    // ---- the general path: the cluster's first block alone; refinements over the row itself, then one ordered pass ----
+    if (rank != 0) {   // (the others meet the first block at the cluster's last barrier: it may still be reading their first histogram)
+        cluster_arrive(); cluster_wait();
+        return;
+    }
     if (!keep_all_live) {
         for (int round = 0; round < 2; ++round) {
             const int shift = round == 0 ? 10 : 0;
             const uint32_t bins = round == 0 ? 2048u : 1024u, decided = round == 0 ? 21u : 10u;
-            for (uint32_t i = t; i < bins; i += kThreads) hist[i] = 0;
+            for (uint32_t i = t; i < bins; i += kThreads) hist_b[i] = 0;   // (hist_a may still be read by the other blocks)
             __syncthreads();
             for (size_t base = 0; base < groups; base += kThreads) {
                 const size_t g = base + t;
                 const uint32_t key = g < groups ? sortable(row[g]) : kDead;
-                count_in(hist, (key >> shift) & (bins - 1), key > kDead && (key >> decided) == (prefix >> decided));
+                count_in(hist_b, (key >> shift) & (bins - 1), key > kDead && (key >> decided) == (prefix >> decided));
             }
             __syncthreads();
-            find_band(hist, bins, wanted - above, sh);
+            find_band(hist_b, bins, wanted - above, sh, 1, nullptr);
             prefix |= sh.found_bin << shift;
             above += sh.found_above;
             __syncthreads();
@@ -301,6 +385,7 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
         ties_seen += tile_ties;
     }
     for (size_t i = written + t; i < k; i += kThreads) mine[i] = -1;
+    if (ranks > 1) { cluster_arrive(); cluster_wait(); }
 }
 
 }  // namespace topk
@@ -312,7 +397,35 @@ void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, si
         SDB_CHECK(cudaFuncSetAttribute(topk::top_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(topk::kSmem)));
         configured[d.ordinal & 63] = true;
     }
-    topk::top_k_kernel<<<unsigned(rows), topk::kThreads, topk::kSmem, d.stream>>>(scores, groups, k, out, candidates, blocks, block);
+    // A row's cluster: as many blocks (1, 2, 4, 8) as keep the launch within one block per SM and a block's slice at 8192 scores or more
+    // (the cluster's five barriers cost a shorter slice more than the split saves it).
+    unsigned ranks = 1;
+    while (ranks < 8 && rows * ranks * 2 <= size_t(d.sms) && groups / (ranks * 2) >= 8192) ranks *= 2;
+    cudaLaunchConfig_t config{};
+    config.blockDim = dim3{unsigned(topk::kThreads), 1, 1};
+    config.dynamicSmemBytes = topk::kSmem;
+    config.stream = d.stream;
+    cudaLaunchAttribute cluster{};
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster; config.numAttrs = 1;
+    // A cluster of this size must fit the device (a 1024-thread block with all its shared memory per SM, the cluster's SMs in one
+    // GPC): asked of the driver once per device and size; a size that does not fit is halved.
+    static int fits[64][4] = {};   // [device][log2 size]: 0 unknown, 1 fits, -1 does not
+    for (;; ranks /= 2) {
+        config.gridDim = dim3{unsigned(rows * ranks), 1, 1};
+        cluster.val.clusterDim.x = ranks;
+        if (ranks == 1) break;
+        int& known = fits[d.ordinal & 63][ranks >= 8 ? 3 : ranks >= 4 ? 2 : 1];
+        if (!known) {
+            int clusters = 0;
+            const cudaError_t asked = cudaOccupancyMaxActiveClusters(&clusters, topk::top_k_kernel, &config);
+            if (asked != cudaSuccess) cudaGetLastError();
+            known = asked == cudaSuccess && clusters > 0 ? 1 : -1;
+        }
+        if (known > 0) break;
+    }
+    SDB_CHECK(cudaLaunchKernelEx(&config, topk::top_k_kernel, scores, groups, k, out, candidates, blocks, block));
     ++d.launches;
     SDB_CHECK(cudaGetLastError());
 }

@@ -36,6 +36,41 @@ def test_top_k_random_scores(gpu, rows, groups, k):
     gpu.release(out)
 
 
+def check(gpu, scores, k):
+    rows, groups = scores.shape
+    dev = gpu.upload(scores)
+    out = gpu.buffer(rows * k * 4)
+    gpu.top_k(dev.pointer, rows, groups, k, out.pointer)
+    got = gpu.read(out, np.int32, (rows, k))
+    gpu.release(dev)
+    gpu.release(out)
+    assert np.array_equal(got, oracle.top_k(scores, k))
+
+
+@pytest.mark.parametrize("rows,groups,k", [(1, 65536, 2048), (4, 65536, 512), (20, 32768, 2048), (20, 16384, 2048), (50, 8192, 100), (3, 16387, 4096)])
+def test_a_row_shared_by_several_blocks(gpu, rows, groups, k):
+    """Few rows: a row's slices go to a cluster of 8, 4 or 2 blocks. The k-th score's equals are spread over the slices."""
+    rng = np.random.default_rng(groups + rows)
+    scores = rng.normal(0, 1, (rows, groups)).astype(np.float32)
+    above = int((scores[0] > 2.0).sum())
+    if above < k:
+        ties = rng.choice(groups, size=min(groups // 4, 3000), replace=False)
+        scores[:, ties] = 2.0
+    check(gpu, scores, k)
+
+
+def test_rows_that_leave_the_shared_lists_in_a_cluster(gpu):
+    """Equal scores everywhere (a band of the whole row), k above the shared lists' room, fewer live scores than k."""
+    check(gpu, np.zeros((2, 65536), np.float32), 1000)
+    rng = np.random.default_rng(5)
+    check(gpu, rng.normal(0, 1, (2, 65536)).astype(np.float32), 5000)
+    sparse = np.full((2, 40000), -np.inf, np.float32)
+    sparse[:, rng.choice(40000, size=100, replace=False)] = rng.normal(0, 1, 100).astype(np.float32)
+    check(gpu, sparse, 3000)
+    few = rng.integers(0, 3, (3, 50000)).astype(np.float32)     # three values: the band is a third of the row
+    check(gpu, few, 2048)
+
+
 def test_rounding_into_bf16_is_to_the_nearest_even(gpu):
     # tests/ds_state_bf16_gpu.rs:50-69
     values = XorShift(0x243F6A8885A308D3).floats_scaled(10_000, 1e3)
