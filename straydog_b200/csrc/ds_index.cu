@@ -172,6 +172,117 @@ __global__ void __launch_bounds__(kIndexThreads) index_scores_kernel(const float
     scores[row * scored + place0 + t] = tile_groups[t] < limit ? __fmul_rn(total, scale) : -INFINITY;
 }
 
+// The same scores for the usual shapes (dim a multiple of 16, keys and queries 16-byte aligned): a CTA of 128 threads scores 128 places of
+// one row against all (<= 64) heads, a thread an 8 x 8 register tile (places 4 tg .. + 3 and 64 + 4 tg .. + 3, heads 4 th .. + 3 and
+// 32 + 4 th .. + 3), so a column costs four 16-byte shared-memory reads for 64 fused multiply-adds where the 4 x 4 tile above pays two for
+// 16. The columns come 16 at a time: a thread fetches its place's 16 key values (32 bytes of BF16: one sector) and half a head's 16 query
+// values into registers while the step before is being multiplied, and sets them down the tiles' columns (lanes on consecutive places:
+// no bank conflict) between two barriers. Order of operations as above.
+namespace wide {
+constexpr int kPlaces = 128, kHeads = 64, kStep = 16, kThreads = 128, kTermStride = kPlaces + 4;
+constexpr size_t kSmem = size_t(kHeads) * kTermStride * 4;   // the terms [head][place]; the tiles [column][place] | [column][head] lie in the same bytes before
+static_assert(kSmem >= size_t(kStep) * (kPlaces + kHeads) * 4, "the tiles fit the terms' area");
+}  // namespace wide
+
+__global__ void __launch_bounds__(wide::kThreads) index_scores_wide_kernel(const float* __restrict__ q, const float* keys, const float* __restrict__ weights,
+                                                                           const int32_t* __restrict__ visible, size_t groups, size_t heads, size_t dim,
+                                                                           float scale, float* __restrict__ scores, const int32_t* __restrict__ candidates,
+                                                                           size_t blocks, size_t block) {
+    using namespace wide;
+    const size_t row = blockIdx.y, scored = candidates ? blocks * block : groups, place0 = size_t(blockIdx.x) * kPlaces;
+    const unsigned t = threadIdx.x, tg = t % 16, th = t / 16;
+    const size_t limit = min(groups, size_t(max(visible[row], 0)));
+    extern __shared__ __align__(16) float wide_tiles[];
+    float* ks = wide_tiles;                      // [column of the step][place]
+    float* qs = wide_tiles + kStep * kPlaces;    // [column of the step][head]
+    // this thread's place (its key row) and its half of a head's query step
+    size_t mine = groups;
+    if (place0 + t < scored) {
+        if (!candidates) mine = place0 + t;
+        else { const int32_t b = candidates[row * blocks + (place0 + t) / block]; mine = b < 0 ? groups : size_t(b) * block + (place0 + t) % block; }
+    }
+    const bool live = mine < limit, bf16 = state_is_bf16(keys);
+    const uint16_t* key_halves = state_halves(keys) + mine * dim;
+    const float* key_floats = keys + mine * dim;
+    const unsigned q_head = t % kHeads, q_half = t / kHeads;
+    const float* q_from = q + (row * heads + q_head) * dim + 8 * q_half;
+    const bool q_live = q_head < heads;
+
+    float key_next[kStep], q_next[8];
+    const auto fetch = [&](size_t d0) {
+        if (!live) {
+            #pragma unroll
+            for (int i = 0; i < kStep; ++i) key_next[i] = 0.0f;
+        } else if (bf16) {
+            #pragma unroll
+            for (int v = 0; v < 2; ++v) {
+                const uint4 x = *reinterpret_cast<const uint4*>(key_halves + d0 + 8 * v);
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+                #pragma unroll
+                for (int i = 0; i < 4; ++i) { key_next[8 * v + 2 * i] = __uint_as_float(w[i] << 16); key_next[8 * v + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+            }
+        } else {
+            #pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const float4 x = *reinterpret_cast<const float4*>(key_floats + d0 + 4 * v);
+                key_next[4 * v] = x.x; key_next[4 * v + 1] = x.y; key_next[4 * v + 2] = x.z; key_next[4 * v + 3] = x.w;
+            }
+        }
+        #pragma unroll
+        for (int v = 0; v < 2; ++v) {
+            const float4 x = q_live ? __ldg(reinterpret_cast<const float4*>(q_from + d0 + 4 * v)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            q_next[4 * v] = x.x; q_next[4 * v + 1] = x.y; q_next[4 * v + 2] = x.z; q_next[4 * v + 3] = x.w;
+        }
+    };
+    const auto set_down = [&]() {
+        #pragma unroll
+        for (int i = 0; i < kStep; ++i) ks[i * kPlaces + t] = key_next[i];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) qs[(8 * q_half + i) * kHeads + q_head] = q_next[i];
+    };
+
+    float acc[8][8];   // [place][head]
+    #pragma unroll
+    for (int i = 0; i < 8; ++i)
+        #pragma unroll
+        for (int h = 0; h < 8; ++h) acc[i][h] = 0.0f;
+    fetch(0);
+    set_down();
+    __syncthreads();
+    for (size_t d0 = 0; d0 < dim; d0 += kStep) {
+        const bool more = d0 + kStep < dim;
+        if (more) fetch(d0 + kStep);
+        #pragma unroll
+        for (int c = 0; c < kStep; ++c) {
+            const float4 ka = *reinterpret_cast<const float4*>(ks + c * kPlaces + 4 * tg), kb = *reinterpret_cast<const float4*>(ks + c * kPlaces + 64 + 4 * tg);
+            const float4 qa = *reinterpret_cast<const float4*>(qs + c * kHeads + 4 * th), qb = *reinterpret_cast<const float4*>(qs + c * kHeads + 32 + 4 * th);
+            const float k[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w}, qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            #pragma unroll
+            for (int i = 0; i < 8; ++i)
+                #pragma unroll
+                for (int h = 0; h < 8; ++h) acc[i][h] = fmaf(qv[h], k[i], acc[i][h]);
+        }
+        __syncthreads();
+        if (more) { set_down(); __syncthreads(); }
+    }
+    float* terms = wide_tiles;   // [head][place]
+    #pragma unroll
+    for (int h = 0; h < 8; ++h) {
+        const size_t head = (h < 4 ? 0 : 32) + 4 * th + (h & 3);
+        const float w = head < heads ? weights[row * heads + head] : 0.0f;
+        #pragma unroll
+        for (int half = 0; half < 2; ++half)
+            *reinterpret_cast<float4*>(terms + head * kTermStride + 64 * half + 4 * tg) =
+                make_float4(__fmul_rn(fmaxf(acc[4 * half][h], 0.0f), w), __fmul_rn(fmaxf(acc[4 * half + 1][h], 0.0f), w),
+                            __fmul_rn(fmaxf(acc[4 * half + 2][h], 0.0f), w), __fmul_rn(fmaxf(acc[4 * half + 3][h], 0.0f), w));
+    }
+    __syncthreads();
+    if (place0 + t >= scored) return;
+    float total = 0.0f;
+    for (size_t h = 0; h < heads; ++h) total = __fadd_rn(total, terms[h * kTermStride + t]);
+    scores[row * scored + place0 + t] = live ? __fmul_rn(total, scale) : -INFINITY;
+}
+
 // A block's highest score, a thread a block; the block of the row's last visible group +inf (always kept), blocks of only -inf stay -inf.
 __global__ void __launch_bounds__(256) index_block_tops_kernel(const float* __restrict__ scores, const int32_t* __restrict__ visible, size_t groups,
                                                                size_t block, size_t count, float* __restrict__ tops) {
@@ -187,8 +298,19 @@ __global__ void __launch_bounds__(256) index_block_tops_kernel(const float* __re
 static void launch_index_scores(Device& d, const float* q, const float* keys, const float* weights, const int32_t* visible, size_t rows, size_t groups,
                                 size_t heads, size_t dim, float scale, float* scores, const int32_t* candidates, size_t blocks, size_t block) {
     const size_t scored = candidates ? blocks * block : groups;
-    index_scores_kernel<<<dim3(unsigned((scored + kIndexGroups - 1) / kIndexGroups), unsigned(rows)), kIndexThreads, 0, d.stream>>>(
-        q, keys, weights, visible, groups, heads, dim, scale, scores, candidates, blocks, block);
+    const bool aligned = dim % 16 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0 && reinterpret_cast<uintptr_t>(state_halves(keys)) % 16 == 0;
+    if (aligned) {
+        static bool configured[64] = {};
+        if (!configured[d.ordinal & 63]) {
+            SDB_CHECK(cudaFuncSetAttribute(index_scores_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide::kSmem)));
+            configured[d.ordinal & 63] = true;
+        }
+        index_scores_wide_kernel<<<dim3(unsigned((scored + wide::kPlaces - 1) / wide::kPlaces), unsigned(rows)), wide::kThreads, wide::kSmem, d.stream>>>(
+            q, keys, weights, visible, groups, heads, dim, scale, scores, candidates, blocks, block);
+    } else {
+        index_scores_kernel<<<dim3(unsigned((scored + kIndexGroups - 1) / kIndexGroups), unsigned(rows)), kIndexThreads, 0, d.stream>>>(
+            q, keys, weights, visible, groups, heads, dim, scale, scores, candidates, blocks, block);
+    }
     ++d.launches;
     SDB_CHECK(cudaGetLastError());
 }

@@ -237,3 +237,22 @@ def test_invalid_index_shapes_are_refused(gpu):
     for x in (scores, picked, small):
         gpu.release(x)
     case.close()
+
+
+@pytest.mark.parametrize("heads,dim,half_keys", [(32, 128, False), (64, 128, True), (20, 72, False), (20, 72, True), (7, 16, True), (64, 100, False)])
+def test_scores_of_either_kernel_equal_the_oracle(gpu, heads, dim, half_keys):
+    """Widths that are whole 16-column steps take the 8 x 8 register-tile kernel, the others the general one; F32 and BF16-tagged keys; a
+    number of places that fills no whole tile; rows that see fewer groups than there are."""
+    c = index_case(3, 1000, heads=heads, dim=dim, rope_dims=0, spread=129)
+    keys = c["keys"]
+    if half_keys:
+        keys = oracle.to_bf16(keys)
+    q, weights, visible = gpu.upload(c["q"]), gpu.upload(c["weights"]), gpu.upload(c["visible"])
+    held = gpu.upload(keys)
+    scores = gpu.buffer(3 * 1000 * 4)
+    gpu.index_scores(q.pointer, held.tagged_bf16() if half_keys else held.pointer, weights.pointer, visible.pointer, 3, 1000, heads, dim, c["scale"], scores.pointer)
+    got = gpu.read(scores, np.float32, (3, 1000))
+    want = oracle.index_scores(c["q"], keys, c["weights"], c["visible"], c["scale"])
+    assert np.array_equal(bits(got), bits(want))
+    for x in (q, weights, visible, held, scores):
+        gpu.release(x)
