@@ -771,6 +771,7 @@ def main():
     parser.add_argument("--sequences", type=int, default=64, help="sequences per batch (64 is the benchmark; fewer for a profiler capture)")
     parser.add_argument("--profile", action="store_true", help="device-resident steps only, no load padding: the command an ncu capture wraps")
     parser.add_argument("--no-extras", action="store_true", help="the headline alone: no other configuration, no strong / head-sharded curve")
+    parser.add_argument("--index-ops", action="store_true", help="the index producers' entry alone (sd_op_top_k, sd_op_index_select): the command an ncu capture wraps")
     parser.add_argument("--fixed-cuts", action="store_true", help="the decode work list cut by each sequence's own length (same bits in any batch)")
     args = parser.parse_args()
     args.steps_given = args.steps is not None
@@ -792,6 +793,14 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200 GPU: the attention library has no CPU fallback")
+    if args.index_ops:
+        if rank == 0:
+            from straydog_b200.backend import Backend
+            torch.cuda.set_device(local)
+            gpu = Backend(local, 2 << 30)
+            print(json.dumps({"config_id": "index_ops", **run_index_ops(args, local, gpu)}), flush=True)
+            gpu.close()
+        return
     if args.config != 1:
         if rank == 0:
             torch.cuda.set_device(local)

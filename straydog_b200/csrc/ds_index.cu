@@ -9,9 +9,9 @@
 // multiply-adds over the columns in order, each term one rounded product, the terms added in head order; sd_op_index_select gives
 // the scores and indices that sd_op_rope, sd_op_index_scores and sd_op_top_k give one after the other
 // (crates/straydog-engine/tests/fused_gpu.rs:391-431). The kernels here keep that order of operations with another division of
-// the work: a thread owns a 4 x 4 register tile of (place, head) running dots fed by 16-byte shared-memory reads (see
-// index_scores_kernel), BF16-tagged keys are widened as they land. The tensor cores are not used: their summation order is not the
-// contract's.
+// the work: a thread owns a register tile of (place, head) running dots fed by 16-byte shared-memory reads (16 x 8 with two fused
+// multiply-adds an instruction in index_scores_wide_kernel, 4 x 4 in index_scores_kernel for the widths that one does not take),
+// BF16-tagged keys are widened as they land. The tensor cores are not used: their summation order is not the contract's.
 #include "common.cuh"
 #include "ds_sparse.cuh"
 #include "../../include/straydog_gpu_b200.h"
@@ -172,14 +172,21 @@ __global__ void __launch_bounds__(kIndexThreads) index_scores_kernel(const float
     scores[row * scored + place0 + t] = tile_groups[t] < limit ? __fmul_rn(total, scale) : -INFINITY;
 }
 
-// The same scores for the usual shapes (dim a multiple of 16, keys and queries 16-byte aligned): a CTA of 128 threads scores 128 places of
-// one row against all (<= 64) heads, a thread an 8 x 8 register tile (places 4 tg .. + 3 and 64 + 4 tg .. + 3, heads 4 th .. + 3 and
-// 32 + 4 th .. + 3), so a column costs four 16-byte shared-memory reads for 64 fused multiply-adds where the 4 x 4 tile above pays two for
-// 16. The columns come 16 at a time: a thread fetches its place's 16 key values (32 bytes of BF16: one sector) and half a head's 16 query
-// values into registers while the step before is being multiplied, and sets them down the tiles' columns (lanes on consecutive places:
-// no bank conflict) between two barriers. Order of operations as above.
+// The same scores for the usual shapes (dim a multiple of 8, keys and queries 16-byte aligned): a CTA of 128 threads scores 256 places of
+// one row against all (<= 64) heads, a thread a 16 x 8 register tile (places 4 tg + 64 j .. + 3 for j = 0 .. 3, heads 4 th .. + 3 and
+// 32 + 4 th .. + 3). What bounds such a kernel is the path from shared memory to the registers, four cycles a 16-byte read of a warp
+// whatever is broadcast: the 4 x 4 tile above pays two reads for 16 fused multiply-adds, an 8 x 8 tile four for 64 (the two pipes level),
+// this tile six for 128, which leaves the arithmetic pipe the slower one; and the multiply-adds are issued two to an instruction
+// (fma.rn.f32x2 over a pair of heads: each half one IEEE fma, the scalar chain's bits), which halves their issue slots. The columns come 8 at a time: a thread fetches two places' 8 key
+// values (16 bytes of BF16 each) and a head's 4 query values into registers while the step before is being multiplied, and sets them
+// down the tiles' columns (lanes on consecutive places: no bank conflict) between two barriers. Order of operations as above.
+// Two fused multiply-adds an instruction (each half one IEEE fma, the same bits as two scalar ones): half the issue slots for the same arithmetic.
+__device__ __forceinline__ uint64_t pair_of(float low, float high) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(low), "f"(high)); return r; }
+__device__ __forceinline__ void fma_pair(uint64_t& acc, uint64_t a, uint64_t b) { asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b)); }
+__device__ __forceinline__ float2 halves_of(uint64_t pair) { float2 r; asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(pair)); return r; }
+
 namespace wide {
-constexpr int kPlaces = 128, kHeads = 64, kStep = 16, kThreads = 128, kTermStride = kPlaces + 4;
+constexpr int kPlaces = 256, kHeads = 64, kStep = 8, kThreads = 128, kTermStride = kPlaces + 4;
 constexpr size_t kSmem = size_t(kHeads) * kTermStride * 4;   // the terms [head][place]; the tiles [column][place] | [column][head] lie in the same bytes before
 static_assert(kSmem >= size_t(kStep) * (kPlaces + kHeads) * 4, "the tiles fit the terms' area");
 }  // namespace wide
@@ -195,57 +202,62 @@ __global__ void __launch_bounds__(wide::kThreads) index_scores_wide_kernel(const
     extern __shared__ __align__(16) float wide_tiles[];
     float* ks = wide_tiles;                      // [column of the step][place]
     float* qs = wide_tiles + kStep * kPlaces;    // [column of the step][head]
-    // this thread's place (its key row) and its half of a head's query step
-    size_t mine = groups;
-    if (place0 + t < scored) {
-        if (!candidates) mine = place0 + t;
-        else { const int32_t b = candidates[row * blocks + (place0 + t) / block]; mine = b < 0 ? groups : size_t(b) * block + (place0 + t) % block; }
+    // this thread's two places (their key rows) and its part of a head's query step
+    size_t mine[2];
+    bool live[2];
+    #pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const size_t place = place0 + t + kThreads * j;
+        mine[j] = groups;
+        if (place < scored) {
+            if (!candidates) mine[j] = place;
+            else { const int32_t b = candidates[row * blocks + place / block]; mine[j] = b < 0 ? groups : size_t(b) * block + place % block; }
+        }
+        live[j] = mine[j] < limit;
     }
-    const bool live = mine < limit, bf16 = state_is_bf16(keys);
-    const uint16_t* key_halves = state_halves(keys) + mine * dim;
-    const float* key_floats = keys + mine * dim;
-    const unsigned q_head = t % kHeads, q_half = t / kHeads;
-    const float* q_from = q + (row * heads + q_head) * dim + 8 * q_half;
+    const bool bf16 = state_is_bf16(keys);
+    const uint16_t* key_halves = state_halves(keys);
+    const unsigned q_head = t % kHeads, q_part = t / kHeads;
+    const float* q_from = q + (row * heads + q_head) * dim + 4 * q_part;
     const bool q_live = q_head < heads;
 
-    float key_next[kStep], q_next[8];
+    float key_next[2][kStep];
+    float4 q_next;
     const auto fetch = [&](size_t d0) {
-        if (!live) {
-            #pragma unroll
-            for (int i = 0; i < kStep; ++i) key_next[i] = 0.0f;
-        } else if (bf16) {
-            #pragma unroll
-            for (int v = 0; v < 2; ++v) {
-                const uint4 x = *reinterpret_cast<const uint4*>(key_halves + d0 + 8 * v);
+        #pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            if (!live[j]) {
+                #pragma unroll
+                for (int i = 0; i < kStep; ++i) key_next[j][i] = 0.0f;
+            } else if (bf16) {
+                const uint4 x = *reinterpret_cast<const uint4*>(key_halves + mine[j] * dim + d0);
                 const uint32_t w[4] = {x.x, x.y, x.z, x.w};
                 #pragma unroll
-                for (int i = 0; i < 4; ++i) { key_next[8 * v + 2 * i] = __uint_as_float(w[i] << 16); key_next[8 * v + 2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
-            }
-        } else {
-            #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const float4 x = *reinterpret_cast<const float4*>(key_floats + d0 + 4 * v);
-                key_next[4 * v] = x.x; key_next[4 * v + 1] = x.y; key_next[4 * v + 2] = x.z; key_next[4 * v + 3] = x.w;
+                for (int i = 0; i < 4; ++i) { key_next[j][2 * i] = __uint_as_float(w[i] << 16); key_next[j][2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+            } else {
+                #pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    const float4 x = *reinterpret_cast<const float4*>(keys + mine[j] * dim + d0 + 4 * v);
+                    key_next[j][4 * v] = x.x; key_next[j][4 * v + 1] = x.y; key_next[j][4 * v + 2] = x.z; key_next[j][4 * v + 3] = x.w;
+                }
             }
         }
-        #pragma unroll
-        for (int v = 0; v < 2; ++v) {
-            const float4 x = q_live ? __ldg(reinterpret_cast<const float4*>(q_from + d0 + 4 * v)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            q_next[4 * v] = x.x; q_next[4 * v + 1] = x.y; q_next[4 * v + 2] = x.z; q_next[4 * v + 3] = x.w;
-        }
+        q_next = q_live ? __ldg(reinterpret_cast<const float4*>(q_from + d0)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     };
     const auto set_down = [&]() {
         #pragma unroll
-        for (int i = 0; i < kStep; ++i) ks[i * kPlaces + t] = key_next[i];
-        #pragma unroll
-        for (int i = 0; i < 8; ++i) qs[(8 * q_half + i) * kHeads + q_head] = q_next[i];
+        for (int j = 0; j < 2; ++j)
+            #pragma unroll
+            for (int i = 0; i < kStep; ++i) ks[i * kPlaces + t + kThreads * j] = key_next[j][i];
+        qs[(4 * q_part) * kHeads + q_head] = q_next.x; qs[(4 * q_part + 1) * kHeads + q_head] = q_next.y;
+        qs[(4 * q_part + 2) * kHeads + q_head] = q_next.z; qs[(4 * q_part + 3) * kHeads + q_head] = q_next.w;
     };
 
-    float acc[8][8];   // [place][head]
+    uint64_t acc[16][4];   // [place][pair of heads]
     #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 16; ++i)
         #pragma unroll
-        for (int h = 0; h < 8; ++h) acc[i][h] = 0.0f;
+        for (int h = 0; h < 4; ++h) acc[i][h] = 0;
     fetch(0);
     set_down();
     __syncthreads();
@@ -254,13 +266,21 @@ __global__ void __launch_bounds__(wide::kThreads) index_scores_wide_kernel(const
         if (more) fetch(d0 + kStep);
         #pragma unroll
         for (int c = 0; c < kStep; ++c) {
-            const float4 ka = *reinterpret_cast<const float4*>(ks + c * kPlaces + 4 * tg), kb = *reinterpret_cast<const float4*>(ks + c * kPlaces + 64 + 4 * tg);
-            const float4 qa = *reinterpret_cast<const float4*>(qs + c * kHeads + 4 * th), qb = *reinterpret_cast<const float4*>(qs + c * kHeads + 32 + 4 * th);
-            const float k[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w}, qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            uint64_t k[16], qv[4];
             #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int j = 0; j < 4; ++j) {
+                const float4 x = *reinterpret_cast<const float4*>(ks + c * kPlaces + 64 * j + 4 * tg);
+                k[4 * j] = pair_of(x.x, x.x); k[4 * j + 1] = pair_of(x.y, x.y); k[4 * j + 2] = pair_of(x.z, x.z); k[4 * j + 3] = pair_of(x.w, x.w);
+            }
+            #pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float4 x = *reinterpret_cast<const float4*>(qs + c * kHeads + 32 * j + 4 * th);
+                qv[2 * j] = pair_of(x.x, x.y); qv[2 * j + 1] = pair_of(x.z, x.w);
+            }
+            #pragma unroll
+            for (int i = 0; i < 16; ++i)
                 #pragma unroll
-                for (int h = 0; h < 8; ++h) acc[i][h] = fmaf(qv[h], k[i], acc[i][h]);
+                for (int h = 0; h < 4; ++h) fma_pair(acc[i][h], qv[h], k[i]);
         }
         __syncthreads();
         if (more) { set_down(); __syncthreads(); }
@@ -271,16 +291,24 @@ __global__ void __launch_bounds__(wide::kThreads) index_scores_wide_kernel(const
         const size_t head = (h < 4 ? 0 : 32) + 4 * th + (h & 3);
         const float w = head < heads ? weights[row * heads + head] : 0.0f;
         #pragma unroll
-        for (int half = 0; half < 2; ++half)
-            *reinterpret_cast<float4*>(terms + head * kTermStride + 64 * half + 4 * tg) =
-                make_float4(__fmul_rn(fmaxf(acc[4 * half][h], 0.0f), w), __fmul_rn(fmaxf(acc[4 * half + 1][h], 0.0f), w),
-                            __fmul_rn(fmaxf(acc[4 * half + 2][h], 0.0f), w), __fmul_rn(fmaxf(acc[4 * half + 3][h], 0.0f), w));
+        for (int j = 0; j < 4; ++j) {
+            float dot[4];
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 both = halves_of(acc[4 * j + i][h / 2]); dot[i] = h & 1 ? both.y : both.x; }
+            *reinterpret_cast<float4*>(terms + head * kTermStride + 64 * j + 4 * tg) =
+                make_float4(__fmul_rn(fmaxf(dot[0], 0.0f), w), __fmul_rn(fmaxf(dot[1], 0.0f), w), __fmul_rn(fmaxf(dot[2], 0.0f), w), __fmul_rn(fmaxf(dot[3], 0.0f), w));
+        }
     }
     __syncthreads();
-    if (place0 + t >= scored) return;
-    float total = 0.0f;
-    for (size_t h = 0; h < heads; ++h) total = __fadd_rn(total, terms[h * kTermStride + t]);
-    scores[row * scored + place0 + t] = live ? __fmul_rn(total, scale) : -INFINITY;
+    // a place's terms in head order: one chain of additions a place, two places a thread side by side
+    float total[2] = {0.0f, 0.0f};
+    for (size_t h = 0; h < heads; ++h) {
+        total[0] = __fadd_rn(total[0], terms[h * kTermStride + t]);
+        total[1] = __fadd_rn(total[1], terms[h * kTermStride + t + kThreads]);
+    }
+    #pragma unroll
+    for (int j = 0; j < 2; ++j)
+        if (place0 + t + kThreads * j < scored) scores[row * scored + place0 + t + kThreads * j] = live[j] ? __fmul_rn(total[j], scale) : -INFINITY;
 }
 
 // A block's highest score, a thread a block; the block of the row's last visible group +inf (always kept), blocks of only -inf stay -inf.
@@ -298,7 +326,7 @@ __global__ void __launch_bounds__(256) index_block_tops_kernel(const float* __re
 static void launch_index_scores(Device& d, const float* q, const float* keys, const float* weights, const int32_t* visible, size_t rows, size_t groups,
                                 size_t heads, size_t dim, float scale, float* scores, const int32_t* candidates, size_t blocks, size_t block) {
     const size_t scored = candidates ? blocks * block : groups;
-    const bool aligned = dim % 16 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0 && reinterpret_cast<uintptr_t>(state_halves(keys)) % 16 == 0;
+    const bool aligned = dim % 8 == 0 && reinterpret_cast<uintptr_t>(q) % 16 == 0 && reinterpret_cast<uintptr_t>(state_halves(keys)) % 16 == 0;
     if (aligned) {
         static bool configured[64] = {};
         if (!configured[d.ordinal & 63]) {
