@@ -305,11 +305,18 @@ int sdx_qsa_normalize_rows(void* handle, float* projections, uint64_t stride, ui
    `packed` (all three: the layout sd_attention_sequence and sdx_qsa_attention_rows read, for `count` rows), keys and values into rows
    position .. position + count - 1 of the Q8_0 state (and the mirror ring), every 4-position block the chunk completes is pooled into
    index_state (positions before the chunk from the ring), and the chunk's last four index keys enter the ring. The same bits as
-   sdx_qsa_normalize_rows over the same tokens. */
+   sdx_qsa_normalize_rows over the same tokens. While a rope table is set (sd_rope_rows: a sequence with images) the tokens and the
+   pooled blocks turn by the table's three positions a row (qsa_normalize_axes, qsa_pool_axes: gpu/sparse_attention.hpp:27-50,
+   111-131); a chunk the table does not cover is refused ("invalid Straydog rope table"). */
 int sdx_qsa_normalize_chunk(void* handle, const float* qgate, const float* key, const float* value_rows, float* iq, const float* ik,
                             uint64_t count, uint64_t position, uint64_t heads, uint64_t kv_heads, const float* qnorm,
                             const float* knorm, const float* iqnorm, const float* pool_norm, float* packed, uint64_t selected,
                             void* state, uint64_t context, void* mirror, uint64_t mirror_rows, float* index_state);
+
+/* gpu/straydog_gpu.h:607-609. The rope positions of a sequence with images for the next prompt chunks: three (t, h, w) a position
+   from `first`, `count` (<= 4100) positions in a host array, covering each chunk's rows and the 4-position block its first row is
+   in. count 0: the rows' own positions again. */
+int sd_rope_rows(void* handle, uint64_t first, uint64_t count, const uint32_t* axes);
 
 /* sdx_qsa_attention_rows over a state in host memory (sd_host_state), through the stage registered with sd_kv_stage: the union of
    the rows' selected 4-position blocks is copied into the stage once, in block order, and the selections are renumbered to it

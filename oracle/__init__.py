@@ -42,7 +42,7 @@ _sig("orc_index_scores", [_p, _p, _i32, _p, _p, _u64, _u64, _u64, _u64, _f32, _p
 _sig("orc_index_block_tops", [_p, _p, _u64, _u64, _u64, _p])
 _sig("orc_qsa_index_select", [_p, _u64, _p, _u64, _u64, _p, _u64, _u64, _u64, _p])
 _sig("orc_qsa_normalize_rows", [_p, _u64, _u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _p, _p, _u64, _p])
-_sig("orc_qsa_normalize_chunk", [_p, _p, _p, _p, _p, _u64, _u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _u64, _p])
+_sig("orc_qsa_normalize_chunk", [_p, _p, _p, _p, _p, _u64, _u64, _u64, _u64, _p, _p, _p, _p, _p, _p, _u64, _p, _p, _u64])
 _sig("orc_index_proj", [_p, _i32, _u64, _u64, _p, _i32, _p])
 _sig("orc_top_k", [_p, _u64, _u64, _u64, _p])
 _sig("orc_to_bf16", [_p, _u64, _p])
@@ -240,17 +240,20 @@ def qsa_normalize_rows(projections, heads, kv_heads, qnorm, knorm, iqnorm, pool_
                                 _ptr(packed), _ptr(state), context, _ptr(index_state))
 
 
-def qsa_normalize_chunk(qgate, key, value, iq, ik, position, heads, kv_heads, qnorm, knorm, iqnorm, pool_norm, packed, state, context, index_state):
+def qsa_normalize_chunk(qgate, key, value, iq, ik, position, heads, kv_heads, qnorm, knorm, iqnorm, pool_norm, packed, state, context, index_state,
+                        rope_rows=None, rope_first=0):
     """A prompt chunk's front: qgate [count, heads, 512], key / value [count, kv_heads, 256], iq [count, 4, 128] (normalised in place),
-    ik [count, 128]; packed, state and index_state are written in place."""
+    ik [count, 128]; packed, state and index_state are written in place. rope_rows [n, 3] uint32 from position rope_first: the rope
+    table of a sequence with images."""
     arrays = [qgate, key, value, iq, ik, packed, index_state]
     assert all(x.dtype == np.float32 and x.flags.c_contiguous for x in arrays) and state.dtype == np.uint8 and state.flags.c_contiguous
     count = ik.shape[0]
     assert qgate.size == count * heads * 512 and key.size == value.size == count * kv_heads * 256 and iq.size == count * 512
     assert index_state.size == (context // 4 + 1 + 16) * 128 and state.size == context * 2 * kv_heads * ROW_Q8
     norms = [np.ascontiguousarray(n, np.float32) for n in (qnorm, knorm, iqnorm, pool_norm)]
+    table = np.ascontiguousarray(rope_rows, np.uint32) if rope_rows is not None else None
     _lib.orc_qsa_normalize_chunk(_ptr(qgate), _ptr(key), _ptr(value), _ptr(iq), _ptr(ik), count, position, heads, kv_heads, *[_ptr(n) for n in norms],
-                                 _ptr(packed), _ptr(state), context, _ptr(index_state))
+                                 _ptr(packed), _ptr(state), context, _ptr(index_state), _ptr(table) if table is not None else None, rope_first)
 
 
 def index_proj(w, kind, x, units=True):

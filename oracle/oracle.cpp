@@ -629,6 +629,15 @@ static float qsa_rope(float own, float partner, uint64_t column, uint64_t positi
     const float angle = float(position) / std::pow(1e7f, float(column % 32) / 32.0f);
     return own * std::cos(angle) + (column < 32 ? -partner : partner) * std::sin(angle);
 }
+// gpu/sparse_attention.hpp:27-32 (qsa_rope_axes): a row of a sequence with images has a position for each axis (t, h, w); pair p of
+// the 32 turns by the position of axis p % 3. No table: qsa_rope.
+static float qsa_rope_at(float own, float partner, uint64_t column, uint64_t position, const uint32_t* axes) {
+    if (!axes) return qsa_rope(own, partner, column, position);
+    if (column >= 64) return own;
+    const uint64_t pair = column % 32;
+    const float angle = float(axes[pair % 3]) / std::pow(1e7f, float(pair) / 32.0f);
+    return own * std::cos(angle) + (column < 32 ? -partner : partner) * std::sin(angle);
+}
 // The sum of width squares as the reference's shared-memory loop forms it: column c takes c + width / 2, then c + width / 4, ...
 static float qsa_halving_sum(float* sums, uint64_t width) {
     for (uint64_t offset = width / 2; offset; offset /= 2)
@@ -636,14 +645,15 @@ static float qsa_halving_sum(float* sums, uint64_t width) {
     return sums[0];
 }
 // gpu/sparse_attention.hpp:55-71 (qsa_normalize_block): one head of `width` columns, RMS-normalised, scaled by `norm`, rotated.
-static void qsa_normalize_head(const float* source, const float* norm, uint64_t width, uint64_t position, float* target) {
+static void qsa_normalize_head(const float* source, const float* norm, uint64_t width, uint64_t position, float* target,
+                               const uint32_t* axes = nullptr) {
     float values[256], sums[256];
     for (uint64_t c = 0; c < width; ++c) { values[c] = source[c] * norm[c]; sums[c] = source[c] * source[c]; }
     const float denominator = std::sqrt(qsa_halving_sum(sums, width) / float(width) + 1e-6f);
     float result[256];
     for (uint64_t c = 0; c < width; ++c) {
         const float own = values[c] / denominator, partner = c < 64 ? values[(c + 32) % 64] / denominator : 0.0f;
-        result[c] = qsa_rope(own, partner, c, position);
+        result[c] = qsa_rope_at(own, partner, c, position, axes);
     }
     std::memcpy(target, result, width * sizeof(float));   // (the index queries are normalised in place)
 }
@@ -697,20 +707,23 @@ void orc_qsa_normalize_rows(float* projections, uint64_t stride, uint64_t rows, 
 void orc_qsa_normalize_chunk(const float* qgate, const float* key, const float* value, float* iq, const float* ik, uint64_t count,
                              uint64_t position, uint64_t heads, uint64_t kv_heads, const float* qnorm, const float* knorm,
                              const float* iqnorm, const float* pool_norm, float* packed, uint8_t* state, uint64_t context,
-                             float* index_state) {
+                             float* index_state, const uint32_t* rope_rows, uint64_t rope_first) {
+    // (rope_rows: the table of a sequence with images, three positions a row from rope_first, gpu/prefill_batch.hpp:344 and :360-362
+    // with qsa_normalize_axes / qsa_pool_axes, gpu/sparse_attention.hpp:36-50, 111-131; null: every token turns at its own position)
     const uint64_t pool = context / 4 + 1, Q = heads * 256, K = kv_heads * 256;
     for (uint64_t t = 0; t < count; ++t) {
+        const uint32_t* axes = rope_rows ? rope_rows + (position + t - rope_first) * 3 : nullptr;
         for (uint64_t head = 0; head < heads; ++head)
-            qsa_normalize_head(qgate + (t * heads + head) * 512, qnorm, 256, position + t, packed + t * Q + head * 256);
+            qsa_normalize_head(qgate + (t * heads + head) * 512, qnorm, 256, position + t, packed + t * Q + head * 256, axes);
         for (uint64_t head = 0; head < kv_heads; ++head) {
             float* normalized = packed + count * Q + t * K + head * 256;
-            qsa_normalize_head(key + t * K + head * 256, knorm, 256, position + t, normalized);
+            qsa_normalize_head(key + t * K + head * 256, knorm, 256, position + t, normalized, axes);
             std::memcpy(packed + count * (Q + K) + t * K + head * 256, value + t * K + head * 256, 256 * sizeof(float));
             q8_encode_row(normalized, state + (head * context + position + t) * kRowQ8);
             q8_encode_row(value + t * K + head * 256, state + ((kv_heads + head) * context + position + t) * kRowQ8);
         }
         for (uint64_t head = 0; head < 4; ++head)
-            qsa_normalize_head(iq + t * 512 + head * 128, iqnorm, 128, position + t, iq + t * 512 + head * 128);
+            qsa_normalize_head(iq + t * 512 + head * 128, iqnorm, 128, position + t, iq + t * 512 + head * 128, axes);
     }
     float* history = index_state + pool * 128;
     for (uint64_t block = position / 4; block < (position + count) / 4; ++block) {
@@ -728,7 +741,7 @@ void orc_qsa_normalize_chunk(const float* qgate, const float* key, const float* 
         const float denominator = std::sqrt(qsa_halving_sum(sums, 128) / 128.0f + 1e-6f);
         for (uint64_t c = 0; c < 128; ++c) {
             const float own = vals[c] / denominator, partner = c < 64 ? vals[(c + 32) % 64] / denominator : 0.0f;
-            index_state[c * pool + block] = qsa_rope(own, partner, c, begin);
+            index_state[c * pool + block] = qsa_rope_at(own, partner, c, begin, rope_rows ? rope_rows + (begin - rope_first) * 3 : nullptr);
         }
     }
     const uint64_t kept = count < 4 ? count : 4;

@@ -49,6 +49,7 @@ SIGNATURES = {
     "sdx_kv_grow": ([p, u64, u64, u64, u64, p, p], i32),
     "sdx_qsa_normalize_rows": ([p, p, u64, u64, u64, u64, p, p, p, p, p, p, p, u64, p, u64, p, u64, p], i32),
     "sdx_qsa_normalize_chunk": ([p, p, p, p, p, p, u64, u64, u64, u64, p, p, p, p, p, u64, p, u64, p, u64, p], i32),
+    "sd_rope_rows": ([p, u64, u64, p], i32),
     "sd_op_rope": ([p, p, u64, u64, u64, u64, p, p, i32], i32),
     "sd_op_compress": ([p, p, p, u64, u64, u64, p], i32),
     "sd_op_index_scores": ([p, p, p, p, p, u64, u64, u64, u64, f32, p], i32),

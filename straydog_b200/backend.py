@@ -280,6 +280,15 @@ class Backend:
         self._c(self.lib.sdx_qsa_normalize_chunk(self.handle, qgate, key, value, iq, ik, count, position, heads, kv_heads, qnorm, knorm, iqnorm,
                                                  pool_norm, packed, selected, state, context, mirror, mirror_rows, index_state))
 
+    def rope_rows(self, first, axes):
+        """sd_rope_rows: the rope table of a sequence with images, axes [count, 3] uint32 from position `first`; None or empty clears it."""
+        if axes is None or len(axes) == 0:
+            self._c(self.lib.sd_rope_rows(self.handle, 0, 0, None))
+            return
+        axes = np.ascontiguousarray(axes, np.uint32)
+        assert axes.ndim == 2 and axes.shape[1] == 3
+        self._c(self.lib.sd_rope_rows(self.handle, first, axes.shape[0], axes.ctypes.data_as(C.c_void_p)))
+
     def kv_grow(self, kv_heads, from_context, to_context, valid, state, index_state, row=272):
         """sdx_kv_grow: the state and the index state (Buffers) grown to `to_context` positions; returns the two new Buffers. The library
         has released the old state (and the old index state unless it was large enough: then the same Buffer comes back)."""

@@ -66,6 +66,7 @@ struct Device {
     double* turns = nullptr; size_t turns_rows = 0, turns_pairs = 0;   // rope sincos table (forward, inverse)
     bool turns_ready = false; size_t turns_ready_rows = 0, turns_ready_pairs = 0;
     void* kv_stage = nullptr; uint64_t kv_stage_rows = 0;
+    uint32_t* rope_rows = nullptr; size_t rope_first = 0, rope_count = 0;   // a sequence with images: three rotation positions a row (sd_rope_rows)
     uint64_t launches = 0;   // kernels launched through this handle (the benchmark's gpu_launches)
     bool adopted = false;    // made by sdx_adopt over another library's stream and allocations: no range checks, nothing owned but workspaces
     explicit Device(int o) : ordinal(o) {}

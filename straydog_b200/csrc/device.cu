@@ -192,7 +192,7 @@ void sd_destroy(void* handle) {
             else cudaFree(const_cast<uint8_t*>(entry.first));
         }
         if (value->pinned) cudaFreeHost(value->pinned);
-        for (void* p : {value->work, value->partial, value->tables, value->unions, static_cast<void*>(value->turns)}) if (p) cudaFree(p);
+        for (void* p : {value->work, value->partial, value->tables, value->unions, static_cast<void*>(value->turns), static_cast<void*>(value->rope_rows)}) if (p) cudaFree(p);
         if (value->side) { cudaStreamDestroy(value->side); cudaEventDestroy(value->side_fork); cudaEventDestroy(value->side_join); }
         if (!value->adopted) cudaStreamDestroy(value->stream);
         cudaGetLastError();

@@ -42,6 +42,7 @@ struct NormalizeArgs {
     bool copy_values;         // a prompt chunk's values also go into the packed rows (gpu/sparse_attention.hpp:495)
     const float* qnorm; const float* knorm; const float* iqnorm; const float* pool_norm;
     const uint32_t* positions; const uint32_t* ropes;
+    const uint32_t* axes; size_t axes_first;   // a prompt chunk of a sequence with images: three rotation positions (t, h, w) a position from axes_first
     float* packed;
     uint8_t* state; size_t context; unsigned kv_row;
     uint8_t* mirror; size_t mirror_rows;
@@ -49,10 +50,12 @@ struct NormalizeArgs {
     int* status;
 };
 
-// gpu/sparse_attention.hpp:2-6
-__device__ __forceinline__ float rotate(float own, float partner, size_t column, size_t position) {
+// gpu/sparse_attention.hpp:2-6 (qsa_rope), and :27-32 (qsa_rope_axes) with `axes`: pair p of the 32 turns by the position of axis p % 3
+// (text holds one position on all three axes, which is the first form's angle)
+__device__ __forceinline__ float rotate(float own, float partner, size_t column, size_t position, const uint32_t* axes = nullptr) {
     if (column >= 64) return own;
-    const float angle = float(position) / powf(1e7f, float(column % 32) / 32.0f);
+    const size_t pair = column % 32;
+    const float angle = float(axes ? size_t(axes[pair % 3]) : position) / powf(1e7f, float(pair) / 32.0f);
     return own * cosf(angle) + (column < 32 ? -partner : partner) * sinf(angle);
 }
 
@@ -76,7 +79,7 @@ __device__ __forceinline__ float halving_sum(float* sums, size_t width, size_t c
 
 // one head of `width` columns: normalised and rotated into target[column]; returns this thread's value (0 past the width)
 __device__ __forceinline__ float normalize_head(const float* source, const float* norm, size_t width, size_t position, float* target,
-                                                float* values, float* sums, float* total) {
+                                                float* values, float* sums, float* total, const uint32_t* axes = nullptr) {
     const size_t column = threadIdx.x;
     const bool own = column < width;
     if (own) { const float x = source[column]; values[column] = x * norm[column]; sums[column] = x * x; }
@@ -85,7 +88,7 @@ __device__ __forceinline__ float normalize_head(const float* source, const float
     const float denominator = sqrtf(sum / float(width) + 1e-6f);
     const float mine = values[column] / denominator;
     const float partner = column < 64 ? values[(column + 32) % 64] / denominator : 0.0f;
-    const float result = rotate(mine, partner, column, position);
+    const float result = rotate(mine, partner, column, position, axes);
     target[column] = result;
     return result;
 }
@@ -94,8 +97,9 @@ __global__ void __launch_bounds__(256) qsa_normalize_rows_kernel(const Normalize
     __shared__ float values[256], sums[256], total;
     const size_t block = blockIdx.x, row = blockIdx.y, column = threadIdx.x;
     const size_t rope = a.positions ? a.ropes[row] : a.base + row;
+    const uint32_t* axes = a.axes ? a.axes + (a.base + row - a.axes_first) * 3 : nullptr;   // (a prompt chunk's rows only)
     if (block < a.heads) {
-        normalize_head(a.qgate + row * a.qgate_stride + block * 512, a.qnorm, 256, rope, a.packed + (row * a.heads + block) * 256, values, sums, &total);
+        normalize_head(a.qgate + row * a.qgate_stride + block * 512, a.qnorm, 256, rope, a.packed + (row * a.heads + block) * 256, values, sums, &total, axes);
     } else if (block < a.heads + a.kv_heads) {
         const size_t head = block - a.heads, position = a.positions ? a.positions[row] : a.base + row;
         if (position >= a.context) {   // (a position past the state: nothing of the row is written, and the host is told)
@@ -103,7 +107,7 @@ __global__ void __launch_bounds__(256) qsa_normalize_rows_kernel(const Normalize
             return;
         }
         float* normalized = a.packed + a.rows * a.heads * 256 + (row * a.kv_heads + head) * 256;
-        const float key = normalize_head(a.key + row * a.key_stride + head * 256, a.knorm, 256, rope, normalized, values, sums, &total);
+        const float key = normalize_head(a.key + row * a.key_stride + head * 256, a.knorm, 256, rope, normalized, values, sums, &total, axes);
         const float value = a.value[row * a.value_stride + head * 256 + column];
         if (a.copy_values) a.packed[a.rows * (a.heads + a.kv_heads) * 256 + (row * a.kv_heads + head) * 256 + column] = value;
         __half key_scale, value_scale;
@@ -128,7 +132,7 @@ __global__ void __launch_bounds__(256) qsa_normalize_rows_kernel(const Normalize
     } else if (block < a.heads + a.kv_heads + 4) {
         const size_t head = block - a.heads - a.kv_heads;
         float* mine = a.iq + row * a.iq_stride + head * 128;
-        normalize_head(mine, a.iqnorm, 128, rope, mine, values, sums, &total);
+        normalize_head(mine, a.iqnorm, 128, rope, mine, values, sums, &total, axes);
     } else if (row == 0) {
         float* history = a.blocks + a.pool * 128;
         const bool mine = column < 128;
@@ -179,7 +183,7 @@ __global__ void __launch_bounds__(128) qsa_pool_chunk_kernel(const NormalizeArgs
         const float denominator = sqrtf(sum / 128.0f + 1e-6f);
         const float value = values[column] / denominator;
         const float partner = column < 64 ? values[(column + 32) % 64] / denominator : 0.0f;
-        a.blocks[column * a.pool + block] = rotate(value, partner, column, begin);
+        a.blocks[column * a.pool + block] = rotate(value, partner, column, begin, a.axes ? a.axes + (begin - a.axes_first) * 3 : nullptr);   // (:111-131 qsa_pool_axes)
     }
     if (blockIdx.x == 0) {
         __syncthreads();   // (the ring has been read)
@@ -255,11 +259,33 @@ extern "C" int sdx_qsa_normalize_chunk(void* handle, const float* qgate, const f
     a.iq = iq; a.iq_stride = 512; a.ik = ik; a.ik_stride = 128;
     a.rows = count; a.heads = heads; a.kv_heads = kv_heads; a.base = position; a.copy_values = true;
     a.qnorm = qnorm; a.knorm = knorm; a.iqnorm = iqnorm; a.pool_norm = pool_norm;
+    if (value.rope_count) {   // (gpu/prefill_batch.hpp:344, 360-362: the table covers the chunk's rows and the block its first row is in)
+        const uint64_t first_read = (position + count) / 4 > position / 4 ? position / 4 * 4 : position;
+        if (first_read < value.rope_first || position + count > value.rope_first + value.rope_count)
+            throw std::runtime_error("invalid Straydog rope table");
+        a.axes = value.rope_rows; a.axes_first = value.rope_first;
+    }
     a.packed = packed; a.state = static_cast<uint8_t*>(state); a.context = context;
     a.mirror = static_cast<uint8_t*>(mirror); a.mirror_rows = mirror_rows; a.blocks = index_state; a.pool = pool; a.status = status_word(value); a.kv_row = value.kv_row;
     qsa_normalize_rows_kernel<<<dim3(unsigned(heads + kv_heads + 4), unsigned(count)), 256, 0, value.stream>>>(a);
     const uint64_t completed = (position + count) / 4 - position / 4;
     qsa_pool_chunk_kernel<<<unsigned(std::max<uint64_t>(completed, 1)), 128, 0, value.stream>>>(a, completed);
     value.launches += 2;
+    SDB_OP_END
+}
+
+// gpu/straydog_gpu.h:607-609, gpu/kernels.cpp:1526-1536. The rope positions of a sequence with images for the next prompt chunks:
+// three (t, h, w) a position from `first`, `count` positions (a host array), covering each chunk's rows and the block its first
+// row is in; count 0: the rows' own positions again. sdx_qsa_normalize_chunk turns by the table while one is set.
+extern "C" int sd_rope_rows(void* handle, uint64_t first, uint64_t count, const uint32_t* axes) {
+    SDB_OP_BEGIN
+    constexpr size_t most = 4096 + 4;
+    if (count > most || (count && !axes)) throw std::runtime_error("invalid Straydog rope table");
+    if (count && !value.rope_rows) SDB_CHECK(cudaMalloc(reinterpret_cast<void**>(&value.rope_rows), most * 3 * 4));
+    if (count) {
+        SDB_CHECK(cudaMemcpyAsync(value.rope_rows, axes, size_t(count) * 3 * 4, cudaMemcpyHostToDevice, value.stream));
+        SDB_CHECK(cudaStreamSynchronize(value.stream));   // (the host array is the caller's again on return)
+    }
+    value.rope_first = size_t(first); value.rope_count = size_t(count);
     SDB_OP_END
 }

@@ -260,6 +260,69 @@ def test_a_chunks_front_equals_the_oracles_and_its_tokens_taken_as_rows(gpu, hea
         assert np.array_equal(rows["index"][:pool * 128].view(np.uint32), got["index_state"][:pool * 128].view(np.uint32))
 
 
+def image_axes(rng, first, count, position):
+    """Rope positions of a sequence with images: text before (one position on all three axes), then an image's grid (t fixed, h and w
+    running), then text again: three positions a row from `first`."""
+    axes = np.zeros((count, 3), np.uint32)
+    for i in range(count):
+        p = first + i
+        if p < position + 3:
+            axes[i] = p
+        elif p < position + 3 + 48:
+            g = p - (position + 3)
+            axes[i] = (position + 3, position + 3 + g // 8, position + 3 + g % 8)
+        else:
+            axes[i] = p - 40
+    return axes
+
+
+@pytest.mark.parametrize("heads,kv_heads,context,position,count", [(16, 2, 2048, 1021, 70), (24, 2, 1024, 0, 64), (16, 2, 512, 6, 1)])
+def test_a_chunk_of_a_sequence_with_images_turns_by_the_rope_table(gpu, heads, kv_heads, context, position, count):
+    """sd_rope_rows (gpu/straydog_gpu.h:607-609): with a table set the chunk's tokens and pooled blocks turn by three positions a row
+    (gpu/sparse_attention.hpp:27-50, 111-131). A table of the rows' own positions on all three axes gives the bits of no table at all
+    (text: the reference's own remark); an image's table gives the oracle's restatement; a table that does not cover the chunk is refused."""
+    c = chunk_case(position + count + 1, heads, kv_heads, context, position, count)
+    plain = run_chunk(gpu, c)
+    first = position // 4 * 4
+    own = np.repeat(np.arange(first, position + count, dtype=np.uint32)[:, None], 3, axis=1)
+    try:
+        gpu.rope_rows(first, own)
+        same = run_chunk(gpu, c)
+        for name in ("iq", "packed", "state", "index_state"):
+            assert np.array_equal(np.ascontiguousarray(same[name]).view(np.uint8), np.ascontiguousarray(plain[name]).view(np.uint8)), name
+        axes = image_axes(np.random.default_rng(3), first, position + count - first, position)
+        gpu.rope_rows(first, axes)
+        got = run_chunk(gpu, c)
+        want = {n: c[n].copy() for n in ("iq", "packed", "state", "index_state")}
+        oracle.qsa_normalize_chunk(c["qgate"], c["key"], c["value"], want["iq"], c["ik"], position, heads, kv_heads, *c["norms"], want["packed"],
+                                   want["state"], context, want["index_state"], rope_rows=axes, rope_first=first)
+        live, pool = count * (heads + kv_heads) * 256, c["pool"]
+        assert np.abs(got["packed"][:live] - want["packed"][:live]).max() < 2e-4
+        assert np.abs(got["iq"] - want["iq"]).max() < 2e-4
+        assert np.abs(got["index_state"][:pool * 128] - want["index_state"][:pool * 128]).max() < 2e-4
+        assert np.array_equal(got["index_state"][pool * 128:], want["index_state"][pool * 128:]), "the history ring"
+        if count > 8:
+            assert np.abs(got["packed"][:live] - plain["packed"][:live]).max() > 1e-2, "the image's rows turn elsewhere"
+        mine, theirs = (x.reshape(2 * kv_heads, context, 272) for x in (got["state"], want["state"]))
+        assert np.array_equal(mine[kv_heads:], theirs[kv_heads:]), "value rows"
+        keys = got["packed"][count * heads * 256:live].reshape(count, kv_heads, 256)
+        for h in range(kv_heads):
+            assert np.array_equal(mine[h, position:position + count], oracle.q8_encode_rows(keys[:, h]))
+        # a table that starts behind the chunk's first row, or ends before its last
+        gpu.rope_rows(position + 1, axes)
+        with pytest.raises(StraydogError, match="rope table"):
+            run_chunk(gpu, c)
+        gpu.rope_rows(first, axes[:-1])
+        with pytest.raises(StraydogError, match="rope table"):
+            run_chunk(gpu, c)
+        with pytest.raises(StraydogError, match="rope table"):
+            gpu.rope_rows(0, np.zeros((4101, 3), np.uint32))
+    finally:
+        gpu.rope_rows(0, None)
+    again = run_chunk(gpu, c)
+    assert np.array_equal(again["packed"].view(np.uint32), plain["packed"].view(np.uint32)), "count 0: the rows' own positions again"
+
+
 def test_invalid_chunk_shapes_are_refused(gpu):
     c = chunk_case(2, 16, 2, 256, 100, 8)
     for kwargs in (dict(count=0), dict(position=250), dict(heads=0), dict(context=0)):

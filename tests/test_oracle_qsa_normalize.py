@@ -140,3 +140,36 @@ def test_a_prompt_chunks_front_equals_its_tokens_taken_as_rows(position, count):
     done = list(range(position // 4, (position + count) // 4))
     blocks = index_state[:pool * 128].reshape(128, pool)
     assert all(blocks[:, b].any() for b in done) and not np.delete(blocks, done, axis=1).any()
+
+
+def test_a_rope_table_of_the_rows_own_positions_is_no_table_and_an_images_rows_turn_by_their_axes():
+    # gpu/sparse_attention.hpp:27-32: text holds one position on all three axes, which is qsa_rope's angle; pair p turns by axis p % 3
+    position, count = 13, 30
+    c = chunk_case(7, 4, 2, 64, position, count)
+    outs = []
+    first = position // 4 * 4
+    own = np.repeat(np.arange(first, position + count, dtype=np.uint32)[:, None], 3, axis=1)
+    axes = own.copy()
+    axes[5:25, 1] += 7          # an image's rows: other positions on the h and w axes
+    axes[5:25, 2] += 11
+    for table in (None, own, axes):
+        iq, packed, state, index_state = c["iq"].copy(), c["packed"].copy(), c["state"].copy(), c["index_state"].copy()
+        oracle.qsa_normalize_chunk(c["qgate"], c["key"], c["value"], iq, c["ik"], position, 4, 2, *c["norms"], packed, state, 64, index_state,
+                                   rope_rows=table, rope_first=first)
+        outs.append((iq, packed, state, index_state))
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+    queries = [o[1][:count * 4 * 256].reshape(count, 4, 256) for o in outs]
+    turned = np.abs(queries[2] - queries[0]).max(axis=1)        # [token][column]
+    rows = np.arange(5, 25) - (position - first)                # the table's rows 5..24 are tokens 4..23
+    pairs = np.arange(32)
+    assert not turned[:, 64:].any(), "columns from 64 on pass"
+    assert not turned[:rows[0]].any() and not turned[rows[-1] + 1:].any(), "text rows turn as before"
+    assert not turned[rows][:, pairs[pairs % 3 == 0]].any(), "the t axis kept its position"
+    assert (turned[rows][:, pairs[pairs % 3 == 1]] > 0).any() and (turned[rows][:, pairs[pairs % 3 == 2]] > 0).any()
+    # a pooled block turns by the table's row of its first position
+    blocks = [o[3][:c["pool"] * 128].reshape(128, c["pool"]) for o in outs]
+    changed = np.abs(blocks[2] - blocks[0]).max(axis=0) > 0
+    begins = np.arange(c["pool"]) * 4
+    inside = (begins >= first + 5) & (begins < first + 25) & (begins + 4 <= position + count)
+    assert changed[inside].all() and not changed[~inside].any()
