@@ -50,8 +50,10 @@ int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* outp
 
 /* ---- K/V format and staging ---- */
 /* gpu/straydog_gpu.h:113. row: 272 (Q8_0) or 512 (FP16: a value's nearest FP16). FP16 rows are written (sdx_kv_write, the fused
-   fronts), decoded, grown and attended by sd_attention_sequence; the tensor-core kernels (sdx_qsa_decode*, sdx_attention_batch,
-   sdx_qsa_attention_rows, sdx_qsa_attention_gathered, sdx_qsa_prompt) read Q8_0 rows only and refuse a handle set to FP16 rows. */
+   fronts), decoded, grown and attended by sd_attention_sequence and by the decode seam's selection-list attention
+   (sdx_qsa_attention_rows, sdx_qsa_attention_gathered: the rows' halves are the tensor cores' operands as they lie); the dense batch
+   decode and the prompt kernel (sdx_qsa_decode*, sdx_attention_batch, sdx_qsa_prompt) read Q8_0 rows only and refuse a handle set to
+   FP16 rows. */
 int sd_kv_format(void* handle, uint32_t row);
 /* gpu/straydog_gpu.h:114. The VRAM stage of host-resident K/V: an allocation of rows * 4096 bytes. With K/V resident in HBM the
    stage is registered and validated but never needed; sdx_qsa_attention_gathered copies a host-resident state's selected blocks

@@ -305,7 +305,8 @@ int sd_buffer_read(void* handle, const void* buffer, uint64_t offset, void* outp
 }
 
 // gpu/kernels.cpp:4266-4275: 512 (FP16 rows) or 272 (Q8_0 rows). The codec, the fused fronts and the FP32 check path
-// (sd_attention_sequence) handle both; the tensor-core kernels stream Q8_0 rows only and refuse FP16 rows at the call.
+// (sd_attention_sequence) handle both, and so does the selection-list attention of the decode seam (sdx_qsa_attention_rows, _gathered);
+// the dense batch decode and the prompt kernel stream Q8_0 rows only and refuse FP16 rows at the call.
 int sd_kv_format(void* handle, uint32_t row) {
     try {
         auto& value = device(handle);

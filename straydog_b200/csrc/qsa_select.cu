@@ -17,14 +17,22 @@
 // scale applied in FP32, softmax in FP32 (exp2 domain), V^T.P' with the value block's scale folded into P'. The queries arrive
 // as F32 and the weights are F32, so both enter the tensor cores as FP16 hi + lo pairs (two products each): nothing is rounded
 // to 11 bits on the way, and the result differs from the reference's FP32 kernels by summation order only.
+// FP16 rows (sd_kv_format(512): 256 halves a row) take the same kernel without the int8 steps: the rows' halves are the tensor
+// cores' operands as they lie (a row every 528 bytes of shared memory, so that eight rows fall on eight bank groups), the value
+// fragments come through transposing ldmatrix loads of 16-bit units, and the rows of dead slots are zeroed (a stale NaN times a
+// zero weight would be a NaN).
 #include "common.cuh"
 #include "../../include/straydog_gpu_b200.h"
 
 namespace sdb {
 
 constexpr int kSelTile = 16, kSelTiles = 4, kSelChunk = kSelTile * kSelTiles;      // slots a tile, tiles a chunk
-constexpr int kSelTileBytes = 2 * kSelTile * int(kv_row_q8);                       // K rows then V rows
-constexpr size_t kSelSmem = size_t(kSelTiles) * kSelTileBytes + kSelTiles * 8 + kSelChunk * 4 + 16;
+template <bool F16> struct SelShape {
+    static constexpr int kRow = F16 ? int(kv_row_f16) : int(kv_row_q8);            // a row in memory
+    static constexpr int kPitch = F16 ? int(kv_row_f16) + 16 : int(kv_row_q8);     // a row in shared memory
+    static constexpr int kTileBytes = 2 * kSelTile * kPitch;                       // K rows then V rows
+    static constexpr size_t kSmem = size_t(kSelTiles) * kTileBytes + kSelTiles * 8 + kSelChunk * 4 + 16;
+};
 
 struct SelectArgs {
     const uint8_t* state;      // 2 * kv_heads planes of `context` rows
@@ -61,7 +69,10 @@ __device__ __forceinline__ void split_pair(float a, float b, uint32_t& hi, uint3
 }
 
 // grid (chunks, kv_heads, steps); block = 32 x ceil(group / 8) threads: warp w takes query heads 8w .. of the group
+template <bool F16>
 __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
+    using S = SelShape<F16>;
+    constexpr int kRow = S::kRow, kPitch = S::kPitch, kSelTileBytes = S::kTileBytes;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kSelTiles) * kSelTileBytes);
     int* tokens = reinterpret_cast<int*>(bars + kSelTiles);
@@ -90,18 +101,23 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
             tokens[half * 32 + lane] = token;
             // two tiles per half: lanes 0-15 and 16-31
             const unsigned live = __ballot_sync(0xffffffffu, token >= 0);
-            if (lane == 0 && (live & 0xffffu)) mbar_expect_tx(&bars[2 * half], __popc(live & 0xffffu) * 2 * kv_row_q8);
-            if (lane == 16 && (live >> 16)) mbar_expect_tx(&bars[2 * half + 1], __popc(live >> 16) * 2 * kv_row_q8);
+            if (lane == 0 && (live & 0xffffu)) mbar_expect_tx(&bars[2 * half], __popc(live & 0xffffu) * 2 * kRow);
+            if (lane == 16 && (live >> 16)) mbar_expect_tx(&bars[2 * half + 1], __popc(live >> 16) * 2 * kRow);
             __syncwarp();
+            const int tile = 2 * half + lane / 16, r = lane % 16;
+            uint8_t* dst = smem + size_t(tile) * kSelTileBytes + r * kPitch;
             if (token >= 0) {
                 // a recent position is read from the ring mirror of a host-resident state (gpu/sparse_attention_compute.hpp:65-68)
                 const bool cached = a.mirror && size_t(token) + a.mirror_rows > last + 8;
                 const uint8_t* source = cached ? a.mirror : a.state;
                 const size_t capacity = cached ? a.mirror_rows : a.context, at = cached ? size_t(token) % a.mirror_rows : size_t(token);
-                const int tile = 2 * half + lane / 16, r = lane % 16;
-                uint8_t* dst = smem + size_t(tile) * kSelTileBytes + r * kv_row_q8;
-                bulk_g2s(dst, source + (kv * capacity + at) * kv_row_q8, kv_row_q8, &bars[tile]);
-                bulk_g2s(dst + kSelTile * kv_row_q8, source + ((a.kv_heads + kv) * capacity + at) * kv_row_q8, kv_row_q8, &bars[tile]);
+                bulk_g2s(dst, source + (kv * capacity + at) * kRow, kRow, &bars[tile]);
+                bulk_g2s(dst + kSelTile * kPitch, source + ((a.kv_heads + kv) * capacity + at) * kRow, kRow, &bars[tile]);
+            } else if (F16) {   // (a dead slot's halves enter the products as they lie: zeros)
+                for (int i = 0; i < kRow / 16; ++i) {
+                    reinterpret_cast<uint4*>(dst)[i] = make_uint4(0, 0, 0, 0);
+                    reinterpret_cast<uint4*>(dst + kSelTile * kPitch)[i] = make_uint4(0, 0, 0, 0);
+                }
             }
         }
     }
@@ -133,7 +149,9 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
     const int ka = sel_tile_row(2 * t), kb = sel_tile_row(2 * t + 1);
     // (a block's value bytes come through one transposing ldmatrix, as in the dense decode kernel: matrix m holds the keys
     //  k-index j -> sel_tile_row(j) + 8 (m & 1) and the 16-bit units of columns 16 (m >> 1) ..)
-    const uint32_t v_lane = uint32_t((sel_tile_row(lane % 8) + 8 * ((lane / 8) & 1)) * int(kv_row_q8) + 16 * (lane / 16));
+    //  FP16 rows: matrix m holds the keys sel_tile_row(j) + 8 (m >> 1) and the columns 8 (m & 1) .. of a 16-column piece: the A fragment's order)
+    const uint32_t v_lane = F16 ? uint32_t((sel_tile_row(lane % 8) + 8 * (lane / 16)) * kPitch + 16 * ((lane / 8) & 1))
+                                : uint32_t((sel_tile_row(lane % 8) + 8 * ((lane / 8) & 1)) * kPitch + 16 * (lane / 16));
 
     #pragma unroll 1
     for (int tile = 0; tile < kSelTiles; ++tile) {
@@ -143,12 +161,25 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
         if (!live) continue;
         if (!mbar_wait(&bars[tile], 0)) { if (lane == 0) atomicExch(a.status, 1); drain_delay(); return; }
         const uint8_t* kt = smem + size_t(tile) * kSelTileBytes;
-        const uint8_t* vt = kt + kSelTile * kv_row_q8;
+        const uint8_t* vt = kt + kSelTile * kPitch;
         const uint32_t vt_address = smem_u32(vt);
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if constexpr (F16) {
+            // ---- S = K Q^T: the rows' halves are the A fragments (columns 32 b + 8 t .. + 7 of rows r0 and r1 a block) ----
+            #pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                const uint4 w0 = *reinterpret_cast<const uint4*>(kt + r0 * kPitch + 64 * b + 16 * t);
+                const uint4 w1 = *reinterpret_cast<const uint4*>(kt + r1 * kPitch + 64 * b + 16 * t);
+                const uint32_t af[4] = {w0.x, w1.x, w0.y, w1.y}, ag[4] = {w0.z, w1.z, w0.w, w1.w};
+                mma_f16(s, af, ql[b][0], ql[b][1]);
+                mma_f16(s, af, qh[b][0], qh[b][1]);
+                mma_f16(s, ag, ql[b][2], ql[b][3]);
+                mma_f16(s, ag, qh[b][2], qh[b][3]);
+            }
+        } else {
         // ---- S = K Q^T per 32-column block, then the block's scale (rows nobody fetched hold stale bytes: masked below) ----
         const uint4 ks0 = *reinterpret_cast<const uint4*>(kt + r0 * kv_row_q8 + 256);
         const uint4 ks1 = *reinterpret_cast<const uint4*>(kt + r1 * kv_row_q8 + 256);
-        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         #pragma unroll
         for (int b = 0; b < 8; ++b) {
             uint2 w0 = *reinterpret_cast<const uint2*>(kt + r0 * kv_row_q8 + 32 * b + 8 * t);
@@ -164,6 +195,7 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
             const float c0 = (live >> r0 & 1) ? sel_half_at(ks0, b) : 0.0f, c1 = (live >> r1 & 1) ? sel_half_at(ks1, b) : 0.0f;
             s[0] = fmaf(acc[0], c0, s[0]); s[1] = fmaf(acc[1], c0, s[1]);
             s[2] = fmaf(acc[2], c1, s[2]); s[3] = fmaf(acc[3], c1, s[3]);
+        }
         }
         const bool live0 = live >> r0 & 1, live1 = live >> r1 & 1;
         float x[4] = {live0 ? s[0] * a.scale_log2 : -INFINITY, live0 ? s[1] * a.scale_log2 : -INFINITY,
@@ -195,6 +227,22 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
             const uint32_t lo2 = movmatrix_trans(prmt(u2, u3, 0x5410u)), hi2 = movmatrix_trans(prmt(u2, u3, 0x7632u));
             pc = __uint_as_float(prmt(lo2, hi2, 0x5410u)); pd = __uint_as_float(prmt(lo2, hi2, 0x7632u));
         }
+        if constexpr (F16) {
+            // ---- O^T += V^T P: P as hi + lo; the value fragments of a 16-column piece through one transposing ldmatrix ----
+            uint32_t ph0, pl0, ph1, pl1;
+            split_pair(pa, pb, ph0, pl0);
+            split_pair(pc, pd, ph1, pl1);
+            #pragma unroll
+            for (int b = 0; b < 8; ++b)
+                #pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    uint32_t w[4];
+                    ldmatrix_x4_trans(w, vt_address + v_lane + 64 * b + 32 * i);
+                    mma_f16(o[b][i], w, pl0, pl1);
+                    mma_f16(o[b][i], w, ph0, ph1);
+                }
+            continue;
+        }
         // ---- O^T += V^T P': the value block's scale folded into P' in FP32, P' as hi + lo ----
         uint4 va = *reinterpret_cast<const uint4*>(vt + ka * kv_row_q8 + 256);
         uint4 vb = *reinterpret_cast<const uint4*>(vt + kb * kv_row_q8 + 256);
@@ -221,7 +269,8 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
             mma_f16(o[b][1], ag, ph0, ph1);
         }
     }
-    // ---- the chunk's partial: o[b][i][c] is head 2t + (c & 1) of this warp's eight, column 32b + 16i + 2g + (c >> 1) ----
+    // ---- the chunk's partial: o[b][i][c] is head 2t + (c & 1) of this warp's eight, column 32b + 16i + 2g + (c >> 1)
+    //      (FP16 rows: column 32b + 16i + g + 8 (c >> 1), the tensor cores' own order) ----
     #pragma unroll
     for (int offset = 4; offset < 32; offset *= 2) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, offset);
@@ -236,8 +285,13 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
         for (int b = 0; b < 8; ++b)
             #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const int column = 32 * b + 16 * i + 2 * g;
-                *reinterpret_cast<float2*>(mine + column) = make_float2(o[b][i][which], o[b][i][2 + which]);
+                if constexpr (F16) {
+                    mine[32 * b + 16 * i + g] = o[b][i][which];
+                    mine[32 * b + 16 * i + g + 8] = o[b][i][2 + which];
+                } else {
+                    const int column = 32 * b + 16 * i + 2 * g;
+                    *reinterpret_cast<float2*>(mine + column) = make_float2(o[b][i][which], o[b][i][2 + which]);
+                }
             }
         if (g == 0) { mine[256] = which ? m1 : m0; mine[257] = which ? l1 : l0; }
     }
@@ -280,11 +334,14 @@ static void launch_select(Device& value, SelectArgs& args, size_t row0, size_t r
     args.status = status_word(value);
     static bool configured[64] = {};
     if (!configured[value.ordinal & 63]) {
-        SDB_CHECK(cudaFuncSetAttribute(qsa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSelSmem)));
+        SDB_CHECK(cudaFuncSetAttribute(qsa_select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SelShape<false>::kSmem)));
+        SDB_CHECK(cudaFuncSetAttribute(qsa_select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SelShape<true>::kSmem)));
         configured[value.ordinal & 63] = true;
     }
     const unsigned warps = unsigned((args.group + 7) / 8);
-    qsa_select_kernel<<<dim3(unsigned(args.chunks), unsigned(args.kv_heads), unsigned(rows)), 32 * warps, kSelSmem, value.stream>>>(args);
+    const dim3 grid(unsigned(args.chunks), unsigned(args.kv_heads), unsigned(rows));
+    if (value.kv_row == kv_row_f16) qsa_select_kernel<true><<<grid, 32 * warps, SelShape<true>::kSmem, value.stream>>>(args);
+    else qsa_select_kernel<false><<<grid, 32 * warps, SelShape<false>::kSmem, value.stream>>>(args);
     qsa_select_merge_kernel<<<dim3(unsigned(args.heads), unsigned(rows)), 256, 0, value.stream>>>(args, gates, gate_stride, out);
     value.launches += 2;
 }
@@ -342,16 +399,16 @@ __global__ void __launch_bounds__(1024) union_place_kernel(uint32_t* __restrict_
 // Union place p's four rows of every plane, from the K/V into rows 4 p .. 4 p + 3 of the stage; a CTA per place, 16-byte pieces.
 __global__ void __launch_bounds__(256) union_gather_kernel(const uint8_t* __restrict__ state, size_t context, size_t planes,
                                                            const uint32_t* __restrict__ blocks, const uint32_t* __restrict__ total,
-                                                           uint8_t* __restrict__ stage, size_t capacity) {
-    constexpr size_t pieces = kv_row_q8 / 16;
+                                                           uint8_t* __restrict__ stage, size_t capacity, size_t kv_row) {
+    const size_t pieces = kv_row / 16;
     const size_t place = blockIdx.x;
     if (place >= *total) return;
     const size_t block = blocks[place];
     for (size_t i = threadIdx.x; i < planes * 4 * pieces; i += 256) {
         const size_t plane = i / (4 * pieces), row = i / pieces % 4, piece = i % pieces, position = block * 4 + row;
         if (position >= context) continue;
-        reinterpret_cast<uint4*>(stage + (plane * capacity + place * 4 + row) * kv_row_q8)[piece] =
-            __ldg(reinterpret_cast<const uint4*>(state + (plane * context + position) * kv_row_q8) + piece);
+        reinterpret_cast<uint4*>(stage + (plane * capacity + place * 4 + row) * kv_row)[piece] =
+            __ldg(reinterpret_cast<const uint4*>(state + (plane * context + position) * kv_row) + piece);
     }
 }
 // Rows [first, first + gridDim.x)'s selections renumbered to the union's places, into the library's copy of the packed rows (the
@@ -379,17 +436,16 @@ extern "C" int sdx_qsa_attention_rows(void* handle, const void* state, uint64_t 
                                       uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float scale, const float* input,
                                       const void* mirror, uint64_t mirror_rows, const float* gates, uint64_t gate_stride, float* out) {
     SDB_OP_BEGIN
-    if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
     const uint64_t group = kv_heads ? heads / kv_heads : 0;
     if (!context || context > (uint64_t(1) << 24) || !steps || steps > max_batch || !selected || selected > 8192 || !heads || !kv_heads ||
         heads % kv_heads || group > 16 || kv_heads > 65535 || (mirror && !mirror_rows) || base > context)
         throw std::runtime_error("invalid Straydog attention dimensions");
     const size_t packed = checked_product({steps, heads * 256 + kv_heads * 512 + selected + 1, 4});
-    span(value, state, checked_product({context, 2 * kv_heads, kv_row_q8}), "a K/V state");
+    span(value, state, checked_product({context, 2 * kv_heads, value.kv_row}), "a K/V state");
     span(value, input, packed, "packed attention rows");
     span(value, out, checked_product({steps, heads, 256, 4}), "an attention output");
     if (positions) span(value, positions, steps * 4, "attention positions");
-    if (mirror) span(value, mirror, checked_product({mirror_rows, 2 * kv_heads, kv_row_q8}), "a K/V mirror");
+    if (mirror) span(value, mirror, checked_product({mirror_rows, 2 * kv_heads, value.kv_row}), "a K/V mirror");
     if (gates) span(value, gates, checked_product({(steps - 1) * gate_stride + heads * 512, 4}), "attention gates");
     if (reinterpret_cast<uintptr_t>(state) % 16 || reinterpret_cast<uintptr_t>(mirror) % 16 || reinterpret_cast<uintptr_t>(input) % 16)
         throw std::runtime_error("Straydog attention operands must be 16-byte aligned");
@@ -413,16 +469,15 @@ extern "C" int sdx_qsa_attention_gathered(void* handle, const void* state, uint6
                                           uint64_t steps, uint64_t selected, uint64_t heads, uint64_t kv_heads, float scale, const float* input,
                                           const float* gates, uint64_t gate_stride, float* out, uint64_t* passes) {
     SDB_OP_BEGIN
-    if (value.kv_row != kv_row_q8) throw std::runtime_error("this Straydog build's attention reads Q8_0 K/V rows only");
     const uint64_t group = kv_heads ? heads / kv_heads : 0;
     if (!context || context > (uint64_t(1) << 24) || !steps || steps > max_batch || !selected || selected > 8192 || !heads || !kv_heads ||
         heads % kv_heads || group > 16 || kv_heads > 65535 || base > context)
         throw std::runtime_error("invalid Straydog attention dimensions");
     if (!value.kv_stage) throw std::runtime_error("no Straydog K/V stage is registered");
-    const size_t planes = 2 * kv_heads, capacity = size_t(value.kv_stage_rows) * 4096 / (kv_row_q8 * planes);
+    const size_t planes = 2 * kv_heads, capacity = size_t(value.kv_stage_rows) * 4096 / (value.kv_row * planes);
     if (capacity < 4) throw std::runtime_error("invalid Straydog K/V stage");
     const size_t packed = checked_product({steps, heads * 256 + kv_heads * 512 + selected + 1, 4});
-    span(value, state, checked_product({context, planes, kv_row_q8}), "a K/V state");
+    span(value, state, checked_product({context, planes, value.kv_row}), "a K/V state");
     span(value, input, packed, "packed attention rows");
     span(value, out, checked_product({steps, heads, 256, 4}), "an attention output");
     if (positions) span(value, positions, steps * 4, "attention positions");
@@ -459,7 +514,7 @@ extern "C" int sdx_qsa_attention_gathered(void* handle, const void* state, uint6
         }
         if (size_t(total) * 4 <= capacity) {
             if (total) {
-                union_gather_kernel<<<total, 256, 0, value.stream>>>(args.state, context, planes, blocks, places + end, stage, capacity);
+                union_gather_kernel<<<total, 256, 0, value.stream>>>(args.state, context, planes, blocks, places + end, stage, capacity, value.kv_row);
                 ++value.launches;
             }
             union_renumber_kernel<<<unsigned(count), 256, 0, value.stream>>>(args, first, places, renumbered);

@@ -70,8 +70,9 @@ def test_kv_stage_registration_is_validated(gpu):
 
 def test_fp16_rows_are_written_decoded_and_attended_by_the_check_path():
     # gpu/kernels.cpp:4266-4275 takes 512 (FP16 rows) and 272 (Q8_0 rows). FP16 rows (a value's nearest FP16, gpu/kernels.cpp:42, 70)
-    # are written, decoded and attended by sd_attention_sequence, the path Q8_0 results are checked against; the tensor-core decode
-    # and prompt kernels read Q8_0 rows only and say so at the call instead of misreading FP16 rows
+    # are written, decoded and attended by sd_attention_sequence, the path Q8_0 results are checked against (the selection-list kernel
+    # reads them too: test_gpu_qsa_select.py); the dense batch decode and the prompt kernel read Q8_0 rows only and say so at the call
+    # instead of misreading FP16 rows
     from straydog_b200.backend import Backend, StraydogError
     from util import attention_sequence_input
     rng = np.random.default_rng(21)

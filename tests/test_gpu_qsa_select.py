@@ -167,3 +167,79 @@ def test_a_host_resident_state_is_attended_through_the_gathered_union(gpu, stage
     from straydog_b200.backend import StraydogError
     with pytest.raises(StraydogError, match="no Straydog K/V stage"):
         gpu.qsa_attention_gathered(device_state.pointer, context, base, None, steps, selected, heads, kv_heads, 0.0625, inp.pointer, out.pointer)
+
+
+def dense_f64(planes, packed, steps, selected, heads, kv_heads, base, context, scale=0.0625):
+    """The definition in float64 over FP16 rows' values: softmax of q . k over the row's live slots, times v."""
+    group = heads // kv_heads
+    q = packed[:steps * heads * 256].reshape(steps, heads, 256).astype(np.float64)
+    at = steps * (heads + 2 * kv_heads) * 256
+    lists, counts = packed[at:at + steps * selected].reshape(steps, selected), packed[at + steps * selected:]
+    out = np.zeros((steps, heads, 256))
+    for r in range(steps):
+        live = [int(x) for x in lists[r, :int(counts[r])] if 0 <= x <= base + r and x < context]
+        for h in range(heads):
+            scores = planes[h // group, live] @ q[r, h] * scale
+            w = np.exp(scores - scores.max())
+            out[r, h] = (w / w.sum()) @ planes[kv_heads + h // group, live]
+    return out
+
+
+@pytest.mark.parametrize("steps,selected,base,context,heads,kv_heads,kind", [(5, 64, 40, 96, 24, 2, "sparse"), (4, 2052, 3000, 4096, 24, 2, "sparse"),
+                                                                             (8, 700, 1500, 2048, 16, 2, "sparse"), (3, 130, 200, 256, 12, 1, "dense")])
+def test_fp16_rows_are_attended_on_the_tensor_cores(steps, selected, base, context, heads, kv_heads, kind):
+    """sd_kv_format(512): the selection-list kernel reads FP16 rows (256 halves) as the tensor cores' operands. Held to the float64
+    definition over the rows' values, to the FP32 check path (sd_attention_sequence, at its own 24 / 2 heads) and to the contract that a
+    row's bits do not depend on the rows beside it; dead slots (lists with -1, positions past the row's own) carry no weight."""
+    from straydog_b200.backend import Backend
+    rng = np.random.default_rng(steps * 100 + selected)
+    with Backend(0, 1 << 29) as gpu:
+        gpu.kv_format(512)
+        filled = rng.normal(0, 1, (2 * kv_heads, context, 256)).astype(np.float16)
+        filled[:, base:] = 0
+        packed = attention_sequence_input(rng, steps, selected, base, context, kind, heads, kv_heads)
+        state = gpu.allocate(filled.nbytes)
+        gpu.write(state, filled)
+        got = attend(gpu, state, context, base, steps, selected, heads, kv_heads, packed)   # (writes the rows' keys and values first)
+        rows = gpu.download(state, np.empty_like(filled))
+        k = packed[steps * heads * 256:steps * (heads + kv_heads) * 256].reshape(steps, kv_heads, 256)
+        assert np.array_equal(rows[:kv_heads, base:base + steps].view(np.uint16), k.transpose(1, 0, 2).astype(np.float16).view(np.uint16))
+        want = dense_f64(rows.astype(np.float64), packed, steps, selected, heads, kv_heads, base, context)
+        assert np.abs(got - want).max() < 5e-5, np.abs(got - want).max()
+        if (heads, kv_heads) == (24, 2):
+            check = gpu.attention_sequence(state, context, base, steps, selected, packed)
+            assert np.abs(got - check).max() < 1e-4
+        positions = np.arange(base, base + steps, dtype=np.uint32)
+        for r in (0, steps - 1):
+            width = heads * 256 + kv_heads * 512
+            q_at, k_at, v_at = r * heads * 256, steps * heads * 256 + r * kv_heads * 256, steps * (heads + kv_heads) * 256 + r * kv_heads * 256
+            at = steps * (heads + 2 * kv_heads) * 256
+            one = np.concatenate([packed[q_at:q_at + heads * 256], packed[k_at:k_at + kv_heads * 256], packed[v_at:v_at + kv_heads * 256],
+                                  packed[at + r * selected:at + (r + 1) * selected], packed[at + steps * selected + r:at + steps * selected + r + 1]])
+            alone = attend(gpu, state, context, base, 1, selected, heads, kv_heads, one, positions=positions[r:r + 1])
+            assert np.array_equal(alone[0].view(np.uint32), got[r].view(np.uint32)), r
+        gpu.release(state)
+
+
+def test_fp16_rows_of_a_host_resident_state_go_through_the_gathered_union():
+    from straydog_b200.backend import Backend
+    rng = np.random.default_rng(78)
+    steps, selected, base, context, heads, kv_heads = 8, 600, 3000, 4096, 16, 2
+    with Backend(0, 1 << 29) as gpu:
+        gpu.kv_format(512)
+        filled = rng.normal(0, 1, (2 * kv_heads, context, 256)).astype(np.float16)
+        packed = attention_sequence_input(rng, steps, selected, base, context, "sparse", heads, kv_heads)
+        positions = np.arange(base, base + steps, dtype=np.uint32)
+        device_state = gpu.allocate(filled.nbytes)
+        gpu.write(device_state, filled)
+        want = attend(gpu, device_state, context, base, steps, selected, heads, kv_heads, packed, positions=positions)
+        host_state = gpu.host_state(filled.nbytes)
+        gpu.write(host_state, filled)
+        stage = gpu.allocate(1400 * 4096)
+        gpu.kv_stage(stage, 1400)
+        inp, pos, out = gpu.upload(packed), gpu.upload(positions), gpu.buffer(steps * heads * 256 * 4)
+        passes = gpu.qsa_attention_gathered(host_state, context, base, pos.pointer, steps, selected, heads, kv_heads, 0.0625, inp.pointer, out.pointer)
+        assert passes > 1 and gpu.decode_status() == 0
+        assert np.array_equal(gpu.read(out, np.float32, want.shape).view(np.uint32), want.view(np.uint32))
+        for b in (device_state, inp, pos, out, stage, host_state):
+            gpu.release(b)
