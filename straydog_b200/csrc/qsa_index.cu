@@ -20,7 +20,8 @@
 
 namespace sdb {
 
-void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block);
+void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block,
+                  bool dependent);
 
 constexpr int kIndexRows = 8, kIndexBlocks = 64, kIndexKeep = 512, kIndexOwn = 4;
 
@@ -32,6 +33,7 @@ __global__ void __launch_bounds__(2 * kIndexBlocks) qsa_block_scores_kernel(cons
                                                                             size_t pool, size_t base, const uint32_t* __restrict__ positions, size_t steps,
                                                                             float* __restrict__ scores) {
     __shared__ __align__(16) float q[128][kIndexRows * 4];   // [column][row * 4 + head]
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // (the choice queued behind this kernel waits for its end before it reads the scores)
     const int t = threadIdx.x % kIndexBlocks, part = threadIdx.x / kIndexBlocks;   // (a warp is of one part: its query reads are broadcasts)
     const size_t row0 = size_t(blockIdx.y) * kIndexRows, block = size_t(blockIdx.x) * kIndexBlocks + t;
     const int rows = int(min(size_t(kIndexRows), steps - row0));
@@ -96,6 +98,7 @@ __global__ void __launch_bounds__(256) qsa_expand_selection_kernel(const int32_t
                                                                    size_t steps, size_t selected, size_t row_floats, float* __restrict__ packed) {
     const size_t row = blockIdx.x, position = positions ? positions[row] : base + row, complete = (position + 1) / 4;
     const size_t index_start = steps * row_floats;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the chosen blocks are complete from here on
     float* indices = packed + index_start + row * selected;
     if (complete <= size_t(kIndexKeep)) {
         for (size_t i = threadIdx.x; i <= position; i += 256) indices[i] = float(i);
@@ -131,8 +134,19 @@ extern "C" int sdx_qsa_index_select(void* handle, const float* queries, uint64_t
         queries, size_t(query_stride), blocks, size_t(pool), size_t(base), positions, size_t(steps), scores);
     ++value.launches;
     SDB_CHECK(cudaGetLastError());
-    launch_top_k(value, scores, size_t(steps), size_t(pool), size_t(kIndexKeep), picked, nullptr, 0, 1);
-    qsa_expand_selection_kernel<<<unsigned(steps), 256, 0, value.stream>>>(picked, size_t(base), positions, size_t(steps), size_t(selected), row_floats, packed);
+    // (the three kernels as programmatic dependents: each is placed while the one before drains and starts at its end)
+    launch_top_k(value, scores, size_t(steps), size_t(pool), size_t(kIndexKeep), picked, nullptr, 0, 1, true);
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(unsigned(steps));
+    config.blockDim = dim3(256);
+    config.stream = value.stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    SDB_CHECK(cudaLaunchKernelEx(&config, qsa_expand_selection_kernel, static_cast<const int32_t*>(picked), size_t(base), positions, size_t(steps), size_t(selected),
+                                 row_floats, packed));
     ++value.launches;
     SDB_OP_END
 }

@@ -76,6 +76,8 @@ __global__ void __launch_bounds__(64) qsa_select_kernel(const SelectArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(kSelTiles) * kSelTileBytes);
     int* tokens = reinterpret_cast<int*>(bars + kSelTiles);
+    // the merge launched behind this kernel may take its place on the SMs now: it waits for this grid's end before it reads
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t chunk = blockIdx.x, kv = blockIdx.y, row = a.row0 + blockIdx.z;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, g = lane / 4, t = lane % 4;
     const size_t index_start = a.steps * (a.heads * 256 + a.kv_heads * 512);
@@ -306,6 +308,7 @@ __global__ void __launch_bounds__(256) qsa_select_merge_kernel(const SelectArgs 
     const size_t index_start = a.steps * (a.heads * 256 + a.kv_heads * 512);
     const size_t count = size_t(a.input[index_start + a.steps * a.selected + row]);
     const size_t used = min((count + kSelChunk - 1) / kSelChunk, a.chunks);
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the chunks' partials are complete and visible from here on
     const float* source = a.partial + (row * a.heads + head) * a.chunks * 258;
     float top = -INFINITY;
     for (size_t c = 0; c < used; ++c) top = fmaxf(top, source[c * 258 + 256]);
@@ -342,7 +345,17 @@ static void launch_select(Device& value, SelectArgs& args, size_t row0, size_t r
     const dim3 grid(unsigned(args.chunks), unsigned(args.kv_heads), unsigned(rows));
     if (value.kv_row == kv_row_f16) qsa_select_kernel<true><<<grid, 32 * warps, SelShape<true>::kSmem, value.stream>>>(args);
     else qsa_select_kernel<false><<<grid, 32 * warps, SelShape<false>::kSmem, value.stream>>>(args);
-    qsa_select_merge_kernel<<<dim3(unsigned(args.heads), unsigned(rows)), 256, 0, value.stream>>>(args, gates, gate_stride, out);
+    // programmatic dependent launch: the merge's blocks are placed while the chunks' kernel drains and start at its end
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(unsigned(args.heads), unsigned(rows));
+    config.blockDim = dim3(256);
+    config.stream = value.stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    SDB_CHECK(cudaLaunchKernelEx(&config, qsa_select_merge_kernel, static_cast<const SelectArgs>(args), gates, gate_stride, out));
     value.launches += 2;
 }
 

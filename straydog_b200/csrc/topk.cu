@@ -155,8 +155,12 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
     const size_t slice = ((groups + ranks - 1) / ranks + 3) & ~size_t(3);
     const size_t low = min(groups, size_t(rank) * slice), high = min(groups, low + slice);
 
+    // (launched as a programmatic dependent, this grid was placed while the kernel before it drained: that kernel's scores are complete
+    //  behind the wait; the kernel after this one may be placed now and waits for this grid's end the same way. Plain launches: no-ops.)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- read 1: the top 11 key bits ----
     for (uint32_t i = t; i < kBins; i += kThreads) hist_a[i] = 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
     // Slices of up to a million scores: sixteen private histograms (a pair of warps each), two 16-bit counts a word (bins b and b + 1024),
     // filled by plain shared-memory atomics and added up afterwards. A warp-wide match (one add per distinct bin of a warp) cost three
@@ -391,7 +395,9 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
 }  // namespace topk
 
 // rows x groups scores -> rows x k indices (with candidates: see top_k_kernel)
-void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block) {
+// dependent: launched as a programmatic dependent of the kernel queued before it (which issues griddepcontrol.launch_dependents)
+void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block,
+                  bool dependent) {
     static bool configured[64] = {};
     if (!configured[d.ordinal & 63]) {
         SDB_CHECK(cudaFuncSetAttribute(topk::top_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(topk::kSmem)));
@@ -405,10 +411,13 @@ void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, si
     config.blockDim = dim3{unsigned(topk::kThreads), 1, 1};
     config.dynamicSmemBytes = topk::kSmem;
     config.stream = d.stream;
-    cudaLaunchAttribute cluster{};
+    cudaLaunchAttribute attributes[2] = {};
+    cudaLaunchAttribute& cluster = attributes[0];
     cluster.id = cudaLaunchAttributeClusterDimension;
     cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
-    config.attrs = &cluster; config.numAttrs = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes; config.numAttrs = dependent ? 2 : 1;
     // A cluster of this size must fit the device (a 1024-thread block with all its shared memory per SM, the cluster's SMs in one
     // GPC): asked of the driver once per device and size; a size that does not fit is halved.
     static int fits[64][4] = {};   // [device][log2 size]: 0 unknown, 1 fits, -1 does not
@@ -450,7 +459,7 @@ int sd_op_top_k(void* handle, const float* scores, uint64_t rows, uint64_t group
         throw std::runtime_error("invalid Straydog top-k shape");
     span(value, scores, checked_product({rows, groups, 4}), "scores");
     span(value, out, checked_product({rows, k, 4}), "top-k indices");
-    launch_top_k(value, scores, size_t(rows), size_t(groups), size_t(k), out, nullptr, 0, 1);
+    launch_top_k(value, scores, size_t(rows), size_t(groups), size_t(k), out, nullptr, 0, 1, false);
     SDB_OP_END
 }
 
