@@ -333,7 +333,8 @@ int sdx_qsa_attention_gathered(void* handle, const void* state, uint64_t context
 /* One decode step of a batch from HOST buffers (the batched twin of sd_attention_sequence): for
    sequence s the new token's keys/values (k, v: [sequences][kv_heads][256] F32, host) are written
    to row bases[s] of states[s], then its query (q: [sequences][heads][256] FP16, host) attends rows
-   0..bases[s]; out [sequences][heads][256] F32, host. Copies both ways are inside the call. */
+   0..bases[s]; out [sequences][heads][256] F32, host. Copies both ways are inside the call; page-locked k, v and out are read and
+   written in place by the kernels instead (the same bits), which takes three of the four copies off the call. */
 int sdx_attention_batch(void* handle, void* const* states, const uint64_t* contexts, const uint64_t* bases, uint64_t sequences,
                         uint64_t heads, uint64_t kv_heads, float scale, const void* q, const float* k, const float* v, float* out);
 

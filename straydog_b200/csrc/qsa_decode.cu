@@ -581,9 +581,20 @@ void attention_batch(Device& d, void* const* states, const uint64_t* contexts, c
     const size_t k_at = (q_bytes + 255) / 256 * 256, v_at = k_at + (new_bytes + 255) / 256 * 256,
                  out_at = v_at + (new_bytes + 255) / 256 * 256, total = out_at + out_bytes;
     auto* work = static_cast<uint8_t*>(ensure(d, d.work, d.work_bytes, total));
+    // Page-locked host buffers are read and written in place by the kernels (the device's view of the same memory): the new rows by the
+    // append, the outputs by the merge, whose stores cross the bus while it runs instead of in a copy behind it. The queries, which every
+    // piece of a sequence reads again, are copied. Pageable buffers take the copies.
+    const auto in_place = [&](const void* host) -> void* {
+        cudaPointerAttributes attributes{};
+        if (cudaPointerGetAttributes(&attributes, host) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        return attributes.type == cudaMemoryTypeHost ? attributes.devicePointer : nullptr;
+    };
+    const float* k_device = static_cast<const float*>(in_place(k));
+    const float* v_device = static_cast<const float*>(in_place(v));
+    float* out_device = static_cast<float*>(in_place(out));
     SDB_CHECK(cudaMemcpyAsync(work, q, q_bytes, cudaMemcpyHostToDevice, d.stream));
-    SDB_CHECK(cudaMemcpyAsync(work + k_at, k, new_bytes, cudaMemcpyHostToDevice, d.stream));
-    SDB_CHECK(cudaMemcpyAsync(work + v_at, v, new_bytes, cudaMemcpyHostToDevice, d.stream));
+    if (!k_device) { SDB_CHECK(cudaMemcpyAsync(work + k_at, k, new_bytes, cudaMemcpyHostToDevice, d.stream)); k_device = reinterpret_cast<const float*>(work + k_at); }
+    if (!v_device) { SDB_CHECK(cudaMemcpyAsync(work + v_at, v, new_bytes, cudaMemcpyHostToDevice, d.stream)); v_device = reinterpret_cast<const float*>(work + v_at); }
     if (!d.batch_cache) d.batch_cache = std::make_shared<BatchCache>();
     BatchCache& cache = *static_cast<BatchCache*>(d.batch_cache.get());
     std::vector<uint32_t> tiles(sequences);
@@ -625,11 +636,11 @@ void attention_batch(Device& d, void* const* states, const uint64_t* contexts, c
     plan.status = status_word(d);
     // the new rows, appended by one launch over the work list's segments (plane bases and lengths)
     launch_kv_append(d, reinterpret_cast<const Segment*>(static_cast<uint8_t*>(cache.tables) + plan.segment_offset), host.segments.size(),
-                     reinterpret_cast<const float*>(work + k_at), reinterpret_cast<const float*>(work + v_at));
+                     k_device, v_device);
     SDB_CHECK(cudaGetLastError());
-    run_plan(d, plan, scale, work, reinterpret_cast<float*>(work + out_at));
+    run_plan(d, plan, scale, work, out_device ? out_device : reinterpret_cast<float*>(work + out_at));
     SDB_CHECK(cudaGetLastError());
-    SDB_CHECK(cudaMemcpyAsync(out, work + out_at, out_bytes, cudaMemcpyDeviceToHost, d.stream));
+    if (!out_device) SDB_CHECK(cudaMemcpyAsync(out, work + out_at, out_bytes, cudaMemcpyDeviceToHost, d.stream));
     SDB_CHECK(cudaStreamSynchronize(d.stream));
 }
 

@@ -193,6 +193,52 @@ def test_attention_batch_from_host_buffers(gpu):
         gpu.release(b)
 
 
+def test_page_locked_host_buffers_are_used_in_place_with_the_bits_of_the_copied_ones(gpu):
+    # page-locked buffers: the append reads the new rows and the merge writes the outputs in place (no copies of theirs); pageable
+    # buffers take the copies. The same states, rows and outputs either way, bit for bit; a mix of the two kinds as well.
+    import torch
+    rng = np.random.default_rng(701)
+    n, heads, kv_heads = 7, 16, 2
+    bases = [0, 15, 16, 200, 1023, 31, 700]
+    contexts = [64, 64, 64, 512, 1024, 64, 1024]
+    states_np = [q8_state(rng, c, kv_heads, filled=b) for c, b in zip(contexts, bases)]
+    q = queries_f16(rng, n, heads, 256)
+    k = rng.normal(0, 1, (n, kv_heads, 256)).astype(np.float32)
+    v = rng.normal(0, 1, (n, kv_heads, 256)).astype(np.float32)
+
+    def locked(a):
+        t = torch.from_numpy(a.copy()).pin_memory()
+        return t, t.numpy()
+    results = []
+    for kinds in ("pageable", "locked", "mixed"):
+        states = [gpu.upload(s) for s in states_np]
+        keep = []
+        def pick(a, lock):
+            if not lock:
+                return a.copy()
+            t, view = locked(a)
+            keep.append(t)
+            return view
+        qq = pick(q, kinds == "locked")
+        kk = pick(k, kinds != "pageable")
+        vv = pick(v, kinds == "locked")
+        out = pick(np.full((n, heads, 256), -7.0, np.float32), kinds != "pageable")
+        gpu.attention_batch(states, contexts, bases, heads, kv_heads, 1 / 16, qq, kk, vv, out)
+        results.append((out.copy(), [gpu.read(s, np.uint8, sn.shape) for s, sn in zip(states, states_np)]))
+        for b in states:
+            gpu.release(b)
+    for out, rows in results[1:]:
+        assert np.array_equal(out.view(np.uint32), results[0][0].view(np.uint32))
+        assert all(np.array_equal(a, b) for a, b in zip(rows, results[0][1]))
+    for s in range(n):
+        want_state = states_np[s].copy()
+        oracle.kv_write(want_state, contexts[s], kv_heads, bases[s], k[s:s + 1], v[s:s + 1])
+        assert np.array_equal(results[1][1][s], want_state)
+        want = oracle.gqa_decode_q8(want_state, contexts[s], bases[s] + 1, heads, kv_heads, q[s], 1 / 16, f64=True)
+        ok, worst = close(results[1][0][s], want)
+        assert ok, (s, worst)
+
+
 def test_batch_steps_reuse_the_work_list_until_a_sequence_enters_a_new_tile(gpu):
     # a run of decode steps: the entry keeps the step before's work list while no sequence crosses into a new 16-key tile and builds a
     # new one when one does (positions 15 -> 16, 31 -> 32 ...); another batch, another entry of the handle and a changed batch in
