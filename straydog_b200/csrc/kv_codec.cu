@@ -81,9 +81,9 @@ void launch_kv_write(Device& d, uint8_t* state, size_t context, size_t kv_heads,
     ++d.launches;
 }
 
-void launch_kv_append(Device& d, const Segment* segments, size_t count, const float* keys, const float* values) {
+void launch_kv_append(Device& d, const Segment* segments, size_t count, const float* keys, const float* values, cudaStream_t stream) {
     const unsigned grid = unsigned(std::min<size_t>((count * 16 + 7) / 8, size_t(d.sms) * 8));
-    kv_append_kernel<<<grid, 256, 0, d.stream>>>(segments, count, keys, values);
+    kv_append_kernel<<<grid, 256, 0, stream>>>(segments, count, keys, values);
     ++d.launches;
 }
 

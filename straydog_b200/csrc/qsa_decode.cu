@@ -508,7 +508,7 @@ int* status_word(Device& d) {
     return word;
 }
 
-void launch_kv_append(Device& d, const Segment* segments, size_t count, const float* keys, const float* values);
+void launch_kv_append(Device& d, const Segment* segments, size_t count, const float* keys, const float* values, cudaStream_t stream);
 
 void qsa_decode_dense(Device& d, const void* const* states, const uint64_t* contexts, const uint64_t* lengths, uint64_t sequences,
                       uint64_t heads, uint64_t kv_heads, float scale, const void* q, float* out) {
@@ -592,9 +592,6 @@ void attention_batch(Device& d, void* const* states, const uint64_t* contexts, c
     const float* k_device = static_cast<const float*>(in_place(k));
     const float* v_device = static_cast<const float*>(in_place(v));
     float* out_device = static_cast<float*>(in_place(out));
-    SDB_CHECK(cudaMemcpyAsync(work, q, q_bytes, cudaMemcpyHostToDevice, d.stream));
-    if (!k_device) { SDB_CHECK(cudaMemcpyAsync(work + k_at, k, new_bytes, cudaMemcpyHostToDevice, d.stream)); k_device = reinterpret_cast<const float*>(work + k_at); }
-    if (!v_device) { SDB_CHECK(cudaMemcpyAsync(work + v_at, v, new_bytes, cudaMemcpyHostToDevice, d.stream)); v_device = reinterpret_cast<const float*>(work + v_at); }
     if (!d.batch_cache) d.batch_cache = std::make_shared<BatchCache>();
     BatchCache& cache = *static_cast<BatchCache*>(d.batch_cache.get());
     std::vector<uint32_t> tiles(sequences);
@@ -605,6 +602,11 @@ void attention_batch(Device& d, void* const* states, const uint64_t* contexts, c
         serves = tiles[s] == cache.tiles[s] || (!d.fixed_cuts && tiles[s] > cache.tiles[s] && tiles[s] - cache.built[s] <= kCacheGrowth);
     HostTables& host = cache.host;
     DecodePlan& plan = cache.plan;
+    // The order of the queue: the work list first (a few tens of KB), then the append on the side stream (it needs the list's segments,
+    // and reads the new rows over the bus while it runs) beside the queries' copy on the main one; the decode waits for both. A list
+    // that has to be built is built while the queries' copy is in flight instead.
+    bool q_queued = false;
+    if (!serves) { SDB_CHECK(cudaMemcpyAsync(work, q, q_bytes, cudaMemcpyHostToDevice, d.stream)); q_queued = true; }
     // (the buffers grow on the first call of a size only)
     if (serves) {
         for (size_t i = 0; i < host.segments.size(); ++i) {
@@ -635,9 +637,14 @@ void attention_batch(Device& d, void* const* states, const uint64_t* contexts, c
     plan.partial = static_cast<float*>(d.partial);
     plan.status = status_word(d);
     // the new rows, appended by one launch over the work list's segments (plane bases and lengths)
+    const cudaStream_t side = side_stream_begin(d);
+    if (!k_device) { SDB_CHECK(cudaMemcpyAsync(work + k_at, k, new_bytes, cudaMemcpyHostToDevice, side)); k_device = reinterpret_cast<const float*>(work + k_at); }
+    if (!v_device) { SDB_CHECK(cudaMemcpyAsync(work + v_at, v, new_bytes, cudaMemcpyHostToDevice, side)); v_device = reinterpret_cast<const float*>(work + v_at); }
     launch_kv_append(d, reinterpret_cast<const Segment*>(static_cast<uint8_t*>(cache.tables) + plan.segment_offset), host.segments.size(),
-                     k_device, v_device);
+                     k_device, v_device, side);
     SDB_CHECK(cudaGetLastError());
+    if (!q_queued) SDB_CHECK(cudaMemcpyAsync(work, q, q_bytes, cudaMemcpyHostToDevice, d.stream));
+    side_stream_end(d);
     run_plan(d, plan, scale, work, out_device ? out_device : reinterpret_cast<float*>(work + out_at));
     SDB_CHECK(cudaGetLastError());
     if (!out_device) SDB_CHECK(cudaMemcpyAsync(out, work + out_at, out_bytes, cudaMemcpyDeviceToHost, d.stream));
