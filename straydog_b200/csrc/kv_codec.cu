@@ -57,6 +57,40 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const Segment* __restric
     }
 }
 
+// The same append with a warp a row (a segment's 256 keys or values): a lane takes 8 consecutive values in two 16-byte loads, so a row
+// crosses the bus (the new rows may lie in page-locked host memory, read in place) in two requests of 512 bytes instead of eight of
+// 128; a block is four lanes, its largest magnitude two shuffles. The arithmetic is q8_encode's, value by value.
+__global__ void __launch_bounds__(256) kv_append_wide_kernel(const Segment* __restrict__ segments, size_t count,
+                                                              const float* __restrict__ keys, const float* __restrict__ values) {
+    const unsigned lane = threadIdx.x % 32;
+    const size_t rows = 2 * count;
+    for (size_t row = (size_t(blockIdx.x) * blockDim.x + threadIdx.x) / 32; row < rows; row += size_t(gridDim.x) * blockDim.x / 32) {
+        const bool is_value = row >= count;
+        const size_t segment = is_value ? row - count : row;
+        const float4* source = reinterpret_cast<const float4*>((is_value ? values : keys) + segment * 256) + 2 * lane;
+        const float4 a = source[0], b = source[1];
+        const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        float top = 0.0f;
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) top = fmaxf(top, fabsf(x[i]));
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+        const __half scale_h = __float2half_rn(__fdiv_rn(top, 127.0f));
+        const float scale = __half2float(scale_h);
+        uint32_t packed[2] = {0, 0};
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            int q = scale > 0.0f ? __float2int_rn(__fdiv_rn(x[i], scale)) : 0;
+            q = q > 127 ? 127 : q < -127 ? -127 : q;
+            packed[i / 4] |= uint32_t(uint8_t(int8_t(q))) << (8 * (i % 4));
+        }
+        const Segment s = segments[segment];
+        uint8_t* target = const_cast<uint8_t*>(is_value ? s.values : s.keys) + size_t(s.length - 1) * kv_row_q8;
+        *reinterpret_cast<uint2*>(target + 8 * lane) = make_uint2(packed[0], packed[1]);
+        if (lane % 4 == 0) reinterpret_cast<__half*>(target + 256)[lane / 4] = scale_h;
+    }
+}
+
 // rows of 272 bytes -> rows of 256 F32: value = float(int8) * float(scale), one FP32 multiply; rows of 512 bytes: the FP16 values widened.
 template<bool F16>
 __global__ void __launch_bounds__(256) kv_decode_rows_kernel(const uint8_t* __restrict__ rows, size_t count, float* __restrict__ out) {
@@ -82,8 +116,12 @@ void launch_kv_write(Device& d, uint8_t* state, size_t context, size_t kv_heads,
 }
 
 void launch_kv_append(Device& d, const Segment* segments, size_t count, const float* keys, const float* values, cudaStream_t stream) {
-    const unsigned grid = unsigned(std::min<size_t>((count * 16 + 7) / 8, size_t(d.sms) * 8));
-    kv_append_kernel<<<grid, 256, 0, stream>>>(segments, count, keys, values);
+    if (reinterpret_cast<uintptr_t>(keys) % 16 == 0 && reinterpret_cast<uintptr_t>(values) % 16 == 0) {
+        kv_append_wide_kernel<<<unsigned(std::min<size_t>((count * 2 + 7) / 8, size_t(d.sms) * 8)), 256, 0, stream>>>(segments, count, keys, values);
+    } else {
+        const unsigned grid = unsigned(std::min<size_t>((count * 16 + 7) / 8, size_t(d.sms) * 8));
+        kv_append_kernel<<<grid, 256, 0, stream>>>(segments, count, keys, values);
+    }
     ++d.launches;
 }
 

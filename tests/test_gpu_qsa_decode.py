@@ -206,22 +206,25 @@ def test_page_locked_host_buffers_are_used_in_place_with_the_bits_of_the_copied_
     k = rng.normal(0, 1, (n, kv_heads, 256)).astype(np.float32)
     v = rng.normal(0, 1, (n, kv_heads, 256)).astype(np.float32)
 
-    def locked(a):
-        t = torch.from_numpy(a.copy()).pin_memory()
-        return t, t.numpy()
+    def locked(a, off=0):
+        # (off: the view starts `off` elements into the page-locked allocation: an address that is not 16-byte aligned)
+        t = torch.empty(a.size + off, dtype=torch.from_numpy(a).dtype).pin_memory()
+        view = t.numpy()[off:].reshape(a.shape)
+        view[...] = a
+        return t, view
     results = []
-    for kinds in ("pageable", "locked", "mixed"):
+    for kinds in ("pageable", "locked", "mixed", "off"):
         states = [gpu.upload(s) for s in states_np]
         keep = []
         def pick(a, lock):
             if not lock:
                 return a.copy()
-            t, view = locked(a)
+            t, view = locked(a, 1 if kinds == "off" else 0)
             keep.append(t)
             return view
         qq = pick(q, kinds == "locked")
         kk = pick(k, kinds != "pageable")
-        vv = pick(v, kinds == "locked")
+        vv = pick(v, kinds in ("locked", "off"))
         out = pick(np.full((n, heads, 256), -7.0, np.float32), kinds != "pageable")
         gpu.attention_batch(states, contexts, bases, heads, kv_heads, 1 / 16, qq, kk, vv, out)
         results.append((out.copy(), [gpu.read(s, np.uint8, sn.shape) for s, sn in zip(states, states_np)]))
