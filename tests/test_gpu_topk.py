@@ -71,6 +71,18 @@ def test_rows_that_leave_the_shared_lists_in_a_cluster(gpu):
     check(gpu, few, 2048)
 
 
+def test_slices_of_more_than_a_million_scores_keep_the_matching_count(gpu):
+    """A block's slice over 2^20 - 1024 scores no longer fits the first read's 16-bit private counts: it counts with the warp-wide match
+    instead. One row of nine million scores (eight blocks of 1 125 000), with ties at the k-th score; and a row that is one block's
+    (many rows) at 1 100 000."""
+    rng = np.random.default_rng(11)
+    scores = rng.normal(0, 1, (1, 9_000_000)).astype(np.float32)
+    scores[0, rng.choice(9_000_000, size=5000, replace=False)] = 4.25
+    check(gpu, scores, 3000)
+    scores = rng.normal(0, 1, (80, 1_100_000)).astype(np.float32)
+    check(gpu, scores, 64)
+
+
 def test_rounding_into_bf16_is_to_the_nearest_even(gpu):
     # tests/ds_state_bf16_gpu.rs:50-69
     values = XorShift(0x243F6A8885A308D3).floats_scaled(10_000, 1e3)
