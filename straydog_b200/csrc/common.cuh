@@ -80,6 +80,14 @@ void span_or_peer(Device& d, const void* pointer, size_t bytes, const char* what
 size_t allocation_bytes(Device& d, const void* base);   // requested bytes of the allocation that starts at `base`, 0 if none (takes the lock)
 void* ensure(Device& d, void*& slot, size_t& have, size_t bytes, bool pinned_host = false);
 int* status_word(Device& d);
+// top_k_kernel's other output (csrc/topk.cu): a row's chosen 4-position blocks written into its packed attention row as positions
+struct TopKExpand {
+    float* packed;               // null: off
+    size_t index_start, selected, steps, base;
+    const uint32_t* positions;   // a row's position, or null: base + row
+    uint32_t keep;
+};
+
 cudaStream_t side_stream_begin(Device& d);   // the side stream, made to wait for everything queued on d.stream so far
 void side_stream_end(Device& d);             // d.stream made to wait for everything queued on the side stream so far   // the device's word a kernel's bounded wait sets when it gives up (read by sdx_decode_status)
 

@@ -21,7 +21,7 @@
 namespace sdb {
 
 void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block,
-                  bool dependent);
+                  bool dependent, const TopKExpand* expand);
 
 __global__ void __launch_bounds__(256) rope_kernel(float* __restrict__ x, size_t count, size_t vectors, size_t width, size_t pairs,
                                                    const int32_t* __restrict__ positions, const float* __restrict__ frequencies, int inverse) {
@@ -407,7 +407,7 @@ int sd_op_index_candidates(void* handle, const float* scores, const int32_t* vis
     index_block_tops_kernel<<<dim3(unsigned((count + 255) / 256), unsigned(rows)), 256, 0, value.stream>>>(scores, visible, size_t(groups), size_t(block), size_t(count), scratch);
     ++value.launches;
     SDB_CHECK(cudaGetLastError());
-    launch_top_k(value, scratch, size_t(rows), size_t(count), size_t(blocks), out, nullptr, 0, 1, false);
+    launch_top_k(value, scratch, size_t(rows), size_t(count), size_t(blocks), out, nullptr, 0, 1, false, nullptr);
     SDB_OP_END
 }
 
@@ -445,7 +445,7 @@ int sd_op_index_select(void* handle, const float* q, const float* keys, const fl
         q_used = rotated;
     }
     launch_index_scores(value, q_used, keys, weights, visible, size_t(rows), size_t(groups), size_t(heads), size_t(dim), scale, scores, candidates, size_t(blocks), size_t(block ? block : 1));
-    launch_top_k(value, scores, size_t(rows), size_t(scored), size_t(k), out, candidates, size_t(blocks), size_t(block ? block : 1), false);
+    launch_top_k(value, scores, size_t(rows), size_t(scored), size_t(k), out, candidates, size_t(blocks), size_t(block ? block : 1), false, nullptr);
     SDB_OP_END
 }
 

@@ -14,14 +14,14 @@
 //
 // Here: one scores kernel for any number of rows (a thread owns a block and four rows' four running dots, so a key column value is
 // loaded once for 16 fused multiply-adds; the rows' queries sit in shared memory, a column's 32 values side by side), then the library's top-k kernel (two reads of a
-// row, ties by lowest index, ascending output: the same rule) and a kernel that expands the chosen blocks into the packed rows.
+// row, ties by lowest index, ascending output: the same rule), which writes the chosen blocks into the packed rows as positions itself.
 #include "common.cuh"
 #include "../../include/straydog_gpu_b200.h"
 
 namespace sdb {
 
 void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block,
-                  bool dependent);
+                  bool dependent, const TopKExpand* expand);
 
 constexpr int kIndexRows = 8, kIndexBlocks = 64, kIndexKeep = 512, kIndexOwn = 4;
 
@@ -93,24 +93,6 @@ __global__ void __launch_bounds__(2 * kIndexBlocks) qsa_block_scores_kernel(cons
     }
 }
 
-// grid steps: the row's list and count into the packed rows
-__global__ void __launch_bounds__(256) qsa_expand_selection_kernel(const int32_t* __restrict__ picked, size_t base, const uint32_t* __restrict__ positions,
-                                                                   size_t steps, size_t selected, size_t row_floats, float* __restrict__ packed) {
-    const size_t row = blockIdx.x, position = positions ? positions[row] : base + row, complete = (position + 1) / 4;
-    const size_t index_start = steps * row_floats;
-    asm volatile("griddepcontrol.wait;" ::: "memory");   // the chosen blocks are complete from here on
-    float* indices = packed + index_start + row * selected;
-    if (complete <= size_t(kIndexKeep)) {
-        for (size_t i = threadIdx.x; i <= position; i += 256) indices[i] = float(i);
-        if (threadIdx.x == 0) packed[index_start + steps * selected + row] = float(position + 1);
-        return;
-    }
-    for (size_t i = threadIdx.x; i < size_t(kIndexKeep) * 4; i += 256) indices[i] = float(size_t(picked[row * kIndexKeep + i / 4]) * 4 + i % 4);
-    const size_t head = size_t(kIndexKeep) * 4;
-    for (size_t i = threadIdx.x; complete * 4 + i <= position; i += 256) indices[head + i] = float(complete * 4 + i);
-    if (threadIdx.x == 0) packed[index_start + steps * selected + row] = float(head + position + 1 - complete * 4);
-}
-
 }  // namespace sdb
 
 using namespace sdb;
@@ -126,27 +108,16 @@ extern "C" int sdx_qsa_index_select(void* handle, const float* queries, uint64_t
     span(value, blocks, checked_product({128, pool, 4}), "pooled index keys");
     span(value, packed, checked_product({steps, row_floats + selected + 1, 4}), "packed attention rows");
     if (positions) span(value, positions, steps * 4, "attention positions");
-    // scores [steps][pool] and the chosen blocks [steps][512]: a library-owned workspace (make the first call of a size outside a capture)
-    const size_t scores_bytes = checked_product({steps, pool, 4});
-    auto* scores = static_cast<float*>(ensure(value, value.work, value.work_bytes, scores_bytes + checked_product({steps, size_t(kIndexKeep), 4})));
-    auto* picked = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(scores) + scores_bytes);
+    // scores [steps][pool]: a library-owned workspace (make the first call of a size outside a capture)
+    auto* scores = static_cast<float*>(ensure(value, value.work, value.work_bytes, checked_product({steps, pool, 4})));
     qsa_block_scores_kernel<<<dim3(unsigned((pool + kIndexBlocks - 1) / kIndexBlocks), unsigned((steps + kIndexRows - 1) / kIndexRows)), 2 * kIndexBlocks, 0, value.stream>>>(
         queries, size_t(query_stride), blocks, size_t(pool), size_t(base), positions, size_t(steps), scores);
     ++value.launches;
     SDB_CHECK(cudaGetLastError());
-    // (the three kernels as programmatic dependents: each is placed while the one before drains and starts at its end)
-    launch_top_k(value, scores, size_t(steps), size_t(pool), size_t(kIndexKeep), picked, nullptr, 0, 1, true);
-    cudaLaunchConfig_t config{};
-    config.gridDim = dim3(unsigned(steps));
-    config.blockDim = dim3(256);
-    config.stream = value.stream;
-    cudaLaunchAttribute attribute{};
-    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attribute.val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    SDB_CHECK(cudaLaunchKernelEx(&config, qsa_expand_selection_kernel, static_cast<const int32_t*>(picked), size_t(base), positions, size_t(steps), size_t(selected),
-                                 row_floats, packed));
-    ++value.launches;
+    // (the choice as a programmatic dependent of the scores: placed while they drain; it writes the rows' lists itself)
+    TopKExpand expand{};
+    expand.packed = packed; expand.index_start = size_t(steps) * row_floats; expand.selected = size_t(selected); expand.steps = size_t(steps);
+    expand.base = size_t(base); expand.positions = positions; expand.keep = uint32_t(kIndexKeep);
+    launch_top_k(value, scores, size_t(steps), size_t(pool), size_t(kIndexKeep), nullptr, nullptr, 0, 1, true, &expand);
     SDB_OP_END
 }

@@ -131,11 +131,16 @@ __device__ __forceinline__ void find_band(const uint32_t* hist, uint32_t bins, u
     __syncthreads();
 }
 
+// With `expand.packed` the kept indices are not written as they are: the rows are Qwen's block scores, and a row's list goes into its
+// packed attention row as the reference's selection does (gpu/sparse_attention.hpp:172-243, 307-395): four positions a chosen block,
+// then the positions of the row's incomplete block, then the count; a row with no more whole blocks than `keep` lists every position
+// and takes no part in the choice.
+
 // With `candidates` (a row's `blocks` block numbers in index order, -1 past the last; gpu/ops.hpp:1942-1951) the row's scores are
 // those of its candidate groups in candidate order, and a kept place v is written as the group it stands for,
 // candidates[v / block] * block + v % block: index order both ways, so the list still ascends.
 __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict__ scores, size_t groups, size_t k, int32_t* __restrict__ out,
-                                                         const int32_t* __restrict__ candidates, size_t blocks, size_t block) {
+                                                         const int32_t* __restrict__ candidates, size_t blocks, size_t block, const TopKExpand expand) {
     extern __shared__ __align__(16) uint32_t dynamic[];
     uint32_t* hist_a = dynamic;                 // the histograms of the first read and of the band's last bits
     uint32_t* hist_b = hist_a + kBins;          // the histogram between them: a block may still be reading the one before in another block
@@ -151,6 +156,31 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
     const unsigned t = threadIdx.x;
     const int32_t* mapped = candidates ? candidates + row_number * blocks : nullptr;
     const auto group_of = [&](uint32_t place) { return mapped ? int32_t(size_t(mapped[place / block]) * block + place % block) : int32_t(place); };
+    float* listed = nullptr;   // expand: the row's list in its packed row
+    if (expand.packed) {
+        const size_t position = expand.positions ? expand.positions[row_number] : expand.base + row_number, complete = (position + 1) / 4;
+        listed = expand.packed + expand.index_start + row_number * expand.selected;
+        float* count = expand.packed + expand.index_start + expand.steps * expand.selected + row_number;
+        const size_t head = size_t(expand.keep) * 4;
+        if (rank == 0) {
+            if (complete <= expand.keep) {
+                for (size_t i = threadIdx.x; i <= position; i += kThreads) listed[i] = float(i);
+                if (threadIdx.x == 0) *count = float(position + 1);
+            } else {
+                for (size_t i = threadIdx.x; complete * 4 + i <= position; i += kThreads) listed[head + i] = float(complete * 4 + i);
+                if (threadIdx.x == 0) *count = float(head + position + 1 - complete * 4);
+            }
+        }
+        if (complete <= expand.keep) return;   // (the same for every block of the row's cluster, before its first barrier)
+    }
+    // place `at` of the row's list takes the group standing at `place`
+    const auto put = [&](size_t at, uint32_t place) {
+        if (!listed) { mine[at] = group_of(place); return; }
+        const float first_position = float(size_t(place) * 4);
+        float* four = listed + 4 * at;
+        if (reinterpret_cast<uintptr_t>(four) % 16 == 0) *reinterpret_cast<float4*>(four) = make_float4(first_position, first_position + 1.0f, first_position + 2.0f, first_position + 3.0f);
+        else { four[0] = first_position; four[1] = first_position + 1.0f; four[2] = first_position + 2.0f; four[3] = first_position + 3.0f; }
+    };
     // this block's slice of the row
     const size_t slice = ((groups + ranks - 1) / ranks + 3) & ~size_t(3);
     const size_t low = min(groups, size_t(rank) * slice), high = min(groups, low + slice);
@@ -327,9 +357,10 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
             while (low < high) { const uint32_t mid = (low + high) / 2; if (list[mid] < index) low = mid + 1; else high = mid; }
             return low;
         };
-        for (uint32_t i = t; i < sure_count; i += kThreads) mine[start + i + before_in(chosen, chosen_count, sure[i])] = group_of(sure[i]);
-        for (uint32_t i = t; i < chosen_count; i += kThreads) mine[start + i + before_in(sure, sure_count, chosen[i])] = group_of(chosen[i]);
-        for (size_t i = size_t(total) + rank * kThreads + t; i < k; i += size_t(ranks) * kThreads) mine[i] = -1;
+        for (uint32_t i = t; i < sure_count; i += kThreads) put(start + i + before_in(chosen, chosen_count, sure[i]), sure[i]);
+        for (uint32_t i = t; i < chosen_count; i += kThreads) put(start + i + before_in(sure, sure_count, chosen[i]), chosen[i]);
+        if (!listed)
+            for (size_t i = size_t(total) + rank * kThreads + t; i < k; i += size_t(ranks) * kThreads) mine[i] = -1;
         if (ranks > 1) cluster_wait();   // nobody leaves while its shared memory may still be read
         return;
     }
@@ -384,11 +415,12 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
         size_t at = written + prefix_before(kept, sh, tile_kept);
         #pragma unroll
         for (int i = 0; i < kPerThread; ++i)
-            if (keep[i] && at < k) mine[at++] = group_of(uint32_t(first + i));
+            if (keep[i] && at < k) put(at++, uint32_t(first + i));
         written += tile_kept;
         ties_seen += tile_ties;
     }
-    for (size_t i = written + t; i < k; i += kThreads) mine[i] = -1;
+    if (!listed)
+        for (size_t i = written + t; i < k; i += kThreads) mine[i] = -1;
     if (ranks > 1) { cluster_arrive(); cluster_wait(); }
 }
 
@@ -397,7 +429,7 @@ __global__ void __launch_bounds__(kThreads) top_k_kernel(const float* __restrict
 // rows x groups scores -> rows x k indices (with candidates: see top_k_kernel)
 // dependent: launched as a programmatic dependent of the kernel queued before it (which issues griddepcontrol.launch_dependents)
 void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, size_t k, int32_t* out, const int32_t* candidates, size_t blocks, size_t block,
-                  bool dependent) {
+                  bool dependent, const TopKExpand* expand) {
     static bool configured[64] = {};
     if (!configured[d.ordinal & 63]) {
         SDB_CHECK(cudaFuncSetAttribute(topk::top_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(topk::kSmem)));
@@ -434,7 +466,7 @@ void launch_top_k(Device& d, const float* scores, size_t rows, size_t groups, si
         }
         if (known > 0) break;
     }
-    SDB_CHECK(cudaLaunchKernelEx(&config, topk::top_k_kernel, scores, groups, k, out, candidates, blocks, block));
+    SDB_CHECK(cudaLaunchKernelEx(&config, topk::top_k_kernel, scores, groups, k, out, candidates, blocks, block, expand ? *expand : TopKExpand{}));
     ++d.launches;
     SDB_CHECK(cudaGetLastError());
 }
@@ -459,7 +491,7 @@ int sd_op_top_k(void* handle, const float* scores, uint64_t rows, uint64_t group
         throw std::runtime_error("invalid Straydog top-k shape");
     span(value, scores, checked_product({rows, groups, 4}), "scores");
     span(value, out, checked_product({rows, k, 4}), "top-k indices");
-    launch_top_k(value, scores, size_t(rows), size_t(groups), size_t(k), out, nullptr, 0, 1, false);
+    launch_top_k(value, scores, size_t(rows), size_t(groups), size_t(k), out, nullptr, 0, 1, false, nullptr);
     SDB_OP_END
 }
 
