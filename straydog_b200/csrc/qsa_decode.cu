@@ -312,7 +312,7 @@ struct HostTables {
 // for a segment shorter than 512 tiles) and a tail that halves down to single tiles - and a chunk is never shared by two warps.
 // The chunks are dealt to the warps longest first, each to the warp with the least work so far; the halving tails are what lets
 // that come out even. A segment's partials are merged in chunk order, so a sequence's result has the same bits in any batch (the
-// reference's verification contract, docs/DESIGN.md:40-41, kept for this library's own batched decode).
+// reference's verification contract, lines 40-41 of the reference's own design notes under docs/, kept for this library's own batched decode).
 //
 // Moving cuts: the segments' tiles laid end to end and cut into equal runs, one per warp. Fewer partials (one per warp and one
 // per segment border), but where a segment is cut depends on what else is in the batch. Kept for sdx_qsa_decode_static, whose

@@ -7,7 +7,7 @@
 // gpu/core.hpp:392), the same rule for a live slot (slot < count, 0 <= position <= the row's own position, position < context:
 // :58-64), the same ring-mirror addressing (:65-68), the same optional sigmoid gate in the merge (:168).
 //
-// Contract kept bit for bit (docs/DESIGN.md:40-41, gpu/qsa_decode.hpp:46-50): a row's result does not depend on how many rows
+// Contract kept bit for bit (lines 40-41 of the reference's own design notes under docs/, gpu/qsa_decode.hpp:46-50): a row's result does not depend on how many rows
 // share the launch. The work is cut at fixed places: a chunk is 64 consecutive slots of one row, a CTA owns one (chunk, K/V
 // head, row), the merge combines a row's chunks in chunk order.
 //

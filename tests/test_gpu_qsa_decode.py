@@ -89,7 +89,7 @@ def test_ragged_batch_and_plan_replay(gpu):
 
 
 def test_a_sequence_result_does_not_depend_on_its_batch(gpu):
-    # the reference's verification contract (docs/DESIGN.md:40-41) asks a row's bits to be those of a one-token decode. With the
+    # the reference's verification contract (lines 40-41 of the reference's own design notes under docs/) asks a row's bits to be those of a one-token decode. With the
     # default moving cuts the split points move with the batch, so the value is the same to FP32 rounding; with fixed cuts
     # (sdx_decode_cuts) a sequence is cut by its own length alone and the bits are the same in any batch.
     rng = np.random.default_rng(500)
